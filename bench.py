@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized decode hot path on B200.
+
+Headline workload (one "step"): the fused-dequant GEMVs of one Qwen2.5-7B-shaped decode token
+(hidden 3584, intermediate 18944, 28 Q / 4 KV heads x 128, vocab 152064; 28 layers + lm_head),
+batch 1, f32 activations, once with Q4_K weights and once with Q4_0 weights, every matrix a
+distinct device-resident instance (8 GB of weights, far larger than L2).  Metric: achieved HBM
+GB/s on the ALGORITHMIC bytes (weights once + vectors), whole job over all ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N>1 is launched with torch.distributed.run, one rank per GPU; each rank streams its own replica of
+the weights (weak scaling, no data-path collective), timing is CUDA events + max over ranks.
+`--impl reference` times the CPU oracle (the reference's own implementation is Rust + Metal and
+cannot be built or run here) on the host cores for the same metric.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, INTER, VOCAB, LAYERS = 3584, 18944, 152064, 28
+Q_DIM, KV_DIM = 28 * 128, 4 * 128
+FMT_Q8_0, FMT_Q4_0, FMT_Q4K = 0, 1, 2
+BLOCK = {FMT_Q8_0: (32, 34), FMT_Q4_0: (32, 18), FMT_Q4K: (256, 144)}
+METRIC = "fused_dequant_gemv_hbm_gbs"
+
+
+def row_bytes(fmt, k):
+    return k // BLOCK[fmt][0] * BLOCK[fmt][1]
+
+
+def gemv_bytes(fmt, m, k, residual=False, batch=1):
+    """Algorithmic bytes of one GEMV: weights once + input + output (+ residual read)."""
+    return m * row_bytes(fmt, k) + batch * 4 * k + batch * 4 * m + (batch * 4 * m if residual else 0)
+
+
+# (name, rows, k, residual)
+LAYER_MATS = [("q", Q_DIM, HIDDEN, False), ("k", KV_DIM, HIDDEN, False), ("v", KV_DIM, HIDDEN, False),
+              ("o", HIDDEN, Q_DIM, True), ("gate", INTER, HIDDEN, False), ("up", INTER, HIDDEN, False),
+              ("down", HIDDEN, INTER, True)]
+
+
+def pass_bytes(fmt, layers=LAYERS):
+    b = sum(gemv_bytes(fmt, m, k, r) for _, m, k, r in LAYER_MATS) * layers
+    return b + gemv_bytes(fmt, VOCAB, HIDDEN)
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except Exception:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class GemvSet:
+    """Device-resident weights and scratch vectors for one weight format of the workload."""
+
+    def __init__(self, R, ctx, fmt, seed, layers=LAYERS):
+        self.R, self.ctx, self.fmt, self.layers = R, ctx, fmt, layers
+        sigma = 0.01 if fmt == FMT_Q4K else 0.02
+        self.w = []
+        for l in range(layers):
+            d = {}
+            for i, (name, m, k, _) in enumerate(LAYER_MATS):
+                buf = ctx.new_buffer(m * row_bytes(fmt, k))
+                R.fill_weights(ctx, fmt, buf, m * (k // BLOCK[fmt][0]), seed * 100003 + l * 16 + i, sigma)
+                d[name] = buf
+            self.w.append(d)
+        self.lm_head = ctx.new_buffer(VOCAB * row_bytes(fmt, HIDDEN))
+        R.fill_weights(ctx, fmt, self.lm_head, VOCAB * (HIDDEN // BLOCK[fmt][0]), seed * 100003 + 99991, sigma)
+        f4 = lambda n: ctx.new_buffer(4 * n)
+        self.x, self.xn, self.q, self.kk, self.v = f4(HIDDEN), f4(HIDDEN), f4(Q_DIM), f4(KV_DIM), f4(KV_DIM)
+        self.gate, self.up, self.act, self.logits = f4(INTER), f4(INTER), f4(INTER), f4(VOCAB)
+        R.fill_normal_f32(ctx, self.xn, HIDDEN, seed + 7, 1.0)
+        R.fill_normal_f32(ctx, self.q, Q_DIM, seed + 8, 1.0)
+        R.fill_normal_f32(ctx, self.act, INTER, seed + 9, 1.0)
+        ctx.call("memset", self.x, 0, 4 * HIDDEN)
+        ctx.flush()
+
+    def run(self):
+        """All GEMVs of one decode token, issued through the reference-shaped operator calls.  The
+        activations that RMSNorm / attention would produce are fixed synthetic vectors: only the
+        GEMV family is on this benchmark's path."""
+        R, ctx, f = self.R, self.ctx, self.fmt
+        n = {FMT_Q4_0: "q4_0", FMT_Q4K: "q4k", FMT_Q8_0: "q8_0"}[f]
+        gemv = getattr(R, "gemv_%s_f32in_f32out" % n)
+        gemv_add = getattr(R, "gemv_%s_add_f32_f32in" % n)
+        for w in self.w:
+            gemv(ctx, w["q"], self.xn, self.q, Q_DIM, HIDDEN)
+            gemv(ctx, w["k"], self.xn, self.kk, KV_DIM, HIDDEN)
+            gemv(ctx, w["v"], self.xn, self.v, KV_DIM, HIDDEN)
+            gemv_add(ctx, w["o"], self.q, self.x, self.x, HIDDEN, Q_DIM)
+            if f == FMT_Q4_0:   # the engine's fused gate+up+SiLU for Q4_0 (forward.rs:1687-1690)
+                R.fused_ffn_q4_0_f32(ctx, w["gate"], w["up"], self.xn, self.act, INTER, HIDDEN)
+            else:               # Q4_K has no fused FFN in the reference: 2 GEMVs (forward.rs:1696-1699)
+                gemv(ctx, w["gate"], self.xn, self.gate, INTER, HIDDEN)
+                gemv(ctx, w["up"], self.xn, self.up, INTER, HIDDEN)
+            gemv_add(ctx, w["down"], self.act, self.x, self.x, HIDDEN, INTER)
+        gemv(ctx, self.lm_head, self.xn, self.logits, VOCAB, HIDDEN)
+
+
+def cpu_sample(fmt_list, threads, repeats, layers_sample=2, log=None):
+    """Oracle GEMV (engine CPU dequant formulas + f32 dot, OpenMP over rows) on a bounded sample of
+    the workload: `layers_sample` layers + lm_head per format.  Returns (GB/s, seconds, description)."""
+    import oracle as O
+    O.build_oracle()
+    if threads:
+        O.set_num_threads(threads)
+    rng = np.random.default_rng(1002)
+    total_bytes, total_t = 0, 0.0
+    for fmt in fmt_list:
+        mats = [(m, k) for _, m, k, _ in LAYER_MATS] * layers_sample + [(VOCAB, HIDDEN)]
+        ws = {}
+        for m, k in set(mats):
+            # random bytes with a valid f16 scale in each block (content does not affect CPU time)
+            rb = row_bytes(fmt, k)
+            w = rng.integers(0, 256, (m, rb), dtype=np.uint8)
+            bb = BLOCK[fmt][1]
+            w.reshape(m, -1, bb)[:, :, 1] = 0x1C   # d ~ 2^-8: finite, small
+            if fmt == FMT_Q4K:
+                w.reshape(m, -1, bb)[:, :, 3] = 0x1C
+            ws[(m, k)] = w
+        xs = {k: rng.normal(0, 1, k).astype(np.float32) for k in (HIDDEN, INTER)}
+        for _ in range(repeats):
+            for m, k in mats:
+                t0 = time.perf_counter()
+                O.gemv(fmt, ws[(m, k)], xs[k], m, k, O.TIER_DEQUANT)
+                total_t += time.perf_counter() - t0
+                total_bytes += gemv_bytes(fmt, m, k)
+    desc = "%d layer(s) + lm_head of the workload per format x %d repeat(s), formats %s" % (
+        layers_sample, repeats, [{1: "Q4_0", 2: "Q4_K"}[f] for f in fmt_list])
+    return total_bytes / total_t / 1e9, total_t, desc, O.num_threads()
+
+
+def run_reference(args):
+    """--impl reference: the CPU arm.  The reference's own code for this path is Rust + Apple Metal
+    (no toolchain, no Metal here), so the timed implementation is the oracle port of its CPU formulas."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    vals = []
+    # calibrate so that K+W steps stay within a few minutes: one step = 1 layer + lm_head per format
+    for i in range(args.warmup + args.steps):
+        gbs, t, desc, threads = cpu_sample([FMT_Q4K, FMT_Q4_0], cores, 1, layers_sample=1)
+        if i >= args.warmup:
+            vals.append((gbs, t))
+    v = float(np.mean([g for g, _ in vals]))
+    ms = float(np.mean([t for _, t in vals]) * 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "qwen2.5-7b decode GEMV set, Q4_K + Q4_0, batch 1 (CPU: bounded sample per step)",
+                   "l2": "inputs larger than any cache"},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the workload (default: the full 28)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--tune", default="", help="key=value[,key=value] kernel tuning knobs (experiments)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    import runit_mac_b200 as R
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.current_stream()
+    ctx = R.Context(local, stream=stream.cuda_stream)   # kernels and torch events share this stream
+    for kv in filter(None, args.tune.split(",")):
+        k, v = kv.split("=")
+        ctx.set_tuning(k, int(v))
+
+    sets = [GemvSet(R, ctx, FMT_Q4K, 1002 + rank, args.layers), GemvSet(R, ctx, FMT_Q4_0, 2002 + rank, args.layers)]
+    bytes_fmt = [pass_bytes(s.fmt, args.layers) for s in sets]
+    step_bytes = sum(bytes_fmt)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        for s in sets:
+            s.run()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ── timed region: inputs resident in HBM ──
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 + 2 * len(sets))]
+    l0 = ctx.launches
+    barrier()
+    ev[0].record(stream)
+    fmt_ms = [0.0] * len(sets)
+    sub = [[torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for _ in range(args.steps * len(sets))]
+    for i in range(args.steps):
+        for j, s in enumerate(sets):
+            a, b = sub[i * len(sets) + j]
+            a.record(stream)
+            s.run()
+            b.record(stream)
+    ev[1].record(stream)
+    barrier()
+    launches = ctx.launches - l0
+    ms = ev[0].elapsed_time(ev[1])
+    for i in range(args.steps):
+        for j in range(len(sets)):
+            a, b = sub[i * len(sets) + j]
+            fmt_ms[j] += a.elapsed_time(b)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * step_bytes * args.steps / (ms_max * 1e-3) / 1e9
+
+    # ── end to end through the public call with HOST buffers: x from pinned memory in, logits out ──
+    hx = torch.randn(HIDDEN, dtype=torch.float32).pin_memory()
+    hlogits = torch.empty(VOCAB, dtype=torch.float32).pin_memory()
+    lib, h = ctx.lib, ctx.handle
+
+    def e2e_step():
+        for s in sets:
+            lib.runit_memcpy_h2d(h, s.xn.ptr, hx.data_ptr(), 4 * HIDDEN)
+            s.run()
+            lib.runit_memcpy_d2h(h, hlogits.data_ptr(), s.logits.ptr, 4 * VOCAB)
+            ctx.flush()   # the caller reads the logits before the next token
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * step_bytes * args.steps / (float(t.item()) * 1e-3) / 1e9
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        # dominant kernel: the Q4_K staged GEMV; its launches = the Q4_K sub-pass (8 per layer incl. one
+        # tiny silu-free set: 7 GEMVs per layer + lm_head)
+        q4k_launches = args.layers * 7 + 1
+        q4k_ms = fmt_ms[0] / args.steps
+        achieved = bytes_fmt[0] / (q4k_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen2.5-7b decode GEMV set (28 layers q,k,v,o,gate,up,down + lm_head), Q4_K pass + Q4_0 pass, "
+                                   "batch 1, f32 activations",
+                       "layers": args.layers, "bytes_per_step": step_bytes,
+                       "l2": "inputs larger than L2: every matrix is a distinct instance, %.1f GB streamed per step" % (step_bytes / 1e9)},
+            "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K,batch 1>", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "bytes_per_launch": bytes_fmt[0] / q4k_launches, "launches_per_step": q4k_launches,
+                         "avg_launch_us": q4k_ms * 1e3 / q4k_launches},
+            "per_format": {"q4k_gbs": achieved, "q4_0_gbs": bytes_fmt[1] / (fmt_ms[1] / args.steps * 1e-3) / 1e9},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * 4 * HIDDEN, "d2h_bytes_per_step": 2 * 4 * VOCAB},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if not args.no_cpu and world == 1:
+            gbs, tsec, desc, threads = cpu_sample([FMT_Q4K, FMT_Q4_0], os.cpu_count() or 1, 2, layers_sample=2)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc,
+                                    "seconds": tsec}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,166 @@
+/*
+ * runit_cuda.h — C ABI of the B200 (sm_100a) implementation of RunIT's quantized decode path.
+ *
+ * Every "twin" entry point replaces one free function of the reference's dispatch layer
+ * (crates/kernels/src/dispatch.rs, cited per function as dispatch.rs:LINE; paths are relative
+ * to the reference project root).  Names are the reference's, prefixed `runit_`; the argument
+ * order is the reference's with `&MetalContext` -> `runit_ctx_t*`, `&metal::Buffer` -> device
+ * pointer, `u32` -> uint32_t, `Result<()>` -> int32_t status.
+ *
+ * Execution model (replaces MetalContext::encode / flush, crates/kernels/src/context.rs:248-296):
+ * every op is an in-order launch on the context's CUDA stream and returns at once;
+ * runit_flush() waits for the stream and returns the first error since the last flush.
+ * Ops never allocate, never synchronise and never retain pointers; the caller keeps buffers
+ * alive until the next flush.  `output == residual` aliasing is allowed (the engine relies on
+ * it, crates/engine/src/forward.rs:1619).  Arguments are validated on the host: a bad call
+ * returns a status and launches nothing.
+ *
+ * There is no CPU fallback: without a CUDA device runit_ctx_create fails with
+ * RUNIT_ERR_NO_DEVICE.  A context is used by one host thread at a time (the reference's
+ * MetalContext is !Sync, context.rs:158).
+ *
+ * Weight layouts (row-major rows of blocks, as the reference lays them out):
+ *   Q8_0: 34-byte blocks {f16 d; i8 qs[32]}, value = d*qs            gemv_q8_0.metal:11-14
+ *   Q4_0: 18-byte blocks {f16 d; u8 qs[16]}, low nibble = element 2i, high = 2i+1,
+ *         value = d*(nibble-8)                                        gemv_q4_0.metal:10-15
+ *   Q4_K: 144-byte superblocks {f16 d; f16 dmin; u8 scales[12]; u8 qs[128]} of 256 elements;
+ *         pair j: low nibbles of qs[32j..] -> elements 64j.., scale index j; high nibbles ->
+ *         elements 64j+32.., scale index j+4                          dequant.metal:74-82
+ * Alignment contract: weight base pointers 16-byte aligned (cudaMalloc gives 256); vectors
+ * 16-byte aligned; k a multiple of 32 (Q8_0, Q4_0) or 256 (Q4_K).
+ */
+#ifndef RUNIT_CUDA_H
+#define RUNIT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct runit_ctx runit_ctx_t;
+
+/* Status codes; the Rust shim maps them onto KernelError (crates/kernels/src/error.rs:4-22). */
+enum {
+    RUNIT_OK = 0,
+    RUNIT_ERR_NO_DEVICE = 1,   /* KernelError::NoDevice */
+    RUNIT_ERR_BAD_ARG = 2,     /* null pointer, k not a block multiple, zero rows, ... */
+    RUNIT_ERR_BUFFER_SIZE = 3, /* KernelError::BufferSize */
+    RUNIT_ERR_LAUNCH = 4,      /* a CUDA call failed; text in runit_last_error_string */
+    RUNIT_ERR_NCCL = 5,
+    RUNIT_ERR_TIMEOUT = 6,     /* a bounded device- or host-side wait ran out */
+    RUNIT_ERR_UNSUPPORTED = 7,
+    RUNIT_ERR_ALLOC = 8
+};
+
+enum { RUNIT_BUF_DEVICE = 0, RUNIT_BUF_HOST_VISIBLE = 1 };
+enum { RUNIT_FMT_Q8_0 = 0, RUNIT_FMT_Q4_0 = 1, RUNIT_FMT_Q4K = 2 };
+
+/* ── context, buffers, flush: MetalContext::{new,new_buffer,flush}, context.rs:163-296 ── */
+int32_t runit_ctx_create(int32_t device, runit_ctx_t** out);
+/* Adopt a stream the caller owns (e.g. the stream a collective library runs on). */
+int32_t runit_ctx_create_on_stream(int32_t device, void* cuda_stream, runit_ctx_t** out);
+int32_t runit_ctx_destroy(runit_ctx_t* ctx);
+void*   runit_ctx_stream(runit_ctx_t* ctx);
+int32_t runit_flush(runit_ctx_t* ctx);
+const char* runit_last_error_string(runit_ctx_t* ctx);
+const char* runit_status_string(int32_t status);
+int32_t runit_buf_alloc(runit_ctx_t* ctx, size_t bytes, int32_t flags, void** dptr);
+int32_t runit_buf_free(runit_ctx_t* ctx, void* dptr);
+int32_t runit_memcpy_h2d(runit_ctx_t* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int32_t runit_memcpy_d2h(runit_ctx_t* ctx, void* dst_host, const void* src_dev, size_t bytes);
+int32_t runit_memset(runit_ctx_t* ctx, void* dst_dev, int32_t byte, size_t bytes);
+/* Per-op launch counter (kernels launched by this context since creation). */
+uint64_t runit_launch_count(runit_ctx_t* ctx);
+/* Kernel tuning knob for experiments: 0 = default.  See DESIGN notes in gemv.cu. */
+int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value);
+
+/* ── Q8_0 fused-dequant GEMV family ── */
+/* dispatch.rs:1280  y_f32[m] = W_q8_0[m,k] . x_f32[k] */
+int32_t runit_gemv_q8_0_f32in_f32out(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1298  y_f32 = W.x_f32 + residual_f32 (output may alias residual) */
+int32_t runit_gemv_q8_0_add_f32_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:1317  y_f16 = W.x_f32 */
+int32_t runit_gemv_q8_0_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1335  y_f16 = W.x_f16 */
+int32_t runit_gemv_q8_0_f16(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1353  y_f16 = W.x_f16 + residual_f16 */
+int32_t runit_gemv_q8_0_add_f16(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:1372  y_f32 = W.x_f16 + residual_f32 */
+int32_t runit_gemv_q8_0_add_f32res_f16(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:1083,1101 (4 rows per threadgroup) and dispatch.rs:1397,1414,1432 (256-wide):
+ * launch-shape variants of the same operators; here they are the same kernel. */
+int32_t runit_gemv_q8_0_f32in_f32out_mr(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+int32_t runit_gemv_q8_0_add_f32_f32in_mr(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+int32_t runit_gemv_q8_0_f32in_f32out_wide(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+int32_t runit_gemv_q8_0_add_f32_f32in_wide(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+int32_t runit_gemv_q8_0_f32in_wide(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:813  Q|K|V rows in one launch, f32 in/out */
+int32_t runit_fused_qkv_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
+                                 void* out_q, void* out_k, void* out_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+/* dispatch.rs:842  same + f16 bias per row (the reference uploads biases as f16) */
+int32_t runit_fused_qkv_bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
+                                      void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,
+                                      const void* bias_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+/* dispatch.rs:903  act_f32[ff] = silu(Wg.x) * (Wu.x) */
+int32_t runit_fused_ffn_q8_0_f32(runit_ctx_t*, const void* w_gate, const void* w_up, const void* x_vec, void* act_out, uint32_t ff_dim, uint32_t k);
+
+/* ── Q4_0 ── */
+/* dispatch.rs:1456 */
+int32_t runit_gemv_q4_0_f32in_f32out(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1471 */
+int32_t runit_gemv_q4_0_add_f32_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:1486  f32 in, f16 out */
+int32_t runit_gemv_q4_0_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1501  f16 in, f16 out */
+int32_t runit_gemv_q4_0_f16(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1516  f16 in, f16 out + f16 residual */
+int32_t runit_gemv_q4_0_add_f16(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:1531 */
+int32_t runit_fused_ffn_q4_0_f32(runit_ctx_t*, const void* w_gate, const void* w_up, const void* x_vec, void* act_out, uint32_t ff_dim, uint32_t k);
+
+/* ── Q4_K ── */
+/* dispatch.rs:1229 */
+int32_t runit_gemv_q4k_f32in_f32out(runit_ctx_t*, const void* weight_q4k, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:1251 */
+int32_t runit_gemv_q4k_add_f32_f32in(runit_ctx_t*, const void* weight_q4k, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:621  f16 in, f16 out */
+int32_t runit_gemv_q4k_f16(runit_ctx_t*, const void* weight_q4k, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:585  f16 in, f16 out + f16 residual */
+int32_t runit_gemv_q4k_add_f16(runit_ctx_t*, const void* weight_q4k, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:358  f16 in, f32 out + f32 residual */
+int32_t runit_gemv_q4k_add_f32res_f16(runit_ctx_t*, const void* weight_q4k, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+/* dispatch.rs:756  Q4_K blocks -> f16 elements */
+int32_t runit_dequant_q4k_f16(runit_ctx_t*, const void* input, void* output, uint32_t n_blocks);
+
+/* ── MoE glue and router ── */
+/* dispatch.rs:270  y_f16[m] = W_f16[m,k] . x_f32[k]  (router logits) */
+int32_t runit_gemv_f16w_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+/* dispatch.rs:15 / dispatch.rs:35 */
+int32_t runit_silu_mul_f16(runit_ctx_t*, const void* gate, const void* up, void* out, uint32_t n);
+int32_t runit_silu_mul_f32(runit_ctx_t*, const void* gate, const void* up, void* out, uint32_t n);
+/* dispatch.rs:1639  acc_f16 += half(float(src_f16) * weight) */
+int32_t runit_scale_accumulate_f16(runit_ctx_t*, const void* src, void* acc, float weight, uint32_t n);
+/* dispatch.rs:316  acc_f32 += float(src_f16) */
+int32_t runit_add_f16_into_f32(runit_ctx_t*, const void* src, void* acc, uint32_t n);
+
+/* ── entry points with no twin in the reference ── */
+/* Batched fused-dequant GEMV: x [batch][k] f32, y [batch][m] f32 (+ residual [batch][m], may be
+ * NULL); weights streamed once for the whole batch; batch in 1..8. */
+int32_t runit_gemv_batched_f32(runit_ctx_t*, int32_t fmt, const void* weight, const void* input, void* output,
+                               const void* residual, uint32_t m, uint32_t k, uint32_t batch);
+/* Fused Q|K|V with an f32 bias (the benchmark configuration states an f32 bias); bias may be NULL. */
+int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
+                                         void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,
+                                         const void* bias_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+/* Synthetic weights written on the device (benchmark / test data, distributions of the
+ * benchmark configurations): n_blocks blocks of the format from a counter-based generator. */
+int32_t runit_fill_weights(runit_ctx_t*, int32_t fmt, void* dst, uint64_t n_blocks, uint64_t seed, float sigma);
+/* N(0, sigma) f32 values from the same generator. */
+int32_t runit_fill_normal_f32(runit_ctx_t*, void* dst, uint64_t n, uint64_t seed, float sigma);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,242 @@
+// Host side of the fused-dequant GEMV family: argument validation, kernel selection and
+// the extern "C" twins of the reference's dispatch functions (crates/kernels/src/dispatch.rs).
+//
+// Kernel selection mirrors WeightBuf's role in the reference (crates/engine/src/forward.rs:84-248):
+// one operator per (weight format, input dtype, output dtype, residual) combination.  Here
+// every combination is an epilogue/prologue flag of one streaming kernel per format.
+#include "gemv_launch.cuh"
+
+namespace runit {
+
+struct GemvCall {
+    int fmt = 0;
+    const void* w[3] = {nullptr, nullptr, nullptr};
+    const void* w2 = nullptr;          // fused gate/up: second matrix
+    void* y[3] = {nullptr, nullptr, nullptr};
+    const void* res[3] = {nullptr, nullptr, nullptr};
+    const void* bias[3] = {nullptr, nullptr, nullptr};
+    uint32_t rows[3] = {0, 0, 0};
+    int nseg = 1;
+    const void* x = nullptr;
+    uint32_t k = 0, batch = 1;
+    bool x_f16 = false, out_f16 = false;
+    int res_kind = RES_NONE, bias_kind = BIAS_NONE;
+    bool dual = false;
+    const char* name = "gemv";
+};
+
+static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    const char* nm = c.name;
+    RUNIT_REQUIRE(ctx, c.fmt >= 0 && c.fmt <= 2, "%s: unknown weight format %d", nm, c.fmt);
+    const uint32_t be = (uint32_t)runit_block_elems(c.fmt);
+    RUNIT_REQUIRE(ctx, c.k > 0 && c.k % be == 0, "%s: k=%u is not a positive multiple of %u", nm, c.k, be);
+    RUNIT_REQUIRE(ctx, c.k <= (1u << 24), "%s: k=%u exceeds 2^24", nm, c.k);
+    RUNIT_REQUIRE(ctx, c.batch >= 1 && c.batch <= 8, "%s: batch=%u not in 1..8", nm, c.batch);
+    RUNIT_REQUIRE(ctx, c.x && runit_aligned(c.x, 16), "%s: input null or not 16-byte aligned", nm);
+    RUNIT_REQUIRE(ctx, !c.dual || c.nseg == 1, "%s: fused gate/up takes one segment", nm);
+    RUNIT_REQUIRE(ctx, c.nseg == 1 || c.batch == 1, "%s: multi-segment launch is batch 1", nm);
+
+    GemvArgs a;
+    memset(&a, 0, sizeof(a));
+    a.nseg = c.nseg;
+    a.x = c.x;
+    a.k = c.k;
+    a.nb = c.k / be;
+    a.row_bytes = (uint32_t)runit_row_bytes(c.fmt, c.k);
+    a.out_f16 = c.out_f16;
+    a.res_kind = c.res_kind;
+    a.bias_kind = c.bias_kind;
+    a.dual = c.dual;
+
+    uint32_t tiles = 0, total_rows = 0;
+    const uint32_t rpt = c.dual ? kRT / 2 : kRT;
+    bool w_align4 = (a.row_bytes % 4) == 0, w_align8 = (a.row_bytes % 8) == 0, w_align16 = (a.row_bytes % 16) == 0;
+    for (int i = 0; i < c.nseg; i++) {
+        RUNIT_REQUIRE(ctx, c.rows[i] > 0, "%s: segment %d has zero rows", nm, i);
+        RUNIT_REQUIRE(ctx, c.rows[i] <= (1u << 28), "%s: segment %d has too many rows", nm, i);
+        RUNIT_REQUIRE(ctx, c.w[i] && c.y[i], "%s: null weight or output pointer", nm);
+        RUNIT_REQUIRE(ctx, runit_aligned(c.w[i], 16), "%s: weight pointer not 16-byte aligned", nm);
+        RUNIT_REQUIRE(ctx, runit_aligned(c.y[i], 4), "%s: output pointer misaligned", nm);
+        RUNIT_REQUIRE(ctx, c.res_kind == RES_NONE || c.res[i], "%s: null residual", nm);
+        RUNIT_REQUIRE(ctx, c.bias_kind == BIAS_NONE || c.bias[i], "%s: null bias", nm);
+        a.seg[i].w = (const uint8_t*)c.w[i];
+        a.seg[i].w2 = (const uint8_t*)c.w2;
+        a.seg[i].y = c.y[i];
+        a.seg[i].res = c.res[i];
+        a.seg[i].bias = c.bias[i];
+        a.seg[i].rows = c.rows[i];
+        a.seg[i].tile_begin = tiles;
+        tiles += (c.rows[i] + rpt - 1) / rpt;
+        total_rows += c.rows[i];
+    }
+    if (c.dual) RUNIT_REQUIRE(ctx, c.w2 && runit_aligned(c.w2, 16), "%s: null or misaligned second weight", nm);
+    a.ldy = c.rows[0];
+
+    const bool staged_ok = (c.fmt == RUNIT_FMT_Q8_0) ? w_align4 : w_align16;
+    const bool simple = ctx->tune.gemv_variant == 1 || !staged_ok;
+    const int cpb = w_align16 ? 16 : (w_align8 ? 8 : 4);
+    const uint32_t bpu = c.fmt == RUNIT_FMT_Q8_0 ? Traits<RUNIT_FMT_Q8_0>::BPU
+                         : c.fmt == RUNIT_FMT_Q4_0 ? Traits<RUNIT_FMT_Q4_0>::BPU : Traits<RUNIT_FMT_Q4K>::BPU;
+    a.n_units = (a.nb + bpu - 1) / bpu;
+    a.n_stages = (a.n_units + kKS - 1) / kKS;
+    switch (c.fmt) {
+        case RUNIT_FMT_Q8_0: return gemv_launch_q8_0(ctx, a, tiles, total_rows, cpb, c.batch, c.x_f16, simple, nm);
+        case RUNIT_FMT_Q4_0: return gemv_launch_q4_0(ctx, a, tiles, total_rows, cpb, c.batch, c.x_f16, simple, nm);
+        default: return gemv_launch_q4k(ctx, a, tiles, total_rows, cpb, c.batch, c.x_f16, simple, nm);
+    }
+}
+
+// Plain single-matrix call shared by the twins below.
+static int32_t gemv1(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res,
+                     uint32_t m, uint32_t k, bool x_f16, bool out_f16, int res_kind) {
+    GemvCall c;
+    c.name = name;
+    c.fmt = fmt;
+    c.w[0] = w;
+    c.x = x;
+    c.y[0] = y;
+    c.res[0] = res;
+    c.rows[0] = m;
+    c.k = k;
+    c.x_f16 = x_f16;
+    c.out_f16 = out_f16;
+    c.res_kind = res_kind;
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, m > 0, "%s: m == 0", name);
+    return gemv_dispatch(ctx, c);
+}
+
+static int32_t fused_qkv(runit_ctx* ctx, const char* name, int fmt, const void* wq, const void* wk, const void* wv,
+                         const void* x, void* oq, void* ok, void* ov, const void* bq, const void* bk, const void* bv,
+                         int bias_kind, uint32_t q_dim, uint32_t kv_dim, uint32_t k) {
+    GemvCall c;
+    c.name = name;
+    c.fmt = fmt;
+    c.nseg = 3;
+    c.w[0] = wq; c.w[1] = wk; c.w[2] = wv;
+    c.y[0] = oq; c.y[1] = ok; c.y[2] = ov;
+    c.bias[0] = bq; c.bias[1] = bk; c.bias[2] = bv;
+    c.rows[0] = q_dim; c.rows[1] = kv_dim; c.rows[2] = kv_dim;
+    c.x = x;
+    c.k = k;
+    c.bias_kind = bias_kind;
+    return gemv_dispatch(ctx, c);
+}
+
+static int32_t fused_ffn(runit_ctx* ctx, const char* name, int fmt, const void* wg, const void* wu, const void* x,
+                         void* act, uint32_t ff, uint32_t k) {
+    GemvCall c;
+    c.name = name;
+    c.fmt = fmt;
+    c.w[0] = wg;
+    c.w2 = wu;
+    c.y[0] = act;
+    c.rows[0] = ff;
+    c.x = x;
+    c.k = k;
+    c.dual = true;
+    return gemv_dispatch(ctx, c);
+}
+
+}  // namespace runit
+
+using namespace runit;
+
+extern "C" {
+
+#define GEMV_TWIN(NAME, FMT, XF16, OF16)                                                                     \
+    int32_t runit_##NAME(runit_ctx_t* ctx, const void* w, const void* x, void* y, uint32_t m, uint32_t k) { \
+        return gemv1(ctx, #NAME, FMT, w, x, y, nullptr, m, k, XF16, OF16, RES_NONE);                         \
+    }
+#define GEMV_TWIN_RES(NAME, FMT, XF16, OF16, RES)                                                            \
+    int32_t runit_##NAME(runit_ctx_t* ctx, const void* w, const void* x, void* y, const void* r, uint32_t m, \
+                         uint32_t k) {                                                                       \
+        return gemv1(ctx, #NAME, FMT, w, x, y, r, m, k, XF16, OF16, RES);                                    \
+    }
+
+// Q8_0: crates/kernels/shaders/gemv_q8_0.metal:56-240
+GEMV_TWIN(gemv_q8_0_f32in_f32out, RUNIT_FMT_Q8_0, false, false)
+GEMV_TWIN_RES(gemv_q8_0_add_f32_f32in, RUNIT_FMT_Q8_0, false, false, RES_F32)
+GEMV_TWIN(gemv_q8_0_f32in, RUNIT_FMT_Q8_0, false, true)
+GEMV_TWIN(gemv_q8_0_f16, RUNIT_FMT_Q8_0, true, true)
+GEMV_TWIN_RES(gemv_q8_0_add_f16, RUNIT_FMT_Q8_0, true, true, RES_F16)
+GEMV_TWIN_RES(gemv_q8_0_add_f32res_f16, RUNIT_FMT_Q8_0, true, false, RES_F32)
+// launch-shape variants: gemv_multirow.metal:163-243, gemv_q8_0_wide.metal:28-163
+GEMV_TWIN(gemv_q8_0_f32in_f32out_mr, RUNIT_FMT_Q8_0, false, false)
+GEMV_TWIN_RES(gemv_q8_0_add_f32_f32in_mr, RUNIT_FMT_Q8_0, false, false, RES_F32)
+GEMV_TWIN(gemv_q8_0_f32in_f32out_wide, RUNIT_FMT_Q8_0, false, false)
+GEMV_TWIN_RES(gemv_q8_0_add_f32_f32in_wide, RUNIT_FMT_Q8_0, false, false, RES_F32)
+GEMV_TWIN(gemv_q8_0_f32in_wide, RUNIT_FMT_Q8_0, false, true)
+// Q4_0: crates/kernels/shaders/gemv_q4_0.metal:75-246
+GEMV_TWIN(gemv_q4_0_f32in_f32out, RUNIT_FMT_Q4_0, false, false)
+GEMV_TWIN_RES(gemv_q4_0_add_f32_f32in, RUNIT_FMT_Q4_0, false, false, RES_F32)
+GEMV_TWIN(gemv_q4_0_f32in, RUNIT_FMT_Q4_0, false, true)
+GEMV_TWIN(gemv_q4_0_f16, RUNIT_FMT_Q4_0, true, true)
+GEMV_TWIN_RES(gemv_q4_0_add_f16, RUNIT_FMT_Q4_0, true, true, RES_F16)
+// Q4_K: crates/kernels/shaders/gemv_q4k.metal:126-271
+GEMV_TWIN(gemv_q4k_f32in_f32out, RUNIT_FMT_Q4K, false, false)
+GEMV_TWIN_RES(gemv_q4k_add_f32_f32in, RUNIT_FMT_Q4K, false, false, RES_F32)
+GEMV_TWIN(gemv_q4k_f16, RUNIT_FMT_Q4K, true, true)
+GEMV_TWIN_RES(gemv_q4k_add_f16, RUNIT_FMT_Q4K, true, true, RES_F16)
+GEMV_TWIN_RES(gemv_q4k_add_f32res_f16, RUNIT_FMT_Q4K, true, false, RES_F32)
+
+// crates/kernels/shaders/fused_qkv.metal:13-119
+int32_t runit_fused_qkv_q8_0_f32(runit_ctx_t* ctx, const void* w_q, const void* w_k, const void* w_v, const void* x,
+                                 void* out_q, void* out_k, void* out_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k) {
+    return fused_qkv(ctx, "fused_qkv_q8_0_f32", RUNIT_FMT_Q8_0, w_q, w_k, w_v, x, out_q, out_k, out_v, nullptr, nullptr,
+                     nullptr, BIAS_NONE, q_dim, kv_dim, k);
+}
+int32_t runit_fused_qkv_bias_q8_0_f32(runit_ctx_t* ctx, const void* w_q, const void* w_k, const void* w_v, const void* x,
+                                      void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,
+                                      const void* bias_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k) {
+    return fused_qkv(ctx, "fused_qkv_bias_q8_0_f32", RUNIT_FMT_Q8_0, w_q, w_k, w_v, x, out_q, out_k, out_v, bias_q, bias_k,
+                     bias_v, BIAS_F16, q_dim, kv_dim, k);
+}
+int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t* ctx, const void* w_q, const void* w_k, const void* w_v,
+                                         const void* x, void* out_q, void* out_k, void* out_v, const void* bias_q,
+                                         const void* bias_k, const void* bias_v, uint32_t q_dim, uint32_t kv_dim,
+                                         uint32_t k) {
+    const bool has_bias = bias_q || bias_k || bias_v;
+    return fused_qkv(ctx, "fused_qkv_f32bias_q8_0_f32", RUNIT_FMT_Q8_0, w_q, w_k, w_v, x, out_q, out_k, out_v, bias_q,
+                     bias_k, bias_v, has_bias ? BIAS_F32 : BIAS_NONE, q_dim, kv_dim, k);
+}
+// crates/kernels/shaders/fused_ffn.metal:36-93 and gemv_q4_0.metal:254-311
+int32_t runit_fused_ffn_q8_0_f32(runit_ctx_t* ctx, const void* w_gate, const void* w_up, const void* x, void* act_out,
+                                 uint32_t ff_dim, uint32_t k) {
+    return fused_ffn(ctx, "fused_ffn_q8_0_f32", RUNIT_FMT_Q8_0, w_gate, w_up, x, act_out, ff_dim, k);
+}
+int32_t runit_fused_ffn_q4_0_f32(runit_ctx_t* ctx, const void* w_gate, const void* w_up, const void* x, void* act_out,
+                                 uint32_t ff_dim, uint32_t k) {
+    return fused_ffn(ctx, "fused_ffn_q4_0_f32", RUNIT_FMT_Q4_0, w_gate, w_up, x, act_out, ff_dim, k);
+}
+
+int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* input, void* output,
+                               const void* residual, uint32_t m, uint32_t k, uint32_t batch) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, batch >= 1 && batch <= 8, "gemv_batched_f32: batch=%u not in 1..8", batch);
+    RUNIT_REQUIRE(ctx, m > 0, "gemv_batched_f32: m == 0");
+    // Kernels exist for batch 1, 2, 4, 8; other sizes run as a sum of those.
+    uint32_t done = 0;
+    while (done < batch) {
+        const uint32_t left = batch - done;
+        const uint32_t b = left >= 8 ? 8 : left >= 4 ? 4 : left >= 2 ? 2 : 1;
+        GemvCall c;
+        c.name = "gemv_batched_f32";
+        c.fmt = fmt;
+        c.w[0] = weight;
+        c.x = (const float*)input + (size_t)done * k;
+        c.y[0] = (float*)output + (size_t)done * m;
+        c.res[0] = residual ? (const float*)residual + (size_t)done * m : nullptr;
+        c.res_kind = residual ? RES_F32 : RES_NONE;
+        c.rows[0] = m;
+        c.k = k;
+        c.batch = b;
+        int32_t st = gemv_dispatch(ctx, c);
+        if (st != RUNIT_OK) return st;
+        done += b;
+    }
+    return RUNIT_OK;
+}
+
+}  // extern "C"

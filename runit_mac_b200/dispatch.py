@@ -1,0 +1,206 @@
+"""Host-side mirror of the reference's kernel dispatch layer over the C ABI.
+
+The reference exposes free functions ``op(ctx: &MetalContext, buffers..., dims...) -> Result<()>``
+(crates/kernels/src/dispatch.rs) and a ``MetalContext`` with ``new_buffer`` / ``flush``
+(crates/kernels/src/context.rs:163-296).  This module keeps those names and argument orders:
+``Context`` replaces ``MetalContext``, ``DeviceBuffer`` replaces ``metal::Buffer``, a failed call
+raises ``KernelError`` (crates/kernels/src/error.rs:4-22) instead of returning ``Err``.
+
+Every function here forwards to the ``extern "C"`` symbol of the same name prefixed ``runit_``;
+nothing is computed in Python.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+
+OK = 0
+ERR_NO_DEVICE, ERR_BAD_ARG, ERR_BUFFER_SIZE, ERR_LAUNCH, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_ALLOC = range(1, 9)
+FMT_Q8_0, FMT_Q4_0, FMT_Q4K = 0, 1, 2
+BUF_DEVICE, BUF_HOST_VISIBLE = 0, 1
+
+BLOCK_ELEMS = {FMT_Q8_0: 32, FMT_Q4_0: 32, FMT_Q4K: 256}     # dispatch.rs:735-747
+BLOCK_BYTES = {FMT_Q8_0: 34, FMT_Q4_0: 18, FMT_Q4K: 144}
+
+
+def row_bytes(fmt: int, k: int) -> int:
+    return k // BLOCK_ELEMS[fmt] * BLOCK_BYTES[fmt]
+
+
+class KernelError(RuntimeError):
+    """Mirror of KernelError (crates/kernels/src/error.rs:4-22); ``status`` is the C status code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class DeviceBuffer:
+    """Device memory owned by a Context (replaces metal::Buffer; caller-owned, ops never allocate)."""
+
+    def __init__(self, ctx: "Context", nbytes: int, flags: int = BUF_DEVICE):
+        self.ctx, self.nbytes = ctx, int(nbytes)
+        p = C.c_void_p()
+        ctx._check(ctx.lib.runit_buf_alloc(ctx.handle, self.nbytes, flags, C.byref(p)))
+        self.ptr = p.value
+
+    def free(self):
+        if self.ptr:
+            self.ctx.lib.runit_buf_free(self.ctx.handle, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            if self.ptr and self.ctx.handle:
+                self.free()
+        except Exception:
+            pass
+
+    def upload(self, arr: np.ndarray, offset: int = 0) -> "DeviceBuffer":
+        arr = np.ascontiguousarray(arr)
+        if offset + arr.nbytes > self.nbytes:
+            raise KernelError(ERR_BUFFER_SIZE, "upload of %d bytes at %d into a %d-byte buffer"
+                              % (arr.nbytes, offset, self.nbytes))
+        self.ctx._check(self.ctx.lib.runit_memcpy_h2d(self.ctx.handle, self.ptr + offset, arr.ctypes.data, arr.nbytes))
+        self.ctx.flush()   # the host array may go away after this call
+        return self
+
+    def download(self, dtype, count: int, offset: int = 0) -> np.ndarray:
+        out = np.empty(count, dtype)
+        if offset + out.nbytes > self.nbytes:
+            raise KernelError(ERR_BUFFER_SIZE, "download of %d bytes at %d from a %d-byte buffer"
+                              % (out.nbytes, offset, self.nbytes))
+        self.ctx._check(self.ctx.lib.runit_memcpy_d2h(self.ctx.handle, out.ctypes.data, self.ptr + offset, out.nbytes))
+        self.ctx.flush()
+        return out
+
+
+def _ptr(b) -> int:
+    """Accept a DeviceBuffer, a raw integer address, or anything with ``data_ptr()`` (torch)."""
+    if b is None:
+        return None
+    if isinstance(b, DeviceBuffer):
+        return b.ptr
+    if isinstance(b, int):
+        return b
+    if hasattr(b, "data_ptr"):
+        return b.data_ptr()
+    raise TypeError("not a device buffer: %r" % (b,))
+
+
+class Context:
+    """One CUDA stream on one GPU; replaces MetalContext.  Single-threaded, like the reference's."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        if stream is None:
+            st = self.lib.runit_ctx_create(device, C.byref(h))
+        else:
+            st = self.lib.runit_ctx_create_on_stream(device, C.c_void_p(stream), C.byref(h))
+        if st != OK:
+            raise KernelError(st, "runit_ctx_create(device=%d) failed: %s (no CPU fallback exists)"
+                              % (device, self.lib.runit_status_string(st).decode()))
+        self.handle = h
+        self.device = device
+
+    def close(self):
+        if self.handle:
+            self.lib.runit_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, status: int):
+        if status != OK:
+            raise KernelError(status, self.lib.runit_last_error_string(self.handle).decode())
+
+    # MetalContext::new_buffer (context.rs:215-220)
+    def new_buffer(self, nbytes: int, host_visible: bool = False) -> DeviceBuffer:
+        return DeviceBuffer(self, nbytes, BUF_HOST_VISIBLE if host_visible else BUF_DEVICE)
+
+    def buffer_from(self, arr: np.ndarray) -> DeviceBuffer:
+        arr = np.ascontiguousarray(arr)
+        return DeviceBuffer(self, max(arr.nbytes, 16)).upload(arr)
+
+    # MetalContext::flush (context.rs:289-296)
+    def flush(self):
+        self._check(self.lib.runit_flush(self.handle))
+
+    @property
+    def stream(self) -> int:
+        return self.lib.runit_ctx_stream(self.handle) or 0
+
+    @property
+    def launches(self) -> int:
+        return self.lib.runit_launch_count(self.handle)
+
+    def set_tuning(self, key: str, value: int):
+        self._check(self.lib.runit_set_tuning(self.handle, key.encode(), value))
+
+    def call(self, name: str, *args):
+        """Call ``runit_<name>(ctx, *args)``; buffers may be DeviceBuffers, ints or torch tensors."""
+        fn = getattr(self.lib, "runit_" + name)
+        conv = [(_ptr(a) if (isinstance(a, DeviceBuffer) or hasattr(a, "data_ptr") or a is None) else a) for a in args]
+        self._check(fn(self.handle, *conv))
+
+
+def _twin(name: str, doc: str):
+    def f(ctx: Context, *args):
+        ctx.call(name, *args)
+    f.__name__ = name
+    f.__doc__ = doc
+    return f
+
+
+# (name, reference citation) — signatures are those of include/runit_cuda.h
+_TWINS = [
+    ("gemv_q8_0_f32in_f32out", "dispatch.rs:1280 (weight, input, output, m, k)"),
+    ("gemv_q8_0_add_f32_f32in", "dispatch.rs:1298 (weight, input, output, residual, m, k)"),
+    ("gemv_q8_0_f32in", "dispatch.rs:1317"),
+    ("gemv_q8_0_f16", "dispatch.rs:1335"),
+    ("gemv_q8_0_add_f16", "dispatch.rs:1353"),
+    ("gemv_q8_0_add_f32res_f16", "dispatch.rs:1372"),
+    ("gemv_q8_0_f32in_f32out_mr", "dispatch.rs:1083"),
+    ("gemv_q8_0_add_f32_f32in_mr", "dispatch.rs:1101"),
+    ("gemv_q8_0_f32in_f32out_wide", "dispatch.rs:1397"),
+    ("gemv_q8_0_add_f32_f32in_wide", "dispatch.rs:1414"),
+    ("gemv_q8_0_f32in_wide", "dispatch.rs:1432"),
+    ("fused_qkv_q8_0_f32", "dispatch.rs:813 (w_q, w_k, w_v, x, out_q, out_k, out_v, q_dim, kv_dim, k)"),
+    ("fused_qkv_bias_q8_0_f32", "dispatch.rs:842 (+ bias_q, bias_k, bias_v as f16)"),
+    ("fused_qkv_f32bias_q8_0_f32", "no twin: f32 bias"),
+    ("fused_ffn_q8_0_f32", "dispatch.rs:903 (w_gate, w_up, x, act_out, ff_dim, k)"),
+    ("gemv_q4_0_f32in_f32out", "dispatch.rs:1456"),
+    ("gemv_q4_0_add_f32_f32in", "dispatch.rs:1471"),
+    ("gemv_q4_0_f32in", "dispatch.rs:1486"),
+    ("gemv_q4_0_f16", "dispatch.rs:1501"),
+    ("gemv_q4_0_add_f16", "dispatch.rs:1516"),
+    ("fused_ffn_q4_0_f32", "dispatch.rs:1531"),
+    ("gemv_q4k_f32in_f32out", "dispatch.rs:1229"),
+    ("gemv_q4k_add_f32_f32in", "dispatch.rs:1251"),
+    ("gemv_q4k_f16", "dispatch.rs:621"),
+    ("gemv_q4k_add_f16", "dispatch.rs:585"),
+    ("gemv_q4k_add_f32res_f16", "dispatch.rs:358"),
+    ("dequant_q4k_f16", "dispatch.rs:756 (input, output, n_blocks)"),
+    ("gemv_f16w_f32in", "dispatch.rs:270 (weight, input, output, m, k)"),
+    ("silu_mul_f16", "dispatch.rs:15 (gate, up, out, n)"),
+    ("silu_mul_f32", "dispatch.rs:35"),
+    ("scale_accumulate_f16", "dispatch.rs:1639 (src, acc, weight, n)"),
+    ("add_f16_into_f32", "dispatch.rs:316 (src, acc, n)"),
+    ("gemv_batched_f32", "no twin: (fmt, weight, input, output, residual, m, k, batch)"),
+    ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
+    ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),
+]
+for _n, _d in _TWINS:
+    globals()[_n] = _twin(_n, _d)
+del _n, _d
+
+__all__ = ["Context", "DeviceBuffer", "KernelError", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+           "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K"] + [n for n, _ in _TWINS]

@@ -1,0 +1,25 @@
+"""Comparison helpers shared by the parity tests."""
+import numpy as np
+
+REL_TOL = 1e-3   # |gpu - ref| <= REL_TOL * max(|ref|, rms(ref)): the bound the path's spec states
+ABS_TOL_F16 = 1e-2   # the reference's own tolerance for f16 kernels (dispatch.rs:1782)
+
+
+def assert_close(oracle, ref, got, rel_tol=REL_TOL, what=""):
+    ref = np.asarray(ref, np.float32).reshape(-1)
+    got = np.asarray(got, np.float32).reshape(-1)
+    assert ref.shape == got.shape, (ref.shape, got.shape)
+    assert np.isfinite(got).all(), "%s: non-finite output" % what
+    st = oracle.compare(ref, got, abs_tol=1e30, rel_tol=rel_tol)
+    assert st.n_mismatch_rel == 0, "%s: %r" % (what, st)
+    return st
+
+
+def f16_ulp_close(ref16, got16, ulps=1):
+    """f16 outputs: equal up to `ulps` units in the last place (the f32 sum feeding the rounding
+    differs in order between implementations)."""
+    a = np.asarray(ref16, np.float16).view(np.int16).astype(np.int32)
+    b = np.asarray(got16, np.float16).view(np.int16).astype(np.int32)
+    a = np.where(a < 0, -(a & 0x7FFF), a)
+    b = np.where(b < 0, -(b & 0x7FFF), b)
+    return np.abs(a - b).max() <= ulps

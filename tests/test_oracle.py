@@ -1,0 +1,271 @@
+"""CPU tests of the oracle: every known answer the reference's own tests hold for this path, the
+hand-derived single-block cases that follow from the block layouts documented in the shaders,
+agreement of the three accumulation tiers, and the committed golden vectors.
+
+(The reference has no golden vector for any quantized operator — parity for them is unpinned;
+what it does pin is exercised here.)"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+GOLD = Path(__file__).parent / "golden" / "path_golden.npz"
+
+
+def test_f16_conversion_is_ieee_rne(oracle):
+    O = oracle
+    rng = np.random.default_rng(1)
+    x = np.concatenate([rng.normal(0, 1, 50000), rng.normal(0, 1e-6, 5000), rng.normal(0, 3e4, 5000),
+                        [0.0, -0.0, 65504, 65519.99, 65520, 1e-8, 5.96e-8, 2.98e-8, 2.99e-8, 6.1e-5]]).astype(np.float32)
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    assert (O.f32_to_f16_bits(x) == want).all()
+    h = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    f, g = O.f16_bits_to_f32(h), h.view(np.float16).astype(np.float32)
+    assert ((f == g) | (np.isnan(f) & np.isnan(g))).all()
+
+
+# ── known answers of crates/engine/src/bin/test_gemv.rs (f16-weight GEMV = the router GEMV) ──
+def test_router_gemv_identity_4x4(oracle):
+    # test_gemv.rs:10-56
+    y = oracle.gemv_f16w_f32in(np.eye(4, dtype=np.float16), np.array([1, 2, 3, 4], np.float32), 4, 4)
+    assert np.abs(y - [1, 2, 3, 4]).max() < 0.01
+
+
+def test_router_gemv_ones_32x32(oracle):
+    # test_gemv.rs:58-85: all-ones x [1..32] = 528
+    y = oracle.gemv_f16w_f32in(np.ones((32, 32), np.float16), np.arange(1, 33, dtype=np.float32), 32, 32)
+    assert np.abs(y - 528.0).max() < 1.0 and y[0] == 528.0
+
+
+def test_router_gemv_896_pattern(oracle):
+    # test_gemv.rs:87-136: w=((i%17)-8)*1e-3, x=((i%13)-6)*1e-2, |gpu - f64 cpu| < 0.1
+    m = k = 896
+    i = np.arange(m * k)
+    w = (((i % 17).astype(np.float32) - 8.0) * np.float32(0.001)).astype(np.float16).reshape(m, k)
+    x = ((np.arange(k) % 13).astype(np.float32) - 6.0) * np.float32(0.01)
+    ref = w.astype(np.float64) @ x.astype(np.float64)
+    y = oracle.gemv_f16w_f32in(w, x, m, k)
+    assert np.abs(y - ref).max() < 0.1
+    assert np.abs(y - ref).max() < 1e-4   # and in fact far closer
+
+
+# ── crates/engine/tests/qwen2_load_test.rs:104-118: Q4_K blocks d=1, everything else zero ──
+def test_q4k_zero_blocks_give_exact_zero(oracle):
+    O = oracle
+    m, k = 6, 512
+    w = np.zeros((m, k // 256, 144), np.uint8)
+    w[:, :, 0:2] = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)
+    x = np.random.default_rng(3).normal(0, 1, k).astype(np.float32)
+    for tier in (O.TIER_SHADER, O.TIER_DEQUANT, O.TIER_F64):
+        assert (O.gemv(O.Q4K, w, x, m, k, tier) == 0).all()
+
+
+# ── hand-derived single-block cases from the documented layouts ──
+def test_q8_0_single_block(oracle):
+    O = oracle
+    # gemv_q8_0.metal:11-14: value = d*qs; d=1, qs=i-16, x=1 -> sum = -16
+    w = O.pack_q8_0(np.ones((1, 1)), (np.arange(32) - 16).reshape(1, 1, 32))
+    assert w.shape == (1, 34) and w[0, 0] == 0x00 and w[0, 1] == 0x3C   # f16(1.0) little-endian, scale first
+    for tier in range(3):
+        assert O.gemv(O.Q8_0, w, np.ones(32, np.float32), 1, 32, tier)[0] == -16.0
+    # d=0.5, x = e_5 picks qs[5]*0.5
+    w = O.pack_q8_0(np.full((1, 1), 0.5), (np.arange(32) * 3 - 40).reshape(1, 1, 32))
+    x = np.zeros(32, np.float32); x[5] = 2.0
+    assert O.gemv(O.Q8_0, w, x, 1, 32, O.TIER_SHADER)[0] == 0.5 * (15 - 40) * 2.0
+
+
+def test_q4_0_interleaved_nibbles(oracle):
+    O = oracle
+    # gemv_q4_0.metal:10-15: low nibble = element 2i, high nibble = element 2i+1, value = d*(nib-8)
+    raw = np.zeros((1, 18), np.uint8)
+    raw[0, 0:2] = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)
+    raw[0, 2:] = 0xF0   # low nibble 0 -> -8 at even elements, high nibble 15 -> +7 at odd elements
+    deq = O.dequant_rows(O.Q4_0, raw, 1, 32)[0]
+    assert (deq[0::2] == -8).all() and (deq[1::2] == 7).all()
+    x = np.zeros(32, np.float32); x[0::2] = 1.0
+    assert O.gemv(O.Q4_0, raw, x, 1, 32, O.TIER_SHADER)[0] == -8.0 * 16
+    x = np.zeros(32, np.float32); x[1::2] = 1.0
+    assert O.gemv(O.Q4_0, raw, x, 1, 32, O.TIER_F64)[0] == 7.0 * 16
+    # packer agrees with the layout
+    nib = np.zeros((1, 1, 32), np.uint8); nib[0, 0, 1::2] = 15
+    assert (O.pack_q4_0(np.ones((1, 1)), nib) == raw).all()
+
+
+def test_q4k_scale_unpack_and_nibble_mapping(oracle):
+    O = oracle
+    # dequant.metal:42-51,74-82: sub-block j<4 -> low nibbles of qs[32j..] (elements 64j..64j+31);
+    # sub-block j+4 -> high nibbles (elements 64j+32..64j+63); 6-bit scales, upper two bits of
+    # scale j+4 live in scales[j]>>6.
+    for j in range(8):
+        sc = np.zeros((1, 1, 8), np.uint8); mn = np.zeros((1, 1, 8), np.uint8)
+        sc[0, 0, j] = 49 if j >= 4 else 1      # 49 needs the two high bits
+        nib = np.full((1, 1, 256), 3, np.uint8)
+        w = O.pack_q4k(np.ones((1, 1)), np.zeros((1, 1)), sc, mn, nib)
+        deq = O.dequant_rows(O.Q4K, w, 1, 256)[0]
+        pair, hi = (j - 4, 1) if j >= 4 else (j, 0)
+        lo_el = 64 * pair + 32 * hi
+        want = np.zeros(256, np.float32); want[lo_el:lo_el + 32] = 3.0 * sc[0, 0, j]
+        assert (deq == want).all(), j
+    # min term: dmin*m subtracted
+    sc = np.zeros((1, 1, 8), np.uint8); mn = np.zeros((1, 1, 8), np.uint8); mn[0, 0, 6] = 37
+    w = O.pack_q4k(np.zeros((1, 1)), np.full((1, 1), 0.5), sc, mn, np.zeros((1, 1, 256), np.uint8))
+    deq = O.dequant_rows(O.Q4K, w, 1, 256)[0]
+    assert (deq[64 * 2 + 32:64 * 2 + 64] == -18.5).all() and np.count_nonzero(deq) == 32
+    # dequant_q4k_f16 agrees with the row dequant rounded to f16
+    rng = np.random.default_rng(5)
+    w = O.rand_q4k(rng, 3, 512)
+    assert (O.dequant_q4k_f16(w, 6).view(np.uint16) ==
+            O.dequant_rows(O.Q4K, w, 3, 512).astype(np.float16).reshape(-1).view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("fmt,m,k", [(0, 19, 896), (0, 4, 4864), (1, 21, 3584), (1, 7, 96), (2, 13, 2048), (2, 5, 18944)])
+def test_tiers_agree(oracle, fmt, m, k):
+    """Shader-order f32, dequant-then-dot f32 and f64 accumulation agree to f32 rounding; this
+    cross-checks the packers against three independently written decoders."""
+    O = oracle
+    rng = np.random.default_rng(100 + fmt * 7 + m)
+    w = O.rand_weights(fmt, rng, m, k)
+    x = rng.normal(0, 1, (2, k)).astype(np.float32)
+    y64 = O.gemv_f64(fmt, w, x, m, k)
+    mag = np.abs(O.dequant_rows(fmt, w, m, k)) @ np.abs(x).T   # [m, batch] sum |w||x|
+    for tier in (O.TIER_SHADER, O.TIER_DEQUANT):
+        y = O.gemv(fmt, w, x, m, k, tier)
+        assert (np.abs(y - y64) <= 4e-6 * mag.T + 1e-30).all()
+    # and against a numpy restatement of the dequantised matrix
+    ref = x.astype(np.float64) @ O.dequant_rows(fmt, w, m, k).astype(np.float64).T
+    assert np.allclose(y64, ref, rtol=1e-12, atol=1e-12)
+
+
+def test_topk_softmax_semantics(oracle):
+    O = oracle
+    rng = np.random.default_rng(9)
+    lg = rng.normal(0, 1, 64).astype(np.float32)
+    idx, w, probs = O.topk_softmax(lg, 8, False)
+    order = np.argsort(-probs, kind="stable")[:8]
+    assert (idx == order).all()                       # descending probability
+    assert np.allclose(probs.sum(), 1.0, atol=1e-6)   # softmax over ALL experts first (forward.rs:2424-2428)
+    assert np.allclose(w, probs[idx]) and w.sum() < 1.0
+    _, wr, _ = O.topk_softmax(lg, 8, True)            # renormalised (forward.rs:2438-2445)
+    assert np.allclose(wr.sum(), 1.0, atol=1e-6) and np.allclose(wr, w / w.sum(), rtol=1e-6)
+    # ties: lowest index first
+    idx, _, _ = O.topk_softmax(np.zeros(16, np.float32), 4, False)
+    assert list(idx) == [0, 1, 2, 3]
+    with pytest.raises(ValueError):
+        O.topk_softmax(lg, 65, False)
+
+
+def test_moe_glue_ops(oracle):
+    O = oracle
+    rng = np.random.default_rng(11)
+    g = rng.normal(0, 2, 300).astype(np.float32); u = rng.normal(0, 2, 300).astype(np.float32)
+    want = g / (1 + np.exp(-g.astype(np.float64))) * u
+    assert np.allclose(O.silu_mul_f32(g, u), want, rtol=1e-6, atol=1e-7)
+    g16, u16 = g.astype(np.float16), u.astype(np.float16)
+    want16 = (g16.astype(np.float64) / (1 + np.exp(-g16.astype(np.float64))) * u16.astype(np.float64)).astype(np.float16)
+    got16 = O.silu_mul_f16(g16, u16)
+    assert np.abs(got16.astype(np.float32) - want16.astype(np.float32)).max() <= 2e-3 * np.abs(want16).max()
+    acc = rng.normal(0, 1, 300).astype(np.float16)
+    out = O.scale_accumulate_f16(g16, acc, 0.37)
+    want = (acc.astype(np.float32) + (g16.astype(np.float32) * np.float32(0.37)).astype(np.float16).astype(np.float32)).astype(np.float16)
+    assert (out.view(np.uint16) == want.view(np.uint16)).all()
+    a32 = rng.normal(0, 1, 300).astype(np.float32)
+    assert (O.add_f16_into_f32(g16, a32) == a32 + g16.astype(np.float32)).all()
+
+
+def test_moe_layer_modes(oracle):
+    O = oracle
+    rng = np.random.default_rng(13)
+    h, ff, E, k = 256, 256, 4, 2
+    router = rng.normal(0, 0.02, (E, h)).astype(np.float32)
+    gate, up, down = O.rand_q4k(rng, E * ff, h), O.rand_q4k(rng, E * ff, h), O.rand_q4k(rng, E * h, ff)
+    x = rng.normal(0, 1, (2, h)).astype(np.float32)
+    y, idx, w = O.moe_layer_q4k(router, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, renorm=False)
+    # rebuild token 0 from the primitive oracle ops
+    lg = O.gemv_f32w(router, x[0], E, h)
+    i0, w0, _ = O.topk_softmax(lg, k, False)
+    assert (i0 == idx[0]).all() and np.allclose(w0, w[0])
+    acc = np.zeros(h, np.float64)
+    rb_h, rb_ff = O.row_bytes(O.Q4K, h), O.row_bytes(O.Q4K, ff)
+    for e, we in zip(i0, w0):
+        g = O.gemv(O.Q4K, gate.reshape(-1)[e * ff * rb_h:], x[0], ff, h)
+        u = O.gemv(O.Q4K, up.reshape(-1)[e * ff * rb_h:], x[0], ff, h)
+        a = O.silu_mul_f32(g, u)
+        acc += np.float32(we) * O.gemv(O.Q4K, down.reshape(-1)[e * h * rb_ff:], a, h, ff)
+    assert np.allclose(y[0], acc, rtol=2e-6, atol=1e-6 * np.abs(acc).max())
+    # residual is added on top; renorm rescales the combine
+    yr, _, wr = O.moe_layer_q4k(router, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, renorm=True, residual=x)
+    assert np.allclose(wr.sum(1), 1.0, atol=1e-6)
+    # the reference's f16 rounding points stay within its own tolerance scale of the f32 mode
+    y16, idx16, _ = O.moe_layer_q4k(router, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, renorm=False,
+                                    mode=O.MOE_REF_F16)
+    if (idx16 == idx).all():
+        finite = np.isfinite(y16)
+        assert np.abs(y16[finite] - y[finite]).max() <= 2e-2 * np.abs(y).max()
+
+
+def test_decode_ops(oracle):
+    O = oracle
+    rng = np.random.default_rng(17)
+    x = rng.normal(0, 1, (3, 128)).astype(np.float32); g = rng.normal(1, 0.1, 128).astype(np.float32)
+    want = x / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-5) * g
+    assert np.allclose(O.rms_norm_f32(x, g, 1e-5), want, rtol=1e-6)
+    # rope: position 0 is the identity; norm is preserved; pairs are (d, d+hd/2)
+    q = rng.normal(0, 1, 4 * 64).astype(np.float32); kk = rng.normal(0, 1, 2 * 64).astype(np.float32)
+    q0, k0 = O.rope_qk_f32(q, kk, 64, 4, 2, 0, 10000.0)
+    assert (q0 == q).all() and (k0 == kk).all()
+    q5, _ = O.rope_qk_f32(q, kk, 64, 4, 2, 5, 10000.0)
+    assert np.allclose(np.linalg.norm(q5), np.linalg.norm(q), rtol=1e-6)
+    ang = 5.0 / 10000.0 ** (2 * 3 / 64)
+    assert np.allclose(q5[3], q[3] * np.cos(ang) - q[3 + 32] * np.sin(ang), rtol=1e-5, atol=1e-6)
+    # attention against a plain softmax
+    heads, kvh, hd, max_seq, L = 4, 2, 64, 16, 9
+    kc = rng.normal(0, 1, (kvh, max_seq, hd)).astype(np.float16); vc = rng.normal(0, 1, (kvh, max_seq, hd)).astype(np.float16)
+    out = O.decode_attention_f32q_f16kv(q, kc, vc, L, heads, kvh, hd, max_seq).reshape(heads, hd)
+    for hq in range(heads):
+        s = kc[hq // 2, :L].astype(np.float64) @ q[hq * hd:(hq + 1) * hd].astype(np.float64) / np.sqrt(hd)
+        p = np.exp(s - s.max()); p /= p.sum()
+        assert np.allclose(out[hq], p @ vc[hq // 2, :L].astype(np.float64), rtol=1e-5, atol=1e-6)
+    assert O.argmax_f32(np.array([1, 7, 7, 3], np.float32)) == 1
+
+
+def test_comparator_semantics(oracle):
+    # crates/reference/src/lib.rs:116-153: identical -> 0 mismatches; one element off by 0.5 at tol 1e-3 -> 1
+    O = oracle
+    a = np.array([1.0, 2.0, 3.0], np.float32)
+    assert O.compare(a, a).n_mismatch_abs == 0
+    st = O.compare(a, np.array([1.0, 2.5, 3.0], np.float32), abs_tol=1e-3)
+    assert st.n_mismatch_abs == 1 and abs(st.max_abs - 0.5) < 1e-7
+    st = O.compare(a, a + 1e-4, abs_tol=1e-3)
+    assert st.n_mismatch_abs == 0
+    assert O.compare(np.zeros(0, np.float32), np.zeros(0, np.float32)).n == 0
+
+
+def test_lcg_matches_reference_generator(oracle):
+    # crates/kernels/src/dispatch.rs:1805-1813
+    v = oracle.lcg_random_f32(4, 42)
+    s = 42
+    for i in range(4):
+        s = (s * 6364136223846793005 + 1442695040888963407) % 2 ** 64
+        assert v[i] == np.float32(np.float32(s >> 33) / np.float32(4294967295.0) * np.float32(2) - np.float32(1))
+    assert (np.abs(oracle.lcg_random_f32(1000, 7)) <= 1).all()
+
+
+def test_golden_vectors_regression(oracle):
+    """The committed fixtures reproduce bit-for-bit on this host (f64 tier, -ffp-contract=off)."""
+    O = oracle
+    G = np.load(GOLD)
+    i = 0
+    while "gemv%d_fmt" % i in G:
+        fmt, m, k = map(int, G["gemv%d_fmt" % i])
+        y = O.gemv(fmt, G["gemv%d_w" % i], G["gemv%d_x" % i], m, k, O.TIER_F64)
+        assert (y == G["gemv%d_y" % i]).all(), i
+        i += 1
+    assert i == 6
+    for r in range(G["route_logits"].shape[0]):
+        idx, w, _ = O.topk_softmax(G["route_logits"][r], 8, False)
+        assert (idx == G["route_idx"][r]).all() and np.allclose(w, G["route_w"][r], rtol=1e-6)
+    h, ff, E, k = map(int, G["moe_dims"])
+    y, idx, w = O.moe_layer_q4k(G["moe_router"], G["moe_gate"], G["moe_up"], G["moe_down"], G["moe_x"], h=h, ff=ff,
+                                E=E, top_k=k, renorm=False)
+    assert (idx == G["moe_idx"]).all() and np.allclose(y, G["moe_y"], rtol=1e-6, atol=1e-6 * np.abs(y).max())
