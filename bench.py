@@ -246,7 +246,8 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()   # not the legacy default stream: command lists are recorded on it
+    torch.cuda.set_stream(stream)
     ctx = R.Context(local, stream=stream.cuda_stream)   # kernels and torch events share this stream
     for kv in filter(None, args.tune.split(",")):
         k, v = kv.split("=")

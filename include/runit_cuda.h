@@ -76,6 +76,16 @@ uint64_t runit_launch_count(runit_ctx_t* ctx);
 /* Kernel tuning knob for experiments: 0 = default.  See DESIGN notes in gemv.cu. */
 int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value);
 
+/* ── recorded command lists (no twin as a function; the role of the reference's command buffer,
+ *    context.rs:248-296: ops are encoded once and committed together) ──
+ * Between begin and end every op call on the context is recorded instead of executed; the
+ * recorded list replays with one launch.  Pointers and sizes are baked in at record time.  */
+typedef struct runit_graph runit_graph_t;
+int32_t runit_graph_begin(runit_ctx_t* ctx);
+int32_t runit_graph_end(runit_ctx_t* ctx, runit_graph_t** out);
+int32_t runit_graph_launch(runit_ctx_t* ctx, runit_graph_t* graph);
+int32_t runit_graph_destroy(runit_ctx_t* ctx, runit_graph_t* graph);
+
 /* ── Q8_0 fused-dequant GEMV family ── */
 /* dispatch.rs:1280  y_f32[m] = W_q8_0[m,k] . x_f32[k] */
 int32_t runit_gemv_q8_0_f32in_f32out(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);

@@ -23,7 +23,7 @@ _CTYPES = {
     "const runit_model_desc*": C.c_void_p, "runit_model_t*": C.c_void_p,
     "runit_model_t**": C.POINTER(C.c_void_p), "const void* const*": C.POINTER(C.c_void_p),
     "void* const*": C.POINTER(C.c_void_p), "float*": C.POINTER(C.c_float),
-    "uint64_t*": C.POINTER(C.c_uint64),
+    "uint64_t*": C.POINTER(C.c_uint64), "runit_graph_t*": C.c_void_p, "runit_graph_t**": C.POINTER(C.c_void_p),
 }
 
 

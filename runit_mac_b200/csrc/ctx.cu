@@ -26,7 +26,10 @@ const char* runit_status_name(int32_t st) {
 
 int32_t runit_fail(runit_ctx* ctx, int32_t st, const char* fmt, ...) {
     if (ctx) {
-        if (ctx->sticky_status == RUNIT_OK) ctx->sticky_status = st;
+        // Argument errors are reported to the caller at once and launch nothing; only failures of
+        // work that was already accepted are kept for the next flush.
+        const bool async_kind = st == RUNIT_ERR_LAUNCH || st == RUNIT_ERR_NCCL || st == RUNIT_ERR_TIMEOUT;
+        if (async_kind && ctx->sticky_status == RUNIT_OK) ctx->sticky_status = st;
         va_list ap;
         va_start(ap, fmt);
         int n = snprintf(ctx->err, sizeof(ctx->err), "%s: ", runit_status_name(st));
@@ -69,15 +72,55 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
         }
         c->owns_stream = true;
     }
-    if (cudaMalloc(&c->d_status, 64) != cudaSuccess) {
+    // Status word for kernels with bounded waits: pinned host memory mapped into the device, so
+    // the host reads it after a flush without a copy.
+    if (cudaHostAlloc((void**)&c->h_status, 64, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void**)&c->d_status, c->h_status, 0) != cudaSuccess) {
+        cudaGetLastError();
         if (c->owns_stream) cudaStreamDestroy(c->stream);
         delete c;
         return RUNIT_ERR_ALLOC;
     }
-    cudaMemsetAsync(c->d_status, 0, 64, c->stream);
+    memset(c->h_status, 0, 64);
+    {
+        cudaDriverEntryPointQueryResult qres;
+        void* fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            c->encode_tiled = fn;
+        else
+            cudaGetLastError();
+    }
     const char* v = getenv("RUNIT_GEMV_VARIANT");
     if (v) c->tune.gemv_variant = atoi(v);
     *out = c;
+    return RUNIT_OK;
+}
+
+int32_t runit_get_tmap(runit_ctx* ctx, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                       uint32_t box_bytes, CUtensorMap* out) {
+    if (!ctx->encode_tiled) return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
+    uint64_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull ^ (rows * 31 + row_bytes * 7 + box_rows);
+    runit_tmap_entry& e = ctx->tmaps[(h >> 32) & 255];
+    if (e.ptr == ptr && e.rows == rows && e.row_bytes == row_bytes && e.box_rows == box_rows && e.box_bytes == box_bytes) {
+        *out = e.map;
+        return RUNIT_OK;
+    }
+    auto encode = reinterpret_cast<CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill)>(
+        ctx->encode_tiled);
+    const cuuint64_t gdim[2] = {row_bytes, rows};
+    const cuuint64_t gstride[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    e.ptr = ptr; e.rows = rows; e.row_bytes = row_bytes; e.box_rows = box_rows; e.box_bytes = box_bytes; e.map = m;
+    *out = m;
     return RUNIT_OK;
 }
 
@@ -93,7 +136,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);   // Drop flushes, context.rs:299-304
-    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RUNIT_OK;
@@ -105,6 +148,10 @@ int32_t runit_flush(runit_ctx_t* ctx) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) runit_fail(ctx, RUNIT_ERR_LAUNCH, "stream synchronize: %s", cudaGetErrorString(e));
+    if (ctx->h_status && ctx->h_status[0] != 0) {
+        ctx->h_status[0] = 0;
+        runit_fail(ctx, RUNIT_ERR_TIMEOUT, "a kernel gave up a bounded wait (bulk copy never completed)");
+    }
     int32_t st = ctx->sticky_status;
     ctx->sticky_status = RUNIT_OK;   // the message stays readable until the next error
     return st;
@@ -122,7 +169,49 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "gemv_stages")) ctx->tune.gemv_stages = value;
     else if (!strcmp(key, "moe_variant")) ctx->tune.moe_variant = value;
     else if (!strcmp(key, "pdl")) ctx->tune.pdl = value;
+    else if (!strcmp(key, "gemv_load")) ctx->tune.gemv_load = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
+    return RUNIT_OK;
+}
+
+// CUDA graphs stand in for the reference's encoded command buffer: record once, replay per token.
+int32_t runit_graph_begin(runit_ctx_t* ctx) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, !ctx->capturing, "runit_graph_begin: a recording is already open");
+    RUNIT_CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return RUNIT_OK;
+}
+
+int32_t runit_graph_end(runit_ctx_t* ctx, runit_graph_t** out) {
+    if (!ctx || !out) return RUNIT_ERR_BAD_ARG;
+    *out = nullptr;
+    RUNIT_REQUIRE(ctx, ctx->capturing, "runit_graph_end: no recording is open");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (e != cudaSuccess || !g) {
+        cudaGetLastError();
+        return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    }
+    cudaGraphExec_t ex = nullptr;
+    e = cudaGraphInstantiate(&ex, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    *out = reinterpret_cast<runit_graph_t*>(ex);
+    return RUNIT_OK;
+}
+
+int32_t runit_graph_launch(runit_ctx_t* ctx, runit_graph_t* graph) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, graph, "runit_graph_launch: null graph");
+    RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph), ctx->stream));
+    return RUNIT_OK;
+}
+
+int32_t runit_graph_destroy(runit_ctx_t* ctx, runit_graph_t* graph) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    if (graph) RUNIT_CUDA_TRY(ctx, cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(graph)));
     return RUNIT_OK;
 }
 

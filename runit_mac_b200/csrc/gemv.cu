@@ -79,11 +79,28 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
     const uint32_t bpu = c.fmt == RUNIT_FMT_Q8_0 ? Traits<RUNIT_FMT_Q8_0>::BPU
                          : c.fmt == RUNIT_FMT_Q4_0 ? Traits<RUNIT_FMT_Q4_0>::BPU : Traits<RUNIT_FMT_Q4K>::BPU;
     a.n_units = (a.nb + bpu - 1) / bpu;
-    a.n_stages = (a.n_units + kKS - 1) / kKS;
+    a.status = ctx->d_status;
+    // Tiled bulk loads (TMA) for the 4-bit formats: one tensor map per weight matrix.
+    GemvMaps maps;
+    const bool tma = !simple && c.fmt != RUNIT_FMT_Q8_0 && ctx->tune.gemv_load == 0 && ctx->encode_tiled != nullptr;
+    if (tma) {
+        const uint32_t box_rows = c.dual ? kRT / 2 : kRT;
+        for (int i = 0; i < c.nseg; i++) {
+            int32_t st = runit_get_tmap(ctx, c.w[i], c.rows[i], a.row_bytes, box_rows, 144, &maps.m[i]);
+            if (st != RUNIT_OK) return st;
+        }
+        if (c.dual) {
+            int32_t st = runit_get_tmap(ctx, c.w2, c.rows[0], a.row_bytes, box_rows, 144, &maps.m[3]);
+            if (st != RUNIT_OK) return st;
+        }
+    }
     switch (c.fmt) {
-        case RUNIT_FMT_Q8_0: return gemv_launch_q8_0(ctx, a, tiles, total_rows, cpb, c.batch, c.x_f16, simple, nm);
-        case RUNIT_FMT_Q4_0: return gemv_launch_q4_0(ctx, a, tiles, total_rows, cpb, c.batch, c.x_f16, simple, nm);
-        default: return gemv_launch_q4k(ctx, a, tiles, total_rows, cpb, c.batch, c.x_f16, simple, nm);
+        case RUNIT_FMT_Q8_0:
+            return gemv_launch_q8_0(ctx, a, maps, tiles, total_rows, cpb, tma, c.batch, c.x_f16, simple, nm);
+        case RUNIT_FMT_Q4_0:
+            return gemv_launch_q4_0(ctx, a, maps, tiles, total_rows, cpb, tma, c.batch, c.x_f16, simple, nm);
+        default:
+            return gemv_launch_q4k(ctx, a, maps, tiles, total_rows, cpb, tma, c.batch, c.x_f16, simple, nm);
     }
 }
 

@@ -1,11 +1,14 @@
 // Device helpers shared by the fused-dequant GEMV kernels and the MoE expert kernels.
 //
-// Dequantisation without integer->float conversion instructions: a 4-bit field at bit p of a
-// word is turned into the float 2^23 + q*2^p by one LOP3 ((v & (15<<p)) | 0x4B000000), and
-// one packed FADD removes the 2^23 (and, for Q4_0, the -8 offset).  The factor 2^p is
-// cancelled by pre-scaling the activation vector once per stage (exact: powers of two), so
-// the per-weight cost is one LOP3, half a packed FADD and half a packed FFMA (sm_100
-// add.f32x2 / fma.f32x2).
+// Dequantisation without integer->float conversion instructions.  Weights are handled as
+// 64-bit register pairs P = (word 2n, word 2n+1) exactly as they arrive from a 128-bit
+// shared-memory load.  A 4-bit (or 8-bit) field at bit p of BOTH words becomes the packed
+// float pair (2^23 + q*2^p, 2^23 + q'*2^p) with one 64-bit logic op (two LOP3), one packed
+// add.f32x2 removes the 2^23 (and the -8 / -128 offsets), and one packed fma.f32x2 multiplies
+// by the activation pair.  The factor 2^p is cancelled by pre-scaling the activations once per
+// stage (exact: powers of two), and the activations are stored permuted so that a 128-bit load
+// yields exactly the pairs the fields need.  Per weight: one LOP3, half an add.f32x2, half an
+// fma.f32x2 — and no register-pair shuffling.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -15,7 +18,7 @@
 
 namespace runit {
 
-constexpr uint32_t kMagic = 0x4B000000u;   // 2^23 as float bits
+constexpr uint64_t kMagic2 = 0x4B0000004B000000ull;   // (2^23, 2^23) as packed float bits
 constexpr float kTwo23 = 8388608.0f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -33,22 +36,67 @@ __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
 }
+template <int CPB>
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src) {
+    if (CPB == 16) cp_async16(dst, src);
+    else if (CPB == 8) cp_async8(dst, src);
+    else cp_async4(dst, src);
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return __fadd2_rn(a, b); }
-
-__device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
-    return make_float2(__uint_as_float(a), __uint_as_float(b));
+// Packed f32x2 arithmetic on 64-bit registers (sm_100: add.f32x2 / fma.f32x2).
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// One LOP3 per 32-bit half: ((word & MASK) | 2^23-bits) and ((word & MASK) ^ C).  Written as explicit
+// lop3.b32 because 64-bit and/or pairs are not fused into one LOP3 per half by the compiler.
+template <uint32_t MASK>
+__device__ __forceinline__ uint64_t field_or_magic(uint64_t P) {
+    uint64_t out;
+    asm("{\n .reg .b32 lo, hi, a, b;\n mov.b64 {lo, hi}, %1;\n"
+        " lop3.b32 a, lo, %2, 0x4B000000, 0xEA;\n lop3.b32 b, hi, %2, 0x4B000000, 0xEA;\n"
+        " mov.b64 %0, {a, b};\n}"
+        : "=l"(out)
+        : "l"(P), "n"(MASK));
+    return out;
+}
+template <uint32_t MASK, uint32_t C>
+__device__ __forceinline__ uint64_t field_xor(uint64_t P) {
+    uint64_t out;
+    asm("{\n .reg .b32 lo, hi, a, b;\n mov.b64 {lo, hi}, %1;\n"
+        " lop3.b32 a, lo, %2, %3, 0x6A;\n lop3.b32 b, hi, %2, %3, 0x6A;\n"
+        " mov.b64 %0, {a, b};\n}"
+        : "=l"(out)
+        : "l"(P), "n"(MASK), "n"(C));
+    return out;
+}
+__host__ __device__ constexpr uint64_t pack2(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+__device__ __forceinline__ uint64_t packf(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return pack2(b, b);
+}
+__device__ __forceinline__ float sum2(uint64_t v) {
+    return __uint_as_float((uint32_t)v) + __uint_as_float((uint32_t)(v >> 32));
+}
+// 4-bit field at bit p of both words
+__host__ __device__ constexpr uint64_t nib_mask(int p) { return (0xFull << p) | (0xFull << (p + 32)); }
+__host__ __device__ constexpr uint64_t byte_mask(int p) { return (0xFFull << p) | (0xFFull << (p + 32)); }
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
     return __half2float(__ushort_as_half((unsigned short)(h16 & 0xFFFFu)));
 }
+__device__ __forceinline__ float exp2_neg(int sh) { return __uint_as_float((uint32_t)(127 - sh) << 23); }
 
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
@@ -59,42 +107,36 @@ __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v));
 struct Q4KScales {
     uint32_t sl, ml, sh, mh;
 };
-__device__ __forceinline__ Q4KScales q4k_unpack_scales(uint4 h) {
+__device__ __forceinline__ Q4KScales q4k_unpack_scales(uint32_t hy, uint32_t hz, uint32_t hw) {
     Q4KScales s;
-    s.sl = h.y & 0x3F3F3F3Fu;
-    s.ml = h.z & 0x3F3F3F3Fu;
-    s.sh = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-    s.mh = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    s.sl = hy & 0x3F3F3F3Fu;
+    s.ml = hz & 0x3F3F3F3Fu;
+    s.sh = (hw & 0x0F0F0F0Fu) | ((hy >> 2) & 0x30303030u);
+    s.mh = ((hw >> 4) & 0x0F0F0F0Fu) | ((hz >> 2) & 0x30303030u);
     return s;
 }
 __device__ __forceinline__ float byte_to_float(uint32_t w, int j) {
     return (float)((w >> (8 * j)) & 0xFFu);
 }
 
-// Pre-scale factors applied to the activation vector so that the 2^p of each nibble position
-// cancels.  Q4_K: element l of a 32-element sub-block sits in byte l%4 of its qs word; low
-// nibbles (first half of a 64-element pair) at bit 8b or, for b==3, bit 12 of (v>>12); high
-// nibbles at bit 8b+4, or bit 8/16 of (v>>12) for b==2/3.
-__device__ __forceinline__ float q4k_xscale(int elem_in_unit) {
-    const int b = elem_in_unit & 3;
-    const bool hi = (elem_in_unit >> 5) & 1;
-    // lo: 2^0, 2^-8, 2^-16, 2^-12      hi: 2^-4, 2^-12, 2^-8, 2^-16
-    const int sh = hi ? (b == 0 ? 4 : (b == 1 ? 12 : (b == 2 ? 8 : 16)))
-                      : (b == 0 ? 0 : (b == 1 ? 8 : (b == 2 ? 16 : 12)));
-    return __uint_as_float((uint32_t)(127 - sh) << 23);
-}
+// ─────────────── activation layout: permutation and pre-scale per format ───────────────
+// pos8: within a group of 8 elements the stored order is e0,e4,e1,e5,e2,e6,e3,e7 (pairs that sit
+// at the same byte position of two consecutive weight words).
+__device__ __forceinline__ int pos8(int t) { return t < 4 ? 2 * t : 2 * (t - 4) + 1; }
 
-// Q4_0: element e of a 256-element unit (8 blocks of 18 bytes): block b=e/32, byte i=(e%32)/2,
-// h=e%2 (low/high nibble).  The byte sits at unit offset 18b+2+i, i.e. byte position
-// bp=(2b+2+i)%4 of its word.  Fields: bp0 (bit 0, bit 4); bp1 (8, 12); bp2 (16, bit 8 of v>>12);
-// bp3 (bit 12 and bit 16 of v>>12).
-__device__ __forceinline__ int q4_0_shift(int bp, int h) {
-    return bp == 0 ? (h ? 4 : 0) : bp == 1 ? (h ? 12 : 8) : bp == 2 ? (h ? 8 : 16) : (h ? 16 : 12);
+// Q4_K, element l (0..31) of a sub-block, hi = second half of the 64-element pair: byte l%4 of
+// its word.  Low nibbles sit at bit 8b (b==3: bit 12 of P>>12); high nibbles at bit 8b+4
+// (b==2,3: bits 8,16 of P>>12).
+__device__ __forceinline__ int q4k_shift(int b, bool hi) {
+    return hi ? (b == 0 ? 4 : (b == 1 ? 12 : (b == 2 ? 8 : 16))) : (b == 0 ? 0 : (b == 1 ? 8 : (b == 2 ? 16 : 12)));
 }
-__device__ __forceinline__ float q4_0_xscale(int elem_in_unit) {
-    const int b = elem_in_unit >> 5, i = (elem_in_unit & 31) >> 1, h = elem_in_unit & 1;
-    const int bp = (2 * b + 2 + i) & 3;
-    return __uint_as_float((uint32_t)(127 - q4_0_shift(bp, h)) << 23);
+// Q4_0, element e (0..31) of a block: byte i=e/2, nibble h=e%2, byte position b=i%4 of its
+// (realigned) word: field at bit 8b+4h, fields above bit 16 taken from P>>12.
+__device__ __forceinline__ int q4_0_shift(int b, int h) {
+    const int p = 8 * b + 4 * h;
+    return p <= 16 ? p : p - 12;
 }
+// Q8_0, byte position b of the word: bits 0 / 8 of P (b = 0, 1) or of P>>16 (b = 2, 3).
+__device__ __forceinline__ int q8_0_shift(int b) { return (b & 1) ? 8 : 0; }
 
 }  // namespace runit

@@ -2,49 +2,51 @@
 //
 // Replaces the Metal kernels of crates/kernels/shaders/{gemv_q8_0,gemv_q4_0,gemv_q4k,
 // fused_qkv,fused_ffn}.metal.  Design (HBM-bound streaming kernel):
-//   * a CTA of 128 threads owns a tile of 32 rows and walks K in stages; a stage holds, per
-//     row, the bytes of 4 "units" (a unit = 256 weights for the 4-bit formats, 128 for Q8_0);
-//   * weights move HBM -> shared memory with 16-byte cp.async copies in a 3- or 4-deep ring,
-//     so the bytes in flight per SM do not depend on register pressure or occupancy;
-//   * thread (lane, warp) dots row `lane` with unit `warp` of the stage: weights are read
-//     from the padded, conflict-free shared tile with 128-bit loads, the activation slice is
-//     a warp-wide broadcast read, and no cross-lane reduction is needed until the end;
-//   * the activation slice of the next stage is pre-scaled (and, for Q4_K, block-summed) by
-//     all threads one stage ahead, which removes the per-weight scale multiply and the
-//     integer->float conversion (see gemv_common.cuh);
+//   * a CTA of 4 warps owns a tile of 32 rows; warp w dots the rows with the K "units"
+//     w, w+4, w+8, ... (a unit = 256 weights of a row for the 4-bit formats, 128 for Q8_0);
+//   * every warp runs its OWN cp.async ring (3 stages of 32 rows x 1 unit + the matching slice
+//     of the activations), synchronised with __syncwarp only: there is no CTA barrier in the
+//     K loop, so the bytes in flight per SM depend neither on registers nor on the slowest warp;
+//   * lane l owns row l: it reads its unit from the shared tile with 128-bit loads (row pitch is
+//     an odd multiple of the load width: conflict-free), the activation slice is a warp-wide
+//     broadcast, and no cross-lane reduction is needed until the end;
+//   * the activation slice of the next stage is permuted, pre-scaled and (Q4_K) block-summed by
+//     the warp one stage ahead, which removes integer->float conversions, per-weight scale
+//     multiplies and register-pair shuffles from the inner loop (see gemv_common.cuh);
 //   * the four K-slices of a row are added in a fixed order (deterministic results).
 #pragma once
 
+#include <type_traits>
+
 #include "gemv_common.cuh"
 #include "runit_cuda.h"
+#include "tma.cuh"
 
 namespace runit {
 
 constexpr int kNT = 128;   // threads per CTA
 constexpr int kRT = 32;    // rows per tile (one per lane)
-constexpr int kKS = 4;     // K-slices per stage (one per warp)
+constexpr int kKS = 4;     // K-slices (one per warp)
 
 template <int FMT> struct Traits;
-template <> struct Traits<RUNIT_FMT_Q8_0> { static constexpr int UE = 128, UB = 136, BPU = 4, BE = 32; };
-template <> struct Traits<RUNIT_FMT_Q4_0> { static constexpr int UE = 256, UB = 144, BPU = 8, BE = 32; };
-template <> struct Traits<RUNIT_FMT_Q4K>  { static constexpr int UE = 256, UB = 144, BPU = 1, BE = 256; };
+template <> struct Traits<RUNIT_FMT_Q8_0> { static constexpr int UE = 128, UB = 136, BPU = 4; };
+template <> struct Traits<RUNIT_FMT_Q4_0> { static constexpr int UE = 256, UB = 144, BPU = 8; };
+template <> struct Traits<RUNIT_FMT_Q4K>  { static constexpr int UE = 256, UB = 144, BPU = 1; };
 
+// One stage of one warp's ring.
 template <int FMT, int B, bool XF16>
-struct StageLayout {
+struct WarpStage {
     using T = Traits<FMT>;
-    // Row pitch in shared memory: an odd multiple of the unit's load width (16 bytes for the
-    // 4-bit formats, 8 for Q8_0), so that the 32 lanes of a warp hit distinct banks.
-    static constexpr int ROW_STRIDE = kKS * T::UB + (FMT == RUNIT_FMT_Q8_0 ? 8 : 16);
-    static constexpr int W_BYTES = kRT * ROW_STRIDE;
-    static constexpr int XE = kKS * T::UE;                         // activations per stage per batch row
+    static constexpr int W_BYTES = kRT * T::UB;                    // dense rows, pitch UB
     static constexpr int XR_OFF = W_BYTES;                         // raw f16 activations (XF16 only)
-    static constexpr int XR_BYTES = XF16 ? B * XE * 2 : 0;
+    static constexpr int XR_BYTES = XF16 ? B * T::UE * 2 : 0;
     static constexpr int XP_OFF = XR_OFF + XR_BYTES;               // prepared f32 activations
-    static constexpr int XP_BYTES = B * XE * 4;
+    static constexpr int XP_BYTES = B * T::UE * 4;
     static constexpr int XS_OFF = XP_OFF + XP_BYTES;               // 32-element block sums (Q4_K)
-    static constexpr int XS_BYTES = (FMT == RUNIT_FMT_Q4K) ? B * kKS * 8 * 4 : 0;
-    static constexpr int BYTES = XS_OFF + XS_BYTES;
-    static_assert(BYTES % 16 == 0, "stage must stay 16-byte aligned");
+    static constexpr int XS_BYTES = (FMT == RUNIT_FMT_Q4K) ? B * 8 * 4 : 0;
+    // padded to 128 bytes: the destination of a tiled bulk load must be 128-byte aligned
+    static constexpr int BYTES = (XS_OFF + XS_BYTES + 127) / 128 * 128;
+    static_assert(W_BYTES % 16 == 0 && XP_OFF % 16 == 0 && XS_OFF % 16 == 0, "regions stay 16-byte aligned");
 };
 
 enum { RES_NONE = 0, RES_F32 = 1, RES_F16 = 2 };
@@ -64,66 +66,106 @@ struct GemvArgs {
     GemvSeg seg[3];
     int32_t nseg;
     const void* x;
-    uint32_t k, nb, row_bytes, n_units, n_stages;
+    uint32_t k, nb, row_bytes, n_units;
     uint32_t ldy;          // elements between batch rows of y / residual
     int32_t out_f16, res_kind, bias_kind, dual;
+    int32_t* status;       // host-visible word: set non-zero if a bounded wait ran out
+};
+
+// Tensor maps of the weight matrices (bulk-load path): one per segment, plus the second matrix of
+// a fused gate/up launch in slot 3.
+struct GemvMaps {
+    CUtensorMap m[4];
 };
 
 // ───────────────────────── unit dot products ─────────────────────────
+// All take: up = this lane's unit in shared memory, xp = the unit's prepared activations
+// (batch stride XPS floats), and add the dot products into the running accumulators.
+//
+// Accumulation is organised for instruction-level parallelism: every bit-field position has its
+// own packed accumulator (short dependency chains), and block scales are applied with packed
+// FMAs into two running packed sums per batch row, which are only folded to a scalar at the very
+// end of the K loop.
 
-// One Q4_K superblock (144 bytes in shared memory) against B prepared activation slices.
-// Formula: crates/kernels/shaders/gemv_q4k.metal:85-122 (sum over pairs j of
-// (d*sc_j*q - dmin*m_j)*x for the low nibbles and the same with index j+4 for the high ones).
+struct RowAcc {
+    uint64_t t0, t1;   // packed partial sums
+    float s;           // scalar part (Q4_K min terms)
+};
+
+__device__ __forceinline__ float magic_byte(uint32_t w, int j) {
+    // float value of byte j of w without an int->float conversion instruction
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u | (uint32_t)j)) - kTwo23;
+}
+
+// One Q4_K superblock (144 bytes).  Formula: crates/kernels/shaders/gemv_q4k.metal:85-122
+// (sum over pairs j of (d*sc_j*q - dmin*m_j)*x for the low nibbles, index j+4 for the high ones).
 template <int B, int XPS, int XSS>
-__device__ __forceinline__ void unit_q4k(const uint8_t* up, const float* xp, const float* xs, float (&acc)[B]) {
-    const uint4* u4 = reinterpret_cast<const uint4*>(up);
-    const uint4 h = u4[0];
-    const float d = half_bits_to_float(h.x), dmin = half_bits_to_float(h.x >> 16);
-    const Q4KScales s = q4k_unpack_scales(h);
-    const float2 m2 = make_float2(-kTwo23, -kTwo23);
+__device__ __forceinline__ void unit_q4k(const uint8_t* up, const float* xp, const float* xs, RowAcc (&acc)[B]) {
+    const ulonglong2* u = reinterpret_cast<const ulonglong2*>(up);
+    const ulonglong2 h = u[0];
+    const uint32_t h0 = (uint32_t)h.x;
+    const float d = half_bits_to_float(h0), dmin = half_bits_to_float(h0 >> 16);
+    const Q4KScales s = q4k_unpack_scales((uint32_t)(h.x >> 32), (uint32_t)h.y, (uint32_t)(h.y >> 32));
+    const uint64_t neg = packf(-kTwo23);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const float dl = d * byte_to_float(s.sl, j), ml = dmin * byte_to_float(s.ml, j);
-        const float dh = d * byte_to_float(s.sh, j), mh = dmin * byte_to_float(s.mh, j);
-        float2 al0[B], al1[B], ah0[B], ah1[B];
+        const float dl = d * magic_byte(s.sl, j), ml = dmin * magic_byte(s.ml, j);
+        const float dh = d * magic_byte(s.sh, j), mh = dmin * magic_byte(s.mh, j);
+        uint64_t al[B][4], ah[B][4];
 #pragma unroll
-        for (int b = 0; b < B; b++) al0[b] = al1[b] = ah0[b] = ah1[b] = make_float2(0.f, 0.f);
+        for (int b = 0; b < B; b++)
 #pragma unroll
-        for (int c4 = 0; c4 < 2; c4++) {
-            const uint4 q = u4[1 + 2 * j + c4];
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            for (int f = 0; f < 4; f++) al[b][f] = ah[b][f] = 0ull;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const uint32_t v = w[c], v12 = v >> 12;
-                const float2 l01 = fadd2(bits2((v & 0xFu) | kMagic, (v & 0xF00u) | kMagic), m2);
-                const float2 l23 = fadd2(bits2((v & 0xF0000u) | kMagic, (v12 & 0xF000u) | kMagic), m2);
-                const float2 h01 = fadd2(bits2((v & 0xF0u) | kMagic, (v & 0xF000u) | kMagic), m2);
-                const float2 h23 = fadd2(bits2((v12 & 0xF00u) | kMagic, (v12 & 0xF0000u) | kMagic), m2);
+        for (int n2 = 0; n2 < 2; n2++) {
+            const ulonglong2 q = u[1 + 2 * j + n2];
+#pragma unroll
+            for (int t = 0; t < 2; t++) {
+                const uint64_t P = t ? q.y : q.x, P12 = P >> 12;
+                const int n = 2 * n2 + t;   // 8-element group of the sub-block
+                const uint64_t l0 = fadd2(field_or_magic<0xFu << 0>(P), neg);
+                const uint64_t l1 = fadd2(field_or_magic<0xFu << 8>(P), neg);
+                const uint64_t l2 = fadd2(field_or_magic<0xFu << 16>(P), neg);
+                const uint64_t l3 = fadd2(field_or_magic<0xFu << 12>(P12), neg);
+                const uint64_t g0 = fadd2(field_or_magic<0xFu << 4>(P), neg);
+                const uint64_t g1 = fadd2(field_or_magic<0xFu << 12>(P), neg);
+                const uint64_t g2 = fadd2(field_or_magic<0xFu << 8>(P12), neg);
+                const uint64_t g3 = fadd2(field_or_magic<0xFu << 16>(P12), neg);
 #pragma unroll
                 for (int b = 0; b < B; b++) {
-                    const float4 xl = *reinterpret_cast<const float4*>(xp + b * XPS + 64 * j + 16 * c4 + 4 * c);
-                    const float4 xh = *reinterpret_cast<const float4*>(xp + b * XPS + 64 * j + 32 + 16 * c4 + 4 * c);
-                    al0[b] = ffma2(l01, make_float2(xl.x, xl.y), al0[b]);
-                    al1[b] = ffma2(l23, make_float2(xl.z, xl.w), al1[b]);
-                    ah0[b] = ffma2(h01, make_float2(xh.x, xh.y), ah0[b]);
-                    ah1[b] = ffma2(h23, make_float2(xh.z, xh.w), ah1[b]);
+                    const float* xb = xp + b * XPS + 64 * j + 8 * n;
+                    const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(xb);
+                    const ulonglong2 xc = *reinterpret_cast<const ulonglong2*>(xb + 4);
+                    const ulonglong2 ya = *reinterpret_cast<const ulonglong2*>(xb + 32);
+                    const ulonglong2 yc = *reinterpret_cast<const ulonglong2*>(xb + 36);
+                    al[b][0] = ffma2(l0, xa.x, al[b][0]);
+                    al[b][1] = ffma2(l1, xa.y, al[b][1]);
+                    al[b][2] = ffma2(l2, xc.x, al[b][2]);
+                    al[b][3] = ffma2(l3, xc.y, al[b][3]);
+                    ah[b][0] = ffma2(g0, ya.x, ah[b][0]);
+                    ah[b][1] = ffma2(g1, ya.y, ah[b][1]);
+                    ah[b][2] = ffma2(g2, yc.x, ah[b][2]);
+                    ah[b][3] = ffma2(g3, yc.y, ah[b][3]);
                 }
             }
         }
+        const uint64_t dl2 = packf(dl), dh2 = packf(dh);
 #pragma unroll
         for (int b = 0; b < B; b++) {
-            const float sl = (al0[b].x + al0[b].y) + (al1[b].x + al1[b].y);
-            const float sh = (ah0[b].x + ah0[b].y) + (ah1[b].x + ah1[b].y);
-            const float Xl = xs[b * XSS + 2 * j], Xh = xs[b * XSS + 2 * j + 1];
-            acc[b] += (dl * sl - ml * Xl) + (dh * sh - mh * Xh);
+            acc[b].t0 = ffma2(dl2, fadd2(al[b][0], al[b][1]), acc[b].t0);
+            acc[b].t1 = ffma2(dl2, fadd2(al[b][2], al[b][3]), acc[b].t1);
+            acc[b].t0 = ffma2(dh2, fadd2(ah[b][0], ah[b][1]), acc[b].t0);
+            acc[b].t1 = ffma2(dh2, fadd2(ah[b][2], ah[b][3]), acc[b].t1);
+            acc[b].s = fmaf(-ml, xs[b * XSS + 2 * j], acc[b].s);
+            acc[b].s = fmaf(-mh, xs[b * XSS + 2 * j + 1], acc[b].s);
         }
     }
 }
 
-// Eight Q4_0 blocks (144 bytes) against B prepared slices.  Formula:
-// crates/kernels/shaders/gemv_q4_0.metal:26-49 (d * sum((nib-8)*x), interleaved nibbles).
+// Eight Q4_0 blocks (144 bytes).  Formula: crates/kernels/shaders/gemv_q4_0.metal:26-49
+// (d * sum((nib-8)*x), low nibble = element 2i, high nibble = element 2i+1).
 template <int B, int XPS>
-__device__ __forceinline__ void unit_q4_0(const uint8_t* up, const float* xp, int nblk, float (&acc)[B]) {
+__device__ __forceinline__ void unit_q4_0(const uint8_t* up, const float* xp, int nblk, RowAcc (&acc)[B]) {
     const uint4* u4 = reinterpret_cast<const uint4*>(up);
     uint32_t w[36];
 #pragma unroll
@@ -134,45 +176,53 @@ __device__ __forceinline__ void unit_q4_0(const uint8_t* up, const float* xp, in
 #pragma unroll
     for (int blk = 0; blk < 8; blk++) {
         if (blk < nblk) {
-            const int o0 = 18 * blk;
+            const int o0 = 18 * blk, s = (o0 + 2) >> 2;
             const uint32_t dw = w[o0 >> 2];
-            const float d = half_bits_to_float((o0 & 2) ? (dw >> 16) : dw);
-            float2 a0[B], a1[B];
+            const uint64_t d2 = packf(half_bits_to_float((o0 & 2) ? (dw >> 16) : dw));
+            uint32_t Q[4];
 #pragma unroll
-            for (int b = 0; b < B; b++) a0[b] = a1[b] = make_float2(0.f, 0.f);
+            for (int i = 0; i < 4; i++)   // the 16 quant bytes start 2 bytes into a word in even blocks
+                Q[i] = ((o0 + 2) & 2) ? __funnelshift_r(w[s + i], w[s + i + 1], 16) : w[s + i];
+            uint64_t a[B][8];
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                // bytes i and i+1 of the block: element pairs (2i, 2i+1) and (2i+2, 2i+3)
-                float2 q2[2];
-#pragma unroll
-                for (int t = 0; t < 2; t++) {
-                    const int o = o0 + 2 + i + t, bp = o & 3;
-                    const uint32_t v = w[o >> 2], v12 = v >> 12;
-                    uint32_t lo, hi;
-                    float cl, ch;
-                    if (bp == 0)      { lo = v & 0xFu;       hi = v & 0xF0u;       cl = 8.f;      ch = 128.f; }
-                    else if (bp == 1) { lo = v & 0xF00u;     hi = v & 0xF000u;     cl = 2048.f;   ch = 32768.f; }
-                    else if (bp == 2) { lo = v & 0xF0000u;   hi = v12 & 0xF00u;    cl = 524288.f; ch = 2048.f; }
-                    else              { lo = v12 & 0xF000u;  hi = v12 & 0xF0000u;  cl = 32768.f;  ch = 524288.f; }
-                    q2[t] = fadd2(bits2(lo | kMagic, hi | kMagic), make_float2(-(kTwo23 + cl), -(kTwo23 + ch)));
-                }
+            for (int g = 0; g < 2; g++) {
+                const uint64_t P = pack2(Q[2 * g], Q[2 * g + 1]), P12 = P >> 12;
+                // field i = nibble at bit 4i of both words (bits above 16 are read from P >> 12)
+                uint64_t f[8];
+                f[0] = fadd2(field_or_magic<0xFu << 0>(P), packf(-(kTwo23 + 8.0f)));
+                f[1] = fadd2(field_or_magic<0xFu << 4>(P), packf(-(kTwo23 + 128.0f)));
+                f[2] = fadd2(field_or_magic<0xFu << 8>(P), packf(-(kTwo23 + 2048.0f)));
+                f[3] = fadd2(field_or_magic<0xFu << 12>(P), packf(-(kTwo23 + 32768.0f)));
+                f[4] = fadd2(field_or_magic<0xFu << 16>(P), packf(-(kTwo23 + 524288.0f)));
+                f[5] = fadd2(field_or_magic<0xFu << 8>(P12), packf(-(kTwo23 + 2048.0f)));
+                f[6] = fadd2(field_or_magic<0xFu << 12>(P12), packf(-(kTwo23 + 32768.0f)));
+                f[7] = fadd2(field_or_magic<0xFu << 16>(P12), packf(-(kTwo23 + 524288.0f)));
 #pragma unroll
                 for (int b = 0; b < B; b++) {
-                    const float4 x4 = *reinterpret_cast<const float4*>(xp + b * XPS + 32 * blk + 2 * i);
-                    a0[b] = ffma2(q2[0], make_float2(x4.x, x4.y), a0[b]);
-                    a1[b] = ffma2(q2[1], make_float2(x4.z, x4.w), a1[b]);
+                    const float* xb = xp + b * XPS + 32 * blk + 16 * g;
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++) {
+                        const ulonglong2 xv = *reinterpret_cast<const ulonglong2*>(xb + 4 * k4);
+                        a[b][2 * k4] = ffma2(f[2 * k4], xv.x, g ? a[b][2 * k4] : 0ull);
+                        a[b][2 * k4 + 1] = ffma2(f[2 * k4 + 1], xv.y, g ? a[b][2 * k4 + 1] : 0ull);
+                    }
                 }
             }
 #pragma unroll
-            for (int b = 0; b < B; b++) acc[b] += d * ((a0[b].x + a0[b].y) + (a1[b].x + a1[b].y));
+            for (int b = 0; b < B; b++) {
+                const uint64_t s01 = fadd2(fadd2(a[b][0], a[b][1]), fadd2(a[b][2], a[b][3]));
+                const uint64_t s23 = fadd2(fadd2(a[b][4], a[b][5]), fadd2(a[b][6], a[b][7]));
+                acc[b].t0 = ffma2(d2, s01, acc[b].t0);
+                acc[b].t1 = ffma2(d2, s23, acc[b].t1);
+            }
         }
     }
 }
 
-// Four Q8_0 blocks (136 bytes, 8-byte aligned) against B slices.  Formula:
+// Four Q8_0 blocks (136 bytes, 8-byte aligned).  Formula:
 // crates/kernels/shaders/gemv_q8_0.metal:24-36 (d * sum(int8 * x)).
 template <int B, int XPS>
-__device__ __forceinline__ void unit_q8_0(const uint8_t* up, const float* xp, int nblk, float (&acc)[B]) {
+__device__ __forceinline__ void unit_q8_0(const uint8_t* up, const float* xp, int nblk, RowAcc (&acc)[B]) {
     const uint2* u2 = reinterpret_cast<const uint2*>(up);
     uint32_t w[34];
 #pragma unroll
@@ -180,196 +230,272 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t* up, const float* xp, in
         const uint2 q = u2[i];
         w[2 * i] = q.x; w[2 * i + 1] = q.y;
     }
-    const float2 m2 = make_float2(-(kTwo23 + 128.f), -(kTwo23 + 128.f));
+    // int8 -> biased uint8 and magic in one LOP3: ((v & mask) ^ c), c = (0x80<<p | 2^23 bits)
+    const uint64_t n0 = packf(-(kTwo23 + 128.0f)), n8 = packf(-(kTwo23 + 32768.0f));
 #pragma unroll
     for (int blk = 0; blk < 4; blk++) {
         if (blk < nblk) {
-            const int o0 = 34 * blk;
+            const int o0 = 34 * blk, s = (o0 + 2) >> 2;
             const uint32_t dw = w[o0 >> 2];
-            const float d = half_bits_to_float((o0 & 2) ? (dw >> 16) : dw);
-            float2 a0[B], a1[B];
+            const uint64_t d2 = packf(half_bits_to_float((o0 & 2) ? (dw >> 16) : dw));
+            uint64_t a[B][4];
 #pragma unroll
-            for (int b = 0; b < B; b++) a0[b] = a1[b] = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                float2 q2[2];
-#pragma unroll
-                for (int t = 0; t < 2; t++) {
-                    const int o = o0 + 2 + i + 2 * t, bp = o & 3;   // o is even: bytes o, o+1 share a word
-                    const uint32_t wx = w[o >> 2] ^ 0x80808080u;    // int8 -> biased uint8
-                    q2[t] = fadd2(bits2(__byte_perm(wx, kMagic, 0x7540 | bp), __byte_perm(wx, kMagic, 0x7540 | (bp + 1))), m2);
+            for (int n = 0; n < 4; n++) {
+                uint32_t q0, q1;
+                if ((o0 + 2) & 2) {
+                    q0 = __funnelshift_r(w[s + 2 * n], w[s + 2 * n + 1], 16);
+                    q1 = __funnelshift_r(w[s + 2 * n + 1], w[s + 2 * n + 2], 16);
+                } else {
+                    q0 = w[s + 2 * n];
+                    q1 = w[s + 2 * n + 1];
                 }
+                const uint64_t P = pack2(q0, q1), P16 = P >> 16;
+                const uint64_t f0 = fadd2(field_xor<0xFFu, 0x4B000080u>(P), n0);
+                const uint64_t f1 = fadd2(field_xor<0xFF00u, 0x4B008000u>(P), n8);
+                const uint64_t f2 = fadd2(field_xor<0xFFu, 0x4B000080u>(P16), n0);
+                const uint64_t f3 = fadd2(field_xor<0xFF00u, 0x4B008000u>(P16), n8);
 #pragma unroll
                 for (int b = 0; b < B; b++) {
-                    const float4 x4 = *reinterpret_cast<const float4*>(xp + b * XPS + 32 * blk + i);
-                    a0[b] = ffma2(q2[0], make_float2(x4.x, x4.y), a0[b]);
-                    a1[b] = ffma2(q2[1], make_float2(x4.z, x4.w), a1[b]);
+                    const float* xb = xp + b * XPS + 32 * blk + 8 * n;
+                    const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(xb);
+                    const ulonglong2 xc = *reinterpret_cast<const ulonglong2*>(xb + 4);
+                    a[b][0] = ffma2(f0, xa.x, n ? a[b][0] : 0ull);
+                    a[b][1] = ffma2(f1, xa.y, n ? a[b][1] : 0ull);
+                    a[b][2] = ffma2(f2, xc.x, n ? a[b][2] : 0ull);
+                    a[b][3] = ffma2(f3, xc.y, n ? a[b][3] : 0ull);
                 }
             }
 #pragma unroll
-            for (int b = 0; b < B; b++) acc[b] += d * ((a0[b].x + a0[b].y) + (a1[b].x + a1[b].y));
+            for (int b = 0; b < B; b++) {
+                acc[b].t0 = ffma2(d2, fadd2(a[b][0], a[b][1]), acc[b].t0);
+                acc[b].t1 = ffma2(d2, fadd2(a[b][2], a[b][3]), acc[b].t1);
+            }
         }
     }
 }
 
 // ───────────────────────── staged kernel ─────────────────────────
+// LD = 0: weights and activations arrive with per-thread cp.async copies (any row alignment >= 4).
+// LD = 1: one elected lane per warp issues a 2-D tiled bulk load (TMA) of the 32-row x 1-unit box
+//         and a 1-D bulk copy of the activation slice; completion is tracked by one mbarrier per
+//         stage and warp.  Needs 16-byte aligned rows (always true for the 4-bit formats here).
 
-template <int FMT, int B, bool XF16, int CPB, int S>
-__global__ void __launch_bounds__(kNT) gemv_staged_kernel(const GemvArgs a) {
+template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD>
+__global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, const __grid_constant__ GemvMaps maps) {
     using T = Traits<FMT>;
-    using L = StageLayout<FMT, B, XF16>;
-    extern __shared__ __align__(128) uint8_t smem[];
+    using L = WarpStage<FMT, B, XF16>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float red[kKS][kRT][B];
+    __shared__ __align__(8) uint64_t mbar[kKS][4];
 
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    uint8_t* ring = smem + warp * (S * L::BYTES);
+    const uint32_t ring_u32 = smem_u32(ring);
+    const uint32_t bar0 = smem_u32(&mbar[warp][0]);
 
-    // Which segment / tile is this CTA?
     int si = 0;
 #pragma unroll
     for (int i = 1; i < 3; i++)
         if (i < a.nseg && blockIdx.x >= a.seg[i].tile_begin) si = i;
     const GemvSeg sg = a.seg[si];
-    const int rows_per_tile = a.dual ? kRT / 2 : kRT;
-    const uint32_t row0 = (blockIdx.x - sg.tile_begin) * rows_per_tile;
+    constexpr int RPT = DUAL ? kRT / 2 : kRT;   // real rows per tile
+    const uint32_t row0 = (blockIdx.x - sg.tile_begin) * RPT;
+    const uint32_t rows_here = min((uint32_t)RPT, sg.rows - row0);
+    const bool row_ok = (uint32_t)(DUAL ? (lane & 15) : lane) < rows_here;
+    const int n_it = ((int)a.n_units - warp + kKS - 1) / kKS;   // units warp, warp+4, ...
 
-    // Copy role: thread <-> (virtual row, quarter of the row's stage bytes).
-    const int crow = t >> 2, cq = t & 3;
-    const int crow_real = a.dual ? (crow & 15) : crow;
-    const bool crow_ok = row0 + crow_real < sg.rows;
-    const uint8_t* cw = (a.dual && crow >= 16) ? sg.w2 : sg.w;
-    const uint8_t* gsrc = cw + (size_t)(row0 + (crow_ok ? crow_real : 0)) * a.row_bytes + cq * CPB;
-    const uint32_t sdst = smem_u32(smem) + crow * L::ROW_STRIDE + cq * CPB;
-
-    auto issue = [&](int st) {
-        if (st < (int)a.n_stages) {
-            const uint32_t slot = (st % S) * L::BYTES;
-            const uint32_t off = (uint32_t)st * (kKS * T::UB);
-            const int vb = min((int)(kKS * T::UB), (int)(a.row_bytes - off));
-            if (crow_ok) {
-                const uint8_t* g = gsrc + off;
-                const uint32_t sd = sdst + slot;
-                constexpr int NCH = (kKS * T::UB / CPB + 3) / 4;
+    if (LD == 1) {
+        if (lane == 0) {
 #pragma unroll
-                for (int j = 0; j < NCH; j++) {
-                    const int bo = (cq + 4 * j) * CPB;
-                    if (bo < vb) {
-                        if (CPB == 16) cp_async16(sd + 4 * j * CPB, g + 4 * j * CPB);
-                        else if (CPB == 8) cp_async8(sd + 4 * j * CPB, g + 4 * j * CPB);
-                        else cp_async4(sd + 4 * j * CPB, g + 4 * j * CPB);
-                    }
+            for (int s = 0; s < S; s++) mbar_init(bar0 + 8 * s, 1);
+            fence_mbar_init();
+        }
+        __syncwarp();
+    }
+
+    constexpr int CPR = T::UB / CPB;        // copy chunks per row of one unit
+    constexpr int DR = 32 / CPR, DC = 32 % CPR;
+    const int c_row0 = lane / CPR, c_col0 = lane % CPR;
+
+    auto issue = [&](int it) {
+        if (LD == 1) {
+            if (it < n_it && lane == 0) {
+                const uint32_t u = warp + kKS * it;
+                const uint32_t slot = ring_u32 + (it % S) * L::BYTES;
+                const uint32_t bar = bar0 + 8 * (it % S);
+                const uint32_t e0 = u * T::UE;
+                const uint32_t nx = min((uint32_t)T::UE, a.k - e0);   // activations of this unit
+                const uint32_t xbytes = nx * (XF16 ? 2u : 4u);
+                fence_proxy_async();   // earlier generic-proxy accesses to this slot precede the bulk writes
+                mbar_expect_tx(bar, (uint32_t)L::W_BYTES + B * xbytes);
+                if (DUAL) {
+                    tma_load_2d(slot, &maps.m[0], (int32_t)(u * T::UB), (int32_t)row0, bar);
+                    tma_load_2d(slot + 16 * T::UB, &maps.m[3], (int32_t)(u * T::UB), (int32_t)row0, bar);
+                } else {
+                    tma_load_2d(slot, &maps.m[si], (int32_t)(u * T::UB), (int32_t)row0, bar);
+                }
+#pragma unroll
+                for (int b = 0; b < B; b++) {
+                    if (XF16)
+                        bulk_load_1d(slot + L::XR_OFF + b * T::UE * 2,
+                                     reinterpret_cast<const __half*>(a.x) + (size_t)b * a.k + e0, xbytes, bar);
+                    else
+                        bulk_load_1d(slot + L::XP_OFF + b * T::UE * 4,
+                                     reinterpret_cast<const float*>(a.x) + (size_t)b * a.k + e0, xbytes, bar);
                 }
             }
-            // activations of this stage
-            const uint32_t e0 = (uint32_t)st * L::XE;
+            return;
+        }
+        if (it < n_it) {
+            const uint32_t u = warp + kKS * it;
+            const uint32_t slot = ring_u32 + (it % S) * L::BYTES;
+            const uint32_t uoff = u * T::UB;
+            const int vb = min((int)T::UB, (int)(a.row_bytes - uoff));
+            int row = c_row0, col = c_col0;
+#pragma unroll
+            for (int j = 0; j < CPR; j++) {
+                const int rr = DUAL ? (row & 15) : row;
+                if (row < kRT && (uint32_t)rr < rows_here && col * CPB < vb) {
+                    const uint8_t* base = (DUAL && row >= 16) ? sg.w2 : sg.w;
+                    cp_async<CPB>(slot + row * T::UB + col * CPB,
+                                  base + (size_t)(row0 + rr) * a.row_bytes + uoff + col * CPB);
+                }
+                row += DR;
+                col += DC;
+                if (col >= CPR) { col -= CPR; row++; }
+            }
+            const uint32_t e0 = u * T::UE;
             if (XF16) {
                 const __half* xg = reinterpret_cast<const __half*>(a.x);
-                constexpr int NX = L::XE / 8;   // 16-byte chunks per batch row
 #pragma unroll
                 for (int b = 0; b < B; b++)
-                    for (int c = t; c < NX; c += kNT)
+#pragma unroll
+                    for (int c = lane; c < T::UE / 8; c += 32)
                         if (e0 + c * 8 < a.k)
-                            cp_async16(smem_u32(smem) + slot + L::XR_OFF + (b * L::XE + c * 8) * 2,
-                                       xg + (size_t)b * a.k + e0 + c * 8);
+                            cp_async16(slot + L::XR_OFF + (b * T::UE + c * 8) * 2, xg + (size_t)b * a.k + e0 + c * 8);
             } else {
                 const float* xg = reinterpret_cast<const float*>(a.x);
-                constexpr int NX = L::XE / 4;
 #pragma unroll
                 for (int b = 0; b < B; b++)
 #pragma unroll
-                    for (int c = t; c < NX; c += kNT)
+                    for (int c = lane; c < T::UE / 4; c += 32)
                         if (e0 + c * 4 < a.k)
-                            cp_async16(smem_u32(smem) + slot + L::XP_OFF + (b * L::XE + c * 4) * 4,
-                                       xg + (size_t)b * a.k + e0 + c * 4);
+                            cp_async16(slot + L::XP_OFF + (b * T::UE + c * 4) * 4, xg + (size_t)b * a.k + e0 + c * 4);
             }
         }
         cp_async_commit();
     };
 
-    // Prepare the activations of stage st: f16 -> f32, nibble-position pre-scaling, block sums.
-    auto prep = [&](int st) {
-        if (st >= (int)a.n_stages) return;
-        if (FMT == RUNIT_FMT_Q8_0 && !XF16) return;
-        uint8_t* slot = smem + (st % S) * L::BYTES;
-        constexpr int EPT = L::XE / kNT;   // 8 (4-bit formats) or 4 (Q8_0) consecutive elements
-        const int e = t * EPT;             // stage-local element index
-        const int eu = e % T::UE;          // unit-local
-#pragma unroll
-        for (int b = 0; b < B; b++) {
-            float v[EPT];
-            float* xp = reinterpret_cast<float*>(slot + L::XP_OFF) + b * L::XE + e;
-            if (XF16) {
-                const __half* xr = reinterpret_cast<const __half*>(slot + L::XR_OFF) + b * L::XE + e;
-#pragma unroll
-                for (int i = 0; i < EPT; i++) v[i] = __half2float(xr[i]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < EPT; i++) v[i] = xp[i];
-            }
-            // e is a multiple of EPT (8 for the 4-bit formats), so the position inside a qs
-            // word depends only on i; the half of the pair (Q4_K) or the block parity (Q4_0)
-            // is uniform over the thread's elements.
-            const int par = (eu >> 5) & 1;
-            if (FMT == RUNIT_FMT_Q4K) {
-                float s = 0.f;
-#pragma unroll
-                for (int i = 0; i < EPT; i++) s += v[i];
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                if ((t & 3) == 0) reinterpret_cast<float*>(slot + L::XS_OFF)[b * (kKS * 8) + (e >> 5)] = s;
-#pragma unroll
-                for (int i = 0; i < EPT; i++) v[i] *= par ? q4k_xscale(32 + i) : q4k_xscale(i);
-            } else if (FMT == RUNIT_FMT_Q4_0) {
-#pragma unroll
-                for (int i = 0; i < EPT; i++) v[i] *= par ? q4_0_xscale(32 + i) : q4_0_xscale(i);
-            }
-#pragma unroll
-            for (int i = 0; i < EPT; i++) xp[i] = v[i];
+    // Wait until stage `it` has landed for this lane (`pending` = cp.async groups that may stay open).
+    bool timed_out = false;
+    auto wait_stage = [&](int it, auto pending) {
+        if (LD == 1) {
+            // after one failed wait the warp stops waiting (its results are reported as invalid)
+            if (it < n_it && !timed_out && !mbar_wait(bar0 + 8 * (it % S), (uint32_t)(it / S) & 1u)) timed_out = true;
+        } else {
+            cp_async_wait<decltype(pending)::value>();
         }
     };
 
-    float acc[B];
+    // Prepare the activations of stage `it` (warp-private): f16 -> f32, permutation into the pair
+    // order of the weight words, pre-scaling by the nibble position, 32-element block sums.
+    auto prep = [&](int it) {
+        if (it >= n_it) return;
+        uint8_t* slot = ring + (it % S) * L::BYTES;
+        constexpr int EPL = T::UE / 32;   // 8 (4-bit formats) or 4 (Q8_0) consecutive elements per lane
+        float v[B][EPL];
 #pragma unroll
-    for (int b = 0; b < B; b++) acc[b] = 0.f;
+        for (int b = 0; b < B; b++) {
+            if (XF16) {
+                const __half* xr = reinterpret_cast<const __half*>(slot + L::XR_OFF) + b * T::UE + lane * EPL;
+#pragma unroll
+                for (int i = 0; i < EPL; i++) v[b][i] = __half2float(xr[i]);
+            } else {
+                const float4* xr = reinterpret_cast<const float4*>(slot + L::XP_OFF) + (b * T::UE + lane * EPL) / 4;
+#pragma unroll
+                for (int i = 0; i < EPL / 4; i++) {
+                    const float4 t4 = xr[i];
+                    v[b][4 * i] = t4.x; v[b][4 * i + 1] = t4.y; v[b][4 * i + 2] = t4.z; v[b][4 * i + 3] = t4.w;
+                }
+            }
+        }
+        __syncwarp();   // in-place: every lane has read its inputs before anyone overwrites them
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            float* xp = reinterpret_cast<float*>(slot + L::XP_OFF) + b * T::UE;
+            if (FMT == RUNIT_FMT_Q4K) {
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < EPL; i++) sum += v[b][i];
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if ((lane & 3) == 0) reinterpret_cast<float*>(slot + L::XS_OFF)[b * 8 + (lane >> 2)] = sum;
+                // elements 8*lane .. 8*lane+7: sub-block half = (lane>>2)&1, byte position = i%4.
+                // low half: 2^-{0,8,16,12}; high half: 2^-{4,12,8,16}: the high-half exponent is the
+                // low-half one + 4 for byte positions 0,1,3... except position 2 (16 -> 8)
+                const bool hi = (lane >> 2) & 1;
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    o[pos8(i)] = v[b][i] * (hi ? exp2_neg(q4k_shift(i & 3, true)) : exp2_neg(q4k_shift(i & 3, false)));
+                float4* dst = reinterpret_cast<float4*>(xp + 8 * lane);
+                dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+                dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+            } else if (FMT == RUNIT_FMT_Q4_0) {
+                // element t of this lane: field 2*(t/2)+(t%2) = t of its word; stored as pair member lane&1
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    xp[16 * (lane >> 1) + 2 * i + (lane & 1)] = v[b][i] * exp2_neg(q4_0_shift(i >> 1, i & 1));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    xp[8 * (lane >> 1) + 2 * i + (lane & 1)] = v[b][i] * exp2_neg(q8_0_shift(i));
+            }
+        }
+    };
 
-    const bool row_ok = a.dual ? (row0 + (lane & 15) < sg.rows) : (row0 + lane < sg.rows);
+    RowAcc acc[B];
+#pragma unroll
+    for (int b = 0; b < B; b++) { acc[b].t0 = 0ull; acc[b].t1 = 0ull; acc[b].s = 0.f; }
 
 #pragma unroll
     for (int s = 0; s < S - 1; s++) issue(s);
-    cp_async_wait<S - 2>();
-    __syncthreads();
+    wait_stage(0, std::integral_constant<int, S - 2>());
+    __syncwarp();
     prep(0);
 
-    for (int st = 0; st < (int)a.n_stages; st++) {
-        cp_async_wait<S - 3>();          // stages <= st+1 have landed
-        __syncthreads();                 // slot (st-1)%S is free; prep(st) is visible
-        issue(st + S - 1);
-        prep(st + 1);
-        const uint32_t u = (uint32_t)st * kKS + warp;
-        if (row_ok && u < a.n_units) {
-            const uint8_t* slot = smem + (st % S) * L::BYTES;
-            const uint8_t* up = slot + lane * L::ROW_STRIDE + warp * T::UB;
-            const float* xp = reinterpret_cast<const float*>(slot + L::XP_OFF) + warp * T::UE;
+    for (int it = 0; it < n_it; it++) {
+        wait_stage(it + 1, std::integral_constant<int, S - 3>());   // this lane sees stage it+1
+        __syncwarp();             // ... and everyone's copies; prep(it) is visible; slot (it-1)%S is free
+        issue(it + S - 1);
+        prep(it + 1);
+        if (row_ok) {
+            const uint32_t u = warp + kKS * it;
+            const uint8_t* slot = ring + (it % S) * L::BYTES;
+            const uint8_t* up = slot + lane * T::UB;
+            const float* xp = reinterpret_cast<const float*>(slot + L::XP_OFF);
             if (FMT == RUNIT_FMT_Q4K) {
-                const float* xs = reinterpret_cast<const float*>(slot + L::XS_OFF) + warp * 8;
-                unit_q4k<B, L::XE, kKS * 8>(up, xp, xs, acc);
+                unit_q4k<B, T::UE, 8>(up, xp, reinterpret_cast<const float*>(slot + L::XS_OFF), acc);
             } else if (FMT == RUNIT_FMT_Q4_0) {
-                unit_q4_0<B, L::XE>(up, xp, min(T::BPU, (int)(a.nb - u * T::BPU)), acc);
+                unit_q4_0<B, T::UE>(up, xp, min(T::BPU, (int)(a.nb - u * T::BPU)), acc);
             } else {
-                unit_q8_0<B, L::XE>(up, xp, min(T::BPU, (int)(a.nb - u * T::BPU)), acc);
+                unit_q8_0<B, T::UE>(up, xp, min(T::BPU, (int)(a.nb - u * T::BPU)), acc);
             }
         }
     }
-    cp_async_wait<0>();
+    if (LD == 0) cp_async_wait<0>();
+    if (timed_out && a.status) atomicExch(a.status, 1);
 
     // Add the four K-slices of each row in slice order, then the epilogue.
 #pragma unroll
-    for (int b = 0; b < B; b++) red[warp][lane][b] = acc[b];
+    for (int b = 0; b < B; b++) red[warp][lane][b] = (sum2(acc[b].t0) + sum2(acc[b].t1)) + acc[b].s;
     __syncthreads();
     if (warp == 0) {
         float r[B];
 #pragma unroll
         for (int b = 0; b < B; b++) r[b] = ((red[0][lane][b] + red[1][lane][b]) + red[2][lane][b]) + red[3][lane][b];
-        if (a.dual) {
+        if (DUAL) {
             // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows:
             // act = silu(gate) * up  (crates/kernels/shaders/fused_ffn.metal:24-26,89-92)
 #pragma unroll
@@ -378,8 +504,8 @@ __global__ void __launch_bounds__(kNT) gemv_staged_kernel(const GemvArgs a) {
                 r[b] = silu(r[b]) * up_v;
             }
         }
-        const uint32_t row = row0 + (a.dual ? (lane & 15) : lane);
-        const bool writer = a.dual ? (lane < 16 && row < sg.rows) : (row < sg.rows);
+        const uint32_t row = row0 + (DUAL ? (lane & 15) : lane);
+        const bool writer = DUAL ? (lane < 16 && row_ok) : row_ok;
         if (writer) {
 #pragma unroll
             for (int b = 0; b < B; b++) {
@@ -409,7 +535,7 @@ __global__ void __launch_bounds__(128) gemv_simple_kernel(const GemvArgs a, int 
     {
         uint32_t acc_rows = 0;
         for (int i = 0; i < a.nseg; i++) {
-            const uint32_t nr = a.dual ? a.seg[i].rows : a.seg[i].rows;
+            const uint32_t nr = a.seg[i].rows;
             if (grow >= acc_rows && grow < acc_rows + nr) { si = i; base = acc_rows; }
             acc_rows += nr;
         }

@@ -1,6 +1,7 @@
 // Internal definitions shared by the translation units of librunit_cuda.so.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 
@@ -15,6 +16,15 @@ struct runit_tuning {
     int32_t gemv_stages = 0;    // 0 = default
     int32_t moe_variant = 0;
     int32_t pdl = 0;            // programmatic dependent launch between ops
+    int32_t gemv_load = 0;      // 0 = tiled bulk loads (TMA) where rows allow, 1 = cp.async everywhere
+};
+
+// Cached tensor map of one weight matrix view (encoding costs ~1 us on the host).
+struct runit_tmap_entry {
+    const void* ptr = nullptr;
+    uint64_t rows = 0, row_bytes = 0;
+    uint32_t box_rows = 0, box_bytes = 0;
+    CUtensorMap map;
 };
 
 // One per GPU; replaces the reference's MetalContext (crates/kernels/src/context.rs:137-160).
@@ -25,12 +35,20 @@ struct runit_ctx {
     int32_t sm_count = 0;
     int32_t max_smem_optin = 0;
     uint64_t launches = 0;
+    bool capturing = false;             // a command list is being recorded on the stream
     int32_t sticky_status = RUNIT_OK;   // first error since the last flush
     char err[512] = {0};
     runit_tuning tune;
     // Device scratch owned by the context (allocated at creation; ops never allocate).
-    int32_t* d_status = nullptr;        // status word written by kernels with bounded waits
+    int32_t* d_status = nullptr;        // device address of the status word written by kernels with bounded waits
+    int32_t* h_status = nullptr;        // the same word, host side (pinned, mapped)
+    void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation
+    runit_tmap_entry tmaps[256];
 };
+
+// Tensor map of a [rows][row_bytes] byte matrix with a [box_rows][box_bytes] box (cached per context).
+int32_t runit_get_tmap(runit_ctx* ctx, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                       uint32_t box_bytes, CUtensorMap* out);
 
 const char* runit_status_name(int32_t st);
 

@@ -145,11 +145,35 @@ class Context:
     def set_tuning(self, key: str, value: int):
         self._check(self.lib.runit_set_tuning(self.handle, key.encode(), value))
 
+    # Recorded command lists (the role of the reference's command buffer, context.rs:248-296).
+    def graph_begin(self):
+        self._check(self.lib.runit_graph_begin(self.handle))
+
+    def graph_end(self) -> "Graph":
+        g = C.c_void_p()
+        self._check(self.lib.runit_graph_end(self.handle, C.byref(g)))
+        return Graph(self, g)
+
     def call(self, name: str, *args):
         """Call ``runit_<name>(ctx, *args)``; buffers may be DeviceBuffers, ints or torch tensors."""
         fn = getattr(self.lib, "runit_" + name)
         conv = [(_ptr(a) if (isinstance(a, DeviceBuffer) or hasattr(a, "data_ptr") or a is None) else a) for a in args]
         self._check(fn(self.handle, *conv))
+
+
+class Graph:
+    """A recorded list of ops that replays with one launch."""
+
+    def __init__(self, ctx: Context, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def launch(self):
+        self.ctx._check(self.ctx.lib.runit_graph_launch(self.ctx.handle, self.handle))
+
+    def destroy(self):
+        if self.handle:
+            self.ctx.lib.runit_graph_destroy(self.ctx.handle, self.handle)
+            self.handle = None
 
 
 def _twin(name: str, doc: str):
@@ -202,5 +226,5 @@ for _n, _d in _TWINS:
     globals()[_n] = _twin(_n, _d)
 del _n, _d
 
-__all__ = ["Context", "DeviceBuffer", "KernelError", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
            "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K"] + [n for n, _ in _TWINS]

@@ -15,11 +15,16 @@ def assert_close(oracle, ref, got, rel_tol=REL_TOL, what=""):
     return st
 
 
-def f16_ulp_close(ref16, got16, ulps=1):
-    """f16 outputs: equal up to `ulps` units in the last place (the f32 sum feeding the rounding
-    differs in order between implementations)."""
+def f16_ulp_close(ref16, got16, ulps=1, rel_tol=REL_TOL):
+    """f16 outputs: equal to the rounded oracle up to `ulps` units in the last place, or — where the
+    dot product cancels to a value far below its terms — within rel_tol of the output scale (the f32
+    sum feeding the rounding differs in order between implementations)."""
     a = np.asarray(ref16, np.float16).view(np.int16).astype(np.int32)
     b = np.asarray(got16, np.float16).view(np.int16).astype(np.int32)
     a = np.where(a < 0, -(a & 0x7FFF), a)
     b = np.where(b < 0, -(b & 0x7FFF), b)
-    return np.abs(a - b).max() <= ulps
+    rf = np.asarray(ref16, np.float16).astype(np.float32)
+    gf = np.asarray(got16, np.float16).astype(np.float32)
+    scale = np.maximum(np.abs(rf), np.sqrt(np.mean(rf.astype(np.float64) ** 2)))
+    ok = (np.abs(a - b) <= ulps) | (np.abs(rf - gf) <= rel_tol * scale)
+    return bool(ok.all()) and bool(np.isfinite(gf).all())
