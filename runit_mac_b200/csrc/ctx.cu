@@ -170,6 +170,7 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "moe_variant")) ctx->tune.moe_variant = value;
     else if (!strcmp(key, "pdl")) ctx->tune.pdl = value;
     else if (!strcmp(key, "gemv_load")) ctx->tune.gemv_load = value;
+    else if (!strcmp(key, "gemv_ksl")) ctx->tune.gemv_ksl = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
     return RUNIT_OK;
 }

@@ -80,6 +80,7 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
                          : c.fmt == RUNIT_FMT_Q4_0 ? Traits<RUNIT_FMT_Q4_0>::BPU : Traits<RUNIT_FMT_Q4K>::BPU;
     a.n_units = (a.nb + bpu - 1) / bpu;
     a.status = ctx->d_status;
+    a.n_tiles = tiles;
     // Tiled bulk loads (TMA) for the 4-bit formats: one tensor map per weight matrix.
     GemvMaps maps;
     const bool tma = !simple && c.fmt != RUNIT_FMT_Q8_0 && ctx->tune.gemv_load == 0 && ctx->encode_tiled != nullptr;

@@ -66,7 +66,7 @@ struct GemvArgs {
     GemvSeg seg[3];
     int32_t nseg;
     const void* x;
-    uint32_t k, nb, row_bytes, n_units;
+    uint32_t k, nb, row_bytes, n_units, n_tiles;
     uint32_t ldy;          // elements between batch rows of y / residual
     int32_t out_f16, res_kind, bias_kind, dual;
     int32_t* status;       // host-visible word: set non-zero if a bounded wait ran out
@@ -280,8 +280,11 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t* up, const float* xp, in
 //         and a 1-D bulk copy of the activation slice; completion is tracked by one mbarrier per
 //         stage and warp.  Needs 16-byte aligned rows (always true for the 4-bit formats here).
 
-template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD>
-__global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, const __grid_constant__ GemvMaps maps) {
+//
+// KSL = number of warps that share one 32-row tile (each takes every KSL-th unit of K); a CTA
+// holds 4/KSL tiles.  The host picks KSL so that the units divide evenly among the warps.
+template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int KSL>
+__global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const GemvArgs a, const __grid_constant__ GemvMaps maps) {
     using T = Traits<FMT>;
     using L = WarpStage<FMT, B, XF16>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -294,16 +297,20 @@ __global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, c
     const uint32_t ring_u32 = smem_u32(ring);
     const uint32_t bar0 = smem_u32(&mbar[warp][0]);
 
+    constexpr int TPC = kKS / KSL;              // tiles per CTA
+    const int slice = warp % KSL;
+    const uint32_t tile = blockIdx.x * TPC + warp / KSL;   // global tile index over all segments
     int si = 0;
 #pragma unroll
     for (int i = 1; i < 3; i++)
-        if (i < a.nseg && blockIdx.x >= a.seg[i].tile_begin) si = i;
+        if (i < a.nseg && tile >= a.seg[i].tile_begin) si = i;
     const GemvSeg sg = a.seg[si];
     constexpr int RPT = DUAL ? kRT / 2 : kRT;   // real rows per tile
-    const uint32_t row0 = (blockIdx.x - sg.tile_begin) * RPT;
-    const uint32_t rows_here = min((uint32_t)RPT, sg.rows - row0);
+    const uint32_t row0 = (tile - sg.tile_begin) * RPT;
+    const bool tile_ok = tile < a.n_tiles;
+    const uint32_t rows_here = tile_ok ? min((uint32_t)RPT, sg.rows - row0) : 0u;
     const bool row_ok = (uint32_t)(DUAL ? (lane & 15) : lane) < rows_here;
-    const int n_it = ((int)a.n_units - warp + kKS - 1) / kKS;   // units warp, warp+4, ...
+    const int n_it = tile_ok ? ((int)a.n_units - slice + KSL - 1) / KSL : 0;   // units slice, slice+KSL, ...
 
     if (LD == 1) {
         if (lane == 0) {
@@ -321,7 +328,7 @@ __global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, c
     auto issue = [&](int it) {
         if (LD == 1) {
             if (it < n_it && lane == 0) {
-                const uint32_t u = warp + kKS * it;
+                const uint32_t u = slice + KSL * it;
                 const uint32_t slot = ring_u32 + (it % S) * L::BYTES;
                 const uint32_t bar = bar0 + 8 * (it % S);
                 const uint32_t e0 = u * T::UE;
@@ -348,7 +355,7 @@ __global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, c
             return;
         }
         if (it < n_it) {
-            const uint32_t u = warp + kKS * it;
+            const uint32_t u = slice + KSL * it;
             const uint32_t slot = ring_u32 + (it % S) * L::BYTES;
             const uint32_t uoff = u * T::UB;
             const int vb = min((int)T::UB, (int)(a.row_bytes - uoff));
@@ -460,18 +467,15 @@ __global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, c
     for (int b = 0; b < B; b++) { acc[b].t0 = 0ull; acc[b].t1 = 0ull; acc[b].s = 0.f; }
 
 #pragma unroll
-    for (int s = 0; s < S - 1; s++) issue(s);
-    wait_stage(0, std::integral_constant<int, S - 2>());
-    __syncwarp();
-    prep(0);
+    for (int s = 0; s < S; s++) issue(s);
 
     for (int it = 0; it < n_it; it++) {
-        wait_stage(it + 1, std::integral_constant<int, S - 3>());   // this lane sees stage it+1
-        __syncwarp();             // ... and everyone's copies; prep(it) is visible; slot (it-1)%S is free
-        issue(it + S - 1);
-        prep(it + 1);
+        wait_stage(it, std::integral_constant<int, S - 1>());   // this lane's copies of stage `it` have landed
+        __syncwarp();                                           // ... and every lane's
+        prep(it);
+        __syncwarp();                                           // prepared activations visible to the warp
         if (row_ok) {
-            const uint32_t u = warp + kKS * it;
+            const uint32_t u = slice + KSL * it;
             const uint8_t* slot = ring + (it % S) * L::BYTES;
             const uint8_t* up = slot + lane * T::UB;
             const float* xp = reinterpret_cast<const float*>(slot + L::XP_OFF);
@@ -483,18 +487,24 @@ __global__ void __launch_bounds__(kNT, 3) gemv_staged_kernel(const GemvArgs a, c
                 unit_q8_0<B, T::UE>(up, xp, min(T::BPU, (int)(a.nb - u * T::BPU)), acc);
             }
         }
+        __syncwarp();             // every lane is done with slot it%S: refill it with stage it+S
+        issue(it + S);
     }
     if (LD == 0) cp_async_wait<0>();
     if (timed_out && a.status) atomicExch(a.status, 1);
 
-    // Add the four K-slices of each row in slice order, then the epilogue.
+    // Add the K-slices of each row in slice order, then the epilogue (first warp of each tile).
 #pragma unroll
     for (int b = 0; b < B; b++) red[warp][lane][b] = (sum2(acc[b].t0) + sum2(acc[b].t1)) + acc[b].s;
     __syncthreads();
-    if (warp == 0) {
+    if (slice == 0) {
         float r[B];
 #pragma unroll
-        for (int b = 0; b < B; b++) r[b] = ((red[0][lane][b] + red[1][lane][b]) + red[2][lane][b]) + red[3][lane][b];
+        for (int b = 0; b < B; b++) {
+            r[b] = red[warp][lane][b];
+#pragma unroll
+            for (int k = 1; k < KSL; k++) r[b] += red[warp + k][lane][b];
+        }
         if (DUAL) {
             // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows:
             // act = silu(gate) * up  (crates/kernels/shaders/fused_ffn.metal:24-26,89-92)
