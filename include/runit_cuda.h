@@ -164,6 +164,27 @@ int32_t runit_gemv_batched_f32(runit_ctx_t*, int32_t fmt, const void* weight, co
 int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
                                          void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,
                                          const void* bias_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+/* ── MoE block (no twin as one function; replaces the sequence crates/engine/src/forward.rs:1644-1679
+ *    and the CPU routing forward.rs:2420-2448, without the per-layer host synchronisation) ── */
+/* logits_f32[T][E] = router_f32[E][h] . x_f32[T][h] */
+int32_t runit_moe_router_f32(runit_ctx_t*, const void* router_w, const void* x, void* logits, uint32_t E, uint32_t h, uint32_t T);
+/* softmax over all E experts, top-k by probability (descending; ties: lowest index), weights optionally
+ * renormalised to sum 1.  logits: [T][E] f32, or f16 when logits_f16 != 0 (the reference's router dtype);
+ * out_idx: int32 [T][k]; out_w: f32 [T][k].  E <= 256, k <= 32. */
+int32_t runit_moe_route_topk(runit_ctx_t*, const void* logits, int32_t logits_f16, uint32_t E, uint32_t k, int32_t renorm,
+                             uint32_t T, void* out_idx, void* out_w);
+/* Scratch bytes runit_moe_layer_q4k needs for these shapes. */
+size_t runit_moe_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);
+/* One MoE block over T tokens, all on the device:
+ *   out[t] = (residual ? residual[t] : 0) + sum_i w_i * Wdown[e_i] . (silu(Wgate[e_i].x[t]) * (Wup[e_i].x[t]))
+ * router_w: f32 [E][h]; gate, up: Q4_K [E][ff][h]; down: Q4_K [E][h][ff] (experts stacked contiguously, as
+ * the reference slices merged expert tensors, forward.rs:1339-1408); x, residual, out: f32 [T][h] (out may
+ * alias residual); idx_out (int32 [T][k]) and w_out (f32 [T][k]) may be NULL; scratch: caller-owned device
+ * memory of at least runit_moe_scratch_bytes(), 256-byte aligned.  h, ff multiples of 256. */
+int32_t runit_moe_layer_q4k(runit_ctx_t*, const void* router_w, const void* gate, const void* up, const void* down,
+                            const void* x, const void* residual, void* out, void* idx_out, void* w_out, void* scratch,
+                            size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
+
 /* Synthetic weights written on the device (benchmark / test data, distributions of the
  * benchmark configurations): n_blocks blocks of the format from a counter-based generator. */
 int32_t runit_fill_weights(runit_ctx_t*, int32_t fmt, void* dst, uint64_t n_blocks, uint64_t seed, float sigma);

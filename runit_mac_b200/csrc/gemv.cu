@@ -23,6 +23,9 @@ struct GemvCall {
     int res_kind = RES_NONE, bias_kind = BIAS_NONE;
     bool dual = false;
     const char* name = "gemv";
+    // grouped (mixture-of-experts) launch: see GemvArgs
+    const int32_t* grp_expert = nullptr;
+    uint32_t grp_slots = 0, grp_experts = 0, grp_xdiv = 1;
 };
 
 static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
@@ -72,9 +75,21 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
     }
     if (c.dual) RUNIT_REQUIRE(ctx, c.w2 && runit_aligned(c.w2, 16), "%s: null or misaligned second weight", nm);
     a.ldy = c.rows[0];
+    if (c.grp_expert) {
+        RUNIT_REQUIRE(ctx, c.nseg == 1 && c.batch == 1 && c.grp_slots > 0 && c.grp_experts > 0 && c.grp_xdiv > 0,
+                      "%s: bad grouped launch", nm);
+        a.grp_expert = c.grp_expert;
+        a.grp_rows = c.rows[0];
+        a.grp_tiles = tiles;           // tiles per slot
+        a.grp_xdiv = c.grp_xdiv;
+        RUNIT_REQUIRE(ctx, (uint64_t)tiles * c.grp_slots < (1ull << 31), "%s: too many grouped tiles", nm);
+        tiles *= c.grp_slots;
+        total_rows *= c.grp_slots;
+    }
 
     const bool staged_ok = (c.fmt == RUNIT_FMT_Q8_0) ? w_align4 : w_align16;
-    const bool simple = ctx->tune.gemv_variant == 1 || !staged_ok;
+    const bool simple = (ctx->tune.gemv_variant == 1 || !staged_ok) && !c.grp_expert;
+    RUNIT_REQUIRE(ctx, staged_ok || !c.grp_expert, "%s: grouped launch needs aligned rows", nm);
     const int cpb = w_align16 ? 16 : (w_align8 ? 8 : 4);
     const uint32_t bpu = c.fmt == RUNIT_FMT_Q8_0 ? Traits<RUNIT_FMT_Q8_0>::BPU
                          : c.fmt == RUNIT_FMT_Q4_0 ? Traits<RUNIT_FMT_Q4_0>::BPU : Traits<RUNIT_FMT_Q4K>::BPU;
@@ -87,11 +102,13 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
     if (tma) {
         const uint32_t box_rows = c.dual ? kRT / 2 : kRT;
         for (int i = 0; i < c.nseg; i++) {
-            int32_t st = runit_get_tmap(ctx, c.w[i], c.rows[i], a.row_bytes, box_rows, 144, &maps.m[i]);
+            const uint64_t map_rows = c.grp_expert ? (uint64_t)c.rows[i] * c.grp_experts : c.rows[i];
+            int32_t st = runit_get_tmap(ctx, c.w[i], map_rows, a.row_bytes, box_rows, 144, &maps.m[i]);
             if (st != RUNIT_OK) return st;
         }
         if (c.dual) {
-            int32_t st = runit_get_tmap(ctx, c.w2, c.rows[0], a.row_bytes, box_rows, 144, &maps.m[3]);
+            const uint64_t map_rows = c.grp_expert ? (uint64_t)c.rows[0] * c.grp_experts : c.rows[0];
+            int32_t st = runit_get_tmap(ctx, c.w2, map_rows, a.row_bytes, box_rows, 144, &maps.m[3]);
             if (st != RUNIT_OK) return st;
         }
     }
@@ -154,6 +171,29 @@ static int32_t fused_ffn(runit_ctx* ctx, const char* name, int fmt, const void* 
     c.x = x;
     c.k = k;
     c.dual = true;
+    return gemv_dispatch(ctx, c);
+}
+
+// Grouped fused-dequant GEMVs for the MoE block: slot s multiplies the rows of expert slot_expert[s]
+// (inside the stacked matrix w: [n_experts][rows][k]) with input row s / xdiv and writes output row s.
+// With w2 != nullptr the launch computes silu(w.x) * (w2.x) (gate/up fusion).
+int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
+                     uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
+                     uint32_t n_slots) {
+    GemvCall c;
+    c.name = name;
+    c.fmt = fmt;
+    c.w[0] = w;
+    c.w2 = w2;
+    c.dual = w2 != nullptr;
+    c.x = x;
+    c.y[0] = y;
+    c.rows[0] = rows;
+    c.k = k;
+    c.grp_expert = slot_expert;
+    c.grp_slots = n_slots;
+    c.grp_experts = n_experts;
+    c.grp_xdiv = xdiv;
     return gemv_dispatch(ctx, c);
 }
 

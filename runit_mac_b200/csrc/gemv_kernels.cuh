@@ -70,6 +70,12 @@ struct GemvArgs {
     uint32_t ldy;          // elements between batch rows of y / residual
     int32_t out_f16, res_kind, bias_kind, dual;
     int32_t* status;       // host-visible word: set non-zero if a bounded wait ran out
+    // Grouped (mixture-of-experts) mode, active when grp_expert != nullptr: the launch covers
+    // n_slots independent GEMVs; slot s uses the weight rows of expert grp_expert[s] inside the
+    // stacked matrix seg[0].w ([E][grp_rows][row_bytes]), the input row s / grp_xdiv and the
+    // output row s.
+    const int32_t* grp_expert;
+    uint32_t grp_rows, grp_tiles, grp_xdiv;
 };
 
 // Tensor maps of the weight matrices (bulk-load path): one per segment, plus the second matrix of
@@ -304,10 +310,19 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
 #pragma unroll
     for (int i = 1; i < 3; i++)
         if (i < a.nseg && tile >= a.seg[i].tile_begin) si = i;
-    const GemvSeg sg = a.seg[si];
+    GemvSeg sg = a.seg[si];
     constexpr int RPT = DUAL ? kRT / 2 : kRT;   // real rows per tile
-    const uint32_t row0 = (tile - sg.tile_begin) * RPT;
     const bool tile_ok = tile < a.n_tiles;
+    uint32_t row0 = (tile - sg.tile_begin) * RPT;
+    uint32_t wrow0 = row0;                       // row of the tile inside the weight matrix
+    const uint8_t* xbase = reinterpret_cast<const uint8_t*>(a.x);
+    if (a.grp_expert != nullptr && tile_ok) {
+        const uint32_t slot = tile / a.grp_tiles;
+        row0 = (tile - slot * a.grp_tiles) * RPT;
+        wrow0 = (uint32_t)a.grp_expert[slot] * a.grp_rows + row0;
+        xbase += (size_t)(slot / a.grp_xdiv) * a.k * (XF16 ? 2 : 4);
+        sg.y = reinterpret_cast<uint8_t*>(sg.y) + (size_t)slot * a.ldy * (a.out_f16 ? 2 : 4);
+    }
     const uint32_t rows_here = tile_ok ? min((uint32_t)RPT, sg.rows - row0) : 0u;
     const bool row_ok = (uint32_t)(DUAL ? (lane & 15) : lane) < rows_here;
     const int n_it = tile_ok ? ((int)a.n_units - slice + KSL - 1) / KSL : 0;   // units slice, slice+KSL, ...
@@ -337,19 +352,19 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                 fence_proxy_async();   // earlier generic-proxy accesses to this slot precede the bulk writes
                 mbar_expect_tx(bar, (uint32_t)L::W_BYTES + B * xbytes);
                 if (DUAL) {
-                    tma_load_2d(slot, &maps.m[0], (int32_t)(u * T::UB), (int32_t)row0, bar);
-                    tma_load_2d(slot + 16 * T::UB, &maps.m[3], (int32_t)(u * T::UB), (int32_t)row0, bar);
+                    tma_load_2d(slot, &maps.m[0], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
+                    tma_load_2d(slot + 16 * T::UB, &maps.m[3], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
                 } else {
-                    tma_load_2d(slot, &maps.m[si], (int32_t)(u * T::UB), (int32_t)row0, bar);
+                    tma_load_2d(slot, &maps.m[si], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
                 }
 #pragma unroll
                 for (int b = 0; b < B; b++) {
                     if (XF16)
                         bulk_load_1d(slot + L::XR_OFF + b * T::UE * 2,
-                                     reinterpret_cast<const __half*>(a.x) + (size_t)b * a.k + e0, xbytes, bar);
+                                     reinterpret_cast<const __half*>(xbase) + (size_t)b * a.k + e0, xbytes, bar);
                     else
                         bulk_load_1d(slot + L::XP_OFF + b * T::UE * 4,
-                                     reinterpret_cast<const float*>(a.x) + (size_t)b * a.k + e0, xbytes, bar);
+                                     reinterpret_cast<const float*>(xbase) + (size_t)b * a.k + e0, xbytes, bar);
                 }
             }
             return;
@@ -366,7 +381,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                 if (row < kRT && (uint32_t)rr < rows_here && col * CPB < vb) {
                     const uint8_t* base = (DUAL && row >= 16) ? sg.w2 : sg.w;
                     cp_async<CPB>(slot + row * T::UB + col * CPB,
-                                  base + (size_t)(row0 + rr) * a.row_bytes + uoff + col * CPB);
+                                  base + (size_t)(wrow0 + rr) * a.row_bytes + uoff + col * CPB);
                 }
                 row += DR;
                 col += DC;
@@ -374,7 +389,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
             }
             const uint32_t e0 = u * T::UE;
             if (XF16) {
-                const __half* xg = reinterpret_cast<const __half*>(a.x);
+                const __half* xg = reinterpret_cast<const __half*>(xbase);
 #pragma unroll
                 for (int b = 0; b < B; b++)
 #pragma unroll
@@ -382,7 +397,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                         if (e0 + c * 8 < a.k)
                             cp_async16(slot + L::XR_OFF + (b * T::UE + c * 8) * 2, xg + (size_t)b * a.k + e0 + c * 8);
             } else {
-                const float* xg = reinterpret_cast<const float*>(a.x);
+                const float* xg = reinterpret_cast<const float*>(xbase);
 #pragma unroll
                 for (int b = 0; b < B; b++)
 #pragma unroll

@@ -41,12 +41,7 @@ static inline int32_t pick_slices(runit_ctx* ctx, const GemvArgs& a, const GemvM
 template <int FMT, int B, bool XF16, int CPB, int LD>
 static inline int32_t pick_stages(runit_ctx* ctx, const GemvArgs& a, const GemvMaps& maps, const char* name) {
     if constexpr (B == 1 && !XF16) {
-        if (a.dual) {
-            if constexpr (FMT != RUNIT_FMT_Q4K)
-                return launch_staged<FMT, 1, false, CPB, 3, true, LD, 4>(ctx, a, maps, name);
-            else
-                return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "%s: no fused gate/up kernel for Q4_K", name);
-        }
+        if (a.dual) return launch_staged<FMT, 1, false, CPB, 3, true, LD, 4>(ctx, a, maps, name);
         // Two stages per warp leave room for 4 CTAs (16 warps) per SM, which hides more latency than a
         // deeper ring with 12 warps; measured best on every large shape.
         if (ctx->tune.gemv_stages == 3) return pick_slices<FMT, 1, false, CPB, 3, false, LD>(ctx, a, maps, name);

@@ -1,0 +1,229 @@
+// OLMoE-style mixture-of-experts block on the device, without the reference's per-layer host sync.
+//
+// Reference sequence (crates/engine/src/forward.rs:1644-1679): router GEMV -> flush -> CPU
+// softmax/top-k (forward.rs:2420-2448) -> per selected expert: gate GEMV, up GEMV, silu*up, down
+// GEMV, scale-accumulate -> residual add.  Here: router GEMV, device softmax/top-k, ONE grouped
+// launch for gate+up+SiLU of all (token, expert) slots, ONE grouped launch for down, and a combine
+// kernel that adds the weighted expert outputs in routing order (deterministic) plus the residual.
+// All intermediates are f32.
+#include "gemv_common.cuh"
+#include "runit_internal.h"
+
+namespace runit {
+
+// logits[t][e] = W[e][:] . x[t][:]   (f32 router weights).  One warp per expert; the weight row
+// stays in registers while the warp walks the tokens.
+template <int KPL>   // floats of the row per lane (K = 32*KPL)
+__global__ void __launch_bounds__(256) router_f32_kernel(const float* __restrict__ w, const float* __restrict__ x,
+                                                          float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
+    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (e >= E) return;
+    float wr[KPL];
+    const float4* wrow = reinterpret_cast<const float4*>(w + (size_t)e * K);
+#pragma unroll
+    for (int i = 0; i < KPL / 4; i++) {
+        const float4 v = wrow[lane + 32 * i];
+        wr[4 * i] = v.x; wr[4 * i + 1] = v.y; wr[4 * i + 2] = v.z; wr[4 * i + 3] = v.w;
+    }
+    for (uint32_t t = blockIdx.y; t < T; t += gridDim.y) {
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)t * K);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < KPL / 4; i++) {
+            const float4 v = xr[lane + 32 * i];
+            a0 = fmaf(wr[4 * i], v.x, a0); a1 = fmaf(wr[4 * i + 1], v.y, a1);
+            a2 = fmaf(wr[4 * i + 2], v.z, a2); a3 = fmaf(wr[4 * i + 3], v.w, a3);
+        }
+        float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) logits[(size_t)t * E + e] = acc;
+    }
+}
+
+// Generic fallback for any K (multiple of 4).
+__global__ void __launch_bounds__(256) router_f32_generic_kernel(const float* __restrict__ w, const float* __restrict__ x,
+                                                                  float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
+    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (e >= E) return;
+    for (uint32_t t = blockIdx.y; t < T; t += gridDim.y) {
+        float acc = 0.f;
+        for (uint32_t c = lane; c < K; c += 32) acc = fmaf(w[(size_t)e * K + c], x[(size_t)t * K + c], acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) logits[(size_t)t * E + e] = acc;
+    }
+}
+
+// softmax over all experts, then the top-k probabilities in descending order (ties: lowest index),
+// optionally renormalised to sum 1 (crates/engine/src/forward.rs:2420-2448).  One warp per token,
+// E <= 256.  in_f16 != 0: the logits are f16 (the reference's router output dtype).
+__global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict__ logits, int in_f16, uint32_t E, uint32_t k,
+                                                          int renorm, uint32_t T, int32_t* __restrict__ out_idx,
+                                                          float* __restrict__ out_w) {
+    const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float v[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t e = lane + 32 * i;
+        float lv = -INFINITY;
+        if (e < E) lv = in_f16 ? __half2float(reinterpret_cast<const __half*>(logits)[(size_t)t * E + e])
+                               : reinterpret_cast<const float*>(logits)[(size_t)t * E + e];
+        v[i] = lv;
+        mx = fmaxf(mx, lv);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // exp values; the sum runs over experts in index order so that it is reproducible
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = (lane + 32 * i < E) ? expf(v[i] - mx) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float part = v[i];   // 0 beyond E; a fixed shuffle tree per group of 32 experts: deterministic
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        sum += part;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = v[i] / sum;   // probabilities (0 beyond E)
+    uint32_t taken = 0;
+    float wsum = 0.f;
+    float my_w = 0.f;   // lane s keeps the s-th selected weight (k <= 32)
+    int my_i = 0;
+    for (uint32_t s = 0; s < k; s++) {
+        float bv = -1.f;
+        uint32_t bi = 0xFFFFFFFFu;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t e = lane + 32 * i;
+            if (e < E && !((taken >> i) & 1u) && (v[i] > bv)) { bv = v[i]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31u) == lane && bi != 0xFFFFFFFFu) taken |= 1u << (bi >> 5);
+        if (lane == s) { my_w = bv; my_i = (int)bi; }
+        wsum += bv;
+    }
+    if (lane < k) {
+        float wv = my_w;
+        if (renorm && wsum > 0.f) wv = wv / wsum;
+        out_idx[(size_t)t * k + lane] = my_i;
+        out_w[(size_t)t * k + lane] = wv;
+    }
+}
+
+// out[t][r] = (res ? res[t][r] : 0) + sum_i w[t][i] * y[t*k+i][r], i ascending (routing order).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ w,
+                                                           const float* res, float* out, uint32_t T, uint32_t h, uint32_t k) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (r >= h) return;
+    float acc = 0.f;
+    for (uint32_t i = 0; i < k; i++) acc = fmaf(w[(size_t)t * k + i], y[((size_t)t * k + i) * h + r], acc);
+    const size_t o = (size_t)t * h + r;
+    out[o] = (res ? res[o] : 0.f) + acc;
+}
+
+struct MoeScratch {
+    float* logits;   // [T][E]
+    int32_t* idx;    // [T][k]
+    float* w;        // [T][k]
+    float* act;      // [T*k][ff]
+    float* y;        // [T*k][h]
+    size_t bytes;
+};
+
+static MoeScratch moe_carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    uint8_t* p = reinterpret_cast<uint8_t*>(base);
+    MoeScratch s;
+    size_t o = 0;
+    s.logits = reinterpret_cast<float*>(p + o); o += up((size_t)T * E * 4);
+    s.idx = reinterpret_cast<int32_t*>(p + o); o += up((size_t)T * k * 4);
+    s.w = reinterpret_cast<float*>(p + o); o += up((size_t)T * k * 4);
+    s.act = reinterpret_cast<float*>(p + o); o += up((size_t)T * k * ff * 4);
+    s.y = reinterpret_cast<float*>(p + o); o += up((size_t)T * k * h * 4);
+    s.bytes = o;
+    return s;
+}
+
+static int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
+    dim3 grid((E + 7) / 8, T < 64 ? T : 64);
+    if (K == 2048) router_f32_kernel<64><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
+    else if (K == 1024) router_f32_kernel<32><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
+    else if (K == 4096) router_f32_kernel<128><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
+    else router_f32_generic_kernel<<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
+    return runit_after_launch(ctx, "moe_router_f32");
+}
+
+// The whole block; scratch carved from `scratch`.
+int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
+                           const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
+                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {
+    RUNIT_REQUIRE(ctx, router_w && gate && up && down && x && out && scratch, "moe_layer_q4k: null pointer");
+    RUNIT_REQUIRE(ctx, T > 0 && T <= 65536, "moe_layer_q4k: T=%u out of range", T);
+    RUNIT_REQUIRE(ctx, h % 256 == 0 && ff % 256 == 0 && h > 0 && ff > 0, "moe_layer_q4k: h=%u, ff=%u must be multiples of 256", h, ff);
+    RUNIT_REQUIRE(ctx, E > 0 && E <= 256 && k > 0 && k <= E && k <= 32, "moe_layer_q4k: E=%u, k=%u unsupported", E, k);
+    RUNIT_REQUIRE(ctx, runit_aligned(scratch, 256), "moe_layer_q4k: scratch must be 256-byte aligned");
+    const MoeScratch s = moe_carve(scratch, T, h, ff, E, k);
+    if (s.bytes > scratch_bytes)
+        return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "moe_layer_q4k: scratch has %zu bytes, needs %zu", scratch_bytes, s.bytes);
+    int32_t st = moe_router(ctx, (const float*)router_w, (const float*)x, s.logits, E, h, T);
+    if (st != RUNIT_OK) return st;
+    int32_t* idx = idx_out ? idx_out : s.idx;
+    float* wts = w_out ? w_out : s.w;
+    route_topk_kernel<<<(T + 3) / 4, 128, 0, ctx->stream>>>(s.logits, 0, E, k, renorm, T, idx, wts);
+    st = runit_after_launch(ctx, "moe_route_topk");
+    if (st != RUNIT_OK) return st;
+    const uint32_t slots = T * k;
+    // gate+up+SiLU for every (token, expert) slot: act[s][ff]
+    st = gemv_grouped(ctx, "moe_gate_up", RUNIT_FMT_Q4K, gate, up, E, ff, h, x, k, s.act, idx, slots);
+    if (st != RUNIT_OK) return st;
+    // down: y[s][h] = Wd[e_s] . act[s]
+    st = gemv_grouped(ctx, "moe_down", RUNIT_FMT_Q4K, down, nullptr, E, h, ff, s.act, 1, s.y, idx, slots);
+    if (st != RUNIT_OK) return st;
+    moe_combine_kernel<<<dim3((h + 255) / 256, T), 256, 0, ctx->stream>>>(s.y, wts, (const float*)residual, (float*)out, T, h, k);
+    return runit_after_launch(ctx, "moe_combine");
+}
+
+}  // namespace runit
+
+using namespace runit;
+
+extern "C" {
+
+size_t runit_moe_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
+    return moe_carve(nullptr, T, h, ff, E, k).bytes;
+}
+
+int32_t runit_moe_router_f32(runit_ctx_t* ctx, const void* router_w, const void* x, void* logits, uint32_t E, uint32_t h,
+                             uint32_t T) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, router_w && x && logits && E > 0 && T > 0 && h > 0 && h % 4 == 0, "moe_router_f32: bad argument");
+    return moe_router(ctx, (const float*)router_w, (const float*)x, (float*)logits, E, h, T);
+}
+
+int32_t runit_moe_route_topk(runit_ctx_t* ctx, const void* logits, int32_t logits_f16, uint32_t E, uint32_t k, int32_t renorm,
+                             uint32_t T, void* out_idx, void* out_w) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, logits && out_idx && out_w, "moe_route_topk: null pointer");
+    RUNIT_REQUIRE(ctx, E > 0 && E <= 256 && k > 0 && k <= E && k <= 32 && T > 0, "moe_route_topk: E=%u k=%u T=%u unsupported", E, k, T);
+    route_topk_kernel<<<(T + 3) / 4, 128, 0, ctx->stream>>>(logits, logits_f16, E, k, renorm, T, (int32_t*)out_idx, (float*)out_w);
+    return runit_after_launch(ctx, "moe_route_topk");
+}
+
+int32_t runit_moe_layer_q4k(runit_ctx_t* ctx, const void* router_w, const void* gate, const void* up, const void* down,
+                            const void* x, const void* residual, void* out, void* idx_out, void* w_out, void* scratch,
+                            size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    return moe_layer_q4k_impl(ctx, router_w, gate, up, down, x, residual, out, (int32_t*)idx_out, (float*)w_out, scratch,
+                              scratch_bytes, T, h, ff, E, k, renorm);
+}
+
+}  // extern "C"

@@ -89,3 +89,10 @@ static inline size_t runit_block_bytes(int fmt) {
 static inline size_t runit_row_bytes(int fmt, uint32_t k) {
     return (size_t)k / runit_block_elems(fmt) * runit_block_bytes(fmt);
 }
+
+namespace runit {
+// gemv.cu: grouped GEMVs over stacked expert matrices (MoE block).
+int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
+                     uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
+                     uint32_t n_slots);
+}  // namespace runit

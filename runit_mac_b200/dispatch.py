@@ -219,6 +219,10 @@ _TWINS = [
     ("scale_accumulate_f16", "dispatch.rs:1639 (src, acc, weight, n)"),
     ("add_f16_into_f32", "dispatch.rs:316 (src, acc, n)"),
     ("gemv_batched_f32", "no twin: (fmt, weight, input, output, residual, m, k, batch)"),
+    ("moe_router_f32", "no twin: (router_w, x, logits, E, h, T)"),
+    ("moe_route_topk", "forward.rs:2420-2448 on the device: (logits, logits_f16, E, k, renorm, T, out_idx, out_w)"),
+    ("moe_layer_q4k", "forward.rs:1644-1679 as one call: (router_w, gate, up, down, x, residual, out, idx_out, w_out, "
+                      "scratch, scratch_bytes, T, h, ff, E, k, renorm)"),
     ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
     ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),
 ]
@@ -226,5 +230,25 @@ for _n, _d in _TWINS:
     globals()[_n] = _twin(_n, _d)
 del _n, _d
 
-__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+def moe_scratch_bytes(ctx: Context, T: int, h: int, ff: int, E: int, k: int) -> int:
+    return ctx.lib.runit_moe_scratch_bytes(T, h, ff, E, k)
+
+
+def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top_k, renorm=False, residual=None):
+    """Convenience for tests: upload host arrays, run runit_moe_layer_q4k once, download
+    (out [T][h], idx [T][k], weights [T][k])."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, h)
+    T = x.shape[0]
+    bufs = [ctx.buffer_from(np.ascontiguousarray(a)) for a in (np.asarray(router, np.float32), gate, up, down, x)]
+    res = None if residual is None else ctx.buffer_from(np.ascontiguousarray(residual, np.float32))
+    out, idx, w = ctx.new_buffer(T * h * 4), ctx.new_buffer(T * top_k * 4), ctx.new_buffer(T * top_k * 4)
+    nbytes = moe_scratch_bytes(ctx, T, h, ff, E, top_k)
+    scratch = ctx.new_buffer(nbytes)
+    ctx.call("moe_layer_q4k", *bufs, res, out, idx, w, scratch, nbytes, T, h, ff, E, top_k, int(renorm))
+    ctx.flush()
+    return (out.download(np.float32, T * h).reshape(T, h), idx.download(np.int32, T * top_k).reshape(T, top_k),
+            w.download(np.float32, T * top_k).reshape(T, top_k))
+
+
+__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "moe_scratch_bytes", "moe_layer_q4k_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
            "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K"] + [n for n, _ in _TWINS]

@@ -1,0 +1,164 @@
+"""GPU parity tests of the MoE block (router, softmax/top-k routing, grouped expert products, weighted
+combine), through the C ABI, against the CPU oracle.
+
+Bars: router expert indices bit-exact (set and order) except where the decisive probabilities are
+closer than 1e-6 (ties excluded, and counted); routing weights and block outputs within
+|gpu - oracle| <= 1e-3 * max(|ref|, rms(ref)) (f32 accumulation)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).parent / "golden" / "path_golden.npz"
+
+
+def check_routing(O, logits, k, renorm, gidx, gw, tie=1e-6):
+    """Compare device routing with the oracle token by token; returns the number of excluded ties."""
+    excluded = 0
+    for t in range(logits.shape[0]):
+        ridx, rw, probs = O.topk_softmax(logits[t], k, renorm)
+        srt = np.sort(probs)[::-1]
+        gaps = srt[:k] - srt[1:k + 1]           # gap between consecutive ranks up to the k/(k+1) boundary
+        if (ridx != gidx[t]).any():
+            assert gaps.min() <= tie, ("routing differs without a near-tie", t, ridx, gidx[t], gaps.min())
+            excluded += 1
+            continue
+        assert np.allclose(gw[t], rw, rtol=1e-5, atol=1e-8), (t, gw[t], rw)
+    return excluded
+
+
+@pytest.mark.parametrize("E,k", [(64, 8), (128, 8), (8, 2), (256, 32), (40, 3)])
+def test_route_topk_matches_oracle(ctx, oracle, E, k):
+    import runit_mac_b200 as R
+    O = oracle
+    rng = np.random.default_rng(E * 100 + k)
+    T = 300
+    logits = rng.normal(0, 1.5, (T, E)).astype(np.float32)
+    for renorm in (0, 1):
+        idx, w = ctx.new_buffer(T * k * 4), ctx.new_buffer(T * k * 4)
+        R.moe_route_topk(ctx, ctx.buffer_from(logits), 0, E, k, renorm, T, idx, w)
+        ctx.flush()
+        gi = idx.download(np.int32, T * k).reshape(T, k)
+        gw = w.download(np.float32, T * k).reshape(T, k)
+        assert check_routing(O, logits, k, bool(renorm), gi, gw) <= 2
+        if renorm:
+            assert np.allclose(gw.sum(1), 1.0, atol=1e-5)
+    # f16 logits, the reference's router output dtype (forward.rs:1650, 2421-2422)
+    l16 = logits.astype(np.float16)
+    idx, w = ctx.new_buffer(T * k * 4), ctx.new_buffer(T * k * 4)
+    R.moe_route_topk(ctx, ctx.buffer_from(l16), 1, E, k, 1, T, idx, w)
+    ctx.flush()
+    gi = idx.download(np.int32, T * k).reshape(T, k)
+    gw = w.download(np.float32, T * k).reshape(T, k)
+    assert check_routing(O, l16.astype(np.float32), k, True, gi, gw) <= T // 10   # f16 logits collide often
+
+
+def test_route_topk_ties_pick_lowest_index(ctx):
+    import runit_mac_b200 as R
+    idx, w = ctx.new_buffer(16), ctx.new_buffer(16)
+    R.moe_route_topk(ctx, ctx.buffer_from(np.zeros(16, np.float32)), 0, 16, 4, 0, 1, idx, w)
+    ctx.flush()
+    assert list(idx.download(np.int32, 4)) == [0, 1, 2, 3]
+    assert np.allclose(w.download(np.float32, 4), 1.0 / 16)
+
+
+def test_router_gemv_f32(ctx, oracle):
+    import runit_mac_b200 as R
+    O = oracle
+    rng = np.random.default_rng(3)
+    for E, h, T in ((64, 2048, 5), (128, 2048, 3), (8, 256, 2), (64, 1024, 70)):
+        w = rng.normal(0, 0.02, (E, h)).astype(np.float32)
+        x = rng.normal(0, 1, (T, h)).astype(np.float32)
+        lg = ctx.new_buffer(T * E * 4)
+        R.moe_router_f32(ctx, ctx.buffer_from(w), ctx.buffer_from(x), lg, E, h, T)
+        ctx.flush()
+        got = lg.download(np.float32, T * E).reshape(T, E)
+        ref = np.stack([O.gemv_f32w(w, x[t], E, h) for t in range(T)])
+        assert_close(O, ref, got, rel_tol=1e-5, what="router")
+
+
+def test_moe_golden_fixture(ctx, oracle):
+    import runit_mac_b200 as R
+    G = np.load(GOLD)
+    h, ff, E, k = map(int, G["moe_dims"])
+    out, idx, w = R.moe_layer_q4k_host(ctx, G["moe_router"], G["moe_gate"], G["moe_up"], G["moe_down"], G["moe_x"], h=h, ff=ff,
+                                       E=E, top_k=k, renorm=False)
+    assert (idx == G["moe_idx"]).all()
+    assert np.allclose(w, G["moe_w"], rtol=1e-5)
+    assert_close(oracle, G["moe_y"], out, what="moe golden")
+
+
+def make_olmoe_layer(O, rng, E=64, h=2048, ff=1024):
+    router = rng.normal(0, 0.02, (E, h)).astype(np.float32)
+    gate = O.rand_q4k(rng, E * ff, h)
+    up = O.rand_q4k(rng, E * ff, h)
+    down = O.rand_q4k(rng, E * h, ff)
+    return router, gate, up, down
+
+
+@pytest.fixture(scope="module")
+def olmoe_layer(oracle):
+    return make_olmoe_layer(oracle, np.random.default_rng(1003))
+
+
+@pytest.mark.parametrize("T", [1, 16])
+def test_moe_layer_olmoe_shape(ctx, oracle, olmoe_layer, T):
+    """Single OLMoE-1B-7B-shaped layer: hidden 2048, 64 experts, top-8, expert intermediate 1024, f32
+    router ~N(0,0.02), softmax then top-8 without renormalisation, Q4_K experts, x ~ N(0,1)."""
+    import runit_mac_b200 as R
+    O = oracle
+    router, gate, up, down = olmoe_layer
+    rng = np.random.default_rng(10 + T)
+    x = rng.normal(0, 1, (T, 2048)).astype(np.float32)
+    res = rng.normal(0, 1, (T, 2048)).astype(np.float32)
+    ref, ridx, rw = O.moe_layer_q4k(router, gate, up, down, x, h=2048, ff=1024, E=64, top_k=8, renorm=False, residual=res)
+    out, idx, w = R.moe_layer_q4k_host(ctx, router, gate, up, down, x, h=2048, ff=1024, E=64, top_k=8, renorm=False, residual=res)
+    logits = np.stack([O.gemv_f32w(router, x[t], 64, 2048) for t in range(T)])
+    excluded = check_routing(O, logits, 8, False, idx, w)
+    assert excluded == 0 or T > 1
+    ok = [(idx[t] == ridx[t]).all() for t in range(T)]
+    assert_close(O, ref[ok], out[ok], what="moe layer T=%d" % T)
+    # renormalised variant (the reference's behaviour, forward.rs:2438-2445)
+    ref, _, rw = O.moe_layer_q4k(router, gate, up, down, x, h=2048, ff=1024, E=64, top_k=8, renorm=True)
+    out, idx2, w2 = R.moe_layer_q4k_host(ctx, router, gate, up, down, x, h=2048, ff=1024, E=64, top_k=8, renorm=True)
+    assert np.allclose(w2.sum(1), 1.0, atol=1e-5)
+    ok = [(idx2[t] == ridx[t]).all() for t in range(T)]
+    assert_close(O, ref[ok], out[ok], what="moe layer renorm T=%d" % T)
+
+
+def test_moe_layer_256_tokens_sampled(ctx, oracle, olmoe_layer):
+    """T=256: every token is routed on the device; a sample of tokens is recomputed by the oracle
+    (tokens are independent), and the block is checked for linearity in the residual."""
+    import runit_mac_b200 as R
+    O = oracle
+    router, gate, up, down = olmoe_layer
+    T = 256
+    rng = np.random.default_rng(256)
+    x = rng.normal(0, 1, (T, 2048)).astype(np.float32)
+    out, idx, w = R.moe_layer_q4k_host(ctx, router, gate, up, down, x, h=2048, ff=1024, E=64, top_k=8, renorm=False)
+    assert len(np.unique(idx)) == 64                      # with 2048 assignments every expert is hit
+    assert (np.sort(idx, 1)[:, 1:] != np.sort(idx, 1)[:, :-1]).all()   # 8 distinct experts per token
+    sample = [0, 1, 17, 100, 255] + list(rng.integers(0, T, 7))
+    ref, ridx, _ = O.moe_layer_q4k(router, gate, up, down, x[sample], h=2048, ff=1024, E=64, top_k=8, renorm=False)
+    for j, t in enumerate(sample):
+        if (ridx[j] == idx[t]).all():
+            assert_close(O, ref[j], out[t], what="token %d" % t)
+    res = rng.normal(0, 1, (T, 2048)).astype(np.float32)
+    out2, _, _ = R.moe_layer_q4k_host(ctx, router, gate, up, down, x, h=2048, ff=1024, E=64, top_k=8, renorm=False, residual=res)
+    assert_close(O, out + res, out2, rel_tol=1e-5, what="residual")
+
+
+def test_moe_bad_arguments(ctx):
+    import runit_mac_b200 as R
+    b = ctx.new_buffer(1 << 20)
+    with pytest.raises(R.KernelError) as e:   # scratch too small
+        R.moe_layer_q4k(ctx, b, b, b, b, b, None, b, None, None, b, 1024, 4, 2048, 1024, 64, 8, 0)
+    assert e.value.status == 3
+    with pytest.raises(R.KernelError):        # hidden not a multiple of 256
+        R.moe_layer_q4k(ctx, b, b, b, b, b, None, b, None, None, b, 1 << 20, 1, 2000, 1024, 64, 8, 0)
+    with pytest.raises(R.KernelError):        # more experts per token than experts
+        R.moe_route_topk(ctx, b, 0, 4, 8, 0, 1, b, b)
+    ctx.flush()
