@@ -185,6 +185,24 @@ int32_t runit_moe_layer_q4k(runit_ctx_t*, const void* router_w, const void* gate
                             const void* x, const void* residual, void* out, void* idx_out, void* w_out, void* scratch,
                             size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
 
+/* No counterpart in the reference.  The same MoE block as runit_moe_layer_q4k for callers that cannot hand
+ * over scratch memory: a host engine that gives every free byte of device memory to its own weight and
+ * KV-cache pools at start-up, or a serving loop that must not call cudaMalloc because that call stalls the
+ * whole device.  This entry point allocates nothing (no cudaMalloc/cudaFree, no allocating library call);
+ * its intermediates live in a fixed 4 MiB region (runit_moe_static_scratch_capacity()) built into the
+ * library image, which every GPU that loads the library holds until the process exits.
+ *   - Shapes whose intermediates do not fit (runit_moe_scratch_bytes(T,h,ff,E,k) > capacity; e.g. OLMoE
+ *     shapes beyond 32 tokens) are rejected with RUNIT_ERR_BUFFER_SIZE and nothing is launched.
+ *   - The first call on a device looks up the region's device address (once per device, with that device
+ *     made current for the lookup); make that first call before any stream capture is started.
+ *   - All calls share the one region and it keeps the previous call's contents; every part the block reads
+ *     is rewritten first, so nothing needs clearing, but two calls that overlap on the GPU (different
+ *     streams or contexts of one process on the same device) race on it: keep them ordered. */
+size_t  runit_moe_static_scratch_capacity(void);
+int32_t runit_moe_layer_q4k_static(runit_ctx_t*, const void* router_w, const void* gate, const void* up, const void* down,
+                                   const void* x, const void* residual, void* out, void* idx_out, void* w_out,
+                                   uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
+
 /* Synthetic weights written on the device (benchmark / test data, distributions of the
  * benchmark configurations): n_blocks blocks of the format from a counter-based generator. */
 int32_t runit_fill_weights(runit_ctx_t*, int32_t fmt, void* dst, uint64_t n_blocks, uint64_t seed, float sigma);

@@ -192,11 +192,58 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     return runit_after_launch(ctx, "moe_combine");
 }
 
+// ───────────────────────── built-in scratch (entry point that allocates nothing) ─────────────────────────
+// A fixed region inside the library's own device image.  Every GPU that loads the library carries it
+// until the process exits.  In host code `g_moe_static_scratch` is only a stand-in for the symbol, never a
+// device address: the address a kernel may use comes from cudaGetSymbolAddress, asked once per device
+// with that device current.
+constexpr size_t kMoeStaticScratchBytes = 4u << 20;   // 4 MiB
+static __device__ __align__(256) unsigned char g_moe_static_scratch[kMoeStaticScratchBytes];
+
+static int32_t moe_static_scratch(runit_ctx* ctx, void** out) {
+    static void* per_device[64] = {nullptr};
+    *out = nullptr;
+    if (ctx->device < 0 || ctx->device >= 64) return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "device index %d out of range", ctx->device);
+    if (!per_device[ctx->device]) {
+        int cur = -1;
+        RUNIT_CUDA_TRY(ctx, cudaGetDevice(&cur));
+        if (cur != ctx->device) RUNIT_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_moe_static_scratch);
+        if (cur != ctx->device) cudaSetDevice(cur);
+        if (e != cudaSuccess || !p)
+            return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cudaGetSymbolAddress(built-in MoE scratch): %s", cudaGetErrorString(e));
+        per_device[ctx->device] = p;
+    }
+    *out = per_device[ctx->device];
+    return RUNIT_OK;
+}
+
 }  // namespace runit
 
 using namespace runit;
 
 extern "C" {
+
+size_t runit_moe_static_scratch_capacity(void) { return kMoeStaticScratchBytes; }
+
+int32_t runit_moe_layer_q4k_static(runit_ctx_t* ctx, const void* router_w, const void* gate, const void* up,
+                                   const void* down, const void* x, const void* residual, void* out, void* idx_out,
+                                   void* w_out, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, T > 0 && h > 0 && ff > 0 && E > 0 && k > 0, "moe_layer_q4k_static: empty shape");
+    const size_t need = moe_carve(nullptr, T, h, ff, E, k).bytes;
+    if (need > kMoeStaticScratchBytes)
+        return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE,
+                          "moe_layer_q4k_static: T=%u k=%u h=%u ff=%u E=%u needs %zu bytes of scratch, the built-in region "
+                          "holds %zu; use runit_moe_layer_q4k with caller-owned scratch",
+                          T, k, h, ff, E, need, (size_t)kMoeStaticScratchBytes);
+    void* scratch = nullptr;
+    int32_t st = moe_static_scratch(ctx, &scratch);
+    if (st != RUNIT_OK) return st;
+    return moe_layer_q4k_impl(ctx, router_w, gate, up, down, x, residual, out, (int32_t*)idx_out, (float*)w_out, scratch,
+                              kMoeStaticScratchBytes, T, h, ff, E, k, renorm);
+}
 
 size_t runit_moe_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
     return moe_carve(nullptr, T, h, ff, E, k).bytes;
