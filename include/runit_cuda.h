@@ -203,6 +203,67 @@ int32_t runit_moe_layer_q4k_static(runit_ctx_t*, const void* router_w, const voi
                                    const void* x, const void* residual, void* out, void* idx_out, void* w_out,
                                    uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
 
+/* ── decode-step operators besides the GEMVs ── */
+/* dispatch.rs:152  y = x * rsqrt(mean(x^2)+eps) * gamma_f16, num_rows rows of `hidden` (x may equal y) */
+int32_t runit_rms_norm_f32_f32(runit_ctx_t*, const void* x, void* y, const void* gamma, float eps, uint32_t hidden, uint32_t num_rows);
+/* dispatch.rs:177  same with f32 gamma */
+int32_t runit_rms_norm_f32_f32_f32g(runit_ctx_t*, const void* x, void* y, const void* gamma, float eps, uint32_t hidden, uint32_t num_rows);
+/* dispatch.rs:945  rotary embedding of Q [q_heads][hd] and K [kv_heads][hd] in place, pairs (d, d+hd/2) */
+int32_t runit_fused_rope_qk_f32(runit_ctx_t*, void* q, void* k, uint32_t head_dim, uint32_t q_heads, uint32_t kv_heads, uint32_t pos, float theta);
+/* dispatch.rs:1159 / 1183  scatter [kv_heads][hd] into the cache [kv_heads][max_seq][hd] at pos */
+int32_t runit_kv_copy_to_cache_f16(runit_ctx_t*, const void* src, void* dst, uint32_t pos, uint32_t max_seq, uint32_t head_dim, uint32_t num_kv_heads);
+int32_t runit_kv_copy_to_cache_f32(runit_ctx_t*, const void* src, void* dst, uint32_t pos, uint32_t max_seq, uint32_t head_dim, uint32_t num_kv_heads);
+/* no twin: f32 source rounded into an f16 cache */
+int32_t runit_kv_copy_to_cache_f32_f16(runit_ctx_t*, const void* src, void* dst, uint32_t pos, uint32_t max_seq, uint32_t head_dim, uint32_t num_kv_heads);
+/* dispatch.rs:1575 (f32) / dispatch.rs:697 (f16)  q_len = 1 attention over kv_len cached positions,
+ * scale 1/sqrt(head_dim), GQA kv_head = q_head / (heads/kv_heads); head_dim in {32,64,96,128} */
+int32_t runit_decode_attention_f32(runit_ctx_t*, const void* q, const void* k, const void* v, void* out, uint32_t batch, uint32_t kv_len,
+                                   uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t kv_head_stride);
+int32_t runit_decode_attention_f16(runit_ctx_t*, const void* q, const void* k, const void* v, void* out, uint32_t batch, uint32_t kv_len,
+                                   uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t kv_head_stride);
+/* no twin: f32 query and output over an f16 cache */
+int32_t runit_decode_attention_f32q_f16kv(runit_ctx_t*, const void* q, const void* k, const void* v, void* out, uint32_t batch, uint32_t kv_len,
+                                          uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t kv_head_stride);
+/* dispatch.rs:1615  index of the maximum of n f16 values -> result[0] (int32); ties: lowest index */
+int32_t runit_argmax_f16(runit_ctx_t*, const void* input, void* result, uint32_t n);
+/* no twin: f32 input (sampler.rs:111-116 on the device) */
+int32_t runit_argmax_f32(runit_ctx_t*, const void* input, void* result, uint32_t n);
+
+/* ── greedy decoder for an OLMoE-shaped model with Q4_K matrices: the role of Executor::forward_greedy,
+ *    crates/engine/src/forward.rs:1795-1975, with token id, position and arg-max kept on the device ── */
+typedef struct {
+    int32_t n_layers, hidden, n_heads, n_kv_heads, head_dim, vocab;
+    int32_t n_experts, top_k, ff, max_seq, renorm;
+    float   eps, theta;
+} runit_model_cfg;
+typedef struct {          /* device pointers; the model keeps them, the caller keeps the memory alive */
+    const void* tok_emb;   /* f32 [vocab][hidden] */
+    const void* attn_norm; /* f32 [L][hidden] */
+    const void* ffn_norm;  /* f32 [L][hidden] */
+    const void* out_norm;  /* f32 [hidden] */
+    const void* wq;        /* Q4_K [L][n_heads*head_dim][hidden] */
+    const void* wk;        /* Q4_K [L][n_kv_heads*head_dim][hidden] */
+    const void* wv;        /* Q4_K [L][n_kv_heads*head_dim][hidden] */
+    const void* wo;        /* Q4_K [L][hidden][n_heads*head_dim] */
+    const void* router;    /* f32 [L][E][hidden] */
+    const void* gate;      /* Q4_K [L][E][ff][hidden] */
+    const void* up;        /* Q4_K [L][E][ff][hidden] */
+    const void* down;      /* Q4_K [L][E][hidden][ff] */
+    const void* lm_head;   /* Q4_K [vocab][hidden] */
+} runit_model_weights;
+typedef struct runit_model runit_model_t;
+/* Allocates the f16 KV cache and all scratch, runs one warm-up step and records the per-token command lists. */
+int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, runit_model_t** out);
+int32_t runit_model_destroy(runit_model_t* model);
+int32_t runit_model_reset(runit_model_t* model, int32_t token, int32_t pos);
+/* forward.rs:1795  one token at position pos -> arg-max next token (synchronous, like the reference) */
+int32_t runit_model_forward_greedy(runit_model_t* model, int32_t token_id, int32_t pos, int32_t* next_token);
+/* prompt (forced tokens) + n_gen greedy steps without host round trips; out_tokens: n_prompt+n_gen int32 on the host */
+int32_t runit_model_generate_greedy(runit_model_t* model, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen,
+                                    int32_t start_pos, int32_t skip_prompt_logits, int32_t* out_tokens);
+void*   runit_model_logits(runit_model_t* model);           /* device pointer, f32 [vocab], of the last step */
+uint64_t runit_model_launches_per_token(runit_model_t* model);
+
 /* Synthetic weights written on the device (benchmark / test data, distributions of the
  * benchmark configurations): n_blocks blocks of the format from a counter-based generator. */
 int32_t runit_fill_weights(runit_ctx_t*, int32_t fmt, void* dst, uint64_t n_blocks, uint64_t seed, float sigma);

@@ -1,0 +1,285 @@
+// Greedy decoder for an OLMoE-shaped model with Q4_K matrices: the op sequence of
+// Executor::forward_greedy (crates/engine/src/forward.rs:1795-1975) as one recorded command list per
+// token, with the token id, the position and the argmax result kept on the device so that successive
+// tokens need no host round trip (the reference synchronises once per MoE layer and once per token).
+//
+// Differences from the reference that the benchmark configuration asks for: f32 router weights, f32
+// expert intermediates and combine, top-k weights not renormalised unless cfg.renorm, f16 KV cache
+// fed from f32 K/V, f32 logits with a lowest-index argmax.
+#include "decode_ops.cuh"
+#include "runit_internal.h"
+
+#include <new>
+#include <vector>
+
+struct runit_model {
+    runit_ctx* ctx = nullptr;
+    runit_model_cfg cfg;
+    runit_model_weights w;
+    // device state
+    __half* kc = nullptr;       // [L][kv_heads][max_seq][head_dim]
+    __half* vc = nullptr;
+    float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *logits = nullptr;
+    float* attn_part = nullptr;
+    void* moe_scratch = nullptr;
+    size_t moe_scratch_bytes = 0;
+    int32_t* state = nullptr;   // [0] = token, [1] = pos, [2] = step counter
+    int32_t* forced = nullptr;  // forced input tokens (prompt), n_forced entries
+    int32_t* out_tokens = nullptr;
+    uint32_t forced_cap = 0, out_cap = 0;
+    uint32_t nsplit = 8;
+    cudaGraphExec_t graph_full = nullptr;    // step with lm_head + argmax
+    cudaGraphExec_t graph_prompt = nullptr;  // step without them (prompt positions whose logits nobody reads)
+    std::vector<void*> owned;
+};
+
+namespace runit {
+
+// x = tok_emb[token]; token comes from the forced list while step < n_forced, else from state[0].
+__global__ void embed_kernel(const float* __restrict__ emb, float* __restrict__ x, int32_t* state,
+                             const int32_t* __restrict__ forced, uint32_t n_forced, uint32_t hidden, uint32_t vocab) {
+    const uint32_t step = (uint32_t)state[2];
+    int32_t tok = state[0];
+    if (step < n_forced) {
+        const int32_t f = forced[step];   // negative = this step is not forced
+        if (f >= 0) tok = f;
+    }
+    if (tok < 0 || (uint32_t)tok >= vocab) tok = 0;   // ids are validated on the host; never index out of range
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x)
+        x[i] = emb[(size_t)tok * hidden + i];
+}
+
+// After the step: record the produced token, advance position and step.
+__global__ void advance_kernel(int32_t* state, const int32_t* argmax_result, int32_t* out_tokens, uint32_t out_cap,
+                               int has_logits) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const uint32_t step = (uint32_t)state[2];
+        if (has_logits) {
+            state[0] = argmax_result[0];
+            if (step < out_cap) out_tokens[step] = argmax_result[0];
+        } else if (step < out_cap) {
+            out_tokens[step] = -1;
+        }
+        state[1] += 1;
+        state[2] += 1;
+    }
+}
+
+static int32_t dev_alloc(runit_model* m, void** p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return runit_fail(m->ctx, RUNIT_ERR_ALLOC, "model: allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
+    m->owned.push_back(*p);
+    return RUNIT_OK;
+}
+
+// Issue the launches of one decode step on the context's stream.
+static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
+    runit_ctx* ctx = m->ctx;
+    const runit_model_cfg& c = m->cfg;
+    const uint32_t h = c.hidden, hd = c.head_dim, q_dim = c.n_heads * hd, kv_dim = c.n_kv_heads * hd;
+    const size_t rb_h = runit_row_bytes(RUNIT_FMT_Q4K, h), rb_q = runit_row_bytes(RUNIT_FMT_Q4K, q_dim);
+    const size_t rb_ff = runit_row_bytes(RUNIT_FMT_Q4K, c.ff);
+    const size_t kv_layer = (size_t)c.n_kv_heads * c.max_seq * hd;
+    const int32_t* pos_ptr = m->state + 1;
+    int32_t st;
+    embed_kernel<<<8, 256, 0, ctx->stream>>>((const float*)m->w.tok_emb, m->x, m->state, m->forced, n_forced, h, c.vocab);
+    if ((st = runit_after_launch(ctx, "embed")) != RUNIT_OK) return st;
+    for (int l = 0; l < c.n_layers; l++) {
+        const uint8_t* wq = (const uint8_t*)m->w.wq + (size_t)l * q_dim * rb_h;
+        const uint8_t* wk = (const uint8_t*)m->w.wk + (size_t)l * kv_dim * rb_h;
+        const uint8_t* wv = (const uint8_t*)m->w.wv + (size_t)l * kv_dim * rb_h;
+        const uint8_t* wo = (const uint8_t*)m->w.wo + (size_t)l * h * rb_q;
+        // attention block (forward.rs:1833-1896)
+        if ((st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.attn_norm + (size_t)l * h, false, c.eps, h, 1))) return st;
+        const void* ws[3] = {wq, wk, wv};
+        void* ys[3] = {m->q, m->k, m->v};
+        const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
+        if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, m->xn, h))) return st;
+        if ((st = launch_rope(ctx, m->q, m->k, hd, c.n_heads, c.n_kv_heads, 0, pos_ptr, c.theta))) return st;
+        __half* kcl = m->kc + (size_t)l * kv_layer;
+        __half* vcl = m->vc + (size_t)l * kv_layer;
+        if ((st = launch_kv_copy(ctx, m->k, false, kcl, true, 0, pos_ptr, c.max_seq, hd, c.n_kv_heads))) return st;
+        if ((st = launch_kv_copy(ctx, m->v, false, vcl, true, 0, pos_ptr, c.max_seq, hd, c.n_kv_heads))) return st;
+        if ((st = launch_decode_attention(ctx, 0, 1, m->q, kcl, vcl, m->ao, m->attn_part, m->nsplit, 1, 0, pos_ptr, c.n_heads,
+                                          c.n_kv_heads, hd, c.max_seq)))
+            return st;
+        if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, m->x, m->x, h, q_dim))) return st;
+        // MoE block (forward.rs:1898-1931)
+        if ((st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.ffn_norm + (size_t)l * h, false, c.eps, h, 1))) return st;
+        const size_t eg = (size_t)c.n_experts * c.ff * rb_h, ed = (size_t)c.n_experts * h * rb_ff;
+        if ((st = moe_layer_q4k_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
+                                     (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
+                                     (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr,
+                                     m->moe_scratch, m->moe_scratch_bytes, 1, h, c.ff, c.n_experts, c.top_k, c.renorm)))
+            return st;
+    }
+    int32_t* argmax_out = m->state + 3;
+    if (with_logits) {
+        if ((st = launch_rms_norm(ctx, m->x, m->xn, m->w.out_norm, false, c.eps, h, 1))) return st;
+        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->xn, m->logits, nullptr, c.vocab, h))) return st;
+        if ((st = launch_argmax(ctx, m->logits, false, argmax_out, c.vocab))) return st;
+    }
+    advance_kernel<<<1, 32, 0, ctx->stream>>>(m->state, argmax_out, m->out_tokens, m->out_cap, with_logits ? 1 : 0);
+    return runit_after_launch(ctx, "advance");
+}
+
+static int32_t record_graph(runit_model* m, bool with_logits, cudaGraphExec_t* out) {
+    runit_ctx* ctx = m->ctx;
+    RUNIT_CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    int32_t st = issue_step(m, with_logits, m->forced_cap);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (st != RUNIT_OK) {
+        if (g) cudaGraphDestroy(g);
+        return st;
+    }
+    if (e != cudaSuccess || !g) {
+        cudaGetLastError();
+        return runit_fail(ctx, RUNIT_ERR_LAUNCH, "model: stream capture failed: %s", cudaGetErrorString(e));
+    }
+    e = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "model: graph instantiate failed: %s", cudaGetErrorString(e));
+    return RUNIT_OK;
+}
+
+}  // namespace runit
+
+using namespace runit;
+
+extern "C" {
+
+int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, runit_model_t** out) {
+    if (!ctx || !out) return RUNIT_ERR_BAD_ARG;
+    *out = nullptr;
+    RUNIT_REQUIRE(ctx, cfg && weights, "model_create: null config or weights");
+    const runit_model_cfg& c = *cfg;
+    RUNIT_REQUIRE(ctx, c.n_layers > 0 && c.n_layers <= 256 && c.hidden > 0 && c.hidden % 256 == 0, "model_create: bad hidden/layers");
+    RUNIT_REQUIRE(ctx, c.n_heads > 0 && c.n_kv_heads > 0 && c.n_heads % c.n_kv_heads == 0, "model_create: bad head counts");
+    RUNIT_REQUIRE(ctx, c.head_dim == 32 || c.head_dim == 64 || c.head_dim == 96 || c.head_dim == 128, "model_create: head_dim must be 32/64/96/128");
+    RUNIT_REQUIRE(ctx, (c.n_heads * c.head_dim) % 256 == 0, "model_create: n_heads*head_dim must be a multiple of 256");
+    RUNIT_REQUIRE(ctx, c.ff > 0 && c.ff % 256 == 0 && c.n_experts > 0 && c.n_experts <= 256 && c.top_k > 0 && c.top_k <= c.n_experts && c.top_k <= 32,
+                  "model_create: bad MoE shape");
+    RUNIT_REQUIRE(ctx, c.vocab > 0 && c.max_seq > 0, "model_create: bad vocab/max_seq");
+    const void* ptrs[] = {weights->tok_emb, weights->attn_norm, weights->ffn_norm, weights->out_norm, weights->wq, weights->wk,
+                          weights->wv, weights->wo, weights->router, weights->gate, weights->up, weights->down, weights->lm_head};
+    for (const void* p : ptrs) RUNIT_REQUIRE(ctx, p != nullptr, "model_create: null weight pointer");
+    runit_model* m = new (std::nothrow) runit_model();
+    if (!m) return RUNIT_ERR_ALLOC;
+    m->ctx = ctx;
+    m->cfg = c;
+    m->w = *weights;
+    const uint32_t h = c.hidden, q_dim = c.n_heads * c.head_dim, kv_dim = c.n_kv_heads * c.head_dim;
+    const size_t kv_elems = (size_t)c.n_layers * c.n_kv_heads * c.max_seq * c.head_dim;
+    m->moe_scratch_bytes = moe_scratch_bytes_impl(1, h, c.ff, c.n_experts, c.top_k);
+    m->forced_cap = (uint32_t)c.max_seq;
+    m->out_cap = (uint32_t)c.max_seq;
+    int32_t st = RUNIT_OK;
+    auto A = [&](void** p, size_t b) { if (st == RUNIT_OK) st = dev_alloc(m, p, b); };
+    A((void**)&m->kc, kv_elems * 2); A((void**)&m->vc, kv_elems * 2);
+    A((void**)&m->x, h * 4); A((void**)&m->xn, h * 4); A((void**)&m->q, q_dim * 4); A((void**)&m->k, kv_dim * 4);
+    A((void**)&m->v, kv_dim * 4); A((void**)&m->ao, q_dim * 4); A((void**)&m->logits, (size_t)c.vocab * 4);
+    A((void**)&m->attn_part, (size_t)c.n_heads * m->nsplit * (c.head_dim + 2) * 4);
+    A(&m->moe_scratch, m->moe_scratch_bytes);
+    A((void**)&m->state, 64); A((void**)&m->forced, (size_t)m->forced_cap * 4); A((void**)&m->out_tokens, (size_t)m->out_cap * 4);
+    if (st == RUNIT_OK) {
+        cudaMemsetAsync(m->kc, 0, kv_elems * 2, ctx->stream);
+        cudaMemsetAsync(m->vc, 0, kv_elems * 2, ctx->stream);
+        cudaMemsetAsync(m->state, 0, 64, ctx->stream);
+        cudaMemsetAsync(m->forced, 0xFF, (size_t)m->forced_cap * 4, ctx->stream);   // nothing forced
+        // one eager step configures every kernel (shared-memory attributes, tensor maps) before capture
+        st = issue_step(m, true, 0);
+        if (st == RUNIT_OK) st = runit_flush(ctx);
+        cudaMemsetAsync(m->state, 0, 64, ctx->stream);
+        cudaMemsetAsync(m->kc, 0, kv_elems * 2, ctx->stream);
+        cudaMemsetAsync(m->vc, 0, kv_elems * 2, ctx->stream);
+    }
+    if (st == RUNIT_OK) st = record_graph(m, true, &m->graph_full);
+    if (st == RUNIT_OK) st = record_graph(m, false, &m->graph_prompt);
+    if (st != RUNIT_OK) {
+        runit_model_destroy(m);
+        return st;
+    }
+    *out = m;
+    return RUNIT_OK;
+}
+
+int32_t runit_model_destroy(runit_model_t* m) {
+    if (!m) return RUNIT_ERR_BAD_ARG;
+    cudaStreamSynchronize(m->ctx->stream);
+    if (m->graph_full) cudaGraphExecDestroy(m->graph_full);
+    if (m->graph_prompt) cudaGraphExecDestroy(m->graph_prompt);
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+    return RUNIT_OK;
+}
+
+// Clear the KV position: the next step runs at `pos` with input token `token`.
+int32_t runit_model_reset(runit_model_t* m, int32_t token, int32_t pos) {
+    if (!m) return RUNIT_ERR_BAD_ARG;
+    runit_ctx* ctx = m->ctx;
+    RUNIT_REQUIRE(ctx, token >= 0 && token < m->cfg.vocab, "model_reset: token id %d out of range", token);   // forward.rs:1804-1806
+    RUNIT_REQUIRE(ctx, pos >= 0 && pos < m->cfg.max_seq, "model_reset: position %d out of range", pos);
+    const int32_t init[4] = {token, pos, 0, 0};
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->state, init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
+    RUNIT_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));   // `init` lives on this stack frame
+    return RUNIT_OK;
+}
+
+// Executor::forward_greedy(token_id, pos, kv) -> next token (forward.rs:1795-1975): one step, synchronous.
+int32_t runit_model_forward_greedy(runit_model_t* m, int32_t token_id, int32_t pos, int32_t* next_token) {
+    if (!m) return RUNIT_ERR_BAD_ARG;
+    runit_ctx* ctx = m->ctx;
+    int32_t st = runit_model_reset(m, token_id, pos);
+    if (st != RUNIT_OK) return st;
+    // step 0 must not be forced by a prompt left over from runit_model_generate_greedy
+    RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(m->forced, 0xFF, 4, ctx->stream));
+    RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(m->graph_full, ctx->stream));
+    int32_t tok = -1;
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(&tok, m->state, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    st = runit_flush(ctx);
+    if (st != RUNIT_OK) return st;
+    if (next_token) *next_token = tok;
+    return RUNIT_OK;
+}
+
+// Run a prompt of n_prompt known tokens followed by n_gen greedy steps, starting at position start_pos,
+// entirely on the device.  out_tokens (host, n_prompt + n_gen entries): out_tokens[i] is the arg-max token
+// after step i; prompt steps before the last give -1 when skip_prompt_logits is set (their logits are not
+// computed).  The generated continuation is out_tokens[n_prompt-1 ...].  One synchronisation at the end.
+int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen,
+                                    int32_t start_pos, int32_t skip_prompt_logits, int32_t* out_tokens) {
+    if (!m) return RUNIT_ERR_BAD_ARG;
+    runit_ctx* ctx = m->ctx;
+    RUNIT_REQUIRE(ctx, prompt && n_prompt > 0 && out_tokens, "model_generate_greedy: null or empty prompt");
+    const uint32_t n_steps = n_prompt + n_gen;
+    RUNIT_REQUIRE(ctx, start_pos >= 0 && (uint64_t)start_pos + n_steps <= (uint64_t)m->cfg.max_seq,
+                  "model_generate_greedy: %u steps from position %d exceed max_seq %d", n_steps, start_pos, m->cfg.max_seq);   // kv_cache.rs:63
+    RUNIT_REQUIRE(ctx, n_prompt <= m->forced_cap && n_steps <= m->out_cap, "model_generate_greedy: too many steps");
+    for (uint32_t i = 0; i < n_prompt; i++)
+        RUNIT_REQUIRE(ctx, prompt[i] >= 0 && prompt[i] < m->cfg.vocab, "model_generate_greedy: token id %d out of range", prompt[i]);
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->forced, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, ctx->stream));
+    int32_t st = runit_model_reset(m, prompt[0], start_pos);
+    if (st != RUNIT_OK) return st;
+    // Steps past the prompt are not forced: their entries are negative and the step takes the previous argmax.
+    RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(m->forced + n_prompt, 0xFF, (size_t)(m->forced_cap - n_prompt) * 4, ctx->stream));
+    for (uint32_t i = 0; i < n_steps; i++) {
+        const bool prompt_step = i + 1 < n_prompt;
+        cudaGraphExec_t g = (prompt_step && skip_prompt_logits) ? m->graph_prompt : m->graph_full;
+        RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(g, ctx->stream));
+    }
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(out_tokens, m->out_tokens, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return runit_flush(ctx);
+}
+
+void* runit_model_logits(runit_model_t* m) { return m ? (void*)m->logits : nullptr; }
+uint64_t runit_model_launches_per_token(runit_model_t* m) {
+    if (!m) return 0;
+    // embed + per layer (norm, qkv, rope, 2 kv, attention+combine, o-proj, norm, 5 MoE) + norm, lm_head, argmax, advance
+    return 1 + (uint64_t)m->cfg.n_layers * (1 + 1 + 1 + 2 + (m->nsplit > 1 ? 2 : 1) + 1 + 1 + 5) + 4;
+}
+
+}  // extern "C"

@@ -1,0 +1,370 @@
+// Decode-step operators besides the GEMVs: RMSNorm, RoPE, KV-cache scatter, q_len=1 attention, argmax.
+//
+// Twins of crates/kernels/shaders/{norm.metal:95-154, fused_rope.metal:17-56, activation.metal:13-110,
+// attention.metal:172-308} of the reference.  The position / KV length can come from a device word
+// (pos_ptr) so that a recorded command list can be replayed for successive tokens.
+#include "decode_ops.cuh"
+#include "runit_internal.h"
+
+namespace runit {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// y = x * rsqrt(mean(x^2) + eps) * gamma, one CTA per row (norm.metal:95-154).
+template <typename G>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                        const G* __restrict__ gamma, float eps, uint32_t hidden) {
+    __shared__ float part[8];
+    const float* row = x + (size_t)blockIdx.x * hidden;
+    float* out = y + (size_t)blockIdx.x * hidden;
+    float s = 0.f;
+    for (uint32_t i = threadIdx.x; i < hidden; i += 256) {
+        const float v = row[i];
+        s = fmaf(v, v, s);
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += part[i];
+    const float r = rsqrtf(tot / (float)hidden + eps);
+    for (uint32_t i = threadIdx.x; i < hidden; i += 256) {
+        float g;
+        if (sizeof(G) == 2) g = __half2float(reinterpret_cast<const __half*>(gamma)[i]);
+        else g = reinterpret_cast<const float*>(gamma)[i];
+        out[i] = row[i] * r * g;   // x and y may be the same buffer (QK-norm is applied in place)
+    }
+}
+
+// Rotary embedding of Q and K in one launch: pairs (d, d+hd/2), freq = theta^(-2d/hd)
+// (fused_rope.metal:17-56).  Optionally scatters the rotated K and the V vector into f16 caches.
+__global__ void rope_qk_kernel(float* q, float* k, uint32_t head_dim, uint32_t q_heads, uint32_t kv_heads, uint32_t pos_val,
+                               const int32_t* pos_ptr, float theta) {
+    const uint32_t d = threadIdx.x, hid = blockIdx.x, half = head_dim / 2;
+    if (d >= half) return;
+    const uint32_t pos = pos_ptr ? (uint32_t)*pos_ptr : pos_val;
+    const float freq = 1.0f / powf(theta, (float)(2 * d) / (float)head_dim);
+    const float angle = (float)pos * freq;
+    const float c = cosf(angle), s = sinf(angle);
+    if (hid < q_heads) {
+        float* p = q + (size_t)hid * head_dim;
+        const float a = p[d], b = p[d + half];
+        p[d] = a * c - b * s;
+        p[d + half] = a * s + b * c;
+    }
+    if (hid < kv_heads) {
+        float* p = k + (size_t)hid * head_dim;
+        const float a = p[d], b = p[d + half];
+        p[d] = a * c - b * s;
+        p[d + half] = a * s + b * c;
+    }
+}
+
+// dst[(h*max_seq + pos)*hd + d] = src[h*hd + d]   (activation.metal:13-44)
+template <typename S, typename D>
+__global__ void kv_copy_kernel(const S* __restrict__ src, D* __restrict__ dst, uint32_t pos_val, const int32_t* pos_ptr,
+                               uint32_t max_seq, uint32_t head_dim) {
+    const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y;
+    if (d >= head_dim) return;
+    const uint32_t pos = pos_ptr ? (uint32_t)*pos_ptr : pos_val;
+    if (pos >= max_seq) return;
+    const float v = (float)src[(size_t)h * head_dim + d];
+    dst[((size_t)h * max_seq + pos) * head_dim + d] = (D)v;
+}
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p, size_t i) { return (float)p[i]; }
+
+// q_len = 1 attention with online softmax (attention.metal:172-308), split over the KV positions.
+//   grid (heads, nsplit, batch), 128 threads.  Score phase: lane <-> KV position (32 positions per warp
+//   step, full dot product per lane); value phase: lane <-> output dims, probabilities broadcast by
+//   shuffle.  nsplit == 1: writes the normalised output; else partial (m, l, o[hd]) per split.
+template <typename TQ, typename TKV, typename TO, int DPL>
+__global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__ Q, const TKV* __restrict__ K,
+                                                           const TKV* __restrict__ V, TO* __restrict__ O, float* part,
+                                                           uint32_t kv_len_val, const int32_t* pos_ptr, uint32_t heads,
+                                                           uint32_t kv_heads, uint32_t kv_head_stride, float scale) {
+    constexpr int HD = 32 * DPL;
+    __shared__ float qs[HD];
+    __shared__ float sm_m[4], sm_l[4];
+    __shared__ float sm_o[4][HD];
+    const uint32_t head = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, batch = blockIdx.z;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t kv_len = pos_ptr ? (uint32_t)*pos_ptr + 1u : kv_len_val;
+    const uint32_t kvh = head / (heads / kv_heads);
+    const size_t qbase = ((size_t)batch * heads + head) * HD;
+    const size_t kvbase = ((size_t)batch * kv_heads + kvh) * kv_head_stride * HD;
+    for (uint32_t d = threadIdx.x; d < HD; d += 128) qs[d] = ldf(Q, qbase + d);
+    __syncthreads();
+    const uint32_t chunk = ((kv_len + nsplit - 1) / nsplit + 31) / 32 * 32;
+    const uint32_t beg = split * chunk, end = min(kv_len, beg + chunk);
+    float m = -INFINITY, l = 0.f, o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; i++) o[i] = 0.f;
+    for (uint32_t g = beg + 32 * warp; g < end; g += 128) {
+        const uint32_t p = g + lane;
+        float score = -INFINITY;
+        if (p < end) {
+            const TKV* kr = K + kvbase + (size_t)p * HD;
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+            for (int d = 0; d < HD; d += 2) {
+                a0 = fmaf(qs[d], (float)kr[d], a0);
+                a1 = fmaf(qs[d + 1], (float)kr[d + 1], a1);
+            }
+            score = (a0 + a1) * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(score));
+        const float resc = expf(m - m_new);      // exp(-inf) = 0 on the first group
+        const float pe = (p < end) ? expf(score - m_new) : 0.f;
+        l = l * resc + warp_sum(pe);
+#pragma unroll
+        for (int i = 0; i < DPL; i++) o[i] *= resc;
+        const uint32_t cnt = min(32u, end - g);
+        for (uint32_t j = 0; j < cnt; j++) {
+            const float pj = __shfl_sync(0xffffffffu, pe, j);
+            const TKV* vr = V + kvbase + (size_t)(g + j) * HD + lane * DPL;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) o[i] = fmaf(pj, (float)vr[i], o[i]);
+        }
+        m = m_new;
+    }
+    // merge the four warps in warp order
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < DPL; i++) sm_o[warp][lane * DPL + i] = o[i];
+    __syncthreads();
+    if (warp == 0) {
+        float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+        float Lt = 0.f, acc[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; i++) acc[i] = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float f = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - M);
+            Lt += sm_l[w] * f;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) acc[i] += sm_o[w][lane * DPL + i] * f;
+        }
+        if (nsplit == 1) {
+            const float inv = Lt > 0.f ? 1.0f / Lt : 0.f;
+#pragma unroll
+            for (int i = 0; i < DPL; i++) O[qbase + lane * DPL + i] = (TO)(acc[i] * inv);
+        } else {
+            float* pp = part + (((size_t)batch * heads + head) * nsplit + split) * (HD + 2);
+            if (lane == 0) { pp[0] = M; pp[1] = Lt; }
+#pragma unroll
+            for (int i = 0; i < DPL; i++) pp[2 + lane * DPL + i] = acc[i];
+        }
+    }
+}
+
+// Merge the per-split partials of one head in split order.
+template <typename TO>
+__global__ void decode_attn_combine_kernel(const float* __restrict__ part, TO* __restrict__ O, uint32_t nsplit, uint32_t hd) {
+    const uint32_t bh = blockIdx.x, d = threadIdx.x;
+    if (d >= hd) return;
+    const float* pp = part + (size_t)bh * nsplit * (hd + 2);
+    float M = -INFINITY;
+    for (uint32_t s = 0; s < nsplit; s++) M = fmaxf(M, pp[s * (hd + 2)]);
+    float L = 0.f, acc = 0.f;
+    for (uint32_t s = 0; s < nsplit; s++) {
+        const float ms = pp[s * (hd + 2)];
+        const float f = (ms == -INFINITY) ? 0.f : expf(ms - M);
+        L += pp[s * (hd + 2) + 1] * f;
+        acc += pp[s * (hd + 2) + 2 + d] * f;
+    }
+    O[(size_t)bh * hd + d] = (TO)(L > 0.f ? acc / L : 0.f);
+}
+
+// Index of the maximum, lowest index among equal maxima; one CTA of 1024 threads (activation.metal:56-110
+// scans the same way but leaves ties unspecified).
+template <typename T>
+__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ in, int32_t* __restrict__ result, uint32_t n) {
+    __shared__ float sv[32];
+    __shared__ uint32_t sidx[32];
+    float bv = -INFINITY;
+    uint32_t bi = 0xFFFFFFFFu;
+    for (uint32_t i = threadIdx.x; i < n; i += 1024) {
+        const float v = (float)in[i];
+        if (v > bv || bi == 0xFFFFFFFFu) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; sidx[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        bv = sv[threadIdx.x];
+        bi = sidx[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) result[0] = (int32_t)bi;
+    }
+}
+
+// ───────────────────────── host launchers (shared with decode_model.cu) ─────────────────────────
+
+int32_t launch_rms_norm(runit_ctx* ctx, const float* x, float* y, const void* gamma, bool gamma_f16, float eps,
+                        uint32_t hidden, uint32_t rows) {
+    if (gamma_f16) rms_norm_kernel<__half><<<rows, 256, 0, ctx->stream>>>(x, y, (const __half*)gamma, eps, hidden);
+    else rms_norm_kernel<float><<<rows, 256, 0, ctx->stream>>>(x, y, (const float*)gamma, eps, hidden);
+    return runit_after_launch(ctx, "rms_norm");
+}
+
+int32_t launch_rope(runit_ctx* ctx, float* q, float* k, uint32_t hd, uint32_t qh, uint32_t kvh, uint32_t pos,
+                    const int32_t* pos_ptr, float theta) {
+    const uint32_t hmax = qh > kvh ? qh : kvh;
+    rope_qk_kernel<<<hmax, hd / 2, 0, ctx->stream>>>(q, k, hd, qh, kvh, pos, pos_ptr, theta);
+    return runit_after_launch(ctx, "fused_rope_qk_f32");
+}
+
+int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst, bool dst_f16, uint32_t pos,
+                       const int32_t* pos_ptr, uint32_t max_seq, uint32_t hd, uint32_t kvh) {
+    dim3 grid((hd + 127) / 128, kvh);
+    if (src_f16 && dst_f16) kv_copy_kernel<__half, __half><<<grid, 128, 0, ctx->stream>>>((const __half*)src, (__half*)dst, pos, pos_ptr, max_seq, hd);
+    else if (!src_f16 && !dst_f16) kv_copy_kernel<float, float><<<grid, 128, 0, ctx->stream>>>((const float*)src, (float*)dst, pos, pos_ptr, max_seq, hd);
+    else if (!src_f16 && dst_f16) kv_copy_kernel<float, __half><<<grid, 128, 0, ctx->stream>>>((const float*)src, (__half*)dst, pos, pos_ptr, max_seq, hd);
+    else return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "kv_copy: f16 source into an f32 cache");
+    return runit_after_launch(ctx, "kv_copy_to_cache");
+}
+
+template <typename TQ, typename TKV, typename TO>
+static int32_t attn_typed(runit_ctx* ctx, const void* q, const void* k, const void* v, void* out, float* part, uint32_t nsplit,
+                          uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr, uint32_t heads, uint32_t kv_heads,
+                          uint32_t hd, uint32_t stride) {
+    const float scale = 1.0f / sqrtf((float)hd);   // dispatch.rs:1588
+    dim3 grid(heads, nsplit, batch);
+#define ATTN_CASE(D)                                                                                                   \
+    decode_attn_kernel<TQ, TKV, TO, D><<<grid, 128, 0, ctx->stream>>>((const TQ*)q, (const TKV*)k, (const TKV*)v, (TO*)out, \
+                                                                      part, kv_len, pos_ptr, heads, kv_heads, stride, scale)
+    switch (hd) {
+        case 32: ATTN_CASE(1); break;
+        case 64: ATTN_CASE(2); break;
+        case 96: ATTN_CASE(3); break;
+        case 128: ATTN_CASE(4); break;
+        default: return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "decode_attention: head_dim %u not in {32,64,96,128}", hd);
+    }
+#undef ATTN_CASE
+    int32_t st = runit_after_launch(ctx, "decode_attention");
+    if (st != RUNIT_OK || nsplit == 1) return st;
+    decode_attn_combine_kernel<TO><<<batch * heads, hd, 0, ctx->stream>>>(part, (TO*)out, nsplit, hd);
+    return runit_after_launch(ctx, "decode_attention_combine");
+}
+
+int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const void* q, const void* k, const void* v, void* out,
+                                float* part, uint32_t nsplit, uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr,
+                                uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride) {
+    if (q_kind == 0 && kv_kind == 0)
+        return attn_typed<float, float, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride);
+    if (q_kind == 1 && kv_kind == 1)
+        return attn_typed<__half, __half, __half>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride);
+    if (q_kind == 0 && kv_kind == 1)
+        return attn_typed<float, __half, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride);
+    return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "decode_attention: f16 query with f32 cache");
+}
+
+int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* result, uint32_t n) {
+    if (in_f16) argmax_kernel<__half><<<1, 1024, 0, ctx->stream>>>((const __half*)in, result, n);
+    else argmax_kernel<float><<<1, 1024, 0, ctx->stream>>>((const float*)in, result, n);
+    return runit_after_launch(ctx, "argmax");
+}
+
+}  // namespace runit
+
+using namespace runit;
+
+extern "C" {
+
+int32_t runit_rms_norm_f32_f32(runit_ctx_t* ctx, const void* x, void* y, const void* gamma, float eps, uint32_t hidden,
+                               uint32_t num_rows) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, x && y && gamma && hidden > 0 && num_rows > 0, "rms_norm_f32_f32: bad argument");
+    return launch_rms_norm(ctx, (const float*)x, (float*)y, gamma, true, eps, hidden, num_rows);
+}
+
+int32_t runit_rms_norm_f32_f32_f32g(runit_ctx_t* ctx, const void* x, void* y, const void* gamma, float eps, uint32_t hidden,
+                                    uint32_t num_rows) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, x && y && gamma && hidden > 0 && num_rows > 0, "rms_norm_f32_f32_f32g: bad argument");
+    return launch_rms_norm(ctx, (const float*)x, (float*)y, gamma, false, eps, hidden, num_rows);
+}
+
+int32_t runit_fused_rope_qk_f32(runit_ctx_t* ctx, void* q, void* k, uint32_t head_dim, uint32_t q_heads, uint32_t kv_heads,
+                                uint32_t pos, float theta) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, q && k && head_dim >= 2 && head_dim % 2 == 0 && head_dim <= 2048 && (q_heads > 0 || kv_heads > 0),
+                  "fused_rope_qk_f32: bad argument");
+    return launch_rope(ctx, (float*)q, (float*)k, head_dim, q_heads, kv_heads, pos, nullptr, theta);
+}
+
+int32_t runit_kv_copy_to_cache_f16(runit_ctx_t* ctx, const void* src, void* dst, uint32_t pos, uint32_t max_seq,
+                                   uint32_t head_dim, uint32_t num_kv_heads) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, src && dst && head_dim > 0 && num_kv_heads > 0, "kv_copy_to_cache_f16: bad argument");
+    RUNIT_REQUIRE(ctx, pos < max_seq, "kv_copy_to_cache_f16: pos %u >= max_seq %u", pos, max_seq);   // kv_cache.rs:63
+    return launch_kv_copy(ctx, src, true, dst, true, pos, nullptr, max_seq, head_dim, num_kv_heads);
+}
+
+int32_t runit_kv_copy_to_cache_f32(runit_ctx_t* ctx, const void* src, void* dst, uint32_t pos, uint32_t max_seq,
+                                   uint32_t head_dim, uint32_t num_kv_heads) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, src && dst && head_dim > 0 && num_kv_heads > 0, "kv_copy_to_cache_f32: bad argument");
+    RUNIT_REQUIRE(ctx, pos < max_seq, "kv_copy_to_cache_f32: pos %u >= max_seq %u", pos, max_seq);
+    return launch_kv_copy(ctx, src, false, dst, false, pos, nullptr, max_seq, head_dim, num_kv_heads);
+}
+
+int32_t runit_kv_copy_to_cache_f32_f16(runit_ctx_t* ctx, const void* src, void* dst, uint32_t pos, uint32_t max_seq,
+                                       uint32_t head_dim, uint32_t num_kv_heads) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, src && dst && head_dim > 0 && num_kv_heads > 0, "kv_copy_to_cache_f32_f16: bad argument");
+    RUNIT_REQUIRE(ctx, pos < max_seq, "kv_copy_to_cache_f32_f16: pos %u >= max_seq %u", pos, max_seq);
+    return launch_kv_copy(ctx, src, false, dst, true, pos, nullptr, max_seq, head_dim, num_kv_heads);
+}
+
+#define ATTN_ENTRY(NAME, QK, KVK)                                                                                        \
+    int32_t runit_##NAME(runit_ctx_t* ctx, const void* q, const void* k, const void* v, void* out, uint32_t batch,       \
+                         uint32_t kv_len, uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim,                   \
+                         uint32_t kv_head_stride) {                                                                      \
+        if (!ctx) return RUNIT_ERR_BAD_ARG;                                                                              \
+        RUNIT_REQUIRE(ctx, q && k && v && out, #NAME ": null pointer");                                                  \
+        RUNIT_REQUIRE(ctx, batch > 0 && kv_len > 0 && num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0, \
+                      #NAME ": bad shape");                                                                              \
+        RUNIT_REQUIRE(ctx, kv_len <= kv_head_stride, #NAME ": kv_len %u exceeds the cache stride %u", kv_len, kv_head_stride); \
+        return launch_decode_attention(ctx, QK, KVK, q, k, v, out, nullptr, 1, batch, kv_len, nullptr, num_heads,        \
+                                       num_kv_heads, head_dim, kv_head_stride);                                          \
+    }
+ATTN_ENTRY(decode_attention_f32, 0, 0)
+ATTN_ENTRY(decode_attention_f16, 1, 1)
+ATTN_ENTRY(decode_attention_f32q_f16kv, 0, 1)
+
+int32_t runit_argmax_f16(runit_ctx_t* ctx, const void* input, void* result, uint32_t n) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, input && result && n > 0, "argmax_f16: bad argument");
+    return launch_argmax(ctx, input, true, (int32_t*)result, n);
+}
+
+int32_t runit_argmax_f32(runit_ctx_t* ctx, const void* input, void* result, uint32_t n) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, input && result && n > 0, "argmax_f32: bad argument");
+    return launch_argmax(ctx, input, false, (int32_t*)result, n);
+}
+
+}  // extern "C"

@@ -1,0 +1,32 @@
+// Launchers of the decode-step operators, shared by the C-ABI twins and the decoder (decode_model.cu).
+// pos_ptr != nullptr: the position (and kv_len = pos + 1) is read from that device word at run time.
+#pragma once
+
+#include "runit_internal.h"
+
+namespace runit {
+
+int32_t launch_rms_norm(runit_ctx* ctx, const float* x, float* y, const void* gamma, bool gamma_f16, float eps,
+                        uint32_t hidden, uint32_t rows);
+int32_t launch_rope(runit_ctx* ctx, float* q, float* k, uint32_t hd, uint32_t qh, uint32_t kvh, uint32_t pos,
+                    const int32_t* pos_ptr, float theta);
+int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst, bool dst_f16, uint32_t pos,
+                       const int32_t* pos_ptr, uint32_t max_seq, uint32_t hd, uint32_t kvh);
+// q_kind / kv_kind: 0 = f32, 1 = f16.  part: scratch of batch*heads*nsplit*(hd+2) floats when nsplit > 1.
+int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const void* q, const void* k, const void* v, void* out,
+                                float* part, uint32_t nsplit, uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr,
+                                uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride);
+int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* result, uint32_t n);
+
+// gemv.cu: one fused-dequant GEMV with up to three row segments sharing the input (Q|K|V) — any format.
+int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const void* const* w, void* const* y,
+                      const uint32_t* rows, const void* x, uint32_t k);
+int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
+                   uint32_t m, uint32_t k);
+// moe.cu
+int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
+                           const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
+                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
+size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);
+
+}  // namespace runit

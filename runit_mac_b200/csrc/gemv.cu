@@ -197,6 +197,27 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
     return gemv_dispatch(ctx, c);
 }
 
+int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const void* const* w, void* const* y,
+                      const uint32_t* rows, const void* x, uint32_t k) {
+    GemvCall c;
+    c.name = name;
+    c.fmt = fmt;
+    c.nseg = nseg;
+    for (int i = 0; i < nseg && i < 3; i++) {
+        c.w[i] = w[i];
+        c.y[i] = y[i];
+        c.rows[i] = rows[i];
+    }
+    c.x = x;
+    c.k = k;
+    return gemv_dispatch(ctx, c);
+}
+
+int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
+                   uint32_t m, uint32_t k) {
+    return gemv1(ctx, name, fmt, w, x, y, res_f32, m, k, false, false, res_f32 ? RES_F32 : RES_NONE);
+}
+
 }  // namespace runit
 
 using namespace runit;

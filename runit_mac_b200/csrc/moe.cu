@@ -6,6 +6,7 @@
 // launch for gate+up+SiLU of all (token, expert) slots, ONE grouped launch for down, and a combine
 // kernel that adds the weighted expert outputs in routing order (deterministic) plus the residual.
 // All intermediates are f32.
+#include "decode_ops.cuh"
 #include "gemv_common.cuh"
 #include "runit_internal.h"
 
@@ -160,6 +161,10 @@ static int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float*
     else if (K == 4096) router_f32_kernel<128><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
     else router_f32_generic_kernel<<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
     return runit_after_launch(ctx, "moe_router_f32");
+}
+
+size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
+    return moe_carve(nullptr, T, h, ff, E, k).bytes;
 }
 
 // The whole block; scratch carved from `scratch`.

@@ -219,6 +219,17 @@ _TWINS = [
     ("scale_accumulate_f16", "dispatch.rs:1639 (src, acc, weight, n)"),
     ("add_f16_into_f32", "dispatch.rs:316 (src, acc, n)"),
     ("gemv_batched_f32", "no twin: (fmt, weight, input, output, residual, m, k, batch)"),
+    ("rms_norm_f32_f32", "dispatch.rs:152 (x, y, gamma_f16, eps, hidden, num_rows)"),
+    ("rms_norm_f32_f32_f32g", "dispatch.rs:177 (x, y, gamma_f32, eps, hidden, num_rows)"),
+    ("fused_rope_qk_f32", "dispatch.rs:945 (q, k, head_dim, q_heads, kv_heads, pos, theta)"),
+    ("kv_copy_to_cache_f16", "dispatch.rs:1159 (src, dst, pos, max_seq, head_dim, num_kv_heads)"),
+    ("kv_copy_to_cache_f32", "dispatch.rs:1183"),
+    ("kv_copy_to_cache_f32_f16", "no twin: f32 source, f16 cache"),
+    ("decode_attention_f32", "dispatch.rs:1575 (q, k, v, out, batch, kv_len, num_heads, num_kv_heads, head_dim, kv_head_stride)"),
+    ("decode_attention_f16", "dispatch.rs:697"),
+    ("decode_attention_f32q_f16kv", "no twin: f32 query over an f16 cache"),
+    ("argmax_f16", "dispatch.rs:1615 (input, result, n)"),
+    ("argmax_f32", "no twin: f32 logits"),
     ("moe_router_f32", "no twin: (router_w, x, logits, E, h, T)"),
     ("moe_route_topk", "forward.rs:2420-2448 on the device: (logits, logits_f16, E, k, renorm, T, out_idx, out_w)"),
     ("moe_layer_q4k", "forward.rs:1644-1679 as one call: (router_w, gate, up, down, x, residual, out, idx_out, w_out, "
@@ -230,6 +241,57 @@ _TWINS = [
 for _n, _d in _TWINS:
     globals()[_n] = _twin(_n, _d)
 del _n, _d
+
+class ModelCfg(C.Structure):
+    """runit_model_cfg; field names follow ModelConfig (crates/engine/src/config.rs:42-89)."""
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "vocab", "n_experts",
+                                         "top_k", "ff", "max_seq", "renorm")] + [("eps", C.c_float), ("theta", C.c_float)]
+
+
+class ModelWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("tok_emb", "attn_norm", "ffn_norm", "out_norm", "wq", "wk", "wv", "wo", "router",
+                                          "gate", "up", "down", "lm_head")]
+
+
+class Model:
+    """Greedy decoder over device-resident Q4_K weights; the role of Executor (forward.rs:1239, 1795-1975)."""
+
+    def __init__(self, ctx: Context, cfg: ModelCfg, weights: dict):
+        self.ctx, self.cfg, self._keep = ctx, cfg, weights
+        w = ModelWeights(**{k: _ptr(v) for k, v in weights.items()})
+        h = C.c_void_p()
+        ctx._check(ctx.lib.runit_model_create(ctx.handle, C.byref(cfg), C.byref(w), C.byref(h)))
+        self.handle = h
+
+    def forward_greedy(self, token_id: int, pos: int) -> int:
+        nxt = C.c_int32(-1)
+        self.ctx._check(self.ctx.lib.runit_model_forward_greedy(self.handle, token_id, pos, C.byref(nxt)))
+        return nxt.value
+
+    def generate_greedy(self, prompt, n_gen: int, start_pos: int = 0, skip_prompt_logits: bool = True) -> np.ndarray:
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.empty(len(prompt) + n_gen, np.int32)
+        self.ctx._check(self.ctx.lib.runit_model_generate_greedy(
+            self.handle, prompt.ctypes.data_as(C.POINTER(C.c_int32)), len(prompt), n_gen, start_pos,
+            int(skip_prompt_logits), out.ctypes.data_as(C.POINTER(C.c_int32))))
+        return out
+
+    def logits(self) -> np.ndarray:
+        out = np.empty(self.cfg.vocab, np.float32)
+        p = self.ctx.lib.runit_model_logits(self.handle)
+        self.ctx._check(self.ctx.lib.runit_memcpy_d2h(self.ctx.handle, out.ctypes.data, p, out.nbytes))
+        self.ctx.flush()
+        return out
+
+    @property
+    def launches_per_token(self) -> int:
+        return self.ctx.lib.runit_model_launches_per_token(self.handle)
+
+    def close(self):
+        if self.handle:
+            self.ctx.lib.runit_model_destroy(self.handle)
+            self.handle = None
+
 
 def moe_scratch_bytes(ctx: Context, T: int, h: int, ff: int, E: int, k: int) -> int:
     return ctx.lib.runit_moe_scratch_bytes(T, h, ff, E, k)
@@ -251,5 +313,5 @@ def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top
             w.download(np.float32, T * top_k).reshape(T, top_k))
 
 
-__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "moe_scratch_bytes", "moe_layer_q4k_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "moe_scratch_bytes", "moe_layer_q4k_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
            "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K"] + [n for n, _ in _TWINS]
