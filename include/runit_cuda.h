@@ -185,6 +185,14 @@ int32_t runit_moe_layer_q4k(runit_ctx_t*, const void* router_w, const void* gate
                             const void* x, const void* residual, void* out, void* idx_out, void* w_out, void* scratch,
                             size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
 
+/* The expert part alone, for expert-parallel execution: slot s holds one token row x_slots[s] (f32 [h]) routed to
+ * local expert slot_expert[s] (int32; a negative id marks an unused slot: nothing is computed or written for it);
+ * y_slots[s] = Wdown[e] . (silu(Wgate[e].x) * (Wup[e].x)).  gate/up: Q4_K [n_experts][ff][h]; down: Q4_K
+ * [n_experts][h][ff]; act_scratch: f32 [n_slots][ff], caller-owned. */
+int32_t runit_moe_experts_q4k(runit_ctx_t*, const void* gate, const void* up, const void* down, const void* x_slots,
+                              const void* slot_expert, void* y_slots, void* act_scratch, uint32_t n_slots, uint32_t h,
+                              uint32_t ff, uint32_t n_experts);
+
 /* No counterpart in the reference.  The same MoE block as runit_moe_layer_q4k for callers that cannot hand
  * over scratch memory: a host engine that gives every free byte of device memory to its own weight and
  * KV-cache pools at start-up, or a serving loop that must not call cudaMalloc because that call stalls the

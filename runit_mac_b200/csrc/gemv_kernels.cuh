@@ -316,16 +316,19 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     uint32_t row0 = (tile - sg.tile_begin) * RPT;
     uint32_t wrow0 = row0;                       // row of the tile inside the weight matrix
     const uint8_t* xbase = reinterpret_cast<const uint8_t*>(a.x);
+    bool slot_live = true;   // grouped mode: a negative expert id marks an unused slot (nothing is computed or written)
     if (a.grp_expert != nullptr && tile_ok) {
         const uint32_t slot = tile / a.grp_tiles;
         row0 = (tile - slot * a.grp_tiles) * RPT;
-        wrow0 = (uint32_t)a.grp_expert[slot] * a.grp_rows + row0;
+        const int32_t eid = a.grp_expert[slot];
+        slot_live = eid >= 0;
+        wrow0 = (uint32_t)(slot_live ? eid : 0) * a.grp_rows + row0;
         xbase += (size_t)(slot / a.grp_xdiv) * a.k * (XF16 ? 2 : 4);
         sg.y = reinterpret_cast<uint8_t*>(sg.y) + (size_t)slot * a.ldy * (a.out_f16 ? 2 : 4);
     }
-    const uint32_t rows_here = tile_ok ? min((uint32_t)RPT, sg.rows - row0) : 0u;
+    const uint32_t rows_here = (tile_ok && slot_live) ? min((uint32_t)RPT, sg.rows - row0) : 0u;
     const bool row_ok = (uint32_t)(DUAL ? (lane & 15) : lane) < rows_here;
-    const int n_it = tile_ok ? ((int)a.n_units - slice + KSL - 1) / KSL : 0;   // units slice, slice+KSL, ...
+    const int n_it = (tile_ok && slot_live) ? ((int)a.n_units - slice + KSL - 1) / KSL : 0;   // units slice, slice+KSL, ...
 
     if (LD == 1) {
         if (lane == 0) {

@@ -270,6 +270,19 @@ int32_t runit_moe_route_topk(runit_ctx_t* ctx, const void* logits, int32_t logit
     return runit_after_launch(ctx, "moe_route_topk");
 }
 
+int32_t runit_moe_experts_q4k(runit_ctx_t* ctx, const void* gate, const void* up, const void* down, const void* x_slots,
+                              const void* slot_expert, void* y_slots, void* act_scratch, uint32_t n_slots, uint32_t h,
+                              uint32_t ff, uint32_t n_experts) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, gate && up && down && x_slots && slot_expert && y_slots && act_scratch, "moe_experts_q4k: null pointer");
+    RUNIT_REQUIRE(ctx, n_slots > 0 && n_experts > 0 && h % 256 == 0 && ff % 256 == 0 && h > 0 && ff > 0, "moe_experts_q4k: bad shape");
+    int32_t st = gemv_grouped(ctx, "moe_gate_up", RUNIT_FMT_Q4K, gate, up, n_experts, ff, h, x_slots, 1, act_scratch,
+                              (const int32_t*)slot_expert, n_slots);
+    if (st != RUNIT_OK) return st;
+    return gemv_grouped(ctx, "moe_down", RUNIT_FMT_Q4K, down, nullptr, n_experts, h, ff, act_scratch, 1, y_slots,
+                        (const int32_t*)slot_expert, n_slots);
+}
+
 int32_t runit_moe_layer_q4k(runit_ctx_t* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                             const void* x, const void* residual, void* out, void* idx_out, void* w_out, void* scratch,
                             size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {

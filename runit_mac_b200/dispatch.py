@@ -234,6 +234,7 @@ _TWINS = [
     ("moe_route_topk", "forward.rs:2420-2448 on the device: (logits, logits_f16, E, k, renorm, T, out_idx, out_w)"),
     ("moe_layer_q4k", "forward.rs:1644-1679 as one call: (router_w, gate, up, down, x, residual, out, idx_out, w_out, "
                       "scratch, scratch_bytes, T, h, ff, E, k, renorm)"),
+    ("moe_experts_q4k", "no twin: (gate, up, down, x_slots, slot_expert, y_slots, act_scratch, n_slots, h, ff, n_experts)"),
     ("moe_layer_q4k_static", "no twin: moe_layer_q4k without the scratch arguments (built-in 4 MiB region)"),
     ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
     ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),

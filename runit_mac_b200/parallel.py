@@ -1,0 +1,200 @@
+"""Single-node multi-GPU execution of the two parts of the path that shard: one process per GPU,
+`torch.distributed` (NCCL over NVLink / NVSwitch on GPUs, gloo on CPU for the host-logic tests).
+
+The reference is single-device (crates/engine/src/server/mod.rs:20-30 serialises everything behind one
+Mutex<Executor>); both schemes below are new:
+
+* row-sharded GEMV (lm_head): rank r owns rows [r*M/G, (r+1)*M/G) of the weight matrix, the input vector is
+  replicated, the logits are all-gathered;
+* expert-parallel MoE: rank r owns experts [r*E/G, (r+1)*E/G); tokens are data-parallel.  Every rank routes
+  its own tokens, sends each (token, expert) slot to the expert's owner with ONE fixed-capacity all-to-all
+  (no count exchange, hence no host synchronisation), the owner runs the expert FFN on the slots it received,
+  a second all-to-all returns the results and the source adds them weighted in routing order.
+
+All remote data lands in local memory through the collective before a kernel reads it.  The arithmetic is
+supplied by a backend object so the same host logic runs on CPU in the tests (backend supplied by the test)
+and on GPU (`CudaBackend`, C-ABI calls on torch tensors).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def shard_rows(m: int, world: int, rank: int):
+    """(first row, row count) of `rank`; requires world | m (152064 and 50304 divide by 2, 4, 8)."""
+    if m % world:
+        raise ValueError("rows %d do not divide over %d ranks" % (m, world))
+    n = m // world
+    return rank * n, n
+
+
+def expert_owner(expert_ids, n_experts: int, world: int):
+    """Rank owning each expert id (contiguous blocks of n_experts/world)."""
+    if n_experts % world:
+        raise ValueError("experts %d do not divide over %d ranks" % (n_experts, world))
+    return expert_ids // (n_experts // world)
+
+
+def sharded_gemv(backend, dist, torch, x, rows_total: int, world: int, rank: int):
+    """y = W.x with W row-sharded: local product + all-gather.  backend.local_gemv(x) -> [rows_total/world]."""
+    _, n = shard_rows(rows_total, world, rank)
+    y_local = backend.local_gemv(x)
+    assert y_local.numel() == n
+    y = torch.empty(rows_total, dtype=y_local.dtype, device=y_local.device)
+    if world > 1:
+        dist.all_gather_into_tensor(y, y_local.contiguous())
+    else:
+        y.copy_(y_local)
+    return y
+
+
+def ep_pack(torch, idx, n_experts: int, world: int):
+    """Placement of the local (token, expert) slots in the fixed-capacity send buffer.
+
+    idx: [T, k] expert ids.  Returns (dest [T*k], pos [T*k], cap) with slot s = t*k+i going to row
+    dest[s]*cap + pos[s] of a [world*cap] buffer; pos counts the slots already sent to that destination in
+    slot order (deterministic)."""
+    T, k = idx.shape
+    cap = T * k
+    flat = idx.reshape(-1).to(torch.int64)
+    dest = expert_owner(flat, n_experts, world)
+    onehot = torch.nn.functional.one_hot(dest, world)                       # [S, world]
+    pos = (torch.cumsum(onehot, 0) - onehot).gather(1, dest[:, None])[:, 0]  # exclusive running count per destination
+    return dest, pos, cap
+
+
+def ep_moe_forward(backend, dist, torch, x, n_experts: int, top_k: int, renorm: bool, world: int, rank: int, residual=None):
+    """Expert-parallel MoE block for this rank's tokens x [T, h] (f32).  Returns (out [T, h], idx, w).
+
+    backend.route(x) -> (idx int32 [T,k], w f32 [T,k]); backend.experts(x_slots [n,h], local_expert int32 [n])
+    -> y [n,h] (rows with local_expert < 0 are ignored)."""
+    T, h = x.shape
+    idx, w = backend.route(x)
+    dest, pos, cap = ep_pack(torch, idx, n_experts, world)
+    per_rank = n_experts // world
+    row = dest * cap + pos
+    send_x = torch.zeros(world * cap, h, dtype=x.dtype, device=x.device)
+    send_e = torch.full((world * cap,), -1, dtype=torch.int32, device=x.device)
+    tok = torch.arange(T * top_k, device=x.device) // top_k
+    send_x[row] = x[tok]
+    send_e[row] = (idx.reshape(-1).to(torch.int64) - dest * per_rank).to(torch.int32)   # expert id local to its owner
+    if world > 1:
+        recv_x, recv_e = torch.empty_like(send_x), torch.empty_like(send_e)
+        dist.all_to_all_single(recv_x, send_x)
+        dist.all_to_all_single(recv_e, send_e)
+    else:
+        recv_x, recv_e = send_x, send_e
+    y = backend.experts(recv_x, recv_e)
+    if world > 1:
+        back = torch.empty_like(y)
+        dist.all_to_all_single(back, y.contiguous())
+    else:
+        back = y
+    ys = back[row].reshape(T, top_k, h)
+    out = torch.zeros(T, h, dtype=x.dtype, device=x.device) if residual is None else residual.clone()
+    acc = torch.zeros(T, h, dtype=x.dtype, device=x.device)
+    for i in range(top_k):            # routing order, like scale_accumulate in forward.rs:1667-1676
+        acc = acc + w[:, i:i + 1] * ys[:, i, :]
+    return out + acc, idx, w
+
+
+# ───────────────────────── GPU backend (C-ABI calls on torch tensors) ─────────────────────────
+
+class CudaBackend:
+    """Arithmetic of the two schemes on the local GPU through librunit_cuda.so."""
+
+    def __init__(self, R, ctx, torch):
+        self.R, self.ctx, self.torch = R, ctx, torch
+
+    # row-sharded GEMV
+    def set_lm_head(self, fmt, w_local, rows_local, k):
+        self.fmt, self.w_local, self.rows_local, self.k = fmt, w_local, rows_local, k
+        self.y_local = self.torch.empty(rows_local, dtype=self.torch.float32, device="cuda")
+
+    def local_gemv(self, x):
+        name = {0: "q8_0", 1: "q4_0", 2: "q4k"}[self.fmt]
+        getattr(self.R, "gemv_%s_f32in_f32out" % name)(self.ctx, self.w_local, x, self.y_local, self.rows_local, self.k)
+        return self.y_local
+
+    # expert parallel
+    def set_experts(self, router, gate, up, down, n_experts, n_local, h, ff, top_k, renorm):
+        self.router, self.gate, self.up, self.down = router, gate, up, down
+        self.E, self.n_local, self.h, self.ff, self.top_k, self.renorm = n_experts, n_local, h, ff, top_k, renorm
+
+    def route(self, x):
+        t, T = self.torch, x.shape[0]
+        logits = t.empty(T, self.E, dtype=t.float32, device="cuda")
+        idx = t.empty(T, self.top_k, dtype=t.int32, device="cuda")
+        w = t.empty(T, self.top_k, dtype=t.float32, device="cuda")
+        self.R.moe_router_f32(self.ctx, self.router, x, logits, self.E, self.h, T)
+        self.R.moe_route_topk(self.ctx, logits, 0, self.E, self.top_k, int(self.renorm), T, idx, w)
+        return idx, w
+
+    def experts(self, x_slots, local_expert):
+        t, n = self.torch, x_slots.shape[0]
+        y = t.zeros(n, self.h, dtype=t.float32, device="cuda")
+        act = t.empty(n, self.ff, dtype=t.float32, device="cuda")
+        self.R.moe_experts_q4k(self.ctx, self.gate, self.up, self.down, x_slots, local_expert, y, act, n, self.h, self.ff, self.n_local)
+        return y
+
+
+def _time_steps(torch, dist, stream, ctx, fn, steps, world):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def bench_sharded_lm_head(R, ctx, torch, dist, stream, rank, world, steps=20):
+    """Qwen2.5-7B lm_head (152064 x 3584), Q4_K and Q4_0, rows split over the ranks, logits all-gathered."""
+    out = {}
+    M, K = 152064, 3584
+    _, n = shard_rows(M, world, rank)
+    x = torch.randn(K, dtype=torch.float32, device="cuda")
+    for fmt, name in ((2, "q4k"), (1, "q4_0")):
+        be = CudaBackend(R, ctx, torch)
+        rb = R.row_bytes(fmt, K)
+        w = ctx.new_buffer(n * rb)
+        R.fill_weights(ctx, fmt, w, n * (K // R.BLOCK_ELEMS[fmt]), 1002 + rank, 0.01)
+        be.set_lm_head(fmt, w, n, K)
+        ms = _time_steps(torch, dist, stream, ctx, lambda: sharded_gemv(be, dist, torch, x, M, world, rank), steps, world)
+        ms_local = _time_steps(torch, dist, stream, ctx, lambda: be.local_gemv(x), steps, world)
+        alg = M * rb + 4 * (K + M)
+        out[name] = {"us_per_call": ms * 1e3, "us_local_gemv": ms_local * 1e3, "aggregate_gbs": alg / (ms * 1e-3) / 1e9,
+                     "rows_per_rank": n}
+        w.free()
+    return out
+
+
+def bench_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
+    """One OLMoE-shaped MoE layer (hidden 2048, 64 experts, top-8, intermediate 1024, Q4_K), experts split 64/G per
+    rank, T tokens per rank."""
+    E, h, ff, k = 64, 2048, 1024, 8
+    n_local = E // world
+    rb = lambda kk: kk // 256 * 144
+    gate, up = ctx.new_buffer(n_local * ff * rb(h)), ctx.new_buffer(n_local * ff * rb(h))
+    down = ctx.new_buffer(n_local * h * rb(ff))
+    for i, (b, rows, kk) in enumerate(((gate, n_local * ff, h), (up, n_local * ff, h), (down, n_local * h, ff))):
+        R.fill_weights(ctx, 2, b, rows * (kk // 256), 77 + i + 10 * rank, 0.01)
+    router = torch.randn(E, h, dtype=torch.float32, device="cuda") * 0.02
+    if world > 1:
+        dist.broadcast(router, 0)
+    be = CudaBackend(R, ctx, torch)
+    be.set_experts(router, gate, up, down, E, n_local, h, ff, k, False)
+    out = {}
+    for T in (1, 16):
+        x = torch.randn(T, h, dtype=torch.float32, device="cuda")
+        ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
+        out["T%d_per_rank" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s_all_ranks": world * T / (ms * 1e-3)}
+    return out

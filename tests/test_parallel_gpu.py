@@ -1,0 +1,87 @@
+"""GPU check of the sharded paths through the C ABI: with one visible GPU the schemes run with world size 1
+(same host logic, CUDA backend); with two or more GPUs two NCCL ranks are spawned (NVLS disabled, plain
+collectives) and compared with the single-GPU MoE block and the oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+H, FF, E, K_TOP = 512, 256, 8, 2
+M_ROWS, K_IN = 256, 512
+
+
+def make_data(O):
+    rng = np.random.default_rng(321)
+    return {"lm": O.rand_q4k(rng, M_ROWS, K_IN).reshape(-1), "router": rng.normal(0, 0.02, (E, H)).astype(np.float32),
+            "gate": O.rand_q4k(rng, E * FF, H).reshape(-1), "up": O.rand_q4k(rng, E * FF, H).reshape(-1),
+            "down": O.rand_q4k(rng, E * H, FF).reshape(-1), "x_lm": rng.normal(0, 1, K_IN).astype(np.float32),
+            "x": rng.normal(0, 1, (8, H)).astype(np.float32)}
+
+
+def run_rank(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    import oracle as O
+    import runit_mac_b200 as R
+    from runit_mac_b200 import parallel as P
+    torch.cuda.set_device(rank)
+    if world > 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx = R.Context(rank, stream=stream.cuda_stream)
+    d = make_data(O)
+    be = P.CudaBackend(R, ctx, torch)
+    rb_in, rb_h, rb_ff = O.row_bytes(O.Q4K, K_IN), O.row_bytes(O.Q4K, H), O.row_bytes(O.Q4K, FF)
+    r0, n = P.shard_rows(M_ROWS, world, rank)
+    be.set_lm_head(2, torch.from_numpy(d["lm"].reshape(M_ROWS, rb_in)[r0:r0 + n].copy()).cuda(), n, K_IN)
+    y = P.sharded_gemv(be, dist, torch, torch.from_numpy(d["x_lm"]).cuda(), M_ROWS, world, rank)
+    nl = E // world
+    sl = lambda a, per: torch.from_numpy(a.reshape(E, per)[rank * nl:(rank + 1) * nl].copy()).cuda()
+    be.set_experts(torch.from_numpy(d["router"]).cuda(), sl(d["gate"], FF * rb_h), sl(d["up"], FF * rb_h), sl(d["down"], H * rb_ff),
+                   E, nl, H, FF, K_TOP, False)
+    T = d["x"].shape[0] // world
+    xs = torch.from_numpy(d["x"][rank * T:(rank + 1) * T]).cuda()
+    out, idx, w = P.ep_moe_forward(be, dist, torch, xs, E, K_TOP, False, world, rank)
+    torch.cuda.synchronize()
+    ctx.flush()
+    res = (rank, y.cpu().numpy(), out.cpu().numpy(), idx.cpu().numpy())
+    if world > 1:
+        dist.destroy_process_group()
+    if q is not None:
+        q.put(res)
+    return res
+
+
+def test_sharded_paths_match_oracle(oracle):
+    import torch
+    O = oracle
+    world = 2 if torch.cuda.device_count() >= 2 else 1
+    if world == 1:
+        res = [run_rank(0, 1, 0, None)]
+    else:
+        import torch.multiprocessing as mp
+        s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+        ctxm = mp.get_context("spawn")
+        q = ctxm.Queue()
+        procs = [ctxm.Process(target=run_rank, args=(r, world, port, q)) for r in range(world)]
+        for p in procs:
+            p.start()
+        res = sorted([q.get(timeout=300) for _ in range(world)], key=lambda t: t[0])
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    d = make_data(O)
+    full = O.gemv(O.Q4K, d["lm"], d["x_lm"], M_ROWS, K_IN)
+    for r in res:
+        st = O.compare(full, r[1], rel_tol=1e-3)
+        assert st.n_mismatch_rel == 0, st
+    ref, ridx, _ = O.moe_layer_q4k(d["router"], d["gate"], d["up"], d["down"], d["x"], h=H, ff=FF, E=E, top_k=K_TOP, renorm=False)
+    out = np.concatenate([r[2] for r in res])
+    idx = np.concatenate([r[3] for r in res])
+    assert (idx == ridx).all()
+    st = O.compare(ref, out, rel_tol=1e-3)
+    assert st.n_mismatch_rel == 0, st
