@@ -47,15 +47,21 @@ def gemv_bytes(fmt, m, k, residual=False, batch=1):
     return m * row_bytes(fmt, k) + batch * 4 * k + batch * 4 * m + (batch * 4 * m if residual else 0)
 
 
-# (name, rows, k, residual)
+# (name, rows, k, residual): the weight matrices of one layer
 LAYER_MATS = [("q", Q_DIM, HIDDEN, False), ("k", KV_DIM, HIDDEN, False), ("v", KV_DIM, HIDDEN, False),
               ("o", HIDDEN, Q_DIM, True), ("gate", INTER, HIDDEN, False), ("up", INTER, HIDDEN, False),
               ("down", HIDDEN, INTER, True)]
+LAUNCHES_PER_LAYER = 4   # fused Q|K|V, o-proj (+residual), fused gate/up+SiLU, down (+residual)
 
 
 def pass_bytes(fmt, layers=LAYERS):
-    b = sum(gemv_bytes(fmt, m, k, r) for _, m, k, r in LAYER_MATS) * layers
-    return b + gemv_bytes(fmt, VOCAB, HIDDEN)
+    """Algorithmic bytes of one pass: every weight matrix once, every launch's input and output vectors once."""
+    rb_h, rb_i = row_bytes(fmt, HIDDEN), row_bytes(fmt, INTER)
+    qkv = (Q_DIM + 2 * KV_DIM) * rb_h + 4 * HIDDEN + 4 * (Q_DIM + 2 * KV_DIM)
+    o = HIDDEN * row_bytes(fmt, Q_DIM) + 4 * Q_DIM + 2 * 4 * HIDDEN
+    ffn = 2 * INTER * rb_h + 4 * HIDDEN + 4 * INTER
+    down = HIDDEN * rb_i + 4 * INTER + 2 * 4 * HIDDEN
+    return (qkv + o + ffn + down) * layers + gemv_bytes(fmt, VOCAB, HIDDEN)
 
 
 def measured_peak():
@@ -138,23 +144,19 @@ class GemvSet:
         ctx.flush()
 
     def run(self):
-        """All GEMVs of one decode token, issued through the reference-shaped operator calls.  The
-        activations that RMSNorm / attention would produce are fixed synthetic vectors: only the
-        GEMV family is on this benchmark's path."""
+        """All GEMVs of one decode token through the C-ABI operator calls: fused Q|K|V, o-proj + residual, fused
+        gate/up + SiLU, down + residual per layer, then lm_head.  The activations that RMSNorm / attention would
+        produce are fixed synthetic vectors: only the GEMV family is on this benchmark's path."""
         R, ctx, f = self.R, self.ctx, self.fmt
         n = {FMT_Q4_0: "q4_0", FMT_Q4K: "q4k", FMT_Q8_0: "q8_0"}[f]
         gemv = getattr(R, "gemv_%s_f32in_f32out" % n)
         gemv_add = getattr(R, "gemv_%s_add_f32_f32in" % n)
+        qkv = getattr(R, "fused_qkv_%s_f32" % n)
+        ffn = getattr(R, "fused_ffn_%s_f32" % n)
         for w in self.w:
-            gemv(ctx, w["q"], self.xn, self.q, Q_DIM, HIDDEN)
-            gemv(ctx, w["k"], self.xn, self.kk, KV_DIM, HIDDEN)
-            gemv(ctx, w["v"], self.xn, self.v, KV_DIM, HIDDEN)
+            qkv(ctx, w["q"], w["k"], w["v"], self.xn, self.q, self.kk, self.v, Q_DIM, KV_DIM, HIDDEN)
             gemv_add(ctx, w["o"], self.q, self.x, self.x, HIDDEN, Q_DIM)
-            if f == FMT_Q4_0:   # the engine's fused gate+up+SiLU for Q4_0 (forward.rs:1687-1690)
-                R.fused_ffn_q4_0_f32(ctx, w["gate"], w["up"], self.xn, self.act, INTER, HIDDEN)
-            else:               # Q4_K has no fused FFN in the reference: 2 GEMVs (forward.rs:1696-1699)
-                gemv(ctx, w["gate"], self.xn, self.gate, INTER, HIDDEN)
-                gemv(ctx, w["up"], self.xn, self.up, INTER, HIDDEN)
+            ffn(ctx, w["gate"], w["up"], self.xn, self.act, INTER, HIDDEN)
             gemv_add(ctx, w["down"], self.act, self.x, self.x, HIDDEN, INTER)
         gemv(ctx, self.lm_head, self.xn, self.logits, VOCAB, HIDDEN)
 
@@ -356,7 +358,7 @@ def main():
         ctx.graph_begin()
         s_.run()
         graphs.append(ctx.graph_end())
-    launches_per_pass = [args.layers * 7 + 1, args.layers * 6 + 1]
+    launches_per_pass = [args.layers * LAUNCHES_PER_LAYER + 1] * len(sets)
 
     def step():
         for g in graphs:
@@ -440,8 +442,8 @@ def main():
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen2.5-7b decode GEMV set (28 layers q,k,v,o,gate,up,down + lm_head), Q4_K pass + Q4_0 pass, "
-                                   "batch 1, f32 activations",
+            "config": {"workload": "qwen2.5-7b decode GEMV set (28 layers: fused q|k|v, o, fused gate/up, down; + lm_head), "
+                                   "Q4_K pass + Q4_0 pass, batch 1, f32 activations",
                        "layers": args.layers, "bytes_per_step": step_bytes,
                        "l2": "inputs larger than L2: every matrix is a distinct instance, %.1f GB streamed per step" % (step_bytes / 1e9)},
             "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K,batch 1>", "achieved": achieved, "peak": peak,

@@ -156,6 +156,14 @@ int32_t runit_scale_accumulate_f16(runit_ctx_t*, const void* src, void* acc, flo
 int32_t runit_add_f16_into_f32(runit_ctx_t*, const void* src, void* acc, uint32_t n);
 
 /* ── entry points with no twin in the reference ── */
+/* Q|K|V in one launch for the 4-bit formats and gate/up+SiLU for Q4_K (the reference has these fusions only
+ * for Q8_0 / Q4_0: dispatch.rs:813, 903, 1531). */
+int32_t runit_fused_qkv_q4_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
+                                 void* out_q, void* out_k, void* out_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+int32_t runit_fused_qkv_q4k_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
+                                void* out_q, void* out_k, void* out_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+int32_t runit_fused_ffn_q4k_f32(runit_ctx_t*, const void* w_gate, const void* w_up, const void* x_vec, void* act_out,
+                                uint32_t ff_dim, uint32_t k);
 /* Batched fused-dequant GEMV: x [batch][k] f32, y [batch][m] f32 (+ residual [batch][m], may be
  * NULL); weights streamed once for the whole batch; batch in 1..8. */
 int32_t runit_gemv_batched_f32(runit_ctx_t*, int32_t fmt, const void* weight, const void* input, void* output,

@@ -91,6 +91,7 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
         else
             cudaGetLastError();
     }
+    c->tune.pdl = 2;   // dependent launch where it was measured to pay (see gemv_launch.cuh)
     const char* v = getenv("RUNIT_GEMV_VARIANT");
     if (v) c->tune.gemv_variant = atoi(v);
     *out = c;
@@ -171,6 +172,8 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "pdl")) ctx->tune.pdl = value;
     else if (!strcmp(key, "gemv_load")) ctx->tune.gemv_load = value;
     else if (!strcmp(key, "gemv_ksl")) ctx->tune.gemv_ksl = value;
+    else if (!strcmp(key, "gemv_csplit")) ctx->tune.gemv_csplit = value;
+    else if (!strcmp(key, "gemv_no_cluster")) ctx->tune.gemv_no_cluster = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
     return RUNIT_OK;
 }

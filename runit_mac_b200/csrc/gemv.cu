@@ -290,6 +290,23 @@ int32_t runit_fused_ffn_q4_0_f32(runit_ctx_t* ctx, const void* w_gate, const voi
     return fused_ffn(ctx, "fused_ffn_q4_0_f32", RUNIT_FMT_Q4_0, w_gate, w_up, x, act_out, ff_dim, k);
 }
 
+// No twins: the reference fuses Q|K|V and gate/up only for Q8_0 (and gate/up for Q4_0); the same launches
+// for the other formats save two (one) kernel launches per layer.
+int32_t runit_fused_qkv_q4_0_f32(runit_ctx_t* ctx, const void* w_q, const void* w_k, const void* w_v, const void* x,
+                                 void* out_q, void* out_k, void* out_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k) {
+    return fused_qkv(ctx, "fused_qkv_q4_0_f32", RUNIT_FMT_Q4_0, w_q, w_k, w_v, x, out_q, out_k, out_v, nullptr, nullptr,
+                     nullptr, BIAS_NONE, q_dim, kv_dim, k);
+}
+int32_t runit_fused_qkv_q4k_f32(runit_ctx_t* ctx, const void* w_q, const void* w_k, const void* w_v, const void* x,
+                                void* out_q, void* out_k, void* out_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k) {
+    return fused_qkv(ctx, "fused_qkv_q4k_f32", RUNIT_FMT_Q4K, w_q, w_k, w_v, x, out_q, out_k, out_v, nullptr, nullptr,
+                     nullptr, BIAS_NONE, q_dim, kv_dim, k);
+}
+int32_t runit_fused_ffn_q4k_f32(runit_ctx_t* ctx, const void* w_gate, const void* w_up, const void* x, void* act_out,
+                                uint32_t ff_dim, uint32_t k) {
+    return fused_ffn(ctx, "fused_ffn_q4k_f32", RUNIT_FMT_Q4K, w_gate, w_up, x, act_out, ff_dim, k);
+}
+
 int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* input, void* output,
                                const void* residual, uint32_t m, uint32_t k, uint32_t batch) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;

@@ -67,6 +67,7 @@ struct GemvArgs {
     int32_t nseg;
     const void* x;
     uint32_t k, nb, row_bytes, n_units, n_tiles;
+    uint32_t csplit;       // CTAs per tile (thread-block cluster size along K): 1, 2 or 4
     uint32_t ldy;          // elements between batch rows of y / residual
     int32_t out_f16, res_kind, bias_kind, dual;
     int32_t* status;       // host-visible word: set non-zero if a bounded wait ran out
@@ -303,9 +304,16 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     const uint32_t ring_u32 = smem_u32(ring);
     const uint32_t bar0 = smem_u32(&mbar[warp][0]);
 
+    grid_launch_dependents();                   // let the next kernel of the stream begin its own prologue
+    if (LD != 1 || a.grp_expert != nullptr) grid_dependency_wait();
     constexpr int TPC = kKS / KSL;              // tiles per CTA
-    const int slice = warp % KSL;
-    const uint32_t tile = blockIdx.x * TPC + warp / KSL;   // global tile index over all segments
+    // With csplit > 1 (host guarantees KSL == 4) a cluster of csplit CTAs shares one tile: CTA c of the
+    // cluster and warp w take K-slice w*csplit + c of 4*csplit slices; partial sums meet in CTA 0 through
+    // distributed shared memory.
+    const uint32_t csplit = a.csplit, crank = csplit > 1 ? cluster_ctarank() : 0u;
+    const int slice = (warp % KSL) * (int)csplit + (int)crank;
+    const int n_slices = KSL * (int)csplit;
+    const uint32_t tile = (blockIdx.x / csplit) * TPC + warp / KSL;   // global tile index over all segments
     int si = 0;
 #pragma unroll
     for (int i = 1; i < 3; i++)
@@ -328,7 +336,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     }
     const uint32_t rows_here = (tile_ok && slot_live) ? min((uint32_t)RPT, sg.rows - row0) : 0u;
     const bool row_ok = (uint32_t)(DUAL ? (lane & 15) : lane) < rows_here;
-    const int n_it = (tile_ok && slot_live) ? ((int)a.n_units - slice + KSL - 1) / KSL : 0;   // units slice, slice+KSL, ...
+    const int n_it = (tile_ok && slot_live) ? ((int)a.n_units - slice + n_slices - 1) / n_slices : 0;   // units slice, slice+n_slices, ...
 
     if (LD == 1) {
         if (lane == 0) {
@@ -343,37 +351,43 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     constexpr int DR = 32 / CPR, DC = 32 % CPR;
     const int c_row0 = lane / CPR, c_col0 = lane % CPR;
 
-    auto issue = [&](int it) {
+    // part: 0 = weights and activations, 1 = weights only (arms the barrier for both), 2 = activations only.
+    // The split lets the prologue prefetch weights before it waits for the producer of the activations.
+    auto issue = [&](int it, int part = 0) {
         if (LD == 1) {
             if (it < n_it && lane == 0) {
-                const uint32_t u = slice + KSL * it;
+                const uint32_t u = slice + n_slices * it;
                 const uint32_t slot = ring_u32 + (it % S) * L::BYTES;
                 const uint32_t bar = bar0 + 8 * (it % S);
                 const uint32_t e0 = u * T::UE;
                 const uint32_t nx = min((uint32_t)T::UE, a.k - e0);   // activations of this unit
                 const uint32_t xbytes = nx * (XF16 ? 2u : 4u);
-                fence_proxy_async();   // earlier generic-proxy accesses to this slot precede the bulk writes
-                mbar_expect_tx(bar, (uint32_t)L::W_BYTES + B * xbytes);
-                if (DUAL) {
-                    tma_load_2d(slot, &maps.m[0], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
-                    tma_load_2d(slot + 16 * T::UB, &maps.m[3], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
-                } else {
-                    tma_load_2d(slot, &maps.m[si], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
+                if (part != 2) {
+                    fence_proxy_async();   // earlier generic-proxy accesses to this slot precede the bulk writes
+                    mbar_expect_tx(bar, (uint32_t)L::W_BYTES + B * xbytes);
+                    if (DUAL) {
+                        tma_load_2d(slot, &maps.m[0], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
+                        tma_load_2d(slot + 16 * T::UB, &maps.m[3], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
+                    } else {
+                        tma_load_2d(slot, &maps.m[si], (int32_t)(u * T::UB), (int32_t)wrow0, bar);
+                    }
                 }
+                if (part != 1) {
 #pragma unroll
-                for (int b = 0; b < B; b++) {
-                    if (XF16)
-                        bulk_load_1d(slot + L::XR_OFF + b * T::UE * 2,
-                                     reinterpret_cast<const __half*>(xbase) + (size_t)b * a.k + e0, xbytes, bar);
-                    else
-                        bulk_load_1d(slot + L::XP_OFF + b * T::UE * 4,
-                                     reinterpret_cast<const float*>(xbase) + (size_t)b * a.k + e0, xbytes, bar);
+                    for (int b = 0; b < B; b++) {
+                        if (XF16)
+                            bulk_load_1d(slot + L::XR_OFF + b * T::UE * 2,
+                                         reinterpret_cast<const __half*>(xbase) + (size_t)b * a.k + e0, xbytes, bar);
+                        else
+                            bulk_load_1d(slot + L::XP_OFF + b * T::UE * 4,
+                                         reinterpret_cast<const float*>(xbase) + (size_t)b * a.k + e0, xbytes, bar);
+                    }
                 }
             }
             return;
         }
         if (it < n_it) {
-            const uint32_t u = slice + KSL * it;
+            const uint32_t u = slice + n_slices * it;
             const uint32_t slot = ring_u32 + (it % S) * L::BYTES;
             const uint32_t uoff = u * T::UB;
             const int vb = min((int)T::UB, (int)(a.row_bytes - uoff));
@@ -484,8 +498,20 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
 #pragma unroll
     for (int b = 0; b < B; b++) { acc[b].t0 = 0ull; acc[b].t1 = 0ull; acc[b].s = 0.f; }
 
+    // Programmatic dependent launch: this grid may start while its predecessor in the stream is still
+    // draining.  Weights do not depend on the predecessor, so (outside grouped mode, where the expert id does)
+    // their first stages are requested before the dependency wait; activations, residual and every store
+    // come after it.
+    if (LD == 1 && a.grp_expert == nullptr) {
 #pragma unroll
-    for (int s = 0; s < S; s++) issue(s);
+        for (int s = 0; s < S; s++) issue(s, 1);
+        grid_dependency_wait();
+#pragma unroll
+        for (int s = 0; s < S; s++) issue(s, 2);
+    } else {
+#pragma unroll
+        for (int s = 0; s < S; s++) issue(s);
+    }
 
     for (int it = 0; it < n_it; it++) {
         wait_stage(it, std::integral_constant<int, S - 1>());   // this lane's copies of stage `it` have landed
@@ -493,7 +519,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
         prep(it);
         __syncwarp();                                           // prepared activations visible to the warp
         if (row_ok) {
-            const uint32_t u = slice + KSL * it;
+            const uint32_t u = slice + n_slices * it;
             const uint8_t* slot = ring + (it % S) * L::BYTES;
             const uint8_t* up = slot + lane * T::UB;
             const float* xp = reinterpret_cast<const float*>(slot + L::XP_OFF);
@@ -515,13 +541,36 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
 #pragma unroll
     for (int b = 0; b < B; b++) red[warp][lane][b] = (sum2(acc[b].t0) + sum2(acc[b].t1)) + acc[b].s;
     __syncthreads();
-    if (slice == 0) {
+    if (csplit > 1) {
+        // CTA-local sum of the four warps (warp 0), published in red[0]; then CTA 0 of the cluster adds the
+        // other CTAs' sums in rank order.  The second cluster barrier keeps every CTA alive until it was read.
+        if (warp == 0) {
+#pragma unroll
+            for (int b = 0; b < B; b++)
+                red[0][lane][b] = ((red[0][lane][b] + red[1][lane][b]) + red[2][lane][b]) + red[3][lane][b];
+        }
+        cluster_sync();
+        if (crank == 0 && warp == 0) {
+#pragma unroll
+            for (int b = 0; b < B; b++) {
+                float v = red[0][lane][b];
+                for (uint32_t c = 1; c < csplit; c++) v += ld_cluster_f32(&red[0][lane][b], c);
+                red[1][lane][b] = v;   // own slot, nobody reads red[1] remotely
+            }
+        }
+        cluster_sync();
+    }
+    if ((warp % KSL) == 0 && crank == 0) {
         float r[B];
 #pragma unroll
         for (int b = 0; b < B; b++) {
-            r[b] = red[warp][lane][b];
+            if (csplit > 1) {
+                r[b] = red[1][lane][b];
+            } else {
+                r[b] = red[warp][lane][b];
 #pragma unroll
-            for (int k = 1; k < KSL; k++) r[b] += red[warp + k][lane][b];
+                for (int k = 1; k < KSL; k++) r[b] += red[warp + k][lane][b];
+            }
         }
         if (DUAL) {
             // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows:

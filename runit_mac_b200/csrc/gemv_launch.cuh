@@ -19,7 +19,44 @@ static inline int32_t launch_staged(runit_ctx* ctx, const GemvArgs& a, const Gem
         configured[ctx->device] = true;
     }
     constexpr uint32_t tpc = kKS / KSL;
-    kern<<<(a.n_tiles + tpc - 1) / tpc, kNT, smem, ctx->stream>>>(a, maps);
+    GemvArgs args = a;
+    // Few-tile shapes (fewer CTAs than ~2 per SM) with a long K: split K over a thread-block cluster of 2 or 4
+    // CTAs per tile so that every SM has warps to run; partial sums meet through distributed shared memory.
+    uint32_t csplit = 1;
+    if (KSL == 4 && !ctx->tune.gemv_no_cluster) {
+        const uint32_t ctas = a.n_tiles;
+        if (ctx->tune.gemv_csplit == 2 || ctx->tune.gemv_csplit == 4) csplit = ctx->tune.gemv_csplit;
+        else if (ctas < 2u * (uint32_t)ctx->sm_count) csplit = a.n_units >= 24 ? 4 : (a.n_units >= 12 ? 2 : 1);
+        if (4 * csplit > a.n_units) csplit = 1;
+    }
+    args.csplit = csplit;
+    const uint32_t grid = ((a.n_tiles + tpc - 1) / tpc) * csplit;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kNT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    // Dependent launch pays when the grid is much smaller or much larger than the machine; grids of about one
+    // CTA per SM were measured slower with it (early CTAs of the next grid double up on busy SMs).
+    const bool pdl = ctx->tune.pdl == 1 || (ctx->tune.pdl == 2 && (grid <= (uint32_t)ctx->sm_count / 2 || grid >= 2u * (uint32_t)ctx->sm_count));
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (csplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = csplit;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        na++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args, maps);
+    if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "launch of %s failed: %s", name, cudaGetErrorString(e));
     return runit_after_launch(ctx, name);
 }
 

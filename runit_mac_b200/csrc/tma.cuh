@@ -55,4 +55,26 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                  : "memory");
 }
 
+// Thread-block clusters: rank of this CTA in its cluster, cluster-wide barrier, and a float read from the
+// shared memory of another CTA of the cluster (distributed shared memory).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local_smem_ptr, uint32_t cta_rank) {
+    uint32_t laddr = (uint32_t)__cvta_generic_to_shared(local_smem_ptr), raddr;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(laddr), "r"(cta_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
+
+// Programmatic dependent launch (griddepcontrol): no-ops when the kernel was launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace runit

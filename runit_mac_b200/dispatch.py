@@ -200,6 +200,9 @@ _TWINS = [
     ("fused_qkv_q8_0_f32", "dispatch.rs:813 (w_q, w_k, w_v, x, out_q, out_k, out_v, q_dim, kv_dim, k)"),
     ("fused_qkv_bias_q8_0_f32", "dispatch.rs:842 (+ bias_q, bias_k, bias_v as f16)"),
     ("fused_qkv_f32bias_q8_0_f32", "no twin: f32 bias"),
+    ("fused_qkv_q4_0_f32", "no twin: Q|K|V for Q4_0"),
+    ("fused_qkv_q4k_f32", "no twin: Q|K|V for Q4_K"),
+    ("fused_ffn_q4k_f32", "no twin: gate/up + SiLU for Q4_K"),
     ("fused_ffn_q8_0_f32", "dispatch.rs:903 (w_gate, w_up, x, act_out, ff_dim, k)"),
     ("gemv_q4_0_f32in_f32out", "dispatch.rs:1456"),
     ("gemv_q4_0_add_f32_f32in", "dispatch.rs:1471"),

@@ -166,7 +166,55 @@ def test_fused_qkv_q8_0(ctx, oracle):
         assert_close(O, r + b, o.download(np.float32, n), what="fused_qkv f32 bias")
 
 
-@pytest.mark.parametrize("fmt,ff,k", [(0, 4864, 896), (0, 40, 96), (1, 1000, 3584), (1, 17, 256)])
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_fused_qkv_4bit(ctx, oracle, fmt):
+    """Q|K|V in one launch for Q4_0 / Q4_K (Qwen2.5-7B shapes: q 3584, kv 512, k 3584), also with dependent launch."""
+    import runit_mac_b200 as R
+    O = oracle
+    q_dim, kv_dim, k = 3584, 512, 3584
+    rng = np.random.default_rng(40 + fmt)
+    ws = [O.rand_weights(fmt, rng, n, k) for n in (q_dim, kv_dim, kv_dim)]
+    x = rng.normal(0, 1, k).astype(np.float32)
+    refs = [O.gemv(fmt, w, x, n, k) for w, n in zip(ws, (q_dim, kv_dim, kv_dim))]
+    wb = [ctx.buffer_from(w) for w in ws]
+    outs = [ctx.new_buffer(n * 4) for n in (q_dim, kv_dim, kv_dim)]
+    for pdl in (0, 1):
+        ctx.set_tuning("pdl", pdl)
+        try:
+            getattr(R, "fused_qkv_%s_f32" % FMT_NAME[fmt])(ctx, *wb, ctx.buffer_from(x), *outs, q_dim, kv_dim, k)
+            ctx.flush()
+        finally:
+            ctx.set_tuning("pdl", 0)
+        for o, r, n in zip(outs, refs, (q_dim, kv_dim, kv_dim)):
+            assert_close(O, r, o.download(np.float32, n), what="fused_qkv 4-bit pdl=%d" % pdl)
+
+
+def test_dependent_launch_chain_is_ordered(ctx, oracle):
+    """A chain y1 = W1.x, y2 = W2.y1 + y2 launched with programmatic dependent launch gives the serial result."""
+    import runit_mac_b200 as R
+    O = oracle
+    n = 1024
+    rng = np.random.default_rng(8)
+    w1, w2 = O.rand_q4k(rng, n, n), O.rand_q4k(rng, n, n)
+    x = rng.normal(0, 1, n).astype(np.float32)
+    y1 = O.gemv(O.Q4K, w1, x, n, n)
+    res = rng.normal(0, 1, n).astype(np.float32)
+    ref = O.gemv(O.Q4K, w2, y1, n, n) + res
+    b1, b2, xb = ctx.buffer_from(w1), ctx.buffer_from(w2), ctx.buffer_from(x)
+    t, out = ctx.new_buffer(n * 4), ctx.buffer_from(res)
+    ctx.set_tuning("pdl", 1)
+    try:
+        for _ in range(3):
+            ctx.call("memcpy_h2d", out, res.ctypes.data, res.nbytes)
+            R.gemv_q4k_f32in_f32out(ctx, b1, xb, t, n, n)
+            R.gemv_q4k_add_f32_f32in(ctx, b2, t, out, out, n, n)
+            ctx.flush()
+            assert_close(O, ref, out.download(np.float32, n), rel_tol=1e-3, what="pdl chain")
+    finally:
+        ctx.set_tuning("pdl", 0)
+
+
+@pytest.mark.parametrize("fmt,ff,k", [(0, 4864, 896), (0, 40, 96), (1, 1000, 3584), (1, 17, 256), (2, 1000, 3584), (2, 33, 256)])
 def test_fused_ffn(ctx, oracle, fmt, ff, k):
     """act = silu(Wg.x) * (Wu.x)  (fused_ffn.metal:36-93, gemv_q4_0.metal:254-311)."""
     import runit_mac_b200 as R
