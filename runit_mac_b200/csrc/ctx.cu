@@ -173,6 +173,7 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "gemv_load")) ctx->tune.gemv_load = value;
     else if (!strcmp(key, "gemv_ksl")) ctx->tune.gemv_ksl = value;
     else if (!strcmp(key, "gemv_csplit")) ctx->tune.gemv_csplit = value;
+    else if (!strcmp(key, "gemv_math")) ctx->tune.gemv_math = value;
     else if (!strcmp(key, "gemv_no_cluster")) ctx->tune.gemv_no_cluster = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
     return RUNIT_OK;

@@ -19,6 +19,7 @@
 #include <type_traits>
 
 #include "gemv_common.cuh"
+#include "gemv_int8.cuh"
 #include "runit_cuda.h"
 #include "tma.cuh"
 
@@ -290,7 +291,9 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t* up, const float* xp, in
 //
 // KSL = number of warps that share one 32-row tile (each takes every KSL-th unit of K); a CTA
 // holds 4/KSL tiles.  The host picks KSL so that the units divide evenly among the warps.
-template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int KSL>
+// MATH = 0: packed f32 arithmetic (any batch); MATH = 1: integer dot products on 8-bit limbs of the activations
+// (batch 1; see gemv_int8.cuh).
+template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int KSL, int MATH>
 __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const GemvArgs a, const __grid_constant__ GemvMaps maps) {
     using T = Traits<FMT>;
     using L = WarpStage<FMT, B, XF16>;
@@ -460,6 +463,10 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
             }
         }
         __syncwarp();   // in-place: every lane has read its inputs before anyone overwrites them
+        if (MATH == 1) {
+            prep_int_block<EPL, T::UE / 32, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(slot + L::XP_OFF, v[0], lane);
+            return;
+        }
 #pragma unroll
         for (int b = 0; b < B; b++) {
             float* xp = reinterpret_cast<float*>(slot + L::XP_OFF) + b * T::UE;
@@ -523,7 +530,11 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
             const uint8_t* slot = ring + (it % S) * L::BYTES;
             const uint8_t* up = slot + lane * T::UB;
             const float* xp = reinterpret_cast<const float*>(slot + L::XP_OFF);
-            if (FMT == RUNIT_FMT_Q4K) {
+            if (MATH == 1) {
+                if (FMT == RUNIT_FMT_Q4K) acc[0].s += unit_q4k_i8(up, slot + L::XP_OFF);
+                else if (FMT == RUNIT_FMT_Q4_0) acc[0].s += unit_q4_0_i8(up, slot + L::XP_OFF, min(T::BPU, (int)(a.nb - u * T::BPU)));
+                else acc[0].s += unit_q8_0_i8(up, slot + L::XP_OFF, min(T::BPU, (int)(a.nb - u * T::BPU)));
+            } else if (FMT == RUNIT_FMT_Q4K) {
                 unit_q4k<B, T::UE, 8>(up, xp, reinterpret_cast<const float*>(slot + L::XS_OFF), acc);
             } else if (FMT == RUNIT_FMT_Q4_0) {
                 unit_q4_0<B, T::UE>(up, xp, min(T::BPU, (int)(a.nb - u * T::BPU)), acc);

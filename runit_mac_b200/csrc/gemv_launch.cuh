@@ -7,12 +7,12 @@
 
 namespace runit {
 
-template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int KSL>
+template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int KSL, int MATH>
 static inline int32_t launch_staged(runit_ctx* ctx, const GemvArgs& a, const GemvMaps& maps, const char* name) {
     using L = WarpStage<FMT, B, XF16>;
     constexpr int smem = kKS * S * L::BYTES + 128;   // + slack to align the rings to 128 bytes
     static_assert(smem <= 227 * 1024, "stage rings exceed shared memory");
-    auto kern = gemv_staged_kernel<FMT, B, XF16, CPB, S, DUAL, LD, KSL>;
+    auto kern = gemv_staged_kernel<FMT, B, XF16, CPB, S, DUAL, LD, KSL, MATH>;
     static bool configured[16] = {false};
     if (ctx->device < 16 && !configured[ctx->device]) {
         RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -63,30 +63,39 @@ static inline int32_t launch_staged(runit_ctx* ctx, const GemvArgs& a, const Gem
 // K-slices per tile: the largest of 4, 2, 1 that divides the unit count evenly among the warps
 // (e.g. k=3584 has 14 units: 2 warps x 7 units instead of 4 warps with 4,4,3,3), unless there are
 // too few tiles to fill the GPU, in which case 4 slices keep more warps busy.
-template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD>
+template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int MATH>
 static inline int32_t pick_slices(runit_ctx* ctx, const GemvArgs& a, const GemvMaps& maps, const char* name) {
     int ksl = 4;
     if (ctx->tune.gemv_ksl == 1 || ctx->tune.gemv_ksl == 2 || ctx->tune.gemv_ksl == 4) ksl = ctx->tune.gemv_ksl;
     else if (a.n_units % 4 != 0 && a.n_tiles >= (uint32_t)ctx->sm_count * 4) ksl = (a.n_units % 2 == 0) ? 2 : 1;
-    if constexpr (B == 1) {
-        if (ksl == 2) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 2>(ctx, a, maps, name);
-        if (ksl == 1) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 1>(ctx, a, maps, name);
+    if constexpr (B == 1 && !DUAL) {
+        if (ksl == 2) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 2, MATH>(ctx, a, maps, name);
+        if (ksl == 1) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 1, MATH>(ctx, a, maps, name);
     }
-    return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 4>(ctx, a, maps, name);
+    return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 4, MATH>(ctx, a, maps, name);
+}
+
+// Batch 1 uses the integer dot-product arithmetic unless the tuning knob gemv_math = 1 asks for packed f32.
+template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD>
+static inline int32_t pick_math(runit_ctx* ctx, const GemvArgs& a, const GemvMaps& maps, const char* name) {
+    if constexpr (B == 1) {
+        if (ctx->tune.gemv_math != 1) return pick_slices<FMT, B, XF16, CPB, S, DUAL, LD, 1>(ctx, a, maps, name);
+    }
+    return pick_slices<FMT, B, XF16, CPB, S, DUAL, LD, 0>(ctx, a, maps, name);
 }
 
 template <int FMT, int B, bool XF16, int CPB, int LD>
 static inline int32_t pick_stages(runit_ctx* ctx, const GemvArgs& a, const GemvMaps& maps, const char* name) {
     if constexpr (B == 1 && !XF16) {
-        if (a.dual) return launch_staged<FMT, 1, false, CPB, 3, true, LD, 4>(ctx, a, maps, name);
+        if (a.dual) return pick_math<FMT, 1, false, CPB, 2, true, LD>(ctx, a, maps, name);
         // Two stages per warp leave room for 4 CTAs (16 warps) per SM, which hides more latency than a
         // deeper ring with 12 warps; measured best on every large shape.
-        if (ctx->tune.gemv_stages == 3) return pick_slices<FMT, 1, false, CPB, 3, false, LD>(ctx, a, maps, name);
-        if (ctx->tune.gemv_stages == 4) return pick_slices<FMT, 1, false, CPB, 4, false, LD>(ctx, a, maps, name);
-        return pick_slices<FMT, 1, false, CPB, 2, false, LD>(ctx, a, maps, name);
+        if (ctx->tune.gemv_stages == 3) return pick_math<FMT, 1, false, CPB, 3, false, LD>(ctx, a, maps, name);
+        return pick_math<FMT, 1, false, CPB, 2, false, LD>(ctx, a, maps, name);
     }
     if (a.dual) return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "%s: fused gate/up is batch 1, f32 input", name);
-    return pick_slices<FMT, B, XF16, CPB, 3, false, LD>(ctx, a, maps, name);
+    if constexpr (B == 1) return pick_math<FMT, B, XF16, CPB, 2, false, LD>(ctx, a, maps, name);
+    else return pick_slices<FMT, B, XF16, CPB, 3, false, LD, 0>(ctx, a, maps, name);
 }
 
 template <int FMT, int B, bool XF16>
