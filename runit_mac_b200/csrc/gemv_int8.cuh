@@ -99,19 +99,19 @@ __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL
 // 32 weights (8 words of unsigned 4-bit values in bytes) x one activation block: sum q*v as an int.
 __device__ __forceinline__ int dot32_u4(const uint32_t (&q)[8], const uint8_t* xblk) {
     const uint4* xl = reinterpret_cast<const uint4*>(xblk);
-    int s0 = 0, s1 = 0, s2 = 0;
+    int s0[2] = {0, 0}, s1[2] = {0, 0}, s2[2] = {0, 0};   // one accumulator set per 16-byte half: short chains
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const uint4 l0 = xl[h], l1 = xl[2 + h], l2 = xl[4 + h];
         const uint32_t x0[4] = {l0.x, l0.y, l0.z, l0.w}, x1[4] = {l1.x, l1.y, l1.z, l1.w}, x2[4] = {l2.x, l2.y, l2.z, l2.w};
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            s0 = dp4a_us(q[4 * h + c], x0[c], s0);
-            s1 = dp4a_us(q[4 * h + c], x1[c], s1);
-            s2 = dp4a_us(q[4 * h + c], x2[c], s2);
+            s0[h] = dp4a_us(q[4 * h + c], x0[c], s0[h]);
+            s1[h] = dp4a_us(q[4 * h + c], x1[c], s1[h]);
+            s2[h] = dp4a_us(q[4 * h + c], x2[c], s2[h]);
         }
     }
-    return s0 + (s1 << 8) + (s2 << 16);   // |sum| <= 15 * 32 * 2^22 < 2^31
+    return (s0[0] + s0[1]) + ((s1[0] + s1[1]) << 8) + ((s2[0] + s2[1]) << 16);   // |sum| <= 15 * 32 * 2^22 < 2^31
 }
 
 // One Q4_K superblock: formula of crates/kernels/shaders/gemv_q4k.metal:85-122.

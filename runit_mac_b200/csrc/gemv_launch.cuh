@@ -38,9 +38,10 @@ static inline int32_t launch_staged(runit_ctx* ctx, const GemvArgs& a, const Gem
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
-    // Dependent launch pays when the grid is much smaller or much larger than the machine; grids of about one
-    // CTA per SM were measured slower with it (early CTAs of the next grid double up on busy SMs).
-    const bool pdl = ctx->tune.pdl == 1 || (ctx->tune.pdl == 2 && (grid <= (uint32_t)ctx->sm_count / 2 || grid >= 2u * (uint32_t)ctx->sm_count));
+    // Dependent launch pays except for grids of about one CTA per SM, which were measured 15-25% slower with it
+    // (the early CTAs of the next grid double up on busy SMs instead of spreading out).
+    const uint32_t sms = (uint32_t)ctx->sm_count;
+    const bool pdl = ctx->tune.pdl == 1 || (ctx->tune.pdl == 2 && (grid < (2 * sms) / 3 || grid > (4 * sms) / 3));
     if (pdl) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
@@ -68,9 +69,11 @@ static inline int32_t pick_slices(runit_ctx* ctx, const GemvArgs& a, const GemvM
     int ksl = 4;
     if (ctx->tune.gemv_ksl == 1 || ctx->tune.gemv_ksl == 2 || ctx->tune.gemv_ksl == 4) ksl = ctx->tune.gemv_ksl;
     else if (a.n_units % 4 != 0 && a.n_tiles >= (uint32_t)ctx->sm_count * 4) ksl = (a.n_units % 2 == 0) ? 2 : 1;
-    if constexpr (B == 1 && !DUAL) {
+    if constexpr (B == 1) {
         if (ksl == 2) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 2, MATH>(ctx, a, maps, name);
-        if (ksl == 1) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 1, MATH>(ctx, a, maps, name);
+        if constexpr (!DUAL) {
+            if (ksl == 1) return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 1, MATH>(ctx, a, maps, name);
+        }
     }
     return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 4, MATH>(ctx, a, maps, name);
 }
