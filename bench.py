@@ -64,6 +64,10 @@ def pass_bytes(fmt, layers=LAYERS):
     return (qkv + o + ffn + down) * layers + gemv_bytes(fmt, VOCAB, HIDDEN)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the ncu capture of one Q4_K launch.
+NCU_TRAFFIC_RATIO = (306.78e6 + 4.28e6) / 307.18e6
+
+
 def measured_peak():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -87,7 +91,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -199,6 +203,60 @@ def cpu_sample(fmt_list, threads, min_seconds, layers_sample=2):
     return total_bytes / total_t / 1e9, total_t, desc, O.num_threads()
 
 
+SHAPES = {
+    FMT_Q4K: [(3584, 3584), (512, 3584), (18944, 3584), (3584, 18944), (152064, 3584), (1024, 2048), (2048, 1024), (2048, 2048),
+              (50304, 2048)],
+    FMT_Q4_0: [(3584, 3584), (512, 3584), (18944, 3584), (3584, 18944), (152064, 3584)],
+    FMT_Q8_0: [(1152, 896), (896, 896), (4864, 896), (896, 4864), (151936, 896)],
+}
+
+
+def run_shapes(R, ctx, torch, stream, reps=20, min_bytes=600e6):
+    """Pipelined GB/s per decode shape: each shape is launched over enough distinct weight instances to exceed
+    L2 several times (>= 600 MB), recorded as one command list, replayed `reps` times between CUDA events."""
+    peak, _ = measured_peak()
+    names = {FMT_Q8_0: "q8_0", FMT_Q4_0: "q4_0", FMT_Q4K: "q4k"}
+    for fmt in (FMT_Q4K, FMT_Q4_0, FMT_Q8_0):
+        for m, k in SHAPES[fmt]:
+            for batch in ((1, 8) if (m, k) in ((18944, 3584), (4864, 896)) else (1,)):
+                wbytes = m * row_bytes(fmt, k)
+                n_inst = int(min(64, max(2, np.ceil(min_bytes / wbytes))))
+                ws = []
+                for i in range(n_inst):
+                    b = ctx.new_buffer(wbytes)
+                    R.fill_weights(ctx, fmt, b, m * (k // BLOCK[fmt][0]), 17 + i, 0.01)
+                    ws.append(b)
+                x, y = ctx.new_buffer(4 * k * batch), ctx.new_buffer(4 * m * batch)
+                R.fill_normal_f32(ctx, x, k * batch, 3, 1.0)
+
+                def run():
+                    for w in ws:
+                        if batch == 1:
+                            getattr(R, "gemv_%s_f32in_f32out" % names[fmt])(ctx, w, x, y, m, k)
+                        else:
+                            R.gemv_batched_f32(ctx, fmt, w, x, y, None, m, k, batch)
+                run()
+                ctx.flush()
+                ctx.graph_begin(); run(); g = ctx.graph_end()
+                for _ in range(3):
+                    g.launch()
+                ctx.flush()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    g.launch()
+                e1.record(stream)
+                ctx.flush()
+                us = e0.elapsed_time(e1) / reps / n_inst * 1e3
+                alg = gemv_bytes(fmt, m, k, batch=batch)
+                print(json.dumps({"fmt": names[fmt], "m": m, "k": k, "batch": batch, "instances": n_inst, "us_per_launch": round(us, 2),
+                                  "algorithmic_bytes": alg, "gbs": round(alg / us / 1e3, 1), "frac_of_measured_peak": round(alg / us / 1e3 / peak, 3)}),
+                      flush=True)
+                g.destroy()
+                for w in ws:
+                    w.free()
+
+
 def run_extras(R, ctx, torch, dist, stream, rank, world, args):
     """Figures for the other rows of the path: one OLMoE-shaped MoE layer (1/16/256 tokens), the full
     OLMoE-shaped greedy decode (tok/s) and, at N>1, the row-sharded lm_head with its all-gather."""
@@ -308,13 +366,15 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the workload (default: the full 28)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--tune", default="", help="key=value[,key=value] kernel tuning knobs (experiments)")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE-layer / OLMoE-decode / sharded lm_head figures")
+    ap.add_argument("--one", default="", help="fmt,m,k[,batch]: launch this one GEMV shape three times and exit (for ncu captures)")
+    ap.add_argument("--shapes", action="store_true", help="per-shape GEMV table (one JSON line per shape) instead of the headline run")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -339,6 +399,21 @@ def main():
         k, v = kv.split("=")
         ctx.set_tuning(k, int(v))
 
+    if args.one:
+        f, m, k, *rest = args.one.split(",")
+        fmt = {"q8_0": FMT_Q8_0, "q4_0": FMT_Q4_0, "q4k": FMT_Q4K}[f]
+        m, k, batch = int(m), int(k), int(rest[0]) if rest else 1
+        w = ctx.new_buffer(m * row_bytes(fmt, k))
+        R.fill_weights(ctx, fmt, w, m * (k // BLOCK[fmt][0]), 5, 0.01)
+        x, y = ctx.new_buffer(4 * k * batch), ctx.new_buffer(4 * m * batch)
+        R.fill_normal_f32(ctx, x, k * batch, 3, 1.0)
+        for _ in range(3):
+            R.gemv_batched_f32(ctx, fmt, w, x, y, None, m, k, batch)
+        ctx.flush()
+        print(json.dumps({"one": args.one, "launches": ctx.launches}))
+        return
+    if args.shapes:
+        return run_shapes(R, ctx, torch, stream)
     sets = [GemvSet(R, ctx, FMT_Q4K, 1002 + rank, args.layers), GemvSet(R, ctx, FMT_Q4_0, 2002 + rank, args.layers)]
     bytes_fmt = [pass_bytes(s.fmt, args.layers) for s in sets]
     step_bytes = sum(bytes_fmt)
@@ -391,7 +466,6 @@ def main():
         for j in range(len(sets)):
             a, b = sub[i * len(sets) + j]
             fmt_ms[j] += a.elapsed_time(b)
-    clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -423,6 +497,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = world * step_bytes * args.steps / (float(t.item()) * 1e-3) / 1e9
+    clocks = sampler.stop() if rank == 0 else None   # sampled over both timed regions
 
     extras = {}
     if not args.no_extras:
@@ -447,8 +522,11 @@ def main():
                        "layers": args.layers, "bytes_per_step": step_bytes,
                        "l2": "inputs larger than L2: every matrix is a distinct instance, %.1f GB streamed per step" % (step_bytes / 1e9)},
             "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K,batch 1>", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
-                         "traffic_note": "dram read+write of the lm_head launch from ncu (profiles/): 306.6 MB + 4.6 MB vs 307.2 MB algorithmic",
+                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                         "traffic": NCU_TRAFFIC_RATIO * bytes_fmt[0] / q4k_launches,
+                         "traffic_note": "ncu capture of the 152064x3584 Q4_K launch (profiles/gemv_q4k_lm_head_152064x3584_ncu.md): dram read "
+                                         "306.78 MB + write 4.28 MB for 307.18 MB algorithmic = x1.0126; scaled to the average launch of "
+                                         "the pass (weights are streamed once by every launch, so traffic grows with the bytes)",
                          "bytes_per_launch": bytes_fmt[0] / q4k_launches, "launches_per_step": q4k_launches,
                          "avg_launch_us": q4k_ms * 1e3 / q4k_launches},
             "per_format": {"q4k_gbs": achieved, "q4_0_gbs": bytes_fmt[1] / (fmt_ms[1] / args.steps * 1e-3) / 1e9},

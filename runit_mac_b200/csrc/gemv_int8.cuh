@@ -9,7 +9,7 @@
 // nibbles of a word are separated with three logic ops per 8 weights and multiplied with dp4a: 0.75 dp4a per
 // weight, integer accumulation (exact), one int->float conversion per 32 weights, scales applied in f32.
 // The only deviation from the f32 product is the rounding of x to 2^-22 of its block maximum — the size of
-// the rounding error of an f32 accumulation — so results stay within a few 1e-7 of the f64 oracle.
+// the rounding error of an f32 accumulation — so results stay within a few 1e-7 of an f64 evaluation of the same sums.
 #pragma once
 
 #include "gemv_common.cuh"
