@@ -257,6 +257,67 @@ def run_shapes(R, ctx, torch, stream, reps=20, min_bytes=600e6):
                     w.free()
 
 
+def measured_tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def zipf_routing(torch, T, E, k, seed, s=1.1):
+    """8 distinct experts per token, expert popularity ~ Zipf(s) over the expert index; uniform routing weights."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    p = 1.0 / torch.arange(1, E + 1, device="cuda", dtype=torch.float64) ** s
+    idx = torch.multinomial((p / p.sum()).float().expand(T, E).contiguous(), k, replacement=False, generator=g).to(torch.int32)
+    w = torch.rand(T, k, device="cuda", generator=g)
+    return idx, w
+
+
+def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8):
+    """Qwen3-MoE-shaped batched MoE block (hidden 2048, 128 experts, top-8, expert intermediate 768, Q4_K experts
+    dequantised to bf16 tiles feeding the tcgen05 grouped GEMM), T tokens ~ N(0,1), Zipf(1.1) expert popularity.
+    Timed per layer over the expert part (permutation, both grouped GEMMs, combine) with the routing given."""
+    rb = lambda kk: kk // 256 * 144
+    gate, up, down = ctx.new_buffer(E * ff * rb(h)), ctx.new_buffer(E * ff * rb(h)), ctx.new_buffer(E * h * rb(ff))
+    for i, (b, rows, kk) in enumerate(((gate, E * ff, h), (up, E * ff, h), (down, E * h, ff))):
+        R.fill_weights(ctx, FMT_Q4K, b, rows * (kk // 256), 5 + i, 0.01)
+    x = torch.randn(T, h, device="cuda")
+    idx, w = zipf_routing(torch, T, E, k, 1)
+    out = torch.empty(T, h, device="cuda")
+    nbytes = R.moe_grouped_scratch_bytes(ctx, T, h, ff, E, k)
+    scratch = ctx.new_buffer(nbytes)
+    cnt = torch.bincount(idx.flatten().long(), minlength=E)
+    tiles = int(((cnt + 127) // 128).sum().item())
+
+    def step():
+        R.moe_experts_grouped_q4k_bf16(ctx, gate, up, down, x, idx, w, None, out, scratch, nbytes, T, h, ff, E, k)
+    l0 = ctx.launches
+    for _ in range(3):
+        step()
+    ctx.flush()
+    launches_per_layer = (ctx.launches - l0) // 3
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        step()
+    e1.record(stream)
+    ctx.flush()
+    ms = e0.elapsed_time(e1) / reps
+    flops = 2.0 * T * k * 3 * h * ff                  # useful multiply-adds of the three expert products
+    padded = 2.0 * tiles * 128 * 3 * h * ff           # what the 128-slot tiles issue
+    peak, kind = measured_tensor_peak()
+    return {"workload": "qwen3-moe-shaped MoE block, %d tokens, %d experts top-%d, hidden %d, intermediate %d, Q4_K -> bf16 tiles, "
+                        "Zipf(1.1) routing" % (T, E, k, h, ff),
+            "ms_per_layer": ms, "tokens_per_s": T / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+            "frac_of_tensor_peak": flops / (ms * 1e-3) / 1e12 / peak, "peak_tflops": peak, "peak_kind": kind,
+            "issued_over_useful_flops": padded / flops, "token_tiles": tiles, "slots_per_expert_max": int(cnt.max().item()),
+            "slots_per_expert_min": int(cnt.min().item()), "launches_per_layer": int(launches_per_layer),
+            "finite": bool(torch.isfinite(out).all().item())}
+
+
 def run_extras(R, ctx, torch, dist, stream, rank, world, args):
     """Figures for the other rows of the path: one OLMoE-shaped MoE layer (1/16/256 tokens), the full
     OLMoE-shaped greedy decode (tok/s) and, at N>1, the row-sharded lm_head with its all-gather."""
@@ -374,6 +435,7 @@ def main():
     ap.add_argument("--tune", default="", help="key=value[,key=value] kernel tuning knobs (experiments)")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE-layer / OLMoE-decode / sharded lm_head figures")
     ap.add_argument("--one", default="", help="fmt,m,k[,batch]: launch this one GEMV shape three times and exit (for ncu captures)")
+    ap.add_argument("--block", default="", help="T: run the Qwen3-MoE-shaped batched MoE block on T tokens, print its figures and exit")
     ap.add_argument("--shapes", action="store_true", help="per-shape GEMV table (one JSON line per shape) instead of the headline run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -414,6 +476,9 @@ def main():
         return
     if args.shapes:
         return run_shapes(R, ctx, torch, stream)
+    if args.block:
+        print(json.dumps(run_block(R, ctx, torch, stream, T=int(args.block), reps=max(args.steps // 2, 3))), flush=True)
+        return
     sets = [GemvSet(R, ctx, FMT_Q4K, 1002 + rank, args.layers), GemvSet(R, ctx, FMT_Q4_0, 2002 + rank, args.layers)]
     bytes_fmt = [pass_bytes(s.fmt, args.layers) for s in sets]
     step_bytes = sum(bytes_fmt)

@@ -219,6 +219,25 @@ int32_t runit_moe_layer_q4k_static(runit_ctx_t*, const void* router_w, const voi
                                    const void* x, const void* residual, void* out, void* idx_out, void* w_out,
                                    uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
 
+/* ── batched (prefill-sized) MoE block on the tensor cores.  No twin: the reference's prefill runs the decode
+ *    block once per token (crates/engine/src/prefill.rs:156-215).  Same block as runit_moe_layer_q4k with bf16
+ *    operands: slots are sorted by expert on the device, every Q4_K weight d*sc*q - dmin*m
+ *    (crates/engine/src/forward.rs:1026-1057) is rounded to bf16 in shared-memory tiles, activations are rounded to
+ *    bf16, products accumulate in f32 (tcgen05.mma, accumulators in tensor memory):
+ *      act[s] = bf16(silu(Wg[e].bf16(x[t])) * (Wu[e].bf16(x[t]))), y[s] = Wd[e].act[s],
+ *      out[t] = (residual ? residual[t] : 0) + sum_i w_i * y[s_i]        (routing order)
+ *    Shapes: h, ff multiples of 256; E <= 256; k <= min(E, 32).  scratch: caller-owned, 1024-byte aligned,
+ *    at least runit_moe_grouped_scratch_bytes(); tensors 16-byte aligned; out may alias residual. ── */
+size_t  runit_moe_grouped_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);
+/* router (f32 [E][h]) -> softmax/top-k -> experts; idx_out (int32 [T][k]) and w_out (f32 [T][k]) may be NULL. */
+int32_t runit_moe_layer_q4k_bf16(runit_ctx_t*, const void* router_w, const void* gate, const void* up, const void* down,
+                                 const void* x, const void* residual, void* out, void* idx_out, void* w_out, void* scratch,
+                                 size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
+/* The expert part for given routing: idx int32 [T][k] (ids outside [0, E) are skipped), w f32 [T][k]. */
+int32_t runit_moe_experts_grouped_q4k_bf16(runit_ctx_t*, const void* gate, const void* up, const void* down, const void* x,
+                                           const void* idx, const void* w, const void* residual, void* out, void* scratch,
+                                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);
+
 /* ── decode-step operators besides the GEMVs ── */
 /* dispatch.rs:152  y = x * rsqrt(mean(x^2)+eps) * gamma_f16, num_rows rows of `hidden` (x may equal y) */
 int32_t runit_rms_norm_f32_f32(runit_ctx_t*, const void* x, void* y, const void* gamma, float eps, uint32_t hidden, uint32_t num_rows);

@@ -16,7 +16,7 @@ __all__ = [
     "build_oracle", "lib", "num_threads", "set_num_threads", "row_bytes", "block_elems",
     "block_bytes", "dequant_rows", "dequant_q4k_f16", "gemv", "gemv_f64", "gemv_f16w_f32in",
     "gemv_f32w", "silu_mul_f32", "silu_mul_f16", "scale_accumulate_f16", "add_f16_into_f32",
-    "topk_softmax", "moe_layer_q4k", "rms_norm_f32", "rope_qk_f32", "kv_copy_to_cache_f16",
+    "topk_softmax", "moe_layer_q4k", "moe_grouped_q4k_bf16", "bf16_round", "rms_norm_f32", "rope_qk_f32", "kv_copy_to_cache_f16",
     "decode_attention_f32q_f16kv", "argmax_f32", "ModelCfg", "ModelWeights", "decode_step",
     "compare", "DiffStats", "f32_to_f16_bits", "f16_bits_to_f32",
 ]
@@ -93,6 +93,10 @@ def lib():
         L.ro_topk_softmax.restype = C.c_int
         L.ro_topk_softmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_void_p]
+        L.ro_moe_grouped_q4k_bf16.restype = C.c_int
+        L.ro_moe_grouped_q4k_bf16.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 8 + [C.c_int] * 5
+        L.ro_bf16_round.restype = C.c_float
+        L.ro_bf16_round.argtypes = [C.c_float]
         L.ro_moe_layer_q4k.restype = C.c_int
         L.ro_moe_layer_q4k.argtypes = [C.c_int, C.c_int] + [C.c_void_p] * 9 + [C.c_int] * 5
         L.ro_rms_norm_f32.argtypes = [C.c_void_p] * 3 + [C.c_float, C.c_int, C.c_int]
@@ -268,6 +272,36 @@ def moe_layer_q4k(router, gate, up, down, x, *, h, ff, E, top_k, renorm=False, m
     if rc:
         raise ValueError("ro_moe_layer_q4k rejected the shapes")
     return out, idx, w
+
+
+def moe_grouped_q4k_bf16(router, gate, up, down, x, *, h, ff, E, top_k, renorm=False, residual=None, routing=None):
+    """Batched block with bf16 operands.  routing=(idx, w): use it (router ignored); else route with the f32 router."""
+    gate, up, down = (_c(a, np.uint8).reshape(-1) for a in (gate, up, down))
+    x = _c(x, np.float32).reshape(-1, h)
+    T = x.shape[0]
+    res = None if residual is None else _c(residual, np.float32).reshape(T, h)
+    out = np.empty((T, h), np.float32)
+    if routing is None:
+        router = _c(router, np.float32)
+        idx = np.empty((T, top_k), np.int32)
+        w = np.empty((T, top_k), np.float32)
+        rp = _p(router)
+    else:
+        idx = np.array(routing[0], dtype=np.int32, copy=True).reshape(T, top_k)
+        w = np.array(routing[1], dtype=np.float32, copy=True).reshape(T, top_k)
+        rp = None
+    rc = lib().ro_moe_grouped_q4k_bf16(rp, int(renorm), _p(gate), _p(up), _p(down), _p(x),
+                                       None if res is None else _p(res), _p(out), _p(idx), _p(w), T, h, ff, E, top_k)
+    if rc:
+        raise ValueError("ro_moe_grouped_q4k_bf16 rejected the shapes")
+    return out, idx, w
+
+
+def bf16_round(a) -> np.ndarray:
+    """Round-to-nearest-even to bf16, returned as f32."""
+    u = _c(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
 
 
 def rms_norm_f32(x, gamma, eps: float) -> np.ndarray:

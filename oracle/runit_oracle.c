@@ -501,6 +501,110 @@ int ro_moe_layer_q4k(int mode, int renorm, const float* router, const uint8_t* g
     return err;
 }
 
+/* Batched MoE block with bf16 operands (the arithmetic of a tensor-core grouped GEMM; the reference's
+ * analogue is the per-token loop crates/engine/src/prefill.rs:156-215 with f16 intermediates).
+ *   weights  : bf16( d*sc*q - dmin*m )   (the f32 values of crates/engine/src/forward.rs:1026-1057, rounded)
+ *   x        : rounded to bf16;  products exact, accumulated in f64, rounded once to f32
+ *   act      : bf16( silu(g) * u );  y = Wd.act (f32);  out = residual + sum_i w_i*y_i in routing order
+ * router != NULL: routing is computed here (f32 router, softmax/top-k) and returned in idx_io / w_io;
+ * router == NULL: the routing in idx_io / w_io is used (ids outside [0,E) are skipped). */
+float ro_bf16_round(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return f;
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    u &= 0xFFFF0000u;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+int ro_moe_grouped_q4k_bf16(const float* router, int renorm, const uint8_t* gate, const uint8_t* up,
+                            const uint8_t* down, const float* x, const float* residual, float* out,
+                            int32_t* idx_io, float* w_io, int T, int h, int ff, int E, int top_k) {
+    if (h % 256 || ff % 256 || top_k > E || top_k > 64) return -1;
+    size_t rb_h = ro_row_bytes(RO_Q4K, h), rb_ff = ro_row_bytes(RO_Q4K, ff);
+    size_t gate_stride = (size_t)ff * rb_h, down_stride = (size_t)h * rb_ff;
+    int err = 0;
+    if (router) {
+        for (int t = 0; t < T && !err; t++) {
+            float* logits = (float*)malloc(sizeof(float) * (size_t)E);
+            ro_gemv_f32w(router, x + (size_t)t * h, logits, E, h);
+            if (ro_topk_softmax(logits, E, top_k, renorm, idx_io + (size_t)t * top_k, w_io + (size_t)t * top_k, NULL)) err = -1;
+            free(logits);
+        }
+        if (err) return err;
+    }
+    /* dequantise the experts that are used, once */
+    char* used = (char*)calloc((size_t)E, 1);
+    for (size_t s = 0; s < (size_t)T * top_k; s++)
+        if (idx_io[s] >= 0 && idx_io[s] < E) used[idx_io[s]] = 1;
+    float** wg = (float**)calloc((size_t)E, sizeof(float*));
+    float** wu = (float**)calloc((size_t)E, sizeof(float*));
+    float** wd = (float**)calloc((size_t)E, sizeof(float*));
+    for (int e = 0; e < E; e++) {
+        if (!used[e]) continue;
+        wg[e] = (float*)malloc(sizeof(float) * (size_t)ff * h);
+        wu[e] = (float*)malloc(sizeof(float) * (size_t)ff * h);
+        wd[e] = (float*)malloc(sizeof(float) * (size_t)h * ff);
+#pragma omp parallel for schedule(static)
+        for (int r = 0; r < ff; r++) {
+            ro_dequant_row(RO_Q4K, gate + e * gate_stride + (size_t)r * rb_h, h, wg[e] + (size_t)r * h);
+            ro_dequant_row(RO_Q4K, up + e * gate_stride + (size_t)r * rb_h, h, wu[e] + (size_t)r * h);
+            for (int c = 0; c < h; c++) {
+                wg[e][(size_t)r * h + c] = ro_bf16_round(wg[e][(size_t)r * h + c]);
+                wu[e][(size_t)r * h + c] = ro_bf16_round(wu[e][(size_t)r * h + c]);
+            }
+        }
+#pragma omp parallel for schedule(static)
+        for (int r = 0; r < h; r++) {
+            ro_dequant_row(RO_Q4K, down + e * down_stride + (size_t)r * rb_ff, ff, wd[e] + (size_t)r * ff);
+            for (int c = 0; c < ff; c++) wd[e][(size_t)r * ff + c] = ro_bf16_round(wd[e][(size_t)r * ff + c]);
+        }
+    }
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int t = 0; t < T; t++) {
+        float* xb = (float*)malloc(sizeof(float) * (size_t)h);
+        float* act = (float*)malloc(sizeof(float) * (size_t)ff);
+        float* acc = (float*)calloc((size_t)h, sizeof(float));
+        for (int c = 0; c < h; c++) xb[c] = ro_bf16_round(x[(size_t)t * h + c]);
+        for (int s = 0; s < top_k; s++) {
+            int e = idx_io[(size_t)t * top_k + s];
+            if (e < 0 || e >= E) continue;
+            float wt = w_io[(size_t)t * top_k + s];
+            for (int r = 0; r < ff; r++) {
+                const float* g = wg[e] + (size_t)r * h;
+                const float* u = wu[e] + (size_t)r * h;
+                double ag = 0.0, au = 0.0;
+                for (int c = 0; c < h; c++) {
+                    ag += (double)g[c] * (double)xb[c];
+                    au += (double)u[c] * (double)xb[c];
+                }
+                act[r] = ro_bf16_round(ro_silu((float)ag) * (float)au);
+            }
+            for (int r = 0; r < h; r++) {
+                const float* d = wd[e] + (size_t)r * ff;
+                double ad = 0.0;
+                for (int c = 0; c < ff; c++) ad += (double)d[c] * (double)act[c];
+                acc[r] += wt * (float)ad;
+            }
+        }
+        for (int r = 0; r < h; r++) out[(size_t)t * h + r] = (residual ? residual[(size_t)t * h + r] : 0.0f) + acc[r];
+        free(xb);
+        free(act);
+        free(acc);
+    }
+    for (int e = 0; e < E; e++) {
+        free(wg[e]);
+        free(wu[e]);
+        free(wd[e]);
+    }
+    free(wg);
+    free(wu);
+    free(wd);
+    free(used);
+    return 0;
+}
+
 /* ───────────────────────── decode ops ───────────────────────── */
 
 /* crates/kernels/shaders/norm.metal:125-154 (f32 gamma); cpu_rms_norm dispatch.rs:1699-1702.

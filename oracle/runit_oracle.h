@@ -85,6 +85,10 @@ int      ro_topk_softmax(const float* logits, int n_experts, int top_k, int reno
 /* One MoE block over T tokens.  router: f32 [E][h]; gate/up: Q4_K [E][ff][h]; down: Q4_K
  * [E][h][ff]; x: [T][h]; out: [T][h] = (residual ? residual : 0) + sum_i w_i * expert_i(x).
  * idx_out/w_out (nullable): [T][top_k]. */
+float    ro_bf16_round(float f);
+int      ro_moe_grouped_q4k_bf16(const float* router, int renorm, const uint8_t* gate, const uint8_t* up,
+                                 const uint8_t* down, const float* x, const float* residual, float* out,
+                                 int32_t* idx_io, float* w_io, int T, int h, int ff, int E, int top_k);
 int      ro_moe_layer_q4k(int mode, int renorm, const float* router,
                           const uint8_t* gate, const uint8_t* up, const uint8_t* down,
                           const float* x, const float* residual, float* out,

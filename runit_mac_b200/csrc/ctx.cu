@@ -99,11 +99,12 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
 }
 
 int32_t runit_get_tmap(runit_ctx* ctx, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
-                       uint32_t box_bytes, CUtensorMap* out) {
+                       uint32_t box_bytes, CUtensorMap* out, uint32_t swizzle128) {
     if (!ctx->encode_tiled) return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
-    uint64_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull ^ (rows * 31 + row_bytes * 7 + box_rows);
+    uint64_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull ^ (rows * 31 + row_bytes * 7 + box_rows + swizzle128 * 131);
     runit_tmap_entry& e = ctx->tmaps[(h >> 32) & 255];
-    if (e.ptr == ptr && e.rows == rows && e.row_bytes == row_bytes && e.box_rows == box_rows && e.box_bytes == box_bytes) {
+    if (e.ptr == ptr && e.rows == rows && e.row_bytes == row_bytes && e.box_rows == box_rows && e.box_bytes == box_bytes &&
+        e.swizzle128 == swizzle128) {
         *out = e.map;
         return RUNIT_OK;
     }
@@ -117,10 +118,11 @@ int32_t runit_get_tmap(runit_ctx* ctx, const void* ptr, uint64_t rows, uint64_t 
     const cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
     CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
-    e.ptr = ptr; e.rows = rows; e.row_bytes = row_bytes; e.box_rows = box_rows; e.box_bytes = box_bytes; e.map = m;
+    e.ptr = ptr; e.rows = rows; e.row_bytes = row_bytes; e.box_rows = box_rows; e.box_bytes = box_bytes; e.swizzle128 = swizzle128; e.map = m;
     *out = m;
     return RUNIT_OK;
 }

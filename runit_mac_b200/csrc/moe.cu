@@ -154,13 +154,19 @@ static MoeScratch moe_carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uin
     return s;
 }
 
-static int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
+// Shared with the batched block (moe_grouped.cu).
+int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
     dim3 grid((E + 7) / 8, T < 64 ? T : 64);
     if (K == 2048) router_f32_kernel<64><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
     else if (K == 1024) router_f32_kernel<32><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
     else if (K == 4096) router_f32_kernel<128><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
     else router_f32_generic_kernel<<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
     return runit_after_launch(ctx, "moe_router_f32");
+}
+
+int32_t moe_topk(runit_ctx* ctx, const float* logits, uint32_t E, uint32_t k, int32_t renorm, uint32_t T, int32_t* idx, float* w) {
+    route_topk_kernel<<<(T + 3) / 4, 128, 0, ctx->stream>>>(logits, 0, E, k, renorm, T, idx, w);
+    return runit_after_launch(ctx, "moe_route_topk");
 }
 
 size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {

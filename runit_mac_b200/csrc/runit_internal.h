@@ -27,7 +27,7 @@ struct runit_tuning {
 struct runit_tmap_entry {
     const void* ptr = nullptr;
     uint64_t rows = 0, row_bytes = 0;
-    uint32_t box_rows = 0, box_bytes = 0;
+    uint32_t box_rows = 0, box_bytes = 0, swizzle128 = 0;
     CUtensorMap map;
 };
 
@@ -51,8 +51,11 @@ struct runit_ctx {
 };
 
 // Tensor map of a [rows][row_bytes] byte matrix with a [box_rows][box_bytes] box (cached per context).
+// swizzle128 != 0: the box (at most 128 bytes wide) lands in shared memory in the 128-byte swizzled layout the
+// tensor cores read (16-byte chunk c of row r at chunk position c ^ (r % 8)); the destination must be 1024-byte
+// aligned.
 int32_t runit_get_tmap(runit_ctx* ctx, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
-                       uint32_t box_bytes, CUtensorMap* out);
+                       uint32_t box_bytes, CUtensorMap* out, uint32_t swizzle128 = 0);
 
 const char* runit_status_name(int32_t st);
 

@@ -239,6 +239,9 @@ _TWINS = [
                       "scratch, scratch_bytes, T, h, ff, E, k, renorm)"),
     ("moe_experts_q4k", "no twin: (gate, up, down, x_slots, slot_expert, y_slots, act_scratch, n_slots, h, ff, n_experts)"),
     ("moe_layer_q4k_static", "no twin: moe_layer_q4k without the scratch arguments (built-in 4 MiB region)"),
+    ("moe_layer_q4k_bf16", "no twin (prefill.rs:156-215 batched): same arguments as moe_layer_q4k, scratch from "
+                           "moe_grouped_scratch_bytes"),
+    ("moe_experts_grouped_q4k_bf16", "no twin: (gate, up, down, x, idx, w, residual, out, scratch, scratch_bytes, T, h, ff, E, k)"),
     ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
     ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),
 ]
@@ -301,6 +304,34 @@ def moe_scratch_bytes(ctx: Context, T: int, h: int, ff: int, E: int, k: int) -> 
     return ctx.lib.runit_moe_scratch_bytes(T, h, ff, E, k)
 
 
+def moe_grouped_scratch_bytes(ctx: Context, T: int, h: int, ff: int, E: int, k: int) -> int:
+    return ctx.lib.runit_moe_grouped_scratch_bytes(T, h, ff, E, k)
+
+
+def moe_layer_q4k_bf16_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top_k, renorm=False, residual=None,
+                            routing=None):
+    """Convenience for tests: upload host arrays, run the batched tensor-core block once, download
+    (out [T][h], idx [T][k], weights [T][k]).  routing=(idx, w) skips the router and uses the given routing."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, h)
+    T = x.shape[0]
+    gate, up, down, xb = (ctx.buffer_from(np.ascontiguousarray(a)) for a in (gate, up, down, x))
+    res = None if residual is None else ctx.buffer_from(np.ascontiguousarray(residual, np.float32))
+    out = ctx.new_buffer(T * h * 4)
+    nbytes = moe_grouped_scratch_bytes(ctx, T, h, ff, E, top_k)
+    scratch = ctx.new_buffer(nbytes)
+    if routing is None:
+        rb = ctx.buffer_from(np.ascontiguousarray(router, np.float32))
+        idx, w = ctx.new_buffer(T * top_k * 4), ctx.new_buffer(T * top_k * 4)
+        ctx.call("moe_layer_q4k_bf16", rb, gate, up, down, xb, res, out, idx, w, scratch, nbytes, T, h, ff, E, top_k, int(renorm))
+    else:
+        idx = ctx.buffer_from(np.ascontiguousarray(routing[0], np.int32))
+        w = ctx.buffer_from(np.ascontiguousarray(routing[1], np.float32))
+        ctx.call("moe_experts_grouped_q4k_bf16", gate, up, down, xb, idx, w, res, out, scratch, nbytes, T, h, ff, E, top_k)
+    ctx.flush()
+    return (out.download(np.float32, T * h).reshape(T, h), idx.download(np.int32, T * top_k).reshape(T, top_k),
+            w.download(np.float32, T * top_k).reshape(T, top_k))
+
+
 def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top_k, renorm=False, residual=None):
     """Convenience for tests: upload host arrays, run runit_moe_layer_q4k once, download
     (out [T][h], idx [T][k], weights [T][k])."""
@@ -317,5 +348,5 @@ def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top
             w.download(np.float32, T * top_k).reshape(T, top_k))
 
 
-__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "moe_scratch_bytes", "moe_layer_q4k_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "moe_scratch_bytes", "moe_layer_q4k_host", "moe_grouped_scratch_bytes", "moe_layer_q4k_bf16_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
            "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K"] + [n for n, _ in _TWINS]

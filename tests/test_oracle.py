@@ -204,6 +204,40 @@ def test_moe_layer_modes(oracle):
         assert np.abs(y16[finite] - y[finite]).max() <= 2e-2 * np.abs(y).max()
 
 
+def test_bf16_block_mode(oracle):
+    """bf16 rounding is round-to-nearest-even on the top 16 bits; the bf16-operand block stays near the f32 block and
+    gives the same result whether it routes itself or is handed that routing."""
+    O = oracle
+    v = np.array([1.0, 1.00390625, 1.01171875, 1.0078125, -3.14159, 0.0, 65504.0, 1e-30], np.float32)
+    r = O.bf16_round(v)
+    assert r.tolist()[:4] == [1.0, 1.0, 1.015625, 1.0078125]     # ties go to the even mantissa
+    assert (r.view(np.uint32) & 0xFFFF == 0).all() and np.abs(r - v).max() <= np.abs(v).max() * 2.0 ** -8
+    assert all(O.lib().ro_bf16_round(float(a)) == float(b) for a, b in zip(v, r))
+    rng = np.random.default_rng(21)
+    h, ff, E, k, T = 256, 256, 4, 2, 5
+    router = rng.normal(0, 0.02, (E, h)).astype(np.float32)
+    gate, up, down = O.rand_q4k(rng, E * ff, h), O.rand_q4k(rng, E * ff, h), O.rand_q4k(rng, E * h, ff)
+    x = rng.normal(0, 1, (T, h)).astype(np.float32)
+    y32, i32, w32 = O.moe_layer_q4k(router, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, renorm=False)
+    yb, ib, wb = O.moe_grouped_q4k_bf16(router, gate, up, down, x, h=h, ff=ff, E=E, top_k=k)
+    assert (ib == i32).all() and np.array_equal(wb, w32)
+    assert np.abs(yb - y32).max() <= 3e-2 * np.sqrt(np.mean(y32 ** 2))
+    yg, _, _ = O.moe_grouped_q4k_bf16(None, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, routing=(ib, wb))
+    assert np.array_equal(yg, yb)
+    # rebuild one output element from the primitive ops: dequantised rows rounded to bf16, x rounded to bf16
+    rb_h, rb_ff = O.row_bytes(O.Q4K, h), O.row_bytes(O.Q4K, ff)
+    xb = O.bf16_round(x[0]).astype(np.float64)
+    acc = np.float32(0)
+    for e, we in zip(ib[0], wb[0]):
+        wg = O.bf16_round(O.dequant_rows(O.Q4K, gate.reshape(-1)[e * ff * rb_h:(e + 1) * ff * rb_h], ff, h)).astype(np.float64)
+        wu = O.bf16_round(O.dequant_rows(O.Q4K, up.reshape(-1)[e * ff * rb_h:(e + 1) * ff * rb_h], ff, h)).astype(np.float64)
+        wd = O.bf16_round(O.dequant_rows(O.Q4K, down.reshape(-1)[e * h * rb_ff:(e + 1) * h * rb_ff], h, ff)).astype(np.float64)
+        g, u = (wg @ xb).astype(np.float32), (wu @ xb).astype(np.float32)
+        act = O.bf16_round(O.silu_mul_f32(g, u)).astype(np.float64)
+        acc = np.float32(acc + np.float32(we) * np.float32(wd[3] @ act))
+    assert abs(acc - yb[0, 3]) <= 2e-6 * abs(yb[0]).max()
+
+
 def test_decode_ops(oracle):
     O = oracle
     rng = np.random.default_rng(17)
