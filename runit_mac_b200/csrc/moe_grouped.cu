@@ -64,6 +64,11 @@ __device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
 __device__ __forceinline__ float lo_f(uint64_t v) { return __uint_as_float((uint32_t)v); }
 __device__ __forceinline__ float hi_f(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
 
+// silu without the IEEE division: v / (1 + exp(-v)) takes the division's slow path whenever the denominator is
+// huge or infinite (v below about -87), and gate values that far out are common at these weight scales.
+// __fdividef returns 0 for an infinite or very large denominator, which is the limit of silu there; error <= 2 ulp.
+__device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
 template <bool LO, bool HI>
 __device__ __forceinline__ void dequant_chunk(const uint32_t* q, float s_lo, float m_lo, float s_hi, float m_hi,
                                               uint32_t row_addr, uint32_t rx) {
@@ -212,7 +217,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
             const uint32_t tt = item / a.nb, rb = item % a.nb;
             const int32_t nvalid = a.tile_nvalid[tt];
             const uint32_t b = n & 1;
-            if (!mbar_wait_timed(bar_accf + 8 * b, (n >> 1) & 1, abort_flag)) break;
+            // one lane polls; the others are released (and ordered) by the warp barrier
+            uint32_t got = 1;
+            if (lane == 0) got = mbar_wait_timed(bar_accf + 8 * b, (n >> 1) & 1, abort_flag);
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) break;
             tc_fence_after_sync();
             const uint32_t col = rb * kRows + quarter * 32 + lane;   // output feature = weight row
             const size_t row0 = (size_t)tt * kTok;
@@ -231,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
                     for (int i = 0; i < 32; i++)
                         if (cg * 32 + i < nvalid)
                             out[(row0 + cg * 32 + i) * a.ld + col] =
-                                __float2bfloat16_rn(silu(__uint_as_float(g[i])) * __uint_as_float(u[i]));
+                                __float2bfloat16_rn(silu_fast(__uint_as_float(g[i])) * __uint_as_float(u[i]));
                 } else {
                     tmem_ld_wait();
                     float* out = reinterpret_cast<float*>(a.out);
@@ -271,7 +280,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
 #pragma unroll
             for (int j = 0; j < 4; j++, it++) {
                 const uint32_t s = it % C::NS, ph = (it / C::NS) & 1;
-                if (!mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
+                uint32_t got = 1;
+                if (lane == 0) got = mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag);
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (!got) { ok = false; break; }
                 const float s_lo = dd * byte_to_float(sc.sl, j), m_lo = dmin * byte_to_float(sc.ml, j);
                 const float s_hi = dd * byte_to_float(sc.sh, j), m_hi = dmin * byte_to_float(sc.mh, j);
                 const uint32_t tile = base + s * C::STAGE + (DUAL ? part * kTileBytes : 0);

@@ -83,22 +83,21 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "memory");
     return done != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Wait bounded by wall time (1 s) and by the CTA's abort flag: returns false when the wait gave up; the first
-// thread to give up raises the flag so that every other role of the CTA leaves its loop too.
+// Wait bounded by time (2^31 SM cycles, about a second) and by the CTA's abort flag: returns false when the wait gave
+// up; the first thread to give up raises the flag so that every other role of the CTA leaves its loop too.  The
+// cycle counter is read only once per 256 failed polls (each poll may itself suspend the thread for a while).
+// Wait bounded by time (2^31 SM cycles, about a second) and by the CTA's abort flag: returns false when the wait gave
+// up; the first thread to give up raises the flag so that every other role of the CTA leaves its loop too.  The
+// cycle counter is read only once per 256 failed polls (each poll may itself suspend the thread for a while).
 __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
-        for (int i = 0; i < 32; i++)
+        for (int i = 0; i < 256; i++)
             if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > 1000000000ull) {
+        if (clock64() - t0 > (1ll << 31)) {
             *abort_flag = 1;
             return false;
         }

@@ -1,13 +1,13 @@
 """GPU parity tests of the batched (prefill-sized) MoE block on the tensor cores, through the C ABI.
 
 Oracle: the bf16-operand restatement of the block (weights = bf16 of the Q4_K value, activations bf16,
-f64 accumulation rounded to f32).  Bar: |gpu - oracle| <= 1e-3 * max(|ref|, rms(ref)); the residue comes from
-the f32 accumulation order inside the MMA and from intermediate activations that land on the other side of a
-bf16 rounding boundary.  Routing indices must be identical (ties closer than 1e-6 excluded)."""
+f64 accumulation rounded to f32).  Bar: |gpu - oracle| <= 1e-3 * max(|ref|, rms(ref)) for at least 99.9 % of the outputs and
+4e-3 for all of them: the residue comes from the f32 accumulation order inside the MMA and from intermediate
+activations that land on the other side of a bf16 rounding boundary (helpers.assert_close_bf16_chain).  Routing indices must be identical (ties closer than 1e-6 excluded)."""
 import numpy as np
 import pytest
 
-from helpers import assert_close
+from helpers import assert_close, assert_close_bf16_chain
 
 pytestmark = pytest.mark.gpu
 
@@ -30,7 +30,7 @@ def test_grouped_block_with_router(ctx, oracle, T, E, k, h, ff):
     same = (idx == ridx).all(1)
     assert same.sum() >= T - max(1, T // 100), "routing differs on %d tokens" % (T - same.sum())
     assert np.allclose(w[same], rw[same], rtol=1e-5, atol=1e-8)
-    assert_close(O, ref[same], out[same], what="grouped block T=%d" % T)
+    assert_close_bf16_chain(O, ref[same], out[same], what="grouped block T=%d" % T)
     # the bf16 block stays close to the f32 block (bf16 operands: ~2^-9 per product, averaged over the sum)
     ref32, i32, _ = O.moe_layer_q4k(router, gate, up, down, x[:4], h=h, ff=ff, E=E, top_k=k, renorm=False)
     ok = (i32 == idx[:4]).all(1)
@@ -57,7 +57,7 @@ def test_grouped_block_given_routing_edge_cases(ctx, oracle):
     w = rng.random((T, k)).astype(np.float32)
     ref, _, _ = O.moe_grouped_q4k_bf16(None, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, residual=res, routing=(idx, w))
     out, _, _ = R.moe_layer_q4k_bf16_host(ctx, None, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, residual=res, routing=(idx, w))
-    assert_close(O, ref - res, out - res, what="given routing")
+    assert_close_bf16_chain(O, ref - res, out - res, what="given routing")
     assert np.array_equal(out[255], res[255])     # both slots of the last token are skipped
 
 
@@ -111,7 +111,7 @@ def test_full_size_block_sampled_and_properties(oracle, qwen3_moe_block):
     xs = b["x"][sample].cpu().numpy()
     ref, _, _ = O.moe_grouped_q4k_bf16(None, gate, up, down, xs, h=h, ff=ff, E=E, top_k=k,
                                        routing=(b["idx"][sample].cpu().numpy(), b["w"][sample].cpu().numpy()))
-    assert_close(O, ref, out[sample].cpu().numpy(), what="sampled tokens of the full-size block")
+    assert_close_bf16_chain(O, ref, out[sample].cpu().numpy(), what="sampled tokens of the full-size block")
     # (2) permuting the tokens permutes the outputs bit for bit (no token sees another token's data)
     perm = torch.randperm(T, device="cuda", generator=torch.Generator(device="cuda").manual_seed(9))
     out_p = run_block(b, b["x"][perm].contiguous(), b["idx"][perm].contiguous(), b["w"][perm].contiguous())
