@@ -45,11 +45,13 @@ struct Args {
     uint32_t K;
     uint32_t nb;                  // rows / 128
     const int32_t* tile_expert;   // per token tile
-    const int32_t* tile_nvalid;   // valid slots of the tile (1..128)
+    const int32_t* tile_nvalid;   // valid slots of the tile (1..tile size)
+    const int32_t* tile_row0;     // first row of the tile in the permuted order
     const int32_t* n_tok_tiles;   // device-resident count
     void* out;                    // bf16 [rows_padded][ld] (fused gate/up) or f32 [rows_padded][ld]
     uint32_t ld;
     int32_t* status;
+    int32_t dbg_ld;               // timing study: record a timeline when ld equals this
 };
 
 // ── dequantisation of one 64-element K chunk of one weight row into the swizzled A tile ──
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const uint32_t row_start = (item / a.nb) * kTok;
+                const uint32_t row_start = (uint32_t)a.tile_row0[item / a.nb];
                 for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
                     const uint32_t s = it % C::NS, ph = (it / C::NS) & 1;
                     if (!mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag)) break;
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
             if (!got) break;
             tc_fence_after_sync();
             const uint32_t col = rb * kRows + quarter * 32 + lane;   // output feature = weight row
-            const size_t row0 = (size_t)tt * kTok;
+            const size_t row0 = (size_t)a.tile_row0[tt];
 #pragma unroll 1
             for (int cg = 0; cg < 4; cg++) {
                 if (cg * 32 >= nvalid) break;
@@ -310,6 +312,282 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
     if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 2);
 }
 
+// ───────────────────────── CTA-pair kernel (cta_group::2) ─────────────────────────
+// Two CTAs of one cluster share a work item of 256 weight rows x up to 256 token slots.  Each CTA dequantises 128
+// of the rows and loads half of the token tile; the leader CTA issues M = 256 MMAs that read both CTAs' shared
+// memory and write 128 accumulator rows into each CTA's tensor memory.  Against the single-CTA kernel every
+// dequantised weight serves twice as many tokens and every loaded token row twice as many weight rows.
+//   * Q4_K rows arrive by TMA (box 128 rows x 144 bytes = one superblock per row) into a 3-deep raw ring; the
+//     dequantisers read them from shared memory, so no thread holds a superblock in registers.
+//   * 16 dequantiser warps in two groups that take alternate 64-wide K chunks: while one group waits for its
+//     stage or for the barrier round trip, the other one computes.
+//   * fused gate/up: the CTA's 128 tile rows are 64 gate rows followed by the 64 up rows of the same
+//     intermediate indices; the epilogue warps of the up half hand their values to the gate half through shared
+//     memory.
+// Barriers: full[s] and acc_empty[b] live in the leader and also take arrivals from the peer (cluster-scope);
+// empty[s] and acc_full[b] are signalled in both CTAs at once by the leader's tcgen05.commit.
+namespace pair {
+
+__device__ long long g_dbg[2 * 8 * 512];
+#define GG_DBG(slot, step) do { if (a.status == nullptr) {} if (dbg_on && blockIdx.x < 2 && (step) < 512) g_dbg[(blockIdx.x * 8 + (slot)) * 512 + (step)] = clock64(); } while (0)
+
+constexpr int kThreads = 736;              // 23 warps: token-tile producer, MMA, 4 epilogue, 16 dequantisers, raw producer
+constexpr int kRawWarp = 22;
+constexpr int kDeqWarp0 = 6, kGroupWarps = 8;
+constexpr int kNS = 5;                     // A/B stages
+constexpr int kNR = 3;                     // raw superblock ring
+constexpr int kStage = 2 * kTileBytes;     // A tile + token tile
+constexpr int kRawBytes = 128 * 144;
+constexpr int kXchgBytes = 2 * 32 * 33 * 4;
+constexpr int kOffRaw = kNS * kStage;
+constexpr int kOffXchg = kOffRaw + kNR * kRawBytes;
+constexpr int kOffCtrl = kOffXchg + kXchgBytes;
+constexpr int kSmem = kOffCtrl + 256 + 1024;
+constexpr int kTmemCols = 512, kAccCols = 256;
+constexpr int kTokPair = 256;
+
+template <bool DUAL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_w0,
+                         const __grid_constant__ CUtensorMap map_w1, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_p = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t ctrl = base + kOffCtrl;
+    const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * kNS, bar_rawf = bar_empty + 8 * kNS, bar_rawe = bar_rawf + 8 * kNR,
+                   bar_accf = bar_rawe + 8 * kNR, bar_acce = bar_accf + 16, holder = bar_acce + 16;
+    volatile uint32_t* holder_p = reinterpret_cast<volatile uint32_t*>(base_p + kOffCtrl + (holder - ctrl));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_p + kOffCtrl + (holder - ctrl) + 4);
+    float* xchg = reinterpret_cast<float*>(base_p + kOffXchg);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    if (tid == 0) {
+        for (int s = 0; s < kNS; s++) {
+            mbar_init(bar_full + 8 * s, 2 * kGroupWarps + 1);   // both CTAs' dequantiser group + the leader's expect_tx
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int u = 0; u < kNR; u++) {
+            mbar_init(bar_rawf + 8 * u, 1);
+            mbar_init(bar_rawe + 8 * u, 2 * kGroupWarps);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar_accf + 8 * b, 1);
+            mbar_init(bar_acce + 8 * b, 8);                      // 4 epilogue warps of each CTA
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc_pair(holder, kTmemCols);
+        tmem_relinquish_pair();
+    }
+    __syncwarp();
+    tc_fence_before_sync();
+    cluster_sync();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *holder_p;
+    const bool dbg_on = a.ld == (uint32_t)a.dbg_ld || (a.dbg_ld < 0 && a.ld == 768);
+
+    const uint32_t nb = DUAL ? a.rows / 128 : a.rows / 256;
+    const uint32_t n_items = (uint32_t)(*a.n_tok_tiles) * nb;
+    const uint32_t units = a.K / 256;
+    const uint32_t leader_full = cluster_map(bar_full, 0), leader_acce = cluster_map(bar_acce, 0);
+
+    auto tile_cols = [&](int32_t nvalid) -> uint32_t { return nvalid <= 32 ? 32u : (uint32_t)((nvalid + 31) & ~31); };
+
+    if (warp == 0) {
+        // ───────── TMA producer: the token tile of every stage ─────────
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t item = pair_id; item < n_items && ok && !*abort_flag; item += n_pairs) {
+                const uint32_t tt = item / nb;
+                const uint32_t ncols = tile_cols(a.tile_nvalid[tt]);
+                const int32_t row_b = a.tile_row0[tt] + (int32_t)(rank * (ncols / 2));
+                for (uint32_t kc = 0; kc < units * 4; kc++, it++) {
+                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
+                    if (!mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
+                    GG_DBG(1, it);
+                    if (a.dbg_ld < 0 && ((-a.dbg_ld) & 1)) { if (rank == 0) mbar_arrive(bar_full + 8 * s); continue; }
+                    if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kTileBytes);
+                    tma_load_2d_pair(base + s * kStage + kTileBytes, &map_b, (int32_t)(kc * 128), row_b, leader_full + 8 * s);
+                }
+            }
+        }
+    } else if (warp == kRawWarp) {
+        // ───────── TMA producer: raw Q4_K superblocks, one unit (256 K) of the CTA's 128 rows per ring slot ─────────
+        if (lane == 0) {
+            uint32_t uc = 0;
+            bool ok = true;
+            for (uint32_t item = pair_id; item < n_items && ok && !*abort_flag; item += n_pairs) {
+                const uint32_t tt = item / nb, rb = item % nb;
+                const uint32_t e = (uint32_t)a.tile_expert[tt];
+                for (uint32_t u = 0; u < units; u++, uc++) {
+                    const uint32_t ur = uc % kNR;
+                    if (!mbar_wait_timed(bar_rawe + 8 * ur, ((uc / kNR) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t dst = base + kOffRaw + ur * kRawBytes;
+                    GG_DBG(0, uc);
+                    if (a.dbg_ld < 0 && ((-a.dbg_ld) & 4)) { mbar_arrive(bar_rawf + 8 * ur); continue; }
+                    mbar_expect_tx(bar_rawf + 8 * ur, kRawBytes);
+                    if (DUAL) {
+                        const int32_t row = (int32_t)(e * a.rows + rb * 128 + rank * 64);
+                        tma_load_2d(dst, &map_w0, (int32_t)(u * 144), row, bar_rawf + 8 * ur);
+                        tma_load_2d(dst + 64 * 144, &map_w1, (int32_t)(u * 144), row, bar_rawf + 8 * ur);
+                    } else {
+                        tma_load_2d(dst, &map_w0, (int32_t)(u * 144), (int32_t)(e * a.rows + rb * 256 + rank * 128), bar_rawf + 8 * ur);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ───────── MMA issuer (leader CTA only) ─────────
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, n = 0;
+            bool ok = true;
+            for (uint32_t item = pair_id; item < n_items && ok && !*abort_flag; item += n_pairs, n++) {
+                const uint32_t idesc = umma_idesc_bf16(256, tile_cols(a.tile_nvalid[item / nb]));
+                const uint32_t b = n & 1;
+                if (!mbar_wait_timed_cluster(bar_acce + 8 * b, ((n >> 1) & 1) ^ 1, abort_flag)) break;
+                tc_fence_after_sync();
+                const uint32_t d_addr = tmem_base + b * kAccCols;
+                for (uint32_t kc = 0; kc < units * 4; kc++, it++) {
+                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
+                    if (!mbar_wait_timed_cluster(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    GG_DBG(2, it);
+                    const uint32_t sb = base + s * kStage;
+                    const uint64_t da = umma_desc_sw128(sb), db = umma_desc_sw128(sb + kTileBytes);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < 4; k4++) { if (a.dbg_ld < 0 && ((-a.dbg_ld) & 8)) break; umma_bf16_pair(d_addr, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0); }
+                    umma_commit_pair(bar_empty + 8 * s, 3);
+                    GG_DBG(3, it);
+                }
+                if (ok) umma_commit_pair(bar_accf + 8 * b, 3);
+            }
+        }
+    } else if (warp < kDeqWarp0) {
+        // ───────── epilogue ─────────
+        // The four warps meet on a named barrier inside the loop, so they must leave it together: one thread waits
+        // for the accumulator and publishes the verdict (also on abort) to the other 127.
+        const uint32_t quarter = warp & 3;
+        volatile int* go = reinterpret_cast<volatile int*>(base_p + kOffCtrl + (holder - ctrl) + 8);
+        uint32_t n = 0;
+        for (uint32_t item = pair_id; item < n_items; item += n_pairs, n++) {
+            const uint32_t tt = item / nb, rb = item % nb;
+            const int32_t nvalid = a.tile_nvalid[tt];
+            const size_t row0 = (size_t)a.tile_row0[tt];
+            const uint32_t b = n & 1;
+            if (warp == kEpiWarp0 && lane == 0)
+                *go = (mbar_wait_timed(bar_accf + 8 * b, (n >> 1) & 1, abort_flag) && !*abort_flag) ? 1 : 0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int verdict = *go;
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone has read it before the next item overwrites it
+            if (!verdict) break;
+            tc_fence_after_sync();
+            const uint32_t taddr0 = tmem_base + ((quarter * 32) << 16) + b * kAccCols;
+#pragma unroll 1
+            for (int cg = 0; cg * 32 < nvalid; cg++) {
+                uint32_t v[32];
+                tmem_ld32(taddr0 + cg * 32, v);
+                tmem_ld_wait();
+                if (DUAL) {
+                    // tile rows 0..63 = gate (quarters 0, 1), 64..127 = up of the same intermediate indices (quarters 2, 3)
+                    float* x = xchg + (quarter & 1) * (32 * 33) + lane * 33;
+                    if (quarter >= 2) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) x[i] = __uint_as_float(v[i]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (quarter < 2) {
+                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
+                        const uint32_t col = rb * 128 + rank * 64 + quarter * 32 + lane;
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (cg * 32 + i < nvalid)
+                                out[(row0 + cg * 32 + i) * a.ld + col] = __float2bfloat16_rn(silu_fast(__uint_as_float(v[i])) * x[i]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                } else {
+                    float* out = reinterpret_cast<float*>(a.out);
+                    const uint32_t col = rb * 256 + rank * 128 + quarter * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (cg * 32 + i < nvalid) out[(row0 + cg * 32 + i) * a.ld + col] = __uint_as_float(v[i]);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(bar_acce + 8 * b);
+                else mbar_arrive_cluster(leader_acce + 8 * b);
+            }
+        }
+    } else if (warp < kRawWarp) {
+        // ───────── dequantisers: raw ring -> bf16 swizzled A tile; group g takes the chunks j with j % 2 == g ─────────
+        const uint32_t g = (warp - kDeqWarp0) / kGroupWarps;
+        const uint32_t t = ((warp - kDeqWarp0) % kGroupWarps) * 32 + lane;
+        const uint32_t r = t & 127, part = t >> 7, rx = r & 7;
+        uint32_t uc = 0;
+        bool ok = true;
+        for (uint32_t item = pair_id; item < n_items && ok && !*abort_flag; item += n_pairs) {
+            for (uint32_t u = 0; u < units && ok; u++, uc++) {
+                const uint32_t ur = uc % kNR;
+                if (!mbar_wait_timed(bar_rawf + 8 * ur, (uc / kNR) & 1, abort_flag)) { ok = false; break; }
+                if (t == 0 && g == 0) GG_DBG(4, uc);
+                const uint32_t raw_row = base + kOffRaw + ur * kRawBytes + r * 144;
+                uint32_t h0, h1, h2, h3;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(raw_row) : "memory");
+                const float dd = half_bits_to_float(h0), dmin = half_bits_to_float(h0 >> 16);
+                const Q4KScales sc = q4k_unpack_scales(h1, h2, h3);
+#pragma unroll
+                for (int jj = 0; jj < 2; jj++) {
+                    const uint32_t j = 2 * jj + g;
+                    const uint32_t it = uc * 4 + j;
+                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
+                    uint32_t q[8];
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]) : "r"(raw_row + 16 + 32 * j) : "memory");
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]) : "r"(raw_row + 32 + 32 * j) : "memory");
+                    const uint32_t sh = 8 * j;
+                    const float s_lo = dd * (float)((sc.sl >> sh) & 0xFFu), m_lo = dmin * (float)((sc.ml >> sh) & 0xFFu);
+                    const float s_hi = dd * (float)((sc.sh >> sh) & 0xFFu), m_hi = dmin * (float)((sc.mh >> sh) & 0xFFu);
+                    uint32_t got = 1;
+                    if (lane == 0) got = mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag);
+                    got = __shfl_sync(0xffffffffu, got, 0);
+                    if (!got) { ok = false; break; }
+                    if (t == 0) GG_DBG(5, it);
+                    const uint32_t row_addr = base + s * kStage + r * 128;
+                    if (!(a.dbg_ld < 0 && ((-a.dbg_ld) & 2))) {
+                    if (part == 0) dequant_chunk<true, false>(q, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
+                    else dequant_chunk<false, true>(q, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (t == 0) GG_DBG(6, it);
+                    if (lane == 0) {
+                        if (rank == 0) mbar_arrive(bar_full + 8 * s);
+                        else mbar_arrive_cluster(leader_full + 8 * s);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(bar_rawe + 8 * ur);
+            }
+        }
+    }
+
+    __syncwarp();            // the single-lane roles rejoin their warps before the aligned cluster barrier
+    tc_fence_before_sync();
+    cluster_sync();
+    if (warp == 0) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+    if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 2);
+}
+
+}  // namespace pair
+
 // ───────────────────────── token permutation ─────────────────────────
 
 // counts[e] = slots routed to expert e; slots with an id outside [0, E) get position -1.
@@ -328,31 +606,34 @@ __global__ void __launch_bounds__(256) count_kernel(const int32_t* __restrict__ 
 }
 
 // One CTA per expert: first row of the expert in the permuted order (experts in index order, each padded to a
-// multiple of 128 rows), the token-tile table, and the position of each of its slots (slot order kept).
+// multiple of 128 rows), the token-tile table (tiles of `tile_tok` slots, 128 or 256, never across experts), and the
+// position of each of its slots (slot order kept).
 __global__ void __launch_bounds__(1024) place_kernel(const int32_t* __restrict__ idx, uint32_t S, uint32_t E,
-                                                      const int32_t* __restrict__ counts, int32_t* __restrict__ pos_of_slot,
-                                                      int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_nvalid,
+                                                      const int32_t* __restrict__ counts, int tile_tok,
+                                                      int32_t* __restrict__ pos_of_slot, int32_t* __restrict__ tile_expert,
+                                                      int32_t* __restrict__ tile_nvalid, int32_t* __restrict__ tile_row0,
                                                       int32_t* __restrict__ n_tok_tiles) {
-    __shared__ int s_pad[256];
+    __shared__ int s_cnt[256];
     __shared__ int s_warp[32];
-    __shared__ int s_off, s_chunk;
+    __shared__ int s_off, s_tile0, s_chunk;
     const uint32_t e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < 256) s_pad[tid] = tid < E ? ((counts[tid] + kTok - 1) / kTok) * kTok : 0;
+    if (tid < 256) s_cnt[tid] = tid < E ? counts[tid] : 0;
     __syncthreads();
     if (tid == 0) {
-        int off = 0, total = 0;
+        int off = 0, tiles = 0;
         for (uint32_t i = 0; i < E; i++) {
-            if (i == e) off = total;
-            total += s_pad[i];
+            if (i == e) { s_off = off; s_tile0 = tiles; }
+            off += ((s_cnt[i] + kTok - 1) / kTok) * kTok;
+            tiles += (s_cnt[i] + tile_tok - 1) / tile_tok;
         }
-        s_off = off;
-        if (e == 0) n_tok_tiles[0] = total / kTok;
+        if (e == 0) n_tok_tiles[0] = tiles;
     }
     __syncthreads();
-    const int cnt = counts[e], off = s_off;
-    for (int i = tid; i * kTok < cnt; i += 1024) {
-        tile_expert[off / kTok + i] = (int32_t)e;
-        tile_nvalid[off / kTok + i] = min(kTok, cnt - i * kTok);
+    const int cnt = s_cnt[e], off = s_off, tile0 = s_tile0;
+    for (int i = tid; i * tile_tok < cnt; i += 1024) {
+        tile_expert[tile0 + i] = (int32_t)e;
+        tile_nvalid[tile0 + i] = min(tile_tok, cnt - i * tile_tok);
+        tile_row0[tile0 + i] = off + i * tile_tok;
     }
     int running = 0;
     for (uint32_t s0 = 0; s0 < S; s0 += 1024) {
@@ -418,7 +699,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
 // ───────────────────────── host side ─────────────────────────
 
 struct Scratch {
-    int32_t *counts, *n_tok_tiles, *tile_expert, *tile_nvalid, *pos_of_slot, *idx;
+    int32_t *counts, *n_tok_tiles, *tile_expert, *tile_nvalid, *tile_row0, *pos_of_slot, *idx;
     float *logits, *w, *y;
     __nv_bfloat16 *xperm, *act;
     uint32_t max_tiles;
@@ -429,7 +710,7 @@ static Scratch carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uint32_t E
     Scratch s{};
     const size_t S = (size_t)T * k;
     s.max_tiles = (uint32_t)((S + kTok - 1) / kTok) + E;
-    const size_t rows = (size_t)s.max_tiles * kTok;
+    const size_t rows = (size_t)s.max_tiles * kTok + 256;   // + slack: a tile's load may reach past its last valid row
     size_t off = 0;
     auto take = [&](size_t bytes) {
         void* p = base ? (void*)((uint8_t*)base + off) : nullptr;
@@ -440,6 +721,7 @@ static Scratch carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uint32_t E
     s.n_tok_tiles = (int32_t*)take(16);
     s.tile_expert = (int32_t*)take(4 * (size_t)s.max_tiles);
     s.tile_nvalid = (int32_t*)take(4 * (size_t)s.max_tiles);
+    s.tile_row0 = (int32_t*)take(4 * (size_t)s.max_tiles);
     s.pos_of_slot = (int32_t*)take(4 * S);
     s.idx = (int32_t*)take(4 * S);
     s.w = (float*)take(4 * S);
@@ -468,31 +750,62 @@ static int32_t launch_gemm(runit_ctx* ctx, const char* name, const Args& a, cons
     return runit_after_launch(ctx, name);
 }
 
+template <bool DUAL>
+static int32_t launch_pair(runit_ctx* ctx, const char* name, const Args& a, const void* b_ptr, uint32_t b_rows, uint32_t n_experts,
+                           uint32_t max_items) {
+    static bool attr_set[64] = {false};
+    if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
+        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(pair::grouped_gemm_pair_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmem));
+        attr_set[ctx->device] = true;
+    }
+    CUtensorMap map_b, map_w0, map_w1;
+    int32_t st = runit_get_tmap(ctx, b_ptr, b_rows, (uint64_t)a.K * 2, kTok, 128, &map_b, 1);
+    if (st != RUNIT_OK) return st;
+    const uint64_t w_rows = (uint64_t)n_experts * a.rows, row_bytes = (uint64_t)a.K / 256 * 144;
+    st = runit_get_tmap(ctx, a.w0, w_rows, row_bytes, DUAL ? 64 : 128, 144, &map_w0);
+    if (st != RUNIT_OK) return st;
+    map_w1 = map_w0;
+    if (DUAL && (st = runit_get_tmap(ctx, a.w1, w_rows, row_bytes, 64, 144, &map_w1)) != RUNIT_OK) return st;
+    uint32_t pairs = (uint32_t)ctx->sm_count / 2;
+    if (pairs > max_items) pairs = max_items;
+    if (pairs == 0) pairs = 1;
+    pair::grouped_gemm_pair_kernel<DUAL><<<2 * pairs, pair::kThreads, pair::kSmem, ctx->stream>>>(map_b, map_w0, map_w1, a);
+    return runit_after_launch(ctx, name);
+}
+
 // The expert part of the block for given routing (idx int32 [T][k], w f32 [T][k]).
+// tune.moe_variant == 1 selects the single-CTA kernels (128-slot tiles); the default is the CTA-pair kernels.
 static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, const void* up, const void* down,
                             const float* x, const int32_t* idx, const float* w, const float* residual, float* out,
                             uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
     const uint32_t S = T * k;
+    const bool single = ctx->tune.moe_variant > 0 && (ctx->tune.moe_variant & 15) == 1;
     RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(s.counts, 0, 4 * 256, ctx->stream));
     count_kernel<<<(S + 4095) / 4096, 256, 0, ctx->stream>>>(idx, S, E, s.counts, s.pos_of_slot);
     int32_t st = runit_after_launch(ctx, "moe_grouped_count");
     if (st != RUNIT_OK) return st;
-    place_kernel<<<E, 1024, 0, ctx->stream>>>(idx, S, E, s.counts, s.pos_of_slot, s.tile_expert, s.tile_nvalid, s.n_tok_tiles);
+    place_kernel<<<E, 1024, 0, ctx->stream>>>(idx, S, E, s.counts, single ? kTok : pair::kTokPair, s.pos_of_slot, s.tile_expert,
+                                              s.tile_nvalid, s.tile_row0, s.n_tok_tiles);
     if ((st = runit_after_launch(ctx, "moe_grouped_place")) != RUNIT_OK) return st;
     gather_kernel<<<S, 256, 0, ctx->stream>>>(x, s.pos_of_slot, s.xperm, h, k);
     if ((st = runit_after_launch(ctx, "moe_grouped_gather")) != RUNIT_OK) return st;
 
-    const uint32_t rows = s.max_tiles * kTok;
+    const uint32_t rows = s.max_tiles * kTok + 256;
     Args a1{};
     a1.w0 = (const uint8_t*)gate; a1.w1 = (const uint8_t*)up; a1.rows = ff; a1.K = h; a1.nb = ff / kRows;
-    a1.tile_expert = s.tile_expert; a1.tile_nvalid = s.tile_nvalid; a1.n_tok_tiles = s.n_tok_tiles;
-    a1.out = s.act; a1.ld = ff; a1.status = ctx->d_status;
-    if ((st = launch_gemm<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, s.max_tiles * a1.nb)) != RUNIT_OK) return st;
+    a1.tile_expert = s.tile_expert; a1.tile_nvalid = s.tile_nvalid; a1.tile_row0 = s.tile_row0; a1.n_tok_tiles = s.n_tok_tiles;
+    a1.out = s.act; a1.ld = ff; a1.status = ctx->d_status; a1.dbg_ld = ctx->tune.moe_variant < 0 ? ctx->tune.moe_variant : ctx->tune.moe_variant >> 4;
     Args a2{};
     a2.w0 = (const uint8_t*)down; a2.w1 = nullptr; a2.rows = h; a2.K = ff; a2.nb = h / kRows;
-    a2.tile_expert = s.tile_expert; a2.tile_nvalid = s.tile_nvalid; a2.n_tok_tiles = s.n_tok_tiles;
-    a2.out = s.y; a2.ld = h; a2.status = ctx->d_status;
-    if ((st = launch_gemm<false>(ctx, "moe_grouped_down", a2, s.act, rows, s.max_tiles * a2.nb)) != RUNIT_OK) return st;
+    a2.tile_expert = s.tile_expert; a2.tile_nvalid = s.tile_nvalid; a2.tile_row0 = s.tile_row0; a2.n_tok_tiles = s.n_tok_tiles;
+    a2.out = s.y; a2.ld = h; a2.status = ctx->d_status; a2.dbg_ld = ctx->tune.moe_variant < 0 ? ctx->tune.moe_variant : ctx->tune.moe_variant >> 4;
+    if (single) {
+        if ((st = launch_gemm<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, s.max_tiles * a1.nb)) != RUNIT_OK) return st;
+        if ((st = launch_gemm<false>(ctx, "moe_grouped_down", a2, s.act, rows, s.max_tiles * a2.nb)) != RUNIT_OK) return st;
+    } else {
+        if ((st = launch_pair<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, E, s.max_tiles * (ff / 128))) != RUNIT_OK) return st;
+        if ((st = launch_pair<false>(ctx, "moe_grouped_down", a2, s.act, rows, E, s.max_tiles * (h / 256))) != RUNIT_OK) return st;
+    }
     combine_kernel<<<dim3((h / 4 + 255) / 256, T), 256, 0, ctx->stream>>>(s.y, s.pos_of_slot, w, residual, out, h, k);
     return runit_after_launch(ctx, "moe_grouped_combine");
 }
@@ -516,6 +829,8 @@ int32_t moe_topk(runit_ctx* ctx, const float* logits, uint32_t E, uint32_t k, in
 using namespace runit;
 
 extern "C" {
+
+int32_t runit_debug_timeline(void* dst) { return (int32_t)cudaMemcpyFromSymbol(dst, gg::pair::g_dbg, sizeof(long long) * 2 * 8 * 512); }
 
 size_t runit_moe_grouped_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
     return gg::carve(nullptr, T, h, ff, E, k).bytes;

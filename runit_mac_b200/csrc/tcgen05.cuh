@@ -1,8 +1,11 @@
 // Thin wrappers over the sm_100a tensor-core instructions (tcgen05) and tensor memory (TMEM) used by the
 // grouped expert GEMM: allocation, single-thread MMA issue with shared-memory operand descriptors, commit to an
-// mbarrier, and accumulator read-back.  cta_group::1 only (one CTA per tile).
+// mbarrier, and accumulator read-back; cta_group::1 (one CTA per tile) and cta_group::2 (a pair of CTAs of one
+// cluster shares a 256-row tile: the leader CTA issues the MMAs, each CTA holds half of both operands and its
+// 128 accumulator rows).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -86,9 +89,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // Wait bounded by time (2^31 SM cycles, about a second) and by the CTA's abort flag: returns false when the wait gave
 // up; the first thread to give up raises the flag so that every other role of the CTA leaves its loop too.  The
 // cycle counter is read only once per 256 failed polls (each poll may itself suspend the thread for a while).
-// Wait bounded by time (2^31 SM cycles, about a second) and by the CTA's abort flag: returns false when the wait gave
-// up; the first thread to give up raises the flag so that every other role of the CTA leaves its loop too.  The
-// cycle counter is read only once per 256 failed polls (each poll may itself suspend the thread for a while).
 __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
@@ -102,6 +102,76 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, v
             return false;
         }
     }
+}
+
+// ───────────────────────── CTA pairs (cta_group::2) ─────────────────────────
+// Allocation and release are executed by the same warp index in BOTH CTAs of the pair, with the same holder offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t holder, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// Issued by one thread of the leader CTA; both CTAs' shared-memory tiles sit at the offsets the descriptors name.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the mbarrier at this shared-memory offset in every CTA of `cta_mask` once the MMAs issued so far
+// have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask)
+                 : "memory");
+}
+// Address of a shared-memory location of CTA `rank` of the cluster, in the cluster-wide shared window.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+// Arrival on an mbarrier of another CTA of the cluster (address from cluster_map).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+// Same bounded wait, for barriers that threads of the peer CTA arrive on.  (Cluster-scope release/acquire
+// qualifiers on the arrive and the wait were measured to cost about 1500 cycles per remote arrival; the default
+// semantics, which the dequantisers' proxy fence completes, are the ones used.)
+__device__ __forceinline__ bool mbar_wait_timed_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > (1ll << 31)) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+// 2-D tiled load into this CTA's shared memory whose completion bytes are counted on an mbarrier of the pair's
+// leader CTA (`bar_cluster_addr` from cluster_map); no data is shared between the CTAs by this load.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+        : "memory");
 }
 
 }  // namespace runit
