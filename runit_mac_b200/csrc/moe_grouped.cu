@@ -51,7 +51,6 @@ struct Args {
     void* out;                    // bf16 [rows_padded][ld] (fused gate/up) or f32 [rows_padded][ld]
     uint32_t ld;
     int32_t* status;
-    int32_t dbg_ld;               // timing study: record a timeline when ld equals this
 };
 
 // ── dequantisation of one 64-element K chunk of one weight row into the swizzled A tile ──
@@ -104,6 +103,34 @@ __device__ __forceinline__ void dequant_chunk(const uint32_t* q, float s_lo, flo
                          "r"(v0), "r"(v1), "r"(v2), "r"(v3)
                          : "memory");
         }
+    }
+}
+
+// The same arithmetic with the 32 values of one nibble half (low nibbles: elements 0..31, high: 32..63 of the chunk)
+// packed as 16 bf16 pairs in registers, in K order: out[i] = (element 2i, element 2i+1).
+template <bool HI>
+__device__ __forceinline__ void dequant_half(const uint32_t* q, float sc, float mn, uint32_t (&out)[16]) {
+    const uint64_t neg_magic = packf(-kTwo23), nm = packf(-mn);
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint64_t P = pack2(q[2 * c], q[2 * c + 1]);
+        const uint64_t P12 = pack2(q[2 * c] >> 12, q[2 * c + 1] >> 12);
+        uint64_t o0, o1, o2, o3;
+        if (!HI) {
+            o0 = ffma2(fadd2(field_or_magic<0xFu << 0>(P), neg_magic), packf(sc), nm);
+            o1 = ffma2(fadd2(field_or_magic<0xFu << 8>(P), neg_magic), packf(sc * exp2_neg(8)), nm);
+            o2 = ffma2(fadd2(field_or_magic<0xFu << 16>(P), neg_magic), packf(sc * exp2_neg(16)), nm);
+            o3 = ffma2(fadd2(field_or_magic<0xFu << 12>(P12), neg_magic), packf(sc * exp2_neg(12)), nm);
+        } else {
+            o0 = ffma2(fadd2(field_or_magic<0xFu << 4>(P), neg_magic), packf(sc * exp2_neg(4)), nm);
+            o1 = ffma2(fadd2(field_or_magic<0xFu << 12>(P), neg_magic), packf(sc * exp2_neg(12)), nm);
+            o2 = ffma2(fadd2(field_or_magic<0xFu << 8>(P12), neg_magic), packf(sc * exp2_neg(8)), nm);
+            o3 = ffma2(fadd2(field_or_magic<0xFu << 16>(P12), neg_magic), packf(sc * exp2_neg(16)), nm);
+        }
+        out[4 * c + 0] = bf16x2(lo_f(o0), lo_f(o1));
+        out[4 * c + 1] = bf16x2(lo_f(o2), lo_f(o3));
+        out[4 * c + 2] = bf16x2(hi_f(o0), hi_f(o1));
+        out[4 * c + 3] = bf16x2(hi_f(o2), hi_f(o3));
     }
 }
 
@@ -314,36 +341,44 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
 
 // ───────────────────────── CTA-pair kernel (cta_group::2) ─────────────────────────
 // Two CTAs of one cluster share a work item of 256 weight rows x up to 256 token slots.  Each CTA dequantises 128
-// of the rows and loads half of the token tile; the leader CTA issues M = 256 MMAs that read both CTAs' shared
-// memory and write 128 accumulator rows into each CTA's tensor memory.  Against the single-CTA kernel every
-// dequantised weight serves twice as many tokens and every loaded token row twice as many weight rows.
-//   * Q4_K rows arrive by TMA (box 128 rows x 144 bytes = one superblock per row) into a 3-deep raw ring; the
-//     dequantisers read them from shared memory, so no thread holds a superblock in registers.
-//   * 16 dequantiser warps in two groups that take alternate 64-wide K chunks: while one group waits for its
-//     stage or for the barrier round trip, the other one computes.
+// of the rows and loads half of the token tile; the leader CTA issues M = 256 MMAs that write 128 accumulator rows
+// into each CTA's tensor memory.  What shaped it (all measured on B200):
+//   * one thread can issue a tcgen05.mma about every 110-130 cycles, whatever its size: only M = 256, N = 256 MMAs
+//     (128 cycles of tensor work) keep the pipe busy, and barrier waits, the fence and the commits are all paid by
+//     that same thread, so a pipeline step covers 128 K (8 MMAs) rather than 64;
+//   * with the weight operand in shared memory the dequantisers' stores, the TMA writes and the MMAs' operand reads
+//     need more than the 128 B/clk an SM's shared memory delivers: the dequantiser warps write their bf16 rows
+//     straight into tensor memory (tcgen05.st) and the MMA takes A from there; shared memory carries the token
+//     tiles and the raw superblocks only;
+//   * the commit -> refill -> arrive round trip between the two CTAs costs about 2400 cycles of signalling: 4
+//     weight stages (64 tensor-memory columns each) and 5 token-tile stages (32 KiB each) cover it;
+//   * Q4_K rows arrive by TMA (box 128 rows x 144 bytes = one superblock per row) into a 3-deep raw ring, issued
+//     by a warp of their own so that they never queue behind the token-tile loads;
+//   * 16 dequantiser warps in two groups, each taking one of the two 64-wide chunks of a step;
 //   * fused gate/up: the CTA's 128 tile rows are 64 gate rows followed by the 64 up rows of the same
-//     intermediate indices; the epilogue warps of the up half hand their values to the gate half through shared
-//     memory.
-// Barriers: full[s] and acc_empty[b] live in the leader and also take arrivals from the peer (cluster-scope);
-// empty[s] and acc_full[b] are signalled in both CTAs at once by the leader's tcgen05.commit.
+//     intermediate indices; gate and up warps of the epilogue swap half of their columns through shared memory, so
+//     all four warps compute, and the bf16 results leave through a shared-memory transpose as 16-byte stores
+//     (two-byte stores cost 60 cycles each);
+//   * one 256-column accumulator (the other 256 columns hold the weight stages): the epilogue of an item is not
+//     overlapped with the MMAs of the next, but both rings refill during it.
+// Barriers: a_full[s], b_full[s] and acc_empty live in the leader and also take arrivals from the peer;
+// a_empty[s], b_empty[s] and acc_full are signalled in both CTAs at once by the leader's tcgen05.commit.
 namespace pair {
-
-__device__ long long g_dbg[2 * 8 * 512];
-#define GG_DBG(slot, step) do { if (a.status == nullptr) {} if (dbg_on && blockIdx.x < 2 && (step) < 512) g_dbg[(blockIdx.x * 8 + (slot)) * 512 + (step)] = clock64(); } while (0)
 
 constexpr int kThreads = 736;              // 23 warps: token-tile producer, MMA, 4 epilogue, 16 dequantisers, raw producer
 constexpr int kRawWarp = 22;
 constexpr int kDeqWarp0 = 6, kGroupWarps = 8;
-constexpr int kNS = 5;                     // A/B stages
+constexpr int kNB = 5;                     // token-tile stages (shared memory), each two 64-wide K chunks = 32 KiB
+constexpr int kNA = 4;                     // weight stages (tensor memory), each two K chunks = 64 columns
 constexpr int kNR = 3;                     // raw superblock ring
-constexpr int kStage = 2 * kTileBytes;     // A tile + token tile
+constexpr int kStageB = 2 * kTileBytes;
 constexpr int kRawBytes = 128 * 144;
-constexpr int kXchgBytes = 2 * 32 * 33 * 4;
-constexpr int kOffRaw = kNS * kStage;
+constexpr int kXchgBytes = 2 * 2 * 32 * 17 * 4;
+constexpr int kOffRaw = kNB * kStageB;
 constexpr int kOffXchg = kOffRaw + kNR * kRawBytes;
 constexpr int kOffCtrl = kOffXchg + kXchgBytes;
-constexpr int kSmem = kOffCtrl + 256 + 1024;
-constexpr int kTmemCols = 512, kAccCols = 256;
+constexpr int kSmem = kOffCtrl + 512 + 1024;
+constexpr int kTmemCols = 512, kACol0 = 256;
 constexpr int kTokPair = 256;
 
 template <bool DUAL>
@@ -354,8 +389,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_p = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t ctrl = base + kOffCtrl;
-    const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * kNS, bar_rawf = bar_empty + 8 * kNS, bar_rawe = bar_rawf + 8 * kNR,
-                   bar_accf = bar_rawe + 8 * kNR, bar_acce = bar_accf + 16, holder = bar_acce + 16;
+    const uint32_t bar_bfull = ctrl, bar_bempty = bar_bfull + 8 * kNB, bar_afull = bar_bempty + 8 * kNB,
+                   bar_aempty = bar_afull + 8 * kNA, bar_rawf = bar_aempty + 8 * kNA, bar_rawe = bar_rawf + 8 * kNR,
+                   bar_accf = bar_rawe + 8 * kNR, bar_acce = bar_accf + 8, holder = bar_acce + 8;
     volatile uint32_t* holder_p = reinterpret_cast<volatile uint32_t*>(base_p + kOffCtrl + (holder - ctrl));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_p + kOffCtrl + (holder - ctrl) + 4);
     float* xchg = reinterpret_cast<float*>(base_p + kOffXchg);
@@ -364,18 +400,20 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     const uint32_t rank = cluster_ctarank();
     const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     if (tid == 0) {
-        for (int s = 0; s < kNS; s++) {
-            mbar_init(bar_full + 8 * s, 2 * kGroupWarps + 1);   // both CTAs' dequantiser group + the leader's expect_tx
-            mbar_init(bar_empty + 8 * s, 1);
+        for (int s = 0; s < kNB; s++) {
+            mbar_init(bar_bfull + 8 * s, 1);                    // the leader's expect_tx; bytes from both CTAs' loads
+            mbar_init(bar_bempty + 8 * s, 1);
+        }
+        for (int s = 0; s < kNA; s++) {
+            mbar_init(bar_afull + 8 * s, 4 * kGroupWarps);      // both dequantiser groups of each CTA (one K chunk each)
+            mbar_init(bar_aempty + 8 * s, 1);
         }
         for (int u = 0; u < kNR; u++) {
             mbar_init(bar_rawf + 8 * u, 1);
             mbar_init(bar_rawe + 8 * u, 2 * kGroupWarps);
         }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(bar_accf + 8 * b, 1);
-            mbar_init(bar_acce + 8 * b, 8);                      // 4 epilogue warps of each CTA
-        }
+        mbar_init(bar_accf, 1);
+        mbar_init(bar_acce, 8);                                 // 4 epilogue warps of each CTA
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -388,17 +426,17 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     cluster_sync();
     tc_fence_after_sync();
     const uint32_t tmem_base = *holder_p;
-    const bool dbg_on = a.ld == (uint32_t)a.dbg_ld || (a.dbg_ld < 0 && a.ld == 768);
 
     const uint32_t nb = DUAL ? a.rows / 128 : a.rows / 256;
     const uint32_t n_items = (uint32_t)(*a.n_tok_tiles) * nb;
     const uint32_t units = a.K / 256;
-    const uint32_t leader_full = cluster_map(bar_full, 0), leader_acce = cluster_map(bar_acce, 0);
+    const uint32_t leader_bfull = cluster_map(bar_bfull, 0), leader_afull = cluster_map(bar_afull, 0),
+                   leader_acce = cluster_map(bar_acce, 0);
 
     auto tile_cols = [&](int32_t nvalid) -> uint32_t { return nvalid <= 32 ? 32u : (uint32_t)((nvalid + 31) & ~31); };
 
     if (warp == 0) {
-        // ───────── TMA producer: the token tile of every stage ─────────
+        // ───────── TMA producer: the token tile of every step (128 K = two 64-wide swizzled sub-tiles) ─────────
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
@@ -406,13 +444,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                 const uint32_t tt = item / nb;
                 const uint32_t ncols = tile_cols(a.tile_nvalid[tt]);
                 const int32_t row_b = a.tile_row0[tt] + (int32_t)(rank * (ncols / 2));
-                for (uint32_t kc = 0; kc < units * 4; kc++, it++) {
-                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
-                    if (!mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
-                    GG_DBG(1, it);
-                    if (a.dbg_ld < 0 && ((-a.dbg_ld) & 1)) { if (rank == 0) mbar_arrive(bar_full + 8 * s); continue; }
-                    if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kTileBytes);
-                    tma_load_2d_pair(base + s * kStage + kTileBytes, &map_b, (int32_t)(kc * 128), row_b, leader_full + 8 * s);
+                for (uint32_t st = 0; st < units * 2; st++, it++) {
+                    const uint32_t s = it % kNB, ph = (it / kNB) & 1;
+                    if (!mbar_wait_timed(bar_bempty + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(bar_bfull + 8 * s, 2 * kStageB);
+                    tma_load_2d_pair(base + s * kStageB, &map_b, (int32_t)(st * 256), row_b, leader_bfull + 8 * s);
+                    tma_load_2d_pair(base + s * kStageB + kTileBytes, &map_b, (int32_t)(st * 256 + 128), row_b, leader_bfull + 8 * s);
                 }
             }
         }
@@ -428,8 +465,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                     const uint32_t ur = uc % kNR;
                     if (!mbar_wait_timed(bar_rawe + 8 * ur, ((uc / kNR) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t dst = base + kOffRaw + ur * kRawBytes;
-                    GG_DBG(0, uc);
-                    if (a.dbg_ld < 0 && ((-a.dbg_ld) & 4)) { mbar_arrive(bar_rawf + 8 * ur); continue; }
                     mbar_expect_tx(bar_rawf + 8 * ur, kRawBytes);
                     if (DUAL) {
                         const int32_t row = (int32_t)(e * a.rows + rb * 128 + rank * 64);
@@ -448,23 +483,24 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
             bool ok = true;
             for (uint32_t item = pair_id; item < n_items && ok && !*abort_flag; item += n_pairs, n++) {
                 const uint32_t idesc = umma_idesc_bf16(256, tile_cols(a.tile_nvalid[item / nb]));
-                const uint32_t b = n & 1;
-                if (!mbar_wait_timed_cluster(bar_acce + 8 * b, ((n >> 1) & 1) ^ 1, abort_flag)) break;
-                tc_fence_after_sync();
-                const uint32_t d_addr = tmem_base + b * kAccCols;
-                for (uint32_t kc = 0; kc < units * 4; kc++, it++) {
-                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
-                    if (!mbar_wait_timed_cluster(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait_timed_cluster(bar_acce, (n & 1) ^ 1, abort_flag)) break;   // the epilogue has drained the accumulator
+                for (uint32_t st = 0; st < units * 2; st++, it++) {
+                    const uint32_t sa = it % kNA, pa = (it / kNA) & 1, sb = it % kNB, pb = (it / kNB) & 1;
+                    if (!mbar_wait_timed_cluster(bar_afull + 8 * sa, pa, abort_flag) ||
+                        !mbar_wait_timed_cluster(bar_bfull + 8 * sb, pb, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    GG_DBG(2, it);
-                    const uint32_t sb = base + s * kStage;
-                    const uint64_t da = umma_desc_sw128(sb), db = umma_desc_sw128(sb + kTileBytes);
+                    const uint32_t at = tmem_base + kACol0 + 64 * sa;
 #pragma unroll
-                    for (uint32_t k4 = 0; k4 < 4; k4++) { if (a.dbg_ld < 0 && ((-a.dbg_ld) & 8)) break; umma_bf16_pair(d_addr, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0); }
-                    umma_commit_pair(bar_empty + 8 * s, 3);
-                    GG_DBG(3, it);
+                    for (uint32_t c = 0; c < 2; c++) {
+                        const uint64_t db = umma_desc_sw128(base + sb * kStageB + c * kTileBytes);
+#pragma unroll
+                        for (uint32_t k4 = 0; k4 < 4; k4++)
+                            umma_bf16_pair_ts(tmem_base, at + 32 * c + 8 * k4, db + 2 * k4, idesc, (st | c | k4) != 0);
+                    }
+                    umma_commit_pair(bar_aempty + 8 * sa, 3);
+                    umma_commit_pair(bar_bempty + 8 * sb, 3);
                 }
-                if (ok) umma_commit_pair(bar_accf + 8 * b, 3);
+                if (ok) umma_commit_pair(bar_accf, 3);
             }
         }
     } else if (warp < kDeqWarp0) {
@@ -478,37 +514,58 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
             const uint32_t tt = item / nb, rb = item % nb;
             const int32_t nvalid = a.tile_nvalid[tt];
             const size_t row0 = (size_t)a.tile_row0[tt];
-            const uint32_t b = n & 1;
             if (warp == kEpiWarp0 && lane == 0)
-                *go = (mbar_wait_timed(bar_accf + 8 * b, (n >> 1) & 1, abort_flag) && !*abort_flag) ? 1 : 0;
+                *go = (mbar_wait_timed(bar_accf, n & 1, abort_flag) && !*abort_flag) ? 1 : 0;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             const int verdict = *go;
             asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone has read it before the next item overwrites it
             if (!verdict) break;
             tc_fence_after_sync();
-            const uint32_t taddr0 = tmem_base + ((quarter * 32) << 16) + b * kAccCols;
+            const uint32_t taddr0 = tmem_base + ((quarter * 32) << 16);
 #pragma unroll 1
             for (int cg = 0; cg * 32 < nvalid; cg++) {
                 uint32_t v[32];
                 tmem_ld32(taddr0 + cg * 32, v);
                 tmem_ld_wait();
                 if (DUAL) {
-                    // tile rows 0..63 = gate (quarters 0, 1), 64..127 = up of the same intermediate indices (quarters 2, 3)
-                    float* x = xchg + (quarter & 1) * (32 * 33) + lane * 33;
-                    if (quarter >= 2) {
+                    // tile rows 0..63 = gate (quarters 0, 1), 64..127 = up of the same intermediate indices (quarters
+                    // 2, 3).  Each side hands half of its 32 columns to the other: the gate warp finishes tokens
+                    // 0..15 of the group, the up warp tokens 16..31.
+                    float* xg = xchg + (quarter & 1) * (2 * 32 * 17) + lane * 17;   // gate values 16..31 of my row
+                    float* xu = xg + 32 * 17;                                       // up values 0..15 of my row
+                    const bool is_gate = quarter < 2;
+                    if (is_gate) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) x[i] = __uint_as_float(v[i]);
+                        for (int i = 0; i < 16; i++) xg[i] = __uint_as_float(v[16 + i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) xu[i] = __uint_as_float(v[i]);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (quarter < 2) {
-                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
-                        const uint32_t col = rb * 128 + rank * 64 + quarter * 32 + lane;
+                    float gv[16], uv[16];
 #pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            if (cg * 32 + i < nvalid)
-                                out[(row0 + cg * 32 + i) * a.ld + col] = __float2bfloat16_rn(silu_fast(__uint_as_float(v[i])) * x[i]);
+                    for (int i = 0; i < 16; i++) {
+                        gv[i] = is_gate ? __uint_as_float(v[i]) : xg[i];
+                        uv[i] = is_gate ? xu[i] : __uint_as_float(v[16 + i]);
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");   // the exchange area may be rewritten
+                    // 16 tokens x 32 intermediate indices of bf16 go through the warp's own (now idle) exchange array so
+                    // that every lane stores 16 bytes: 2 stores per lane instead of 16 two-byte ones.
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
+                    const uint32_t col0 = rb * 128 + rank * 64 + (quarter & 1) * 32;
+                    const int tok0 = cg * 32 + (is_gate ? 0 : 16);
+                    uint8_t* stage = reinterpret_cast<uint8_t*>(is_gate ? (xg - lane * 17) : (xu - lane * 17));
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        *reinterpret_cast<__nv_bfloat16*>(stage + i * 64 + lane * 2) = __float2bfloat16_rn(silu_fast(gv[i]) * uv[i]);
+                    __syncwarp();
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        const int tk = (lane >> 2) + 8 * hh, ch = lane & 3;
+                        const uint4 pk = *reinterpret_cast<const uint4*>(stage + tk * 64 + ch * 16);
+                        if (tok0 + tk < nvalid) *reinterpret_cast<uint4*>(out + (row0 + tok0 + tk) * a.ld + col0 + 8 * ch) = pk;
+                    }
+                    __syncwarp();
                 } else {
                     float* out = reinterpret_cast<float*>(a.out);
                     const uint32_t col = rb * 256 + rank * 128 + quarter * 32 + lane;
@@ -520,22 +577,23 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-                if (rank == 0) mbar_arrive(bar_acce + 8 * b);
-                else mbar_arrive_cluster(leader_acce + 8 * b);
+                if (rank == 0) mbar_arrive(bar_acce);
+                else mbar_arrive_cluster(leader_acce);
             }
         }
     } else if (warp < kRawWarp) {
-        // ───────── dequantisers: raw ring -> bf16 swizzled A tile; group g takes the chunks j with j % 2 == g ─────────
-        const uint32_t g = (warp - kDeqWarp0) / kGroupWarps;
-        const uint32_t t = ((warp - kDeqWarp0) % kGroupWarps) * 32 + lane;
-        const uint32_t r = t & 127, part = t >> 7, rx = r & 7;
+        // ───────── dequantisers: raw ring -> bf16 rows in tensor memory.  Group g takes chunk g of every step (the
+        //            chunks j of a unit with j % 2 == g).  A warp may only write the tensor-memory lanes
+        //            32 * (warp % 4) .. + 31: those are its rows. ─────────
+        const uint32_t dw = warp - kDeqWarp0;
+        const uint32_t g = dw / kGroupWarps, part = (dw % kGroupWarps) / 4;   // part 0: low nibbles (K 0..31 of the chunk), 1: high
+        const uint32_t quarter = warp & 3, r = quarter * 32 + lane;
         uint32_t uc = 0;
         bool ok = true;
         for (uint32_t item = pair_id; item < n_items && ok && !*abort_flag; item += n_pairs) {
             for (uint32_t u = 0; u < units && ok; u++, uc++) {
                 const uint32_t ur = uc % kNR;
                 if (!mbar_wait_timed(bar_rawf + 8 * ur, (uc / kNR) & 1, abort_flag)) { ok = false; break; }
-                if (t == 0 && g == 0) GG_DBG(4, uc);
                 const uint32_t raw_row = base + kOffRaw + ur * kRawBytes + r * 144;
                 uint32_t h0, h1, h2, h3;
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(raw_row) : "memory");
@@ -543,31 +601,28 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                 const Q4KScales sc = q4k_unpack_scales(h1, h2, h3);
 #pragma unroll
                 for (int jj = 0; jj < 2; jj++) {
-                    const uint32_t j = 2 * jj + g;
-                    const uint32_t it = uc * 4 + j;
-                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
+                    const uint32_t j = 2 * jj + g;               // chunk of the unit; step 2 * unit + jj holds chunks 2jj, 2jj + 1
+                    const uint32_t it = uc * 2 + jj;
+                    const uint32_t s = it % kNA, ph = (it / kNA) & 1;
                     uint32_t q[8];
                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]) : "r"(raw_row + 16 + 32 * j) : "memory");
                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]) : "r"(raw_row + 32 + 32 * j) : "memory");
                     const uint32_t sh = 8 * j;
-                    const float s_lo = dd * (float)((sc.sl >> sh) & 0xFFu), m_lo = dmin * (float)((sc.ml >> sh) & 0xFFu);
-                    const float s_hi = dd * (float)((sc.sh >> sh) & 0xFFu), m_hi = dmin * (float)((sc.mh >> sh) & 0xFFu);
+                    uint32_t out[16];
+                    if (part == 0) dequant_half<false>(q, dd * (float)((sc.sl >> sh) & 0xFFu), dmin * (float)((sc.ml >> sh) & 0xFFu), out);
+                    else dequant_half<true>(q, dd * (float)((sc.sh >> sh) & 0xFFu), dmin * (float)((sc.mh >> sh) & 0xFFu), out);
                     uint32_t got = 1;
-                    if (lane == 0) got = mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag);
+                    if (lane == 0) got = mbar_wait_timed(bar_aempty + 8 * s, ph ^ 1, abort_flag);
                     got = __shfl_sync(0xffffffffu, got, 0);
                     if (!got) { ok = false; break; }
-                    if (t == 0) GG_DBG(5, it);
-                    const uint32_t row_addr = base + s * kStage + r * 128;
-                    if (!(a.dbg_ld < 0 && ((-a.dbg_ld) & 2))) {
-                    if (part == 0) dequant_chunk<true, false>(q, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
-                    else dequant_chunk<false, true>(q, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
-                    }
-                    fence_proxy_async();
+                    tc_fence_after_sync();
+                    tmem_st16(tmem_base + ((quarter * 32) << 16) + kACol0 + 64 * s + 32 * g + 16 * part, out);
+                    tmem_st_wait();
+                    tc_fence_before_sync();
                     __syncwarp();
-                    if (t == 0) GG_DBG(6, it);
                     if (lane == 0) {
-                        if (rank == 0) mbar_arrive(bar_full + 8 * s);
-                        else mbar_arrive_cluster(leader_full + 8 * s);
+                        if (rank == 0) mbar_arrive(bar_afull + 8 * s);
+                        else mbar_arrive_cluster(leader_afull + 8 * s);
                     }
                 }
                 __syncwarp();
@@ -779,7 +834,7 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
                             const float* x, const int32_t* idx, const float* w, const float* residual, float* out,
                             uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
     const uint32_t S = T * k;
-    const bool single = ctx->tune.moe_variant > 0 && (ctx->tune.moe_variant & 15) == 1;
+    const bool single = ctx->tune.moe_variant == 1;
     RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(s.counts, 0, 4 * 256, ctx->stream));
     count_kernel<<<(S + 4095) / 4096, 256, 0, ctx->stream>>>(idx, S, E, s.counts, s.pos_of_slot);
     int32_t st = runit_after_launch(ctx, "moe_grouped_count");
@@ -794,11 +849,11 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
     Args a1{};
     a1.w0 = (const uint8_t*)gate; a1.w1 = (const uint8_t*)up; a1.rows = ff; a1.K = h; a1.nb = ff / kRows;
     a1.tile_expert = s.tile_expert; a1.tile_nvalid = s.tile_nvalid; a1.tile_row0 = s.tile_row0; a1.n_tok_tiles = s.n_tok_tiles;
-    a1.out = s.act; a1.ld = ff; a1.status = ctx->d_status; a1.dbg_ld = ctx->tune.moe_variant < 0 ? ctx->tune.moe_variant : ctx->tune.moe_variant >> 4;
+    a1.out = s.act; a1.ld = ff; a1.status = ctx->d_status;
     Args a2{};
     a2.w0 = (const uint8_t*)down; a2.w1 = nullptr; a2.rows = h; a2.K = ff; a2.nb = h / kRows;
     a2.tile_expert = s.tile_expert; a2.tile_nvalid = s.tile_nvalid; a2.tile_row0 = s.tile_row0; a2.n_tok_tiles = s.n_tok_tiles;
-    a2.out = s.y; a2.ld = h; a2.status = ctx->d_status; a2.dbg_ld = ctx->tune.moe_variant < 0 ? ctx->tune.moe_variant : ctx->tune.moe_variant >> 4;
+    a2.out = s.y; a2.ld = h; a2.status = ctx->d_status;
     if (single) {
         if ((st = launch_gemm<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, s.max_tiles * a1.nb)) != RUNIT_OK) return st;
         if ((st = launch_gemm<false>(ctx, "moe_grouped_down", a2, s.act, rows, s.max_tiles * a2.nb)) != RUNIT_OK) return st;
@@ -829,8 +884,6 @@ int32_t moe_topk(runit_ctx* ctx, const float* logits, uint32_t E, uint32_t k, in
 using namespace runit;
 
 extern "C" {
-
-int32_t runit_debug_timeline(void* dst) { return (int32_t)cudaMemcpyFromSymbol(dst, gg::pair::g_dbg, sizeof(long long) * 2 * 8 * 512); }
 
 size_t runit_moe_grouped_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
     return gg::carve(nullptr, T, h, ff, E, k).bytes;

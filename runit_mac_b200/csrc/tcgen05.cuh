@@ -75,26 +75,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ── mbarrier helpers for the warp-specialised pipeline ──
+constexpr uint32_t kSuspendHintNs = 200000;   // upper bound of one try_wait; the timed loops re-check abort and clock between tries
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+    // The suspend-time hint (ns) lets the hardware park the thread until the phase completes; without it the
+    // instruction returns almost at once and a waiting role burns the issue slots of the warps that do the work.
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(done)
-                 : "r"(bar), "r"(parity)
+                 : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
                  : "memory");
     return done != 0;
 }
 // Wait bounded by time (2^31 SM cycles, about a second) and by the CTA's abort flag: returns false when the wait gave
 // up; the first thread to give up raises the flag so that every other role of the CTA leaves its loop too.  The
-// cycle counter is read only once per 256 failed polls (each poll may itself suspend the thread for a while).
+// cycle counter is read once per 8 failed polls (each poll suspends the thread for up to kSuspendHintNs).
 __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
-        for (int i = 0; i < 256; i++)
+        for (int i = 0; i < 8; i++)
             if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > (1ll << 31)) {
@@ -130,6 +133,26 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                  ::"r"(bar), "h"(cta_mask)
                  : "memory");
 }
+// Same with the A operand in tensor memory (128 lanes per CTA, 32-bit column c of the operand = K elements 2c, 2c+1).
+__device__ __forceinline__ void umma_bf16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Registers -> tensor memory: 16 consecutive columns of this warp's 32 lanes (whole warp; the lane quarter rule of
+// tmem_ld32 applies).  tmem_st_wait makes the stores of the executing thread complete.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // Address of a shared-memory location of CTA `rank` of the cluster, in the cluster-wide shared window.
 __device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
     uint32_t r;
@@ -142,9 +165,9 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
     uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(done)
-                 : "r"(bar), "r"(parity)
+                 : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
                  : "memory");
     return done != 0;
 }
@@ -156,7 +179,7 @@ __device__ __forceinline__ bool mbar_wait_timed_cluster(uint32_t bar, uint32_t p
     const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
-        for (int i = 0; i < 256; i++)
+        for (int i = 0; i < 8; i++)
             if (mbar_try_cluster(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > (1ll << 31)) {
