@@ -290,7 +290,9 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
     nbytes = R.moe_grouped_scratch_bytes(ctx, T, h, ff, E, k)
     scratch = ctx.new_buffer(nbytes)
     cnt = torch.bincount(idx.flatten().long(), minlength=E)
-    tiles = int(((cnt + 127) // 128).sum().item())
+    tiles = int(((cnt + 255) // 256).sum().item())                       # 256-slot tiles of the CTA-pair kernel
+    full, rest = cnt // 256, cnt % 256
+    issued_cols = int((full * 256 + ((rest + 31) // 32) * 32).sum().item())   # MMA N is the tile's slots rounded up to 32
 
     def step():
         R.moe_experts_grouped_q4k_bf16(ctx, gate, up, down, x, idx, w, None, out, scratch, nbytes, T, h, ff, E, k)
@@ -307,7 +309,7 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
     ctx.flush()
     ms = e0.elapsed_time(e1) / reps
     flops = 2.0 * T * k * 3 * h * ff                  # useful multiply-adds of the three expert products
-    padded = 2.0 * tiles * 128 * 3 * h * ff           # what the 128-slot tiles issue
+    padded = 2.0 * issued_cols * 3 * h * ff            # what the MMAs issue
     peak, kind = measured_tensor_peak()
     return {"workload": "qwen3-moe-shaped MoE block, %d tokens, %d experts top-%d, hidden %d, intermediate %d, Q4_K -> bf16 tiles, "
                         "Zipf(1.1) routing" % (T, E, k, h, ff),
@@ -372,7 +374,27 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args):
         moe["T%d" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3), "distinct_experts_last_layer": U,
                           "algorithmic_gbs": alg / (ms * 1e-3) / 1e9}
         g.destroy()
+    # the same layer at 256 tokens through the tensor-core block (bf16 operands)
+    T = 256
+    x = torch.randn(T, h, device="cuda")
+    o = torch.empty(T, h, device="cuda")
+    nbg = R.moe_grouped_scratch_bytes(ctx, T, h, ff, E, k)
+    scratch = ctx.new_buffer(nbg)
+    eg, ed = E * ff * rb(h), E * h * rb(ff)
+    torch.cuda.synchronize()
+
+    def run_layers_tc():
+        for l in range(L):
+            R.moe_layer_q4k_bf16(ctx, dev["router"].ptr + l * E * h * 4, dev["gate"].ptr + l * eg, dev["up"].ptr + l * eg,
+                                 dev["down"].ptr + l * ed, x, None, o, None, None, scratch, nbg, T, h, ff, E, k, 0)
+    run_layers_tc()
+    ctx.flush()
+    ms = timed(run_layers_tc, 5) / L
+    moe["T256_tensor_cores_bf16"] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
     out["moe_layer_olmoe_q4k"] = moe
+    scratch.free()
+    # Qwen3-MoE-shaped batched block (4096 tokens, 128 experts, Zipf routing) on the tensor cores
+    out["moe_block_qwen3_shape_bf16"] = run_block(R, ctx, torch, stream, T=4096, reps=10)
     # full OLMoE-shaped greedy decode: 128-token prompt, 64 greedy steps, f16 KV, no host round trips
     cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=50304, n_experts=E, top_k=k, ff=ff,
                      max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)

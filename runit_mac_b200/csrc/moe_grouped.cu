@@ -690,39 +690,56 @@ __global__ void __launch_bounds__(1024) place_kernel(const int32_t* __restrict__
         tile_nvalid[tile0 + i] = min(tile_tok, cnt - i * tile_tok);
         tile_row0[tile0 + i] = off + i * tile_tok;
     }
+    // every thread takes 4 consecutive slots per round, so a round covers 4096 slots in slot order
     int running = 0;
-    for (uint32_t s0 = 0; s0 < S; s0 += 1024) {
-        const uint32_t s = s0 + tid;
-        const bool hit = s < S && idx[s] == (int32_t)e;
-        const uint32_t ballot = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) s_warp[warp] = __popc(ballot);
+    for (uint32_t s0 = 0; s0 < S; s0 += 4096) {
+        const uint32_t s = s0 + 4 * tid;
+        bool hit[4];
+        int mine = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            hit[i] = s + i < S && idx[s + i] == (int32_t)e;
+            mine += hit[i];
+        }
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((int)lane >= o) incl += t;
+        }
+        if (lane == 31) s_warp[warp] = incl;
         __syncthreads();
         if (warp == 0) {
-            int v = s_warp[lane], incl = v;
+            int v = s_warp[lane], wi = v;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                if ((int)lane >= o) incl += t;
+                const int t = __shfl_up_sync(0xffffffffu, wi, o);
+                if ((int)lane >= o) wi += t;
             }
-            s_warp[lane] = incl - v;   // exclusive prefix
-            if (lane == 31) s_chunk = incl;
+            s_warp[lane] = wi - v;   // exclusive prefix over the warps
+            if (lane == 31) s_chunk = wi;
         }
         __syncthreads();
-        if (hit) pos_of_slot[s] = off + running + s_warp[warp] + __popc(ballot & ((1u << lane) - 1u));
+        int p = off + running + s_warp[warp] + incl - mine;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (hit[i]) pos_of_slot[s + i] = p++;
         running += s_chunk;
         __syncthreads();
     }
 }
 
-// xperm[pos(s)][:] = bf16(x[s / k][:])
+// xperm[pos(s)][:] = bf16(x[s / k][:]); one warp per slot, 8 slots per CTA.
 __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ x, const int32_t* __restrict__ pos_of_slot,
-                                                      __nv_bfloat16* __restrict__ xperm, uint32_t h, uint32_t k) {
-    const uint32_t s = blockIdx.x;
+                                                      __nv_bfloat16* __restrict__ xperm, uint32_t S, uint32_t h, uint32_t k) {
+    const uint32_t s = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (s >= S) return;
     const int32_t pos = pos_of_slot[s];
     if (pos < 0) return;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)(s / k) * h);
     uint4* dst = reinterpret_cast<uint4*>(xperm + (size_t)pos * h);
-    for (uint32_t c = threadIdx.x; c < h / 8; c += 256) {
+#pragma unroll 4
+    for (uint32_t c = lane; c < h / 8; c += 32) {
         const float4 a0 = __ldg(src + 2 * c), a1 = __ldg(src + 2 * c + 1);
         uint4 o;
         o.x = bf16x2(a0.x, a0.y); o.y = bf16x2(a0.z, a0.w); o.z = bf16x2(a1.x, a1.y); o.w = bf16x2(a1.z, a1.w);
@@ -842,7 +859,7 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
     place_kernel<<<E, 1024, 0, ctx->stream>>>(idx, S, E, s.counts, single ? kTok : pair::kTokPair, s.pos_of_slot, s.tile_expert,
                                               s.tile_nvalid, s.tile_row0, s.n_tok_tiles);
     if ((st = runit_after_launch(ctx, "moe_grouped_place")) != RUNIT_OK) return st;
-    gather_kernel<<<S, 256, 0, ctx->stream>>>(x, s.pos_of_slot, s.xperm, h, k);
+    gather_kernel<<<(S + 7) / 8, 256, 0, ctx->stream>>>(x, s.pos_of_slot, s.xperm, S, h, k);
     if ((st = runit_after_launch(ctx, "moe_grouped_gather")) != RUNIT_OK) return st;
 
     const uint32_t rows = s.max_tiles * kTok + 256;

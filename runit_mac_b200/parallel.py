@@ -103,8 +103,10 @@ def ep_moe_forward(backend, dist, torch, x, n_experts: int, top_k: int, renorm: 
 class CudaBackend:
     """Arithmetic of the two schemes on the local GPU through librunit_cuda.so."""
 
-    def __init__(self, R, ctx, torch):
+    def __init__(self, R, ctx, torch, grouped_min_slots=1 << 30):
         self.R, self.ctx, self.torch = R, ctx, torch
+        self.grouped_min_slots = grouped_min_slots   # slot count from which the tensor-core block serves the experts
+        self._scratch = self._ones = None
 
     # row-sharded GEMV
     def set_lm_head(self, fmt, w_local, rows_local, k):
@@ -131,8 +133,20 @@ class CudaBackend:
         return idx, w
 
     def experts(self, x_slots, local_expert):
+        """Slots received from all ranks -> expert outputs.  Few slots: grouped GEMV (f32).  grouped_min_slots or more:
+        the tensor-core block (bf16 operands) with one slot per "token" (k = 1, weight 1)."""
         t, n = self.torch, x_slots.shape[0]
         y = t.zeros(n, self.h, dtype=t.float32, device="cuda")
+        if n >= self.grouped_min_slots:
+            nbytes = self.R.moe_grouped_scratch_bytes(self.ctx, n, self.h, self.ff, self.n_local, 1)
+            if self._scratch is None or self._scratch.nbytes < nbytes:
+                self._scratch = self.ctx.new_buffer(nbytes)
+            if self._ones is None or self._ones.numel() < n:
+                self._ones = t.ones(n, dtype=t.float32, device="cuda")
+            self.R.moe_experts_grouped_q4k_bf16(self.ctx, self.gate, self.up, self.down, x_slots.contiguous(), local_expert.contiguous(),
+                                                self._ones, None, y, self._scratch, self._scratch.nbytes, n, self.h, self.ff,
+                                                self.n_local, 1)
+            return y
         act = t.empty(n, self.ff, dtype=t.float32, device="cuda")
         self.R.moe_experts_q4k(self.ctx, self.gate, self.up, self.down, x_slots, local_expert, y, act, n, self.h, self.ff, self.n_local)
         return y
@@ -197,4 +211,38 @@ def bench_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
         x = torch.randn(T, h, dtype=torch.float32, device="cuda")
         ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
         out["T%d_per_rank" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s_all_ranks": world * T / (ms * 1e-3)}
+    for b in (gate, up, down):
+        b.free()
+    out["qwen3_shape_prefill"] = bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world)
     return out
+
+
+def bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=5, T_total=4096):
+    """Qwen3-MoE-shaped batched block (hidden 2048, 128 experts, top-8, intermediate 768, Q4_K -> bf16 tensor-core
+    GEMMs), 4096 tokens in all (4096/G per rank), experts split 128/G per rank, Zipf(1.1) expert popularity,
+    fixed-capacity all-to-all dispatch and combine.  Reports the straggler's load beside the mean."""
+    E, h, ff, k = 128, 2048, 768, 8
+    n_local, T = E // world, T_total // world
+    rb = lambda kk: kk // 256 * 144
+    gate, up = ctx.new_buffer(n_local * ff * rb(h)), ctx.new_buffer(n_local * ff * rb(h))
+    down = ctx.new_buffer(n_local * h * rb(ff))
+    for i, (b, rows, kk) in enumerate(((gate, n_local * ff, h), (up, n_local * ff, h), (down, n_local * h, ff))):
+        R.fill_weights(ctx, 2, b, rows * (kk // 256), 177 + i + 10 * rank, 0.01)
+    g = torch.Generator(device="cuda").manual_seed(1 + rank)
+    p = 1.0 / torch.arange(1, E + 1, device="cuda", dtype=torch.float64) ** 1.1
+    idx = torch.multinomial((p / p.sum()).float().expand(T, E).contiguous(), k, replacement=False, generator=g).to(torch.int32)
+    w = torch.rand(T, k, device="cuda", generator=g)
+    x = torch.randn(T, h, device="cuda", generator=g)
+
+    class GivenRouting(CudaBackend):
+        def route(self, _x):
+            return idx, w
+    be = GivenRouting(R, ctx, torch, grouped_min_slots=256)
+    be.set_experts(None, gate, up, down, E, n_local, h, ff, k, False)
+    ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
+    mine = ((idx // n_local) == rank).sum().to(torch.float64)      # slots this rank SENDS to itself; the load is what it receives
+    recv = torch.bincount((idx // n_local).flatten().long(), minlength=world).to(torch.float64)
+    if world > 1:
+        dist.all_reduce(recv)
+    return {"ms_per_layer": ms, "tokens_per_s_all_ranks": T_total / (ms * 1e-3), "tokens_per_rank": T,
+            "slots_per_rank_max": float(recv.max().item()), "slots_per_rank_mean": float(recv.mean().item())}
