@@ -98,6 +98,51 @@ def ep_moe_forward(backend, dist, torch, x, n_experts: int, top_k: int, renorm: 
     return out + acc, idx, w
 
 
+def ep_moe_forward_counted(backend, dist, torch, x, n_experts: int, top_k: int, renorm: bool, world: int, rank: int,
+                           residual=None):
+    """The same block for prefill-sized batches: slots are sorted by destination rank and exchanged with their true
+    counts (one small all-to-all of counts and one host read of them per call), so no padding crosses NVLink and the
+    owner computes only real slots.  Returns (out [T, h], idx, w)."""
+    T, h = x.shape
+    idx, w = backend.route(x)
+    per_rank = n_experts // world
+    flat = idx.reshape(-1).to(torch.int64)
+    dest = expert_owner(flat, n_experts, world)
+    order = torch.argsort(dest, stable=True)                      # slots grouped by destination, slot order kept
+    send_counts = torch.bincount(dest, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    if world > 1:
+        dist.all_to_all_single(recv_counts, send_counts)
+    else:
+        recv_counts.copy_(send_counts)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()            # the one host synchronisation
+    tok = torch.arange(T * top_k, device=x.device) // top_k
+    send_x = x[tok[order]].contiguous()
+    send_e = (flat[order] - dest[order] * per_rank).to(torch.int32)
+    n_recv = int(sum(rc))
+    recv_x = torch.empty(n_recv, h, dtype=x.dtype, device=x.device)
+    recv_e = torch.empty(n_recv, dtype=torch.int32, device=x.device)
+    if world > 1:
+        dist.all_to_all_single(recv_x, send_x, output_split_sizes=rc, input_split_sizes=sc)
+        dist.all_to_all_single(recv_e, send_e, output_split_sizes=rc, input_split_sizes=sc)
+    else:
+        recv_x, recv_e = send_x, send_e
+    y = backend.experts(recv_x, recv_e) if n_recv else recv_x
+    back = torch.empty(T * top_k, h, dtype=x.dtype, device=x.device)
+    if world > 1:
+        dist.all_to_all_single(back, y.contiguous(), output_split_sizes=sc, input_split_sizes=rc)
+    else:
+        back = y
+    ys = torch.empty_like(back)
+    ys[order] = back                                               # back to slot order
+    ys = ys.reshape(T, top_k, h)
+    acc = torch.zeros(T, h, dtype=x.dtype, device=x.device)
+    for i in range(top_k):                                         # routing order
+        acc = acc + w[:, i:i + 1] * ys[:, i, :]
+    base = torch.zeros(T, h, dtype=x.dtype, device=x.device) if residual is None else residual
+    return base + acc, idx, w
+
+
 # ───────────────────────── GPU backend (C-ABI calls on torch tensors) ─────────────────────────
 
 class CudaBackend:
@@ -220,7 +265,7 @@ def bench_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
 def bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=5, T_total=4096):
     """Qwen3-MoE-shaped batched block (hidden 2048, 128 experts, top-8, intermediate 768, Q4_K -> bf16 tensor-core
     GEMMs), 4096 tokens in all (4096/G per rank), experts split 128/G per rank, Zipf(1.1) expert popularity,
-    fixed-capacity all-to-all dispatch and combine.  Reports the straggler's load beside the mean."""
+    count-exchanged all-to-all dispatch and combine.  Reports the straggler's load beside the mean."""
     E, h, ff, k = 128, 2048, 768, 8
     n_local, T = E // world, T_total // world
     rb = lambda kk: kk // 256 * 144
@@ -239,8 +284,7 @@ def bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, step
             return idx, w
     be = GivenRouting(R, ctx, torch, grouped_min_slots=256)
     be.set_experts(None, gate, up, down, E, n_local, h, ff, k, False)
-    ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
-    mine = ((idx // n_local) == rank).sum().to(torch.float64)      # slots this rank SENDS to itself; the load is what it receives
+    ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward_counted(be, dist, torch, x, E, k, False, world, rank), steps, world)
     recv = torch.bincount((idx // n_local).flatten().long(), minlength=world).to(torch.float64)
     if world > 1:
         dist.all_reduce(recv)

@@ -1,5 +1,5 @@
 """Host logic of the two multi-GPU schemes (row-sharded GEMV + all-gather; expert-parallel MoE with
-fixed-capacity all-to-all dispatch/combine) on CPU: two gloo ranks, arithmetic supplied by the oracle.
+fixed-capacity and count-exchanged all-to-all dispatch/combine) on CPU: two gloo ranks, arithmetic supplied by the oracle.
 Checks shard offsets, slot placement, the round trip through both all-to-alls and the weighted combine
 against the single-process oracle."""
 import os
@@ -77,7 +77,9 @@ def worker(rank, world, port, q):
         xs = torch.from_numpy(d["x"][rank * T:(rank + 1) * T])
         rs = torch.from_numpy(d["res"][rank * T:(rank + 1) * T])
         out, idx, w = P.ep_moe_forward(be, dist, torch, xs, E, K_TOP, False, world, rank, residual=rs)
-        q.put((rank, y.numpy(), out.numpy(), idx.numpy(), w.numpy()))
+        out2, idx2, _ = P.ep_moe_forward_counted(be, dist, torch, xs, E, K_TOP, False, world, rank, residual=rs)   # true counts
+        assert (idx2 == idx).all()
+        q.put((rank, y.numpy(), out.numpy(), idx.numpy(), w.numpy(), out2.numpy()))
     finally:
         dist.destroy_process_group()
 
@@ -113,6 +115,8 @@ def test_two_ranks_match_the_single_process_oracle(oracle):
     idx = np.concatenate([res[r][3] for r in range(world)])
     assert (idx == ridx).all()
     assert np.allclose(out, ref, rtol=1e-5, atol=1e-5 * np.abs(ref).max())
+    out2 = np.concatenate([res[r][5] for r in range(world)])      # the count-exchanged variant gives the same block
+    assert np.allclose(out2, ref, rtol=1e-5, atol=1e-5 * np.abs(ref).max())
 
 
 def test_shard_and_pack_helpers():
