@@ -172,6 +172,21 @@ int32_t runit_gemv_batched_f32(runit_ctx_t*, int32_t fmt, const void* weight, co
 int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
                                          void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,
                                          const void* bias_v, uint32_t q_dim, uint32_t kv_dim, uint32_t k);
+/* ── row-sharded GEMV with the all-gather fused into the epilogue (no twin: the reference is single-device,
+ *    crates/engine/src/server/mod.rs:20-30).  Rank `rank` of `world` (<= 8) owns rows [rank*n, (rank+1)*n), n =
+ *    rows_total/world, of the weight matrix (w_local: those n rows).  y_all: HOST array of `world` DEVICE pointers, entry p
+ *    = rank p's full-length f32 output vector as mapped into this process (peer memory for p != rank, e.g. from CUDA
+ *    virtual-memory or IPC mappings / torch symmetric memory).  Every result is stored into all of them by plain peer
+ *    stores.  The vectors are complete on every rank once all ranks have passed runit_peer_barrier. ── */
+int32_t runit_gemv_allgather_f32(runit_ctx_t*, int32_t fmt, const void* w_local, const void* x, void* const* y_all,
+                                 uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k);
+/* One-kernel barrier over peer memory.  signal_pads: HOST array of `world` DEVICE pointers, entry p = rank p's pad of at
+ * least `world` uint32 words (zero before the first use), as mapped into this process.  Announces `epoch` (> 0,
+ * strictly increasing from call to call) to every rank and waits until every rank has announced it; a rank that does
+ * not show up within about half a second makes the next runit_flush return RUNIT_ERR_TIMEOUT (the context stays
+ * usable). */
+int32_t runit_peer_barrier(runit_ctx_t*, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch);
+
 /* ── MoE block (no twin as one function; replaces the sequence crates/engine/src/forward.rs:1644-1679
  *    and the CPU routing forward.rs:2420-2448, without the per-layer host synchronisation) ── */
 /* logits_f32[T][E] = router_f32[E][h] . x_f32[T][h] */

@@ -26,6 +26,9 @@ struct GemvCall {
     // grouped (mixture-of-experts) launch: see GemvArgs
     const int32_t* grp_expert = nullptr;
     uint32_t grp_slots = 0, grp_experts = 0, grp_xdiv = 1;
+    // fused all-gather: the same output slice in the memory of the other GPUs
+    float* peer_y[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    uint32_t n_peer = 0;
 };
 
 static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
@@ -94,6 +97,15 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
     const uint32_t bpu = c.fmt == RUNIT_FMT_Q8_0 ? Traits<RUNIT_FMT_Q8_0>::BPU
                          : c.fmt == RUNIT_FMT_Q4_0 ? Traits<RUNIT_FMT_Q4_0>::BPU : Traits<RUNIT_FMT_Q4K>::BPU;
     a.n_units = (a.nb + bpu - 1) / bpu;
+    if (c.n_peer) {
+        RUNIT_REQUIRE(ctx, c.nseg == 1 && c.batch == 1 && !c.out_f16 && !c.dual && !c.grp_expert && c.n_peer <= 7,
+                      "%s: the fused all-gather takes one f32 segment, batch 1", nm);
+        for (uint32_t p = 0; p < c.n_peer; p++) {
+            RUNIT_REQUIRE(ctx, c.peer_y[p] && runit_aligned(c.peer_y[p], 4), "%s: null or misaligned peer output", nm);
+            a.peer_y[p] = c.peer_y[p];
+        }
+        a.n_peer = c.n_peer;
+    }
     a.status = ctx->d_status;
     a.n_tiles = tiles;
     // Tiled bulk loads (TMA) for the 4-bit formats: one tensor map per weight matrix.
@@ -333,6 +345,67 @@ int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight
         done += b;
     }
     return RUNIT_OK;
+}
+
+
+// ───────────────────────── row-sharded GEMV with the all-gather in the epilogue ─────────────────────────
+// Waits for the flags of all ranks with a time bound; the flags only ever grow (epoch numbers), so nothing is reset.
+struct PeerPads {
+    uint32_t* p[8];   // signal words of every rank: pad[r][q] = latest epoch rank q has announced to rank r
+};
+__global__ void peer_barrier_kernel(const PeerPads pp, uint32_t world, uint32_t rank, uint32_t epoch, int32_t* status) {
+    uint32_t* const* pads = pp.p;
+    const uint32_t p = threadIdx.x;
+    if (p >= world) return;
+    // The stores of the preceding kernels (results pushed into the peers' memory) are ordered before the flag.
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pads[p] + rank), "r"(epoch) : "memory");
+    const uint32_t* mine = pads[rank] + p;
+    const long long t0 = clock64();
+    while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int32_t)(v - epoch) >= 0) break;
+        if (clock64() - t0 > (1ll << 30)) {   // about half a second: the peer never signalled
+            if (status) atomicExch(status, 3);
+            break;
+        }
+        __nanosleep(200);
+    }
+}
+
+int32_t runit_gemv_allgather_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_local, const void* x, void* const* y_all,
+                                 uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, y_all && world >= 1 && world <= 8 && rank < world && rows_total > 0 && rows_total % world == 0,
+                  "gemv_allgather_f32: world=%u rank=%u rows=%u unsupported (1..8 ranks, rows divisible)", world, rank, rows_total);
+    const uint32_t n = rows_total / world;
+    GemvCall c;
+    c.name = "gemv_allgather_f32";
+    c.fmt = fmt;
+    c.w[0] = w_local;
+    c.x = x;
+    c.rows[0] = n;
+    c.k = k;
+    for (uint32_t p = 0; p < world; p++) {
+        RUNIT_REQUIRE(ctx, y_all[p], "gemv_allgather_f32: null output pointer for rank %u", p);
+        float* slice = (float*)y_all[p] + (size_t)rank * n;
+        if (p == rank) c.y[0] = slice;
+        else c.peer_y[c.n_peer++] = slice;
+    }
+    return gemv_dispatch(ctx, c);
+}
+
+int32_t runit_peer_barrier(runit_ctx_t* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, signal_pads && world >= 1 && world <= 8 && rank < world && epoch > 0, "peer_barrier: bad argument");
+    PeerPads h{};
+    for (uint32_t p = 0; p < world; p++) {
+        RUNIT_REQUIRE(ctx, signal_pads[p] && runit_aligned(signal_pads[p], 4), "peer_barrier: null or misaligned pad %u", p);
+        h.p[p] = (uint32_t*)signal_pads[p];
+    }
+    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status);
+    return runit_after_launch(ctx, "peer_barrier");
 }
 
 }  // extern "C"

@@ -78,6 +78,10 @@ struct GemvArgs {
     // output row s.
     const int32_t* grp_expert;
     uint32_t grp_rows, grp_tiles, grp_xdiv;
+    // Row-sharded launch with the all-gather fused into the epilogue: every f32 result of segment 0 is also
+    // stored at the same index of these vectors, which live in the memory of the other GPUs (plain peer stores).
+    float* peer_y[7];
+    uint32_t n_peer;
 };
 
 // Tensor maps of the weight matrices (bulk-load path): one per segment, plus the second matrix of
@@ -605,6 +609,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                 else if (a.res_kind == RES_F16) v += __half2float(reinterpret_cast<const __half*>(sg.res)[o]);
                 if (a.out_f16) reinterpret_cast<__half*>(sg.y)[o] = __float2half_rn(v);
                 else reinterpret_cast<float*>(sg.y)[o] = v;
+                for (uint32_t p = 0; p < a.n_peer; p++) a.peer_y[p][o] = v;
             }
         }
     }
@@ -693,6 +698,7 @@ __global__ void __launch_bounds__(128) gemv_simple_kernel(const GemvArgs a, int 
             else if (a.res_kind == RES_F16) v += __half2float(reinterpret_cast<const __half*>(sg.res)[o]);
             if (a.out_f16) reinterpret_cast<__half*>(sg.y)[o] = __float2half_rn(v);
             else reinterpret_cast<float*>(sg.y)[o] = v;
+            for (uint32_t p = 0; p < a.n_peer; p++) a.peer_y[p][o] = v;
         }
     }
 }

@@ -197,6 +197,40 @@ class CudaBackend:
         return y
 
 
+class FusedAllGatherGemv:
+    """Row-sharded GEMV whose all-gather happens in the kernel's epilogue: every rank stores its slice of the output
+    straight into the output vectors of all ranks (peer stores over NVLink into symmetric memory) and one small
+    barrier kernel announces completion; no collective library call on the data path.  The NCCL variant is
+    `sharded_gemv`."""
+
+    def __init__(self, R, ctx, torch, dist, fmt, w_local, rows_total, k, world, rank):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        self.R, self.ctx, self.torch, self.C = R, ctx, torch, C
+        self.fmt, self.w, self.rows_total, self.k, self.world, self.rank = fmt, w_local, rows_total, k, world, rank
+        self.y = symm.empty(rows_total, dtype=torch.float32, device="cuda")
+        self.pad = symm.empty(64, dtype=torch.int32, device="cuda")
+        self.pad.zero_()
+        torch.cuda.synchronize()
+        group = dist.group.WORLD
+        self._hy = symm.rendezvous(self.y, group)
+        self._hp = symm.rendezvous(self.pad, group)
+        self.y_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hy.buffer_ptrs])
+        self.pad_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hp.buffer_ptrs])
+        self.epoch = 0
+        dist.barrier()        # every pad is zero and mapped before the first flag is written
+        torch.cuda.synchronize()
+
+    def __call__(self, x):
+        """Returns this rank's full-length output vector (valid once the stream has passed the barrier kernel)."""
+        self.epoch += 1
+        # ranks may be an epoch apart: the barrier at the end of call n also keeps call n+1 of a fast rank from
+        # overwriting a vector that a slow rank is still reading, as long as the caller consumes y before the next call
+        self.R.gemv_allgather_f32(self.ctx, self.fmt, self.w, x, self.y_ptrs, self.world, self.rank, self.rows_total, self.k)
+        self.R.peer_barrier(self.ctx, self.pad_ptrs, self.world, self.rank, self.epoch)
+        return self.y
+
+
 def _time_steps(torch, dist, stream, ctx, fn, steps, world):
     for _ in range(3):
         fn()
@@ -232,6 +266,13 @@ def bench_sharded_lm_head(R, ctx, torch, dist, stream, rank, world, steps=20):
         alg = M * rb + 4 * (K + M)
         out[name] = {"us_per_call": ms * 1e3, "us_local_gemv": ms_local * 1e3, "aggregate_gbs": alg / (ms * 1e-3) / 1e9,
                      "rows_per_rank": n}
+        if world > 1:
+            try:
+                fused = FusedAllGatherGemv(R, ctx, torch, dist, fmt, w, M, K, world, rank)
+                ms_f = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
+                out[name].update({"us_per_call_fused_peer_stores": ms_f * 1e3, "aggregate_gbs_fused": alg / (ms_f * 1e-3) / 1e9})
+            except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
+                out[name]["fused_unavailable"] = repr(exc)[:200]
         w.free()
     return out
 

@@ -48,6 +48,17 @@ def run_rank(rank, world, port, q):
     out, idx, w = P.ep_moe_forward(be, dist, torch, xs, E, K_TOP, False, world, rank)
     torch.cuda.synchronize()
     ctx.flush()
+    y_fused = None
+    if world > 1:
+        # the same sharded product with the all-gather fused into the GEMV epilogue (peer stores + barrier kernel),
+        # three calls in a row: the result must be the NCCL one bit for bit every time
+        fused = P.FusedAllGatherGemv(R, ctx, torch, dist, 2, be.w_local, M_ROWS, K_IN, world, rank)
+        for _ in range(3):
+            yf = fused(torch.from_numpy(d["x_lm"]).cuda())
+            ctx.flush()
+            assert torch.equal(yf, y), "fused all-gather differs from the NCCL all-gather"
+            dist.barrier()     # nobody starts the next call while a slow rank still compares this one
+        y_fused = yf.cpu().numpy()
     res = (rank, y.cpu().numpy(), out.cpu().numpy(), idx.cpu().numpy())
     if world > 1:
         dist.destroy_process_group()
@@ -85,3 +96,24 @@ def test_sharded_paths_match_oracle(oracle):
     assert (idx == ridx).all()
     st = O.compare(ref, out, rel_tol=1e-3)
     assert st.n_mismatch_rel == 0, st
+
+
+def test_peer_barrier_times_out_without_a_peer(ctx):
+    """Failure detection without a fault: a two-rank barrier whose second rank never signals (its flag word is a
+    local buffer nothing writes) gives up after its time limit; the next flush reports the time-out and the
+    context keeps working."""
+    import ctypes as C
+    import runit_mac_b200 as R
+    pads = [ctx.new_buffer(256), ctx.new_buffer(256)]
+    for p in pads:
+        p.upload(np.zeros(64, np.uint32))
+    table = (C.c_void_p * 2)(pads[0].ptr, pads[1].ptr)
+    R.peer_barrier(ctx, table, 2, 0, 1)
+    with pytest.raises(R.KernelError) as e:
+        ctx.flush()
+    assert "TIMEOUT" in str(e.value)
+    assert pads[1].download(np.uint32, 2)[0] == 1          # our own announcement did reach the peer's pad
+    # world size 1 completes at once, and the context is still usable
+    one = (C.c_void_p * 1)(pads[0].ptr)
+    R.peer_barrier(ctx, one, 1, 0, 2)
+    ctx.flush()
