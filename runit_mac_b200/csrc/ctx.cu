@@ -82,6 +82,9 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
         return RUNIT_ERR_ALLOC;
     }
     memset(c->h_status, 0, 64);
+    // Staging area of the batched GEMV (its activations, quantised once per call): 4 MiB = K up to 232,960.
+    if (cudaMalloc(&c->d_xq, 4u << 20) == cudaSuccess) c->xq_bytes = 4u << 20;
+    else { c->d_xq = nullptr; cudaGetLastError(); }
     {
         cudaDriverEntryPointQueryResult qres;
         void* fn = nullptr;
@@ -140,6 +143,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);   // Drop flushes, context.rs:299-304
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->d_xq) cudaFree(ctx->d_xq);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RUNIT_OK;

@@ -324,6 +324,10 @@ int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, batch >= 1 && batch <= 8, "gemv_batched_f32: batch=%u not in 1..8", batch);
     RUNIT_REQUIRE(ctx, m > 0, "gemv_batched_f32: m == 0");
+    // 4-bit formats, batch 2..8: integer tensor-core path (activations quantised once, weights streamed once).
+    if (gemv_imma_applies(ctx, fmt, k, batch) && weight && input && output && runit_aligned(weight, 16) && runit_aligned(input, 16) &&
+        runit_aligned(output, 4) && (k / 256 * 144) % 16 == 0 && ctx->tune.gemv_variant != 1)
+        return gemv_imma(ctx, fmt, weight, (const float*)input, (float*)output, (const float*)residual, m, k, batch);
     // Kernels exist for batch 1, 2, 4, 8; other sizes run as a sum of those.
     uint32_t done = 0;
     while (done < batch) {

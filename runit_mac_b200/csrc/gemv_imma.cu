@@ -1,0 +1,316 @@
+// Batched (2..8 activation rows) fused-dequant GEMV for the 4-bit formats on the integer tensor-core path.
+//
+// With 8 activation rows a weight takes part in 8 multiply-adds; on the CUDA cores that is 8 FMAs (or 6 dp4a) per
+// weight and the kernel is arithmetic-bound far below the HBM roofline.  Here the 4-bit weights go into
+// mma.sync.m16n8k32 (8-bit integer operands, one MMA = 16 rows x 8 activation rows x 32 K = exactly one Q4_0 block or
+// one Q4_K sub-block), so the per-block scale is applied to an int32 tile in registers and nothing else has to be
+// dequantised:
+//   * a pre-pass quantises the activations once per call: per 32-block and activation row a scale s = max|x| / 16383
+//     and 15-bit integers q = rint(x / s), stored as a signed high byte and an unsigned low byte in the order the
+//     MMA's B fragments want them, plus s and s * sum(q) per block (for the "- min" / "- 8" terms).  Relative error of
+//     an activation <= 2^-15 of its block maximum, far inside the 1e-3 bar; products and block sums are exact integers.
+//   * the weight nibbles are the MMA's A operand after one mask (low nibbles) or shift+mask (high nibbles).
+//   * per k32 tile: 2 MMAs (high and low activation byte), v = 256 * hi + lo, acc += (scale_w * s) * v - (min_w * s*sum q).
+//   * CTA = 4 warps on the same K range, each with its own rows (RW = 16 or 32 per warp); the activation unit of a stage
+//     is shared by the 4 warps, the weight boxes arrive by TMA (box RW rows x 144 bytes), 3 stages, mbarrier pipeline.
+//     Few-tile shapes split K over a thread-block cluster and reduce through distributed shared memory.
+// Reference formulas: Q4_0 value d * (nibble - 8), low nibble = element 2i, high = 2i + 1
+// (crates/kernels/shaders/gemv_q4_0.metal:26-49); Q4_K value d*sc*q - dmin*m (crates/engine/src/forward.rs:1026-1057).
+#include "gemv_common.cuh"
+#include "runit_internal.h"
+#include "tma.cuh"
+
+namespace runit {
+namespace imma {
+
+constexpr int kUnitBytes = 4608;   // activations of one 256-K unit: 4096 bytes of limbs + 256 scales + 256 block sums
+constexpr int kStages = 3;
+
+// ───────────────────────── activation pre-pass ─────────────────────────
+// Slot of element e (0..31) of a block in the MMA's K order.  Q4_K: natural.  Q4_0: word t of the block holds
+// elements 8t..8t+7 as (low, high) nibble pairs, low nibbles feed K slots 4t..4t+3, high nibbles 16+4t..16+4t+3.
+template <int FMT>
+__device__ __forceinline__ int k_slot(int e) {
+    if (FMT == RUNIT_FMT_Q4K) return e;
+    return 16 * (e & 1) + 4 * (e >> 3) + ((e & 7) >> 1);
+}
+
+// One CTA per unit, one warp per activation row (rows >= batch are written as zeros).
+template <int FMT>
+__global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict__ x, uint8_t* __restrict__ xq, uint32_t k,
+                                                          uint32_t batch) {
+    const uint32_t u = blockIdx.x, n = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* dst = xq + (size_t)u * kUnitBytes;
+    for (int bt = 0; bt < 8; bt++) {
+        const float v = n < batch ? x[(size_t)n * k + (size_t)u * 256 + bt * 32 + lane] : 0.f;
+        float amax = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float s = amax * (1.0f / 16383.0f);
+        const int q = amax > 0.f ? __float2int_rn(v * (16383.0f / amax)) : 0;
+        int qs = q;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);
+        const int slot = k_slot<FMT>((int)lane);
+        uint8_t* p = dst + ((bt * 8 + n) * 4 + ((slot & 15) >> 2)) * 16 + (slot >> 4) * 4 + (slot & 3);
+        p[0] = (uint8_t)(q >> 8);      // signed high byte
+        p[8] = (uint8_t)(q & 255);     // unsigned low byte
+        if (lane == 0) {
+            reinterpret_cast<float*>(dst + 4096)[bt * 8 + n] = s;
+            reinterpret_cast<float*>(dst + 4096 + 256)[bt * 8 + n] = s * (float)qs;
+        }
+    }
+}
+
+// ───────────────────────── main kernel ─────────────────────────
+struct Args {
+    const uint8_t* xq;
+    float* y;
+    const float* res;
+    uint32_t m, units, batch, csplit;
+    int32_t* status;
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+__device__ __forceinline__ void mma_u8u8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// One k32 tile: A = nibbles of rows (g, g+8), B = the activation block; adds the scaled tile into acc.
+// sw0/sw1, mw0/mw1: weight scale and min of rows g / g+8 for this block; xs/xm: activation scale and block sum of
+// columns 2t, 2t+1 (packed float2 loads).
+__device__ __forceinline__ void tile_mma(float (&acc)[4], const uint32_t (&a)[4], uint32_t xaddr, uint32_t saddr, float sw0, float mw0,
+                                         float sw1, float mw1) {
+    uint32_t bh0, bh1, bl0, bl1;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(bh0), "=r"(bh1), "=r"(bl0), "=r"(bl1) : "r"(xaddr));
+    float xs0, xs1, xm0, xm1;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(xs0), "=f"(xs1) : "r"(saddr));
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(xm0), "=f"(xm1) : "r"(saddr + 256));
+    int ch[4], cl[4];
+    mma_u8s8(ch, a, bh0, bh1);
+    mma_u8u8(cl, a, bl0, bl1);
+    const float v0 = (float)(ch[0] * 256 + cl[0]), v1 = (float)(ch[1] * 256 + cl[1]);
+    const float v2 = (float)(ch[2] * 256 + cl[2]), v3 = (float)(ch[3] * 256 + cl[3]);
+    acc[0] = fmaf(v0, sw0 * xs0, fmaf(-mw0, xm0, acc[0]));
+    acc[1] = fmaf(v1, sw0 * xs1, fmaf(-mw0, xm1, acc[1]));
+    acc[2] = fmaf(v2, sw1 * xs0, fmaf(-mw1, xm0, acc[2]));
+    acc[3] = fmaf(v3, sw1 * xs1, fmaf(-mw1, xm1, acc[3]));
+}
+
+template <int FMT, int RW>
+__global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ CUtensorMap wmap, const Args a) {
+    constexpr int WBYTES = RW * 144;                       // one warp's weight box
+    constexpr int STAGE = kUnitBytes + 4 * WBYTES;
+    constexpr int MT = RW / 16;                            // m16 tiles per warp
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * kStages];
+    __shared__ float red[4 * RW][8];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t crank = a.csplit > 1 ? cluster_ctarank() : 0;
+    const uint32_t tile = blockIdx.x / a.csplit;
+    const uint32_t row_tile0 = tile * (4 * RW);
+    const uint32_t u_begin = (uint32_t)(((uint64_t)a.units * crank) / a.csplit), u_end = (uint32_t)(((uint64_t)a.units * (crank + 1)) / a.csplit);
+    const uint32_t nu = u_end - u_begin;
+    const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[kStages]);
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 4);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    bool timed_out = false;
+    auto issue = [&](uint32_t i) {   // loads of the i-th unit of this CTA (thread 0 only)
+        const uint32_t s = i % kStages, u = u_begin + i;
+        const uint32_t sb = base + s * STAGE;
+        mbar_expect_tx(bar_full + 8 * s, STAGE);
+        bulk_load_1d(sb, a.xq + (size_t)u * kUnitBytes, kUnitBytes, bar_full + 8 * s);
+#pragma unroll
+        for (int w = 0; w < 4; w++)
+            tma_load_2d(sb + kUnitBytes + w * WBYTES, &wmap, (int32_t)(u * 144), (int32_t)(row_tile0 + w * RW), bar_full + 8 * s);
+    };
+    if (tid == 0)
+        for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue(i);
+
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
+
+    for (uint32_t i = 0; i < nu; i++) {
+        const uint32_t s = i % kStages;
+        if (tid == 0 && i + kStages - 1 < nu) {
+            const uint32_t j = i + kStages - 1, sj = j % kStages;
+            // the stage being refilled was used by unit j - kStages: wait until all four warps have released it
+            if (j >= kStages && !mbar_wait(bar_empty + 8 * sj, ((j / kStages) - 1) & 1)) timed_out = true;
+            issue(j);
+        }
+        if (!mbar_wait(bar_full + 8 * s, (i / kStages) & 1)) { timed_out = true; break; }
+        const uint32_t sb = base + s * STAGE;
+        const uint32_t wb = sb + kUnitBytes + warp * WBYTES;
+        const uint32_t xb = sb + (g * 4 + t) * 16;       // + bt * 512: limbs of block bt for column g, K quarter t
+        const uint32_t scb = sb + 4096 + (2 * t) * 4;    // + bt * 32: scales of columns 2t, 2t+1
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const uint32_t r0 = wb + (mt * 16 + g) * 144, r1 = r0 + 8 * 144;
+            if (FMT == RUNIT_FMT_Q4K) {
+                uint32_t h0[4], h1[4];
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h0[0]), "=r"(h0[1]), "=r"(h0[2]), "=r"(h0[3]) : "r"(r0));
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h1[0]), "=r"(h1[1]), "=r"(h1[2]), "=r"(h1[3]) : "r"(r1));
+                const float d0 = half_bits_to_float(h0[0]), n0 = half_bits_to_float(h0[0] >> 16);
+                const float d1 = half_bits_to_float(h1[0]), n1 = half_bits_to_float(h1[0] >> 16);
+                const Q4KScales s0 = q4k_unpack_scales(h0[1], h0[2], h0[3]), s1 = q4k_unpack_scales(h1[1], h1[2], h1[3]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t w00 = lds32(r0 + 16 + 32 * j + 4 * t), w01 = lds32(r0 + 32 + 32 * j + 4 * t);
+                    const uint32_t w10 = lds32(r1 + 16 + 32 * j + 4 * t), w11 = lds32(r1 + 32 + 32 * j + 4 * t);
+                    const uint32_t alo[4] = {w00 & 0x0F0F0F0Fu, w10 & 0x0F0F0F0Fu, w01 & 0x0F0F0F0Fu, w11 & 0x0F0F0F0Fu};
+                    const uint32_t ahi[4] = {(w00 >> 4) & 0x0F0F0F0Fu, (w10 >> 4) & 0x0F0F0F0Fu, (w01 >> 4) & 0x0F0F0F0Fu,
+                                             (w11 >> 4) & 0x0F0F0F0Fu};
+                    // low nibbles: sub-block j (elements 64j..64j+31); high nibbles: sub-block j+4 (64j+32..64j+63)
+                    tile_mma(acc[mt], alo, xb + (2 * j) * 512, scb + (2 * j) * 32, d0 * byte_to_float(s0.sl, j), n0 * byte_to_float(s0.ml, j),
+                             d1 * byte_to_float(s1.sl, j), n1 * byte_to_float(s1.ml, j));
+                    tile_mma(acc[mt], ahi, xb + (2 * j + 1) * 512, scb + (2 * j + 1) * 32, d0 * byte_to_float(s0.sh, j),
+                             n0 * byte_to_float(s0.mh, j), d1 * byte_to_float(s1.sh, j), n1 * byte_to_float(s1.mh, j));
+                }
+            } else {
+#pragma unroll
+                for (int b = 0; b < 8; b++) {
+                    // block b of the unit sits at byte 18b of the row: f16 scale, then 16 bytes of nibbles; for even b the
+                    // nibble words straddle aligned words by two bytes
+                    uint32_t w0, w1, sc0, sc1;
+                    if ((b & 1) == 0) {
+                        const uint32_t p0 = r0 + 18 * b + 4 * t, p1 = r1 + 18 * b + 4 * t;
+                        w0 = __funnelshift_r(lds32(p0), lds32(p0 + 4), 16);
+                        w1 = __funnelshift_r(lds32(p1), lds32(p1 + 4), 16);
+                        sc0 = lds32(r0 + 18 * b) & 0xFFFFu;
+                        sc1 = lds32(r1 + 18 * b) & 0xFFFFu;
+                    } else {
+                        w0 = lds32(r0 + 18 * b + 2 + 4 * t);
+                        w1 = lds32(r1 + 18 * b + 2 + 4 * t);
+                        sc0 = lds32(r0 + 18 * b - 2) >> 16;
+                        sc1 = lds32(r1 + 18 * b - 2) >> 16;
+                    }
+                    const uint32_t aa[4] = {w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
+                    const float d0 = half_bits_to_float(sc0), d1 = half_bits_to_float(sc1);
+                    tile_mma(acc[mt], aa, xb + b * 512, scb + b * 32, d0, 8.0f * d0, d1, 8.0f * d1);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_empty + 8 * s) : "memory");
+    }
+
+    // partial sums of this CTA: rows (warp * RW + mt * 16 + g, + 8), columns 2t, 2t+1
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        red[warp * RW + mt * 16 + g][2 * t] = acc[mt][0];
+        red[warp * RW + mt * 16 + g][2 * t + 1] = acc[mt][1];
+        red[warp * RW + mt * 16 + g + 8][2 * t] = acc[mt][2];
+        red[warp * RW + mt * 16 + g + 8][2 * t + 1] = acc[mt][3];
+    }
+    if (a.csplit > 1) cluster_sync();
+    else __syncthreads();
+    if (crank == 0) {
+        for (uint32_t e = tid; e < 4 * RW * 8; e += 128) {
+            const uint32_t r = e % (4 * RW), c = e / (4 * RW);      // consecutive threads -> consecutive rows of one column
+            float v = red[r][c];
+            for (uint32_t p = 1; p < a.csplit; p++) v += ld_cluster_f32(&red[r][c], p);
+            const uint32_t row = row_tile0 + r;
+            if (row < a.m && c < a.batch) {
+                const size_t o = (size_t)c * a.m + row;
+                if (a.res) v += a.res[o];
+                a.y[o] = v;
+            }
+        }
+    }
+    if (a.csplit > 1) cluster_sync();   // keep every CTA's partial sums alive until rank 0 has read them
+    if (timed_out && a.status) atomicExch(a.status, 1);
+}
+
+template <int FMT, int RW>
+static int32_t launch(runit_ctx* ctx, const CUtensorMap& map, const Args& a, uint32_t tiles) {
+    constexpr int smem = kStages * (kUnitBytes + 4 * RW * 144) + 128;
+    auto kern = gemv_imma_kernel<FMT, RW>;
+    static bool configured[16] = {false};
+    if (ctx->device < 16 && !configured[ctx->device]) {
+        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[ctx->device] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * a.csplit);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (a.csplit > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = a.csplit;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        na++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, a);
+    if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "launch of gemv_batched (integer MMA) failed: %s", cudaGetErrorString(e));
+    return runit_after_launch(ctx, "gemv_batched_imma");
+}
+
+}  // namespace imma
+
+// True if the integer tensor-core path serves this call (4-bit format, whole 256-K units, 16-byte aligned rows,
+// the activations fit the context's staging area).
+bool gemv_imma_applies(const runit_ctx* ctx, int fmt, uint32_t k, uint32_t batch) {
+    if (fmt != RUNIT_FMT_Q4_0 && fmt != RUNIT_FMT_Q4K) return false;
+    if (batch < 2 || batch > 8 || k % 256 != 0 || ctx->tune.gemv_math == 1 || !ctx->encode_tiled || !ctx->d_xq) return false;
+    return (size_t)(k / 256) * imma::kUnitBytes <= ctx->xq_bytes;
+}
+
+int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
+                  uint32_t batch) {
+    using namespace imma;
+    const uint32_t units = k / 256;
+    if (fmt == RUNIT_FMT_Q4K) xq_prepare_kernel<RUNIT_FMT_Q4K><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
+    else xq_prepare_kernel<RUNIT_FMT_Q4_0><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
+    int32_t st = runit_after_launch(ctx, "gemv_batched_quantise_x");
+    if (st != RUNIT_OK) return st;
+    // rows per warp: 32 when that still gives every SM two CTAs, else 16
+    const uint32_t sms = (uint32_t)ctx->sm_count;
+    const uint32_t tiles32 = (m + 127) / 128, tiles16 = (m + 63) / 64;
+    const bool rw32 = tiles32 >= 2 * sms;
+    const uint32_t tiles = rw32 ? tiles32 : tiles16;
+    uint32_t csplit = 1;
+    while (csplit < 8 && tiles * csplit < 2 * sms && units / (csplit * 2) >= 4) csplit *= 2;
+    Args a{};
+    a.xq = (const uint8_t*)ctx->d_xq;
+    a.y = y;
+    a.res = res;
+    a.m = m;
+    a.units = units;
+    a.batch = batch;
+    a.csplit = csplit;
+    a.status = ctx->d_status;
+    CUtensorMap map;
+    st = runit_get_tmap(ctx, w, m, (uint64_t)units * 144, rw32 ? 32 : 16, 144, &map);
+    if (st != RUNIT_OK) return st;
+    if (fmt == RUNIT_FMT_Q4K) return rw32 ? launch<RUNIT_FMT_Q4K, 32>(ctx, map, a, tiles) : launch<RUNIT_FMT_Q4K, 16>(ctx, map, a, tiles);
+    return rw32 ? launch<RUNIT_FMT_Q4_0, 32>(ctx, map, a, tiles) : launch<RUNIT_FMT_Q4_0, 16>(ctx, map, a, tiles);
+}
+
+}  // namespace runit

@@ -46,6 +46,8 @@ struct runit_ctx {
     // Device scratch owned by the context (allocated at creation; ops never allocate).
     int32_t* d_status = nullptr;        // device address of the status word written by kernels with bounded waits
     int32_t* h_status = nullptr;        // the same word, host side (pinned, mapped)
+    void* d_xq = nullptr;               // staging area of the batched GEMV's quantised activations
+    size_t xq_bytes = 0;
     void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation
     runit_tmap_entry tmaps[256];
 };
@@ -97,6 +99,10 @@ static inline size_t runit_row_bytes(int fmt, uint32_t k) {
 }
 
 namespace runit {
+// gemv_imma.cu: batched GEMV of the 4-bit formats on the integer tensor-core path.
+bool gemv_imma_applies(const runit_ctx* ctx, int fmt, uint32_t k, uint32_t batch);
+int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
+                  uint32_t batch);
 // gemv.cu: grouped GEMVs over stacked expert matrices (MoE block).
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,

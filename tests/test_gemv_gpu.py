@@ -230,6 +230,31 @@ def test_fused_ffn(ctx, oracle, fmt, ff, k):
     assert_close(O, ref, act.download(np.float32, ff), what="fused_ffn")
 
 
+@pytest.mark.parametrize("fmt,m,k,batch", [(1, 37900, 512, 8), (2, 37900, 512, 7), (1, 200, 18944, 5), (2, 200, 18944, 8),
+                                           (2, 18944, 3584, 8)])
+def test_batched_gemv_tensor_core_path_shapes(ctx, oracle, fmt, m, k, batch):
+    """The integer tensor-core path of the 4-bit formats: 32 rows per warp (many tiles), K split over clusters of 8
+    (few tiles, long K), ragged last tile, and the FFN shape of the benchmark configuration."""
+    import runit_mac_b200 as R
+    O = oracle
+    rng = np.random.default_rng(m + k + batch)
+    w = O.rand_weights(fmt, rng, m, k)
+    x = rng.normal(0, 1, (batch, k)).astype(np.float32)
+    res = rng.normal(0, 1, (batch, m)).astype(np.float32)
+    rows = np.unique(np.concatenate([np.arange(0, min(m, 70)), rng.integers(0, m, 200), np.arange(m - 40, m)]))
+    rb = O.row_bytes(fmt, k)
+    ref = O.gemv(fmt, w.reshape(m, rb)[rows].copy(), x, len(rows), k, O.TIER_F64).reshape(batch, len(rows))
+    yb = ctx.new_buffer(batch * m * 4)
+    R.gemv_batched_f32(ctx, fmt, ctx.buffer_from(w), ctx.buffer_from(x), yb, ctx.buffer_from(res), m, k, batch)
+    ctx.flush()
+    got = yb.download(np.float32, batch * m).reshape(batch, m)
+    assert_close(O, ref + res[:, rows], got[:, rows], what="batched tensor-core path")
+    # the same call twice gives the same bits (fixed reduction order across the cluster)
+    R.gemv_batched_f32(ctx, fmt, ctx.buffer_from(w), ctx.buffer_from(x), yb, ctx.buffer_from(res), m, k, batch)
+    ctx.flush()
+    assert np.array_equal(got, yb.download(np.float32, batch * m).reshape(batch, m))
+
+
 @pytest.mark.parametrize("fmt", [0, 1, 2])
 @pytest.mark.parametrize("batch", [1, 2, 3, 8])
 def test_batched_gemv(ctx, oracle, fmt, batch):
