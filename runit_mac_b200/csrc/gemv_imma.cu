@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict
                                                           uint32_t batch) {
     const uint32_t u = blockIdx.x, n = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* dst = xq + (size_t)u * kUnitBytes;
+    grid_launch_dependents();   // the consumer may start fetching its weights; it waits for this grid before reading xq
     for (int bt = 0; bt < 8; bt++) {
         const float v = n < batch ? x[(size_t)n * k + (size_t)u * 256 + bt * 32 + lane] : 0.f;
         float amax = fabsf(v);
@@ -133,17 +134,26 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     }
     __syncthreads();
     bool timed_out = false;
-    auto issue = [&](uint32_t i) {   // loads of the i-th unit of this CTA (thread 0 only)
+    auto issue_w = [&](uint32_t i) {   // weight boxes of the i-th unit of this CTA (thread 0 only)
         const uint32_t s = i % kStages, u = u_begin + i;
         const uint32_t sb = base + s * STAGE;
         mbar_expect_tx(bar_full + 8 * s, STAGE);
-        bulk_load_1d(sb, a.xq + (size_t)u * kUnitBytes, kUnitBytes, bar_full + 8 * s);
 #pragma unroll
         for (int w = 0; w < 4; w++)
             tma_load_2d(sb + kUnitBytes + w * WBYTES, &wmap, (int32_t)(u * 144), (int32_t)(row_tile0 + w * RW), bar_full + 8 * s);
     };
+    auto issue_x = [&](uint32_t i) {   // its quantised activations
+        const uint32_t s = i % kStages, u = u_begin + i;
+        bulk_load_1d(base + s * STAGE, a.xq + (size_t)u * kUnitBytes, kUnitBytes, bar_full + 8 * s);
+    };
+    auto issue = [&](uint32_t i) { issue_w(i); issue_x(i); };
+    // The weights do not depend on the activation pre-pass: their first loads go out before the dependency wait
+    // (programmatic dependent launch), the activations after it.
     if (tid == 0)
-        for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue(i);
+        for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue_w(i);
+    grid_dependency_wait();
+    if (tid == 0)
+        for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue_x(i);
 
     float acc[MT][4];
 #pragma unroll
@@ -256,8 +266,11 @@ static int32_t launch(runit_ctx* ctx, const CUtensorMap& map, const Args& a, uin
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
     if (a.csplit > 1) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = a.csplit;
@@ -296,7 +309,7 @@ int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float*
     const bool rw32 = tiles32 >= 2 * sms;
     const uint32_t tiles = rw32 ? tiles32 : tiles16;
     uint32_t csplit = 1;
-    while (csplit < 8 && tiles * csplit < 2 * sms && units / (csplit * 2) >= 4) csplit *= 2;
+    while (csplit < 8 && tiles * csplit < 4 * sms && units / (csplit * 2) >= 3) csplit *= 2;
     Args a{};
     a.xq = (const uint8_t*)ctx->d_xq;
     a.y = y;
