@@ -8,6 +8,7 @@
 // fed from f32 K/V, f32 logits with a lowest-index argmax.
 #include "decode_ops.cuh"
 #include "runit_internal.h"
+#include "tma.cuh"
 
 #include <new>
 #include <vector>
@@ -38,6 +39,8 @@ namespace runit {
 // x = tok_emb[token]; token comes from the forced list while step < n_forced, else from state[0].
 __global__ void embed_kernel(const float* __restrict__ emb, float* __restrict__ x, int32_t* state,
                              const int32_t* __restrict__ forced, uint32_t n_forced, uint32_t hidden, uint32_t vocab) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t step = (uint32_t)state[2];
     int32_t tok = state[0];
     if (step < n_forced) {
@@ -52,6 +55,8 @@ __global__ void embed_kernel(const float* __restrict__ emb, float* __restrict__ 
 // After the step: record the produced token, advance position and step.
 __global__ void advance_kernel(int32_t* state, const int32_t* argmax_result, int32_t* out_tokens, uint32_t out_cap,
                                int has_logits) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         const uint32_t step = (uint32_t)state[2];
         if (has_logits) {
@@ -85,7 +90,7 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
     const size_t kv_layer = (size_t)c.n_kv_heads * c.max_seq * hd;
     const int32_t* pos_ptr = m->state + 1;
     int32_t st;
-    embed_kernel<<<8, 256, 0, ctx->stream>>>((const float*)m->w.tok_emb, m->x, m->state, m->forced, n_forced, h, c.vocab);
+    runit_launch_chain(ctx, embed_kernel, dim3(8), dim3(256), (const float*)m->w.tok_emb, m->x, m->state, m->forced, n_forced, h, c.vocab);
     if ((st = runit_after_launch(ctx, "embed")) != RUNIT_OK) return st;
     for (int l = 0; l < c.n_layers; l++) {
         const uint8_t* wq = (const uint8_t*)m->w.wq + (size_t)l * q_dim * rb_h;
@@ -122,7 +127,7 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->xn, m->logits, nullptr, c.vocab, h))) return st;
         if ((st = launch_argmax(ctx, m->logits, false, argmax_out, c.vocab))) return st;
     }
-    advance_kernel<<<1, 32, 0, ctx->stream>>>(m->state, argmax_out, m->out_tokens, m->out_cap, with_logits ? 1 : 0);
+    runit_launch_chain(ctx, advance_kernel, dim3(1), dim3(32), m->state, argmax_out, m->out_tokens, m->out_cap, with_logits ? 1 : 0);
     return runit_after_launch(ctx, "advance");
 }
 

@@ -5,6 +5,7 @@
 // (pos_ptr) so that a recorded command list can be replayed for successive tokens.
 #include "decode_ops.cuh"
 #include "runit_internal.h"
+#include "tma.cuh"
 
 namespace runit {
 
@@ -23,6 +24,8 @@ __device__ __forceinline__ float warp_max(float v) {
 template <typename G>
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                         const G* __restrict__ gamma, float eps, uint32_t hidden) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     __shared__ float part[8];
     const float* row = x + (size_t)blockIdx.x * hidden;
     float* out = y + (size_t)blockIdx.x * hidden;
@@ -50,6 +53,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float* __restrict__
 // (fused_rope.metal:17-56).  Optionally scatters the rotated K and the V vector into f16 caches.
 __global__ void rope_qk_kernel(float* q, float* k, uint32_t head_dim, uint32_t q_heads, uint32_t kv_heads, uint32_t pos_val,
                                const int32_t* pos_ptr, float theta) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t d = threadIdx.x, hid = blockIdx.x, half = head_dim / 2;
     if (d >= half) return;
     const uint32_t pos = pos_ptr ? (uint32_t)*pos_ptr : pos_val;
@@ -74,6 +79,8 @@ __global__ void rope_qk_kernel(float* q, float* k, uint32_t head_dim, uint32_t q
 template <typename S, typename D>
 __global__ void kv_copy_kernel(const S* __restrict__ src, D* __restrict__ dst, uint32_t pos_val, const int32_t* pos_ptr,
                                uint32_t max_seq, uint32_t head_dim) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y;
     if (d >= head_dim) return;
     const uint32_t pos = pos_ptr ? (uint32_t)*pos_ptr : pos_val;
@@ -94,6 +101,8 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
                                                            const TKV* __restrict__ V, TO* __restrict__ O, float* part,
                                                            uint32_t kv_len_val, const int32_t* pos_ptr, uint32_t heads,
                                                            uint32_t kv_heads, uint32_t kv_head_stride, float scale) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     constexpr int HD = 32 * DPL;
     __shared__ float qs[HD];
     __shared__ float sm_m[4], sm_l[4];
@@ -172,6 +181,8 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
 // Merge the per-split partials of one head in split order.
 template <typename TO>
 __global__ void decode_attn_combine_kernel(const float* __restrict__ part, TO* __restrict__ O, uint32_t nsplit, uint32_t hd) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t bh = blockIdx.x, d = threadIdx.x;
     if (d >= hd) return;
     const float* pp = part + (size_t)bh * nsplit * (hd + 2);
@@ -191,6 +202,8 @@ __global__ void decode_attn_combine_kernel(const float* __restrict__ part, TO* _
 // scans the same way but leaves ties unspecified).
 template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ in, int32_t* __restrict__ result, uint32_t n) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     __shared__ float sv[32];
     __shared__ uint32_t sidx[32];
     float bv = -INFINITY;
@@ -224,24 +237,24 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ in, 
 
 int32_t launch_rms_norm(runit_ctx* ctx, const float* x, float* y, const void* gamma, bool gamma_f16, float eps,
                         uint32_t hidden, uint32_t rows) {
-    if (gamma_f16) rms_norm_kernel<__half><<<rows, 256, 0, ctx->stream>>>(x, y, (const __half*)gamma, eps, hidden);
-    else rms_norm_kernel<float><<<rows, 256, 0, ctx->stream>>>(x, y, (const float*)gamma, eps, hidden);
+    if (gamma_f16) runit_launch_chain(ctx, rms_norm_kernel<__half>, dim3(rows), dim3(256), x, y, (const __half*)gamma, eps, hidden);
+    else runit_launch_chain(ctx, rms_norm_kernel<float>, dim3(rows), dim3(256), x, y, (const float*)gamma, eps, hidden);
     return runit_after_launch(ctx, "rms_norm");
 }
 
 int32_t launch_rope(runit_ctx* ctx, float* q, float* k, uint32_t hd, uint32_t qh, uint32_t kvh, uint32_t pos,
                     const int32_t* pos_ptr, float theta) {
     const uint32_t hmax = qh > kvh ? qh : kvh;
-    rope_qk_kernel<<<hmax, hd / 2, 0, ctx->stream>>>(q, k, hd, qh, kvh, pos, pos_ptr, theta);
+    runit_launch_chain(ctx, rope_qk_kernel, dim3(hmax), dim3(hd / 2), q, k, hd, qh, kvh, pos, pos_ptr, theta);
     return runit_after_launch(ctx, "fused_rope_qk_f32");
 }
 
 int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst, bool dst_f16, uint32_t pos,
                        const int32_t* pos_ptr, uint32_t max_seq, uint32_t hd, uint32_t kvh) {
     dim3 grid((hd + 127) / 128, kvh);
-    if (src_f16 && dst_f16) kv_copy_kernel<__half, __half><<<grid, 128, 0, ctx->stream>>>((const __half*)src, (__half*)dst, pos, pos_ptr, max_seq, hd);
-    else if (!src_f16 && !dst_f16) kv_copy_kernel<float, float><<<grid, 128, 0, ctx->stream>>>((const float*)src, (float*)dst, pos, pos_ptr, max_seq, hd);
-    else if (!src_f16 && dst_f16) kv_copy_kernel<float, __half><<<grid, 128, 0, ctx->stream>>>((const float*)src, (__half*)dst, pos, pos_ptr, max_seq, hd);
+    if (src_f16 && dst_f16) runit_launch_chain(ctx, kv_copy_kernel<__half, __half>, dim3(grid), dim3(128), (const __half*)src, (__half*)dst, pos, pos_ptr, max_seq, hd);
+    else if (!src_f16 && !dst_f16) runit_launch_chain(ctx, kv_copy_kernel<float, float>, dim3(grid), dim3(128), (const float*)src, (float*)dst, pos, pos_ptr, max_seq, hd);
+    else if (!src_f16 && dst_f16) runit_launch_chain(ctx, kv_copy_kernel<float, __half>, dim3(grid), dim3(128), (const float*)src, (__half*)dst, pos, pos_ptr, max_seq, hd);
     else return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "kv_copy: f16 source into an f32 cache");
     return runit_after_launch(ctx, "kv_copy_to_cache");
 }
@@ -253,7 +266,7 @@ static int32_t attn_typed(runit_ctx* ctx, const void* q, const void* k, const vo
     const float scale = 1.0f / sqrtf((float)hd);   // dispatch.rs:1588
     dim3 grid(heads, nsplit, batch);
 #define ATTN_CASE(D)                                                                                                   \
-    decode_attn_kernel<TQ, TKV, TO, D><<<grid, 128, 0, ctx->stream>>>((const TQ*)q, (const TKV*)k, (const TKV*)v, (TO*)out, \
+    runit_launch_chain(ctx, decode_attn_kernel<TQ, TKV, TO, D>, dim3(grid), dim3(128), (const TQ*)q, (const TKV*)k, (const TKV*)v, (TO*)out, \
                                                                       part, kv_len, pos_ptr, heads, kv_heads, stride, scale)
     switch (hd) {
         case 32: ATTN_CASE(1); break;
@@ -265,7 +278,7 @@ static int32_t attn_typed(runit_ctx* ctx, const void* q, const void* k, const vo
 #undef ATTN_CASE
     int32_t st = runit_after_launch(ctx, "decode_attention");
     if (st != RUNIT_OK || nsplit == 1) return st;
-    decode_attn_combine_kernel<TO><<<batch * heads, hd, 0, ctx->stream>>>(part, (TO*)out, nsplit, hd);
+    runit_launch_chain(ctx, decode_attn_combine_kernel<TO>, dim3(batch * heads), dim3(hd), part, (TO*)out, nsplit, hd);
     return runit_after_launch(ctx, "decode_attention_combine");
 }
 
@@ -282,8 +295,8 @@ int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const v
 }
 
 int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* result, uint32_t n) {
-    if (in_f16) argmax_kernel<__half><<<1, 1024, 0, ctx->stream>>>((const __half*)in, result, n);
-    else argmax_kernel<float><<<1, 1024, 0, ctx->stream>>>((const float*)in, result, n);
+    if (in_f16) runit_launch_chain(ctx, argmax_kernel<__half>, dim3(1), dim3(1024), (const __half*)in, result, n);
+    else runit_launch_chain(ctx, argmax_kernel<float>, dim3(1), dim3(1024), (const float*)in, result, n);
     return runit_after_launch(ctx, "argmax");
 }
 

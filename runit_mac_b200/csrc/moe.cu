@@ -9,6 +9,7 @@
 #include "decode_ops.cuh"
 #include "gemv_common.cuh"
 #include "runit_internal.h"
+#include "tma.cuh"
 
 namespace runit {
 
@@ -17,6 +18,8 @@ namespace runit {
 template <int KPL>   // floats of the row per lane (K = 32*KPL)
 __global__ void __launch_bounds__(256) router_f32_kernel(const float* __restrict__ w, const float* __restrict__ x,
                                                           float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (e >= E) return;
     float wr[KPL];
@@ -45,6 +48,8 @@ __global__ void __launch_bounds__(256) router_f32_kernel(const float* __restrict
 // Generic fallback for any K (multiple of 4).
 __global__ void __launch_bounds__(256) router_f32_generic_kernel(const float* __restrict__ w, const float* __restrict__ x,
                                                                   float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (e >= E) return;
     for (uint32_t t = blockIdx.y; t < T; t += gridDim.y) {
@@ -62,6 +67,8 @@ __global__ void __launch_bounds__(256) router_f32_generic_kernel(const float* __
 __global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict__ logits, int in_f16, uint32_t E, uint32_t k,
                                                           int renorm, uint32_t T, int32_t* __restrict__ out_idx,
                                                           float* __restrict__ out_w) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     float v[8];
@@ -123,6 +130,8 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict_
 // out[t][r] = (res ? res[t][r] : 0) + sum_i w[t][i] * y[t*k+i][r], i ascending (routing order).
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ w,
                                                            const float* res, float* out, uint32_t T, uint32_t h, uint32_t k) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
     const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (r >= h) return;
     float acc = 0.f;
@@ -157,15 +166,15 @@ static MoeScratch moe_carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uin
 // Shared with the batched block (moe_grouped.cu).
 int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
     dim3 grid((E + 7) / 8, T < 64 ? T : 64);
-    if (K == 2048) router_f32_kernel<64><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
-    else if (K == 1024) router_f32_kernel<32><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
-    else if (K == 4096) router_f32_kernel<128><<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
-    else router_f32_generic_kernel<<<grid, 256, 0, ctx->stream>>>(w, x, logits, E, K, T);
+    if (K == 2048) runit_launch_chain(ctx, router_f32_kernel<64>, dim3(grid), dim3(256), w, x, logits, E, K, T);
+    else if (K == 1024) runit_launch_chain(ctx, router_f32_kernel<32>, dim3(grid), dim3(256), w, x, logits, E, K, T);
+    else if (K == 4096) runit_launch_chain(ctx, router_f32_kernel<128>, dim3(grid), dim3(256), w, x, logits, E, K, T);
+    else runit_launch_chain(ctx, router_f32_generic_kernel, dim3(grid), dim3(256), w, x, logits, E, K, T);
     return runit_after_launch(ctx, "moe_router_f32");
 }
 
 int32_t moe_topk(runit_ctx* ctx, const float* logits, uint32_t E, uint32_t k, int32_t renorm, uint32_t T, int32_t* idx, float* w) {
-    route_topk_kernel<<<(T + 3) / 4, 128, 0, ctx->stream>>>(logits, 0, E, k, renorm, T, idx, w);
+    runit_launch_chain(ctx, route_topk_kernel, dim3((T + 3) / 4), dim3(128), logits, 0, E, k, renorm, T, idx, w);
     return runit_after_launch(ctx, "moe_route_topk");
 }
 
@@ -189,7 +198,7 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     if (st != RUNIT_OK) return st;
     int32_t* idx = idx_out ? idx_out : s.idx;
     float* wts = w_out ? w_out : s.w;
-    route_topk_kernel<<<(T + 3) / 4, 128, 0, ctx->stream>>>(s.logits, 0, E, k, renorm, T, idx, wts);
+    runit_launch_chain(ctx, route_topk_kernel, dim3((T + 3) / 4), dim3(128), s.logits, 0, E, k, renorm, T, idx, wts);
     st = runit_after_launch(ctx, "moe_route_topk");
     if (st != RUNIT_OK) return st;
     const uint32_t slots = T * k;
@@ -199,7 +208,7 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     // down: y[s][h] = Wd[e_s] . act[s]
     st = gemv_grouped(ctx, "moe_down", RUNIT_FMT_Q4K, down, nullptr, E, h, ff, s.act, 1, s.y, idx, slots);
     if (st != RUNIT_OK) return st;
-    moe_combine_kernel<<<dim3((h + 255) / 256, T), 256, 0, ctx->stream>>>(s.y, wts, (const float*)residual, (float*)out, T, h, k);
+    runit_launch_chain(ctx, moe_combine_kernel, dim3((h + 255) / 256, T), dim3(256), (const float*)s.y, (const float*)wts, (const float*)residual, (float*)out, T, h, k);
     return runit_after_launch(ctx, "moe_combine");
 }
 
@@ -272,7 +281,7 @@ int32_t runit_moe_route_topk(runit_ctx_t* ctx, const void* logits, int32_t logit
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, logits && out_idx && out_w, "moe_route_topk: null pointer");
     RUNIT_REQUIRE(ctx, E > 0 && E <= 256 && k > 0 && k <= E && k <= 32 && T > 0, "moe_route_topk: E=%u k=%u T=%u unsupported", E, k, T);
-    route_topk_kernel<<<(T + 3) / 4, 128, 0, ctx->stream>>>(logits, logits_f16, E, k, renorm, T, (int32_t*)out_idx, (float*)out_w);
+    runit_launch_chain(ctx, route_topk_kernel, dim3((T + 3) / 4), dim3(128), logits, logits_f16, E, k, renorm, T, (int32_t*)out_idx, (float*)out_w);
     return runit_after_launch(ctx, "moe_route_topk");
 }
 

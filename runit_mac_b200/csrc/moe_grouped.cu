@@ -506,7 +506,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     } else if (warp < kDeqWarp0) {
         // ───────── epilogue ─────────
         // The four warps meet on a named barrier inside the loop, so they must leave it together: one thread waits
-        // for the accumulator and publishes the verdict (also on abort) to the other 127.
+        // for the accumulator and publishes the outcome (also on abort) to the other 127.
         const uint32_t quarter = warp & 3;
         volatile int* go = reinterpret_cast<volatile int*>(base_p + kOffCtrl + (holder - ctrl) + 8);
         uint32_t n = 0;
@@ -517,9 +517,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
             if (warp == kEpiWarp0 && lane == 0)
                 *go = (mbar_wait_timed(bar_accf, n & 1, abort_flag) && !*abort_flag) ? 1 : 0;
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int verdict = *go;
+            const int ready = *go;
             asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone has read it before the next item overwrites it
-            if (!verdict) break;
+            if (!ready) break;
             tc_fence_after_sync();
             const uint32_t taddr0 = tmem_base + ((quarter * 32) << 16);
 #pragma unroll 1

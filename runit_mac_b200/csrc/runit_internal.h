@@ -86,6 +86,24 @@ static inline int32_t runit_after_launch(runit_ctx* ctx, const char* what) {
     return RUNIT_OK;
 }
 
+// Launch of a small kernel of an operator chain.  With dependent launch enabled (tune.pdl != 0) the kernel may be
+// scheduled while its predecessor on the stream is still draining; every kernel launched through this helper
+// therefore begins with griddepcontrol.wait (grid_dependency_wait) before it touches memory.
+template <typename... KArgs, typename... Args>
+static inline void runit_launch_chain(runit_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl != 0 ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // errors surface in runit_after_launch
+}
+
 static inline bool runit_aligned(const void* p, size_t a) {
     return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }
