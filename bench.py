@@ -320,7 +320,7 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
             "finite": bool(torch.isfinite(out).all().item())}
 
 
-def run_extras(R, ctx, torch, dist, stream, rank, world, args):
+def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False):
     """Figures for the other rows of the path: one OLMoE-shaped MoE layer (1/16/256 tokens), the full
     OLMoE-shaped greedy decode (tok/s) and, at N>1, the row-sharded lm_head with its all-gather."""
     out = {}
@@ -353,7 +353,7 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args):
     ctx.flush()
     # MoE layer alone: 16 distinct layers per replay (3.6 GB of expert weights: nothing stays in L2)
     moe = {}
-    for T in (1, 16, 256):
+    for T in (() if decode_only else (1, 16, 256)):
         x = ctx.new_buffer(T * h * 4)
         R.fill_normal_f32(ctx, x, T * h, 5 + T, 1.0)
         o, idx = ctx.new_buffer(T * h * 4), ctx.new_buffer(T * k * 4)
@@ -374,27 +374,28 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args):
         moe["T%d" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3), "distinct_experts_last_layer": U,
                           "algorithmic_gbs": alg / (ms * 1e-3) / 1e9}
         g.destroy()
-    # the same layer at 256 tokens through the tensor-core block (bf16 operands)
-    T = 256
-    x = torch.randn(T, h, device="cuda")
-    o = torch.empty(T, h, device="cuda")
-    nbg = R.moe_grouped_scratch_bytes(ctx, T, h, ff, E, k)
-    scratch = ctx.new_buffer(nbg)
-    eg, ed = E * ff * rb(h), E * h * rb(ff)
-    torch.cuda.synchronize()
+    if not decode_only:
+        # the same layer at 256 tokens through the tensor-core block (bf16 operands)
+        T = 256
+        x = torch.randn(T, h, device="cuda")
+        o = torch.empty(T, h, device="cuda")
+        nbg = R.moe_grouped_scratch_bytes(ctx, T, h, ff, E, k)
+        scratch = ctx.new_buffer(nbg)
+        eg, ed = E * ff * rb(h), E * h * rb(ff)
+        torch.cuda.synchronize()
 
-    def run_layers_tc():
-        for l in range(L):
-            R.moe_layer_q4k_bf16(ctx, dev["router"].ptr + l * E * h * 4, dev["gate"].ptr + l * eg, dev["up"].ptr + l * eg,
-                                 dev["down"].ptr + l * ed, x, None, o, None, None, scratch, nbg, T, h, ff, E, k, 0)
-    run_layers_tc()
-    ctx.flush()
-    ms = timed(run_layers_tc, 5) / L
-    moe["T256_tensor_cores_bf16"] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
-    out["moe_layer_olmoe_q4k"] = moe
-    scratch.free()
-    # Qwen3-MoE-shaped batched block (4096 tokens, 128 experts, Zipf routing) on the tensor cores
-    out["moe_block_qwen3_shape_bf16"] = run_block(R, ctx, torch, stream, T=4096, reps=10)
+        def run_layers_tc():
+            for l in range(L):
+                R.moe_layer_q4k_bf16(ctx, dev["router"].ptr + l * E * h * 4, dev["gate"].ptr + l * eg, dev["up"].ptr + l * eg,
+                                     dev["down"].ptr + l * ed, x, None, o, None, None, scratch, nbg, T, h, ff, E, k, 0)
+        run_layers_tc()
+        ctx.flush()
+        ms = timed(run_layers_tc, 5) / L
+        moe["T256_tensor_cores_bf16"] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
+        out["moe_layer_olmoe_q4k"] = moe
+        scratch.free()
+        # Qwen3-MoE-shaped batched block (4096 tokens, 128 experts, Zipf routing) on the tensor cores
+        out["moe_block_qwen3_shape_bf16"] = run_block(R, ctx, torch, stream, T=4096, reps=10)
     # full OLMoE-shaped greedy decode: 128-token prompt, 64 greedy steps, f16 KV, no host round trips
     cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=50304, n_experts=E, top_k=k, ff=ff,
                      max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)
@@ -458,6 +459,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE-layer / OLMoE-decode / sharded lm_head figures")
     ap.add_argument("--one", default="", help="fmt,m,k[,batch]: launch this one GEMV shape three times and exit (for ncu captures)")
     ap.add_argument("--block", default="", help="T: run the Qwen3-MoE-shaped batched MoE block on T tokens, print its figures and exit")
+    ap.add_argument("--decode", action="store_true", help="only the OLMoE-shaped greedy decode figure (tok/s), then exit")
     ap.add_argument("--shapes", action="store_true", help="per-shape GEMV table (one JSON line per shape) instead of the headline run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -498,6 +500,10 @@ def main():
         return
     if args.shapes:
         return run_shapes(R, ctx, torch, stream)
+    if args.decode:
+        ex = run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=True)
+        print(json.dumps(ex["olmoe_decode_q4k"]), flush=True)
+        return
     if args.block:
         print(json.dumps(run_block(R, ctx, torch, stream, T=int(args.block), reps=max(args.steps // 2, 3))), flush=True)
         return

@@ -22,6 +22,7 @@ struct runit_model {
     __half* vc = nullptr;
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *logits = nullptr;
     float* attn_part = nullptr;
+    uint32_t* attn_counters = nullptr;   // one ticket counter per head, zero at rest
     void* moe_scratch = nullptr;
     size_t moe_scratch_bytes = 0;
     int32_t* state = nullptr;   // [0] = token, [1] = pos, [2] = step counter
@@ -98,18 +99,17 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         const uint8_t* wv = (const uint8_t*)m->w.wv + (size_t)l * kv_dim * rb_h;
         const uint8_t* wo = (const uint8_t*)m->w.wo + (size_t)l * h * rb_q;
         // attention block (forward.rs:1833-1896)
-        if ((st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.attn_norm + (size_t)l * h, false, c.eps, h, 1))) return st;
+        // the attention norm of layer l > 0 is produced by the previous layer's combine kernel
+        if (l == 0 && (st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.attn_norm, false, c.eps, h, 1))) return st;
         const void* ws[3] = {wq, wk, wv};
         void* ys[3] = {m->q, m->k, m->v};
         const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
         if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, m->xn, h))) return st;
-        if ((st = launch_rope(ctx, m->q, m->k, hd, c.n_heads, c.n_kv_heads, 0, pos_ptr, c.theta))) return st;
         __half* kcl = m->kc + (size_t)l * kv_layer;
         __half* vcl = m->vc + (size_t)l * kv_layer;
-        if ((st = launch_kv_copy(ctx, m->k, false, kcl, true, 0, pos_ptr, c.max_seq, hd, c.n_kv_heads))) return st;
-        if ((st = launch_kv_copy(ctx, m->v, false, vcl, true, 0, pos_ptr, c.max_seq, hd, c.n_kv_heads))) return st;
+        if ((st = launch_rope_kv(ctx, m->q, m->k, m->v, kcl, vcl, hd, c.n_heads, c.n_kv_heads, pos_ptr, c.theta, c.max_seq))) return st;
         if ((st = launch_decode_attention(ctx, 0, 1, m->q, kcl, vcl, m->ao, m->attn_part, m->nsplit, 1, 0, pos_ptr, c.n_heads,
-                                          c.n_kv_heads, hd, c.max_seq)))
+                                          c.n_kv_heads, hd, c.max_seq, m->attn_counters)))
             return st;
         if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, m->x, m->x, h, q_dim))) return st;
         // MoE block (forward.rs:1898-1931)
@@ -118,12 +118,16 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         if ((st = moe_layer_q4k_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
                                      (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
                                      (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr,
-                                     m->moe_scratch, m->moe_scratch_bytes, 1, h, c.ff, c.n_experts, c.top_k, c.renorm)))
+                                     m->moe_scratch, m->moe_scratch_bytes, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
+                                     // followed by the next operator's RMSNorm (next layer's attention norm, or the output norm
+                                     // before lm_head)
+                                     l + 1 < c.n_layers ? (const float*)m->w.attn_norm + (size_t)(l + 1) * h
+                                                        : (with_logits ? (const float*)m->w.out_norm : nullptr),
+                                     m->xn, c.eps, reinterpret_cast<uint32_t*>(m->state + 8))))   // state[8]: ticket counter, zero at rest
             return st;
     }
     int32_t* argmax_out = m->state + 3;
     if (with_logits) {
-        if ((st = launch_rms_norm(ctx, m->x, m->xn, m->w.out_norm, false, c.eps, h, 1))) return st;
         if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->xn, m->logits, nullptr, c.vocab, h))) return st;
         if ((st = launch_argmax(ctx, m->logits, false, argmax_out, c.vocab))) return st;
     }
@@ -189,11 +193,13 @@ int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const r
     A((void**)&m->v, kv_dim * 4); A((void**)&m->ao, q_dim * 4); A((void**)&m->logits, (size_t)c.vocab * 4);
     A((void**)&m->attn_part, (size_t)c.n_heads * m->nsplit * (c.head_dim + 2) * 4);
     A(&m->moe_scratch, m->moe_scratch_bytes);
+    A((void**)&m->attn_counters, (size_t)c.n_heads * 4);
     A((void**)&m->state, 64); A((void**)&m->forced, (size_t)m->forced_cap * 4); A((void**)&m->out_tokens, (size_t)m->out_cap * 4);
     if (st == RUNIT_OK) {
         cudaMemsetAsync(m->kc, 0, kv_elems * 2, ctx->stream);
         cudaMemsetAsync(m->vc, 0, kv_elems * 2, ctx->stream);
         cudaMemsetAsync(m->state, 0, 64, ctx->stream);
+        cudaMemsetAsync(m->attn_counters, 0, (size_t)c.n_heads * 4, ctx->stream);
         cudaMemsetAsync(m->forced, 0xFF, (size_t)m->forced_cap * 4, ctx->stream);   // nothing forced
         // one eager step configures every kernel (shared-memory attributes, tensor maps) before capture
         st = issue_step(m, true, 0);
@@ -283,8 +289,8 @@ int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uin
 void* runit_model_logits(runit_model_t* m) { return m ? (void*)m->logits : nullptr; }
 uint64_t runit_model_launches_per_token(runit_model_t* m) {
     if (!m) return 0;
-    // embed + per layer (norm, qkv, rope, 2 kv, attention+combine, o-proj, norm, 5 MoE) + norm, lm_head, argmax, advance
-    return 1 + (uint64_t)m->cfg.n_layers * (1 + 1 + 1 + 2 + (m->nsplit > 1 ? 2 : 1) + 1 + 1 + 5) + 4;
+    // embed, first norm + per layer (qkv, rope+kv, attention, o-proj, norm, 4 MoE + next norm) + lm_head, argmax, advance
+    return 2 + (uint64_t)m->cfg.n_layers * (1 + 1 + 1 + 1 + 1 + 5) + 3;
 }
 
 }  // extern "C"

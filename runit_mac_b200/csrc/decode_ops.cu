@@ -75,6 +75,42 @@ __global__ void rope_qk_kernel(float* q, float* k, uint32_t head_dim, uint32_t q
     }
 }
 
+// The same rotation, then K (rotated) and V of this position go into the f16 caches (activation.metal:13-44): one launch
+// instead of three in the decode chain.  Same arithmetic per element as rope_qk_kernel + kv_copy_kernel<float, __half>.
+__global__ void rope_kv_kernel(float* q, float* k, const float* __restrict__ v, __half* __restrict__ kc, __half* __restrict__ vc,
+                               uint32_t head_dim, uint32_t q_heads, uint32_t kv_heads, const int32_t* pos_ptr, float theta,
+                               uint32_t max_seq) {
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const uint32_t d = threadIdx.x, hid = blockIdx.x, half = head_dim / 2;
+    if (d >= half) return;
+    const uint32_t pos = (uint32_t)*pos_ptr;
+    const float freq = 1.0f / powf(theta, (float)(2 * d) / (float)head_dim);
+    const float angle = (float)pos * freq;
+    const float c = cosf(angle), s = sinf(angle);
+    if (hid < q_heads) {
+        float* p = q + (size_t)hid * head_dim;
+        const float a = p[d], b = p[d + half];
+        p[d] = a * c - b * s;
+        p[d + half] = a * s + b * c;
+    }
+    if (hid < kv_heads) {
+        float* p = k + (size_t)hid * head_dim;
+        const float a = p[d], b = p[d + half];
+        const float r0 = a * c - b * s, r1 = a * s + b * c;
+        p[d] = r0;
+        p[d + half] = r1;
+        if (pos < max_seq) {
+            const size_t o = ((size_t)hid * max_seq + pos) * head_dim;
+            kc[o + d] = __float2half_rn(r0);
+            kc[o + d + half] = __float2half_rn(r1);
+            const float* vp = v + (size_t)hid * head_dim;
+            vc[o + d] = __float2half_rn(vp[d]);
+            vc[o + d + half] = __float2half_rn(vp[d + half]);
+        }
+    }
+}
+
 // dst[(h*max_seq + pos)*hd + d] = src[h*hd + d]   (activation.metal:13-44)
 template <typename S, typename D>
 __global__ void kv_copy_kernel(const S* __restrict__ src, D* __restrict__ dst, uint32_t pos_val, const int32_t* pos_ptr,
@@ -96,11 +132,28 @@ __device__ __forceinline__ float ldf(const T* p, size_t i) { return (float)p[i];
 //   grid (heads, nsplit, batch), 128 threads.  Score phase: lane <-> KV position (32 positions per warp
 //   step, full dot product per lane); value phase: lane <-> output dims, probabilities broadcast by
 //   shuffle.  nsplit == 1: writes the normalised output; else partial (m, l, o[hd]) per split.
+// Eight consecutive cache elements (16-byte aligned: rows are 256 or 512 bytes) as floats.
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
 template <typename TQ, typename TKV, typename TO, int DPL>
 __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__ Q, const TKV* __restrict__ K,
                                                            const TKV* __restrict__ V, TO* __restrict__ O, float* part,
                                                            uint32_t kv_len_val, const int32_t* pos_ptr, uint32_t heads,
-                                                           uint32_t kv_heads, uint32_t kv_head_stride, float scale) {
+                                                           uint32_t kv_heads, uint32_t kv_head_stride, float scale,
+                                                           uint32_t* counters) {
     grid_dependency_wait();      // inputs come from the previous kernel of the chain
     grid_launch_dependents();
     constexpr int HD = 32 * DPL;
@@ -124,12 +177,18 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
         const uint32_t p = g + lane;
         float score = -INFINITY;
         if (p < end) {
+            // 16-byte loads of the key row; the two accumulators take even and odd dims in ascending order
             const TKV* kr = K + kvbase + (size_t)p * HD;
             float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-            for (int d = 0; d < HD; d += 2) {
-                a0 = fmaf(qs[d], (float)kr[d], a0);
-                a1 = fmaf(qs[d + 1], (float)kr[d + 1], a1);
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {   // fully unrolled: all loads of the row are in flight together
+                float kv8[8];
+                load8(kr + d, kv8);
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    a0 = fmaf(qs[d + i], kv8[i], a0);
+                    a1 = fmaf(qs[d + i + 1], kv8[i + 1], a1);
+                }
             }
             score = (a0 + a1) * scale;
         }
@@ -140,11 +199,25 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
 #pragma unroll
         for (int i = 0; i < DPL; i++) o[i] *= resc;
         const uint32_t cnt = min(32u, end - g);
-        for (uint32_t j = 0; j < cnt; j++) {
-            const float pj = __shfl_sync(0xffffffffu, pe, j);
-            const TKV* vr = V + kvbase + (size_t)(g + j) * HD + lane * DPL;
+        // eight value rows are loaded before they are used (positions past the end read row g and get weight 0:
+        // pe is 0 there), the accumulation order stays j ascending
+        for (uint32_t j0 = 0; j0 < cnt; j0 += 8) {
+            float vv[8][DPL];
 #pragma unroll
-            for (int i = 0; i < DPL; i++) o[i] = fmaf(pj, (float)vr[i], o[i]);
+            for (int jj = 0; jj < 8; jj++) {
+                const uint32_t j = (j0 + jj < cnt) ? j0 + jj : 0;
+                const TKV* vr = V + kvbase + (size_t)(g + j) * HD + lane * DPL;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) vv[jj][i] = (float)vr[i];
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; jj++) {
+                if (j0 + jj < cnt) {
+                    const float pj = __shfl_sync(0xffffffffu, pe, j0 + jj);
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) o[i] = fmaf(pj, vv[jj][i], o[i]);
+                }
+            }
         }
         m = m_new;
     }
@@ -174,6 +247,35 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
             if (lane == 0) { pp[0] = M; pp[1] = Lt; }
 #pragma unroll
             for (int i = 0; i < DPL; i++) pp[2 + lane * DPL + i] = acc[i];
+        }
+    }
+    // With a ticket counter per (batch, head) the CTA that finishes last merges the partials itself (same order and
+    // arithmetic as decode_attn_combine_kernel) and puts the counter back to zero: no second launch.
+    if (nsplit > 1 && counters) {
+        __shared__ uint32_t s_last;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            s_last = atomicAdd(&counters[batch * heads + head], 1u) == nsplit - 1;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const uint32_t d = threadIdx.x;
+            if (d < HD) {
+                const float* pp = part + ((size_t)batch * heads + head) * nsplit * (HD + 2);
+                float Mx = -INFINITY;
+                for (uint32_t sp = 0; sp < nsplit; sp++) Mx = fmaxf(Mx, pp[sp * (HD + 2)]);
+                float L = 0.f, a = 0.f;
+                for (uint32_t sp = 0; sp < nsplit; sp++) {
+                    const float ms = pp[sp * (HD + 2)];
+                    const float f = (ms == -INFINITY) ? 0.f : expf(ms - Mx);
+                    L += pp[sp * (HD + 2) + 1] * f;
+                    a += pp[sp * (HD + 2) + 2 + d] * f;
+                }
+                O[qbase + d] = (TO)(L > 0.f ? a / L : 0.f);
+            }
+            if (threadIdx.x == 0) counters[batch * heads + head] = 0;
         }
     }
 }
@@ -249,6 +351,14 @@ int32_t launch_rope(runit_ctx* ctx, float* q, float* k, uint32_t hd, uint32_t qh
     return runit_after_launch(ctx, "fused_rope_qk_f32");
 }
 
+int32_t launch_rope_kv(runit_ctx* ctx, float* q, float* k, const float* v, void* kcache, void* vcache, uint32_t hd, uint32_t qh,
+                       uint32_t kvh, const int32_t* pos_ptr, float theta, uint32_t max_seq) {
+    const uint32_t hmax = qh > kvh ? qh : kvh;
+    runit_launch_chain(ctx, rope_kv_kernel, dim3(hmax), dim3(hd / 2), q, k, v, (__half*)kcache, (__half*)vcache, hd, qh, kvh, pos_ptr,
+                       theta, max_seq);
+    return runit_after_launch(ctx, "rope_kv");
+}
+
 int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst, bool dst_f16, uint32_t pos,
                        const int32_t* pos_ptr, uint32_t max_seq, uint32_t hd, uint32_t kvh) {
     dim3 grid((hd + 127) / 128, kvh);
@@ -262,12 +372,12 @@ int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst,
 template <typename TQ, typename TKV, typename TO>
 static int32_t attn_typed(runit_ctx* ctx, const void* q, const void* k, const void* v, void* out, float* part, uint32_t nsplit,
                           uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr, uint32_t heads, uint32_t kv_heads,
-                          uint32_t hd, uint32_t stride) {
+                          uint32_t hd, uint32_t stride, uint32_t* counters) {
     const float scale = 1.0f / sqrtf((float)hd);   // dispatch.rs:1588
     dim3 grid(heads, nsplit, batch);
 #define ATTN_CASE(D)                                                                                                   \
     runit_launch_chain(ctx, decode_attn_kernel<TQ, TKV, TO, D>, dim3(grid), dim3(128), (const TQ*)q, (const TKV*)k, (const TKV*)v, (TO*)out, \
-                                                                      part, kv_len, pos_ptr, heads, kv_heads, stride, scale)
+                                                                      part, kv_len, pos_ptr, heads, kv_heads, stride, scale, counters)
     switch (hd) {
         case 32: ATTN_CASE(1); break;
         case 64: ATTN_CASE(2); break;
@@ -277,20 +387,21 @@ static int32_t attn_typed(runit_ctx* ctx, const void* q, const void* k, const vo
     }
 #undef ATTN_CASE
     int32_t st = runit_after_launch(ctx, "decode_attention");
-    if (st != RUNIT_OK || nsplit == 1) return st;
+    if (st != RUNIT_OK || nsplit == 1 || counters) return st;
     runit_launch_chain(ctx, decode_attn_combine_kernel<TO>, dim3(batch * heads), dim3(hd), part, (TO*)out, nsplit, hd);
     return runit_after_launch(ctx, "decode_attention_combine");
 }
 
 int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const void* q, const void* k, const void* v, void* out,
                                 float* part, uint32_t nsplit, uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr,
-                                uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride) {
+                                uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride, uint32_t* counters) {
+    RUNIT_REQUIRE(ctx, runit_aligned(k, 16) && runit_aligned(v, 16), "decode_attention: key/value cache must be 16-byte aligned");
     if (q_kind == 0 && kv_kind == 0)
-        return attn_typed<float, float, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride);
+        return attn_typed<float, float, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride, counters);
     if (q_kind == 1 && kv_kind == 1)
-        return attn_typed<__half, __half, __half>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride);
+        return attn_typed<__half, __half, __half>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride, counters);
     if (q_kind == 0 && kv_kind == 1)
-        return attn_typed<float, __half, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride);
+        return attn_typed<float, __half, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride, counters);
     return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "decode_attention: f16 query with f32 cache");
 }
 
@@ -362,7 +473,7 @@ int32_t runit_kv_copy_to_cache_f32_f16(runit_ctx_t* ctx, const void* src, void* 
                       #NAME ": bad shape");                                                                              \
         RUNIT_REQUIRE(ctx, kv_len <= kv_head_stride, #NAME ": kv_len %u exceeds the cache stride %u", kv_len, kv_head_stride); \
         return launch_decode_attention(ctx, QK, KVK, q, k, v, out, nullptr, 1, batch, kv_len, nullptr, num_heads,        \
-                                       num_kv_heads, head_dim, kv_head_stride);                                          \
+                                       num_kv_heads, head_dim, kv_head_stride, nullptr);                                 \
     }
 ATTN_ENTRY(decode_attention_f32, 0, 0)
 ATTN_ENTRY(decode_attention_f16, 1, 1)

@@ -10,12 +10,16 @@ int32_t launch_rms_norm(runit_ctx* ctx, const float* x, float* y, const void* ga
                         uint32_t hidden, uint32_t rows);
 int32_t launch_rope(runit_ctx* ctx, float* q, float* k, uint32_t hd, uint32_t qh, uint32_t kvh, uint32_t pos,
                     const int32_t* pos_ptr, float theta);
+// rotary embedding of q and k, then k and v of this position into the f16 caches, in one launch (decode)
+int32_t launch_rope_kv(runit_ctx* ctx, float* q, float* k, const float* v, void* kcache, void* vcache, uint32_t hd, uint32_t qh,
+                       uint32_t kvh, const int32_t* pos_ptr, float theta, uint32_t max_seq);
 int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst, bool dst_f16, uint32_t pos,
                        const int32_t* pos_ptr, uint32_t max_seq, uint32_t hd, uint32_t kvh);
 // q_kind / kv_kind: 0 = f32, 1 = f16.  part: scratch of batch*heads*nsplit*(hd+2) floats when nsplit > 1.
 int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const void* q, const void* k, const void* v, void* out,
                                 float* part, uint32_t nsplit, uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr,
-                                uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride);
+                                uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride,
+                                uint32_t* counters = nullptr);   // batch*heads zeroed words: the last split merges, no combine launch
 int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* result, uint32_t n);
 
 // gemv.cu: one fused-dequant GEMV with up to three row segments sharing the input (Q|K|V) — any format.
@@ -26,7 +30,9 @@ int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, con
 // moe.cu
 int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
-                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm);
+                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
+                           const float* next_gamma, float* next_xn, float next_eps,    // next_*: also RMSNorm the result
+                           uint32_t* route_counter);   // zeroed word: router and routing in one launch (T == 1)
 size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);
 
 }  // namespace runit

@@ -64,21 +64,19 @@ __global__ void __launch_bounds__(256) router_f32_generic_kernel(const float* __
 // softmax over all experts, then the top-k probabilities in descending order (ties: lowest index),
 // optionally renormalised to sum 1 (crates/engine/src/forward.rs:2420-2448).  One warp per token,
 // E <= 256.  in_f16 != 0: the logits are f16 (the reference's router output dtype).
-__global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict__ logits, int in_f16, uint32_t E, uint32_t k,
-                                                          int renorm, uint32_t T, int32_t* __restrict__ out_idx,
-                                                          float* __restrict__ out_w) {
-    grid_dependency_wait();      // inputs come from the previous kernel of the chain
-    grid_launch_dependents();
-    const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= T) return;
-    float v[8];
+// Routing of one token by one warp; `logits` points at the token's E logits (global or shared memory),
+// out_idx / out_w at its k outputs.
+template <int NG>   // groups of 32 experts that can be non-empty (E <= 32 * NG); skipping the empty ones adds exact zeros less
+__device__ __forceinline__ void route_topk_groups(const void* logits, int in_f16, uint32_t E, uint32_t k, int renorm, uint32_t lane,
+                                                int32_t* out_idx, float* out_w) {
+    float v[NG];
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < NG; i++) {
         const uint32_t e = lane + 32 * i;
         float lv = -INFINITY;
-        if (e < E) lv = in_f16 ? __half2float(reinterpret_cast<const __half*>(logits)[(size_t)t * E + e])
-                               : reinterpret_cast<const float*>(logits)[(size_t)t * E + e];
+        if (e < E) lv = in_f16 ? __half2float(reinterpret_cast<const __half*>(logits)[e])
+                               : reinterpret_cast<const float*>(logits)[e];
         v[i] = lv;
         mx = fmaxf(mx, lv);
     }
@@ -87,16 +85,16 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict_
     // exp values; the sum runs over experts in index order so that it is reproducible
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = (lane + 32 * i < E) ? expf(v[i] - mx) : 0.f;
+    for (int i = 0; i < NG; i++) v[i] = (lane + 32 * i < E) ? expf(v[i] - mx) : 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < NG; i++) {
         float part = v[i];   // 0 beyond E; a fixed shuffle tree per group of 32 experts: deterministic
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
         sum += part;
     }
 #pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = v[i] / sum;   // probabilities (0 beyond E)
+    for (int i = 0; i < NG; i++) v[i] = v[i] / sum;   // probabilities (0 beyond E)
     uint32_t taken = 0;
     float wsum = 0.f;
     float my_w = 0.f;   // lane s keeps the s-th selected weight (k <= 32)
@@ -105,7 +103,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict_
         float bv = -1.f;
         uint32_t bi = 0xFFFFFFFFu;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < NG; i++) {
             const uint32_t e = lane + 32 * i;
             if (e < E && !((taken >> i) & 1u) && (v[i] > bv)) { bv = v[i]; bi = e; }
         }
@@ -122,8 +120,69 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict_
     if (lane < k) {
         float wv = my_w;
         if (renorm && wsum > 0.f) wv = wv / wsum;
-        out_idx[(size_t)t * k + lane] = my_i;
-        out_w[(size_t)t * k + lane] = wv;
+        out_idx[lane] = my_i;
+        out_w[lane] = wv;
+    }
+}
+
+__device__ __forceinline__ void route_topk_warp(const void* logits, int in_f16, uint32_t E, uint32_t k, int renorm, uint32_t lane,
+                                                int32_t* out_idx, float* out_w) {
+    if (E <= 32) route_topk_groups<1>(logits, in_f16, E, k, renorm, lane, out_idx, out_w);
+    else if (E <= 64) route_topk_groups<2>(logits, in_f16, E, k, renorm, lane, out_idx, out_w);
+    else if (E <= 128) route_topk_groups<4>(logits, in_f16, E, k, renorm, lane, out_idx, out_w);
+    else route_topk_groups<8>(logits, in_f16, E, k, renorm, lane, out_idx, out_w);
+}
+
+__global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict__ logits, int in_f16, uint32_t E, uint32_t k,
+                                                          int renorm, uint32_t T, int32_t* __restrict__ out_idx,
+                                                          float* __restrict__ out_w) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
+    const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const void* row = in_f16 ? (const void*)(reinterpret_cast<const __half*>(logits) + (size_t)t * E)
+                             : (const void*)(reinterpret_cast<const float*>(logits) + (size_t)t * E);
+    route_topk_warp(row, in_f16, E, k, renorm, lane, out_idx + (size_t)t * k, out_w + (size_t)t * k);
+}
+
+// Router and routing of ONE token in one launch (decode): CTAs of 8 warps compute 8 logits each with exactly the
+// arithmetic of router_f32_kernel (same bits), publish them and take a ticket; the CTA that draws the last ticket
+// routes from the complete logits and puts the ticket counter back to zero.  *counter must be zero before the
+// first launch.
+template <int KPL>
+__global__ void __launch_bounds__(256) route_fused_kernel(const float* __restrict__ w, const float* __restrict__ x,
+                                                           float* logits, uint32_t E, uint32_t K, uint32_t k, int renorm,
+                                                           int32_t* __restrict__ out_idx, float* __restrict__ out_w, uint32_t* counter) {
+    grid_dependency_wait();
+    grid_launch_dependents();
+    __shared__ uint32_t s_last;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t e = blockIdx.x * 8 + warp;
+    if (e < E) {
+        const float4* xr = reinterpret_cast<const float4*>(x);
+        const float4* wrow = reinterpret_cast<const float4*>(w + (size_t)e * K);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < KPL / 4; i++) {
+            const float4 wv = wrow[lane + 32 * i], v = xr[lane + 32 * i];
+            a0 = fmaf(wv.x, v.x, a0); a1 = fmaf(wv.y, v.y, a1);
+            a2 = fmaf(wv.z, v.z, a2); a3 = fmaf(wv.w, v.w, a3);
+        }
+        float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) logits[e] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();                                   // this CTA's logits are visible before its ticket
+        s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last && warp == 0) {
+        __threadfence();
+        route_topk_warp(logits, 0, E, k, renorm, lane, out_idx, out_w);
+        if (lane == 0) *counter = 0;
     }
 }
 
@@ -185,7 +244,8 @@ size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, u
 // The whole block; scratch carved from `scratch`.
 int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
-                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {
+                           size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
+                           const float* next_gamma, float* next_xn, float next_eps, uint32_t* route_counter) {
     RUNIT_REQUIRE(ctx, router_w && gate && up && down && x && out && scratch, "moe_layer_q4k: null pointer");
     RUNIT_REQUIRE(ctx, T > 0 && T <= 65536, "moe_layer_q4k: T=%u out of range", T);
     RUNIT_REQUIRE(ctx, h % 256 == 0 && ff % 256 == 0 && h > 0 && ff > 0, "moe_layer_q4k: h=%u, ff=%u must be multiples of 256", h, ff);
@@ -194,13 +254,23 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     const MoeScratch s = moe_carve(scratch, T, h, ff, E, k);
     if (s.bytes > scratch_bytes)
         return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "moe_layer_q4k: scratch has %zu bytes, needs %zu", scratch_bytes, s.bytes);
-    int32_t st = moe_router(ctx, (const float*)router_w, (const float*)x, s.logits, E, h, T);
-    if (st != RUNIT_OK) return st;
     int32_t* idx = idx_out ? idx_out : s.idx;
     float* wts = w_out ? w_out : s.w;
-    runit_launch_chain(ctx, route_topk_kernel, dim3((T + 3) / 4), dim3(128), s.logits, 0, E, k, renorm, T, idx, wts);
-    st = runit_after_launch(ctx, "moe_route_topk");
-    if (st != RUNIT_OK) return st;
+    int32_t st;
+    if (route_counter && T == 1 && (h == 1024 || h == 2048 || h == 4096) && runit_aligned(router_w, 16) && runit_aligned(x, 16)) {
+        // one token: router GEMV and routing in one launch (same bits as the two launches below)
+        const dim3 grid((E + 7) / 8);
+        if (h == 2048) runit_launch_chain(ctx, route_fused_kernel<64>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
+        else if (h == 1024) runit_launch_chain(ctx, route_fused_kernel<32>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
+        else runit_launch_chain(ctx, route_fused_kernel<128>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
+        if ((st = runit_after_launch(ctx, "moe_route_fused")) != RUNIT_OK) return st;
+    } else {
+        st = moe_router(ctx, (const float*)router_w, (const float*)x, s.logits, E, h, T);
+        if (st != RUNIT_OK) return st;
+        runit_launch_chain(ctx, route_topk_kernel, dim3((T + 3) / 4), dim3(128), (const void*)s.logits, 0, E, k, (int)renorm, T, idx, wts);
+        st = runit_after_launch(ctx, "moe_route_topk");
+        if (st != RUNIT_OK) return st;
+    }
     const uint32_t slots = T * k;
     // gate+up+SiLU for every (token, expert) slot: act[s][ff]
     st = gemv_grouped(ctx, "moe_gate_up", RUNIT_FMT_Q4K, gate, up, E, ff, h, x, k, s.act, idx, slots);
@@ -209,7 +279,9 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     st = gemv_grouped(ctx, "moe_down", RUNIT_FMT_Q4K, down, nullptr, E, h, ff, s.act, 1, s.y, idx, slots);
     if (st != RUNIT_OK) return st;
     runit_launch_chain(ctx, moe_combine_kernel, dim3((h + 255) / 256, T), dim3(256), (const float*)s.y, (const float*)wts, (const float*)residual, (float*)out, T, h, k);
-    return runit_after_launch(ctx, "moe_combine");
+    st = runit_after_launch(ctx, "moe_combine");
+    if (st != RUNIT_OK || !next_gamma) return st;
+    return launch_rms_norm(ctx, (const float*)out, next_xn, next_gamma, false, next_eps, h, T);
 }
 
 // ───────────────────────── built-in scratch (entry point that allocates nothing) ─────────────────────────
@@ -262,7 +334,7 @@ int32_t runit_moe_layer_q4k_static(runit_ctx_t* ctx, const void* router_w, const
     int32_t st = moe_static_scratch(ctx, &scratch);
     if (st != RUNIT_OK) return st;
     return moe_layer_q4k_impl(ctx, router_w, gate, up, down, x, residual, out, (int32_t*)idx_out, (float*)w_out, scratch,
-                              kMoeStaticScratchBytes, T, h, ff, E, k, renorm);
+                              kMoeStaticScratchBytes, T, h, ff, E, k, renorm, nullptr, nullptr, 0.f, nullptr);
 }
 
 size_t runit_moe_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
@@ -303,7 +375,7 @@ int32_t runit_moe_layer_q4k(runit_ctx_t* ctx, const void* router_w, const void* 
                             size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     return moe_layer_q4k_impl(ctx, router_w, gate, up, down, x, residual, out, (int32_t*)idx_out, (float*)w_out, scratch,
-                              scratch_bytes, T, h, ff, E, k, renorm);
+                              scratch_bytes, T, h, ff, E, k, renorm, nullptr, nullptr, 0.f, nullptr);
 }
 
 }  // extern "C"
