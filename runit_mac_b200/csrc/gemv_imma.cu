@@ -73,31 +73,29 @@ struct Args {
 };
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 __device__ __forceinline__ void mma_u8u8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
+// Shared-memory reads are plain C++ loads through generic pointers: the compiler may reorder them among themselves and
+// around the MMAs (instruction-level parallelism inside a warp), while the "memory" clobber of the barrier wait keeps
+// them behind the wait.
+__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 // One k32 tile: A = nibbles of rows (g, g+8), B = the activation block; adds the scaled tile into acc.
 // sw0/sw1, mw0/mw1: weight scale and min of rows g / g+8 for this block; xs/xm: activation scale and block sum of
 // columns 2t, 2t+1 (packed float2 loads).
-__device__ __forceinline__ void tile_mma(float (&acc)[4], const uint32_t (&a)[4], uint32_t xaddr, uint32_t saddr, float sw0, float mw0,
-                                         float sw1, float mw1) {
-    uint32_t bh0, bh1, bl0, bl1;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(bh0), "=r"(bh1), "=r"(bl0), "=r"(bl1) : "r"(xaddr));
-    float xs0, xs1, xm0, xm1;
-    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(xs0), "=f"(xs1) : "r"(saddr));
-    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(xm0), "=f"(xm1) : "r"(saddr + 256));
+__device__ __forceinline__ void tile_mma(float (&acc)[4], const uint32_t (&a)[4], const uint8_t* xaddr, const uint8_t* saddr, float sw0,
+                                         float mw0, float sw1, float mw1) {
+    const uint4 bf = *reinterpret_cast<const uint4*>(xaddr);
+    const uint32_t bh0 = bf.x, bh1 = bf.y, bl0 = bf.z, bl1 = bf.w;
+    const float2 xs = *reinterpret_cast<const float2*>(saddr), xm = *reinterpret_cast<const float2*>(saddr + 256);
+    const float xs0 = xs.x, xs1 = xs.y, xm0 = xm.x, xm1 = xm.y;
     int ch[4], cl[4];
     mma_u8s8(ch, a, bh0, bh1);
     mma_u8u8(cl, a, bl0, bl1);
@@ -118,6 +116,7 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     __shared__ __align__(8) uint64_t bars[2 * kStages];
     __shared__ float red[4 * RW][8];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    const uint8_t* base_p = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const uint32_t crank = a.csplit > 1 ? cluster_ctarank() : 0;
     const uint32_t tile = blockIdx.x / a.csplit;
@@ -170,20 +169,19 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
             issue(j);
         }
         if (!mbar_wait(bar_full + 8 * s, (i / kStages) & 1)) { timed_out = true; break; }
-        const uint32_t sb = base + s * STAGE;
-        const uint32_t wb = sb + kUnitBytes + warp * WBYTES;
-        const uint32_t xb = sb + (g * 4 + t) * 16;       // + bt * 512: limbs of block bt for column g, K quarter t
-        const uint32_t scb = sb + 4096 + (2 * t) * 4;    // + bt * 32: scales of columns 2t, 2t+1
+        const uint8_t* sb = base_p + s * STAGE;
+        const uint8_t* wb = sb + kUnitBytes + warp * WBYTES;
+        const uint8_t* xb = sb + (g * 4 + t) * 16;       // + bt * 512: limbs of block bt for column g, K quarter t
+        const uint8_t* scb = sb + 4096 + (2 * t) * 4;    // + bt * 32: scales of columns 2t, 2t+1
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
-            const uint32_t r0 = wb + (mt * 16 + g) * 144, r1 = r0 + 8 * 144;
+            const uint8_t* r0 = wb + (mt * 16 + g) * 144;
+            const uint8_t* r1 = r0 + 8 * 144;
             if (FMT == RUNIT_FMT_Q4K) {
-                uint32_t h0[4], h1[4];
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h0[0]), "=r"(h0[1]), "=r"(h0[2]), "=r"(h0[3]) : "r"(r0));
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h1[0]), "=r"(h1[1]), "=r"(h1[2]), "=r"(h1[3]) : "r"(r1));
-                const float d0 = half_bits_to_float(h0[0]), n0 = half_bits_to_float(h0[0] >> 16);
-                const float d1 = half_bits_to_float(h1[0]), n1 = half_bits_to_float(h1[0] >> 16);
-                const Q4KScales s0 = q4k_unpack_scales(h0[1], h0[2], h0[3]), s1 = q4k_unpack_scales(h1[1], h1[2], h1[3]);
+                const uint4 h0 = *reinterpret_cast<const uint4*>(r0), h1 = *reinterpret_cast<const uint4*>(r1);
+                const float d0 = half_bits_to_float(h0.x), n0 = half_bits_to_float(h0.x >> 16);
+                const float d1 = half_bits_to_float(h1.x), n1 = half_bits_to_float(h1.x >> 16);
+                const Q4KScales s0 = q4k_unpack_scales(h0.y, h0.z, h0.w), s1 = q4k_unpack_scales(h1.y, h1.z, h1.w);
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const uint32_t w00 = lds32(r0 + 16 + 32 * j + 4 * t), w01 = lds32(r0 + 32 + 32 * j + 4 * t);
@@ -204,7 +202,8 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
                     // nibble words straddle aligned words by two bytes
                     uint32_t w0, w1, sc0, sc1;
                     if ((b & 1) == 0) {
-                        const uint32_t p0 = r0 + 18 * b + 4 * t, p1 = r1 + 18 * b + 4 * t;
+                        const uint8_t* p0 = r0 + 18 * b + 4 * t;
+                        const uint8_t* p1 = r1 + 18 * b + 4 * t;
                         w0 = __funnelshift_r(lds32(p0), lds32(p0 + 4), 16);
                         w1 = __funnelshift_r(lds32(p1), lds32(p1 + 4), 16);
                         sc0 = lds32(r0 + 18 * b) & 0xFFFFu;
