@@ -368,13 +368,14 @@ namespace pair {
 constexpr int kThreads = 736;              // 23 warps: token-tile producer, MMA, 4 epilogue, 16 dequantisers, raw producer
 constexpr int kRawWarp = 22;
 constexpr int kDeqWarp0 = 6, kGroupWarps = 8;
-constexpr int kNB = 5;                     // token-tile stages (shared memory), each two 64-wide K chunks = 32 KiB
-constexpr int kNA = 4;                     // weight stages (tensor memory), each two K chunks = 64 columns
+constexpr int kNS = 4;                     // pipeline stages: token tile (shared memory, two 64-wide K chunks = 32 KiB) +
+                                           // weight tile (tensor memory, 64 columns); one full / one empty barrier each, so
+                                           // the MMA thread pays one wait and one commit per step
 constexpr int kNR = 3;                     // raw superblock ring
 constexpr int kStageB = 2 * kTileBytes;
 constexpr int kRawBytes = 128 * 144;
 constexpr int kXchgBytes = 2 * 2 * 32 * 17 * 4;
-constexpr int kOffRaw = kNB * kStageB;
+constexpr int kOffRaw = kNS * kStageB;
 constexpr int kOffXchg = kOffRaw + kNR * kRawBytes;
 constexpr int kOffCtrl = kOffXchg + kXchgBytes;
 constexpr int kSmem = kOffCtrl + 512 + 1024;
@@ -389,8 +390,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_p = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t ctrl = base + kOffCtrl;
-    const uint32_t bar_bfull = ctrl, bar_bempty = bar_bfull + 8 * kNB, bar_afull = bar_bempty + 8 * kNB,
-                   bar_aempty = bar_afull + 8 * kNA, bar_rawf = bar_aempty + 8 * kNA, bar_rawe = bar_rawf + 8 * kNR,
+    const uint32_t bar_full = ctrl, bar_empty = bar_full + 8 * kNS, bar_rawf = bar_empty + 8 * kNS, bar_rawe = bar_rawf + 8 * kNR,
                    bar_accf = bar_rawe + 8 * kNR, bar_acce = bar_accf + 8, holder = bar_acce + 8;
     volatile uint32_t* holder_p = reinterpret_cast<volatile uint32_t*>(base_p + kOffCtrl + (holder - ctrl));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_p + kOffCtrl + (holder - ctrl) + 4);
@@ -400,13 +400,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     const uint32_t rank = cluster_ctarank();
     const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     if (tid == 0) {
-        for (int s = 0; s < kNB; s++) {
-            mbar_init(bar_bfull + 8 * s, 1);                    // the leader's expect_tx; bytes from both CTAs' loads
-            mbar_init(bar_bempty + 8 * s, 1);
-        }
-        for (int s = 0; s < kNA; s++) {
-            mbar_init(bar_afull + 8 * s, 4 * kGroupWarps);      // both dequantiser groups of each CTA (one K chunk each)
-            mbar_init(bar_aempty + 8 * s, 1);
+        for (int s = 0; s < kNS; s++) {
+            // full: both dequantiser groups of each CTA (one K chunk each) + the leader's expect_tx (bytes from both CTAs' loads)
+            mbar_init(bar_full + 8 * s, 4 * kGroupWarps + 1);
+            mbar_init(bar_empty + 8 * s, 1);
         }
         for (int u = 0; u < kNR; u++) {
             mbar_init(bar_rawf + 8 * u, 1);
@@ -430,8 +427,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
     const uint32_t nb = DUAL ? a.rows / 128 : a.rows / 256;
     const uint32_t n_items = (uint32_t)(*a.n_tok_tiles) * nb;
     const uint32_t units = a.K / 256;
-    const uint32_t leader_bfull = cluster_map(bar_bfull, 0), leader_afull = cluster_map(bar_afull, 0),
-                   leader_acce = cluster_map(bar_acce, 0);
+    const uint32_t leader_full = cluster_map(bar_full, 0), leader_acce = cluster_map(bar_acce, 0);
 
     auto tile_cols = [&](int32_t nvalid) -> uint32_t { return nvalid <= 32 ? 32u : (uint32_t)((nvalid + 31) & ~31); };
 
@@ -445,11 +441,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                 const uint32_t ncols = tile_cols(a.tile_nvalid[tt]);
                 const int32_t row_b = a.tile_row0[tt] + (int32_t)(rank * (ncols / 2));
                 for (uint32_t st = 0; st < units * 2; st++, it++) {
-                    const uint32_t s = it % kNB, ph = (it / kNB) & 1;
-                    if (!mbar_wait_timed(bar_bempty + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
-                    if (rank == 0) mbar_expect_tx(bar_bfull + 8 * s, 2 * kStageB);
-                    tma_load_2d_pair(base + s * kStageB, &map_b, (int32_t)(st * 256), row_b, leader_bfull + 8 * s);
-                    tma_load_2d_pair(base + s * kStageB + kTileBytes, &map_b, (int32_t)(st * 256 + 128), row_b, leader_bfull + 8 * s);
+                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
+                    if (!mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kStageB);
+                    tma_load_2d_pair(base + s * kStageB, &map_b, (int32_t)(st * 256), row_b, leader_full + 8 * s);
+                    tma_load_2d_pair(base + s * kStageB + kTileBytes, &map_b, (int32_t)(st * 256 + 128), row_b, leader_full + 8 * s);
                 }
             }
         }
@@ -485,9 +481,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                 const uint32_t idesc = umma_idesc_bf16(256, tile_cols(a.tile_nvalid[item / nb]));
                 if (!mbar_wait_timed_cluster(bar_acce, (n & 1) ^ 1, abort_flag)) break;   // the epilogue has drained the accumulator
                 for (uint32_t st = 0; st < units * 2; st++, it++) {
-                    const uint32_t sa = it % kNA, pa = (it / kNA) & 1, sb = it % kNB, pb = (it / kNB) & 1;
-                    if (!mbar_wait_timed_cluster(bar_afull + 8 * sa, pa, abort_flag) ||
-                        !mbar_wait_timed_cluster(bar_bfull + 8 * sb, pb, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = it % kNS, sb = sa, pa = (it / kNS) & 1;
+                    if (!mbar_wait_timed_cluster(bar_full + 8 * sa, pa, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t at = tmem_base + kACol0 + 64 * sa;
 #pragma unroll
@@ -497,8 +492,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                         for (uint32_t k4 = 0; k4 < 4; k4++)
                             umma_bf16_pair_ts(tmem_base, at + 32 * c + 8 * k4, db + 2 * k4, idesc, (st | c | k4) != 0);
                     }
-                    umma_commit_pair(bar_aempty + 8 * sa, 3);
-                    umma_commit_pair(bar_bempty + 8 * sb, 3);
+                    umma_commit_pair(bar_empty + 8 * sa, 3);
                 }
                 if (ok) umma_commit_pair(bar_accf, 3);
             }
@@ -603,7 +597,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                 for (int jj = 0; jj < 2; jj++) {
                     const uint32_t j = 2 * jj + g;               // chunk of the unit; step 2 * unit + jj holds chunks 2jj, 2jj + 1
                     const uint32_t it = uc * 2 + jj;
-                    const uint32_t s = it % kNA, ph = (it / kNA) & 1;
+                    const uint32_t s = it % kNS, ph = (it / kNS) & 1;
                     uint32_t q[8];
                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]) : "r"(raw_row + 16 + 32 * j) : "memory");
                     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]) : "r"(raw_row + 32 + 32 * j) : "memory");
@@ -612,7 +606,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                     if (part == 0) dequant_half<false>(q, dd * (float)((sc.sl >> sh) & 0xFFu), dmin * (float)((sc.ml >> sh) & 0xFFu), out);
                     else dequant_half<true>(q, dd * (float)((sc.sh >> sh) & 0xFFu), dmin * (float)((sc.mh >> sh) & 0xFFu), out);
                     uint32_t got = 1;
-                    if (lane == 0) got = mbar_wait_timed(bar_aempty + 8 * s, ph ^ 1, abort_flag);
+                    if (lane == 0) got = mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag);
                     got = __shfl_sync(0xffffffffu, got, 0);
                     if (!got) { ok = false; break; }
                     tc_fence_after_sync();
@@ -621,8 +615,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
-                        if (rank == 0) mbar_arrive(bar_afull + 8 * s);
-                        else mbar_arrive_cluster(leader_afull + 8 * s);
+                        if (rank == 0) mbar_arrive(bar_full + 8 * s);
+                        else mbar_arrive_cluster(leader_full + 8 * s);
                     }
                 }
                 __syncwarp();
