@@ -68,6 +68,9 @@ def pass_bytes(fmt, layers=LAYERS):
 NCU_TRAFFIC_RATIO = (306.78e6 + 4.28e6) / 307.18e6
 
 
+EXTRAS_LIMIT_S = 420
+
+
 def measured_peak():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -592,13 +595,7 @@ def main():
     e2e_value = world * step_bytes * args.steps / (float(t.item()) * 1e-3) / 1e9
     clocks = sampler.stop() if rank == 0 else None   # sampled over both timed regions
 
-    extras = {}
-    if not args.no_extras:
-        try:
-            extras = run_extras(R, ctx, torch, dist, stream, rank, world, args)
-        except Exception as exc:   # the extras never invalidate the headline line
-            extras = {"error": repr(exc)[:300]}
-
+    line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
         # dominant kernel: the Q4_K staged GEMV; its launches = the Q4_K sub-pass (8 per layer incl. one
@@ -626,7 +623,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * 4 * HIDDEN, "d2h_bytes_per_step": 2 * 4 * VOCAB},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "extras": extras,
+            "extras": {},
         }
         if not args.no_cpu and world == 1:
             gbs, tsec, desc, threads = cpu_sample([FMT_Q4K, FMT_Q4_0], os.cpu_count() or 1, 12.0, layers_sample=2)
@@ -634,6 +631,28 @@ def main():
                                     "seconds": tsec}
         else:
             line["cpu_baseline"] = None
+    # The extras (other rows of the path; at N > 1 they use collectives) must never cost the headline line: if they do
+    # not finish in time, rank 0 prints the line without them and every rank leaves.
+    import threading
+
+    def give_up():
+        if rank == 0:
+            line["extras"] = {"error": "extras did not finish within %d s" % EXTRAS_LIMIT_S}
+            print(json.dumps(line), flush=True)
+        os._exit(0)
+    watchdog = threading.Timer(EXTRAS_LIMIT_S, give_up)
+    watchdog.daemon = True
+    watchdog.start()
+    extras = {}
+    if not args.no_extras:
+        try:
+            extras = run_extras(R, ctx, torch, dist, stream, rank, world, args)
+        except Exception as exc:   # the extras never invalidate the headline line
+            extras = {"error": repr(exc)[:300]}
+
+    watchdog.cancel()
+    if rank == 0:
+        line["extras"] = extras
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
