@@ -136,3 +136,34 @@ def test_grouped_bad_arguments(ctx):
     with pytest.raises(R.KernelError):        # too many experts
         R.moe_experts_grouped_q4k_bf16(ctx, b, b, b, b, b, b, None, b, b, 1 << 20, 1, 256, 256, 300, 2)
     ctx.flush()
+
+
+def test_grouped_experts_one_slot_per_row_and_command_list(ctx, oracle):
+    """The form expert-parallel owners use: k = 1, weight 1, negative ids for unused rows; and the same call recorded
+    as a command list and replayed gives the same bits."""
+    import runit_mac_b200 as R
+    O = oracle
+    rng = np.random.default_rng(5)
+    n, E, h, ff = 333, 4, 512, 256
+    _, gate, up, down = make_layer(O, rng, E, h, ff)
+    x = rng.normal(0, 1, (n, h)).astype(np.float32)
+    ids = rng.integers(-1, E, (n, 1)).astype(np.int32)
+    w = np.ones((n, 1), np.float32)
+    ref, _, _ = O.moe_grouped_q4k_bf16(None, gate, up, down, x, h=h, ff=ff, E=E, top_k=1, routing=(ids, w))
+    bufs = [ctx.buffer_from(a) for a in (gate, up, down, x, ids, w)]
+    out = ctx.new_buffer(n * h * 4)
+    nbytes = R.moe_grouped_scratch_bytes(ctx, n, h, ff, E, 1)
+    scratch = ctx.new_buffer(nbytes)
+    R.moe_experts_grouped_q4k_bf16(ctx, *bufs, None, out, scratch, nbytes, n, h, ff, E, 1)
+    ctx.flush()
+    got = out.download(np.float32, n * h).reshape(n, h)
+    assert_close_bf16_chain(O, ref, got, what="k = 1 slots")
+    assert (got[ids[:, 0] < 0] == 0).all()
+    ctx.graph_begin()
+    R.moe_experts_grouped_q4k_bf16(ctx, *bufs, None, out, scratch, nbytes, n, h, ff, E, 1)
+    g = ctx.graph_end()
+    out.upload(np.zeros(n * h, np.float32))
+    g.launch()
+    ctx.flush()
+    assert np.array_equal(got, out.download(np.float32, n * h).reshape(n, h))
+    g.destroy()

@@ -48,6 +48,10 @@ def run_rank(rank, world, port, q):
     out, idx, w = P.ep_moe_forward(be, dist, torch, xs, E, K_TOP, False, world, rank)
     torch.cuda.synchronize()
     ctx.flush()
+    out_c, idx_c, _ = P.ep_moe_forward_counted(be, dist, torch, xs, E, K_TOP, False, world, rank)   # true-count exchange
+    torch.cuda.synchronize()
+    ctx.flush()
+    assert torch.equal(idx_c, idx) and torch.allclose(out_c, out, rtol=1e-6, atol=1e-6 * float(out.abs().max()))
     y_fused = None
     if world > 1:
         # the same sharded product with the all-gather fused into the GEMV epilogue (peer stores + barrier kernel),
