@@ -295,8 +295,8 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t* up, const float* xp, in
 //
 // KSL = number of warps that share one 32-row tile (each takes every KSL-th unit of K); a CTA
 // holds 4/KSL tiles.  The host picks KSL so that the units divide evenly among the warps.
-// MATH = 0: packed f32 arithmetic (any batch); MATH = 1: integer dot products on 8-bit limbs of the activations
-// (batch 1; see gemv_int8.cuh).
+// MATH = 0: packed f32 arithmetic (any batch); MATH = 1: integer dot products (dp4a) on 8-bit limbs of the activations
+// (batch 1); MATH = 2: integer tensor-core MMAs on 16-bit activations (batch 1, 4-bit formats).  See gemv_int8.cuh.
 template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD, int KSL, int MATH>
 __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const GemvArgs a, const __grid_constant__ GemvMaps maps) {
     using T = Traits<FMT>;
@@ -471,6 +471,12 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
             prep_int_block<EPL, T::UE / 32, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(slot + L::XP_OFF, v[0], lane);
             return;
         }
+        if constexpr (MATH == 2) {
+            const uint32_t u = slice + n_slices * it;
+            const int nblk = FMT == RUNIT_FMT_Q4K ? 8 : min(8, (int)(a.nb - u * T::BPU));
+            prep_mma_block<8, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(slot + L::XP_OFF, v[0], lane, nblk);
+            return;
+        }
 #pragma unroll
         for (int b = 0; b < B; b++) {
             float* xp = reinterpret_cast<float*>(slot + L::XP_OFF) + b * T::UE;
@@ -508,6 +514,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     RowAcc acc[B];
 #pragma unroll
     for (int b = 0; b < B; b++) { acc[b].t0 = 0ull; acc[b].t1 = 0ull; acc[b].s = 0.f; }
+    float macc[4] = {0.f, 0.f, 0.f, 0.f};   // MATH == 2: rows g, g+8, 16+g, 24+g of the tile (g = lane / 4)
 
     // Programmatic dependent launch: this grid may start while its predecessor in the stream is still
     // draining.  Weights do not depend on the predecessor, so (outside grouped mode, where the expert id does)
@@ -529,7 +536,14 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
         __syncwarp();                                           // ... and every lane's
         prep(it);
         __syncwarp();                                           // prepared activations visible to the warp
-        if (row_ok) {
+        if constexpr (MATH == 2) {
+            // whole-warp MMAs: rows past the end of the matrix are zero-filled boxes (or stale bytes that only reach
+            // their own, unwritten, rows)
+            const uint32_t u = slice + n_slices * it;
+            const uint8_t* slot = ring + (it % S) * L::BYTES;
+            if (FMT == RUNIT_FMT_Q4K) unit_q4k_mma(slot, slot + L::XP_OFF, lane, macc);
+            else unit_q4_0_mma(slot, slot + L::XP_OFF, lane, min(8, (int)(a.nb - u * T::BPU)), macc);
+        } else if (row_ok) {
             const uint32_t u = slice + n_slices * it;
             const uint8_t* slot = ring + (it % S) * L::BYTES;
             const uint8_t* up = slot + lane * T::UB;
@@ -553,8 +567,19 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     if (timed_out && a.status) atomicExch(a.status, 1);
 
     // Add the K-slices of each row in slice order, then the epilogue (first warp of each tile).
+    if constexpr (MATH == 2) {
+        // the four lanes of a row group hold the blocks t, 4+t of their rows: add them, then lane (g, t) files row 8t + g
 #pragma unroll
-    for (int b = 0; b < B; b++) red[warp][lane][b] = (sum2(acc[b].t0) + sum2(acc[b].t1)) + acc[b].s;
+        for (int j = 0; j < 4; j++) {
+            macc[j] += __shfl_xor_sync(0xffffffffu, macc[j], 1);
+            macc[j] += __shfl_xor_sync(0xffffffffu, macc[j], 2);
+        }
+        const int t = lane & 3;
+        red[warp][8 * t + (lane >> 2)][0] = t == 0 ? macc[0] : (t == 1 ? macc[1] : (t == 2 ? macc[2] : macc[3]));
+    } else {
+#pragma unroll
+        for (int b = 0; b < B; b++) red[warp][lane][b] = (sum2(acc[b].t0) + sum2(acc[b].t1)) + acc[b].s;
+    }
     __syncthreads();
     if (csplit > 1) {
         // CTA-local sum of the four warps (warp 0), published in red[0]; then CTA 0 of the cluster adds the

@@ -78,10 +78,14 @@ static inline int32_t pick_slices(runit_ctx* ctx, const GemvArgs& a, const GemvM
     return launch_staged<FMT, B, XF16, CPB, S, DUAL, LD, 4, MATH>(ctx, a, maps, name);
 }
 
-// Batch 1 uses the integer dot-product arithmetic unless the tuning knob gemv_math = 1 asks for packed f32.
+// Batch 1: integer tensor-core MMAs for the 4-bit formats, dp4a for Q8_0 (tuning knob gemv_math: 1 = packed f32,
+// 2 = dp4a for every format).
 template <int FMT, int B, bool XF16, int CPB, int S, bool DUAL, int LD>
 static inline int32_t pick_math(runit_ctx* ctx, const GemvArgs& a, const GemvMaps& maps, const char* name) {
     if constexpr (B == 1) {
+        if constexpr (FMT != RUNIT_FMT_Q8_0) {
+            if (ctx->tune.gemv_math == 0 || ctx->tune.gemv_math == 3) return pick_slices<FMT, B, XF16, CPB, S, DUAL, LD, 2>(ctx, a, maps, name);
+        }
         if (ctx->tune.gemv_math != 1) return pick_slices<FMT, B, XF16, CPB, S, DUAL, LD, 1>(ctx, a, maps, name);
     }
     return pick_slices<FMT, B, XF16, CPB, S, DUAL, LD, 0>(ctx, a, maps, name);

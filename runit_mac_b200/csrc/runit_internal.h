@@ -16,7 +16,7 @@ struct runit_tuning {
     int32_t gemv_stages = 0;    // 0 = default
     int32_t moe_variant = 0;
     int32_t pdl = 0;            // programmatic dependent launch between ops
-    int32_t gemv_math = 0;      // 0 = integer dot products for batch 1, 1 = packed f32 everywhere
+    int32_t gemv_math = 0;      // batch 1: 0 = tensor-core MMAs (4-bit) / dp4a (Q8_0), 1 = packed f32, 2 = dp4a
     int32_t gemv_csplit = 0;    // 0 = automatic cluster split of K, else 2 or 4
     int32_t gemv_no_cluster = 0;
     int32_t gemv_ksl = 0;       // 0 = automatic K-slices per tile, else 1, 2 or 4

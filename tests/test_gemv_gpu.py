@@ -48,8 +48,29 @@ def test_gemv_f32in_f32out_matches_oracle(ctx, oracle, fmt):
         ref = O.gemv(fmt, w, x, m, k, O.TIER_F64)
         got = run_gemv(ctx, R, "gemv_%s_f32in_f32out" % FMT_NAME[fmt], w, x, m, k)
         st = assert_close(O, ref, got, what="%s %dx%d" % (FMT_NAME[fmt], m, k))
-        # well inside the tolerance: the kernel accumulates in f32 like the reference's shader
-        assert st.max_rel < 2e-5, (fmt, m, k, st)
+        # well inside the tolerance: Q8_0 sums exact integer products of 24-bit activations; the 4-bit formats round the
+        # activations to 16-bit block fixed point (2^-16 of a 32-block's maximum) for the integer tensor-core MMAs
+        assert st.max_rel < (2e-5 if fmt == 0 else 2e-4), (fmt, m, k, st)
+
+
+@pytest.mark.parametrize("math", [1, 2])
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_gemv_other_arithmetic_paths_match_oracle(ctx, oracle, fmt, math):
+    """The packed-f32 (1) and dp4a (2) arithmetic of the batch-1 kernel stay selectable and correct."""
+    import runit_mac_b200 as R
+    O = oracle
+    ctx.set_tuning("gemv_math", math)
+    try:
+        for m, k in SHAPES[fmt][:4]:
+            rng = np.random.default_rng(2000 + fmt * 100 + m + k)
+            w = O.rand_weights(fmt, rng, m, k)
+            x = rng.normal(0, 1, k).astype(np.float32)
+            ref = O.gemv(fmt, w, x, m, k, O.TIER_F64)
+            got = run_gemv(ctx, R, "gemv_%s_f32in_f32out" % FMT_NAME[fmt], w, x, m, k)
+            st = assert_close(O, ref, got, what="%s %dx%d math %d" % (FMT_NAME[fmt], m, k, math))
+            assert st.max_rel < 2e-5, (fmt, m, k, math, st)
+    finally:
+        ctx.set_tuning("gemv_math", 0)
 
 
 @pytest.mark.parametrize("fmt", [0, 1, 2])
@@ -418,5 +439,6 @@ def test_full_size_lm_head_sampled_rows(ctx, oracle):
             scale = max(abs(ref), float(np.sqrt(np.mean(ys[0] ** 2))))
             assert abs(ys[0][r] - ref) <= REL_TOL * scale, (fmt, r)
         lin = np.float32(0.5) * ys[0] + ys[1]
-        assert_close(O, lin, ys[2], rel_tol=1e-4, what="linearity")
+        # the three products round their activations to 16-bit block fixed point independently
+        assert_close(O, lin, ys[2], rel_tol=5e-4, what="linearity")
         wb.free()
