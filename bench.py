@@ -65,7 +65,7 @@ def pass_bytes(fmt, layers=LAYERS):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the ncu capture of one Q4_K launch.
-NCU_TRAFFIC_RATIO = (306.78e6 + 4.28e6) / 307.18e6
+NCU_TRAFFIC_RATIO = (306.80e6 + 4.71e6) / 307.18e6
 
 
 EXTRAS_LIMIT_S = 420
@@ -611,11 +611,11 @@ def main():
                                    "Q4_K pass + Q4_0 pass, batch 1, f32 activations",
                        "layers": args.layers, "bytes_per_step": step_bytes,
                        "l2": "inputs larger than L2: every matrix is a distinct instance, %.1f GB streamed per step" % (step_bytes / 1e9)},
-            "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K,batch 1>", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K,batch 1,integer tensor-core MMAs>", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                          "traffic": NCU_TRAFFIC_RATIO * bytes_fmt[0] / q4k_launches,
                          "traffic_note": "ncu capture of the 152064x3584 Q4_K launch (profiles/gemv_q4k_lm_head_152064x3584_ncu.md): dram read "
-                                         "306.78 MB + write 4.28 MB for 307.18 MB algorithmic = x1.0126; scaled to the average launch of "
+                                         "306.80 MB + write 4.71 MB for 307.18 MB algorithmic = x1.0141; scaled to the average launch of "
                                          "the pass (weights are streamed once by every launch, so traffic grows with the bytes)",
                          "bytes_per_launch": bytes_fmt[0] / q4k_launches, "launches_per_step": q4k_launches,
                          "avg_launch_us": q4k_ms * 1e3 / q4k_launches},
