@@ -415,11 +415,61 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
                                "tokens_total_s": 192 / dt_all, "launches_per_token": int(model.launches_per_token),
                                "note": "wall clock around one call that runs 192 recorded steps and synchronises once"}
     model.close()
+    if rank == 0:
+        out["gguf_load"] = run_gguf_load(ctx)
     if world > 1:
         from runit_mac_b200 import parallel
         out["lm_head_row_sharded"] = parallel.bench_sharded_lm_head(R, ctx, torch, dist, stream, rank, world)
         out["moe_expert_parallel"] = parallel.bench_expert_parallel(R, ctx, torch, dist, stream, rank, world)
     return out
+
+
+def run_gguf_load(ctx, layers=2):
+    """Model-file load path: a synthetic GGUF file with OLMoE-shaped packed tensors (Q4_K attention matrices and merged
+    expert tensors of `layers` layers, ~0.44 GB) is written to a temporary directory, parsed and uploaded tensor by tensor."""
+    import struct
+    import tempfile
+    from runit_mac_b200.gguf import parse_gguf_file
+    E, h, ff = 64, 2048, 1024
+    rng = np.random.default_rng(5)
+    tensors = []
+    for l in range(layers):
+        for n in ("attn_q", "attn_k", "attn_v", "attn_output"):
+            tensors.append(("blk.%d.%s.weight" % (l, n), [h, h], 12, h * (h // 256) * 144))
+        for n, (kk, rows) in (("ffn_gate_exps", (h, ff)), ("ffn_up_exps", (h, ff)), ("ffn_down_exps", (ff, h))):
+            tensors.append(("blk.%d.%s.weight" % (l, n), [kk, rows, E], 12, E * rows * (kk // 256) * 144))
+
+    def gstr(b):
+        return struct.pack("<Q", len(b)) + b
+    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), 1) + gstr(b"general.architecture") + struct.pack("<I", 8) + gstr(b"olmoe")
+    off = 0
+    for name, dims, dt, nbytes in tensors:
+        head += gstr(name.encode()) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", dt, off)
+        off += (nbytes + 31) // 32 * 32
+    head += b"\0" * ((len(head) + 31) // 32 * 32 - len(head))
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "synthetic.gguf")
+        with open(path, "wb") as f:
+            f.write(head)
+            for _name, _dims, _dt, nbytes in tensors:
+                f.write(rng.integers(0, 256, (nbytes + 31) // 32 * 32, dtype=np.uint8).tobytes())
+        t0 = time.perf_counter()
+        g = parse_gguf_file(path)
+        t_parse = time.perf_counter() - t0
+        total = sum(t.data_size() for t in g.tensors)
+        bufs = [ctx.new_buffer(t.data_size()) for t in g.tensors]
+        from runit_mac_b200 import gguf as G
+        import ctypes as C
+        t0 = time.perf_counter()
+        for t, b in zip(g.tensors, bufs):
+            G._check(G._api().runit_gguf_upload_tensor(ctx.handle, g._h, t.name.encode(), C.c_void_p(b.ptr), b.nbytes))
+        ctx.flush()
+        t_up = time.perf_counter() - t0
+        g.close()
+    for b in bufs:
+        b.free()
+    return {"file_gb": total / 1e9, "tensors": len(tensors), "parse_ms": t_parse * 1e3, "upload_s": t_up,
+            "upload_gbs": total / 1e9 / t_up, "note": "file in the page cache; packed bytes uploaded as stored (wall clock)"}
 
 
 def run_reference(args):
