@@ -216,6 +216,23 @@ int32_t runit_moe_experts_q4k(runit_ctx_t*, const void* gate, const void* up, co
                               const void* slot_expert, void* y_slots, void* act_scratch, uint32_t n_slots, uint32_t h,
                               uint32_t ff, uint32_t n_experts);
 
+/* Expert-parallel form of runit_moe_layer_q4k for decode sizes, tokens replicated on every rank (no counterpart in
+ * the reference, which runs on one device).  Rank r holds the replicated router and the experts
+ * [r * E/world, (r+1) * E/world) (gate_local, up_local: Q4_K [E/world][ff][h]; down_local: Q4_K [E/world][h][ff]).  Every
+ * rank routes all T tokens itself, computes only the (token, expert) slots it owns, and stores its weighted partial sum
+ * into slot r of the partial buffer of EVERY rank with plain peer stores (the combine exchange fused into the kernel: no
+ * collective library call, no TMA, no multicast); after the one-kernel barrier each rank adds the `world` partial sums in
+ * rank order plus the residual, so all ranks end with identical bits in `out`.
+ * partial_all: HOST array of `world` DEVICE pointers, entry p = rank p's partial buffer, f32 [2][world][T][h], as mapped
+ * into this process (the two halves alternate by epoch parity, so a fast rank's next call never overwrites what a slow
+ * rank is still adding); signal_pads / epoch: as for runit_peer_barrier (a missing rank makes the next runit_flush return
+ * RUNIT_ERR_TIMEOUT).  scratch: runit_moe_scratch_bytes(T, h, ff, E, k). */
+int32_t runit_moe_layer_q4k_ep(runit_ctx_t*, const void* router_w, const void* gate_local, const void* up_local,
+                               const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,
+                               void* scratch, size_t scratch_bytes, void* const* partial_all, void* const* signal_pads,
+                               uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm, uint32_t world,
+                               uint32_t rank, uint32_t epoch);
+
 /* No counterpart in the reference.  The same MoE block as runit_moe_layer_q4k for callers that cannot hand
  * over scratch memory: a host engine that gives every free byte of device memory to its own weight and
  * KV-cache pools at start-up, or a serving loop that must not call cudaMalloc because that call stalls the

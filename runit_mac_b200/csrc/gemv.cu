@@ -26,6 +26,7 @@ struct GemvCall {
     // grouped (mixture-of-experts) launch: see GemvArgs
     const int32_t* grp_expert = nullptr;
     uint32_t grp_slots = 0, grp_experts = 0, grp_xdiv = 1;
+    int32_t grp_lo = 0;
     // fused all-gather: the same output slice in the memory of the other GPUs
     float* peer_y[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint32_t n_peer = 0;
@@ -85,6 +86,8 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
         a.grp_rows = c.rows[0];
         a.grp_tiles = tiles;           // tiles per slot
         a.grp_xdiv = c.grp_xdiv;
+        a.grp_lo = c.grp_lo;
+        a.grp_cnt = c.grp_experts;
         RUNIT_REQUIRE(ctx, (uint64_t)tiles * c.grp_slots < (1ull << 31), "%s: too many grouped tiles", nm);
         tiles *= c.grp_slots;
         total_rows *= c.grp_slots;
@@ -191,7 +194,7 @@ static int32_t fused_ffn(runit_ctx* ctx, const char* name, int fmt, const void* 
 // With w2 != nullptr the launch computes silu(w.x) * (w2.x) (gate/up fusion).
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
-                     uint32_t n_slots) {
+                     uint32_t n_slots, int32_t expert_lo) {
     GemvCall c;
     c.name = name;
     c.fmt = fmt;
@@ -206,6 +209,7 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
     c.grp_slots = n_slots;
     c.grp_experts = n_experts;
     c.grp_xdiv = xdiv;
+    c.grp_lo = expert_lo;
     return gemv_dispatch(ctx, c);
 }
 
@@ -402,6 +406,13 @@ int32_t runit_gemv_allgather_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_lo
 
 int32_t runit_peer_barrier(runit_ctx_t* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
+    return runit::peer_barrier_launch(ctx, signal_pads, world, rank, epoch);
+}
+
+}  // extern "C"
+
+namespace runit {
+int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch) {
     RUNIT_REQUIRE(ctx, signal_pads && world >= 1 && world <= 8 && rank < world && epoch > 0, "peer_barrier: bad argument");
     PeerPads h{};
     for (uint32_t p = 0; p < world; p++) {
@@ -411,5 +422,4 @@ int32_t runit_peer_barrier(runit_ctx_t* ctx, void* const* signal_pads, uint32_t 
     peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status);
     return runit_after_launch(ctx, "peer_barrier");
 }
-
-}  // extern "C"
+}  // namespace runit

@@ -78,6 +78,8 @@ struct GemvArgs {
     // output row s.
     const int32_t* grp_expert;
     uint32_t grp_rows, grp_tiles, grp_xdiv;
+    int32_t grp_lo;        // slot s uses expert grp_expert[s] - grp_lo; ids outside [0, grp_cnt) mark unused slots
+    uint32_t grp_cnt;
     // Row-sharded launch with the all-gather fused into the epilogue: every f32 result of segment 0 is also
     // stored at the same index of these vectors, which live in the memory of the other GPUs (plain peer stores).
     float* peer_y[7];
@@ -331,12 +333,12 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     uint32_t row0 = (tile - sg.tile_begin) * RPT;
     uint32_t wrow0 = row0;                       // row of the tile inside the weight matrix
     const uint8_t* xbase = reinterpret_cast<const uint8_t*>(a.x);
-    bool slot_live = true;   // grouped mode: a negative expert id marks an unused slot (nothing is computed or written)
+    bool slot_live = true;   // grouped mode: an expert id outside the stacked matrix marks an unused slot (nothing is computed or written)
     if (a.grp_expert != nullptr && tile_ok) {
         const uint32_t slot = tile / a.grp_tiles;
         row0 = (tile - slot * a.grp_tiles) * RPT;
-        const int32_t eid = a.grp_expert[slot];
-        slot_live = eid >= 0;
+        const int32_t eid = a.grp_expert[slot] - a.grp_lo;
+        slot_live = eid >= 0 && (uint32_t)eid < a.grp_cnt;
         wrow0 = (uint32_t)(slot_live ? eid : 0) * a.grp_rows + row0;
         xbase += (size_t)(slot / a.grp_xdiv) * a.k * (XF16 ? 2 : 4);
         sg.y = reinterpret_cast<uint8_t*>(sg.y) + (size_t)slot * a.ldy * (a.out_f16 ? 2 : 4);

@@ -121,8 +121,11 @@ namespace runit {
 bool gemv_imma_applies(const runit_ctx* ctx, int fmt, uint32_t k, uint32_t batch);
 int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
                   uint32_t batch);
-// gemv.cu: grouped GEMVs over stacked expert matrices (MoE block).
+// gemv.cu: grouped GEMVs over stacked expert matrices (MoE block).  Slot s uses expert slot_expert[s] - expert_lo of the
+// n_experts stacked ones; an id outside that range marks an unused slot.
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
-                     uint32_t n_slots);
+                     uint32_t n_slots, int32_t expert_lo = 0);
+// gemv.cu: the one-kernel barrier over peer memory behind runit_peer_barrier.
+int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch);
 }  // namespace runit

@@ -244,6 +244,7 @@ _TWINS = [
     ("moe_experts_grouped_q4k_bf16", "no twin: (gate, up, down, x, idx, w, residual, out, scratch, scratch_bytes, T, h, ff, E, k)"),
     ("gemv_allgather_f32", "no twin: (fmt, w_local, x, y_all[world] pointer table, world, rank, rows_total, k)"),
     ("peer_barrier", "no twin: (signal_pads[world] pointer table, world, rank, epoch)"),
+    ("moe_layer_q4k_ep", "no twin: expert-parallel decode block with replicated tokens, combine fused over peer memory"),
     ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
     ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),
 ]

@@ -231,6 +231,48 @@ class FusedAllGatherGemv:
         return self.y
 
 
+class FusedEpDecodeMoe:
+    """Expert-parallel MoE block for decode sizes with replicated tokens: every rank routes the tokens itself, runs the
+    experts it owns and stores its weighted partial sums into every rank's buffer (peer stores into symmetric memory);
+    one barrier kernel, then each rank adds the partials in rank order.  No collective library call on the data path;
+    all ranks end with identical bits.  The NCCL variant (tokens data-parallel, three all-to-alls) is `ep_moe_forward`."""
+
+    def __init__(self, R, ctx, torch, dist, router, gate_local, up_local, down_local, E, h, ff, k, renorm, world, rank, max_tokens=16):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        self.R, self.ctx, self.torch = R, ctx, torch
+        self.w = (router, gate_local, up_local, down_local)
+        self.E, self.h, self.ff, self.k, self.renorm, self.world, self.rank, self.max_tokens = E, h, ff, k, renorm, world, rank, max_tokens
+        self.partial = symm.empty(2 * world * max_tokens * h, dtype=torch.float32, device="cuda")
+        self.pad = symm.empty(64, dtype=torch.int32, device="cuda")
+        self.pad.zero_()
+        torch.cuda.synchronize()
+        group = dist.group.WORLD
+        self._hq = symm.rendezvous(self.partial, group)
+        self._hp = symm.rendezvous(self.pad, group)
+        self.partial_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hq.buffer_ptrs])
+        self.pad_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hp.buffer_ptrs])
+        self.scratch_bytes = R.moe_scratch_bytes(ctx, max_tokens, h, ff, E, k)
+        self.scratch = ctx.new_buffer(self.scratch_bytes)
+        self.out = torch.empty(max_tokens, h, dtype=torch.float32, device="cuda")
+        self.idx = torch.empty(max_tokens, k, dtype=torch.int32, device="cuda")
+        self.wts = torch.empty(max_tokens, k, dtype=torch.float32, device="cuda")
+        self.epoch = 0
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def __call__(self, x, residual=None):
+        """x: f32 [T][h], the same on every rank.  Returns (out [T][h], idx [T][k], weights [T][k]) views."""
+        T = x.shape[0]
+        assert T <= self.max_tokens
+        self.epoch += 1
+        router, gate, up, down = self.w
+        self.R.moe_layer_q4k_ep(self.ctx, router, gate, up, down, x, residual, self.out, self.idx, self.wts, self.scratch,
+                                self.scratch_bytes, self.partial_ptrs, self.pad_ptrs, T, self.h, self.ff, self.E, self.k,
+                                int(self.renorm), self.world, self.rank, self.epoch)
+        return self.out[:T], self.idx[:T], self.wts[:T]
+
+
 def _time_steps(torch, dist, stream, ctx, fn, steps, world):
     for _ in range(3):
         fn()
@@ -297,6 +339,16 @@ def bench_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
         x = torch.randn(T, h, dtype=torch.float32, device="cuda")
         ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
         out["T%d_per_rank" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s_all_ranks": world * T / (ms * 1e-3)}
+    if world > 1:
+        try:
+            fused = FusedEpDecodeMoe(R, ctx, torch, dist, router, gate, up, down, E, h, ff, k, False, world, rank, max_tokens=16)
+            for T in (1, 16):
+                x = torch.randn(T, h, dtype=torch.float32, device="cuda")
+                dist.broadcast(x, 0)
+                ms = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
+                out["T%d_replicated_fused_peer_stores" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
+        except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
+            out["fused_unavailable"] = repr(exc)[:200]
     for b in (gate, up, down):
         b.free()
     out["qwen3_shape_prefill"] = bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world)

@@ -162,3 +162,37 @@ def test_moe_bad_arguments(ctx):
     with pytest.raises(R.KernelError):        # more experts per token than experts
         R.moe_route_topk(ctx, b, 0, 4, 8, 0, 1, b, b)
     ctx.flush()
+
+
+def test_expert_parallel_entry_with_one_rank(ctx, oracle):
+    """runit_moe_layer_q4k_ep with world = 1 (own buffers stand in for the peer-mapped ones): same block as
+    runit_moe_layer_q4k up to the order of the final additions; two calls alternate the halves of the partial buffer."""
+    import ctypes as C
+    import runit_mac_b200 as R
+    O = oracle
+    h, ff, E, k, T = 512, 256, 8, 2, 5
+    rng = np.random.default_rng(31)
+    router = rng.normal(0, 0.02, (E, h)).astype(np.float32)
+    gate = np.stack([O.rand_q4k(rng, ff, h) for _ in range(E)])
+    up = np.stack([O.rand_q4k(rng, ff, h) for _ in range(E)])
+    down = np.stack([O.rand_q4k(rng, h, ff) for _ in range(E)])
+    x = rng.normal(0, 1, (T, h)).astype(np.float32)
+    res = rng.normal(0, 1, (T, h)).astype(np.float32)
+    ref, ridx, _ = O.moe_layer_q4k(router, gate, up, down, x, h=h, ff=ff, E=E, top_k=k, renorm=False, residual=res)
+    bufs = [ctx.buffer_from(a) for a in (router, gate, up, down, x, res)]
+    out, idx, w = ctx.new_buffer(T * h * 4), ctx.new_buffer(T * k * 4), ctx.new_buffer(T * k * 4)
+    nbytes = R.moe_scratch_bytes(ctx, T, h, ff, E, k)
+    scratch = ctx.new_buffer(nbytes)
+    partial = ctx.buffer_from(np.full(2 * T * h, np.nan, np.float32))
+    pad = ctx.buffer_from(np.zeros(64, np.uint32))
+    pt, pp = (C.c_void_p * 1)(partial.ptr), (C.c_void_p * 1)(pad.ptr)
+    for epoch in (1, 2):
+        R.moe_layer_q4k_ep(ctx, *bufs, out, idx, w, scratch, nbytes, pt, pp, T, h, ff, E, k, 0, 1, 0, epoch)
+        ctx.flush()
+        assert (idx.download(np.int32, T * k).reshape(T, k) == ridx).all()
+        assert_close(O, ref, out.download(np.float32, T * h).reshape(T, h), what="ep entry, one rank, epoch %d" % epoch)
+    halves = partial.download(np.float32, 2 * T * h).reshape(2, T * h)
+    assert np.isfinite(halves).all() and np.array_equal(halves[0], halves[1])     # both halves were used, same sums
+    with pytest.raises(R.KernelError):
+        R.moe_layer_q4k_ep(ctx, *bufs, out, idx, w, scratch, nbytes, pt, pp, T, h, ff, E, k, 0, 3, 0, 3)   # 8 experts / 3 ranks
+    ctx.flush()

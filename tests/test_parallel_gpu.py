@@ -63,7 +63,24 @@ def run_rank(rank, world, port, q):
             assert torch.equal(yf, y), "fused all-gather differs from the NCCL all-gather"
             dist.barrier()     # nobody starts the next call while a slow rank still compares this one
         y_fused = yf.cpu().numpy()
-    res = (rank, y.cpu().numpy(), out.cpu().numpy(), idx.cpu().numpy())
+    out_ep = None
+    if world > 1:
+        # decode-size block with replicated tokens and the combine fused over peer memory: three calls in a row give the
+        # same bits (the parent checks them against the oracle and that all ranks hold identical bits)
+        ep = P.FusedEpDecodeMoe(R, ctx, torch, dist, torch.from_numpy(d["router"]).cuda(), sl(d["gate"], FF * rb_h), sl(d["up"], FF * rb_h),
+                                sl(d["down"], H * rb_ff), E, H, FF, K_TOP, False, world, rank, max_tokens=d["x"].shape[0])
+        x_all = torch.from_numpy(d["x"]).cuda()
+        res_all = torch.from_numpy(d["x"][::-1].copy()).cuda()
+        prev = None
+        for _ in range(3):
+            o, i_ep, _w = ep(x_all, res_all)
+            ctx.flush()
+            o = o.clone()
+            assert prev is None or torch.equal(o, prev)
+            prev = o
+        out_ep = (o.cpu().numpy(), i_ep.cpu().numpy())
+        dist.barrier()
+    res = (rank, y.cpu().numpy(), out.cpu().numpy(), idx.cpu().numpy(), out_ep)
     if world > 1:
         dist.destroy_process_group()
     if q is not None:
@@ -100,6 +117,13 @@ def test_sharded_paths_match_oracle(oracle):
     assert (idx == ridx).all()
     st = O.compare(ref, out, rel_tol=1e-3)
     assert st.n_mismatch_rel == 0, st
+    if world > 1:
+        ref_res = ref + d["x"][::-1]
+        for r in res:
+            assert (r[4][1] == ridx).all()
+            st = O.compare(ref_res, r[4][0], rel_tol=1e-3)
+            assert st.n_mismatch_rel == 0, st
+            assert np.array_equal(r[4][0], res[0][4][0]), "ranks disagree on the bits of the fused expert-parallel block"
 
 
 def test_peer_barrier_times_out_without_a_peer(ctx):
