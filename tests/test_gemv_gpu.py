@@ -32,7 +32,7 @@ def run_gemv(ctx, R, name, w, x, m, k, out_dtype=np.float32, residual=None):
 # shapes: benchmark decode shapes scaled down in M, plus ragged tiles/units/stages
 SHAPES = {
     0: [(1152, 896), (37, 896), (896, 4864), (5, 32), (64, 96), (33, 1024), (70, 2080)],
-    1: [(512, 3584), (37, 3584), (40, 18944), (5, 256), (33, 512), (31, 2304)],
+    1: [(512, 3584), (37, 3584), (40, 18944), (5, 256), (33, 512), (31, 2304), (70, 2080), (5, 32), (64, 96), (40, 2176)],
     2: [(512, 3584), (37, 2048), (40, 18944), (3, 256), (65, 1024), (1024, 2048)],
 }
 
