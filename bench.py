@@ -421,6 +421,10 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
         from runit_mac_b200 import parallel
         out["lm_head_row_sharded"] = parallel.bench_sharded_lm_head(R, ctx, torch, dist, stream, rank, world)
         out["moe_expert_parallel"] = parallel.bench_expert_parallel(R, ctx, torch, dist, stream, rank, world)
+        try:
+            out["olmoe_decode_q4k_expert_parallel"] = parallel.bench_ep_decode(R, ctx, torch, dist, rank, world)
+        except Exception as exc:   # symmetric memory unavailable on this host
+            out["olmoe_decode_q4k_expert_parallel"] = {"unavailable": repr(exc)[:200]}
     return out
 
 

@@ -321,6 +321,13 @@ typedef struct {          /* device pointers; the model keeps them, the caller k
 typedef struct runit_model runit_model_t;
 /* Allocates the f16 KV cache and all scratch, runs one warm-up step and records the per-token command lists. */
 int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, runit_model_t** out);
+/* The same decoder with the experts split over `world` ranks (one process and context per GPU): weights->gate / up / down
+ * hold this rank's experts [rank * E/world, (rank+1) * E/world) only ([L][E/world][...]), everything else is replicated and
+ * every rank decodes the same token stream (runit_moe_layer_q4k_ep per layer, barrier epochs kept on the device so the
+ * recorded command list can be replayed).  partial_all / signal_pads: as for runit_moe_layer_q4k_ep with T = 1.  All ranks
+ * must call this (and every generate call) together: the warm-up step already runs the barriers. */
+int32_t runit_model_create_ep(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, uint32_t world,
+                              uint32_t rank, void* const* partial_all, void* const* signal_pads, runit_model_t** out);
 int32_t runit_model_destroy(runit_model_t* model);
 int32_t runit_model_reset(runit_model_t* model, int32_t token, int32_t pos);
 /* forward.rs:1795  one token at position pos -> arg-max next token (synchronous, like the reference) */

@@ -30,6 +30,11 @@ struct runit_model {
     int32_t* out_tokens = nullptr;
     uint32_t forced_cap = 0, out_cap = 0;
     uint32_t nsplit = 8;
+    // expert parallelism (ep_world > 1): gate/up/down hold this rank's experts only, tokens are replicated
+    uint32_t ep_world = 1, ep_rank = 0;
+    void* ep_partial[8] = {nullptr};    // every rank's partial buffer f32 [2][world][1][hidden], as mapped here
+    void* ep_pads[8] = {nullptr};       // every rank's signal pad
+    uint32_t* ep_epoch = nullptr;       // device word: barrier epoch, advanced by the barrier kernel, never reset
     cudaGraphExec_t graph_full = nullptr;    // step with lm_head + argmax
     cudaGraphExec_t graph_prompt = nullptr;  // step without them (prompt positions whose logits nobody reads)
     std::vector<void*> owned;
@@ -114,7 +119,21 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, m->x, m->x, h, q_dim))) return st;
         // MoE block (forward.rs:1898-1931)
         if ((st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.ffn_norm + (size_t)l * h, false, c.eps, h, 1))) return st;
-        const size_t eg = (size_t)c.n_experts * c.ff * rb_h, ed = (size_t)c.n_experts * h * rb_ff;
+        const uint32_t e_local = c.n_experts / m->ep_world;
+        const size_t eg = (size_t)e_local * c.ff * rb_h, ed = (size_t)e_local * h * rb_ff;
+        if (m->ep_world > 1) {
+            // experts split over the ranks, combine fused over peer memory; then the next operator's RMSNorm
+            if ((st = moe_layer_q4k_ep_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
+                                            (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
+                                            (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr, m->moe_scratch,
+                                            m->moe_scratch_bytes, m->ep_partial, m->ep_pads, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
+                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, reinterpret_cast<uint32_t*>(m->state + 8))))
+                return st;
+            const float* gamma = l + 1 < c.n_layers ? (const float*)m->w.attn_norm + (size_t)(l + 1) * h
+                                                    : (with_logits ? (const float*)m->w.out_norm : nullptr);
+            if (gamma && (st = launch_rms_norm(ctx, m->x, m->xn, gamma, false, c.eps, h, 1))) return st;
+            continue;
+        }
         if ((st = moe_layer_q4k_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
                                      (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
                                      (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr,
@@ -161,9 +180,13 @@ using namespace runit;
 
 extern "C" {
 
-int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, runit_model_t** out) {
+static int32_t model_create_impl(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, uint32_t world,
+                                 uint32_t rank, void* const* partial_all, void* const* signal_pads, runit_model_t** out) {
     if (!ctx || !out) return RUNIT_ERR_BAD_ARG;
     *out = nullptr;
+    RUNIT_REQUIRE(ctx, world >= 1 && world <= 8 && rank < world, "model_create: world=%u rank=%u unsupported", world, rank);
+    RUNIT_REQUIRE(ctx, world == 1 || (partial_all && signal_pads && cfg && cfg->n_experts % (int32_t)world == 0),
+                  "model_create: expert parallelism needs peer buffers and an expert count divisible by the ranks");
     RUNIT_REQUIRE(ctx, cfg && weights, "model_create: null config or weights");
     const runit_model_cfg& c = *cfg;
     RUNIT_REQUIRE(ctx, c.n_layers > 0 && c.n_layers <= 256 && c.hidden > 0 && c.hidden % 256 == 0, "model_create: bad hidden/layers");
@@ -181,6 +204,12 @@ int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const r
     m->ctx = ctx;
     m->cfg = c;
     m->w = *weights;
+    m->ep_world = world;
+    m->ep_rank = rank;
+    for (uint32_t p = 0; world > 1 && p < world; p++) {
+        m->ep_partial[p] = partial_all[p];
+        m->ep_pads[p] = signal_pads[p];
+    }
     const uint32_t h = c.hidden, q_dim = c.n_heads * c.head_dim, kv_dim = c.n_kv_heads * c.head_dim;
     const size_t kv_elems = (size_t)c.n_layers * c.n_kv_heads * c.max_seq * c.head_dim;
     m->moe_scratch_bytes = moe_scratch_bytes_impl(1, h, c.ff, c.n_experts, c.top_k);
@@ -194,11 +223,13 @@ int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const r
     A((void**)&m->attn_part, (size_t)c.n_heads * m->nsplit * (c.head_dim + 2) * 4);
     A(&m->moe_scratch, m->moe_scratch_bytes);
     A((void**)&m->attn_counters, (size_t)c.n_heads * 4);
+    A((void**)&m->ep_epoch, 64);
     A((void**)&m->state, 64); A((void**)&m->forced, (size_t)m->forced_cap * 4); A((void**)&m->out_tokens, (size_t)m->out_cap * 4);
     if (st == RUNIT_OK) {
         cudaMemsetAsync(m->kc, 0, kv_elems * 2, ctx->stream);
         cudaMemsetAsync(m->vc, 0, kv_elems * 2, ctx->stream);
         cudaMemsetAsync(m->state, 0, 64, ctx->stream);
+        cudaMemsetAsync(m->ep_epoch, 0, 64, ctx->stream);   // once: the epoch only ever grows afterwards
         cudaMemsetAsync(m->attn_counters, 0, (size_t)c.n_heads * 4, ctx->stream);
         cudaMemsetAsync(m->forced, 0xFF, (size_t)m->forced_cap * 4, ctx->stream);   // nothing forced
         // one eager step configures every kernel (shared-memory attributes, tensor maps) before capture
@@ -216,6 +247,15 @@ int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const r
     }
     *out = m;
     return RUNIT_OK;
+}
+
+int32_t runit_model_create(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, runit_model_t** out) {
+    return model_create_impl(ctx, cfg, weights, 1, 0, nullptr, nullptr, out);
+}
+
+int32_t runit_model_create_ep(runit_ctx_t* ctx, const runit_model_cfg* cfg, const runit_model_weights* weights, uint32_t world,
+                              uint32_t rank, void* const* partial_all, void* const* signal_pads, runit_model_t** out) {
+    return model_create_impl(ctx, cfg, weights, world, rank, partial_all, signal_pads, out);
 }
 
 int32_t runit_model_destroy(runit_model_t* m) {
@@ -289,8 +329,10 @@ int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uin
 void* runit_model_logits(runit_model_t* m) { return m ? (void*)m->logits : nullptr; }
 uint64_t runit_model_launches_per_token(runit_model_t* m) {
     if (!m) return 0;
-    // embed, first norm + per layer (qkv, rope+kv, attention, o-proj, norm, 4 MoE + next norm) + lm_head, argmax, advance
-    return 2 + (uint64_t)m->cfg.n_layers * (1 + 1 + 1 + 1 + 1 + 5) + 3;
+    // embed, first norm + per layer (qkv, rope+kv, attention, o-proj, norm, 4 MoE + next norm) + lm_head, argmax, advance;
+    // expert-parallel: the MoE block is router + routing, gate/up, down, partial sums, barrier, sum (6) + next norm
+    const uint64_t moe = m->ep_world > 1 ? 7 : 5;
+    return 2 + (uint64_t)m->cfg.n_layers * (1 + 1 + 1 + 1 + 1 + moe) + 3;
 }
 
 }  // extern "C"

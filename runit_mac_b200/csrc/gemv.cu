@@ -361,9 +361,15 @@ int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight
 struct PeerPads {
     uint32_t* p[8];   // signal words of every rank: pad[r][q] = latest epoch rank q has announced to rank r
 };
-__global__ void peer_barrier_kernel(const PeerPads pp, uint32_t world, uint32_t rank, uint32_t epoch, int32_t* status) {
+// epoch_ptr != nullptr: the epoch is that device word + 1, and the word is advanced once the barrier has been passed
+// (recorded command lists replay the same launch for every call).
+__global__ void peer_barrier_kernel(const PeerPads pp, uint32_t world, uint32_t rank, uint32_t epoch, int32_t* status,
+                                    uint32_t* epoch_ptr) {
     uint32_t* const* pads = pp.p;
     const uint32_t p = threadIdx.x;
+    if (epoch_ptr) epoch = *epoch_ptr + 1u;
+    __syncwarp();
+    if (p == 0 && epoch_ptr) *epoch_ptr = epoch;   // read by every lane above; the following kernels see the new value
     if (p >= world) return;
     // The stores of the preceding kernels (results pushed into the peers' memory) are ordered before the flag.
     __threadfence_system();
@@ -406,20 +412,21 @@ int32_t runit_gemv_allgather_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_lo
 
 int32_t runit_peer_barrier(runit_ctx_t* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
-    return runit::peer_barrier_launch(ctx, signal_pads, world, rank, epoch);
+    RUNIT_REQUIRE(ctx, epoch > 0, "peer_barrier: epoch must be positive");
+    return runit::peer_barrier_launch(ctx, signal_pads, world, rank, epoch, nullptr);
 }
 
 }  // extern "C"
 
 namespace runit {
-int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch) {
-    RUNIT_REQUIRE(ctx, signal_pads && world >= 1 && world <= 8 && rank < world && epoch > 0, "peer_barrier: bad argument");
+int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr) {
+    RUNIT_REQUIRE(ctx, signal_pads && world >= 1 && world <= 8 && rank < world && (epoch > 0 || epoch_ptr), "peer_barrier: bad argument");
     PeerPads h{};
     for (uint32_t p = 0; p < world; p++) {
         RUNIT_REQUIRE(ctx, signal_pads[p] && runit_aligned(signal_pads[p], 4), "peer_barrier: null or misaligned pad %u", p);
         h.p[p] = (uint32_t*)signal_pads[p];
     }
-    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status);
+    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status, epoch_ptr);
     return runit_after_launch(ctx, "peer_barrier");
 }
 }  // namespace runit

@@ -127,5 +127,12 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
                      uint32_t n_slots, int32_t expert_lo = 0);
 // gemv.cu: the one-kernel barrier over peer memory behind runit_peer_barrier.
-int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch);
+int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch,
+                            uint32_t* epoch_ptr);
+// moe.cu: expert-parallel decode block (runit_moe_layer_q4k_ep); epoch_ptr != nullptr keeps the epoch in a device word.
+int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* gate_local, const void* up_local,
+                              const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,
+                              void* scratch, size_t scratch_bytes, void* const* partial_all, void* const* signal_pads,
+                              uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm, uint32_t world,
+                              uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr, uint32_t* route_counter);
 }  // namespace runit

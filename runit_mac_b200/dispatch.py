@@ -266,11 +266,17 @@ class ModelWeights(C.Structure):
 class Model:
     """Greedy decoder over device-resident Q4_K weights; the role of Executor (forward.rs:1239, 1795-1975)."""
 
-    def __init__(self, ctx: Context, cfg: ModelCfg, weights: dict):
-        self.ctx, self.cfg, self._keep = ctx, cfg, weights
+    def __init__(self, ctx: Context, cfg: ModelCfg, weights: dict, ep=None):
+        """ep = (world, rank, partial_ptrs, pad_ptrs): experts split over the ranks (weights hold this rank's experts),
+        pointer tables as for moe_layer_q4k_ep with one token; every rank creates and drives its model together."""
+        self.ctx, self.cfg, self._keep = ctx, cfg, (weights, ep)
         w = ModelWeights(**{k: _ptr(v) for k, v in weights.items()})
         h = C.c_void_p()
-        ctx._check(ctx.lib.runit_model_create(ctx.handle, C.byref(cfg), C.byref(w), C.byref(h)))
+        if ep is None:
+            ctx._check(ctx.lib.runit_model_create(ctx.handle, C.byref(cfg), C.byref(w), C.byref(h)))
+        else:
+            world, rank, partial_ptrs, pad_ptrs = ep
+            ctx._check(ctx.lib.runit_model_create_ep(ctx.handle, C.byref(cfg), C.byref(w), world, rank, partial_ptrs, pad_ptrs, C.byref(h)))
         self.handle = h
 
     def forward_greedy(self, token_id: int, pos: int) -> int:

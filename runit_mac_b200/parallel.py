@@ -355,6 +355,71 @@ def bench_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
     return out
 
 
+def bench_ep_decode(R, ctx, torch, dist, rank, world):
+    """Full OLMoE-shaped greedy decode (16 layers, hidden 2048, 64 experts top-8, Q4_K, 128-token prompt + 64 steps) with
+    the experts split 64/G per rank and the MoE combine fused over peer memory; attention, router, embeddings and lm_head
+    are replicated (same seeds on every rank), every rank decodes the same token stream."""
+    import ctypes as C
+    import time
+    import numpy as np
+    import torch.distributed._symmetric_memory as symm
+    L, h, E, ff, k, V = 16, 2048, 64, 1024, 8, 50304
+    nl = E // world
+    rb = lambda kk: kk // 256 * 144
+    shapes = {"wq": (L * h, h), "wk": (L * h, h), "wv": (L * h, h), "wo": (L * h, h), "lm_head": (V, h),
+              "gate": (L * nl * ff, h), "up": (L * nl * ff, h), "down": (L * nl * h, ff)}
+    dev = {}
+    for i, (name, (rows, kk)) in enumerate(shapes.items()):
+        dev[name] = ctx.new_buffer(rows * rb(kk))
+        seed = 90001 + i + (1000 * rank if name in ("gate", "up", "down") else 0)
+        R.fill_weights(ctx, R.FMT_Q4K, dev[name], rows * (kk // 256), seed, 0.01)
+    for name, n, sig in (("tok_emb", V * h, 0.02), ("router", L * E * h, 0.02)):
+        dev[name] = ctx.new_buffer(4 * n)
+        R.fill_normal_f32(ctx, dev[name], n, 4242 + len(name), sig)
+    ones = np.ones(L * h, np.float32)
+    dev["attn_norm"], dev["ffn_norm"], dev["out_norm"] = ctx.buffer_from(ones), ctx.buffer_from(ones), ctx.buffer_from(ones[:h])
+    ctx.flush()
+    partial = symm.empty(2 * world * h, dtype=torch.float32, device="cuda")
+    pad = symm.empty(64, dtype=torch.int32, device="cuda")
+    pad.zero_()
+    torch.cuda.synchronize()
+    hq, hp = symm.rendezvous(partial, dist.group.WORLD), symm.rendezvous(pad, dist.group.WORLD)
+    pq = (C.c_void_p * world)(*[int(p) for p in hq.buffer_ptrs])
+    pp = (C.c_void_p * world)(*[int(p) for p in hp.buffer_ptrs])
+    dist.barrier()
+    torch.cuda.synchronize()
+    cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=V, n_experts=E, top_k=k, ff=ff,
+                     max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)
+    model = R.Model(ctx, cfg, dev, ep=(world, rank, pq, pp))
+    prompt = np.random.default_rng(1004).integers(0, V, 128).astype(np.int32)
+    dist.barrier()
+    model.generate_greedy(prompt, 8)
+    dist.barrier()
+    t0 = time.perf_counter()
+    toks = model.generate_greedy(prompt, 64)
+    dt_all = time.perf_counter() - t0
+    dist.barrier()
+    t0 = time.perf_counter()
+    model.generate_greedy(prompt, 0)
+    dt_prompt = time.perf_counter() - t0
+    t = torch.tensor([dt_all, dt_prompt], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    same = torch.tensor(toks[127:].astype(np.int64), device="cuda")
+    ref = same.clone()
+    dist.broadcast(ref, 0)
+    agree = torch.tensor([int(torch.equal(same, ref))], device="cuda")
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    dt_all, dt_prompt = float(t[0].item()), float(t[1].item())
+    res = {"decode_tok_s": 64 / max(dt_all - dt_prompt, 1e-9), "prompt_tok_s": 128 / dt_prompt, "tokens_total_s": 192 / dt_all,
+           "launches_per_token": int(model.launches_per_token), "experts_per_rank": nl, "ranks_agree_on_tokens": bool(agree.item()),
+           "note": "one token stream over the whole group; wall clock (max over ranks) around one call of 192 recorded steps"}
+    dist.barrier()
+    model.close()
+    for b in dev.values():
+        b.free()
+    return res
+
+
 def bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=5, T_total=4096):
     """Qwen3-MoE-shaped batched block (hidden 2048, 128 experts, top-8, intermediate 768, Q4_K -> bf16 tensor-core
     GEMMs), 4096 tokens in all (4096/G per rank), experts split 128/G per rank, Zipf(1.1) expert popularity,

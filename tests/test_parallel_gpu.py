@@ -80,12 +80,58 @@ def run_rank(rank, world, port, q):
             prev = o
         out_ep = (o.cpu().numpy(), i_ep.cpu().numpy())
         dist.barrier()
+        out_ep = out_ep + (ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank),)
     res = (rank, y.cpu().numpy(), out.cpu().numpy(), idx.cpu().numpy(), out_ep)
     if world > 1:
         dist.destroy_process_group()
     if q is not None:
         q.put(res)
     return res
+
+
+def ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank):
+    """Small OLMoE-shaped decoder twice on this rank: all experts local, and experts split over the ranks with the
+    fused peer-memory combine.  Returns both greedy token sequences."""
+    import ctypes as C
+    import torch.distributed._symmetric_memory as symm
+    from test_decode_gpu import SMALL, rand_q4k_zero_mean
+    c = dict(SMALL)
+    L, h, E, ff, V = c["n_layers"], c["hidden"], c["n_experts"], c["ff"], c["vocab"]
+    q_dim, kv_dim = c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"]
+    rb = lambda k: k // 256 * 144
+    shapes = {"wq": (L * q_dim, h), "wk": (L * kv_dim, h), "wv": (L * kv_dim, h), "wo": (L * h, q_dim),
+              "gate": (L * E * ff, h), "up": (L * E * ff, h), "down": (L * E * h, ff), "lm_head": (V, h)}
+    rng = np.random.default_rng(21)          # same seed on every rank: replicated weights
+    host = {n: rand_q4k_zero_mean(O, rng, rows, k).reshape(-1) for n, (rows, k) in shapes.items()}
+    host.update({"tok_emb": rng.normal(0, 0.02, (V, h)).astype(np.float32), "attn_norm": np.ones((L, h), np.float32),
+                 "ffn_norm": np.ones((L, h), np.float32), "out_norm": np.ones(h, np.float32),
+                 "router": rng.normal(0, 0.02, (L, E, h)).astype(np.float32)})
+    prompt = np.random.default_rng(22).integers(0, V, 8).astype(np.int32)
+    full = R.Model(ctx, R.ModelCfg(**c), {n: ctx.buffer_from(a) for n, a in host.items()})
+    tok_full = full.generate_greedy(prompt, 24)
+    full.close()
+    nl = E // world
+    local = dict(host)
+    for n, per in (("gate", ff * rb(h)), ("up", ff * rb(h)), ("down", h * rb(ff))):
+        local[n] = np.ascontiguousarray(host[n].reshape(L, E, per)[:, rank * nl:(rank + 1) * nl]).reshape(-1)
+    partial = symm.empty(2 * world * h, dtype=torch.float32, device="cuda")
+    pad = symm.empty(64, dtype=torch.int32, device="cuda")
+    pad.zero_()
+    torch.cuda.synchronize()
+    hq, hp = symm.rendezvous(partial, dist.group.WORLD), symm.rendezvous(pad, dist.group.WORLD)
+    pq = (C.c_void_p * world)(*[int(p) for p in hq.buffer_ptrs])
+    pp = (C.c_void_p * world)(*[int(p) for p in hp.buffer_ptrs])
+    dist.barrier()
+    torch.cuda.synchronize()
+    model = R.Model(ctx, R.ModelCfg(**c), {n: ctx.buffer_from(a) for n, a in local.items()}, ep=(world, rank, pq, pp))
+    dist.barrier()
+    tok_ep = model.generate_greedy(prompt, 24)
+    tok_ep2 = model.generate_greedy(prompt, 24)       # a second run on the same model: epochs keep growing
+    assert (tok_ep == tok_ep2).all()
+    lpt = int(model.launches_per_token)
+    dist.barrier()
+    model.close()
+    return tok_full, tok_ep, lpt
 
 
 def test_sharded_paths_match_oracle(oracle):
@@ -124,6 +170,9 @@ def test_sharded_paths_match_oracle(oracle):
             st = O.compare(ref_res, r[4][0], rel_tol=1e-3)
             assert st.n_mismatch_rel == 0, st
             assert np.array_equal(r[4][0], res[0][4][0]), "ranks disagree on the bits of the fused expert-parallel block"
+            tok_full, tok_ep, lpt = r[4][2]
+            assert (tok_ep == tok_full).all(), ("expert-parallel decode differs from the single-GPU decode", tok_full, tok_ep)
+            assert (tok_ep == res[0][4][2][1]).all() and len(set(tok_ep[7:].tolist())) > 3 and lpt >= 2 + 2 * 11 + 3
 
 
 def test_peer_barrier_times_out_without_a_peer(ctx):
