@@ -112,10 +112,17 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, m->xn, h))) return st;
         __half* kcl = m->kc + (size_t)l * kv_layer;
         __half* vcl = m->vc + (size_t)l * kv_layer;
-        if ((st = launch_rope_kv(ctx, m->q, m->k, m->v, kcl, vcl, hd, c.n_heads, c.n_kv_heads, pos_ptr, c.theta, c.max_seq))) return st;
-        if ((st = launch_decode_attention(ctx, 0, 1, m->q, kcl, vcl, m->ao, m->attn_part, m->nsplit, 1, 0, pos_ptr, c.n_heads,
-                                          c.n_kv_heads, hd, c.max_seq, m->attn_counters)))
-            return st;
+        if (hd == 128 || hd == 64) {
+            // rotary embedding, cache update and attention in one launch
+            if ((st = launch_decode_attention_rope(ctx, m->q, m->k, m->v, kcl, vcl, m->ao, m->attn_part, m->nsplit, pos_ptr, c.n_heads,
+                                                   c.n_kv_heads, hd, c.max_seq, c.theta, m->attn_counters)))
+                return st;
+        } else {
+            if ((st = launch_rope_kv(ctx, m->q, m->k, m->v, kcl, vcl, hd, c.n_heads, c.n_kv_heads, pos_ptr, c.theta, c.max_seq))) return st;
+            if ((st = launch_decode_attention(ctx, 0, 1, m->q, kcl, vcl, m->ao, m->attn_part, m->nsplit, 1, 0, pos_ptr, c.n_heads,
+                                              c.n_kv_heads, hd, c.max_seq, m->attn_counters)))
+                return st;
+        }
         if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, m->x, m->x, h, q_dim))) return st;
         // MoE block (forward.rs:1898-1931)
         if ((st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.ffn_norm + (size_t)l * h, false, c.eps, h, 1))) return st;
@@ -332,7 +339,8 @@ uint64_t runit_model_launches_per_token(runit_model_t* m) {
     // embed, first norm + per layer (qkv, rope+kv, attention, o-proj, norm, 4 MoE + next norm) + lm_head, argmax, advance;
     // expert-parallel: the MoE block is router + routing, gate/up, down, partial sums, barrier, sum (6) + next norm
     const uint64_t moe = m->ep_world > 1 ? 7 : 5;
-    return 2 + (uint64_t)m->cfg.n_layers * (1 + 1 + 1 + 1 + 1 + moe) + 3;
+    const uint64_t attn = (m->cfg.head_dim == 128 || m->cfg.head_dim == 64) ? 1 : 2;   // rope + cache update fused into the attention launch
+    return 2 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + 1 + moe) + 3;
 }
 
 }  // extern "C"

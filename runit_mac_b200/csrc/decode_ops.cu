@@ -3,6 +3,8 @@
 // Twins of crates/kernels/shaders/{norm.metal:95-154, fused_rope.metal:17-56, activation.metal:13-110,
 // attention.metal:172-308} of the reference.  The position / KV length can come from a device word
 // (pos_ptr) so that a recorded command list can be replayed for successive tokens.
+#include <type_traits>
+
 #include "decode_ops.cuh"
 #include "runit_internal.h"
 #include "tma.cuh"
@@ -148,12 +150,22 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// Optional fusion of the rotary embedding and the cache update of the current position into the attention launch
+// (decode, f32 q and f16 caches, batch 1): q is rotated while it is loaded, and the CTA whose split holds the current
+// position rotates that position's k, rounds k and v to f16 and stores both cache rows before it reads them back.
+// Same arithmetic per element as rope_kv_kernel.  k_raw == nullptr: off (q and the caches are used as they are).
+struct RopeFuse {
+    const float* k_raw;   // [kv_heads][head_dim], not yet rotated
+    const float* v_raw;
+    float theta;
+};
+
 template <typename TQ, typename TKV, typename TO, int DPL>
-__global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__ Q, const TKV* __restrict__ K,
-                                                           const TKV* __restrict__ V, TO* __restrict__ O, float* part,
+__global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__ Q, const TKV* K,
+                                                           const TKV* V, TO* __restrict__ O, float* part,
                                                            uint32_t kv_len_val, const int32_t* pos_ptr, uint32_t heads,
                                                            uint32_t kv_heads, uint32_t kv_head_stride, float scale,
-                                                           uint32_t* counters) {
+                                                           uint32_t* counters, const RopeFuse rope) {
     grid_dependency_wait();      // inputs come from the previous kernel of the chain
     grid_launch_dependents();
     constexpr int HD = 32 * DPL;
@@ -166,10 +178,38 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
     const uint32_t kvh = head / (heads / kv_heads);
     const size_t qbase = ((size_t)batch * heads + head) * HD;
     const size_t kvbase = ((size_t)batch * kv_heads + kvh) * kv_head_stride * HD;
-    for (uint32_t d = threadIdx.x; d < HD; d += 128) qs[d] = ldf(Q, qbase + d);
-    __syncthreads();
     const uint32_t chunk = ((kv_len + nsplit - 1) / nsplit + 31) / 32 * 32;
     const uint32_t beg = split * chunk, end = min(kv_len, beg + chunk);
+    bool roped = false;
+    if constexpr (std::is_same<TQ, float>::value && std::is_same<TKV, __half>::value) {
+        if (rope.k_raw) {
+            roped = true;
+            const uint32_t d = threadIdx.x, half = HD / 2, pos = kv_len - 1;
+            if (d < half) {
+                const float freq = 1.0f / powf(rope.theta, (float)(2 * d) / (float)HD);
+                const float angle = (float)pos * freq;
+                const float c = cosf(angle), sn = sinf(angle);
+                const float a = Q[qbase + d], b = Q[qbase + d + half];
+                qs[d] = a * c - b * sn;
+                qs[d + half] = a * sn + b * c;
+                if (pos >= beg && pos < end && pos < kv_head_stride) {
+                    // several query heads may share this kv head: they store the same bits
+                    const float* kp = rope.k_raw + (size_t)kvh * HD;
+                    const float* vp = rope.v_raw + (size_t)kvh * HD;
+                    const float ka = kp[d], kb = kp[d + half];
+                    __half* kc = const_cast<__half*>(K) + kvbase + (size_t)pos * HD;
+                    __half* vc = const_cast<__half*>(V) + kvbase + (size_t)pos * HD;
+                    kc[d] = __float2half_rn(ka * c - kb * sn);
+                    kc[d + half] = __float2half_rn(ka * sn + kb * c);
+                    vc[d] = __float2half_rn(vp[d]);
+                    vc[d + half] = __float2half_rn(vp[d + half]);
+                }
+            }
+        }
+    }
+    if (!roped)
+        for (uint32_t d = threadIdx.x; d < HD; d += 128) qs[d] = ldf(Q, qbase + d);
+    __syncthreads();   // also orders this CTA's cache stores before its own loads of that row
     float m = -INFINITY, l = 0.f, o[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; i++) o[i] = 0.f;
@@ -372,12 +412,12 @@ int32_t launch_kv_copy(runit_ctx* ctx, const void* src, bool src_f16, void* dst,
 template <typename TQ, typename TKV, typename TO>
 static int32_t attn_typed(runit_ctx* ctx, const void* q, const void* k, const void* v, void* out, float* part, uint32_t nsplit,
                           uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr, uint32_t heads, uint32_t kv_heads,
-                          uint32_t hd, uint32_t stride, uint32_t* counters) {
+                          uint32_t hd, uint32_t stride, uint32_t* counters, const RopeFuse rope = RopeFuse{nullptr, nullptr, 0.f}) {
     const float scale = 1.0f / sqrtf((float)hd);   // dispatch.rs:1588
     dim3 grid(heads, nsplit, batch);
 #define ATTN_CASE(D)                                                                                                   \
     runit_launch_chain(ctx, decode_attn_kernel<TQ, TKV, TO, D>, dim3(grid), dim3(128), (const TQ*)q, (const TKV*)k, (const TKV*)v, (TO*)out, \
-                                                                      part, kv_len, pos_ptr, heads, kv_heads, stride, scale, counters)
+                                                                      part, kv_len, pos_ptr, heads, kv_heads, stride, scale, counters, rope)
     switch (hd) {
         case 32: ATTN_CASE(1); break;
         case 64: ATTN_CASE(2); break;
@@ -403,6 +443,18 @@ int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const v
     if (q_kind == 0 && kv_kind == 1)
         return attn_typed<float, __half, float>(ctx, q, k, v, out, part, nsplit, batch, kv_len, pos_ptr, heads, kv_heads, hd, stride, counters);
     return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "decode_attention: f16 query with f32 cache");
+}
+
+// Decode step of the greedy model: rotary embedding of q and k, cache update and attention in one launch (batch 1, f32 q,
+// f16 caches; the position comes from the device word pos_ptr).
+int32_t launch_decode_attention_rope(runit_ctx* ctx, const float* q, const float* k_raw, const float* v_raw, void* kcache, void* vcache,
+                                     float* out, float* part, uint32_t nsplit, const int32_t* pos_ptr, uint32_t heads, uint32_t kv_heads,
+                                     uint32_t hd, uint32_t max_seq, float theta, uint32_t* counters) {
+    RUNIT_REQUIRE(ctx, q && k_raw && v_raw && kcache && vcache && out && pos_ptr, "decode_attention_rope: null pointer");
+    RUNIT_REQUIRE(ctx, runit_aligned(kcache, 16) && runit_aligned(vcache, 16), "decode_attention_rope: caches must be 16-byte aligned");
+    RUNIT_REQUIRE(ctx, hd == 128 || hd == 64, "decode_attention_rope: head_dim %u unsupported (threads cover half a head)", hd);
+    return attn_typed<float, __half, float>(ctx, q, kcache, vcache, out, part, nsplit, 1, 0, pos_ptr, heads, kv_heads, hd, max_seq, counters,
+                                            RopeFuse{k_raw, v_raw, theta});
 }
 
 int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* result, uint32_t n) {

@@ -20,6 +20,10 @@ int32_t launch_decode_attention(runit_ctx* ctx, int q_kind, int kv_kind, const v
                                 float* part, uint32_t nsplit, uint32_t batch, uint32_t kv_len, const int32_t* pos_ptr,
                                 uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t stride,
                                 uint32_t* counters = nullptr);   // batch*heads zeroed words: the last split merges, no combine launch
+// rotary embedding of q and k, cache update of this position and attention in one launch (decode, batch 1, head_dim 64 / 128)
+int32_t launch_decode_attention_rope(runit_ctx* ctx, const float* q, const float* k_raw, const float* v_raw, void* kcache, void* vcache,
+                                     float* out, float* part, uint32_t nsplit, const int32_t* pos_ptr, uint32_t heads, uint32_t kv_heads,
+                                     uint32_t hd, uint32_t max_seq, float theta, uint32_t* counters);
 int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* result, uint32_t n);
 
 // gemv.cu: one fused-dequant GEMV with up to three row segments sharing the input (Q|K|V) — any format.
