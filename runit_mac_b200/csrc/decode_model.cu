@@ -125,7 +125,8 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         }
         if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, m->x, m->x, h, q_dim))) return st;
         // MoE block (forward.rs:1898-1931)
-        if ((st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.ffn_norm + (size_t)l * h, false, c.eps, h, 1))) return st;
+        // (the block's RMSNorm runs inside its routing launch)
+        const float* ffn_gamma = (const float*)m->w.ffn_norm + (size_t)l * h;
         const uint32_t e_local = c.n_experts / m->ep_world;
         const size_t eg = (size_t)e_local * c.ff * rb_h, ed = (size_t)e_local * h * rb_ff;
         if (m->ep_world > 1) {
@@ -134,7 +135,8 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
                                             (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
                                             (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr, m->moe_scratch,
                                             m->moe_scratch_bytes, m->ep_partial, m->ep_pads, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
-                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, reinterpret_cast<uint32_t*>(m->state + 8))))
+                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, reinterpret_cast<uint32_t*>(m->state + 8), m->x, ffn_gamma,
+                                            c.eps)))
                 return st;
             const float* gamma = l + 1 < c.n_layers ? (const float*)m->w.attn_norm + (size_t)(l + 1) * h
                                                     : (with_logits ? (const float*)m->w.out_norm : nullptr);
@@ -149,7 +151,8 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
                                      // before lm_head)
                                      l + 1 < c.n_layers ? (const float*)m->w.attn_norm + (size_t)(l + 1) * h
                                                         : (with_logits ? (const float*)m->w.out_norm : nullptr),
-                                     m->xn, c.eps, reinterpret_cast<uint32_t*>(m->state + 8))))   // state[8]: ticket counter, zero at rest
+                                     m->xn, c.eps, reinterpret_cast<uint32_t*>(m->state + 8),   // state[8]: ticket counter, zero at rest
+                                     m->x, ffn_gamma, c.eps)))
             return st;
     }
     int32_t* argmax_out = m->state + 3;
@@ -340,7 +343,9 @@ uint64_t runit_model_launches_per_token(runit_model_t* m) {
     // expert-parallel: the MoE block is router + routing, gate/up, down, partial sums, barrier, sum (6) + next norm
     const uint64_t moe = m->ep_world > 1 ? 7 : 5;
     const uint64_t attn = (m->cfg.head_dim == 128 || m->cfg.head_dim == 64) ? 1 : 2;   // rope + cache update fused into the attention launch
-    return 2 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + 1 + moe) + 3;
+    // the RMSNorm before the MoE block runs inside its routing launch when the hidden size is 1024 / 2048 / 4096
+    const uint64_t norm2 = (m->cfg.hidden == 1024 || m->cfg.hidden == 2048 || m->cfg.hidden == 4096) ? 0 : 1;
+    return 2 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + norm2 + moe) + 3;
 }
 
 }  // extern "C"

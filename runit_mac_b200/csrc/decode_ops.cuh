@@ -36,7 +36,9 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
                            size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
                            const float* next_gamma, float* next_xn, float next_eps,    // next_*: also RMSNorm the result
-                           uint32_t* route_counter);   // zeroed word: router and routing in one launch (T == 1)
+                           uint32_t* route_counter,    // zeroed word: router and routing in one launch (T == 1)
+                           // pre_gamma != nullptr: the block first writes RMSNorm(pre_x) into x (inside the routing launch when T == 1)
+                           const float* pre_x, const float* pre_gamma, float pre_eps);
 size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);
 
 }  // namespace runit

@@ -149,17 +149,44 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const void* __restrict_
 // arithmetic of router_f32_kernel (same bits), publish them and take a ticket; the CTA that draws the last ticket
 // routes from the complete logits and puts the ticket counter back to zero.  *counter must be zero before the
 // first launch.
+// gamma != nullptr: x is the un-normalised hidden state; every CTA first computes its RMSNorm (thread order, shuffle tree
+// and rounding of rms_norm_kernel: the same bits in every CTA and as the separate launch), CTA 0 stores the normalised
+// vector to xn_out for the expert GEMVs, and the router reads it from shared memory.
 template <int KPL>
 __global__ void __launch_bounds__(256) route_fused_kernel(const float* __restrict__ w, const float* __restrict__ x,
                                                            float* logits, uint32_t E, uint32_t K, uint32_t k, int renorm,
-                                                           int32_t* __restrict__ out_idx, float* __restrict__ out_w, uint32_t* counter) {
+                                                           int32_t* __restrict__ out_idx, float* __restrict__ out_w, uint32_t* counter,
+                                                           const float* __restrict__ gamma, float eps, float* __restrict__ xn_out) {
     grid_dependency_wait();
     grid_launch_dependents();
     __shared__ uint32_t s_last;
+    __shared__ __align__(16) float xs[KPL * 32];
+    __shared__ float part[8];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (gamma) {
+        float sq = 0.f;
+        for (uint32_t i = threadIdx.x; i < K; i += 256) {
+            const float v = x[i];
+            sq = fmaf(v, v, sq);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) part[warp] = sq;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) tot += part[i];
+        const float r = rsqrtf(tot / (float)K + eps);
+        for (uint32_t i = threadIdx.x; i < K; i += 256) {
+            const float v = x[i] * r * gamma[i];
+            xs[i] = v;
+            if (blockIdx.x == 0) xn_out[i] = v;
+        }
+        __syncthreads();
+    }
     const uint32_t e = blockIdx.x * 8 + warp;
     if (e < E) {
-        const float4* xr = reinterpret_cast<const float4*>(x);
+        const float4* xr = gamma ? reinterpret_cast<const float4*>(xs) : reinterpret_cast<const float4*>(x);
         const float4* wrow = reinterpret_cast<const float4*>(w + (size_t)e * K);
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
@@ -283,7 +310,8 @@ size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, u
 int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
                            size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
-                           const float* next_gamma, float* next_xn, float next_eps, uint32_t* route_counter) {
+                           const float* next_gamma, float* next_xn, float next_eps, uint32_t* route_counter,
+                           const float* pre_x, const float* pre_gamma, float pre_eps) {
     RUNIT_REQUIRE(ctx, router_w && gate && up && down && x && out && scratch, "moe_layer_q4k: null pointer");
     RUNIT_REQUIRE(ctx, T > 0 && T <= 65536, "moe_layer_q4k: T=%u out of range", T);
     RUNIT_REQUIRE(ctx, h % 256 == 0 && ff % 256 == 0 && h > 0 && ff > 0, "moe_layer_q4k: h=%u, ff=%u must be multiples of 256", h, ff);
@@ -295,12 +323,25 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     int32_t* idx = idx_out ? idx_out : s.idx;
     float* wts = w_out ? w_out : s.w;
     int32_t st;
-    if (route_counter && T == 1 && (h == 1024 || h == 2048 || h == 4096) && runit_aligned(router_w, 16) && runit_aligned(x, 16)) {
+    // pre_gamma != nullptr: the block starts with the RMSNorm of pre_x (the un-normalised hidden state, another buffer than
+    // x) into x, which the router and the experts then consume; one token takes it inside the routing launch, else it is a
+    // launch of its own
+    const bool fused_route = route_counter && T == 1 && (h == 1024 || h == 2048 || h == 4096) && runit_aligned(router_w, 16) && runit_aligned(x, 16) &&
+                             (!pre_gamma || (pre_x && pre_x != x && runit_aligned(pre_x, 16)));
+    float* pre_out = pre_gamma ? (float*)const_cast<void*>(x) : nullptr;
+    const float* x_route = pre_gamma ? pre_x : (const float*)x;
+    if (pre_gamma && !fused_route) {
+        RUNIT_REQUIRE(ctx, pre_x, "moe_layer_q4k: null pre-norm input");
+        if ((st = launch_rms_norm(ctx, pre_x, pre_out, pre_gamma, false, pre_eps, h, T)) != RUNIT_OK) return st;
+        pre_gamma = nullptr;
+        x_route = (const float*)x;
+    }
+    if (fused_route) {
         // one token: router GEMV and routing in one launch (same bits as the two launches below)
         const dim3 grid((E + 7) / 8);
-        if (h == 2048) runit_launch_chain(ctx, route_fused_kernel<64>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
-        else if (h == 1024) runit_launch_chain(ctx, route_fused_kernel<32>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
-        else runit_launch_chain(ctx, route_fused_kernel<128>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
+        if (h == 2048) runit_launch_chain(ctx, route_fused_kernel<64>, grid, dim3(256), (const float*)router_w, x_route, s.logits, E, h, k, (int)renorm, idx, wts, route_counter, pre_gamma, pre_eps, pre_out);
+        else if (h == 1024) runit_launch_chain(ctx, route_fused_kernel<32>, grid, dim3(256), (const float*)router_w, x_route, s.logits, E, h, k, (int)renorm, idx, wts, route_counter, pre_gamma, pre_eps, pre_out);
+        else runit_launch_chain(ctx, route_fused_kernel<128>, grid, dim3(256), (const float*)router_w, x_route, s.logits, E, h, k, (int)renorm, idx, wts, route_counter, pre_gamma, pre_eps, pre_out);
         if ((st = runit_after_launch(ctx, "moe_route_fused")) != RUNIT_OK) return st;
     } else {
         st = moe_router(ctx, (const float*)router_w, (const float*)x, s.logits, E, h, T);
@@ -354,7 +395,8 @@ int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* 
                               const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,
                               void* scratch, size_t scratch_bytes, void* const* partial_all, void* const* signal_pads,
                               uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm, uint32_t world,
-                              uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr, uint32_t* route_counter) {
+                              uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr, uint32_t* route_counter, const float* pre_x,
+                              const float* pre_gamma, float pre_eps) {
     RUNIT_REQUIRE(ctx, router_w && gate_local && up_local && down_local && x && out && scratch && partial_all && signal_pads,
                   "moe_layer_q4k_ep: null pointer");
     RUNIT_REQUIRE(ctx, world >= 1 && world <= 8 && rank < world && E % world == 0 && (epoch > 0 || epoch_ptr),
@@ -378,12 +420,22 @@ int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* 
     float* wts = w_out ? (float*)w_out : s.w;
     // every rank routes every token itself (the router is replicated): no dispatch exchange
     int32_t st;
-    if (route_counter && T == 1 && (h == 1024 || h == 2048 || h == 4096) && runit_aligned(router_w, 16) && runit_aligned(x, 16)) {
-        // one token: router GEMV and routing in one launch (same bits as the two launches below)
+    const bool fused_route = route_counter && T == 1 && (h == 1024 || h == 2048 || h == 4096) && runit_aligned(router_w, 16) && runit_aligned(x, 16) &&
+                             (!pre_gamma || (pre_x && pre_x != x && runit_aligned(pre_x, 16)));
+    float* pre_out = pre_gamma ? (float*)const_cast<void*>(x) : nullptr;
+    const float* x_route = pre_gamma ? pre_x : (const float*)x;
+    if (pre_gamma && !fused_route) {
+        RUNIT_REQUIRE(ctx, pre_x, "moe_layer_q4k_ep: null pre-norm input");
+        if ((st = launch_rms_norm(ctx, pre_x, pre_out, pre_gamma, false, pre_eps, h, T)) != RUNIT_OK) return st;
+        pre_gamma = nullptr;
+        x_route = (const float*)x;
+    }
+    if (fused_route) {
+        // one token: (RMSNorm,) router GEMV and routing in one launch (same bits as the separate launches)
         const dim3 grid((E + 7) / 8);
-        if (h == 2048) runit_launch_chain(ctx, route_fused_kernel<64>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
-        else if (h == 1024) runit_launch_chain(ctx, route_fused_kernel<32>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
-        else runit_launch_chain(ctx, route_fused_kernel<128>, grid, dim3(256), (const float*)router_w, (const float*)x, s.logits, E, h, k, (int)renorm, idx, wts, route_counter);
+        if (h == 2048) runit_launch_chain(ctx, route_fused_kernel<64>, grid, dim3(256), (const float*)router_w, x_route, s.logits, E, h, k, (int)renorm, idx, wts, route_counter, pre_gamma, pre_eps, pre_out);
+        else if (h == 1024) runit_launch_chain(ctx, route_fused_kernel<32>, grid, dim3(256), (const float*)router_w, x_route, s.logits, E, h, k, (int)renorm, idx, wts, route_counter, pre_gamma, pre_eps, pre_out);
+        else runit_launch_chain(ctx, route_fused_kernel<128>, grid, dim3(256), (const float*)router_w, x_route, s.logits, E, h, k, (int)renorm, idx, wts, route_counter, pre_gamma, pre_eps, pre_out);
         if ((st = runit_after_launch(ctx, "moe_route_fused")) != RUNIT_OK) return st;
     } else {
         if ((st = moe_router(ctx, (const float*)router_w, (const float*)x, s.logits, E, h, T)) != RUNIT_OK) return st;
@@ -429,7 +481,7 @@ int32_t runit_moe_layer_q4k_static(runit_ctx_t* ctx, const void* router_w, const
     int32_t st = moe_static_scratch(ctx, &scratch);
     if (st != RUNIT_OK) return st;
     return moe_layer_q4k_impl(ctx, router_w, gate, up, down, x, residual, out, (int32_t*)idx_out, (float*)w_out, scratch,
-                              kMoeStaticScratchBytes, T, h, ff, E, k, renorm, nullptr, nullptr, 0.f, nullptr);
+                              kMoeStaticScratchBytes, T, h, ff, E, k, renorm, nullptr, nullptr, 0.f, nullptr, nullptr, nullptr, 0.f);
 }
 
 size_t runit_moe_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
@@ -473,7 +525,7 @@ int32_t runit_moe_layer_q4k_ep(runit_ctx_t* ctx, const void* router_w, const voi
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, epoch > 0, "moe_layer_q4k_ep: epoch must be positive");
     return moe_layer_q4k_ep_impl(ctx, router_w, gate_local, up_local, down_local, x, residual, out, idx_out, w_out, scratch,
-                                 scratch_bytes, partial_all, signal_pads, T, h, ff, E, k, renorm, world, rank, epoch, nullptr, nullptr);
+                                 scratch_bytes, partial_all, signal_pads, T, h, ff, E, k, renorm, world, rank, epoch, nullptr, nullptr, nullptr, nullptr, 0.f);
 }
 
 int32_t runit_moe_layer_q4k(runit_ctx_t* ctx, const void* router_w, const void* gate, const void* up, const void* down,
@@ -481,7 +533,7 @@ int32_t runit_moe_layer_q4k(runit_ctx_t* ctx, const void* router_w, const void* 
                             size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     return moe_layer_q4k_impl(ctx, router_w, gate, up, down, x, residual, out, (int32_t*)idx_out, (float*)w_out, scratch,
-                              scratch_bytes, T, h, ff, E, k, renorm, nullptr, nullptr, 0.f, nullptr);
+                              scratch_bytes, T, h, ff, E, k, renorm, nullptr, nullptr, 0.f, nullptr, nullptr, nullptr, 0.f);
 }
 
 }  // extern "C"

@@ -134,5 +134,6 @@ int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* 
                               const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,
                               void* scratch, size_t scratch_bytes, void* const* partial_all, void* const* signal_pads,
                               uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm, uint32_t world,
-                              uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr, uint32_t* route_counter);
+                              uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr, uint32_t* route_counter, const float* pre_x,
+                              const float* pre_gamma, float pre_eps);
 }  // namespace runit
