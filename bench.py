@@ -647,6 +647,13 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = world * step_bytes * args.steps / (float(t.item()) * 1e-3) / 1e9
+    if rank == 0 and sampler.proc is not None:
+        # a short run can end before nvidia-smi has printed its first line: keep the same load running (untimed) until
+        # a few samples exist, so that the clock record is taken under load and never empty
+        t_wait = time.perf_counter()
+        while len(sampler.rows) < 3 and time.perf_counter() - t_wait < 3.0:
+            step()
+            torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None   # sampled over both timed regions
 
     line = None
