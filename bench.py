@@ -323,7 +323,7 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
             "finite": bool(torch.isfinite(out).all().item())}
 
 
-def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False):
+def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False, stop=lambda: False):
     """Figures for the other rows of the path: one OLMoE-shaped MoE layer (1/16/256 tokens), the full
     OLMoE-shaped greedy decode (tok/s) and, at N>1, the row-sharded lm_head with its all-gather."""
     out = {}
@@ -417,15 +417,204 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
     model.close()
     if rank == 0:
         out["gguf_load"] = run_gguf_load(ctx)
-    if world > 1:
-        from runit_mac_b200 import parallel
-        out["lm_head_row_sharded"] = parallel.bench_sharded_lm_head(R, ctx, torch, dist, stream, rank, world)
-        out["moe_expert_parallel"] = parallel.bench_expert_parallel(R, ctx, torch, dist, stream, rank, world)
+    def go_on():
+        # the ranks decide together whether the next sharded measurement starts (it holds collectives)
+        t = torch.tensor([1 if stop() else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t.item()) == 0
+    if world > 1 and go_on():
+        out["lm_head_row_sharded"] = run_sharded_lm_head(R, ctx, torch, dist, stream, rank, world)
+    if world > 1 and go_on():
+        out["moe_expert_parallel"] = run_expert_parallel(R, ctx, torch, dist, stream, rank, world)
+    if world > 1 and go_on():
         try:
-            out["olmoe_decode_q4k_expert_parallel"] = parallel.bench_ep_decode(R, ctx, torch, dist, rank, world)
+            out["olmoe_decode_q4k_expert_parallel"] = run_ep_decode(R, ctx, torch, dist, rank, world)
         except Exception as exc:   # symmetric memory unavailable on this host
             out["olmoe_decode_q4k_expert_parallel"] = {"unavailable": repr(exc)[:200]}
     return out
+
+
+# ───────────────────────── sharded paths (N > 1) ─────────────────────────
+
+def _time_steps(torch, dist, stream, ctx, fn, steps, world):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_sharded_lm_head(R, ctx, torch, dist, stream, rank, world, steps=20):
+    """Qwen2.5-7B lm_head (152064 x 3584), Q4_K and Q4_0, rows split over the ranks, logits all-gathered."""
+    from runit_mac_b200 import parallel as P
+    out = {}
+    M, K = 152064, 3584
+    _, n = P.shard_rows(M, world, rank)
+    x = torch.randn(K, dtype=torch.float32, device="cuda")
+    for fmt, name in ((2, "q4k"), (1, "q4_0")):
+        be = P.CudaBackend(R, ctx, torch)
+        rb = R.row_bytes(fmt, K)
+        w = ctx.new_buffer(n * rb)
+        R.fill_weights(ctx, fmt, w, n * (K // R.BLOCK_ELEMS[fmt]), 1002 + rank, 0.01)
+        be.set_lm_head(fmt, w, n, K)
+        ms = _time_steps(torch, dist, stream, ctx, lambda: P.sharded_gemv(be, dist, torch, x, M, world, rank), steps, world)
+        ms_local = _time_steps(torch, dist, stream, ctx, lambda: be.local_gemv(x), steps, world)
+        alg = M * rb + 4 * (K + M)
+        out[name] = {"us_per_call": ms * 1e3, "us_local_gemv": ms_local * 1e3, "aggregate_gbs": alg / (ms * 1e-3) / 1e9,
+                     "rows_per_rank": n}
+        if world > 1:
+            try:
+                fused = P.FusedAllGatherGemv(R, ctx, torch, dist, fmt, w, M, K, world, rank)
+                ms_f = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
+                out[name].update({"us_per_call_fused_peer_stores": ms_f * 1e3, "aggregate_gbs_fused": alg / (ms_f * 1e-3) / 1e9})
+            except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
+                out[name]["fused_unavailable"] = repr(exc)[:200]
+        w.free()
+    return out
+
+
+def run_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
+    """One OLMoE-shaped MoE layer (hidden 2048, 64 experts, top-8, intermediate 1024, Q4_K), experts split 64/G per
+    rank, T tokens per rank."""
+    from runit_mac_b200 import parallel as P
+    E, h, ff, k = 64, 2048, 1024, 8
+    n_local = E // world
+    rb = lambda kk: kk // 256 * 144
+    gate, up = ctx.new_buffer(n_local * ff * rb(h)), ctx.new_buffer(n_local * ff * rb(h))
+    down = ctx.new_buffer(n_local * h * rb(ff))
+    for i, (b, rows, kk) in enumerate(((gate, n_local * ff, h), (up, n_local * ff, h), (down, n_local * h, ff))):
+        R.fill_weights(ctx, 2, b, rows * (kk // 256), 77 + i + 10 * rank, 0.01)
+    router = torch.randn(E, h, dtype=torch.float32, device="cuda") * 0.02
+    if world > 1:
+        dist.broadcast(router, 0)
+    be = P.CudaBackend(R, ctx, torch)
+    be.set_experts(router, gate, up, down, E, n_local, h, ff, k, False)
+    out = {}
+    for T in (1, 16):
+        x = torch.randn(T, h, dtype=torch.float32, device="cuda")
+        ms = _time_steps(torch, dist, stream, ctx, lambda: P.ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
+        out["T%d_per_rank" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s_all_ranks": world * T / (ms * 1e-3)}
+    if world > 1:
+        try:
+            fused = P.FusedEpDecodeMoe(R, ctx, torch, dist, router, gate, up, down, E, h, ff, k, False, world, rank, max_tokens=16)
+            for T in (1, 16):
+                x = torch.randn(T, h, dtype=torch.float32, device="cuda")
+                dist.broadcast(x, 0)
+                ms = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
+                out["T%d_replicated_fused_peer_stores" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
+        except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
+            out["fused_unavailable"] = repr(exc)[:200]
+    for b in (gate, up, down):
+        b.free()
+    out["qwen3_shape_prefill"] = run_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world)
+    return out
+
+
+def run_ep_decode(R, ctx, torch, dist, rank, world):
+    """Full OLMoE-shaped greedy decode (16 layers, hidden 2048, 64 experts top-8, Q4_K, 128-token prompt + 64 steps) with
+    the experts split 64/G per rank and the MoE combine fused over peer memory; attention, router, embeddings and lm_head
+    are replicated (same seeds on every rank), every rank decodes the same token stream."""
+    from runit_mac_b200 import parallel as P
+    import ctypes as C
+    import time
+    import numpy as np
+    import torch.distributed._symmetric_memory as symm
+    L, h, E, ff, k, V = 16, 2048, 64, 1024, 8, 50304
+    nl = E // world
+    rb = lambda kk: kk // 256 * 144
+    shapes = {"wq": (L * h, h), "wk": (L * h, h), "wv": (L * h, h), "wo": (L * h, h), "lm_head": (V, h),
+              "gate": (L * nl * ff, h), "up": (L * nl * ff, h), "down": (L * nl * h, ff)}
+    dev = {}
+    for i, (name, (rows, kk)) in enumerate(shapes.items()):
+        dev[name] = ctx.new_buffer(rows * rb(kk))
+        seed = 90001 + i + (1000 * rank if name in ("gate", "up", "down") else 0)
+        R.fill_weights(ctx, R.FMT_Q4K, dev[name], rows * (kk // 256), seed, 0.01)
+    for name, n, sig in (("tok_emb", V * h, 0.02), ("router", L * E * h, 0.02)):
+        dev[name] = ctx.new_buffer(4 * n)
+        R.fill_normal_f32(ctx, dev[name], n, 4242 + len(name), sig)
+    ones = np.ones(L * h, np.float32)
+    dev["attn_norm"], dev["ffn_norm"], dev["out_norm"] = ctx.buffer_from(ones), ctx.buffer_from(ones), ctx.buffer_from(ones[:h])
+    ctx.flush()
+    partial = symm.empty(2 * world * h, dtype=torch.float32, device="cuda")
+    pad = symm.empty(64, dtype=torch.int32, device="cuda")
+    pad.zero_()
+    torch.cuda.synchronize()
+    hq, hp = symm.rendezvous(partial, dist.group.WORLD), symm.rendezvous(pad, dist.group.WORLD)
+    pq = (C.c_void_p * world)(*[int(p) for p in hq.buffer_ptrs])
+    pp = (C.c_void_p * world)(*[int(p) for p in hp.buffer_ptrs])
+    dist.barrier()
+    torch.cuda.synchronize()
+    cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=V, n_experts=E, top_k=k, ff=ff,
+                     max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)
+    model = R.Model(ctx, cfg, dev, ep=(world, rank, pq, pp))
+    prompt = np.random.default_rng(1004).integers(0, V, 128).astype(np.int32)
+    dist.barrier()
+    model.generate_greedy(prompt, 8)
+    dist.barrier()
+    t0 = time.perf_counter()
+    toks = model.generate_greedy(prompt, 64)
+    dt_all = time.perf_counter() - t0
+    dist.barrier()
+    t0 = time.perf_counter()
+    model.generate_greedy(prompt, 0)
+    dt_prompt = time.perf_counter() - t0
+    t = torch.tensor([dt_all, dt_prompt], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    same = torch.tensor(toks[127:].astype(np.int64), device="cuda")
+    ref = same.clone()
+    dist.broadcast(ref, 0)
+    agree = torch.tensor([int(torch.equal(same, ref))], device="cuda")
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    dt_all, dt_prompt = float(t[0].item()), float(t[1].item())
+    res = {"decode_tok_s": 64 / max(dt_all - dt_prompt, 1e-9), "prompt_tok_s": 128 / dt_prompt, "tokens_total_s": 192 / dt_all,
+           "launches_per_token": int(model.launches_per_token), "experts_per_rank": nl, "ranks_agree_on_tokens": bool(agree.item()),
+           "note": "one token stream over the whole group; wall clock (max over ranks) around one call of 192 recorded steps"}
+    dist.barrier()
+    model.close()
+    for b in dev.values():
+        b.free()
+    return res
+
+
+def run_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=5, T_total=4096):
+    """Qwen3-MoE-shaped batched block (hidden 2048, 128 experts, top-8, intermediate 768, Q4_K -> bf16 tensor-core
+    GEMMs), 4096 tokens in all (4096/G per rank), experts split 128/G per rank, Zipf(1.1) expert popularity,
+    count-exchanged all-to-all dispatch and combine.  Reports the straggler's load beside the mean."""
+    from runit_mac_b200 import parallel as P
+    E, h, ff, k = 128, 2048, 768, 8
+    n_local, T = E // world, T_total // world
+    rb = lambda kk: kk // 256 * 144
+    gate, up = ctx.new_buffer(n_local * ff * rb(h)), ctx.new_buffer(n_local * ff * rb(h))
+    down = ctx.new_buffer(n_local * h * rb(ff))
+    for i, (b, rows, kk) in enumerate(((gate, n_local * ff, h), (up, n_local * ff, h), (down, n_local * h, ff))):
+        R.fill_weights(ctx, 2, b, rows * (kk // 256), 177 + i + 10 * rank, 0.01)
+    g = torch.Generator(device="cuda").manual_seed(1 + rank)
+    p = 1.0 / torch.arange(1, E + 1, device="cuda", dtype=torch.float64) ** 1.1
+    idx = torch.multinomial((p / p.sum()).float().expand(T, E).contiguous(), k, replacement=False, generator=g).to(torch.int32)
+    w = torch.rand(T, k, device="cuda", generator=g)
+    x = torch.randn(T, h, device="cuda", generator=g)
+
+    class GivenRouting(P.CudaBackend):
+        def route(self, _x):
+            return idx, w
+    be = GivenRouting(R, ctx, torch, grouped_min_slots=256)
+    be.set_experts(None, gate, up, down, E, n_local, h, ff, k, False)
+    ms = _time_steps(torch, dist, stream, ctx, lambda: P.ep_moe_forward_counted(be, dist, torch, x, E, k, False, world, rank), steps, world)
+    recv = torch.bincount((idx // n_local).flatten().long(), minlength=world).to(torch.float64)
+    if world > 1:
+        dist.all_reduce(recv)
+    return {"ms_per_layer": ms, "tokens_per_s_all_ranks": T_total / (ms * 1e-3), "tokens_per_rank": T,
+            "slots_per_rank_max": float(recv.max().item()), "slots_per_rank_mean": float(recv.mean().item())}
 
 
 def run_gguf_load(ctx, layers=2):
@@ -534,6 +723,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local)
     if world > 1:
+        # plain peer loads/stores and plain NCCL rings only: no NVLink multicast objects are bound (see parallel.py)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     stream = torch.cuda.Stream()   # not the legacy default stream: command lists are recorded on it
     torch.cuda.set_stream(stream)
@@ -693,28 +885,38 @@ def main():
         else:
             line["cpu_baseline"] = None
     # The extras (other rows of the path; at N > 1 they use collectives) must never cost the headline line: if they do
-    # not finish in time, rank 0 prints the line without them and every rank leaves.
-    import threading
+    # not finish in time, rank 0 prints the line without them and the extras stop at their next checkpoint, so that the
+    # ranks leave in order (process group destroyed, contexts closed).  Only if a rank is still stuck two minutes later
+    # (a collective whose peer is gone) does the process end itself: every wait on peer memory in this library is
+    # bounded and symmetric memory is not bound to a multicast object (see runit_mac_b200/parallel.py), so no GPU is
+    # left waiting on the rank that leaves.
+    state = {"printed": False, "stop": False}
+    lock = threading.Lock()
+
+    def emit(extras):
+        with lock:
+            if rank == 0 and not state["printed"]:
+                line["extras"] = extras
+                print(json.dumps(line), flush=True)
+            state["printed"] = True
 
     def give_up():
-        if rank == 0:
-            line["extras"] = {"error": "extras did not finish within %d s" % EXTRAS_LIMIT_S}
-            print(json.dumps(line), flush=True)
-        os._exit(0)
+        state["stop"] = True
+        emit({"error": "extras did not finish within %d s" % EXTRAS_LIMIT_S})
+        last = threading.Timer(120, lambda: os._exit(0))
+        last.daemon = True
+        last.start()
     watchdog = threading.Timer(EXTRAS_LIMIT_S, give_up)
     watchdog.daemon = True
     watchdog.start()
     extras = {}
     if not args.no_extras:
         try:
-            extras = run_extras(R, ctx, torch, dist, stream, rank, world, args)
+            extras = run_extras(R, ctx, torch, dist, stream, rank, world, args, stop=lambda: state["stop"])
         except Exception as exc:   # the extras never invalidate the headline line
             extras = {"error": repr(exc)[:300]}
-
     watchdog.cancel()
-    if rank == 0:
-        line["extras"] = extras
-        print(json.dumps(line), flush=True)
+    emit(extras)
     if world > 1:
         dist.destroy_process_group()
 

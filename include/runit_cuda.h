@@ -73,7 +73,8 @@ int32_t runit_memcpy_d2h(runit_ctx_t* ctx, void* dst_host, const void* src_dev, 
 int32_t runit_memset(runit_ctx_t* ctx, void* dst_dev, int32_t byte, size_t bytes);
 /* Per-op launch counter (kernels launched by this context since creation). */
 uint64_t runit_launch_count(runit_ctx_t* ctx);
-/* Kernel tuning knob for experiments: 0 = default.  See DESIGN notes in gemv.cu. */
+/* Test-only: selects kernel variants so that the parity tests can exercise every code path of the GEMV family
+ * (0 = the default choice for every key).  Not part of the reference's interface; an engine never calls it. */
 int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value);
 
 /* ── recorded command lists (no twin as a function; the role of the reference's command buffer,
@@ -177,7 +178,11 @@ int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const vo
  *    rows_total/world, of the weight matrix (w_local: those n rows).  y_all: HOST array of `world` DEVICE pointers, entry p
  *    = rank p's full-length f32 output vector as mapped into this process (peer memory for p != rank, e.g. from CUDA
  *    virtual-memory or IPC mappings / torch symmetric memory).  Every result is stored into all of them by plain peer
- *    stores.  The vectors are complete on every rank once all ranks have passed runit_peer_barrier. ── */
+ *    stores.  The vectors are complete on every rank once all ranks have passed runit_peer_barrier.
+ *    Reuse: passing the barrier of call n means every rank has ANNOUNCED epoch n, not that it has finished reading
+ *    the result of call n.  A rank that runs ahead would overwrite a vector a slower rank still reads, so alternate
+ *    between two sets of output vectors from call to call (call n+2 can only start after barrier n+1, which each rank
+ *    announces in stream order after its own reads of result n), or put a second barrier after the consumer. ── */
 int32_t runit_gemv_allgather_f32(runit_ctx_t*, int32_t fmt, const void* w_local, const void* x, void* const* y_all,
                                  uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k);
 /* One-kernel barrier over peer memory.  signal_pads: HOST array of `world` DEVICE pointers, entry p = rank p's pad of at
@@ -242,7 +247,9 @@ int32_t runit_moe_layer_q4k_ep(runit_ctx_t*, const void* router_w, const void* g
  *   - Shapes whose intermediates do not fit (runit_moe_scratch_bytes(T,h,ff,E,k) > capacity; e.g. OLMoE
  *     shapes beyond 32 tokens) are rejected with RUNIT_ERR_BUFFER_SIZE and nothing is launched.
  *   - The first call on a device looks up the region's device address (once per device, with that device
- *     made current for the lookup); make that first call before any stream capture is started.
+ *     made current for the lookup) and keeps it for the life of the process; make that first call before any
+ *     stream capture is started.  The kept address does not survive cudaDeviceReset: a process that resets a
+ *     device must not use this entry point on it afterwards.
  *   - All calls share the one region and it keeps the previous call's contents; every part the block reads
  *     is rewritten first, so nothing needs clearing, but two calls that overlap on the GPU (different
  *     streams or contexts of one process on the same device) race on it: keep them ordered. */
@@ -341,6 +348,11 @@ uint64_t runit_model_launches_per_token(runit_model_t* model);
 /* Synthetic weights written on the device (benchmark / test data, distributions of the
  * benchmark configurations): n_blocks blocks of the format from a counter-based generator. */
 int32_t runit_fill_weights(runit_ctx_t*, int32_t fmt, void* dst, uint64_t n_blocks, uint64_t seed, float sigma);
+/* Q4_K blocks whose weights have zero mean: dmin = f16(7.5 d) and min index = scale index in every sub-block, so that
+ * d*sc*q - dmin*m = d*sc*(q - 7.5).  With the benchmark's distributions every weight has a positive mean and a
+ * random-init decoder repeats one token; the parity tests of the full decoder use this variant so that the greedy
+ * token stream depends on its input. */
+int32_t runit_fill_weights_q4k_zero_mean(runit_ctx_t*, void* dst, uint64_t n_blocks, uint64_t seed, float sigma);
 /* N(0, sigma) f32 values from the same generator. */
 int32_t runit_fill_normal_f32(runit_ctx_t*, void* dst, uint64_t n, uint64_t seed, float sigma);
 

@@ -82,6 +82,13 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
         return RUNIT_ERR_ALLOC;
     }
     memset(c->h_status, 0, 64);
+    if (cudaMalloc((void**)&c->d_abort, 64) != cudaSuccess || cudaMemset(c->d_abort, 0, 64) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFreeHost(c->h_status);
+        if (c->owns_stream) cudaStreamDestroy(c->stream);
+        delete c;
+        return RUNIT_ERR_ALLOC;
+    }
     // Staging area of the batched GEMV (its activations, quantised once per call): 4 MiB = K up to 232,960.
     if (cudaMalloc(&c->d_xq, 4u << 20) == cudaSuccess) c->xq_bytes = 4u << 20;
     else { c->d_xq = nullptr; cudaGetLastError(); }
@@ -144,6 +151,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     cudaStreamSynchronize(ctx->stream);   // Drop flushes, context.rs:299-304
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->d_xq) cudaFree(ctx->d_xq);
+    if (ctx->d_abort) cudaFree(ctx->d_abort);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RUNIT_OK;
@@ -156,8 +164,11 @@ int32_t runit_flush(runit_ctx_t* ctx) {
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) runit_fail(ctx, RUNIT_ERR_LAUNCH, "stream synchronize: %s", cudaGetErrorString(e));
     if (ctx->h_status && ctx->h_status[0] != 0) {
+        const int32_t why = ctx->h_status[0];
         ctx->h_status[0] = 0;
-        runit_fail(ctx, RUNIT_ERR_TIMEOUT, "a kernel gave up a bounded wait (bulk copy never completed)");
+        if (ctx->d_abort) cudaMemset(ctx->d_abort, 0, 4);   // the stream is idle: barriers wait again after this report
+        runit_fail(ctx, RUNIT_ERR_TIMEOUT, why == 3 ? "a peer barrier gave up: a rank never announced its epoch"
+                                                    : "a kernel gave up a bounded wait (a copy or a dependency never completed)");
     }
     int32_t st = ctx->sticky_status;
     ctx->sticky_status = RUNIT_OK;   // the message stays readable until the next error
@@ -174,7 +185,6 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     if (!ctx || !key) return RUNIT_ERR_BAD_ARG;
     if (!strcmp(key, "gemv_variant")) ctx->tune.gemv_variant = value;
     else if (!strcmp(key, "gemv_stages")) ctx->tune.gemv_stages = value;
-    else if (!strcmp(key, "moe_variant")) ctx->tune.moe_variant = value;
     else if (!strcmp(key, "pdl")) ctx->tune.pdl = value;
     else if (!strcmp(key, "gemv_load")) ctx->tune.gemv_load = value;
     else if (!strcmp(key, "gemv_ksl")) ctx->tune.gemv_ksl = value;

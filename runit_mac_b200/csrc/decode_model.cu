@@ -331,6 +331,9 @@ int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uin
         const bool prompt_step = i + 1 < n_prompt;
         cudaGraphExec_t g = (prompt_step && skip_prompt_logits) ? m->graph_prompt : m->graph_full;
         RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(g, ctx->stream));
+        // a bounded wait already gave up (e.g. a rank of the expert-parallel group is missing): stop feeding the stream,
+        // the flush below reports it
+        if (ctx->h_status && *reinterpret_cast<volatile int32_t*>(ctx->h_status) != 0) break;
     }
     RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(out_tokens, m->out_tokens, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return runit_flush(ctx);

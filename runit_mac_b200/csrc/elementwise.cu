@@ -114,7 +114,8 @@ __device__ __forceinline__ float normal(uint64_t seed, uint64_t i) {
 // Q4_0: nibbles uniform 0..15, d = f16(|N(0,sigma)|/8).
 // Q4_K: d, dmin = f16(|N(0,sigma)|), 6-bit scales/mins uniform 0..63 (any 12 bytes decode to
 //       that), nibbles uniform 0..15.
-__global__ void fill_weights_kernel(int fmt, uint8_t* dst, uint64_t n_blocks, uint64_t seed, float sigma) {
+// zero_mean (Q4_K only): dmin = f16(7.5 d), the 6-bit min of every sub-block equals its scale.
+__global__ void fill_weights_kernel(int fmt, uint8_t* dst, uint64_t n_blocks, uint64_t seed, float sigma, int zero_mean) {
     const uint64_t blk = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (blk >= n_blocks) return;
     if (fmt == RUNIT_FMT_Q8_0) {
@@ -146,7 +147,8 @@ __global__ void fill_weights_kernel(int fmt, uint8_t* dst, uint64_t n_blocks, ui
     } else {
         uint8_t* p = dst + blk * 144;
         const unsigned short db = __half_as_ushort(__float2half_rn(fabsf(normal(seed, blk * 24)) * sigma));
-        const unsigned short mb = __half_as_ushort(__float2half_rn(fabsf(normal(seed, blk * 24 + 1)) * sigma));
+        unsigned short mb = __half_as_ushort(__float2half_rn(fabsf(normal(seed, blk * 24 + 1)) * sigma));
+        if (zero_mean) mb = __half_as_ushort(__float2half_rn(7.5f * __half2float(__ushort_as_half(db))));
         p[0] = db & 0xFF; p[1] = db >> 8; p[2] = mb & 0xFF; p[3] = mb >> 8;
         for (int i = 0; i < 18; i++) {
             uint64_t r = rnd(seed, blk * 24 + 2 + i);
@@ -154,6 +156,15 @@ __global__ void fill_weights_kernel(int fmt, uint8_t* dst, uint64_t n_blocks, ui
             for (int c = 0; c < 8 && base + c < 144; c++) {
                 p[base + c] = (uint8_t)(r & 0xFF);
                 r >>= 8;
+            }
+        }
+        if (zero_mean) {
+            // scale bytes s[0..11] (get_scale_min_k4, crates/engine/src/forward.rs:359-369): s[j+4] = s[j] makes the low six
+            // bits and the two spill bits of min j (j+4) equal those of scale j (j+4); equal nibbles in s[j+8] do the rest
+            for (int j = 0; j < 4; j++) {
+                p[4 + 4 + j] = p[4 + j];
+                const uint8_t n = p[4 + 8 + j] & 0x0F;
+                p[4 + 8 + j] = (uint8_t)(n | (n << 4));
             }
         }
     }
@@ -225,8 +236,16 @@ int32_t runit_fill_weights(runit_ctx_t* ctx, int32_t fmt, void* dst, uint64_t n_
     RUNIT_REQUIRE(ctx, fmt >= 0 && fmt <= 2 && dst && n_blocks > 0, "fill_weights: bad argument");
     RUNIT_REQUIRE(ctx, n_blocks < (1ull << 38), "fill_weights: too many blocks");
     const uint64_t grid = (n_blocks + 255) / 256;
-    fill_weights_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(fmt, (uint8_t*)dst, n_blocks, seed, sigma);
+    fill_weights_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(fmt, (uint8_t*)dst, n_blocks, seed, sigma, 0);
     return runit_after_launch(ctx, "fill_weights");
+}
+
+int32_t runit_fill_weights_q4k_zero_mean(runit_ctx_t* ctx, void* dst, uint64_t n_blocks, uint64_t seed, float sigma) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, dst && n_blocks > 0 && n_blocks < (1ull << 38), "fill_weights_q4k_zero_mean: bad argument");
+    const uint64_t grid = (n_blocks + 255) / 256;
+    fill_weights_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(RUNIT_FMT_Q4K, (uint8_t*)dst, n_blocks, seed, sigma, 1);
+    return runit_after_launch(ctx, "fill_weights_q4k_zero_mean");
 }
 
 int32_t runit_fill_normal_f32(runit_ctx_t* ctx, void* dst, uint64_t n, uint64_t seed, float sigma) {

@@ -363,17 +363,22 @@ struct PeerPads {
 };
 // epoch_ptr != nullptr: the epoch is that device word + 1, and the word is advanced once the barrier has been passed
 // (recorded command lists replay the same launch for every call).
+// abort: device word of the context.  The first barrier that gives up sets it; while it is set every later barrier still
+// announces its epoch and advances the epoch word but does not wait, so a queue of recorded barriers behind a missing
+// rank costs one time limit in total instead of one each.  runit_flush clears it when it reports the time-out.
 __global__ void peer_barrier_kernel(const PeerPads pp, uint32_t world, uint32_t rank, uint32_t epoch, int32_t* status,
-                                    uint32_t* epoch_ptr) {
+                                    uint32_t* epoch_ptr, uint32_t* abort) {
     uint32_t* const* pads = pp.p;
     const uint32_t p = threadIdx.x;
     if (epoch_ptr) epoch = *epoch_ptr + 1u;
+    const bool aborted = abort && *reinterpret_cast<volatile uint32_t*>(abort) != 0u;
     __syncwarp();
     if (p == 0 && epoch_ptr) *epoch_ptr = epoch;   // read by every lane above; the following kernels see the new value
     if (p >= world) return;
     // The stores of the preceding kernels (results pushed into the peers' memory) are ordered before the flag.
     __threadfence_system();
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pads[p] + rank), "r"(epoch) : "memory");
+    if (aborted) return;
     const uint32_t* mine = pads[rank] + p;
     const long long t0 = clock64();
     while (true) {
@@ -382,6 +387,7 @@ __global__ void peer_barrier_kernel(const PeerPads pp, uint32_t world, uint32_t 
         if ((int32_t)(v - epoch) >= 0) break;
         if (clock64() - t0 > (1ll << 30)) {   // about half a second: the peer never signalled
             if (status) atomicExch(status, 3);
+            if (abort) atomicExch(abort, 1u);
             break;
         }
         __nanosleep(200);
@@ -426,7 +432,7 @@ int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t w
         RUNIT_REQUIRE(ctx, signal_pads[p] && runit_aligned(signal_pads[p], 4), "peer_barrier: null or misaligned pad %u", p);
         h.p[p] = (uint32_t*)signal_pads[p];
     }
-    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status, epoch_ptr);
+    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status, epoch_ptr, ctx->d_abort);
     return runit_after_launch(ctx, "peer_barrier");
 }
 }  // namespace runit

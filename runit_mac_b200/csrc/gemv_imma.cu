@@ -47,8 +47,11 @@ __global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict
         float amax = fabsf(v);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float s = amax * (1.0f / 16383.0f);
-        const int q = amax > 0.f ? __float2int_rn(v * (16383.0f / amax)) : 0;
+        // an Inf or a NaN in the block (fmaxf would drop the NaN) gives a NaN scale: every row's result of that activation
+        // row becomes NaN, as a non-finite activation does (to +-Inf or NaN) in the reference's f32 multiply-add chain
+        const bool bad = __any_sync(0xffffffffu, !(fabsf(v) <= 3.0e38f));
+        const float s = bad ? __uint_as_float(0x7FC00000u) : amax * (1.0f / 16383.0f);
+        const int q = (amax > 0.f && !bad) ? __float2int_rn(v * (16383.0f / amax)) : 0;
         int qs = q;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);

@@ -27,6 +27,23 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // uns
     return d;
 }
 
+// Bit pattern of max |v| over a block of 32 activations held by LPB lanes with EPL values each; a NaN or an Inf anywhere
+// in the block gives a pattern with exponent 255 (fmaxf alone would drop a NaN).  The 0 * v products are exact zeros for
+// finite v and NaN otherwise; the cross-lane maximum is taken on the bit patterns, which order like the magnitudes.
+template <int EPL, int LPB>
+__device__ __forceinline__ uint32_t block_max_bits(const float (&v)[EPL]) {
+    float m = 0.f, z = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; i++) {
+        m = fmaxf(m, fabsf(v[i]));
+        z = fmaf(v[i], 0.f, z);
+    }
+    uint32_t mb = __float_as_uint(fabsf(m + z));
+#pragma unroll
+    for (int o = 1; o < LPB; o <<= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+    return mb;
+}
+
 // Layout of the prepared activations of one unit (in place of the raw f32 slice):
 //   block b (32 elements), limb l: 32 bytes at b*96 + l*32;  then scale[NB] (f32) and vsum[NB] (i32).
 template <int NB>
@@ -39,19 +56,19 @@ struct IntX {
 template <int EPL, int NB, int ORDER>
 __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL], int lane) {
     constexpr int LPB = 32 / EPL;                 // lanes per block
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < EPL; i++) m = fmaxf(m, fabsf(v[i]));
-#pragma unroll
-    for (int o = 1; o < LPB; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const uint32_t e = __float_as_uint(m) >> 23;  // biased exponent of the block maximum
-    const bool live = e >= 22u && e < 255u;       // zero / denormal-tiny (or non-finite) blocks contribute nothing
+    const uint32_t mb = block_max_bits<EPL, LPB>(v);
+    const float m = __uint_as_float(mb);
+    (void)m;
+    const uint32_t e = mb >> 23;                  // biased exponent of the block maximum (255: a non-finite activation)
+    const bool live = e >= 22u && e < 255u;       // zero / denormal-tiny blocks contribute nothing
     const float inv = live ? __uint_as_float((275u - e) << 23) : 0.f;     // 2^22 / 2^(e-126)
-    const float scale = live ? __uint_as_float((e - 21u) << 23) : 0.f;    // 2^(e-126) / 2^22
+    // a block that holds an Inf or a NaN gets a NaN scale: every row's sum becomes NaN, as a non-finite activation
+    // does (to +-Inf or NaN) in the reference's f32 multiply-add chain
+    const float scale = live ? __uint_as_float((e - 21u) << 23) : (e == 255u ? __uint_as_float(0x7FC00000u) : 0.f);    // 2^(e-126) / 2^22
     int a0[EPL], a1[EPL], a2[EPL], vs = 0;
 #pragma unroll
     for (int i = 0; i < EPL; i++) {
-        const int q = __float2int_rn(v[i] * inv);   // exact product, one rounding; |q| < 2^22
+        const int q = live ? __float2int_rn(v[i] * inv) : 0;   // exact product, one rounding; |q| < 2^22
         vs += q;
         a0[i] = (int)(int8_t)q;
         const int q1 = (q - a0[i]) >> 8;
@@ -236,18 +253,18 @@ struct MmaX {   // prepared activations of one unit: per block 32 high bytes + 3
 template <int NB, int ORDER>
 __device__ __forceinline__ void prep_mma_block(uint8_t* xq, float (&v)[8], int lane, int nblk) {
     const int blk = lane >> 2, t = lane & 3;
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) m = fmaxf(m, fabsf(v[i]));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    const uint32_t mb = block_max_bits<8, 4>(v);
+    const float m = __uint_as_float(mb);
     // Power-of-two scale (scaling is exact, small-integer activations stay exact): m in [2^e, 2^(e+1)) maps to
     // |q| < 2^15; the two signed bytes reach 127 * 256 + 127 = 32639, so the top sliver of a binade takes half the scale.
-    const uint32_t eb = __float_as_uint(m) >> 23;                 // biased exponent of the block maximum
-    const bool live = blk < nblk && eb >= 20u && eb < 255u;       // zero, denormal-tiny or non-finite blocks contribute nothing
-    const uint32_t sh = m * __uint_as_float((268u - eb) << 23) > 32639.0f ? 1u : 0u;
+    const uint32_t eb = mb >> 23;                                 // biased exponent of the block maximum (255: non-finite)
+    const bool live = blk < nblk && eb >= 20u && eb < 255u;       // zero or denormal-tiny blocks contribute nothing
+    const uint32_t sh = live && m * __uint_as_float((268u - eb) << 23) > 32639.0f ? 1u : 0u;
     const float inv = live ? __uint_as_float((268u - eb - sh) << 23) : 0.f;     // 2^(14 - e - sh)
-    const float scale = live ? __uint_as_float((eb - 14u + sh) << 23) : 0.f;    // 1 / inv
+    // a block that holds an Inf or a NaN gets a NaN scale (and a NaN scale * sum): every row's result becomes NaN, as a
+    // non-finite activation does (to +-Inf or NaN) in the reference's f32 multiply-add chain
+    const float scale = live ? __uint_as_float((eb - 14u + sh) << 23)           // 1 / inv
+                             : ((blk < nblk && eb == 255u) ? __uint_as_float(0x7FC00000u) : 0.f);
     uint32_t q[8], qa[8];
     int vs = 0;
 #pragma unroll

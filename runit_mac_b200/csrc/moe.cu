@@ -262,8 +262,9 @@ __global__ void __launch_bounds__(256) ep_partial_kernel(const float* __restrict
     for (uint32_t p = 0; p < world; p++) peers.p[p][o] = acc;
 }
 // out[t] = residual[t] + sum over ranks (rank order) of the partial sums that arrived in this rank's buffer.
-__global__ void __launch_bounds__(256) ep_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ residual,
-                                                         float* __restrict__ out, uint32_t world, uint32_t T, uint32_t h,
+// `out` may be the same buffer as `residual` (the decoder adds into its hidden state in place): neither is restrict.
+__global__ void __launch_bounds__(256) ep_reduce_kernel(const float* __restrict__ partial, const float* residual,
+                                                         float* out, uint32_t world, uint32_t T, uint32_t h,
                                                          uint32_t epoch, const uint32_t* __restrict__ epoch_ptr) {
     const uint32_t c = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
     if (c >= h) return;

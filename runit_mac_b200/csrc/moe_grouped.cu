@@ -1,6 +1,6 @@
 // Batched (prefill-sized) MoE block on the tensor cores: token permutation by expert, then two grouped GEMMs whose
-// weight operand is dequantised from Q4_K to bf16 tiles in shared memory and multiplied with tcgen05.mma into
-// f32 accumulators in tensor memory.
+// weight operand is dequantised from Q4_K to bf16 tiles and multiplied with tcgen05.mma into f32 accumulators in
+// tensor memory.
 //
 // The reference has no batched MoE kernel: its prefill runs the decode block once per token
 // (crates/engine/src/prefill.rs:156-215: per token a router GEMV, a flush, CPU top-k, and per selected expert
@@ -9,16 +9,17 @@
 // with every weight the bf16 rounding of the Q4_K value d*sc*q - dmin*m (crates/engine/src/forward.rs:1026-1057),
 // f32 accumulation, and the weighted sum taken in routing order.
 //
-// Layout of one grouped GEMM (weight rows ride the 128-wide M of the MMA, tokens ride N):
-//   * slots (token, expert) are sorted by expert; every expert's slots start at a multiple of 128 rows
-//     ("token tile"), so a tile never mixes experts;
-//   * work item = (token tile, block of 128 weight rows); persistent CTAs take items round-robin;
-//   * per 64-wide K step: A = 128 weight rows x 64 (dequantised by 8 warps straight from global memory into the
-//     128-byte-swizzled K-major layout), B = 128 token rows x 64 (one TMA tiled load with the same swizzle),
-//     4 MMAs of K = 16 (x2 when gate and up are fused);
-//   * warp roles: 0 = TMA producer (+ tensor-memory allocation), 1 = MMA issuer, 2-5 = epilogue (tensor memory ->
-//     registers -> global), 6-13 = dequantisers; two accumulator buffers so that the epilogue of one item overlaps
-//     the MMAs of the next.
+// Layout of one grouped GEMM (weight rows ride the M of the MMA, token slots ride N):
+//   * slots (token, expert) are sorted by expert; every expert's slots start at a multiple of 128 rows of the
+//     permuted order and are cut into token tiles of up to 256 slots, so a tile never mixes experts;
+//   * work item = (token tile, block of 256 weight rows); persistent clusters of two CTAs (cta_group::2) take items
+//     round-robin, each CTA owning 128 of the rows and half of the token tile;
+//   * per 128-wide K step: the weight operand is dequantised by 16 warps from raw Q4_K superblocks (TMA ring in shared
+//     memory) straight into tensor memory (tcgen05.st), the token tile arrives by TMA into 128-byte-swizzled shared
+//     memory, and the leader CTA issues 8 MMAs of M = 256, N <= 256, K = 16;
+//   * 23 warps per CTA: 0 = token-tile producer (+ tensor-memory allocation), 1 = MMA issuer (leader CTA), 2-5 =
+//     epilogue (tensor memory -> registers -> global), 6-21 = dequantisers, 22 = raw-superblock producer.
+// The reasons for each of these choices, with the measurements behind them, are in the comment above the kernel.
 // Every wait is bounded in time; a wait that gives up raises the CTA's abort flag, all roles leave their loops,
 // tensor memory is freed and the host sees RUNIT_ERR_TIMEOUT at the next flush.
 #include <cuda_bf16.h>
@@ -35,8 +36,7 @@ constexpr int kTok = 128;                  // token slots per tile (MMA N, at mo
 constexpr int kRows = 128;                 // weight rows per tile (MMA M)
 constexpr int kKC = 64;                    // K elements per pipeline stage: one 128-byte row of bf16
 constexpr int kTileBytes = kRows * 128;    // 16 KiB
-constexpr int kThreads = 448;              // 14 warps
-constexpr int kEpiWarp0 = 2, kDeqWarp0 = 6, kDeqWarps = 8;
+constexpr int kEpiWarp0 = 2;                // first of the four epilogue warps
 
 struct Args {
     const uint8_t* w0;            // stacked expert matrices [E][rows][K/256 * 144]
@@ -53,7 +53,7 @@ struct Args {
     int32_t* status;
 };
 
-// ── dequantisation of one 64-element K chunk of one weight row into the swizzled A tile ──
+// ── dequantisation of one 64-element K chunk of one weight row ──
 // q: the 8 words (32 bytes) of the chunk; low nibbles are elements 0..31 (scale pair lo), high nibbles elements
 // 32..63 (scale pair hi).  A field at bit p becomes 2^23 + nibble*2^p with one LOP3, the magic is subtracted, and one
 // FMA with (scale * 2^-p, -min) gives exactly fl(scale*nibble - min); pairs are rounded to bf16 with one cvt.
@@ -70,43 +70,7 @@ __device__ __forceinline__ float hi_f(uint64_t v) { return __uint_as_float((uint
 // __fdividef returns 0 for an infinite or very large denominator, which is the limit of silu there; error <= 2 ulp.
 __device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
-template <bool LO, bool HI>
-__device__ __forceinline__ void dequant_chunk(const uint32_t* q, float s_lo, float m_lo, float s_hi, float m_hi,
-                                              uint32_t row_addr, uint32_t rx) {
-    const uint64_t neg_magic = packf(-kTwo23);
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        const uint64_t P = pack2(q[2 * c], q[2 * c + 1]);
-        const uint64_t P12 = pack2(q[2 * c] >> 12, q[2 * c + 1] >> 12);
-        if (LO) {   // bytes 0..3 low nibbles: bits 0, 8, 16 of P and bit 12 of P12
-            const uint64_t nm = packf(-m_lo);
-            const uint64_t o0 = ffma2(fadd2(field_or_magic<0xFu << 0>(P), neg_magic), packf(s_lo), nm);
-            const uint64_t o1 = ffma2(fadd2(field_or_magic<0xFu << 8>(P), neg_magic), packf(s_lo * exp2_neg(8)), nm);
-            const uint64_t o2 = ffma2(fadd2(field_or_magic<0xFu << 16>(P), neg_magic), packf(s_lo * exp2_neg(16)), nm);
-            const uint64_t o3 = ffma2(fadd2(field_or_magic<0xFu << 12>(P12), neg_magic), packf(s_lo * exp2_neg(12)), nm);
-            // elements 8c+{0,1,2,3} come from word 2c (low halves), 8c+{4..7} from word 2c+1 (high halves)
-            const uint32_t v0 = bf16x2(lo_f(o0), lo_f(o1)), v1 = bf16x2(lo_f(o2), lo_f(o3));
-            const uint32_t v2 = bf16x2(hi_f(o0), hi_f(o1)), v3 = bf16x2(hi_f(o2), hi_f(o3));
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)c ^ rx) << 4)), "r"(v0),
-                         "r"(v1), "r"(v2), "r"(v3)
-                         : "memory");
-        }
-        if (HI) {   // high nibbles: bits 4, 12 of P and bits 8, 16 of P12
-            const uint64_t nm = packf(-m_hi);
-            const uint64_t o0 = ffma2(fadd2(field_or_magic<0xFu << 4>(P), neg_magic), packf(s_hi * exp2_neg(4)), nm);
-            const uint64_t o1 = ffma2(fadd2(field_or_magic<0xFu << 12>(P), neg_magic), packf(s_hi * exp2_neg(12)), nm);
-            const uint64_t o2 = ffma2(fadd2(field_or_magic<0xFu << 8>(P12), neg_magic), packf(s_hi * exp2_neg(8)), nm);
-            const uint64_t o3 = ffma2(fadd2(field_or_magic<0xFu << 16>(P12), neg_magic), packf(s_hi * exp2_neg(16)), nm);
-            const uint32_t v0 = bf16x2(lo_f(o0), lo_f(o1)), v1 = bf16x2(lo_f(o2), lo_f(o3));
-            const uint32_t v2 = bf16x2(hi_f(o0), hi_f(o1)), v3 = bf16x2(hi_f(o2), hi_f(o3));
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)(c + 4) ^ rx) << 4)),
-                         "r"(v0), "r"(v1), "r"(v2), "r"(v3)
-                         : "memory");
-        }
-    }
-}
-
-// The same arithmetic with the 32 values of one nibble half (low nibbles: elements 0..31, high: 32..63 of the chunk)
+// The 32 values of one nibble half (low nibbles: elements 0..31, high: 32..63 of the chunk)
 // packed as 16 bf16 pairs in registers, in K order: out[i] = (element 2i, element 2i+1).
 template <bool HI>
 __device__ __forceinline__ void dequant_half(const uint32_t* q, float sc, float mn, uint32_t (&out)[16]) {
@@ -132,211 +96,6 @@ __device__ __forceinline__ void dequant_half(const uint32_t* q, float sc, float 
         out[4 * c + 2] = bf16x2(hi_f(o0), hi_f(o1));
         out[4 * c + 3] = bf16x2(hi_f(o2), hi_f(o3));
     }
-}
-
-struct Raw {   // one Q4_K superblock of one row: header (d, dmin, 12 scale bytes) + 128 quant bytes
-    uint4 v[9];
-};
-__device__ __forceinline__ void load_raw(Raw& r, const uint8_t* p) {
-    const uint4* s = reinterpret_cast<const uint4*>(p);
-#pragma unroll
-    for (int i = 0; i < 9; i++) r.v[i] = __ldg(s + i);
-}
-
-template <bool DUAL>
-struct Cfg {
-    static constexpr int NA = DUAL ? 2 : 1;              // weight tiles per stage
-    static constexpr int NS = DUAL ? 4 : 6;              // pipeline stages
-    static constexpr int STAGE = (NA + 1) * kTileBytes;  // A tile(s) + token tile
-    static constexpr int ACC_COLS = DUAL ? 256 : 128;    // tensor-memory columns of one accumulator buffer
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;
-    static constexpr int CTRL = NS * STAGE;              // offset of the barrier block
-    static constexpr int SMEM = CTRL + 256 + 1024;       // + slack to align the tiles to 1024 bytes
-};
-
-template <bool DUAL>
-__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_b, const Args a) {
-    using C = Cfg<DUAL>;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* ctrl = smem_raw + (base - smem_u32(smem_raw)) + C::CTRL;
-    const uint32_t bar_full = base + C::CTRL, bar_empty = bar_full + 8 * C::NS, bar_accf = bar_empty + 8 * C::NS,
-                   bar_acce = bar_accf + 16;
-    const uint32_t holder = bar_acce + 16;
-    volatile uint32_t* holder_p = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::NS + 32);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * C::NS + 36);
-
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) {
-        for (int s = 0; s < C::NS; s++) {
-            mbar_init(bar_full + 8 * s, kDeqWarps + 1);
-            mbar_init(bar_empty + 8 * s, 1);
-        }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(bar_accf + 8 * b, 1);
-            mbar_init(bar_acce + 8 * b, 4);
-        }
-        *abort_flag = 0;
-        fence_mbar_init();
-    }
-    if (warp == 0) {
-        tmem_alloc(holder, C::TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = *holder_p;
-
-    const uint32_t n_items = (uint32_t)(*a.n_tok_tiles) * a.nb;
-    const uint32_t kchunks = a.K / kKC;
-    const uint32_t units = a.K / 256;
-
-    if (warp == 0) {
-        // ───────── TMA producer: token tile of every stage ─────────
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (uint32_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const uint32_t row_start = (uint32_t)a.tile_row0[item / a.nb];
-                for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
-                    const uint32_t s = it % C::NS, ph = (it / C::NS) & 1;
-                    if (!mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag)) break;
-                    mbar_expect_tx(bar_full + 8 * s, kTileBytes);
-                    tma_load_2d(base + s * C::STAGE + C::NA * kTileBytes, &map_b, (int32_t)(kc * 128), (int32_t)row_start,
-                                bar_full + 8 * s);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ───────── MMA issuer ─────────
-        if (lane == 0) {
-            uint32_t it = 0, n = 0;
-            for (uint32_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x, n++) {
-                const int32_t nvalid = a.tile_nvalid[item / a.nb];
-                const uint32_t ncols = nvalid <= 16 ? 16u : (uint32_t)((nvalid + 15) & ~15);
-                const uint32_t idesc = umma_idesc_bf16(kRows, ncols);
-                const uint32_t b = n & 1;
-                if (!mbar_wait_timed(bar_acce + 8 * b, ((n >> 1) & 1) ^ 1, abort_flag)) break;
-                tc_fence_after_sync();
-                const uint32_t d_addr = tmem_base + b * C::ACC_COLS;
-                bool ok = true;
-                for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
-                    const uint32_t s = it % C::NS, ph = (it / C::NS) & 1;
-                    if (!mbar_wait_timed(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
-                    tc_fence_after_sync();
-                    const uint32_t sb = base + s * C::STAGE;
-                    const uint64_t da0 = umma_desc_sw128(sb), db = umma_desc_sw128(sb + C::NA * kTileBytes);
-#pragma unroll
-                    for (uint32_t k4 = 0; k4 < 4; k4++) {
-                        const uint32_t acc = (kc | k4) != 0;
-                        umma_bf16(d_addr, da0 + 2 * k4, db + 2 * k4, idesc, acc);
-                        if (DUAL) umma_bf16(d_addr + 128, umma_desc_sw128(sb + kTileBytes) + 2 * k4, db + 2 * k4, idesc, acc);
-                    }
-                    umma_commit(bar_empty + 8 * s);   // the stage may be refilled once these MMAs have read it
-                }
-                if (!ok) break;
-                umma_commit(bar_accf + 8 * b);        // accumulator complete
-            }
-        }
-    } else if (warp < kDeqWarp0) {
-        // ───────── epilogue: tensor memory -> registers -> global ─────────
-        const uint32_t quarter = warp & 3;
-        uint32_t n = 0;
-        for (uint32_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x, n++) {
-            const uint32_t tt = item / a.nb, rb = item % a.nb;
-            const int32_t nvalid = a.tile_nvalid[tt];
-            const uint32_t b = n & 1;
-            // one lane polls; the others are released (and ordered) by the warp barrier
-            uint32_t got = 1;
-            if (lane == 0) got = mbar_wait_timed(bar_accf + 8 * b, (n >> 1) & 1, abort_flag);
-            got = __shfl_sync(0xffffffffu, got, 0);
-            if (!got) break;
-            tc_fence_after_sync();
-            const uint32_t col = rb * kRows + quarter * 32 + lane;   // output feature = weight row
-            const size_t row0 = (size_t)a.tile_row0[tt];
-#pragma unroll 1
-            for (int cg = 0; cg < 4; cg++) {
-                if (cg * 32 >= nvalid) break;
-                const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + b * C::ACC_COLS + cg * 32;
-                uint32_t g[32];
-                tmem_ld32(taddr, g);
-                if (DUAL) {
-                    uint32_t u[32];
-                    tmem_ld32(taddr + 128, u);
-                    tmem_ld_wait();
-                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (cg * 32 + i < nvalid)
-                            out[(row0 + cg * 32 + i) * a.ld + col] =
-                                __float2bfloat16_rn(silu_fast(__uint_as_float(g[i])) * __uint_as_float(u[i]));
-                } else {
-                    tmem_ld_wait();
-                    float* out = reinterpret_cast<float*>(a.out);
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (cg * 32 + i < nvalid) out[(row0 + cg * 32 + i) * a.ld + col] = __uint_as_float(g[i]);
-                }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acce + 8 * b);
-        }
-    } else {
-        // ───────── dequantisers: Q4_K rows from global memory -> bf16 swizzled A tiles ─────────
-        const uint32_t d = tid - kDeqWarp0 * 32;
-        const uint32_t part = d >> 7, r = d & 127;     // fused: part = matrix (gate / up); else low / high nibbles
-        const uint32_t rx = r & 7;
-        const uint8_t* wsel = (DUAL && part) ? a.w1 : a.w0;
-        const size_t row_bytes = (size_t)units * 144;
-        auto src = [&](uint32_t item, uint32_t u) -> const uint8_t* {
-            const uint32_t tt = item / a.nb, rb = item % a.nb;
-            const size_t e = (size_t)a.tile_expert[tt];
-            return wsel + ((e * a.rows + (size_t)rb * kRows + r) * row_bytes) + (size_t)u * 144;
-        };
-        Raw cur, nxt;
-        uint32_t item = blockIdx.x, u = 0, it = 0;
-        if (item < n_items) load_raw(cur, src(item, 0));
-        bool ok = true;
-        while (item < n_items && ok && !*abort_flag) {
-            // prefetch the next superblock of this row (or the first one of the next item)
-            uint32_t item2 = item, u2 = u + 1;
-            if (u2 == units) { u2 = 0; item2 += gridDim.x; }
-            if (item2 < n_items) load_raw(nxt, src(item2, u2));
-            const uint32_t* w = reinterpret_cast<const uint32_t*>(&cur.v[0]);
-            const float dd = half_bits_to_float(w[0]), dmin = half_bits_to_float(w[0] >> 16);
-            const Q4KScales sc = q4k_unpack_scales(w[1], w[2], w[3]);
-#pragma unroll
-            for (int j = 0; j < 4; j++, it++) {
-                const uint32_t s = it % C::NS, ph = (it / C::NS) & 1;
-                uint32_t got = 1;
-                if (lane == 0) got = mbar_wait_timed(bar_empty + 8 * s, ph ^ 1, abort_flag);
-                got = __shfl_sync(0xffffffffu, got, 0);
-                if (!got) { ok = false; break; }
-                const float s_lo = dd * byte_to_float(sc.sl, j), m_lo = dmin * byte_to_float(sc.ml, j);
-                const float s_hi = dd * byte_to_float(sc.sh, j), m_hi = dmin * byte_to_float(sc.mh, j);
-                const uint32_t tile = base + s * C::STAGE + (DUAL ? part * kTileBytes : 0);
-                const uint32_t row_addr = tile + r * 128;
-                if (DUAL) dequant_chunk<true, true>(w + 4 + 8 * j, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
-                else if (part == 0) dequant_chunk<true, false>(w + 4 + 8 * j, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
-                else dequant_chunk<false, true>(w + 4 + 8 * j, s_lo, m_lo, s_hi, m_hi, row_addr, rx);
-                fence_proxy_async();   // generic-proxy stores -> visible to the tensor cores' async-proxy reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full + 8 * s);
-            }
-            cur = nxt;
-            item = item2;
-            u = u2;
-        }
-    }
-
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 0) {
-        tc_fence_after_sync();
-        tmem_dealloc(tmem_base, C::TMEM_COLS);
-    }
-    if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 2);
 }
 
 // ───────────────────────── CTA-pair kernel (cta_group::2) ─────────────────────────
@@ -800,23 +559,6 @@ static Scratch carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uint32_t E
 }
 
 template <bool DUAL>
-static int32_t launch_gemm(runit_ctx* ctx, const char* name, const Args& a, const void* b_ptr, uint32_t b_rows, uint32_t max_items) {
-    using C = Cfg<DUAL>;
-    static bool attr_set[64] = {false};
-    if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
-        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(grouped_gemm_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        attr_set[ctx->device] = true;
-    }
-    CUtensorMap map;
-    int32_t st = runit_get_tmap(ctx, b_ptr, b_rows, (uint64_t)a.K * 2, kTok, 128, &map, 1);
-    if (st != RUNIT_OK) return st;
-    uint32_t grid = (uint32_t)ctx->sm_count;
-    if (grid > max_items) grid = max_items;
-    grouped_gemm_kernel<DUAL><<<grid, kThreads, C::SMEM, ctx->stream>>>(map, a);
-    return runit_after_launch(ctx, name);
-}
-
-template <bool DUAL>
 static int32_t launch_pair(runit_ctx* ctx, const char* name, const Args& a, const void* b_ptr, uint32_t b_rows, uint32_t n_experts,
                            uint32_t max_items) {
     static bool attr_set[64] = {false};
@@ -840,17 +582,15 @@ static int32_t launch_pair(runit_ctx* ctx, const char* name, const Args& a, cons
 }
 
 // The expert part of the block for given routing (idx int32 [T][k], w f32 [T][k]).
-// tune.moe_variant == 1 selects the single-CTA kernels (128-slot tiles); the default is the CTA-pair kernels.
 static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, const void* up, const void* down,
                             const float* x, const int32_t* idx, const float* w, const float* residual, float* out,
                             uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
     const uint32_t S = T * k;
-    const bool single = ctx->tune.moe_variant == 1;
     RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(s.counts, 0, 4 * 256, ctx->stream));
     count_kernel<<<(S + 4095) / 4096, 256, 0, ctx->stream>>>(idx, S, E, s.counts, s.pos_of_slot);
     int32_t st = runit_after_launch(ctx, "moe_grouped_count");
     if (st != RUNIT_OK) return st;
-    place_kernel<<<E, 1024, 0, ctx->stream>>>(idx, S, E, s.counts, single ? kTok : pair::kTokPair, s.pos_of_slot, s.tile_expert,
+    place_kernel<<<E, 1024, 0, ctx->stream>>>(idx, S, E, s.counts, pair::kTokPair, s.pos_of_slot, s.tile_expert,
                                               s.tile_nvalid, s.tile_row0, s.n_tok_tiles);
     if ((st = runit_after_launch(ctx, "moe_grouped_place")) != RUNIT_OK) return st;
     gather_kernel<<<(S + 7) / 8, 256, 0, ctx->stream>>>(x, s.pos_of_slot, s.xperm, S, h, k);
@@ -865,13 +605,8 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
     a2.w0 = (const uint8_t*)down; a2.w1 = nullptr; a2.rows = h; a2.K = ff; a2.nb = h / kRows;
     a2.tile_expert = s.tile_expert; a2.tile_nvalid = s.tile_nvalid; a2.tile_row0 = s.tile_row0; a2.n_tok_tiles = s.n_tok_tiles;
     a2.out = s.y; a2.ld = h; a2.status = ctx->d_status;
-    if (single) {
-        if ((st = launch_gemm<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, s.max_tiles * a1.nb)) != RUNIT_OK) return st;
-        if ((st = launch_gemm<false>(ctx, "moe_grouped_down", a2, s.act, rows, s.max_tiles * a2.nb)) != RUNIT_OK) return st;
-    } else {
-        if ((st = launch_pair<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, E, s.max_tiles * (ff / 128))) != RUNIT_OK) return st;
-        if ((st = launch_pair<false>(ctx, "moe_grouped_down", a2, s.act, rows, E, s.max_tiles * (h / 256))) != RUNIT_OK) return st;
-    }
+    if ((st = launch_pair<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, E, s.max_tiles * (ff / 128))) != RUNIT_OK) return st;
+    if ((st = launch_pair<false>(ctx, "moe_grouped_down", a2, s.act, rows, E, s.max_tiles * (h / 256))) != RUNIT_OK) return st;
     combine_kernel<<<dim3((h / 4 + 255) / 256, T), 256, 0, ctx->stream>>>(s.y, s.pos_of_slot, w, residual, out, h, k);
     return runit_after_launch(ctx, "moe_grouped_combine");
 }

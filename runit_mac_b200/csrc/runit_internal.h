@@ -14,7 +14,6 @@
 struct runit_tuning {
     int32_t gemv_variant = 0;   // 0 = staged kernel, 1 = simple warp-per-row kernel
     int32_t gemv_stages = 0;    // 0 = default
-    int32_t moe_variant = 0;
     int32_t pdl = 0;            // programmatic dependent launch between ops
     int32_t gemv_math = 0;      // batch 1: 0 = tensor-core MMAs (4-bit) / dp4a (Q8_0), 1 = packed f32, 2 = dp4a
     int32_t gemv_csplit = 0;    // 0 = automatic cluster split of K, else 2 or 4
@@ -46,6 +45,7 @@ struct runit_ctx {
     // Device scratch owned by the context (allocated at creation; ops never allocate).
     int32_t* d_status = nullptr;        // device address of the status word written by kernels with bounded waits
     int32_t* h_status = nullptr;        // the same word, host side (pinned, mapped)
+    uint32_t* d_abort = nullptr;        // device word: set by the first peer barrier that gave up; later barriers skip their wait
     void* d_xq = nullptr;               // staging area of the batched GEMV's quantised activations
     size_t xq_bytes = 0;
     void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation

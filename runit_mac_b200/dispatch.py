@@ -246,6 +246,7 @@ _TWINS = [
     ("peer_barrier", "no twin: (signal_pads[world] pointer table, world, rank, epoch)"),
     ("moe_layer_q4k_ep", "no twin: expert-parallel decode block with replicated tokens, combine fused over peer memory"),
     ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
+    ("fill_weights_q4k_zero_mean", "no twin: (dst, n_blocks, seed, sigma), Q4_K blocks with zero-mean weights"),
     ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),
 ]
 for _n, _d in _TWINS:

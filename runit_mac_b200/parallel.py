@@ -17,7 +17,15 @@ and on GPU (`CudaBackend`, C-ABI calls on torch tensors).
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
+
+# The kernels here reach peer memory with plain loads and stores only.  Left to its default, torch binds symmetric
+# memory to an NVLink multicast object as well; a rank that exits while bound to one can raise NVLink faults on the
+# other ranks' GPUs, so the binding is switched off before the first rendezvous (NCCL's in-switch reduction likewise).
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
 
 def shard_rows(m: int, world: int, rank: int):
@@ -201,34 +209,40 @@ class FusedAllGatherGemv:
     """Row-sharded GEMV whose all-gather happens in the kernel's epilogue: every rank stores its slice of the output
     straight into the output vectors of all ranks (peer stores over NVLink into symmetric memory) and one small
     barrier kernel announces completion; no collective library call on the data path.  The NCCL variant is
-    `sharded_gemv`."""
+    `sharded_gemv`.
+
+    Two output vectors alternate from call to call.  Passing barrier n only means that every rank has ANNOUNCED epoch
+    n, not that it has finished reading the result of call n, so a fast rank's call n+1 must not write where a slow
+    rank still reads: it writes the other vector.  The vector of call n is written again by call n+2, which a rank can
+    only reach after barrier n+1, and every rank announces n+1 in stream order after its own reads of result n."""
 
     def __init__(self, R, ctx, torch, dist, fmt, w_local, rows_total, k, world, rank):
         import ctypes as C
         import torch.distributed._symmetric_memory as symm
         self.R, self.ctx, self.torch, self.C = R, ctx, torch, C
         self.fmt, self.w, self.rows_total, self.k, self.world, self.rank = fmt, w_local, rows_total, k, world, rank
-        self.y = symm.empty(rows_total, dtype=torch.float32, device="cuda")
+        self.y = symm.empty(2 * rows_total, dtype=torch.float32, device="cuda")
         self.pad = symm.empty(64, dtype=torch.int32, device="cuda")
         self.pad.zero_()
         torch.cuda.synchronize()
         group = dist.group.WORLD
         self._hy = symm.rendezvous(self.y, group)
         self._hp = symm.rendezvous(self.pad, group)
-        self.y_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hy.buffer_ptrs])
+        base = [int(p) for p in self._hy.buffer_ptrs]
+        self.y_ptrs = [(C.c_void_p * world)(*[b + half * 4 * rows_total for b in base]) for half in (0, 1)]
         self.pad_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hp.buffer_ptrs])
         self.epoch = 0
         dist.barrier()        # every pad is zero and mapped before the first flag is written
         torch.cuda.synchronize()
 
     def __call__(self, x):
-        """Returns this rank's full-length output vector (valid once the stream has passed the barrier kernel)."""
+        """Returns this rank's full-length output vector of this call (valid once the stream has passed the barrier
+        kernel; it stays untouched until the call after the next one)."""
         self.epoch += 1
-        # ranks may be an epoch apart: the barrier at the end of call n also keeps call n+1 of a fast rank from
-        # overwriting a vector that a slow rank is still reading, as long as the caller consumes y before the next call
-        self.R.gemv_allgather_f32(self.ctx, self.fmt, self.w, x, self.y_ptrs, self.world, self.rank, self.rows_total, self.k)
+        half = self.epoch & 1
+        self.R.gemv_allgather_f32(self.ctx, self.fmt, self.w, x, self.y_ptrs[half], self.world, self.rank, self.rows_total, self.k)
         self.R.peer_barrier(self.ctx, self.pad_ptrs, self.world, self.rank, self.epoch)
-        return self.y
+        return self.y[half * self.rows_total:(half + 1) * self.rows_total]
 
 
 class FusedEpDecodeMoe:
@@ -271,180 +285,3 @@ class FusedEpDecodeMoe:
                                 self.scratch_bytes, self.partial_ptrs, self.pad_ptrs, T, self.h, self.ff, self.E, self.k,
                                 int(self.renorm), self.world, self.rank, self.epoch)
         return self.out[:T], self.idx[:T], self.wts[:T]
-
-
-def _time_steps(torch, dist, stream, ctx, fn, steps, world):
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(steps):
-        fn()
-    e1.record(stream)
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def bench_sharded_lm_head(R, ctx, torch, dist, stream, rank, world, steps=20):
-    """Qwen2.5-7B lm_head (152064 x 3584), Q4_K and Q4_0, rows split over the ranks, logits all-gathered."""
-    out = {}
-    M, K = 152064, 3584
-    _, n = shard_rows(M, world, rank)
-    x = torch.randn(K, dtype=torch.float32, device="cuda")
-    for fmt, name in ((2, "q4k"), (1, "q4_0")):
-        be = CudaBackend(R, ctx, torch)
-        rb = R.row_bytes(fmt, K)
-        w = ctx.new_buffer(n * rb)
-        R.fill_weights(ctx, fmt, w, n * (K // R.BLOCK_ELEMS[fmt]), 1002 + rank, 0.01)
-        be.set_lm_head(fmt, w, n, K)
-        ms = _time_steps(torch, dist, stream, ctx, lambda: sharded_gemv(be, dist, torch, x, M, world, rank), steps, world)
-        ms_local = _time_steps(torch, dist, stream, ctx, lambda: be.local_gemv(x), steps, world)
-        alg = M * rb + 4 * (K + M)
-        out[name] = {"us_per_call": ms * 1e3, "us_local_gemv": ms_local * 1e3, "aggregate_gbs": alg / (ms * 1e-3) / 1e9,
-                     "rows_per_rank": n}
-        if world > 1:
-            try:
-                fused = FusedAllGatherGemv(R, ctx, torch, dist, fmt, w, M, K, world, rank)
-                ms_f = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
-                out[name].update({"us_per_call_fused_peer_stores": ms_f * 1e3, "aggregate_gbs_fused": alg / (ms_f * 1e-3) / 1e9})
-            except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
-                out[name]["fused_unavailable"] = repr(exc)[:200]
-        w.free()
-    return out
-
-
-def bench_expert_parallel(R, ctx, torch, dist, stream, rank, world, steps=10):
-    """One OLMoE-shaped MoE layer (hidden 2048, 64 experts, top-8, intermediate 1024, Q4_K), experts split 64/G per
-    rank, T tokens per rank."""
-    E, h, ff, k = 64, 2048, 1024, 8
-    n_local = E // world
-    rb = lambda kk: kk // 256 * 144
-    gate, up = ctx.new_buffer(n_local * ff * rb(h)), ctx.new_buffer(n_local * ff * rb(h))
-    down = ctx.new_buffer(n_local * h * rb(ff))
-    for i, (b, rows, kk) in enumerate(((gate, n_local * ff, h), (up, n_local * ff, h), (down, n_local * h, ff))):
-        R.fill_weights(ctx, 2, b, rows * (kk // 256), 77 + i + 10 * rank, 0.01)
-    router = torch.randn(E, h, dtype=torch.float32, device="cuda") * 0.02
-    if world > 1:
-        dist.broadcast(router, 0)
-    be = CudaBackend(R, ctx, torch)
-    be.set_experts(router, gate, up, down, E, n_local, h, ff, k, False)
-    out = {}
-    for T in (1, 16):
-        x = torch.randn(T, h, dtype=torch.float32, device="cuda")
-        ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward(be, dist, torch, x, E, k, False, world, rank), steps, world)
-        out["T%d_per_rank" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s_all_ranks": world * T / (ms * 1e-3)}
-    if world > 1:
-        try:
-            fused = FusedEpDecodeMoe(R, ctx, torch, dist, router, gate, up, down, E, h, ff, k, False, world, rank, max_tokens=16)
-            for T in (1, 16):
-                x = torch.randn(T, h, dtype=torch.float32, device="cuda")
-                dist.broadcast(x, 0)
-                ms = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
-                out["T%d_replicated_fused_peer_stores" % T] = {"us_per_layer": ms * 1e3, "tokens_per_s": T / (ms * 1e-3)}
-        except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
-            out["fused_unavailable"] = repr(exc)[:200]
-    for b in (gate, up, down):
-        b.free()
-    out["qwen3_shape_prefill"] = bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world)
-    return out
-
-
-def bench_ep_decode(R, ctx, torch, dist, rank, world):
-    """Full OLMoE-shaped greedy decode (16 layers, hidden 2048, 64 experts top-8, Q4_K, 128-token prompt + 64 steps) with
-    the experts split 64/G per rank and the MoE combine fused over peer memory; attention, router, embeddings and lm_head
-    are replicated (same seeds on every rank), every rank decodes the same token stream."""
-    import ctypes as C
-    import time
-    import numpy as np
-    import torch.distributed._symmetric_memory as symm
-    L, h, E, ff, k, V = 16, 2048, 64, 1024, 8, 50304
-    nl = E // world
-    rb = lambda kk: kk // 256 * 144
-    shapes = {"wq": (L * h, h), "wk": (L * h, h), "wv": (L * h, h), "wo": (L * h, h), "lm_head": (V, h),
-              "gate": (L * nl * ff, h), "up": (L * nl * ff, h), "down": (L * nl * h, ff)}
-    dev = {}
-    for i, (name, (rows, kk)) in enumerate(shapes.items()):
-        dev[name] = ctx.new_buffer(rows * rb(kk))
-        seed = 90001 + i + (1000 * rank if name in ("gate", "up", "down") else 0)
-        R.fill_weights(ctx, R.FMT_Q4K, dev[name], rows * (kk // 256), seed, 0.01)
-    for name, n, sig in (("tok_emb", V * h, 0.02), ("router", L * E * h, 0.02)):
-        dev[name] = ctx.new_buffer(4 * n)
-        R.fill_normal_f32(ctx, dev[name], n, 4242 + len(name), sig)
-    ones = np.ones(L * h, np.float32)
-    dev["attn_norm"], dev["ffn_norm"], dev["out_norm"] = ctx.buffer_from(ones), ctx.buffer_from(ones), ctx.buffer_from(ones[:h])
-    ctx.flush()
-    partial = symm.empty(2 * world * h, dtype=torch.float32, device="cuda")
-    pad = symm.empty(64, dtype=torch.int32, device="cuda")
-    pad.zero_()
-    torch.cuda.synchronize()
-    hq, hp = symm.rendezvous(partial, dist.group.WORLD), symm.rendezvous(pad, dist.group.WORLD)
-    pq = (C.c_void_p * world)(*[int(p) for p in hq.buffer_ptrs])
-    pp = (C.c_void_p * world)(*[int(p) for p in hp.buffer_ptrs])
-    dist.barrier()
-    torch.cuda.synchronize()
-    cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=V, n_experts=E, top_k=k, ff=ff,
-                     max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)
-    model = R.Model(ctx, cfg, dev, ep=(world, rank, pq, pp))
-    prompt = np.random.default_rng(1004).integers(0, V, 128).astype(np.int32)
-    dist.barrier()
-    model.generate_greedy(prompt, 8)
-    dist.barrier()
-    t0 = time.perf_counter()
-    toks = model.generate_greedy(prompt, 64)
-    dt_all = time.perf_counter() - t0
-    dist.barrier()
-    t0 = time.perf_counter()
-    model.generate_greedy(prompt, 0)
-    dt_prompt = time.perf_counter() - t0
-    t = torch.tensor([dt_all, dt_prompt], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    same = torch.tensor(toks[127:].astype(np.int64), device="cuda")
-    ref = same.clone()
-    dist.broadcast(ref, 0)
-    agree = torch.tensor([int(torch.equal(same, ref))], device="cuda")
-    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
-    dt_all, dt_prompt = float(t[0].item()), float(t[1].item())
-    res = {"decode_tok_s": 64 / max(dt_all - dt_prompt, 1e-9), "prompt_tok_s": 128 / dt_prompt, "tokens_total_s": 192 / dt_all,
-           "launches_per_token": int(model.launches_per_token), "experts_per_rank": nl, "ranks_agree_on_tokens": bool(agree.item()),
-           "note": "one token stream over the whole group; wall clock (max over ranks) around one call of 192 recorded steps"}
-    dist.barrier()
-    model.close()
-    for b in dev.values():
-        b.free()
-    return res
-
-
-def bench_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=5, T_total=4096):
-    """Qwen3-MoE-shaped batched block (hidden 2048, 128 experts, top-8, intermediate 768, Q4_K -> bf16 tensor-core
-    GEMMs), 4096 tokens in all (4096/G per rank), experts split 128/G per rank, Zipf(1.1) expert popularity,
-    count-exchanged all-to-all dispatch and combine.  Reports the straggler's load beside the mean."""
-    E, h, ff, k = 128, 2048, 768, 8
-    n_local, T = E // world, T_total // world
-    rb = lambda kk: kk // 256 * 144
-    gate, up = ctx.new_buffer(n_local * ff * rb(h)), ctx.new_buffer(n_local * ff * rb(h))
-    down = ctx.new_buffer(n_local * h * rb(ff))
-    for i, (b, rows, kk) in enumerate(((gate, n_local * ff, h), (up, n_local * ff, h), (down, n_local * h, ff))):
-        R.fill_weights(ctx, 2, b, rows * (kk // 256), 177 + i + 10 * rank, 0.01)
-    g = torch.Generator(device="cuda").manual_seed(1 + rank)
-    p = 1.0 / torch.arange(1, E + 1, device="cuda", dtype=torch.float64) ** 1.1
-    idx = torch.multinomial((p / p.sum()).float().expand(T, E).contiguous(), k, replacement=False, generator=g).to(torch.int32)
-    w = torch.rand(T, k, device="cuda", generator=g)
-    x = torch.randn(T, h, device="cuda", generator=g)
-
-    class GivenRouting(CudaBackend):
-        def route(self, _x):
-            return idx, w
-    be = GivenRouting(R, ctx, torch, grouped_min_slots=256)
-    be.set_experts(None, gate, up, down, E, n_local, h, ff, k, False)
-    ms = _time_steps(torch, dist, stream, ctx, lambda: ep_moe_forward_counted(be, dist, torch, x, E, k, False, world, rank), steps, world)
-    recv = torch.bincount((idx // n_local).flatten().long(), minlength=world).to(torch.float64)
-    if world > 1:
-        dist.all_reduce(recv)
-    return {"ms_per_layer": ms, "tokens_per_s_all_ranks": T_total / (ms * 1e-3), "tokens_per_rank": T,
-            "slots_per_rank_max": float(recv.max().item()), "slots_per_rank_mean": float(recv.mean().item())}

@@ -144,7 +144,12 @@ def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False):
     for i, (name, (rows, k)) in enumerate(shapes.items()):
         if device_fill:
             b = ctx.new_buffer(rows * rb(k))
-            R.fill_weights(ctx, R.FMT_Q4K, b, rows * (k // 256), seed * 7919 + i, 0.01)
+            if zero_mean:
+                # zero-mean weights of standard deviation ~ 1/sqrt(hidden): attention scores and logits of order one, a
+                # well-conditioned model whose greedy tokens depend on the input
+                R.fill_weights_q4k_zero_mean(ctx, b, rows * (k // 256), seed * 7919 + i, 2e-4)
+            else:
+                R.fill_weights(ctx, R.FMT_Q4K, b, rows * (k // 256), seed * 7919 + i, 0.01)
             ctx.flush()
             host[name] = b.download(np.uint8, rows * rb(k))
         else:
@@ -164,16 +169,21 @@ def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False):
     return model, ocfg, ow, host
 
 
-def run_parity(model, O, ocfg, ow, prompt, n_gen, tie_frac=1e-4):
-    """Step-by-step greedy decode on both sides with the tie rule of this file's docstring."""
+def run_parity(model, O, ocfg, ow, prompt, n_gen, tie_frac=1e-4, start_pos=0, logits_at=()):
+    """Step-by-step greedy decode on both sides with the tie rule of this file's docstring.  The first step runs at
+    position start_pos (earlier cache rows are zero on both sides).  At the steps listed in logits_at the full logit
+    vector is compared as well (1e-3 of the logit scale)."""
     L, kvh, S, hd = ocfg.n_layers, ocfg.n_kv_heads, ocfg.max_seq, ocfg.head_dim
     kc = np.zeros((L, kvh, S, hd), np.float16)
     vc = np.zeros((L, kvh, S, hd), np.float16)
     tok = int(prompt[0])
     ties, produced = 0, []
-    for pos in range(len(prompt) + n_gen - 1):
+    for step in range(len(prompt) + n_gen - 1):
+        pos = start_pos + step
         ref_tok, logits = O.decode_step(ocfg, ow, kc, vc, tok, pos, want_logits=True)
         got_tok = model.forward_greedy(tok, pos)
+        if step in logits_at:
+            assert_close(O, logits, model.logits(), rel_tol=1e-3, what="logits at step %d (position %d)" % (step, pos))
         if got_tok != ref_tok:
             top2 = np.sort(logits)[-2:]
             margin, scale = float(top2[1] - top2[0]), float(np.std(logits))
@@ -182,7 +192,7 @@ def run_parity(model, O, ocfg, ow, prompt, n_gen, tie_frac=1e-4):
             assert got_tok == runner_up, (pos, got_tok, runner_up)
             ties += 1
         produced.append(ref_tok)
-        tok = int(prompt[pos + 1]) if pos + 1 < len(prompt) else ref_tok   # teacher forcing inside the prompt, oracle token after
+        tok = int(prompt[step + 1]) if step + 1 < len(prompt) else ref_tok   # teacher forcing inside the prompt, oracle token after
     return produced, ties
 
 
@@ -236,4 +246,47 @@ def test_olmoe_shaped_decode_128_plus_64(ctx, oracle):
     if ties == 0:
         out = model.generate_greedy(prompt, 64)
         assert list(out[127:191]) == produced[127:191]
+    model.close()
+
+
+OLMOE = dict(n_layers=16, hidden=2048, n_heads=16, n_kv_heads=16, head_dim=128, vocab=50304, n_experts=64, top_k=8, ff=1024,
+             max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)
+
+
+def test_olmoe_shaped_decode_varied_tokens_and_logits(ctx, oracle):
+    """The same 16-layer OLMoE-shaped decode with zero-mean weights (every matrix has standard deviation about
+    1/sqrt(hidden), so attention scores and logits are of order one): the greedy stream depends on its input and
+    visits many distinct tokens, which makes token identity a real check; the full logit vector is compared with
+    the oracle at five steps as well (1e-3 of the logit scale)."""
+    import runit_mac_b200 as R
+    O = oracle
+    model, ocfg, ow, host = build_model(ctx, R, O, OLMOE, 2004, device_fill=True, zero_mean=True)
+    prompt = np.random.default_rng(2004).integers(0, 50304, 128).astype(np.int32)
+    produced, ties = run_parity(model, O, ocfg, ow, prompt, 64, logits_at=(0, 1, 64, 127, 190))
+    gen = produced[127:191]
+    assert len(produced) == 191 and ties <= 4, ties
+    assert len(set(gen)) > 8, ("the generated stream is degenerate", sorted(set(gen)))
+    if ties == 0:
+        out = model.generate_greedy(prompt, 64)
+        assert list(out[127:191]) == gen
+    model.close()
+
+
+def test_olmoe_shaped_decode_reaches_context_2048(ctx, oracle):
+    """The f16 KV path at the end of the 2048-position context: 8 prompt tokens and 60 greedy steps starting at
+    position 1980, so the last step attends over all 2048 cache rows (rows before the start are zero on both sides).
+    Tokens step by step, logits at the first and the last step, and the recorded-command-list path from the same
+    start position."""
+    import runit_mac_b200 as R
+    O = oracle
+    model, ocfg, ow, host = build_model(ctx, R, O, OLMOE, 2005, device_fill=True, zero_mean=True)
+    prompt = np.random.default_rng(2005).integers(0, 50304, 8).astype(np.int32)
+    n_gen = 2048 - 1980 - len(prompt) + 1          # the last step runs at position 2047
+    produced, ties = run_parity(model, O, ocfg, ow, prompt, n_gen, start_pos=1980, logits_at=(0, len(prompt) + n_gen - 2))
+    assert len(produced) == 68 and ties <= 2, ties
+    if ties == 0:
+        out = model.generate_greedy(prompt, n_gen - 1, start_pos=1980, skip_prompt_logits=False)
+        assert list(out[:len(prompt) + n_gen - 1]) == produced[:len(prompt) + n_gen - 1]
+    with pytest.raises(R.KernelError):             # one step more would pass the end of the cache (kv_cache.rs:63)
+        model.generate_greedy(prompt, n_gen + 1, start_pos=1980)
     model.close()

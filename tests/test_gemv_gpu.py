@@ -442,3 +442,48 @@ def test_full_size_lm_head_sampled_rows(ctx, oracle):
         # the three products round their activations to 16-bit block fixed point independently
         assert_close(O, lin, ys[2], rel_tol=5e-4, what="linearity")
         wb.free()
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 2])
+def test_non_finite_activations_are_not_masked(ctx, oracle, fmt):
+    """A NaN or an Inf in the activations must reach the output, as it does through the reference's f32 multiply-add
+    chain (gemv_q8_0.metal:24-36, gemv_q4_0.metal:26-49, gemv_q4k.metal:85-122): every row whose dot product includes
+    the bad element ends non-finite.  The integer paths quantise activations per 32-block, so their rule is: a block
+    that holds a non-finite value makes every row NaN.  Host-made inputs only; batch 1 (integer tensor-core / dp4a
+    paths) and batch 8 (batched integer tensor-core path, only the bad activation row is affected)."""
+    import runit_mac_b200 as R
+    O = oracle
+    m, k = {0: (96, 896), 1: (96, 3584), 2: (96, 2048)}[fmt]
+    rng = np.random.default_rng(77 + fmt)
+    w = O.rand_weights(fmt, rng, m, k)
+    wb = ctx.buffer_from(w)
+    name = "gemv_%s_f32in_f32out" % FMT_NAME[fmt]
+    for bad, pos in ((np.nan, 5), (np.inf, k - 3), (-np.inf, k // 2)):
+        x = rng.normal(0, 1, k).astype(np.float32)
+        x[pos] = bad
+        yb = ctx.new_buffer(m * 4)
+        getattr(R, name)(ctx, wb, ctx.buffer_from(x), yb, m, k)
+        ctx.flush()
+        got = yb.download(np.float32, m)
+        assert not np.isfinite(got).any(), (FMT_NAME[fmt], bad, int(np.isfinite(got).sum()))
+        # the other arithmetic paths of the batch-1 kernel agree
+        for math in (1, 2):
+            ctx.set_tuning("gemv_math", math)
+            try:
+                getattr(R, name)(ctx, wb, ctx.buffer_from(x), yb, m, k)
+                ctx.flush()
+            finally:
+                ctx.set_tuning("gemv_math", 0)
+            assert not np.isfinite(yb.download(np.float32, m)).any(), (FMT_NAME[fmt], bad, math)
+        xs = rng.normal(0, 1, (8, k)).astype(np.float32)
+        xs[3, pos] = bad
+        y8 = ctx.new_buffer(8 * m * 4)
+        R.gemv_batched_f32(ctx, fmt, wb, ctx.buffer_from(xs), y8, None, m, k, 8)
+        ctx.flush()
+        got8 = y8.download(np.float32, 8 * m).reshape(8, m)
+        assert not np.isfinite(got8[3]).any() and np.isfinite(np.delete(got8, 3, 0)).all()
+        ref = O.gemv(fmt, w, np.delete(xs, 3, 0), m, k, O.TIER_F64)
+        assert_close(O, ref, np.delete(got8, 3, 0), what="finite rows beside a non-finite one")
+    # a finite input still gives a finite, correct result afterwards
+    x = rng.normal(0, 1, k).astype(np.float32)
+    assert_close(O, O.gemv(fmt, w, x, m, k, O.TIER_F64), run_gemv(ctx, R, name, w, x, m, k), what="after non-finite")

@@ -196,3 +196,77 @@ def test_expert_parallel_entry_with_one_rank(ctx, oracle):
     with pytest.raises(R.KernelError):
         R.moe_layer_q4k_ep(ctx, *bufs, out, idx, w, scratch, nbytes, pt, pp, T, h, ff, E, k, 0, 3, 0, 3)   # 8 experts / 3 ranks
     ctx.flush()
+
+
+def rand_q4k_small_zero_mean(O, rng, rows, k, sigma):
+    """Q4_K rows with zero-mean weights of a scale that keeps every f16 intermediate of the reference's block far from
+    overflow (d*sc*(q - 7.5): dmin = 7.5 d, min index = scale index)."""
+    nb = k // 256
+    d = np.abs(rng.normal(0.0, sigma, (rows, nb)))
+    sc = rng.integers(0, 64, (rows, nb, 8), dtype=np.uint8)
+    nib = rng.integers(0, 16, (rows, nb, 256), dtype=np.uint8)
+    return O.pack_q4k(d, 7.5 * d, sc, sc, nib)
+
+
+def test_reference_op_sequence_with_f16_twins(ctx, oracle):
+    """The literal drop-in use: the reference's own MoE op sequence (crates/engine/src/forward.rs:1644-1679) issued
+    call by call through the twins, with the reference's dtypes — f16 router weights and f16 logits
+    (gemv_f16w_f32in), renormalised top-k, gate/up through the f16 twin of the Q4_K weights with f32 input and f16
+    output (WeightBuf::gemv_f32in for Q4K, forward.rs:164-180: dequant_q4k_f16 at load, then gemv_f16w_f32in),
+    silu_mul_f16, down from the packed weights with f16 in/out (gemv_q4k_f16), the f16 accumulator
+    (scale_accumulate_f16 in routing order) and add_f16_into_f32 — against the oracle's REF_F16 mode, which places
+    the same f16 roundings.  Tolerance: the reference's own for f16 kernels, abs 1e-2 (dispatch.rs:1782)."""
+    import runit_mac_b200 as R
+    O = oracle
+    rng = np.random.default_rng(1644)
+    E, h, ff, k, T = 64, 2048, 1024, 8, 3
+    rb_h, rb_ff = O.row_bytes(O.Q4K, h), O.row_bytes(O.Q4K, ff)
+    router16 = rng.normal(0, 0.02, (E, h)).astype(np.float16)
+    gate = rand_q4k_small_zero_mean(O, rng, E * ff, h, 2e-4)
+    up = rand_q4k_small_zero_mean(O, rng, E * ff, h, 2e-4)
+    down = rand_q4k_small_zero_mean(O, rng, E * h, ff, 2e-4)
+    x = rng.normal(0, 1, (T, h)).astype(np.float32)
+    res = rng.normal(0, 1, (T, h)).astype(np.float32)
+    ref, ridx, rw = O.moe_layer_q4k(router16.astype(np.float32), gate, up, down, x, h=h, ff=ff, E=E, top_k=k, renorm=True,
+                                    mode=O.MOE_REF_F16, residual=res)
+    assert np.isfinite(ref).all() and np.abs(ref - res).max() > 0.1      # the block contributes, nothing overflowed f16
+
+    # load time: packed weights as stored + the f16 twins of gate and up (forward.rs:1137-1222 keeps both)
+    gate_b, up_b, down_b = ctx.buffer_from(gate), ctx.buffer_from(up), ctx.buffer_from(down)
+    gate16, up16 = ctx.new_buffer(E * ff * h * 2), ctx.new_buffer(E * ff * h * 2)
+    R.dequant_q4k_f16(ctx, gate_b, gate16, E * ff * (h // 256))
+    R.dequant_q4k_f16(ctx, up_b, up16, E * ff * (h // 256))
+    router_b = ctx.buffer_from(router16)
+    logits = ctx.new_buffer(E * 2)
+    idx_b, w_b = ctx.new_buffer(k * 4), ctx.new_buffer(k * 4)
+    g16, u16, act16, ffn16, moe16 = (ctx.new_buffer(n * 2) for n in (ff, ff, ff, h, h))
+    ties = 0
+    for t in range(T):
+        xb = ctx.buffer_from(x[t])
+        xres = ctx.buffer_from(res[t])                     # s.x: the f32 hidden state the block adds into
+        R.gemv_f16w_f32in(ctx, router_b, xb, logits, E, h)
+        R.moe_route_topk(ctx, logits, 1, E, k, 1, 1, idx_b, w_b)
+        ctx.flush()                                        # the reference reads the logits on the host here (forward.rs:1654)
+        eids, ew = idx_b.download(np.int32, k), w_b.download(np.float32, k)
+        if (eids != ridx[t]).any():
+            # f16 logits one rounding apart can swap two experts: only a near-tie of the oracle's own logits excuses it
+            lg = O.gemv_f32w(router16.astype(np.float32), x[t], E, h).astype(np.float16).astype(np.float32)
+            srt = np.sort(lg)[::-1]
+            assert (srt[:k] - srt[1:k + 1]).min() <= 2 * np.spacing(np.float16(abs(srt[0]))), (t, eids, ridx[t])
+            ties += 1
+            continue
+        assert np.allclose(ew, rw[t], rtol=1e-4)
+        ctx.call("memset", moe16, 0, h * 2)
+        for i in range(k):
+            e = int(eids[i])
+            R.gemv_f16w_f32in(ctx, gate16.ptr + e * ff * h * 2, xb, g16, ff, h)
+            R.gemv_f16w_f32in(ctx, up16.ptr + e * ff * h * 2, xb, u16, ff, h)
+            R.silu_mul_f16(ctx, g16, u16, act16, ff)
+            R.gemv_q4k_f16(ctx, down_b.ptr + e * h * rb_ff, act16, ffn16, h, ff)
+            R.scale_accumulate_f16(ctx, ffn16, moe16, float(ew[i]), h)
+        R.add_f16_into_f32(ctx, moe16, xres, h)
+        ctx.flush()
+        got = xres.download(np.float32, h)
+        assert np.isfinite(got).all()
+        assert np.abs(got - ref[t]).max() <= 1e-2, (t, float(np.abs(got - ref[t]).max()))
+    assert ties <= 1

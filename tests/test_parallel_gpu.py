@@ -28,7 +28,7 @@ def run_rank(rank, world, port, q):
     from runit_mac_b200 import parallel as P
     torch.cuda.set_device(rank)
     if world > 1:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
@@ -54,15 +54,19 @@ def run_rank(rank, world, port, q):
     assert torch.equal(idx_c, idx) and torch.allclose(out_c, out, rtol=1e-6, atol=1e-6 * float(out.abs().max()))
     y_fused = None
     if world > 1:
-        # the same sharded product with the all-gather fused into the GEMV epilogue (peer stores + barrier kernel),
-        # three calls in a row: the result must be the NCCL one bit for bit every time
+        # the same sharded product with the all-gather fused into the GEMV epilogue (peer stores + barrier kernel): four
+        # calls in a row with a different input each and no host synchronisation between them (the two output vectors
+        # alternate, so a rank that runs ahead cannot overwrite what a slower rank still reads); every call must give the
+        # NCCL result bit for bit
         fused = P.FusedAllGatherGemv(R, ctx, torch, dist, 2, be.w_local, M_ROWS, K_IN, world, rank)
-        for _ in range(3):
-            yf = fused(torch.from_numpy(d["x_lm"]).cuda())
-            ctx.flush()
-            assert torch.equal(yf, y), "fused all-gather differs from the NCCL all-gather"
-            dist.barrier()     # nobody starts the next call while a slow rank still compares this one
-        y_fused = yf.cpu().numpy()
+        xs_lm = [torch.from_numpy(d["x_lm"] * (1.0 + 0.5 * i)).cuda() for i in range(4)]
+        want = [P.sharded_gemv(be, dist, torch, xi, M_ROWS, world, rank).clone() for xi in xs_lm]
+        got = [fused(xi).clone() for xi in xs_lm]     # the clone is stream-ordered before the next call's barrier
+        ctx.flush()
+        for yf, yw in zip(got, want):
+            assert torch.equal(yf, yw), "fused all-gather differs from the NCCL all-gather"
+        assert torch.equal(want[0], y)
+        y_fused = got[0].cpu().numpy()
     out_ep = None
     if world > 1:
         # decode-size block with replicated tokens and the combine fused over peer memory: three calls in a row give the
@@ -148,10 +152,18 @@ def test_sharded_paths_match_oracle(oracle):
         procs = [ctxm.Process(target=run_rank, args=(r, world, port, q)) for r in range(world)]
         for p in procs:
             p.start()
-        res = sorted([q.get(timeout=300) for _ in range(world)], key=lambda t: t[0])
-        for p in procs:
-            p.join(timeout=60)
-            assert p.exitcode == 0
+        try:
+            res = sorted([q.get(timeout=300) for _ in range(world)], key=lambda t: t[0])
+            for p in procs:
+                p.join(timeout=60)
+                assert p.exitcode == 0
+        finally:
+            # whatever failed (an assert in one child, a time-out here), no child is left behind inside a collective
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+            for p in procs:
+                p.join(timeout=30)
     d = make_data(O)
     full = O.gemv(O.Q4K, d["lm"], d["x_lm"], M_ROWS, K_IN)
     for r in res:
@@ -185,12 +197,28 @@ def test_peer_barrier_times_out_without_a_peer(ctx):
     for p in pads:
         p.upload(np.zeros(64, np.uint32))
     table = (C.c_void_p * 2)(pads[0].ptr, pads[1].ptr)
+    import time
+    t0 = time.perf_counter()
     R.peer_barrier(ctx, table, 2, 0, 1)
     with pytest.raises(R.KernelError) as e:
         ctx.flush()
+    one_limit = time.perf_counter() - t0
     assert "TIMEOUT" in str(e.value)
     assert pads[1].download(np.uint32, 2)[0] == 1          # our own announcement did reach the peer's pad
-    # world size 1 completes at once, and the context is still usable
+    # the give-up is sticky on the device: a queue of barriers behind the missing rank costs about ONE time limit,
+    # not one each (a recorded decode step holds one barrier per layer), and each still announces its epoch
+    t0 = time.perf_counter()
+    for epoch in range(2, 10):
+        R.peer_barrier(ctx, table, 2, 0, epoch)
+    with pytest.raises(R.KernelError):
+        ctx.flush()
+    eight = time.perf_counter() - t0
+    assert eight < 2.5 * one_limit + 0.2, (one_limit, eight)
+    assert pads[1].download(np.uint32, 2)[0] == 9
+    # the report cleared the flag: the next barrier waits again (and gives up again); world size 1 completes at once
+    R.peer_barrier(ctx, table, 2, 0, 10)
+    with pytest.raises(R.KernelError):
+        ctx.flush()
     one = (C.c_void_p * 1)(pads[0].ptr)
-    R.peer_barrier(ctx, one, 1, 0, 2)
+    R.peer_barrier(ctx, one, 1, 0, 11)
     ctx.flush()
