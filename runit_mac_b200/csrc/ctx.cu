@@ -3,6 +3,7 @@
 // Replaces MetalContext::{new, new_buffer, encode, flush} of the reference
 // (crates/kernels/src/context.rs:163-296): one in-order CUDA stream instead of a Metal
 // command buffer; runit_flush == commit + wait_until_completed.
+#include "gemv_stream_host.h"
 #include "runit_internal.h"
 
 #include <cstdarg>
@@ -152,6 +153,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->d_xq) cudaFree(ctx->d_xq);
     if (ctx->d_abort) cudaFree(ctx->d_abort);
+    if (ctx->stream_rec) delete static_cast<std::vector<runit::StreamRec>*>(ctx->stream_rec);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RUNIT_OK;
@@ -191,16 +193,28 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "gemv_csplit")) ctx->tune.gemv_csplit = value;
     else if (!strcmp(key, "gemv_math")) ctx->tune.gemv_math = value;
     else if (!strcmp(key, "gemv_no_cluster")) ctx->tune.gemv_no_cluster = value;
+    else if (!strcmp(key, "stream_fuse")) ctx->tune.stream_fuse = value;
+    else if (!strcmp(key, "stream_cfg")) ctx->tune.stream_cfg = value;
+    else if (!strcmp(key, "stream_waves")) ctx->tune.stream_waves = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
     return RUNIT_OK;
 }
 
-// CUDA graphs stand in for the reference's encoded command buffer: record once, replay per token.
+// CUDA graphs stand in for the reference's encoded command buffer: record once, replay per token.  Runs of consecutive
+// batch-1 GEMVs of a recording are folded into one persistent launch (gemv_stream.cu) before the graph is instantiated.
+struct runit_graph {
+    cudaGraphExec_t exec = nullptr;
+    std::vector<void*> allocs;      // device memory of the fused GEMV programs
+    uint32_t fused_launches = 0;
+    uint32_t kernel_nodes = 0;      // kernel launches one replay performs
+};
+
 int32_t runit_graph_begin(runit_ctx_t* ctx) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, !ctx->capturing, "runit_graph_begin: a recording is already open");
     RUNIT_CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
+    runit::stream_rec_begin(ctx);
     return RUNIT_OK;
 }
 
@@ -213,28 +227,60 @@ int32_t runit_graph_end(runit_ctx_t* ctx, runit_graph_t** out) {
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
     if (e != cudaSuccess || !g) {
         cudaGetLastError();
+        runit::stream_rec_discard(ctx);
         return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
     }
-    cudaGraphExec_t ex = nullptr;
-    e = cudaGraphInstantiate(&ex, g, 0);
+    runit_graph* gr = new (std::nothrow) runit_graph();
+    if (!gr) {
+        cudaGraphDestroy(g);
+        runit::stream_rec_discard(ctx);
+        return RUNIT_ERR_ALLOC;
+    }
+    int32_t st = runit::stream_rec_fuse(ctx, g, &gr->allocs, &gr->fused_launches);
+    runit::stream_rec_discard(ctx);
+    if (st == RUNIT_OK) {
+        size_t n_nodes = 0;
+        if (cudaGraphGetNodes(g, nullptr, &n_nodes) == cudaSuccess && n_nodes > 0) {
+            std::vector<cudaGraphNode_t> nodes(n_nodes);
+            if (cudaGraphGetNodes(g, nodes.data(), &n_nodes) == cudaSuccess)
+                for (size_t i = 0; i < n_nodes; i++) {
+                    cudaGraphNodeType ty;
+                    if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) gr->kernel_nodes++;
+                }
+        }
+        cudaGetLastError();
+        e = cudaGraphInstantiate(&gr->exec, g, 0);
+        if (e != cudaSuccess) st = runit_fail(ctx, RUNIT_ERR_LAUNCH, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
     cudaGraphDestroy(g);
-    if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
-    *out = reinterpret_cast<runit_graph_t*>(ex);
+    if (st != RUNIT_OK) {
+        for (void* p : gr->allocs) cudaFree(p);
+        delete gr;
+        return st;
+    }
+    *out = gr;
     return RUNIT_OK;
 }
 
 int32_t runit_graph_launch(runit_ctx_t* ctx, runit_graph_t* graph) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
-    RUNIT_REQUIRE(ctx, graph, "runit_graph_launch: null graph");
-    RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph), ctx->stream));
+    RUNIT_REQUIRE(ctx, graph && graph->exec, "runit_graph_launch: null graph");
+    RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
     return RUNIT_OK;
 }
 
 int32_t runit_graph_destroy(runit_ctx_t* ctx, runit_graph_t* graph) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
-    if (graph) RUNIT_CUDA_TRY(ctx, cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(graph)));
+    if (!graph) return RUNIT_OK;
+    cudaStreamSynchronize(ctx->stream);   // a replay may still be running on the program memory
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    for (void* p : graph->allocs) cudaFree(p);
+    delete graph;
     return RUNIT_OK;
 }
+
+uint32_t runit_graph_fused_launches(runit_graph_t* graph) { return graph ? graph->fused_launches : 0; }
+uint32_t runit_graph_kernel_launches(runit_graph_t* graph) { return graph ? graph->kernel_nodes : 0; }
 
 int32_t runit_buf_alloc(runit_ctx_t* ctx, size_t bytes, int32_t flags, void** dptr) {
     if (!ctx || !dptr) return RUNIT_ERR_BAD_ARG;

@@ -7,6 +7,7 @@
 // expert intermediates and combine, top-k weights not renormalised unless cfg.renorm, f16 KV cache
 // fed from f32 K/V, f32 logits with a lowest-index argmax.
 #include "decode_ops.cuh"
+#include "gemv_stream_host.h"
 #include "runit_internal.h"
 #include "tma.cuh"
 
@@ -167,16 +168,29 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
 static int32_t record_graph(runit_model* m, bool with_logits, cudaGraphExec_t* out) {
     runit_ctx* ctx = m->ctx;
     RUNIT_CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    stream_rec_begin(ctx);
     int32_t st = issue_step(m, with_logits, m->forced_cap);
+    ctx->capturing = false;
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
     if (st != RUNIT_OK) {
+        stream_rec_discard(ctx);
         if (g) cudaGraphDestroy(g);
         return st;
     }
     if (e != cudaSuccess || !g) {
         cudaGetLastError();
+        stream_rec_discard(ctx);
         return runit_fail(ctx, RUNIT_ERR_LAUNCH, "model: stream capture failed: %s", cudaGetErrorString(e));
+    }
+    // adjacent GEMVs of the step (none today: every GEMV of this model is followed by another kind of operator) would share
+    // one persistent launch, as in any recorded command list
+    st = stream_rec_fuse(ctx, g, &m->owned, nullptr);
+    stream_rec_discard(ctx);
+    if (st != RUNIT_OK) {
+        cudaGraphDestroy(g);
+        return st;
     }
     e = cudaGraphInstantiate(out, g, 0);
     cudaGraphDestroy(g);

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "gemv_kernels.cuh"
+#include "gemv_stream_host.h"
 #include "runit_internal.h"
 
 namespace runit {
@@ -58,6 +59,35 @@ static inline int32_t launch_staged(runit_ctx* ctx, const GemvArgs& a, const Gem
     cfg.numAttrs = na;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args, maps);
     if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "launch of %s failed: %s", name, cudaGetErrorString(e));
+    // While a command list is recorded, launches of this kind are noted: when the recording ends, runs of consecutive
+    // ones are folded into one persistent launch (gemv_stream.cu).
+    if constexpr (FMT != RUNIT_FMT_Q8_0 && B == 1 && !XF16 && LD == 1 && MATH == 2) {
+        if (ctx->capturing && ctx->tune.stream_fuse && a.grp_expert == nullptr && a.n_peer == 0 && a.res_kind != RES_F16) {
+            StreamRec r;
+            memset(&r, 0, sizeof(r));
+            r.func = reinterpret_cast<const void*>(kern);
+            r.w0 = a.seg[0].w;
+            r.x = a.x;
+            r.fmt = FMT;
+            r.dual = DUAL ? 1 : 0;
+            r.nseg = a.nseg;
+            for (int i = 0; i < a.nseg && i < 3; i++) {
+                r.map[i] = maps.m[i];
+                r.y[i] = a.seg[i].y;
+                r.res[i] = a.seg[i].res;
+                r.bias[i] = a.seg[i].bias;
+                r.rows[i] = a.seg[i].rows;
+            }
+            if (DUAL) r.map[3] = maps.m[3];
+            r.k = a.k;
+            r.nb = a.nb;
+            r.n_units = a.n_units;
+            r.out_f16 = a.out_f16;
+            r.res_kind = a.res_kind;
+            r.bias_kind = a.bias_kind;
+            stream_rec_push(ctx, r);
+        }
+    }
     return runit_after_launch(ctx, name);
 }
 

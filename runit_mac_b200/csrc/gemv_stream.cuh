@@ -1,0 +1,345 @@
+// One persistent launch for a run of consecutive fused-dequant GEMVs (batch 1, 4-bit formats).
+//
+// A decode token is a chain of dependent GEMVs (crates/engine/src/forward.rs:1523-1765: fused Q|K|V, o-proj + residual,
+// fused gate/up + SiLU, down + residual per layer, then lm_head).  As separate launches each of them pays the drain of
+// its predecessor, the dependency release and the refill of its own load pipeline (about 3.4 us against 5.9 us of HBM
+// time for a 38 MB matrix).  Here the whole run is ONE kernel:
+//   * the grid is one CTA per SM, NW warps each; the unit of work is a warp-item = one 32-row tile x one K-slice of one
+//     GEMV (the tile/unit/MMA arithmetic is that of gemv_staged_kernel, integer tensor-core path);
+//   * the items of all GEMVs form one list in launch order, and warp w of W takes items w, w + W, ...: static,
+//     deterministic, and free of deadlock because an item only ever waits for items with lower indices;
+//   * every warp keeps its own ring of S weight stages (TMA boxes of 32 rows x 144 bytes) and its load cursor runs S
+//     stages ahead of its compute cursor ACROSS item and GEMV boundaries: weights do not depend on anything, so the
+//     stream from HBM never stops at a boundary;
+//   * activations are read with plain L2 loads (8 floats per lane and stage, one stage ahead, held in registers) once
+//     the GEMVs that produce them have completed: every GEMV has a completion counter (tiles done), and a warp that
+//     reaches the first item of a GEMV waits, with a time bound, until the counters of the GEMVs it depends on are full;
+//   * K-slices of a tile meet through a scratch array in global memory: each slice stores its 32 partial sums and takes
+//     a ticket; the slice that draws the last ticket adds the partials in slice order (bit-reproducible) and runs the
+//     epilogue (bias, residual, SiLU(gate)*up, f16 output), then counts the tile as done.
+// The host side (gemv_stream.cu) builds the item list, the dependency lists (read/write overlap of the recorded calls)
+// and rewrites a recorded command list so that each run of such GEMVs becomes one launch of this kernel.
+#pragma once
+
+#include "gemv_kernels.cuh"
+
+namespace runit {
+namespace gs {
+
+constexpr uint32_t kMaxOps = 128;         // GEMVs per launch (a 28-layer token has 113)
+constexpr uint32_t kMaxDeps = 4;
+constexpr uint32_t kNoDep = 0xFFFFu;
+constexpr uint32_t kNoSeg = 0xFFFFFFFFu;
+constexpr int kStageBytes = kRT * 144;    // one warp stage: 32 rows x one 256-weight unit
+constexpr int kXqBytes = 640;             // prepared activations of one unit (MmaX<8>::BYTES = 576), padded to 128
+
+// What a warp needs to walk the item list; copied to shared memory at kernel start.
+struct alignas(16) OpLite {
+    uint32_t item_begin, n_items;     // this GEMV's range in the global item list
+    uint32_t n_slices, n_units, n_tiles;
+    uint32_t tile_begin1, tile_begin2;   // first tile of segments 1 and 2 (Q|K|V launches), kNoSeg if absent
+    uint32_t dual;                    // fused gate/up: a tile is 16 gate rows + 16 up rows
+    uint32_t k, nb;
+    const float* x;
+    uint16_t dep[kMaxDeps];           // GEMVs (indices in this launch) that must be complete first; kNoDep = none
+    uint32_t partial_off;             // floats: [tile][slice][32] partial sums of this GEMV
+    uint32_t ticket_off;              // words: one arrival counter per tile
+};
+static_assert(sizeof(OpLite) == 64, "OpLite is copied as 16-byte words");
+
+// Tensor maps and epilogue pointers; stays in global memory.
+struct alignas(64) OpFull {
+    CUtensorMap map[4];               // per segment; [3] = the up matrix of a fused gate/up launch
+    void* y[3];
+    const void* res[3];
+    const void* bias[3];
+    uint32_t rows[3];
+    int32_t out_f16, res_kind, bias_kind;
+};
+
+struct Params {
+    const OpFull* full;
+    const OpLite* lite;
+    uint32_t n_ops, total_items;
+    float* partial;
+    uint32_t* tickets;
+    uint32_t n_tickets;
+    uint32_t* done;      // [n_ops] tiles completed; zero at rest
+    uint32_t* ctl;       // [0] exit ticket, [1] abort flag; zero at rest
+    int32_t* status;     // host-visible status word of the context
+};
+
+struct Cursor {
+    uint32_t g;          // global item index; >= total_items: past the end
+    uint32_t op, tile, slice, nsl;
+    uint32_t it, n_it;   // stage inside the item
+    uint32_t stage;      // running stage number of this warp: ring slot = stage % S, barrier phase = (stage / S) & 1
+};
+
+__device__ __forceinline__ void locate(Cursor& c, const OpLite* lite, uint32_t total) {
+    c.it = 0;
+    if (c.g >= total) { c.n_it = 0; return; }
+    while (c.g >= lite[c.op].item_begin + lite[c.op].n_items) c.op++;
+    const uint32_t local = c.g - lite[c.op].item_begin, nsl = lite[c.op].n_slices;
+    c.tile = local / nsl;
+    c.slice = local - c.tile * nsl;
+    c.nsl = nsl;
+    c.n_it = (lite[c.op].n_units - c.slice + nsl - 1) / nsl;
+}
+__device__ __forceinline__ void advance(Cursor& c, const OpLite* lite, uint32_t total, uint32_t W) {
+    c.stage++;
+    if (++c.it >= c.n_it) {
+        c.g += W;
+        locate(c, lite, total);
+    }
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+template <int FMT, int NW, int S>
+__global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p) {
+    static_assert(FMT == RUNIT_FMT_Q4K || FMT == RUNIT_FMT_Q4_0, "4-bit formats");
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ OpLite lite[kMaxOps];
+    __shared__ __align__(8) uint64_t mbar[NW][S];
+    __shared__ uint32_t s_last;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p.lite);
+        uint4* dst = reinterpret_cast<uint4*>(lite);
+        for (uint32_t i = threadIdx.x; i < p.n_ops * (uint32_t)(sizeof(OpLite) / 16); i += NW * 32) dst[i] = src[i];
+    }
+    const uint32_t bar0 = smem_u32(&mbar[warp][0]);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < S; s++) mbar_init(bar0 + 8 * s, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    uint8_t* ring = smem + warp * (S * kStageBytes + kXqBytes);
+    uint8_t* xq = ring + S * kStageBytes;
+    const uint32_t ring_u32 = smem_u32(ring);
+    const uint32_t total = p.total_items, W = gridDim.x * NW;
+
+    // Weight boxes of the stage the cursor points at (lane 0 issues; everything it needs is in shared memory).
+    uint32_t issued_end = 0;    // stages [0, issued_end) of this warp carry a bulk-load transaction
+    auto issue_w = [&](const Cursor& c) {
+        if (c.g >= total) return;
+        issued_end = c.stage + 1;
+        if (lane != 0) return;
+        const OpLite& o = lite[c.op];
+        uint32_t si = 0, tb = 0;
+        if (c.tile >= o.tile_begin2) { si = 2; tb = o.tile_begin2; }
+        else if (c.tile >= o.tile_begin1) { si = 1; tb = o.tile_begin1; }
+        const uint32_t u = c.slice + c.nsl * c.it;
+        const uint32_t slot = ring_u32 + (c.stage % S) * kStageBytes, bar = bar0 + 8 * (c.stage % S);
+        const OpFull* f = p.full + c.op;
+        fence_proxy_async();   // the warp's generic-proxy reads of this slot precede the bulk writes
+        mbar_expect_tx(bar, kStageBytes);
+        if (o.dual) {
+            const int32_t row0 = (int32_t)((c.tile - tb) * (kRT / 2));
+            tma_load_2d(slot, &f->map[0], (int32_t)(u * 144), row0, bar);
+            tma_load_2d(slot + (kRT / 2) * 144, &f->map[3], (int32_t)(u * 144), row0, bar);
+        } else {
+            tma_load_2d(slot, &f->map[si], (int32_t)(u * 144), (int32_t)((c.tile - tb) * kRT), bar);
+        }
+    };
+    // This lane's 8 activations of the stage (L2 loads: the vector may have been written by another SM a moment ago).
+    auto load_x = [&](const Cursor& c, float (&v)[8]) {
+        const OpLite& o = lite[c.op];
+        const uint32_t e0 = (c.slice + c.nsl * c.it) * 256 + lane * 8;
+        if (e0 < o.k) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(o.x + e0));
+            const float4 b = __ldcg(reinterpret_cast<const float4*>(o.x + e0) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = 0.f;
+        }
+    };
+
+    bool dead = false;          // a bounded wait ran out (here or in another warp): stop, drain, leave
+    uint32_t dep_ok = 0;        // GEMVs [0, dep_ok) have had their dependencies checked by this warp
+    // Wait until every GEMV that `op` depends on is complete.  Returns false on time-out / abort.
+    auto ensure_deps = [&](uint32_t op) -> bool {
+        if (op < dep_ok) return true;
+        bool ok = true;
+        if (lane == 0) {
+            const OpLite& o = lite[op];
+#pragma unroll
+            for (int d = 0; d < (int)kMaxDeps; d++) {
+                const uint32_t dop = o.dep[d];
+                if (dop == kNoDep || !ok) continue;
+                const uint32_t want = lite[dop].n_tiles;
+                const uint32_t* ctr = p.done + dop;
+                if (ld_acquire_gpu(ctr) >= want) continue;
+                const long long t0 = clock64();
+                uint32_t spins = 0;
+                while (true) {
+                    __nanosleep(64);
+                    if (ld_acquire_gpu(ctr) >= want) break;
+                    if ((++spins & 63u) == 0u) {
+                        if (*reinterpret_cast<volatile uint32_t*>(p.ctl + 1) != 0u) { ok = false; break; }
+                        if (clock64() - t0 > (1ll << 30)) {   // about half a second: the producer never finished
+                            atomicExch(p.ctl + 1, 1u);
+                            if (p.status) atomicExch(p.status, 4);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        __syncwarp();           // lane 0's acquire is ordered before the other lanes' loads of the produced vectors
+        if (ok) dep_ok = op + 1;
+        return ok;
+    };
+
+    Cursor cur;
+    cur.g = (uint32_t)warp * gridDim.x + blockIdx.x;   // neighbouring items go to different SMs: tails spread evenly
+    cur.op = 0;
+    cur.stage = 0;
+    cur.tile = cur.slice = cur.nsl = 0;
+    locate(cur, lite, total);
+    Cursor lc = cur;
+#pragma unroll
+    for (int s = 0; s < S; s++) {
+        issue_w(lc);
+        advance(lc, lite, total, W);
+    }
+
+    float macc[4] = {0.f, 0.f, 0.f, 0.f};
+    float v[8];
+    bool have_x = false;
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const uint32_t rit = 8u * (uint32_t)t4 + (uint32_t)g8;   // row of the tile this lane files after the K loop
+
+    while (cur.g < total) {
+        if (!have_x) {
+            if (!ensure_deps(cur.op)) { dead = true; break; }
+            load_x(cur, v);
+        }
+        if (!mbar_wait(bar0 + 8 * (cur.stage % S), (cur.stage / S) & 1u)) {
+            if (p.status) atomicExch(p.status, 1);
+            atomicExch(p.ctl + 1, 1u);
+            dead = true;
+            break;
+        }
+        __syncwarp();
+        const OpLite& o = lite[cur.op];
+        const uint32_t u = cur.slice + cur.nsl * cur.it;
+        const int nblk = FMT == RUNIT_FMT_Q4K ? 8 : min(8, (int)(o.nb - u * 8u));
+        prep_mma_block<8, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(xq, v, lane, nblk);
+        __syncwarp();
+        // activations of the next stage travel while this one is multiplied (only if their producers are known complete)
+        Cursor nxt = cur;
+        advance(nxt, lite, total, W);
+        have_x = false;
+        if (nxt.g < total && nxt.op < dep_ok) {
+            load_x(nxt, v);
+            have_x = true;
+        }
+        const uint8_t* slot = ring + (cur.stage % S) * kStageBytes;
+        if (FMT == RUNIT_FMT_Q4K) unit_q4k_mma(slot, xq, lane, macc);
+        else unit_q4_0_mma(slot, xq, lane, nblk, macc);
+        __syncwarp();           // every lane is done with the slot and with xq
+        issue_w(lc);
+        advance(lc, lite, total, W);
+
+        if (cur.it + 1 == cur.n_it) {
+            // ── end of the item: fold the four lanes of a row group, meet the other K-slices, epilogue ──
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                macc[j] += __shfl_xor_sync(0xffffffffu, macc[j], 1);
+                macc[j] += __shfl_xor_sync(0xffffffffu, macc[j], 2);
+            }
+            float r = t4 == 0 ? macc[0] : (t4 == 1 ? macc[1] : (t4 == 2 ? macc[2] : macc[3]));
+            macc[0] = macc[1] = macc[2] = macc[3] = 0.f;
+            bool last = true;
+            if (cur.nsl > 1) {
+                float* part = p.partial + o.partial_off + (size_t)cur.tile * cur.nsl * 32;
+                __stcg(part + cur.slice * 32 + rit, r);
+                __syncwarp();
+                uint32_t ticket = 0;
+                if (lane == 0) {
+                    __threadfence();
+                    ticket = atomicAdd(p.tickets + o.ticket_off + cur.tile, 1u);
+                }
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                last = ticket == cur.nsl - 1;
+                if (last) {
+                    __threadfence();
+                    r = 0.f;
+                    for (uint32_t s = 0; s < cur.nsl; s++) r += __ldcg(part + s * 32 + rit);
+                    if (lane == 0) p.tickets[o.ticket_off + cur.tile] = 0;   // at rest again for the next launch
+                }
+            }
+            if (last) {
+                const OpFull* f = p.full + cur.op;
+                uint32_t si = 0, tb = 0;
+                if (cur.tile >= o.tile_begin2) { si = 2; tb = o.tile_begin2; }
+                else if (cur.tile >= o.tile_begin1) { si = 1; tb = o.tile_begin1; }
+                bool writer = true;
+                uint32_t row = (cur.tile - tb) * kRT + rit;
+                if (o.dual) {
+                    // lanes t = 0, 1 hold gate rows 8t + g, lanes t + 2 the matching up rows:
+                    // act = silu(gate) * up  (crates/kernels/shaders/fused_ffn.metal:24-26,89-92)
+                    const float up_v = __shfl_down_sync(0xffffffffu, r, 2);
+                    r = silu(r) * up_v;
+                    writer = t4 < 2;
+                    row = (cur.tile - tb) * (kRT / 2) + rit;
+                }
+                if (writer && row < f->rows[si]) {
+                    if (f->bias_kind == BIAS_F16) r += __half2float(reinterpret_cast<const __half*>(f->bias[si])[row]);
+                    else if (f->bias_kind == BIAS_F32) r += reinterpret_cast<const float*>(f->bias[si])[row];
+                    if (f->res_kind == RES_F32) r += __ldcg(reinterpret_cast<const float*>(f->res[si]) + row);
+                    if (f->out_f16) reinterpret_cast<__half*>(f->y[si])[row] = __float2half_rn(r);
+                    else reinterpret_cast<float*>(f->y[si])[row] = r;
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence();   // the tile's results are visible before it counts as done
+                    atomicAdd(p.done + cur.op, 1u);
+                }
+            }
+        }
+        cur = nxt;
+    }
+
+    if (dead) {
+        // stages already requested still land in this CTA's shared memory: wait for them (bounded) before leaving
+        for (uint32_t st = cur.stage; st < issued_end; st++) mbar_wait(bar0 + 8 * (st % S), (st / S) & 1u);
+    }
+
+    // The CTA that leaves last puts the counters back to rest for the next launch of this program.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(p.ctl, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        const bool aborted = *reinterpret_cast<volatile uint32_t*>(p.ctl + 1) != 0u;
+        for (uint32_t i = threadIdx.x; i < p.n_ops; i += NW * 32) p.done[i] = 0;
+        if (aborted)
+            for (uint32_t i = threadIdx.x; i < p.n_tickets; i += NW * 32) p.tickets[i] = 0;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            p.ctl[1] = 0;
+            __threadfence();
+            p.ctl[0] = 0;
+        }
+    }
+}
+
+}  // namespace gs
+}  // namespace runit

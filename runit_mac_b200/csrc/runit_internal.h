@@ -20,6 +20,9 @@ struct runit_tuning {
     int32_t gemv_no_cluster = 0;
     int32_t gemv_ksl = 0;       // 0 = automatic K-slices per tile, else 1, 2 or 4
     int32_t gemv_load = 0;      // 0 = tiled bulk loads (TMA) where rows allow, 1 = cp.async everywhere
+    int32_t stream_fuse = 1;    // recorded command lists: runs of consecutive GEMVs become one persistent launch (0 = off)
+    int32_t stream_cfg = 0;     // warps per SM x ring stages of that launch: 0 = default, 1..3 = alternatives
+    int32_t stream_waves = 0;   // target items per GEMV in units of the warp count (0 = default)
 };
 
 // Cached tensor map of one weight matrix view (encoding costs ~1 us on the host).
@@ -50,6 +53,8 @@ struct runit_ctx {
     size_t xq_bytes = 0;
     void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation
     runit_tmap_entry tmaps[256];
+    void* stream_rec = nullptr;         // std::vector<runit::StreamRec>* while a command list is being recorded
+    uint64_t fused_launches = 0;        // GEMV launches that recorded command lists folded into persistent launches
 };
 
 // Tensor map of a [rows][row_bytes] byte matrix with a [box_rows][box_bytes] box (cached per context).

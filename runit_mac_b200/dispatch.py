@@ -170,6 +170,16 @@ class Graph:
     def launch(self):
         self.ctx._check(self.ctx.lib.runit_graph_launch(self.ctx.handle, self.handle))
 
+    @property
+    def fused_launches(self) -> int:
+        """Recorded GEMV launches that were folded into persistent launches."""
+        return self.ctx.lib.runit_graph_fused_launches(self.handle)
+
+    @property
+    def kernel_launches(self) -> int:
+        """Kernel launches one replay performs."""
+        return self.ctx.lib.runit_graph_kernel_launches(self.handle)
+
     def destroy(self):
         if self.handle:
             self.ctx.lib.runit_graph_destroy(self.ctx.handle, self.handle)
