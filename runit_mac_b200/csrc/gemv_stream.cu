@@ -246,7 +246,7 @@ int32_t stream_rec_fuse(runit_ctx* ctx, cudaGraph_t graph, std::vector<void*>* a
     }
     if (ri != recs->size()) return RUNIT_OK;   // a record without its node: leave the graph as recorded
 
-    const uint32_t waves = ctx->tune.stream_waves > 0 ? (uint32_t)ctx->tune.stream_waves : 2u;
+    const uint32_t waves = ctx->tune.stream_waves > 0 ? (uint32_t)ctx->tune.stream_waves : 1u;
     uint32_t fused = 0;
     size_t i = 0;
     while (i < chain.size()) {

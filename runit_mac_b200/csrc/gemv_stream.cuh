@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
     __shared__ OpLite lite[kMaxOps];
     __shared__ __align__(8) uint64_t mbar[NW][S];
     __shared__ uint32_t s_last;
+    __shared__ uint32_t s_ok[kMaxOps], s_lock[kMaxOps];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     {
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         uint4* dst = reinterpret_cast<uint4*>(lite);
         for (uint32_t i = threadIdx.x; i < p.n_ops * (uint32_t)(sizeof(OpLite) / 16); i += NW * 32) dst[i] = src[i];
     }
+    for (uint32_t i = threadIdx.x; i < kMaxOps; i += NW * 32) s_ok[i] = s_lock[i] = 0u;
     const uint32_t bar0 = smem_u32(&mbar[warp][0]);
     if (lane == 0) {
 #pragma unroll
@@ -166,41 +168,61 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
     };
 
     bool dead = false;          // a bounded wait ran out (here or in another warp): stop, drain, leave
-    uint32_t dep_ok = 0;        // GEMVs [0, dep_ok) have had their dependencies checked by this warp
-    // Wait until every GEMV that `op` depends on is complete.  Returns false on time-out / abort.
-    auto ensure_deps = [&](uint32_t op) -> bool {
-        if (op < dep_ok) return true;
-        bool ok = true;
-        if (lane == 0) {
-            const OpLite& o = lite[op];
-#pragma unroll
-            for (int d = 0; d < (int)kMaxDeps; d++) {
-                const uint32_t dop = o.dep[d];
-                if (dop == kNoDep || !ok) continue;
-                const uint32_t want = lite[dop].n_tiles;
-                const uint32_t* ctr = p.done + dop;
-                if (ld_acquire_gpu(ctr) >= want) continue;
-                const long long t0 = clock64();
-                uint32_t spins = 0;
-                while (true) {
-                    __nanosleep(64);
-                    if (ld_acquire_gpu(ctr) >= want) break;
-                    if ((++spins & 63u) == 0u) {
-                        if (*reinterpret_cast<volatile uint32_t*>(p.ctl + 1) != 0u) { ok = false; break; }
-                        if (clock64() - t0 > (1ll << 30)) {   // about half a second: the producer never finished
-                            atomicExch(p.ctl + 1, 1u);
-                            if (p.status) atomicExch(p.status, 4);
-                            ok = false;
-                            break;
-                        }
-                    }
+    // Polls a counter in global memory (gpu-scope acquire) until it reaches `want`.  Returns false if another warp has
+    // raised the abort flag or after about half a second, which it reports through the status word.
+    auto poll_counter = [&](const uint32_t* ctr, uint32_t want, int code) -> bool {
+        if (ld_acquire_gpu(ctr) >= want) return true;
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while (true) {
+            __nanosleep(100);
+            if (ld_acquire_gpu(ctr) >= want) return true;
+            if ((++spins & 31u) == 0u) {
+                if (*reinterpret_cast<volatile uint32_t*>(p.ctl + 1) != 0u) return false;
+                if (clock64() - t0 > (1ll << 30)) {
+                    atomicExch(p.ctl + 1, 1u);
+                    if (p.status) atomicExch(p.status, code);
+                    return false;
                 }
             }
         }
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    };
+    // Wait until every GEMV that `op` depends on is complete.  One warp per CTA polls the completion counters in global
+    // memory (s_lock), the others wait for its verdict in shared memory (s_ok: 1 = complete, 2 = gave up), so a counter
+    // sees one poller per SM instead of one per warp.  Returns false on time-out / abort.
+    uint32_t checked_op = 0xFFFFFFFFu;
+    auto ensure_deps = [&](uint32_t op) -> bool {
+        if (op == checked_op) return true;
+        int ok = 1;
+        if (lane == 0) {
+            volatile uint32_t* okf = &s_ok[op];
+            if (*okf == 0u) {
+                const OpLite& o = lite[op];
+                if (o.dep[0] == kNoDep) {
+                    *okf = 1u;
+                } else if (atomicExch(&s_lock[op], 1u) == 0u) {
+#pragma unroll
+                    for (int d = 0; d < (int)kMaxDeps; d++) {
+                        const uint32_t dop = o.dep[d];
+                        if (dop != kNoDep && ok) ok = poll_counter(p.done + dop, lite[dop].n_tiles, 4) ? 1 : 0;
+                    }
+                    __threadfence_block();
+                    *okf = ok ? 1u : 2u;
+                } else {
+                    const long long t0 = clock64();
+                    while (*okf == 0u) {
+                        __nanosleep(40);
+                        if (clock64() - t0 > (3ll << 29)) break;   // the polling warp itself gives up after 2^30 cycles
+                    }
+                }
+            }
+            if (*okf != 1u) ok = 0;
+            __threadfence_block();
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         __syncwarp();           // lane 0's acquire is ordered before the other lanes' loads of the produced vectors
-        if (ok) dep_ok = op + 1;
-        return ok;
+        if (ok) checked_op = op;
+        return ok != 0;
     };
 
     Cursor cur;
@@ -243,9 +265,11 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         Cursor nxt = cur;
         advance(nxt, lite, total, W);
         have_x = false;
-        if (nxt.g < total && nxt.op < dep_ok) {
+        if (nxt.g < total && (nxt.op == checked_op || *reinterpret_cast<volatile uint32_t*>(&s_ok[nxt.op]) == 1u)) {
+            __threadfence_block();
             load_x(nxt, v);
             have_x = true;
+            checked_op = nxt.op;
         }
         const uint8_t* slot = ring + (cur.stage % S) * kStageBytes;
         if (FMT == RUNIT_FMT_Q4K) unit_q4k_mma(slot, xq, lane, macc);
@@ -263,23 +287,37 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
             }
             float r = t4 == 0 ? macc[0] : (t4 == 1 ? macc[1] : (t4 == 2 ? macc[2] : macc[3]));
             macc[0] = macc[1] = macc[2] = macc[3] = 0.f;
+            // K-slices of a tile: every slice but the last one of the tile files its partial sums and counts itself in
+            // (no reply awaited); the last slice of the tile, which is also the last of them in the item list, waits
+            // for that count, adds the partial sums in slice order with its own at the end, and runs the epilogue.
             bool last = true;
             if (cur.nsl > 1) {
                 float* part = p.partial + o.partial_off + (size_t)cur.tile * cur.nsl * 32;
-                __stcg(part + cur.slice * 32 + rit, r);
-                __syncwarp();
-                uint32_t ticket = 0;
-                if (lane == 0) {
-                    __threadfence();
-                    ticket = atomicAdd(p.tickets + o.ticket_off + cur.tile, 1u);
-                }
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                last = ticket == cur.nsl - 1;
-                if (last) {
-                    __threadfence();
-                    r = 0.f;
-                    for (uint32_t s = 0; s < cur.nsl; s++) r += __ldcg(part + s * 32 + rit);
-                    if (lane == 0) p.tickets[o.ticket_off + cur.tile] = 0;   // at rest again for the next launch
+                uint32_t* ticket = p.tickets + o.ticket_off + cur.tile;
+                if (cur.slice + 1 != cur.nsl) {
+                    last = false;
+                    __stcg(part + cur.slice * 32 + rit, r);
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence();
+                        atomicAdd(ticket, 1u);
+                    }
+                } else {
+                    int ok = 1;
+                    if (lane == 0) ok = poll_counter(ticket, cur.nsl - 1, 5) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    __syncwarp();
+                    if (!ok) { dead = true; break; }
+                    float acc = 0.f;
+                    for (uint32_t s0 = 0; s0 + 1 < cur.nsl; s0 += 8) {
+                        float pv[8];
+#pragma unroll
+                        for (int q = 0; q < 8; q++) pv[q] = s0 + q + 1 < cur.nsl ? __ldcg(part + (s0 + q) * 32 + rit) : 0.f;
+#pragma unroll
+                        for (int q = 0; q < 8; q++) acc += pv[q];
+                    }
+                    r = acc + r;
+                    if (lane == 0) *ticket = 0;   // at rest again for the next launch
                 }
             }
             if (last) {

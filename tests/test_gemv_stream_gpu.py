@@ -150,6 +150,7 @@ def test_mixed_formats_and_long_lists_split_into_several_launches(ctx, oracle):
     x = rng.normal(0, 1, k).astype(np.float32)
     xb = ctx.buffer_from(x)
     ys = [ctx.new_buffer(4 * m) for _ in range(140)]
+    w8 = ctx.buffer_from(O.rand_weights(0, rng, 8, 64))
 
     def calls():
         for i in range(3):
@@ -157,7 +158,7 @@ def test_mixed_formats_and_long_lists_split_into_several_launches(ctx, oracle):
         for i in range(3, 6):
             R.gemv_q4_0_f32in_f32out(ctx, b, xb, ys[i], m, k)
         R.gemv_q4k_f32in_f32out(ctx, a, xb, ys[6], m, k)         # a single one between two other formats stays as it is
-        R.gemv_q8_0_f32in_f32out(ctx, ctx.buffer_from(O.rand_weights(0, rng, 8, 64)), xb, ys[7], 8, 64)
+        R.gemv_q8_0_f32in_f32out(ctx, w8, xb, ys[7], 8, 64)
         for i in range(8, 140):                                   # more GEMVs than one program holds
             R.gemv_q4k_f32in_f32out(ctx, a, xb, ys[i], m, k)
     calls()
