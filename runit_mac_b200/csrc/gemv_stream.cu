@@ -59,7 +59,7 @@ static KernelChoice pick_kernel(int fmt, int cfg) {
     switch (cfg) {
         case 1: return q4k ? choice<RUNIT_FMT_Q4K, 20, 2>() : choice<RUNIT_FMT_Q4_0, 20, 2>();
         case 2: return q4k ? choice<RUNIT_FMT_Q4K, 14, 3>() : choice<RUNIT_FMT_Q4_0, 14, 3>();
-        case 3: return q4k ? choice<RUNIT_FMT_Q4K, 22, 2>() : choice<RUNIT_FMT_Q4_0, 22, 2>();
+        case 3: return q4k ? choice<RUNIT_FMT_Q4K, 18, 2>() : choice<RUNIT_FMT_Q4_0, 18, 2>();
         default: return q4k ? choice<RUNIT_FMT_Q4K, 16, 2>() : choice<RUNIT_FMT_Q4_0, 16, 2>();
     }
 }
@@ -87,10 +87,10 @@ static bool program_add(Program& P, const StreamRec& r, uint32_t n_warps, uint32
     l.tile_begin1 = l.tile_begin2 = kNoSeg;
     for (int i = 0; i < r.nseg; i++) {
         f.map[i] = r.map[i];
-        f.y[i] = r.y[i];
-        f.res[i] = r.res[i];
-        f.bias[i] = r.bias[i];
-        f.rows[i] = r.rows[i];
+        l.y[i] = r.y[i];
+        l.res[i] = r.res[i];
+        l.bias[i] = r.bias[i];
+        l.rows[i] = r.rows[i];
         if (i == 1) l.tile_begin1 = tiles;
         if (i == 2) l.tile_begin2 = tiles;
         tiles += (r.rows[i] + rpt - 1) / rpt;
@@ -99,9 +99,9 @@ static bool program_add(Program& P, const StreamRec& r, uint32_t n_warps, uint32
         if (r.bias_kind != BIAS_NONE) add_range(rd, r.bias[i], (size_t)r.rows[i] * (r.bias_kind == BIAS_F16 ? 2 : 4));
     }
     if (r.dual) f.map[3] = r.map[3];
-    f.out_f16 = r.out_f16;
-    f.res_kind = r.res_kind;
-    f.bias_kind = r.bias_kind;
+    l.out_f16 = (uint8_t)r.out_f16;
+    l.res_kind = (uint8_t)r.res_kind;
+    l.bias_kind = (uint8_t)r.bias_kind;
     add_range(rd, r.x, (size_t)r.k * 4);
 
     // K-slices per tile: items of about (tile-units of this GEMV) / (waves * warps) units each, at least one unit
@@ -110,6 +110,7 @@ static bool program_add(Program& P, const StreamRec& r, uint32_t n_warps, uint32
     upi = std::min(upi, r.n_units);
     uint32_t nsl = (r.n_units + upi - 1) / upi;
     nsl = std::max(1u, std::min(nsl, r.n_units));
+    if (nsl > kMaxSlices) nsl = kMaxSlices;   // the slice that adds the partial sums fetches them in one round trip
     l.item_begin = P.total_items;
     l.n_items = tiles * nsl;
     l.n_slices = nsl;

@@ -30,10 +30,11 @@ constexpr uint32_t kMaxOps = 128;         // GEMVs per launch (a 28-layer token 
 constexpr uint32_t kMaxDeps = 4;
 constexpr uint32_t kNoDep = 0xFFFFu;
 constexpr uint32_t kNoSeg = 0xFFFFFFFFu;
+constexpr uint32_t kMaxSlices = 17;       // K-slices per tile: 16 partial sums + the adder's own
 constexpr int kStageBytes = kRT * 144;    // one warp stage: 32 rows x one 256-weight unit
 constexpr int kXqBytes = 640;             // prepared activations of one unit (MmaX<8>::BYTES = 576), padded to 128
 
-// What a warp needs to walk the item list; copied to shared memory at kernel start.
+// Everything a warp needs about one GEMV except its tensor maps; copied to shared memory at kernel start.
 struct alignas(16) OpLite {
     uint32_t item_begin, n_items;     // this GEMV's range in the global item list
     uint32_t n_slices, n_units, n_tiles;
@@ -44,17 +45,18 @@ struct alignas(16) OpLite {
     uint16_t dep[kMaxDeps];           // GEMVs (indices in this launch) that must be complete first; kNoDep = none
     uint32_t partial_off;             // floats: [tile][slice][32] partial sums of this GEMV
     uint32_t ticket_off;              // words: one arrival counter per tile
-};
-static_assert(sizeof(OpLite) == 64, "OpLite is copied as 16-byte words");
-
-// Tensor maps and epilogue pointers; stays in global memory.
-struct alignas(64) OpFull {
-    CUtensorMap map[4];               // per segment; [3] = the up matrix of a fused gate/up launch
+    // epilogue
     void* y[3];
     const void* res[3];
     const void* bias[3];
     uint32_t rows[3];
-    int32_t out_f16, res_kind, bias_kind;
+    uint8_t out_f16, res_kind, bias_kind, pad;
+};
+static_assert(sizeof(OpLite) == 160, "OpLite is copied as 16-byte words");
+
+// Tensor maps of one GEMV; stay in global memory (the bulk-load unit reads them there).
+struct alignas(64) OpFull {
+    CUtensorMap map[4];               // per segment; [3] = the up matrix of a fused gate/up launch
 };
 
 struct Params {
@@ -190,9 +192,25 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
     // Wait until every GEMV that `op` depends on is complete.  One warp per CTA polls the completion counters in global
     // memory (s_lock), the others wait for its verdict in shared memory (s_ok: 1 = complete, 2 = gave up), so a counter
     // sees one poller per SM instead of one per warp.  Returns false on time-out / abort.
+    // A counter this warp still has to bump (a tile's arrival count or a GEMV's completion count) once its earlier
+    // stores are visible.  The fence that makes them visible costs a round trip to L2 right after the stores and next
+    // to nothing one stage later, so the bump is put off until the next stage has been multiplied — unless the warp is
+    // about to wait for somebody else, in which case it goes out first (a waiting warp never holds a signal back).
+    uint32_t* pending = nullptr;
+    auto flush_pending = [&]() {
+        if (pending != nullptr) {
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence();
+                atomicAdd(pending, 1u);
+            }
+            pending = nullptr;
+        }
+    };
     uint32_t checked_op = 0xFFFFFFFFu;
     auto ensure_deps = [&](uint32_t op) -> bool {
         if (op == checked_op) return true;
+        if (*reinterpret_cast<volatile uint32_t*>(&s_ok[op]) != 1u && lite[op].dep[0] != kNoDep) flush_pending();
         int ok = 1;
         if (lane == 0) {
             volatile uint32_t* okf = &s_ok[op];
@@ -277,6 +295,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         __syncwarp();           // every lane is done with the slot and with xq
         issue_w(lc);
         advance(lc, lite, total, W);
+        flush_pending();        // the signal of the item that ended one stage ago
 
         if (cur.it + 1 == cur.n_it) {
             // ── end of the item: fold the four lanes of a row group, meet the other K-slices, epilogue ──
@@ -297,31 +316,28 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
                 if (cur.slice + 1 != cur.nsl) {
                     last = false;
                     __stcg(part + cur.slice * 32 + rit, r);
-                    __syncwarp();
-                    if (lane == 0) {
-                        __threadfence();
-                        atomicAdd(ticket, 1u);
-                    }
+                    pending = ticket;
                 } else {
+                    flush_pending();
                     int ok = 1;
                     if (lane == 0) ok = poll_counter(ticket, cur.nsl - 1, 5) ? 1 : 0;
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     __syncwarp();
                     if (!ok) { dead = true; break; }
                     float acc = 0.f;
-                    for (uint32_t s0 = 0; s0 + 1 < cur.nsl; s0 += 8) {
-                        float pv[8];
+                    for (uint32_t s0 = 0; s0 + 1 < cur.nsl; s0 += 16) {   // 16 loads in flight per round trip
+                        float pv[16];
 #pragma unroll
-                        for (int q = 0; q < 8; q++) pv[q] = s0 + q + 1 < cur.nsl ? __ldcg(part + (s0 + q) * 32 + rit) : 0.f;
+                        for (int q = 0; q < 16; q++) pv[q] = s0 + q + 1 < cur.nsl ? __ldcg(part + (s0 + q) * 32 + rit) : 0.f;
 #pragma unroll
-                        for (int q = 0; q < 8; q++) acc += pv[q];
+                        for (int q = 0; q < 16; q++) acc += pv[q];
                     }
                     r = acc + r;
                     if (lane == 0) *ticket = 0;   // at rest again for the next launch
                 }
             }
             if (last) {
-                const OpFull* f = p.full + cur.op;
+                const OpLite* f = &o;
                 uint32_t si = 0, tb = 0;
                 if (cur.tile >= o.tile_begin2) { si = 2; tb = o.tile_begin2; }
                 else if (cur.tile >= o.tile_begin1) { si = 1; tb = o.tile_begin1; }
@@ -342,15 +358,14 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
                     if (f->out_f16) reinterpret_cast<__half*>(f->y[si])[row] = __float2half_rn(r);
                     else reinterpret_cast<float*>(f->y[si])[row] = r;
                 }
-                __syncwarp();
-                if (lane == 0) {
-                    __threadfence();   // the tile's results are visible before it counts as done
-                    atomicAdd(p.done + cur.op, 1u);
-                }
+                pending = p.done + cur.op;   // the tile counts as done once its results are visible
+                // nothing else of this warp is ready to run: the consumers should not wait for a later stage of ours
+                if (!have_x) flush_pending();
             }
         }
         cur = nxt;
     }
+    flush_pending();
 
     if (dead) {
         // stages already requested still land in this CTA's shared memory: wait for them (bounded) before leaving
