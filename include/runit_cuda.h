@@ -86,10 +86,12 @@ int32_t runit_graph_begin(runit_ctx_t* ctx);
 int32_t runit_graph_end(runit_ctx_t* ctx, runit_graph_t** out);
 int32_t runit_graph_launch(runit_ctx_t* ctx, runit_graph_t* graph);
 int32_t runit_graph_destroy(runit_ctx_t* ctx, runit_graph_t* graph);
-/* Runs of consecutive batch-1 fused-dequant GEMVs (4-bit formats, f32 activations) of a recording are executed by one
- * persistent launch that streams the weights of the whole run without stopping at the boundaries between the GEMVs; the
- * ops keep their recorded order wherever one reads or overwrites what another wrote or read.  Returns how many of the
- * recorded GEMV launches the list folded this way (0: none were adjacent, or the test-only knob stream_fuse is 0). */
+/* Opt-in (runit_set_tuning(ctx, "stream_fuse", 1) before runit_graph_begin): runs of consecutive batch-1 fused-dequant
+ * GEMVs (4-bit formats, f32 activations) of a recording are executed by ONE persistent launch whose warps stream the
+ * weights of the whole run without stopping at the boundaries between the GEMVs; the ops keep their recorded order
+ * wherever one reads or overwrites what another wrote or read, and the results equal those of the separate launches up
+ * to the summation order over K-slices.  Off by default: on B200 the separate launches (with dependent launch) are still
+ * faster for decode-size matrices.  Returns how many of the recorded GEMV launches the list folded this way. */
 uint32_t runit_graph_fused_launches(runit_graph_t* graph);
 /* Kernel launches one replay of the list performs (after that folding). */
 uint32_t runit_graph_kernel_launches(runit_graph_t* graph);

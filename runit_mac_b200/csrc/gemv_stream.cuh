@@ -6,8 +6,11 @@
 // time for a 38 MB matrix).  Here the whole run is ONE kernel:
 //   * the grid is one CTA per SM, NW warps each; the unit of work is a warp-item = one 32-row tile x one K-slice of one
 //     GEMV (the tile/unit/MMA arithmetic is that of gemv_staged_kernel, integer tensor-core path);
-//   * the items of all GEMVs form one list in launch order, and warp w of W takes items w, w + W, ...: static,
-//     deterministic, and free of deadlock because an item only ever waits for items with lower indices;
+//   * the items of all GEMVs form one list in launch order, dealt into NW interleaved classes; warp w of every CTA
+//     takes the items of class w from that class's counter, lowest index first (SMs differ in speed by about 10 %: a
+//     fixed split leaves the fast ones idle, and one counter for all warps saturates).  An item only ever waits for
+//     items with lower indices, and the lowest unfinished item is always some warp's current one, so no wait can last;
+//     which warp computes an item has no influence on the result;
 //   * every warp keeps its own ring of S weight stages (TMA boxes of 32 rows x 144 bytes) and its load cursor runs S
 //     stages ahead of its compute cursor ACROSS item and GEMV boundaries: weights do not depend on anything, so the
 //     stream from HBM never stops at a boundary;
@@ -67,17 +70,19 @@ struct Params {
     uint32_t* tickets;
     uint32_t n_tickets;
     uint32_t* done;      // [n_ops] tiles completed; zero at rest
-    uint32_t* ctl;       // [0] exit ticket, [1] abort flag; zero at rest
+    uint32_t* ctl;       // [0] exit ticket, [1] abort flag, [2 + w] items of class w handed out beyond the CTAs' first; zero at rest
     int32_t* status;     // host-visible status word of the context
 };
 
 struct Cursor {
     uint32_t g;          // global item index; >= total_items: past the end
+    uint32_t ord;        // how many items this warp has taken before this one
     uint32_t op, tile, slice, nsl;
     uint32_t it, n_it;   // stage inside the item
     uint32_t stage;      // running stage number of this warp: ring slot = stage % S, barrier phase = (stage / S) & 1
 };
 
+// Which GEMV, tile and K-slice item c.g is.  A warp's items come in increasing order, so c.op only moves forward.
 __device__ __forceinline__ void locate(Cursor& c, const OpLite* lite, uint32_t total) {
     c.it = 0;
     if (c.g >= total) { c.n_it = 0; return; }
@@ -87,13 +92,6 @@ __device__ __forceinline__ void locate(Cursor& c, const OpLite* lite, uint32_t t
     c.slice = local - c.tile * nsl;
     c.nsl = nsl;
     c.n_it = (lite[c.op].n_units - c.slice + nsl - 1) / nsl;
-}
-__device__ __forceinline__ void advance(Cursor& c, const OpLite* lite, uint32_t total, uint32_t W) {
-    c.stage++;
-    if (++c.it >= c.n_it) {
-        c.g += W;
-        locate(c, lite, total);
-    }
 }
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
@@ -110,6 +108,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
     __shared__ __align__(8) uint64_t mbar[NW][S];
     __shared__ uint32_t s_last;
     __shared__ uint32_t s_ok[kMaxOps], s_lock[kMaxOps];
+    __shared__ uint32_t s_taken[NW][8];   // the item indices a warp has taken, by ordinal modulo 8 (load cursor -> compute cursor)
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     {
@@ -130,7 +129,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
     uint8_t* ring = smem + warp * (S * kStageBytes + kXqBytes);
     uint8_t* xq = ring + S * kStageBytes;
     const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t total = p.total_items, W = gridDim.x * NW;
+    const uint32_t total = p.total_items;
 
     // Weight boxes of the stage the cursor points at (lane 0 issues; everything it needs is in shared memory).
     uint32_t issued_end = 0;    // stages [0, issued_end) of this warp carry a bulk-load transaction
@@ -194,7 +193,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
     // sees one poller per SM instead of one per warp.  Returns false on time-out / abort.
     // A counter this warp still has to bump (a tile's arrival count or a GEMV's completion count) once its earlier
     // stores are visible.  The fence that makes them visible costs a round trip to L2 right after the stores and next
-    // to nothing one stage later, so the bump is put off until the next stage has been multiplied — unless the warp is
+    // to nothing a little later, so the bump is put off until the next stage's activations are prepared — unless the warp is
     // about to wait for somebody else, in which case it goes out first (a waiting warp never holds a signal back).
     uint32_t* pending = nullptr;
     auto flush_pending = [&]() {
@@ -243,18 +242,47 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         return ok != 0;
     };
 
+    // Item sequence of this warp: the first item is fixed, every later one comes from the counter of the warp's class.  The load cursor takes items; the request for the item after the next is in flight while
+    // the next one is being loaded, so the counter's latency stays hidden.  The compute cursor follows through s_taken.
+    uint32_t take_raw = 0;      // lane 0: reply of the outstanding request
+    auto request_item = [&]() {   // class `warp`: items warp, warp + NW, ...; the first gridDim.x of them are the CTAs' first items
+        if (lane == 0) take_raw = (uint32_t)warp + (uint32_t)NW * (gridDim.x + atomicAdd(p.ctl + 2 + warp, 1u));
+    };
+    auto advance_load = [&](Cursor& c) {
+        c.stage++;
+        if (++c.it >= c.n_it) {
+            if (c.g >= total) { c.it = 0; return; }          // past the end: stay there
+            c.ord++;
+            c.g = __shfl_sync(0xffffffffu, take_raw, 0);
+            if (lane == 0) s_taken[warp][c.ord & 7u] = c.g;
+            if (c.g < total) request_item();
+            locate(c, lite, total);
+        }
+    };
+    auto advance_follow = [&](Cursor& c) {
+        c.stage++;
+        if (++c.it >= c.n_it) {
+            c.ord++;
+            c.g = *reinterpret_cast<volatile uint32_t*>(&s_taken[warp][c.ord & 7u]);
+            locate(c, lite, total);
+        }
+    };
     Cursor cur;
-    cur.g = (uint32_t)warp * gridDim.x + blockIdx.x;   // neighbouring items go to different SMs: tails spread evenly
+    cur.g = (uint32_t)warp + (uint32_t)NW * blockIdx.x;
+    cur.ord = 0;
     cur.op = 0;
     cur.stage = 0;
     cur.tile = cur.slice = cur.nsl = 0;
     locate(cur, lite, total);
+    if (lane == 0) s_taken[warp][0] = cur.g;
+    if (cur.g < total) request_item();
     Cursor lc = cur;
 #pragma unroll
     for (int s = 0; s < S; s++) {
         issue_w(lc);
-        advance(lc, lite, total, W);
+        advance_load(lc);
     }
+    __syncwarp();
 
     float macc[4] = {0.f, 0.f, 0.f, 0.f};
     float v[8];
@@ -279,9 +307,10 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         const int nblk = FMT == RUNIT_FMT_Q4K ? 8 : min(8, (int)(o.nb - u * 8u));
         prep_mma_block<8, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(xq, v, lane, nblk);
         __syncwarp();
+        flush_pending();        // the signal of the item that ended a moment ago: its stores have had time to land
         // activations of the next stage travel while this one is multiplied (only if their producers are known complete)
         Cursor nxt = cur;
-        advance(nxt, lite, total, W);
+        advance_follow(nxt);
         have_x = false;
         if (nxt.g < total && (nxt.op == checked_op || *reinterpret_cast<volatile uint32_t*>(&s_ok[nxt.op]) == 1u)) {
             __threadfence_block();
@@ -294,8 +323,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         else unit_q4_0_mma(slot, xq, lane, nblk, macc);
         __syncwarp();           // every lane is done with the slot and with xq
         issue_w(lc);
-        advance(lc, lite, total, W);
-        flush_pending();        // the signal of the item that ended one stage ago
+        advance_load(lc);
 
         if (cur.it + 1 == cur.n_it) {
             // ── end of the item: fold the four lanes of a row group, meet the other K-slices, epilogue ──
@@ -388,6 +416,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_stream_kernel(const Params p)
         __syncthreads();
         if (threadIdx.x == 0) {
             p.ctl[1] = 0;
+            for (int w = 0; w < NW; w++) p.ctl[2 + w] = 0;
             __threadfence();
             p.ctl[0] = 0;
         }

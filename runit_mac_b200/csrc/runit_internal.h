@@ -20,7 +20,7 @@ struct runit_tuning {
     int32_t gemv_no_cluster = 0;
     int32_t gemv_ksl = 0;       // 0 = automatic K-slices per tile, else 1, 2 or 4
     int32_t gemv_load = 0;      // 0 = tiled bulk loads (TMA) where rows allow, 1 = cp.async everywhere
-    int32_t stream_fuse = 1;    // recorded command lists: runs of consecutive GEMVs become one persistent launch (0 = off)
+    int32_t stream_fuse = 0;    // recorded command lists: 1 = runs of consecutive GEMVs become one persistent launch
     int32_t stream_cfg = 0;     // warps per SM x ring stages of that launch: 0 = default, 1..3 = alternatives
     int32_t stream_waves = 0;   // target items per GEMV in units of the warp count (0 = default)
 };

@@ -1,4 +1,5 @@
-"""GPU parity tests of recorded command lists whose consecutive GEMVs run as one persistent launch.
+"""GPU parity tests of recorded command lists whose consecutive GEMVs run as one persistent launch (opt-in knob
+stream_fuse).
 
 The recorded ops must behave exactly like the same calls issued one by one (the reference commits a token's dispatches
 in one command buffer and its GPU runs them in order, crates/kernels/src/context.rs:248-296): every output is compared
@@ -76,7 +77,7 @@ def test_recorded_token_runs_as_one_launch_and_matches(ctx, oracle, fmt, cfg):
             record_token(ctx, R, layers, lm, bufs, vocab)
             g = ctx.graph_end()
         finally:
-            ctx.set_tuning("stream_fuse", 1)
+            ctx.set_tuning("stream_fuse", 0)
             ctx.set_tuning("stream_cfg", 0)
         outs = []
         bufs["x"].upload(x0)
@@ -127,9 +128,13 @@ def test_recorded_order_is_kept_across_overwrites(ctx, oracle):
     calls()
     ctx.flush()
     xb.upload(x0)
-    ctx.graph_begin()
-    calls()
-    g = ctx.graph_end()
+    ctx.set_tuning("stream_fuse", 1)
+    try:
+        ctx.graph_begin()
+        calls()
+        g = ctx.graph_end()
+    finally:
+        ctx.set_tuning("stream_fuse", 0)
     assert g.fused_launches == 4 and g.kernel_launches == 1
     g.launch()
     ctx.flush()
@@ -163,9 +168,13 @@ def test_mixed_formats_and_long_lists_split_into_several_launches(ctx, oracle):
             R.gemv_q4k_f32in_f32out(ctx, a, xb, ys[i], m, k)
     calls()
     ctx.flush()
-    ctx.graph_begin()
-    calls()
-    g = ctx.graph_end()
+    ctx.set_tuning("stream_fuse", 1)
+    try:
+        ctx.graph_begin()
+        calls()
+        g = ctx.graph_end()
+    finally:
+        ctx.set_tuning("stream_fuse", 0)
     assert g.fused_launches == 3 + 3 + 132 and g.kernel_launches == 1 + 1 + 1 + 1 + 2
     g.launch()
     ctx.flush()
