@@ -169,8 +169,8 @@ int32_t runit_flush(runit_ctx_t* ctx) {
         const int32_t why = ctx->h_status[0];
         ctx->h_status[0] = 0;
         if (ctx->d_abort) cudaMemset(ctx->d_abort, 0, 4);   // the stream is idle: barriers wait again after this report
-        runit_fail(ctx, RUNIT_ERR_TIMEOUT, why == 3 ? "a peer barrier gave up: a rank never announced its epoch"
-                                                    : "a kernel gave up a bounded wait (a copy or a dependency never completed)");
+        runit_fail(ctx, RUNIT_ERR_TIMEOUT, why == 3 ? "a peer barrier gave up: a rank never announced its epoch (code %d)"
+                                                    : "a kernel gave up a bounded wait (a copy or a dependency never completed; code %d)", why);
     }
     int32_t st = ctx->sticky_status;
     ctx->sticky_status = RUNIT_OK;   // the message stays readable until the next error
@@ -195,7 +195,8 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "gemv_no_cluster")) ctx->tune.gemv_no_cluster = value;
     else if (!strcmp(key, "stream_fuse")) ctx->tune.stream_fuse = value;
     else if (!strcmp(key, "stream_cfg")) ctx->tune.stream_cfg = value;
-    else if (!strcmp(key, "stream_waves")) ctx->tune.stream_waves = value;
+    else if (!strcmp(key, "stream_ksl")) ctx->tune.stream_ksl = value;
+    else if (!strcmp(key, "stream_dynamic")) ctx->tune.stream_dynamic = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
     return RUNIT_OK;
 }

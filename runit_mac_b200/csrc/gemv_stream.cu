@@ -59,7 +59,7 @@ static KernelChoice pick_kernel(int fmt, int cfg) {
     switch (cfg) {
         case 1: return q4k ? choice<RUNIT_FMT_Q4K, 20, 2>() : choice<RUNIT_FMT_Q4_0, 20, 2>();
         case 2: return q4k ? choice<RUNIT_FMT_Q4K, 14, 3>() : choice<RUNIT_FMT_Q4_0, 14, 3>();
-        case 3: return q4k ? choice<RUNIT_FMT_Q4K, 18, 2>() : choice<RUNIT_FMT_Q4_0, 18, 2>();
+        case 3: return q4k ? choice<RUNIT_FMT_Q4K, 12, 3>() : choice<RUNIT_FMT_Q4_0, 12, 3>();
         default: return q4k ? choice<RUNIT_FMT_Q4K, 16, 2>() : choice<RUNIT_FMT_Q4_0, 16, 2>();
     }
 }
@@ -69,12 +69,32 @@ struct Program {
     std::vector<OpLite> lite;
     std::vector<std::vector<Range>> reads, writes;
     std::vector<std::bitset<kMaxOps>> anc;   // every earlier GEMV this one is ordered after (transitively)
-    uint32_t total_items = 0, partial_floats = 0, n_tickets = 0;
+    uint32_t total_items = 0;
 };
+
+// Warps per tile (K-slices) and tiles per CTA-item for a GEMV of `tiles` tiles and `units` K-units on `sms` CTAs of `nw`
+// warps: the split with the lowest estimated time in units of one warp-stage.  One wave of items (items <= CTAs) costs
+// the units a warp streams; more waves cost their number plus half an item for the tail that dynamic hand-out leaves;
+// every item and every team reduction adds a little.
+static void pick_split(uint32_t tiles, uint32_t units, uint32_t nw, uint32_t sms, uint32_t* ksl_out, uint32_t* tpc_out) {
+    double best = 1e30;
+    uint32_t bk = 1;
+    for (uint32_t ksl = 1; ksl <= nw && ksl <= units; ksl++) {
+        const uint32_t tpc = nw / ksl;
+        const uint32_t items = (tiles + tpc - 1) / tpc;
+        const double pwu = (double)((units + ksl - 1) / ksl);
+        const double waves = (double)items / sms;
+        double cost = items <= sms ? pwu : (waves + 0.5) * pwu;
+        cost += 0.35 * std::max(1.0, waves) + (ksl > 1 ? 0.3 : 0.0);
+        if (cost < best - 1e-9) { best = cost; bk = ksl; }
+    }
+    *ksl_out = bk;
+    *tpc_out = nw / bk;
+}
 
 // Appends the GEMV to the program.  Returns false (and leaves the program unchanged) if it does not fit: the table is
 // full, or it would need more dependency slots than an entry has.
-static bool program_add(Program& P, const StreamRec& r, uint32_t n_warps, uint32_t waves) {
+static bool program_add(Program& P, const StreamRec& r, uint32_t nw, uint32_t sms, uint32_t force_ksl) {
     const uint32_t n = (uint32_t)P.lite.size();
     if (n >= kMaxOps) return false;
     OpFull f;
@@ -104,24 +124,19 @@ static bool program_add(Program& P, const StreamRec& r, uint32_t n_warps, uint32
     l.bias_kind = (uint8_t)r.bias_kind;
     add_range(rd, r.x, (size_t)r.k * 4);
 
-    // K-slices per tile: items of about (tile-units of this GEMV) / (waves * warps) units each, at least one unit
-    const uint64_t tile_units = (uint64_t)tiles * r.n_units;
-    uint32_t upi = (uint32_t)std::max<uint64_t>(1, tile_units / ((uint64_t)waves * n_warps));
-    upi = std::min(upi, r.n_units);
-    uint32_t nsl = (r.n_units + upi - 1) / upi;
-    nsl = std::max(1u, std::min(nsl, r.n_units));
-    if (nsl > kMaxSlices) nsl = kMaxSlices;   // the slice that adds the partial sums fetches them in one round trip
+    uint32_t ksl = 1, tpc = nw;
+    pick_split(tiles, r.n_units, nw, sms, &ksl, &tpc);
+    if (force_ksl >= 1 && force_ksl <= nw && force_ksl <= r.n_units) { ksl = force_ksl; tpc = nw / ksl; }
     l.item_begin = P.total_items;
-    l.n_items = tiles * nsl;
-    l.n_slices = nsl;
+    l.n_items = (tiles + tpc - 1) / tpc;
+    l.ksl = ksl;
+    l.tpc = tpc;
     l.n_units = r.n_units;
     l.n_tiles = tiles;
     l.dual = (uint32_t)r.dual;
     l.k = r.k;
     l.nb = r.nb;
     l.x = static_cast<const float*>(r.x);
-    l.partial_off = P.partial_floats;
-    l.ticket_off = P.n_tickets;
     if ((uint64_t)P.total_items + l.n_items >= (1ull << 31)) return false;
 
     // dependencies: the latest earlier GEMVs with a read-after-write, write-after-write or write-after-read overlap
@@ -144,8 +159,6 @@ static bool program_add(Program& P, const StreamRec& r, uint32_t n_warps, uint32
     P.writes.push_back(wr);
     P.anc.push_back(anc);
     P.total_items += l.n_items;
-    if (nsl > 1) P.partial_floats += l.n_items * 32;
-    P.n_tickets += tiles;
     return true;
 }
 
@@ -159,9 +172,7 @@ static int32_t program_emit(runit_ctx* ctx, const Program& P, int fmt, const Ker
     const size_t off_lite = align_up(off_full + n * sizeof(OpFull), 256);
     const size_t off_done = align_up(off_lite + n * sizeof(OpLite), 256);
     const size_t off_ctl = align_up(off_done + n * 4, 256);
-    const size_t off_tick = off_ctl + 256;
-    const size_t off_part = align_up(off_tick + (size_t)P.n_tickets * 4, 256);
-    const size_t bytes = off_part + std::max<size_t>(256, (size_t)P.partial_floats * 4);
+    const size_t bytes = off_ctl + 256;
     uint8_t* d = nullptr;
     cudaError_t e = cudaMalloc((void**)&d, bytes);
     if (e != cudaSuccess) {
@@ -169,7 +180,7 @@ static int32_t program_emit(runit_ctx* ctx, const Program& P, int fmt, const Ker
         return runit_fail(ctx, RUNIT_ERR_ALLOC, "fused GEMV stream: allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
     }
     allocs->push_back(d);
-    RUNIT_CUDA_TRY(ctx, cudaMemset(d, 0, off_part));   // counters and tickets at rest; the partial sums need no initial value
+    RUNIT_CUDA_TRY(ctx, cudaMemset(d, 0, bytes));   // counters at rest
     RUNIT_CUDA_TRY(ctx, cudaMemcpy(d + off_full, P.full.data(), n * sizeof(OpFull), cudaMemcpyHostToDevice));
     RUNIT_CUDA_TRY(ctx, cudaMemcpy(d + off_lite, P.lite.data(), n * sizeof(OpLite), cudaMemcpyHostToDevice));
     Params prm;
@@ -178,12 +189,10 @@ static int32_t program_emit(runit_ctx* ctx, const Program& P, int fmt, const Ker
     prm.lite = reinterpret_cast<const OpLite*>(d + off_lite);
     prm.n_ops = (uint32_t)n;
     prm.total_items = P.total_items;
-    prm.partial = reinterpret_cast<float*>(d + off_part);
-    prm.tickets = reinterpret_cast<uint32_t*>(d + off_tick);
-    prm.n_tickets = P.n_tickets;
     prm.done = reinterpret_cast<uint32_t*>(d + off_done);
     prm.ctl = reinterpret_cast<uint32_t*>(d + off_ctl);
     prm.status = ctx->d_status;
+    prm.dynamic = ctx->tune.stream_dynamic ? 1 : 0;
     (void)fmt;
     void* kargs[1] = {&prm};
     cudaKernelNodeParams kp;
@@ -247,7 +256,7 @@ int32_t stream_rec_fuse(runit_ctx* ctx, cudaGraph_t graph, std::vector<void*>* a
     }
     if (ri != recs->size()) return RUNIT_OK;   // a record without its node: leave the graph as recorded
 
-    const uint32_t waves = ctx->tune.stream_waves > 0 ? (uint32_t)ctx->tune.stream_waves : 1u;
+    const uint32_t force_ksl = ctx->tune.stream_ksl > 0 ? (uint32_t)ctx->tune.stream_ksl : 0u;
     uint32_t fused = 0;
     size_t i = 0;
     while (i < chain.size()) {
@@ -266,7 +275,7 @@ int32_t stream_rec_fuse(runit_ctx* ctx, cudaGraph_t graph, std::vector<void*>* a
         Program P;
         size_t j = i;
         while (j < chain.size() && rec_of[j] >= 0 && (*recs)[rec_of[j]].fmt == fmt &&
-               program_add(P, (*recs)[rec_of[j]], (uint32_t)ctx->sm_count * (uint32_t)kc.nw, waves))
+               program_add(P, (*recs)[rec_of[j]], (uint32_t)kc.nw, (uint32_t)ctx->sm_count, force_ksl))
             j++;
         if (j - i < 2) { i = std::max(j, i + 1); continue; }
         cudaGraphNode_t pred = i > 0 ? chain[i - 1] : nullptr, fresh = nullptr;

@@ -184,3 +184,64 @@ def test_mixed_formats_and_long_lists_split_into_several_launches(ctx, oracle):
     for i in range(3, 6):
         assert_close(O, r40, ys[i].download(np.float32, m), what="q4_0 output %d" % i)
     g.destroy()
+
+
+def test_decode_shapes_over_several_layers_match_the_separate_launches(ctx):
+    """Three layers of the 7B-shaped GEMV set (fused Q|K|V, o + residual, fused gate/up, down + residual) plus the output
+    matrix, weights generated on the device: every CTA walks more items than its per-item bookkeeping has slots, through
+    GEMVs with 14, 2 and 16 warps per tile (some warps have no part in some items).  The folded list must reproduce the
+    separate launches (same arithmetic, other summation order over the K-slices)."""
+    import runit_mac_b200 as R
+    hidden, inter, q_dim, kv_dim, vocab, layers = 3584, 18944, 3584, 512, 32000, 3
+    rb = lambda k: k // 256 * 144
+    mats = {"q": (q_dim, hidden), "k": (kv_dim, hidden), "v": (kv_dim, hidden), "o": (hidden, q_dim), "gate": (inter, hidden),
+            "up": (inter, hidden), "down": (hidden, inter)}
+    W = []
+    for l in range(layers):
+        d = {}
+        for i, (n, (m, k)) in enumerate(mats.items()):
+            d[n] = ctx.new_buffer(m * rb(k))
+            R.fill_weights_q4k_zero_mean(ctx, d[n], m * (k // 256), 1000 + 16 * l + i, 2e-4)
+        W.append(d)
+    lm = ctx.new_buffer(vocab * rb(hidden))
+    R.fill_weights_q4k_zero_mean(ctx, lm, vocab * (hidden // 256), 77, 2e-4)
+    f4 = lambda n: ctx.new_buffer(4 * n)
+    xn, x, q, kk, v, act, logits = f4(hidden), f4(hidden), f4(q_dim), f4(kv_dim), f4(kv_dim), f4(inter), f4(vocab)
+    R.fill_normal_f32(ctx, xn, hidden, 5, 1.0)
+    x0 = np.random.default_rng(3).normal(0, 1, hidden).astype(np.float32)
+
+    def calls():
+        for w in W:
+            R.fused_qkv_q4k_f32(ctx, w["q"], w["k"], w["v"], xn, q, kk, v, q_dim, kv_dim, hidden)
+            R.gemv_q4k_add_f32_f32in(ctx, w["o"], q, x, x, hidden, q_dim)
+            R.fused_ffn_q4k_f32(ctx, w["gate"], w["up"], xn, act, inter, hidden)
+            R.gemv_q4k_add_f32_f32in(ctx, w["down"], act, x, x, hidden, inter)
+        R.gemv_q4k_f32in_f32out(ctx, lm, xn, logits, vocab, hidden)
+
+    def run(fuse):
+        ctx.set_tuning("stream_fuse", fuse)
+        try:
+            calls()
+            ctx.flush()
+            ctx.graph_begin()
+            calls()
+            g = ctx.graph_end()
+        finally:
+            ctx.set_tuning("stream_fuse", 0)
+        x.upload(x0)
+        outs = []
+        for _ in range(2):
+            g.launch()
+            ctx.flush()
+            outs.append((x.download(np.float32, hidden), act.download(np.float32, inter), logits.download(np.float32, vocab)))
+        n = (g.fused_launches, g.kernel_launches)
+        g.destroy()
+        return outs, n
+    fused, nf = run(1)
+    plain, npl = run(0)
+    assert nf == (4 * layers + 1, 1) and npl == (0, 4 * layers + 1)
+    for a, b in zip(fused, plain):
+        for va, vb in zip(a, b):
+            assert np.isfinite(va).all()
+            scale = np.sqrt(np.mean(vb.astype(np.float64) ** 2))
+            assert np.abs(va - vb).max() <= 3e-4 * scale
