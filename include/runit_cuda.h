@@ -55,7 +55,7 @@ enum {
 };
 
 enum { RUNIT_BUF_DEVICE = 0, RUNIT_BUF_HOST_VISIBLE = 1 };
-enum { RUNIT_FMT_Q8_0 = 0, RUNIT_FMT_Q4_0 = 1, RUNIT_FMT_Q4K = 2 };
+enum { RUNIT_FMT_Q8_0 = 0, RUNIT_FMT_Q4_0 = 1, RUNIT_FMT_Q4K = 2, RUNIT_FMT_Q5_0 = 3, RUNIT_FMT_Q5K = 4, RUNIT_FMT_Q6K = 5 };
 
 /* ── context, buffers, flush: MetalContext::{new,new_buffer,flush}, context.rs:163-296 ── */
 int32_t runit_ctx_create(int32_t device, runit_ctx_t** out);
@@ -153,6 +153,23 @@ int32_t runit_gemv_q4k_add_f16(runit_ctx_t*, const void* weight_q4k, const void*
 int32_t runit_gemv_q4k_add_f32res_f16(runit_ctx_t*, const void* weight_q4k, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
 /* dispatch.rs:756  Q4_K blocks -> f16 elements */
 int32_t runit_dequant_q4k_f16(runit_ctx_t*, const void* input, void* output, uint32_t n_blocks);
+
+/* ── Q5_0, Q5_K, Q6_K: fused-dequant GEMVs for formats the reference only expands on the CPU at load time
+ *    (crates/engine/src/forward.rs:900-919 Q5_0, 920-949 Q6_K, 979-1012 Q5_K) and then multiplies as f16.  No twin in
+ *    dispatch.rs; names follow the Q4_K twins.  Layouts as the reference decodes them:
+ *      Q5_0: 22-byte blocks {f16 d; u8 qh[4]; u8 qs[16]}, byte j = elements j (low nibble) and j+16 (high), fifth bits in
+ *            bit j of qh (little-endian u32) and bit j+16, value = d*(q-16); k a multiple of 32
+ *      Q5_K: 176-byte superblocks {f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]}: Q4_K plus the fifth bit of
+ *            element e in bit e%8 of qh[e/8]; k a multiple of 256
+ *      Q6_K: 210-byte superblocks {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}, value = d*scale*(q-32), scale index
+ *            8*(e/128) + 2*((e%128)/32); k a multiple of 256
+ *    y_f32[m] = W[m,k] . x_f32[k] (+ residual_f32; output may alias residual). ── */
+int32_t runit_gemv_q5_0_f32in_f32out(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+int32_t runit_gemv_q5_0_add_f32_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+int32_t runit_gemv_q5k_f32in_f32out(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+int32_t runit_gemv_q5k_add_f32_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
+int32_t runit_gemv_q6k_f32in_f32out(runit_ctx_t*, const void* weight, const void* input, void* output, uint32_t m, uint32_t k);
+int32_t runit_gemv_q6k_add_f32_f32in(runit_ctx_t*, const void* weight, const void* input, void* output, const void* residual, uint32_t m, uint32_t k);
 
 /* ── MoE glue and router ── */
 /* dispatch.rs:270  y_f16[m] = W_f16[m,k] . x_f32[k]  (router logits) */

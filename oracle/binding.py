@@ -12,7 +12,7 @@ from pathlib import Path
 import numpy as np
 
 __all__ = [
-    "Q8_0", "Q4_0", "Q4K", "TIER_SHADER", "TIER_DEQUANT", "TIER_F64", "MOE_F32", "MOE_REF_F16",
+    "Q8_0", "Q4_0", "Q4K", "Q5_0", "Q5K", "Q6K", "TIER_SHADER", "TIER_DEQUANT", "TIER_F64", "MOE_F32", "MOE_REF_F16",
     "build_oracle", "lib", "num_threads", "set_num_threads", "row_bytes", "block_elems",
     "block_bytes", "dequant_rows", "dequant_q4k_f16", "gemv", "gemv_f64", "gemv_f16w_f32in",
     "gemv_f32w", "silu_mul_f32", "silu_mul_f16", "scale_accumulate_f16", "add_f16_into_f32",
@@ -21,7 +21,7 @@ __all__ = [
     "compare", "DiffStats", "f32_to_f16_bits", "f16_bits_to_f32",
 ]
 
-Q8_0, Q4_0, Q4K = 0, 1, 2
+Q8_0, Q4_0, Q4K, Q5_0, Q5K, Q6K = 0, 1, 2, 3, 4, 5
 TIER_SHADER, TIER_DEQUANT, TIER_F64 = 0, 1, 2
 MOE_F32, MOE_REF_F16 = 0, 1
 

@@ -14,7 +14,7 @@ from __future__ import annotations
 import numpy as np
 
 __all__ = ["pack_q8_0", "pack_q4_0", "pack_q4k", "pack_q4k_scales", "rand_q8_0", "rand_q4_0",
-           "rand_q4k", "rand_weights", "lcg_random_f32"]
+           "rand_q4k", "rand_weights", "lcg_random_f32", "pack_q5_0", "pack_q5k", "pack_q6k", "rand_q5_0", "rand_q5k", "rand_q6k"]
 
 
 def pack_q8_0(d: np.ndarray, qs: np.ndarray) -> np.ndarray:
@@ -86,8 +86,77 @@ def rand_q4k(rng: np.random.Generator, m: int, k: int, sigma: float = 0.01) -> n
     return pack_q4k(d, dmin, sc, mn, nib)
 
 
+def pack_q5_0(d: np.ndarray, q: np.ndarray) -> np.ndarray:
+    """d: [m, nb]; q: [m, nb, 32] in 0..31 (value = d * (q - 16)) -> uint8 [m, nb*22].
+    Layout the reference decodes (crates/engine/src/forward.rs:900-919): byte j of qs = element j (low nibble) and
+    element j + 16 (high nibble); fifth bit of element e = bit e of the 32-bit little-endian word qh."""
+    m, nb = d.shape
+    q = q.astype(np.uint32).reshape(m, nb, 32)
+    out = np.empty((m, nb, 22), np.uint8)
+    out[:, :, 0:2] = d.astype(np.float16).view(np.uint8).reshape(m, nb, 2)
+    qh = ((q >> 4) << np.arange(32, dtype=np.uint32)).sum(-1).astype(np.uint32)
+    out[:, :, 2:6] = qh.view(np.uint8).reshape(m, nb, 4)
+    out[:, :, 6:] = ((q[:, :, :16] & 15) | ((q[:, :, 16:] & 15) << 4)).astype(np.uint8)
+    return out.reshape(m, nb * 22)
+
+
+def pack_q5k(d, dmin, sc, mn, q) -> np.ndarray:
+    """d, dmin: [m, nb]; sc, mn: [m, nb, 8] in 0..63; q: [m, nb, 256] in 0..31 -> [m, nb*176].
+    Q4_K's layout with 32 bytes of fifth bits after the scales: bit e % 8 of qh[e / 8] belongs to element e
+    (crates/engine/src/forward.rs:979-1012)."""
+    m, nb = d.shape
+    q = q.astype(np.uint8).reshape(m, nb, 256)
+    out = np.empty((m, nb, 176), np.uint8)
+    out[:, :, 0:2] = d.astype(np.float16).view(np.uint8).reshape(m, nb, 2)
+    out[:, :, 2:4] = dmin.astype(np.float16).view(np.uint8).reshape(m, nb, 2)
+    out[:, :, 4:16] = pack_q4k_scales(sc, mn)
+    out[:, :, 16:48] = np.packbits((q >> 4).reshape(m, nb, 32, 8), axis=-1, bitorder="little").reshape(m, nb, 32)
+    n = (q & 15).reshape(m, nb, 4, 2, 32)
+    out[:, :, 48:] = (n[:, :, :, 0, :] | (n[:, :, :, 1, :] << 4)).reshape(m, nb, 128)
+    return out.reshape(m, nb * 176)
+
+
+def pack_q6k(d, sc, q) -> np.ndarray:
+    """d: [m, nb]; sc: [m, nb, 16] int8; q: [m, nb, 256] in -32..31 -> [m, nb*210] as the reference decodes it
+    (crates/engine/src/forward.rs:920-949): per half h of 128 elements and l < 32, ql[64h + l] holds the low nibbles of
+    elements 128h + l (low) and 128h + l + 64 (high), ql[64h + l + 32] those of 128h + l + 32 and 128h + l + 96, and
+    qh[32h + l] the two upper bits of the four, lowest pair first."""
+    m, nb = d.shape
+    u = (q.astype(np.int32) + 32).astype(np.uint8).reshape(m, nb, 2, 4, 32)      # [half][group of 32][l]
+    out = np.empty((m, nb, 210), np.uint8)
+    ql = np.empty((m, nb, 2, 2, 32), np.uint8)
+    ql[:, :, :, 0, :] = (u[:, :, :, 0, :] & 15) | ((u[:, :, :, 2, :] & 15) << 4)
+    ql[:, :, :, 1, :] = (u[:, :, :, 1, :] & 15) | ((u[:, :, :, 3, :] & 15) << 4)
+    out[:, :, 0:128] = ql.reshape(m, nb, 128)
+    qh = (u[:, :, :, 0, :] >> 4) | ((u[:, :, :, 1, :] >> 4) << 2) | ((u[:, :, :, 2, :] >> 4) << 4) | ((u[:, :, :, 3, :] >> 4) << 6)
+    out[:, :, 128:192] = qh.reshape(m, nb, 64)
+    out[:, :, 192:208] = sc.astype(np.int8).view(np.uint8).reshape(m, nb, 16)
+    out[:, :, 208:210] = d.astype(np.float16).view(np.uint8).reshape(m, nb, 2)
+    return out.reshape(m, nb * 210)
+
+
+def rand_q5_0(rng: np.random.Generator, m: int, k: int) -> np.ndarray:
+    """5-bit values uniform in 0..31; d = f16(|N(0, 0.02)| / 16)."""
+    nb = k // 32
+    return pack_q5_0(np.abs(rng.normal(0.0, 0.02, (m, nb))) / 16.0, rng.integers(0, 32, (m, nb, 32), dtype=np.uint8))
+
+
+def rand_q5k(rng: np.random.Generator, m: int, k: int, sigma: float = 0.01) -> np.ndarray:
+    nb = k // 256
+    return pack_q5k(np.abs(rng.normal(0.0, sigma, (m, nb))), np.abs(rng.normal(0.0, sigma, (m, nb))),
+                    rng.integers(0, 64, (m, nb, 8), dtype=np.uint8), rng.integers(0, 64, (m, nb, 8), dtype=np.uint8),
+                    rng.integers(0, 32, (m, nb, 256), dtype=np.uint8))
+
+
+def rand_q6k(rng: np.random.Generator, m: int, k: int, sigma: float = 0.001) -> np.ndarray:
+    """6-bit values uniform in -32..31; int8 sub-block scales uniform in -128..127; d = f16(|N(0, sigma)|)."""
+    nb = k // 256
+    return pack_q6k(np.abs(rng.normal(0.0, sigma, (m, nb))), rng.integers(-128, 128, (m, nb, 16)).astype(np.int8),
+                    rng.integers(-32, 32, (m, nb, 256)).astype(np.int8))
+
+
 def rand_weights(fmt: int, rng: np.random.Generator, m: int, k: int) -> np.ndarray:
-    return (rand_q8_0, rand_q4_0, rand_q4k)[fmt](rng, m, k)
+    return (rand_q8_0, rand_q4_0, rand_q4k, rand_q5_0, rand_q5k, rand_q6k)[fmt](rng, m, k)
 
 
 def lcg_random_f32(n: int, seed: int) -> np.ndarray:

@@ -111,8 +111,17 @@ static inline float rd_f16(const uint8_t* p) {
  * crates/kernels/src/dispatch.rs:735-747; layouts: gemv_q8_0.metal:11-14,
  * gemv_q4_0.metal:10-15, dequant.metal:7-26. */
 
-size_t ro_block_elems(int fmt) { return fmt == RO_Q4K ? 256 : 32; }
-size_t ro_block_bytes(int fmt) { return fmt == RO_Q8_0 ? 34 : (fmt == RO_Q4_0 ? 18 : 144); }
+size_t ro_block_elems(int fmt) { return (fmt == RO_Q4K || fmt == RO_Q5K || fmt == RO_Q6K) ? 256 : 32; }
+size_t ro_block_bytes(int fmt) {
+    switch (fmt) {
+        case RO_Q8_0: return 34;
+        case RO_Q4_0: return 18;
+        case RO_Q4K: return 144;
+        case RO_Q5_0: return 22;    /* crates/engine/src/forward.rs:901-902 */
+        case RO_Q5K: return 176;    /* forward.rs:980-981 */
+        default: return 210;        /* Q6_K, forward.rs:921-922 */
+    }
+}
 size_t ro_row_bytes(int fmt, int k) { return (size_t)k / ro_block_elems(fmt) * ro_block_bytes(fmt); }
 
 /* crates/engine/src/forward.rs:359-369 == dequant.metal:42-51 == gemv_q4k.metal:22-34 */
@@ -147,6 +156,75 @@ void ro_dequant_row(int fmt, const uint8_t* row, int k, float* out) {
                 uint8_t v = blk[2 + i];
                 out[b * 32 + 2 * i] = d * (float)((int)(v & 0x0F) - 8);
                 out[b * 32 + 2 * i + 1] = d * (float)((int)(v >> 4) - 8);
+            }
+        }
+    } else if (fmt == RO_Q5_0) {
+        /* crates/engine/src/forward.rs:900-919: {f16 d; u8 qh[4]; u8 qs[16]}; byte j holds elements j (low nibble) and
+         * j + 16 (high nibble); their fifth bits are bit j%8 of qh[j/8] and of qh[j/8 + 2]; value = d * (q - 16) */
+        int nb = k / 32;
+        for (int b = 0; b < nb; b++) {
+            const uint8_t* blk = row + (size_t)b * 22;
+            float d = rd_f16(blk);
+            const uint8_t* qh = blk + 2;
+            const uint8_t* qs = blk + 6;
+            for (int j = 0; j < 16; j++) {
+                int xh0 = (qh[j / 8] >> (j % 8)) & 1, xh1 = (qh[j / 8 + 2] >> (j % 8)) & 1;
+                int x0 = (qs[j] & 0x0F) | (xh0 << 4), x1 = (qs[j] >> 4) | (xh1 << 4);
+                out[b * 32 + j] = d * (float)(x0 - 16);
+                out[b * 32 + j + 16] = d * (float)(x1 - 16);
+            }
+        }
+    } else if (fmt == RO_Q6K) {
+        /* crates/engine/src/forward.rs:920-949: {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}; per half of 128 elements
+         * the scale index is half/16 + {0, 2, 4, 6} for the four groups of 32 (for every l, as the reference has it) */
+        int nb = k / 256;
+        for (int b = 0; b < nb; b++) {
+            const uint8_t* blk = row + (size_t)b * 210;
+            const uint8_t* ql = blk;
+            const uint8_t* qh = blk + 128;
+            const int8_t* sc = (const int8_t*)(blk + 192);
+            float d = rd_f16(blk + 208);
+            float* o = out + (size_t)b * 256;
+            for (int half = 0; half < 256; half += 128) {
+                int is = half / 16;
+                for (int l = 0; l < 32; l++) {
+                    int a = ql[half / 2 + l], c = ql[half / 2 + l + 32], h = qh[half / 4 + l];
+                    int q1 = ((a & 0x0F) | (((h >> 0) & 3) << 4)) - 32;
+                    int q2 = ((c & 0x0F) | (((h >> 2) & 3) << 4)) - 32;
+                    int q3 = ((a >> 4) | (((h >> 4) & 3) << 4)) - 32;
+                    int q4 = ((c >> 4) | (((h >> 6) & 3) << 4)) - 32;
+                    o[half + l] = d * (float)sc[is + 0] * (float)q1;
+                    o[half + l + 32] = d * (float)sc[is + 2] * (float)q2;
+                    o[half + l + 64] = d * (float)sc[is + 4] * (float)q3;
+                    o[half + l + 96] = d * (float)sc[is + 6] * (float)q4;
+                }
+            }
+        }
+    } else if (fmt == RO_Q5K) {
+        /* crates/engine/src/forward.rs:979-1012: {f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]}; as Q4_K plus a
+         * fifth bit per element: bit e%8 of qh[e/8] for element e */
+        int nb = k / 256;
+        for (int b = 0; b < nb; b++) {
+            const uint8_t* blk = row + (size_t)b * 176;
+            float d = rd_f16(blk), dmin = rd_f16(blk + 2);
+            const uint8_t* sc = blk + 4;
+            const uint8_t* qh = blk + 16;
+            const uint8_t* qs = blk + 48;
+            float* o = out + (size_t)b * 256;
+            for (int j = 0; j < 4; j++) {
+                uint8_t s_lo, m_lo, s_hi, m_hi;
+                ro_q4k_get_scale_min(j, sc, &s_lo, &m_lo);
+                ro_q4k_get_scale_min(j + 4, sc, &s_hi, &m_hi);
+                float d_lo = d * (float)s_lo, m_lo2 = dmin * (float)m_lo;
+                float d_hi = d * (float)s_hi, m_hi2 = dmin * (float)m_hi;
+                for (int l = 0; l < 32; l++) {
+                    uint8_t v = qs[j * 32 + l];
+                    int e_lo = j * 64 + l, e_hi = j * 64 + l + 32;
+                    int q_lo = (v & 0x0F) | (((qh[e_lo / 8] >> (e_lo % 8)) & 1) << 4);
+                    int q_hi = (v >> 4) | (((qh[e_hi / 8] >> (e_hi % 8)) & 1) << 4);
+                    o[e_lo] = d_lo * (float)q_lo - m_lo2;
+                    o[e_hi] = d_hi * (float)q_hi - m_hi2;
+                }
             }
         }
     } else {
@@ -273,7 +351,8 @@ static float row_dot_shader(int fmt, const uint8_t* row, const float* x, int k) 
 
 int ro_gemv(int fmt, int tier, const uint8_t* w, const float* x, float* y, double* y64, int m,
             int k, int batch) {
-    if (fmt < 0 || fmt > 2 || m < 0 || k <= 0 || batch <= 0) return -1;
+    if (fmt < 0 || fmt > 5 || m < 0 || k <= 0 || batch <= 0) return -1;
+    if (fmt > 2 && tier == RO_TIER_SHADER) return -1;   /* the reference has no shader for Q5_0 / Q5_K / Q6_K */
     if (k % (int)ro_block_elems(fmt)) return -1;
     size_t rb = ro_row_bytes(fmt, k);
 #pragma omp parallel

@@ -29,7 +29,7 @@ extern "C" {
 #endif
 
 /* Weight formats (block sizes: crates/kernels/src/dispatch.rs:735-747). */
-enum { RO_Q8_0 = 0, RO_Q4_0 = 1, RO_Q4K = 2 };
+enum { RO_Q8_0 = 0, RO_Q4_0 = 1, RO_Q4K = 2, RO_Q5_0 = 3, RO_Q5K = 4, RO_Q6K = 5 };
 
 /* Accumulation tiers.
  *   SHADER : per-lane block partition and f32 accumulation order of the Metal kernels,

@@ -19,11 +19,11 @@ from . import _lib
 
 OK = 0
 ERR_NO_DEVICE, ERR_BAD_ARG, ERR_BUFFER_SIZE, ERR_LAUNCH, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_ALLOC = range(1, 9)
-FMT_Q8_0, FMT_Q4_0, FMT_Q4K = 0, 1, 2
+FMT_Q8_0, FMT_Q4_0, FMT_Q4K, FMT_Q5_0, FMT_Q5K, FMT_Q6K = 0, 1, 2, 3, 4, 5
 BUF_DEVICE, BUF_HOST_VISIBLE = 0, 1
 
-BLOCK_ELEMS = {FMT_Q8_0: 32, FMT_Q4_0: 32, FMT_Q4K: 256}     # dispatch.rs:735-747
-BLOCK_BYTES = {FMT_Q8_0: 34, FMT_Q4_0: 18, FMT_Q4K: 144}
+BLOCK_ELEMS = {FMT_Q8_0: 32, FMT_Q4_0: 32, FMT_Q4K: 256, FMT_Q5_0: 32, FMT_Q5K: 256, FMT_Q6K: 256}     # dispatch.rs:735-747
+BLOCK_BYTES = {FMT_Q8_0: 34, FMT_Q4_0: 18, FMT_Q4K: 144, FMT_Q5_0: 22, FMT_Q5K: 176, FMT_Q6K: 210}
 
 
 def row_bytes(fmt: int, k: int) -> int:
@@ -226,6 +226,12 @@ _TWINS = [
     ("gemv_q4k_add_f16", "dispatch.rs:585"),
     ("gemv_q4k_add_f32res_f16", "dispatch.rs:358"),
     ("dequant_q4k_f16", "dispatch.rs:756 (input, output, n_blocks)"),
+    ("gemv_q5_0_f32in_f32out", "no twin (forward.rs:900-919 on the device): (weight, input, output, m, k)"),
+    ("gemv_q5_0_add_f32_f32in", "no twin: (weight, input, output, residual, m, k)"),
+    ("gemv_q5k_f32in_f32out", "no twin (forward.rs:979-1012 on the device)"),
+    ("gemv_q5k_add_f32_f32in", "no twin"),
+    ("gemv_q6k_f32in_f32out", "no twin (forward.rs:920-949 on the device)"),
+    ("gemv_q6k_add_f32_f32in", "no twin"),
     ("gemv_f16w_f32in", "dispatch.rs:270 (weight, input, output, m, k)"),
     ("silu_mul_f16", "dispatch.rs:15 (gate, up, out, n)"),
     ("silu_mul_f32", "dispatch.rs:35"),
@@ -369,4 +375,4 @@ def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top
 
 
 __all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "moe_scratch_bytes", "moe_layer_q4k_host", "moe_grouped_scratch_bytes", "moe_layer_q4k_bf16_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
-           "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K"] + [n for n, _ in _TWINS]
+           "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K", "FMT_Q5_0", "FMT_Q5K", "FMT_Q6K"] + [n for n, _ in _TWINS]

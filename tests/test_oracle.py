@@ -303,3 +303,76 @@ def test_golden_vectors_regression(oracle):
     y, idx, w = O.moe_layer_q4k(G["moe_router"], G["moe_gate"], G["moe_up"], G["moe_down"], G["moe_x"], h=h, ff=ff,
                                 E=E, top_k=k, renorm=False)
     assert (idx == G["moe_idx"]).all() and np.allclose(y, G["moe_y"], rtol=1e-6, atol=1e-6 * np.abs(y).max())
+
+
+def test_q5_0_q5k_q6k_decoders_follow_the_reference_formulas(oracle):
+    """The three formats the reference only dequantises on the CPU (crates/engine/src/forward.rs:900-949, 979-1012):
+    the oracle's decoders against values computed here straight from the logical fields, plus single-block cases worked
+    out by hand from the byte layouts."""
+    O = oracle
+    rng = np.random.default_rng(900)
+    m, k = 3, 512
+    # Q5_0: value = d * (q - 16)
+    d = np.abs(rng.normal(0, 0.02, (m, k // 32))).astype(np.float16)
+    q = rng.integers(0, 32, (m, k // 32, 32), dtype=np.uint8)
+    w = O.pack_q5_0(d.astype(np.float64), q)
+    want = (d.astype(np.float32)[..., None] * (q.astype(np.float32) - 16)).reshape(m, k)
+    assert np.array_equal(O.dequant_rows(O.Q5_0, w, m, k), want)
+    # Q5_K: value = d * sc * q - dmin * mn, sub-block j = elements 32j..32j+31 with scale index: pair p = j // 2 holds
+    # elements 64p..64p+31 (scale p) and 64p+32..64p+63 (scale p + 4)
+    nb = k // 256
+    d = np.abs(rng.normal(0, 0.01, (m, nb))).astype(np.float16)
+    dm = np.abs(rng.normal(0, 0.01, (m, nb))).astype(np.float16)
+    sc = rng.integers(0, 64, (m, nb, 8), dtype=np.uint8)
+    mn = rng.integers(0, 64, (m, nb, 8), dtype=np.uint8)
+    q = rng.integers(0, 32, (m, nb, 256), dtype=np.uint8)
+    w = O.pack_q5k(d.astype(np.float64), dm.astype(np.float64), sc, mn, q)
+    idx = np.array([(e // 64) + (4 if (e % 64) >= 32 else 0) for e in range(256)])
+    dl = d.astype(np.float32)[..., None] * sc[..., idx].astype(np.float32)
+    ml = dm.astype(np.float32)[..., None] * mn[..., idx].astype(np.float32)
+    want = (dl * q.astype(np.float32) - ml).reshape(m, k)
+    assert np.array_equal(O.dequant_rows(O.Q5K, w, m, k), want)
+    # Q6_K: value = d * sc[8 * half + 2 * group] * q, half = e // 128, group = (e % 128) // 32
+    d = np.abs(rng.normal(0, 0.001, (m, nb))).astype(np.float16)
+    sc = rng.integers(-128, 128, (m, nb, 16)).astype(np.int8)
+    q = rng.integers(-32, 32, (m, nb, 256)).astype(np.int8)
+    w = O.pack_q6k(d.astype(np.float64), sc, q)
+    idx = np.array([8 * (e // 128) + 2 * ((e % 128) // 32) for e in range(256)])
+    want = ((d.astype(np.float32)[..., None] * sc[..., idx].astype(np.float32)) * q.astype(np.float32)).reshape(m, k)
+    assert np.array_equal(O.dequant_rows(O.Q6K, w, m, k), want)
+    # hand-made blocks.  Q5_0, d = 1: qs all 0x10 and qh = 0x0000FFFF -> elements 0..15 = (0 | 16) - 16 = 0,
+    # elements 16..31 = (1 | 0) - 16 = -15
+    blk = np.zeros(22, np.uint8)
+    blk[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    blk[2:4] = 0xFF
+    blk[6:] = 0x10
+    assert O.dequant_rows(O.Q5_0, blk, 1, 32)[0].tolist() == [0.0] * 16 + [-15.0] * 16
+    # Q6_K, d = 1, scales = 1..16, every 6-bit value 33 (ql nibbles 1, qh = 0xAA: upper bits 2) -> q = 1: the block is
+    # the scale of each group: 1, 3, 5, 7 for the first 128 elements, 9, 11, 13, 15 for the second
+    blk = np.zeros(210, np.uint8)
+    blk[0:128] = 0x11
+    blk[128:192] = 0xAA
+    blk[192:208] = np.arange(1, 17, dtype=np.uint8)
+    blk[208:210] = np.array([1.0], np.float16).view(np.uint8)
+    got = O.dequant_rows(O.Q6K, blk, 1, 256)[0]
+    assert got.reshape(8, 32)[:, 0].tolist() == [1.0, 3.0, 5.0, 7.0, 9.0, 11.0, 13.0, 15.0] and (got.reshape(8, 32).std(1) == 0).all()
+    # Q5_K, d = 1, dmin = 0, scale bytes: sc_0 = 1, sc_5 = 2 (5 >= 4: low nibble of byte 9), qs[0] = 0xF1 and bit 0 of
+    # qh[0] set -> element 0 = 1 * (1 | 16) = 17; element 96 + 0 belongs to pair 1 high half (scale 5): qs[32] = 0x30 and
+    # bit 96 (qh[12] bit 0) set -> 2 * (3 | 16) = 38
+    blk = np.zeros(176, np.uint8)
+    blk[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    blk[4] = 1
+    blk[4 + 9] = 2
+    blk[16] = 1
+    blk[16 + 12] = 1
+    blk[48] = 0xF1
+    blk[48 + 32] = 0x30
+    got = O.dequant_rows(O.Q5K, blk, 1, 256)[0]
+    assert got[0] == 17.0 and got[96] == 38.0 and got[32] == 0.0   # element 32: high nibble 15 of qs[0] but scale 4 = 0
+    # GEMV tiers agree on the new formats
+    for fmt in (O.Q5_0, O.Q5K, O.Q6K):
+        w = O.rand_weights(fmt, rng, 5, 512)
+        x = rng.normal(0, 1, 512).astype(np.float32)
+        a, b = O.gemv(fmt, w, x, 5, 512, O.TIER_DEQUANT), O.gemv(fmt, w, x, 5, 512, O.TIER_F64)
+        assert np.allclose(a, b, rtol=2e-5, atol=1e-6 * np.abs(b).max())
+        assert np.allclose(b, O.dequant_rows(fmt, w, 5, 512).astype(np.float64) @ x.astype(np.float64), rtol=1e-6)
