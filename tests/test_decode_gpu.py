@@ -131,7 +131,7 @@ def rand_q4k_zero_mean(O, rng, rows, k):
     return O.pack_q4k(d, 7.5 * d, sc, sc, nib)
 
 
-def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False):
+def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False, weight_sigma=2e-4, emb_sigma=0.02):
     """Random-init Q4_K model on the device plus a host copy for the oracle."""
     c = dict(cfg_kw)
     L, h, E, ff, V = c["n_layers"], c["hidden"], c["n_experts"], c["ff"], c["vocab"]
@@ -145,9 +145,7 @@ def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False):
         if device_fill:
             b = ctx.new_buffer(rows * rb(k))
             if zero_mean:
-                # zero-mean weights of standard deviation ~ 1/sqrt(hidden): attention scores and logits of order one, a
-                # well-conditioned model whose greedy tokens depend on the input
-                R.fill_weights_q4k_zero_mean(ctx, b, rows * (k // 256), seed * 7919 + i, 2e-4)
+                R.fill_weights_q4k_zero_mean(ctx, b, rows * (k // 256), seed * 7919 + i, weight_sigma)
             else:
                 R.fill_weights(ctx, R.FMT_Q4K, b, rows * (k // 256), seed * 7919 + i, 0.01)
             ctx.flush()
@@ -156,7 +154,7 @@ def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False):
             host[name] = (rand_q4k_zero_mean(O, rng, rows, k) if zero_mean else O.rand_q4k(rng, rows, k)).reshape(-1)
             b = ctx.buffer_from(host[name])
         dev[name] = b
-    f32 = {"tok_emb": rng.normal(0, 0.02, (V, h)).astype(np.float32), "attn_norm": np.ones((L, h), np.float32),
+    f32 = {"tok_emb": rng.normal(0, emb_sigma, (V, h)).astype(np.float32), "attn_norm": np.ones((L, h), np.float32),
            "ffn_norm": np.ones((L, h), np.float32), "out_norm": np.ones(h, np.float32),
            "router": rng.normal(0, 0.02, (L, E, h)).astype(np.float32)}
     for name, arr in f32.items():
@@ -170,13 +168,15 @@ def build_model(ctx, R, O, cfg_kw, seed, device_fill, zero_mean=False):
     return model, ocfg, ow, host
 
 
-# A random-init decoder amplifies rounding differences from layer to layer: against the oracle the logits of a model
-# with zero-mean weights differ by 1e-6 of the logit scale after 2 layers, 7e-6 after 8 and 1e-4 (rms; 5e-4 worst
-# element) after 16 at hidden 512, whichever arithmetic the GEMVs use (integer tensor-core, dp4a or packed f32), and by
-# 3e-4 rms / 2.3e-3 worst element at the 16-layer OLMoE shape.  Each operator on its own holds the 1e-3 bar (the tests of
-# the operators and of the 2-layer model check that); for the 16-layer models the end-to-end bounds are these:
-DEEP_LOGITS_TOL = 8e-3      # worst logit, in units of max(|logit|, rms of the logits)
-DEEP_TIE_FRAC = 1e-2        # a step whose top-two margin is below this fraction of the logit spread counts as a tie
+# A random-init decoder whose layers each rewrite the hidden state amplifies rounding differences from layer to layer
+# and from position to position (through the cache): with zero-mean weights of standard deviation 1/sqrt(hidden) the
+# logits differ from the oracle's by 1e-6 of their scale after 2 layers, 1e-4 after 16 at hidden 512 and 3e-4 (worst
+# element 2e-3) at the 16-layer OLMoE shape at the first position, whichever arithmetic the GEMVs use, and the greedy
+# streams part ways after ~25 positions.  The full-shape tests therefore use a well-conditioned model: unit-variance
+# embeddings and zero-mean weights of a third of that standard deviation, so that every layer adds a correction of the
+# order of a tenth of the hidden state instead of replacing it.  Tokens still depend on the input (the stream visits
+# dozens of distinct tokens) and every kernel of the step contributes to the logits, which are held to 1e-3.
+OLMOE_WEIGHT_SIGMA, OLMOE_EMB_SIGMA = 6e-5, 1.0
 
 
 def run_parity(model, O, ocfg, ow, prompt, n_gen, tie_frac=1e-4, start_pos=0, logits_at=(), logits_tol=1e-3):
@@ -264,18 +264,17 @@ OLMOE = dict(n_layers=16, hidden=2048, n_heads=16, n_kv_heads=16, head_dim=128, 
 
 
 def test_olmoe_shaped_decode_varied_tokens_and_logits(ctx, oracle):
-    """The same 16-layer OLMoE-shaped decode with zero-mean weights (every matrix has standard deviation about
-    1/sqrt(hidden), so attention scores and logits are of order one): the greedy stream depends on its input and
-    visits many distinct tokens, which makes token identity a real check; the full logit vector is compared with
-    the oracle at five steps as well."""
+    """The same 16-layer OLMoE-shaped decode with zero-mean weights and unit-variance embeddings: the greedy stream
+    depends on its input and visits many distinct tokens, which makes token identity a real check; the full logit
+    vector is compared with the oracle at five steps as well (1e-3 of the logit scale)."""
     import runit_mac_b200 as R
     O = oracle
-    model, ocfg, ow, host = build_model(ctx, R, O, OLMOE, 2004, device_fill=True, zero_mean=True)
+    model, ocfg, ow, host = build_model(ctx, R, O, OLMOE, 2004, device_fill=True, zero_mean=True, weight_sigma=OLMOE_WEIGHT_SIGMA,
+                                         emb_sigma=OLMOE_EMB_SIGMA)
     prompt = np.random.default_rng(2004).integers(0, 50304, 128).astype(np.int32)
-    produced, ties = run_parity(model, O, ocfg, ow, prompt, 64, logits_at=(0, 1, 64, 127, 190), logits_tol=DEEP_LOGITS_TOL,
-                                tie_frac=DEEP_TIE_FRAC)
+    produced, ties = run_parity(model, O, ocfg, ow, prompt, 64, logits_at=(0, 1, 64, 127, 190))
     gen = produced[127:191]
-    assert len(produced) == 191 and ties <= 6, ties
+    assert len(produced) == 191 and ties <= 4, ties
     assert len(set(gen)) > 8, ("the generated stream is degenerate", sorted(set(gen)))
     if ties == 0:
         out = model.generate_greedy(prompt, 64)
@@ -290,11 +289,11 @@ def test_olmoe_shaped_decode_reaches_context_2048(ctx, oracle):
     start position."""
     import runit_mac_b200 as R
     O = oracle
-    model, ocfg, ow, host = build_model(ctx, R, O, OLMOE, 2005, device_fill=True, zero_mean=True)
+    model, ocfg, ow, host = build_model(ctx, R, O, OLMOE, 2005, device_fill=True, zero_mean=True, weight_sigma=OLMOE_WEIGHT_SIGMA,
+                                         emb_sigma=OLMOE_EMB_SIGMA)
     prompt = np.random.default_rng(2005).integers(0, 50304, 8).astype(np.int32)
     n_gen = 2048 - 1980 - len(prompt) + 1          # the last step runs at position 2047
-    produced, ties = run_parity(model, O, ocfg, ow, prompt, n_gen, start_pos=1980, logits_at=(0, len(prompt) + n_gen - 2),
-                                logits_tol=DEEP_LOGITS_TOL, tie_frac=DEEP_TIE_FRAC)
+    produced, ties = run_parity(model, O, ocfg, ow, prompt, n_gen, start_pos=1980, logits_at=(0, len(prompt) + n_gen - 2))
     assert len(produced) == 68 and ties <= 2, ties
     if ties == 0:
         out = model.generate_greedy(prompt, n_gen - 1, start_pos=1980, skip_prompt_logits=False)
