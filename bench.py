@@ -33,8 +33,8 @@ sys.path.insert(0, str(ROOT))
 
 HIDDEN, INTER, VOCAB, LAYERS = 3584, 18944, 152064, 28
 Q_DIM, KV_DIM = 28 * 128, 4 * 128
-FMT_Q8_0, FMT_Q4_0, FMT_Q4K = 0, 1, 2
-BLOCK = {FMT_Q8_0: (32, 34), FMT_Q4_0: (32, 18), FMT_Q4K: (256, 144)}
+FMT_Q8_0, FMT_Q4_0, FMT_Q4K, FMT_Q5_0, FMT_Q5K, FMT_Q6K = 0, 1, 2, 3, 4, 5
+BLOCK = {FMT_Q8_0: (32, 34), FMT_Q4_0: (32, 18), FMT_Q4K: (256, 144), FMT_Q5_0: (32, 22), FMT_Q5K: (256, 176), FMT_Q6K: (256, 210)}
 METRIC = "fused_dequant_gemv_hbm_gbs"
 
 
@@ -168,6 +168,74 @@ class GemvSet:
         gemv(ctx, self.lm_head, self.xn, self.logits, VOCAB, HIDDEN)
 
 
+def measure_batch8(R, ctx, torch, stream, gset, reps=5):
+    """The same GEMV set at batch 8 (the second batch size of the configuration): every matrix is streamed once for 8
+    activation rows (integer tensor-core path of gemv_imma.cu); q, k, v and gate, up are separate launches here.
+    Returns (GB/s on the algorithmic bytes, launches per token)."""
+    B = 8
+    fmt = gset.fmt
+    f4 = lambda n: ctx.new_buffer(4 * n * B)
+    xn, x, q, kk, v, gate, up, act, logits = (f4(HIDDEN), f4(HIDDEN), f4(Q_DIM), f4(KV_DIM), f4(KV_DIM), f4(INTER), f4(INTER), f4(INTER),
+                                              f4(VOCAB))
+    for b_, n, sd in ((xn, HIDDEN, 11), (q, Q_DIM, 12), (act, INTER, 13)):
+        R.fill_normal_f32(ctx, b_, n * B, sd, 1.0)
+    ctx.call("memset", x, 0, 4 * HIDDEN * B)
+    l0 = ctx.launches
+
+    def run():
+        for w in gset.w:
+            R.gemv_batched_f32(ctx, fmt, w["q"], xn, q, None, Q_DIM, HIDDEN, B)
+            R.gemv_batched_f32(ctx, fmt, w["k"], xn, kk, None, KV_DIM, HIDDEN, B)
+            R.gemv_batched_f32(ctx, fmt, w["v"], xn, v, None, KV_DIM, HIDDEN, B)
+            R.gemv_batched_f32(ctx, fmt, w["o"], q, x, x, HIDDEN, Q_DIM, B)
+            R.gemv_batched_f32(ctx, fmt, w["gate"], xn, gate, None, INTER, HIDDEN, B)
+            R.gemv_batched_f32(ctx, fmt, w["up"], xn, up, None, INTER, HIDDEN, B)
+            R.gemv_batched_f32(ctx, fmt, w["down"], act, x, x, HIDDEN, INTER, B)
+        R.gemv_batched_f32(ctx, fmt, gset.lm_head, xn, logits, None, VOCAB, HIDDEN, B)
+    run()
+    ctx.flush()
+    launches = ctx.launches - l0
+    ctx.graph_begin(); run(); g = ctx.graph_end()
+    for _ in range(2):
+        g.launch()
+    ctx.flush()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        g.launch()
+    e1.record(stream)
+    ctx.flush()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = sum(gemv_bytes(fmt, m, k, residual=r, batch=B) for _, m, k, r in LAYER_MATS) * gset.layers + gemv_bytes(fmt, VOCAB, HIDDEN, batch=B)
+    g.destroy()
+    for b_ in (xn, x, q, kk, v, gate, up, act, logits):
+        b_.free()
+    return nbytes / (ms * 1e-3) / 1e9, int(launches)
+
+
+def measure_folded(R, ctx, torch, stream, gset, reps=5):
+    """The batch-1 set recorded with the opt-in folding of consecutive GEMVs into one persistent launch."""
+    ctx.set_tuning("stream_fuse", 1)
+    try:
+        ctx.graph_begin(); gset.run(); g = ctx.graph_end()
+    finally:
+        ctx.set_tuning("stream_fuse", 0)
+    for _ in range(2):
+        g.launch()
+    ctx.flush()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        g.launch()
+    e1.record(stream)
+    ctx.flush()
+    ms = e0.elapsed_time(e1) / reps
+    out = {"gbs": pass_bytes(gset.fmt, gset.layers) / (ms * 1e-3) / 1e9, "kernel_launches_per_token": g.kernel_launches,
+           "gemv_launches_folded": g.fused_launches}
+    g.destroy()
+    return out
+
+
 def cpu_sample(fmt_list, threads, min_seconds, layers_sample=2):
     """Oracle GEMV (the engine's CPU dequant formulas + f32 dot, OpenMP over rows) on a bounded sample of
     the workload: `layers_sample` layers + lm_head per format, repeated until `min_seconds` of CPU work.
@@ -211,6 +279,9 @@ SHAPES = {
               (50304, 2048)],
     FMT_Q4_0: [(3584, 3584), (512, 3584), (18944, 3584), (3584, 18944), (152064, 3584)],
     FMT_Q8_0: [(1152, 896), (896, 896), (4864, 896), (896, 4864), (151936, 896)],
+    FMT_Q6K: [(3584, 18944), (152064, 3584)],
+    FMT_Q5K: [(3584, 3584), (152064, 3584)],
+    FMT_Q5_0: [(3584, 3584), (18944, 3584)],
 }
 
 
@@ -218,8 +289,8 @@ def run_shapes(R, ctx, torch, stream, reps=20, min_bytes=600e6):
     """Pipelined GB/s per decode shape: each shape is launched over enough distinct weight instances to exceed
     L2 several times (>= 600 MB), recorded as one command list, replayed `reps` times between CUDA events."""
     peak, _ = measured_peak()
-    names = {FMT_Q8_0: "q8_0", FMT_Q4_0: "q4_0", FMT_Q4K: "q4k"}
-    for fmt in (FMT_Q4K, FMT_Q4_0, FMT_Q8_0):
+    names = {FMT_Q8_0: "q8_0", FMT_Q4_0: "q4_0", FMT_Q4K: "q4k", FMT_Q5_0: "q5_0", FMT_Q5K: "q5k", FMT_Q6K: "q6k"}
+    for fmt in (FMT_Q4K, FMT_Q4_0, FMT_Q8_0, FMT_Q6K, FMT_Q5K, FMT_Q5_0):
         for m, k in SHAPES[fmt]:
             for batch in ((1, 8) if (m, k) in ((18944, 3584), (4864, 896)) else (1,)):
                 wbytes = m * row_bytes(fmt, k)
@@ -227,7 +298,10 @@ def run_shapes(R, ctx, torch, stream, reps=20, min_bytes=600e6):
                 ws = []
                 for i in range(n_inst):
                     b = ctx.new_buffer(wbytes)
-                    R.fill_weights(ctx, fmt, b, m * (k // BLOCK[fmt][0]), 17 + i, 0.01)
+                    if fmt <= FMT_Q4K:
+                        R.fill_weights(ctx, fmt, b, m * (k // BLOCK[fmt][0]), 17 + i, 0.01)
+                    else:   # no generator for these formats: any bytes stream at the same speed; finite scales keep the sums finite
+                        ctx.call("memset", b, 0x11, wbytes)
                     ws.append(b)
                 x, y = ctx.new_buffer(4 * k * batch), ctx.new_buffer(4 * m * batch)
                 R.fill_normal_f32(ctx, x, k * batch, 3, 1.0)
@@ -700,6 +774,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the workload (default: the full 28)")
+    ap.add_argument("--tokens-per-step", type=int, default=25,
+                    help="decode tokens (replays of the GEMV set of both formats) that make one step: 25 x 2.1 ms keeps the "
+                         "timed region of 20 steps above one second")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--tune", default="", help="key=value[,key=value] kernel tuning knobs (experiments)")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE-layer / OLMoE-decode / sharded lm_head figures")
@@ -777,9 +854,12 @@ def main():
         graphs.append(ctx.graph_end())
     launches_per_pass = [args.layers * LAUNCHES_PER_LAYER + 1] * len(sets)
 
+    TPS = max(1, args.tokens_per_step)
+
     def step():
-        for g in graphs:
-            g.launch()
+        for _ in range(TPS):
+            for g in graphs:
+                g.launch()
 
     for _ in range(args.warmup):
         step()
@@ -790,21 +870,22 @@ def main():
     if rank == 0:
         sampler.start()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    sub = [[torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for _ in range(args.steps * len(sets))]
+    sub = [[torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for _ in range(args.steps * TPS * len(sets))]
     barrier()
     ev[0].record(stream)
     for i in range(args.steps):
-        for j, g in enumerate(graphs):
-            a, b = sub[i * len(sets) + j]
-            a.record(stream)
-            g.launch()
-            b.record(stream)
+        for tok in range(TPS):
+            for j, g in enumerate(graphs):
+                a, b = sub[(i * TPS + tok) * len(sets) + j]
+                a.record(stream)
+                g.launch()
+                b.record(stream)
     ev[1].record(stream)
     barrier()
-    launches = args.steps * sum(launches_per_pass)
+    launches = args.steps * TPS * sum(launches_per_pass)
     ms = ev[0].elapsed_time(ev[1])
     fmt_ms = [0.0] * len(sets)
-    for i in range(args.steps):
+    for i in range(args.steps * TPS):
         for j in range(len(sets)):
             a, b = sub[i * len(sets) + j]
             fmt_ms[j] += a.elapsed_time(b)
@@ -812,7 +893,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
-    value = world * step_bytes * args.steps / (ms_max * 1e-3) / 1e9
+    value = world * step_bytes * TPS * args.steps / (ms_max * 1e-3) / 1e9
 
     # ── end to end through the public call with HOST buffers: x from pinned memory in, logits out ──
     hx = torch.randn(HIDDEN, dtype=torch.float32).pin_memory()
@@ -820,14 +901,14 @@ def main():
     lib, h = ctx.lib, ctx.handle
 
     def e2e_step():
-        for s_, g in zip(sets, graphs):
-            lib.runit_memcpy_h2d(h, s_.xn.ptr, hx.data_ptr(), 4 * HIDDEN)
-            g.launch()
-            lib.runit_memcpy_d2h(h, hlogits.data_ptr(), s_.logits.ptr, 4 * VOCAB)
-            ctx.flush()   # the caller reads the logits before the next token
+        for _ in range(TPS):
+            for s_, g in zip(sets, graphs):
+                lib.runit_memcpy_h2d(h, s_.xn.ptr, hx.data_ptr(), 4 * HIDDEN)
+                g.launch()
+                lib.runit_memcpy_d2h(h, hlogits.data_ptr(), s_.logits.ptr, 4 * VOCAB)
+                ctx.flush()   # the caller reads the logits before the next token
 
-    for _ in range(3):
-        e2e_step()
+    e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -838,7 +919,7 @@ def main():
     t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * step_bytes * args.steps / (float(t.item()) * 1e-3) / 1e9
+    e2e_value = world * step_bytes * TPS * args.steps / (float(t.item()) * 1e-3) / 1e9
     if rank == 0 and sampler.proc is not None:
         # a short run can end before nvidia-smi has printed its first line: keep the same load running (untimed) until
         # a few samples exist, so that the clock record is taken under load and never empty
@@ -847,6 +928,14 @@ def main():
             step()
             torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None   # sampled over both timed regions
+    # side figures on the same resident weights (outside the timed regions): batch 8, and the folded command list
+    try:
+        b8_gbs, b8_launches = measure_batch8(R, ctx, torch, stream, sets[0])
+        b8_q40, _ = measure_batch8(R, ctx, torch, stream, sets[1])
+        folded = measure_folded(R, ctx, torch, stream, sets[0])
+    except Exception as exc:
+        b8_gbs = b8_q40 = b8_launches = None
+        folded = {"error": repr(exc)[:200]}
 
     line = None
     if rank == 0:
@@ -854,7 +943,7 @@ def main():
         # dominant kernel: the Q4_K staged GEMV; its launches = the Q4_K sub-pass (8 per layer incl. one
         # tiny silu-free set: 7 GEMVs per layer + lm_head)
         q4k_launches = launches_per_pass[0]
-        q4k_ms = fmt_ms[0] / args.steps
+        q4k_ms = fmt_ms[0] / (args.steps * TPS)
         achieved = bytes_fmt[0] / (q4k_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -862,18 +951,26 @@ def main():
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "qwen2.5-7b decode GEMV set (28 layers: fused q|k|v, o, fused gate/up, down; + lm_head), "
                                    "Q4_K pass + Q4_0 pass, batch 1, f32 activations",
-                       "layers": args.layers, "bytes_per_step": step_bytes,
-                       "l2": "inputs larger than L2: every matrix is a distinct instance, %.1f GB streamed per step" % (step_bytes / 1e9)},
+                       "arithmetic": "f32 activations in, f32 accumulation and output; the 4-bit weights meet 16-bit block-fixed-point "
+                                     "copies of the activations (per 32-block, power-of-two scale) on the integer tensor cores: "
+                                     "within 2e-4 of the output scale of an exact f32 product (bar 1e-3)",
+                       "layers": args.layers, "tokens_per_step": TPS, "bytes_per_step": step_bytes * TPS,
+                       "l2": "inputs larger than L2: every matrix is a distinct instance, %.1f GB streamed per token" % (step_bytes / 1e9)},
             "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K,batch 1,integer tensor-core MMAs>", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                          "traffic": NCU_TRAFFIC_RATIO * bytes_fmt[0] / q4k_launches,
                          "traffic_note": "ncu capture of the 152064x3584 Q4_K launch (profiles/gemv_q4k_lm_head_152064x3584_ncu.md): dram read "
                                          "306.80 MB + write 4.71 MB for 307.18 MB algorithmic = x1.0141; scaled to the average launch of "
                                          "the pass (weights are streamed once by every launch, so traffic grows with the bytes)",
-                         "bytes_per_launch": bytes_fmt[0] / q4k_launches, "launches_per_step": q4k_launches,
+                         "bytes_per_launch": bytes_fmt[0] / q4k_launches, "launches_per_token": q4k_launches,
                          "avg_launch_us": q4k_ms * 1e3 / q4k_launches},
-            "per_format": {"q4k_gbs": achieved, "q4_0_gbs": bytes_fmt[1] / (fmt_ms[1] / args.steps * 1e-3) / 1e9},
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * 4 * HIDDEN, "d2h_bytes_per_step": 2 * 4 * VOCAB},
+            "per_format": {"q4k_gbs": achieved, "q4_0_gbs": bytes_fmt[1] / (fmt_ms[1] / (args.steps * TPS) * 1e-3) / 1e9},
+            "per_batch": {"1": {"q4k_gbs": achieved, "q4_0_gbs": bytes_fmt[1] / (fmt_ms[1] / (args.steps * TPS) * 1e-3) / 1e9},
+                          "8": {"q4k_gbs": b8_gbs, "q4_0_gbs": b8_q40, "frac_of_peak_q4k": (b8_gbs / peak) if b8_gbs else None,
+                                "launches_per_token": b8_launches,
+                                "note": "same weights, 8 activation rows per GEMV, weights counted once; untimed side run of 5 replays"}},
+            "folded_command_list_q4k": folded,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": TPS * 2 * 4 * HIDDEN, "d2h_bytes_per_step": TPS * 2 * 4 * VOCAB},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "extras": {},
@@ -897,6 +994,16 @@ def main():
         with lock:
             if rank == 0 and not state["printed"]:
                 line["extras"] = extras
+                if world > 1 and isinstance(extras, dict):
+                    # the paths that are partitioned over the GPUs (the headline value is N replicas, weak scaling)
+                    lh = (extras.get("lm_head_row_sharded") or {}).get("q4k") or {}
+                    ep = extras.get("olmoe_decode_q4k_expert_parallel") or {}
+                    pf = ((extras.get("moe_expert_parallel") or {}).get("qwen3_shape_prefill") or {})
+                    line["partitioned"] = {"lm_head_q4k_row_sharded_us": lh.get("us_per_call_fused_peer_stores", lh.get("us_per_call")),
+                                           "lm_head_q4k_row_sharded_gbs": lh.get("aggregate_gbs_fused", lh.get("aggregate_gbs")),
+                                           "olmoe_decode_expert_parallel_tok_s": ep.get("decode_tok_s"),
+                                           "qwen3_prefill_block_expert_parallel_ms": pf.get("ms_per_layer"),
+                                           "scaling": "strong (one workload split over the ranks)"}
                 print(json.dumps(line), flush=True)
             state["printed"] = True
 
