@@ -24,7 +24,7 @@ impl CudaContext {
         match unsafe { ffi::runit_ctx_create(device, &mut raw) } {
             ffi::RUNIT_OK => Ok(Self { raw }),
             ffi::RUNIT_ERR_NO_DEVICE => Err(KernelError::NoDevice),
-            s => Err(KernelError::LibraryLoad(format!("runit_ctx_create returned {s}"))),
+            s => Err(KernelError::LibraryLoad { path: "librunit_cuda.so".to_string(), reason: format!("runit_ctx_create returned status {s}") }),
         }
     }
 

@@ -58,3 +58,31 @@ def test_no_product_file_touches_the_oracle():
         if p.is_file() and p.suffix in (".py", ".cu", ".cuh", ".h"):
             t = p.read_text()
             assert "oracle" not in t.lower() or p.name == "__never__", p
+
+
+def test_rust_shim_covers_the_whole_boundary(tmp_path):
+    """crates/kernels-cuda (source a maintainer adds to the reference workspace; no Rust toolchain here): ffi.rs declares
+    every function of both headers, dispatch.rs wraps every operator, both are exactly what gen_bindings.py writes, and
+    KernelError has the reference's variants with their shapes (crates/kernels/src/error.rs:4-22)."""
+    import importlib.util
+    shim = ROOT / "crates" / "kernels-cuda"
+    spec = importlib.util.spec_from_file_location("gen_bindings", shim / "gen_bindings.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    ffi, disp = (shim / "src" / "ffi.rs").read_text(), (shim / "src" / "dispatch.rs").read_text()
+    fns = [f for h in gen.HEADERS for f in gen.parse(h)]
+    assert len(fns) >= 120
+    for _ret, name, _args in fns:
+        assert "pub fn %s(" % name in ffi, name
+    for name in ("gemv_q8_0_f32in_f32out", "gemv_q4k_add_f32_f32in", "fused_qkv_bias_q8_0_f32", "fused_ffn_q4_0_f32", "scale_accumulate_f16",
+                 "moe_layer_q4k", "moe_layer_q4k_ep", "gemv_allgather_f32", "gemv_q6k_f32in_f32out", "decode_attention_f32", "argmax_f16"):
+        assert "pub fn %s(ctx: &CudaContext" % name in disp, name
+    # regenerate into a scratch copy and compare
+    gen.HERE = tmp_path
+    (tmp_path / "src").mkdir()
+    gen.gen()
+    assert (tmp_path / "src" / "ffi.rs").read_text() == ffi and (tmp_path / "src" / "dispatch.rs").read_text() == disp
+    err = (shim / "src" / "error.rs").read_text()
+    for variant in ("NoDevice,", "LibraryLoad { path: String, reason: String }", "PipelineNotFound(String)",
+                    "PipelineCreate { name: String, reason: String }", "Dispatch(String)", "BufferSize { expected: usize, actual: usize }"):
+        assert variant in err, variant
