@@ -195,6 +195,15 @@ int32_t runit_fused_ffn_q4k_f32(runit_ctx_t*, const void* w_gate, const void* w_
  * NULL); weights streamed once for the whole batch; batch in 1..8. */
 int32_t runit_gemv_batched_f32(runit_ctx_t*, int32_t fmt, const void* weight, const void* input, void* output,
                                const void* residual, uint32_t m, uint32_t k, uint32_t batch);
+/* RMSNorm fused into the GEMV that consumes it: x is the un-normalised f32 vector [k], gamma f32 [k]; the matrices multiply
+ * x * rsqrt(mean(x^2) + eps) * gamma (the reference runs rms_norm_f32_f32_f32g, forward.rs:1528-1569 / dispatch.rs:177, then the
+ * GEMV, as two encoders).  Every CTA computes the scale itself, so the scale agrees with the stand-alone operator to
+ * rounding, not to the bit.  fmt: RUNIT_FMT_Q8_0 / Q4_0 / Q4K.  residual f32 [m], may be NULL. */
+int32_t runit_rms_norm_gemv_f32(runit_ctx_t*, int32_t fmt, const void* weight, const void* x, const void* gamma, float eps,
+                                void* output, const void* residual, uint32_t m, uint32_t k);
+int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t*, int32_t fmt, const void* w_q, const void* w_k, const void* w_v, const void* x,
+                                     const void* gamma, float eps, void* out_q, void* out_k, void* out_v, uint32_t q_dim,
+                                     uint32_t kv_dim, uint32_t k);
 /* Fused Q|K|V with an f32 bias (the benchmark configuration states an f32 bias); bias may be NULL. */
 int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
                                          void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,

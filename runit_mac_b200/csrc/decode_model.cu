@@ -24,6 +24,7 @@ struct runit_model {
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *logits = nullptr;
     float* attn_part = nullptr;
     uint32_t* attn_counters = nullptr;   // one ticket counter per head, zero at rest
+    uint32_t* moe_counters = nullptr;    // 1024 ticket counters of the MoE block (routing; weighted sum per row tile), zero at rest
     void* moe_scratch = nullptr;
     size_t moe_scratch_bytes = 0;
     int32_t* state = nullptr;   // [0] = token, [1] = pos, [2] = step counter
@@ -105,12 +106,12 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
         const uint8_t* wv = (const uint8_t*)m->w.wv + (size_t)l * kv_dim * rb_h;
         const uint8_t* wo = (const uint8_t*)m->w.wo + (size_t)l * h * rb_q;
         // attention block (forward.rs:1833-1896)
-        // the attention norm of layer l > 0 is produced by the previous layer's combine kernel
-        if (l == 0 && (st = launch_rms_norm(ctx, m->x, m->xn, (const float*)m->w.attn_norm, false, c.eps, h, 1))) return st;
+        // the attention RMSNorm runs inside the q|k|v launch (every CTA computes the scale of the hidden state itself)
         const void* ws[3] = {wq, wk, wv};
         void* ys[3] = {m->q, m->k, m->v};
         const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
-        if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, m->xn, h))) return st;
+        if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, m->x, h, (const float*)m->w.attn_norm + (size_t)l * h, c.eps)))
+            return st;
         __half* kcl = m->kc + (size_t)l * kv_layer;
         __half* vcl = m->vc + (size_t)l * kv_layer;
         if (hd == 128 || hd == 64) {
@@ -136,29 +137,24 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
                                             (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
                                             (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr, m->moe_scratch,
                                             m->moe_scratch_bytes, m->ep_partial, m->ep_pads, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
-                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, reinterpret_cast<uint32_t*>(m->state + 8), m->x, ffn_gamma,
+                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, m->moe_counters, m->x, ffn_gamma,
                                             c.eps)))
                 return st;
-            const float* gamma = l + 1 < c.n_layers ? (const float*)m->w.attn_norm + (size_t)(l + 1) * h
-                                                    : (with_logits ? (const float*)m->w.out_norm : nullptr);
-            if (gamma && (st = launch_rms_norm(ctx, m->x, m->xn, gamma, false, c.eps, h, 1))) return st;
             continue;
         }
         if ((st = moe_layer_q4k_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
                                      (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
                                      (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr,
                                      m->moe_scratch, m->moe_scratch_bytes, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
-                                     // followed by the next operator's RMSNorm (next layer's attention norm, or the output norm
-                                     // before lm_head)
-                                     l + 1 < c.n_layers ? (const float*)m->w.attn_norm + (size_t)(l + 1) * h
-                                                        : (with_logits ? (const float*)m->w.out_norm : nullptr),
-                                     m->xn, c.eps, reinterpret_cast<uint32_t*>(m->state + 8),   // state[8]: ticket counter, zero at rest
+                                     // (the next operator's RMSNorm runs inside that operator's own launch)
+                                     nullptr, nullptr, c.eps, m->moe_counters,
                                      m->x, ffn_gamma, c.eps)))
             return st;
     }
     int32_t* argmax_out = m->state + 3;
     if (with_logits) {
-        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->xn, m->logits, nullptr, c.vocab, h))) return st;
+        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h,
+                             (const float*)m->w.out_norm, c.eps))) return st;
         if ((st = launch_argmax(ctx, m->logits, false, argmax_out, c.vocab))) return st;
     }
     runit_launch_chain(ctx, advance_kernel, dim3(1), dim3(32), m->state, argmax_out, m->out_tokens, m->out_cap, with_logits ? 1 : 0);
@@ -248,6 +244,7 @@ static int32_t model_create_impl(runit_ctx_t* ctx, const runit_model_cfg* cfg, c
     A(&m->moe_scratch, m->moe_scratch_bytes);
     A((void**)&m->attn_counters, (size_t)c.n_heads * 4);
     A((void**)&m->ep_epoch, 64);
+    A((void**)&m->moe_counters, 4096);
     A((void**)&m->state, 64); A((void**)&m->forced, (size_t)m->forced_cap * 4); A((void**)&m->out_tokens, (size_t)m->out_cap * 4);
     if (st == RUNIT_OK) {
         cudaMemsetAsync(m->kc, 0, kv_elems * 2, ctx->stream);
@@ -255,6 +252,7 @@ static int32_t model_create_impl(runit_ctx_t* ctx, const runit_model_cfg* cfg, c
         cudaMemsetAsync(m->state, 0, 64, ctx->stream);
         cudaMemsetAsync(m->ep_epoch, 0, 64, ctx->stream);   // once: the epoch only ever grows afterwards
         cudaMemsetAsync(m->attn_counters, 0, (size_t)c.n_heads * 4, ctx->stream);
+        cudaMemsetAsync(m->moe_counters, 0, 4096, ctx->stream);
         cudaMemsetAsync(m->forced, 0xFF, (size_t)m->forced_cap * 4, ctx->stream);   // nothing forced
         // one eager step configures every kernel (shared-memory attributes, tensor maps) before capture
         st = issue_step(m, true, 0);
@@ -356,13 +354,15 @@ int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uin
 void* runit_model_logits(runit_model_t* m) { return m ? (void*)m->logits : nullptr; }
 uint64_t runit_model_launches_per_token(runit_model_t* m) {
     if (!m) return 0;
-    // embed, first norm + per layer (qkv, rope+kv, attention, o-proj, norm, 4 MoE + next norm) + lm_head, argmax, advance;
-    // expert-parallel: the MoE block is router + routing, gate/up, down, partial sums, barrier, sum (6) + next norm
-    const uint64_t moe = m->ep_world > 1 ? 7 : 5;
+    // embed + per layer (q|k|v with its RMSNorm, [rope +] attention, o-proj, [norm,] MoE block) + lm_head with its RMSNorm, argmax,
+    // advance.  MoE block at hidden 1024 / 2048 / 4096: norm + router + routing, gate/up, down + weighted sum (3); else
+    // norm, router, routing, gate/up, down, weighted sum.  Expert-parallel: router + routing, gate/up, down, partial sums,
+    // barrier, sum (6).
+    const bool fused = m->cfg.hidden == 1024 || m->cfg.hidden == 2048 || m->cfg.hidden == 4096;
+    const uint64_t moe = m->ep_world > 1 ? 6 : (fused ? 3 : 5);
     const uint64_t attn = (m->cfg.head_dim == 128 || m->cfg.head_dim == 64) ? 1 : 2;   // rope + cache update fused into the attention launch
-    // the RMSNorm before the MoE block runs inside its routing launch when the hidden size is 1024 / 2048 / 4096
-    const uint64_t norm2 = (m->cfg.hidden == 1024 || m->cfg.hidden == 2048 || m->cfg.hidden == 4096) ? 0 : 1;
-    return 2 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + norm2 + moe) + 3;
+    const uint64_t norm2 = fused ? 0 : 1;
+    return 1 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + norm2 + moe) + 3;
 }
 
 }  // extern "C"

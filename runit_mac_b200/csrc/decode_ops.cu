@@ -178,7 +178,11 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
     const uint32_t kvh = head / (heads / kv_heads);
     const size_t qbase = ((size_t)batch * heads + head) * HD;
     const size_t kvbase = ((size_t)batch * kv_heads + kvh) * kv_head_stride * HD;
-    const uint32_t chunk = ((kv_len + nsplit - 1) / nsplit + 31) / 32 * 32;
+    // a split covers at least 128 positions (one group of 32 per warp): short contexts use few splits, and with a ticket
+    // counter the splits beyond the context leave at once (without it they file an empty partial for the combine launch)
+    const uint32_t chunk = max(128u, ((kv_len + nsplit - 1) / nsplit + 31) / 32 * 32);
+    const uint32_t live = max(1u, (kv_len + chunk - 1) / chunk);
+    if (counters && split >= live && split > 0) return;
     const uint32_t beg = split * chunk, end = min(kv_len, beg + chunk);
     bool roped = false;
     if constexpr (std::is_same<TQ, float>::value && std::is_same<TKV, __half>::value) {
@@ -186,23 +190,24 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
             roped = true;
             const uint32_t d = threadIdx.x, half = HD / 2, pos = kv_len - 1;
             if (d < half) {
+                // every load is requested before the trigonometry needs the position
+                const float* kp = rope.k_raw + (size_t)kvh * HD;
+                const float* vp = rope.v_raw + (size_t)kvh * HD;
+                const float a = Q[qbase + d], b = Q[qbase + d + half];
+                const float ka = kp[d], kb = kp[d + half], va = vp[d], vb = vp[d + half];
                 const float freq = 1.0f / powf(rope.theta, (float)(2 * d) / (float)HD);
                 const float angle = (float)pos * freq;
                 const float c = cosf(angle), sn = sinf(angle);
-                const float a = Q[qbase + d], b = Q[qbase + d + half];
                 qs[d] = a * c - b * sn;
                 qs[d + half] = a * sn + b * c;
                 if (pos >= beg && pos < end && pos < kv_head_stride) {
                     // several query heads may share this kv head: they store the same bits
-                    const float* kp = rope.k_raw + (size_t)kvh * HD;
-                    const float* vp = rope.v_raw + (size_t)kvh * HD;
-                    const float ka = kp[d], kb = kp[d + half];
                     __half* kc = const_cast<__half*>(K) + kvbase + (size_t)pos * HD;
                     __half* vc = const_cast<__half*>(V) + kvbase + (size_t)pos * HD;
                     kc[d] = __float2half_rn(ka * c - kb * sn);
                     kc[d + half] = __float2half_rn(ka * sn + kb * c);
-                    vc[d] = __float2half_rn(vp[d]);
-                    vc[d + half] = __float2half_rn(vp[d + half]);
+                    vc[d] = __float2half_rn(va);
+                    vc[d + half] = __float2half_rn(vb);
                 }
             }
         }
@@ -210,9 +215,17 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
     if (!roped)
         for (uint32_t d = threadIdx.x; d < HD; d += 128) qs[d] = ldf(Q, qbase + d);
     __syncthreads();   // also orders this CTA's cache stores before its own loads of that row
-    float m = -INFINITY, l = 0.f, o[DPL];
+    // value phase: lane <-> (row parity, 16-byte chunk of the row) where the chunks of a row divide the warp: the rows of a
+    // group are fetched by coalesced 16-byte loads that are all in flight together; else lane <-> DPL output dims
+    constexpr int CH = HD / 8;                    // 8-element chunks per row
+    constexpr bool WIDE = (32 % CH) == 0;
+    constexpr int RPI = WIDE ? 32 / CH : 1;       // rows per warp-wide load
+    const uint32_t vr_row = lane / CH, vr_col = lane % CH;
+    float m = -INFINITY, l = 0.f, o[DPL], o8[8];
 #pragma unroll
     for (int i = 0; i < DPL; i++) o[i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) o8[i] = 0.f;
     for (uint32_t g = beg + 32 * warp; g < end; g += 128) {
         const uint32_t p = g + lane;
         float score = -INFINITY;
@@ -236,9 +249,27 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
         const float resc = expf(m - m_new);      // exp(-inf) = 0 on the first group
         const float pe = (p < end) ? expf(score - m_new) : 0.f;
         l = l * resc + warp_sum(pe);
+        const uint32_t cnt = min(32u, end - g);
+        if constexpr (WIDE) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) o8[i] *= resc;
+            float vv[32 / RPI][8];
+#pragma unroll
+            for (int t = 0; t < 32 / RPI; t++) {
+                const uint32_t j = t * RPI + vr_row;      // rows past the end read row g and get weight 0 (pe is 0 there)
+                load8(V + kvbase + (size_t)(g + (j < cnt ? j : 0)) * HD + vr_col * 8, vv[t]);
+            }
+#pragma unroll
+            for (int t = 0; t < 32 / RPI; t++) {
+                const float pj = __shfl_sync(0xffffffffu, pe, t * RPI + vr_row);
+#pragma unroll
+                for (int i = 0; i < 8; i++) o8[i] = fmaf(pj, vv[t][i], o8[i]);
+            }
+            m = m_new;
+            continue;
+        }
 #pragma unroll
         for (int i = 0; i < DPL; i++) o[i] *= resc;
-        const uint32_t cnt = min(32u, end - g);
         // eight value rows are loaded before they are used (positions past the end read row g and get weight 0:
         // pe is 0 there), the accumulation order stays j ascending
         for (uint32_t j0 = 0; j0 < cnt; j0 += 8) {
@@ -263,8 +294,20 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
     }
     // merge the four warps in warp order
     if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+    if constexpr (WIDE) {
+        // add the row parities (ascending), then the lanes of parity 0 file their chunk
 #pragma unroll
-    for (int i = 0; i < DPL; i++) sm_o[warp][lane * DPL + i] = o[i];
+        for (int off = CH; off < 32; off <<= 1)
+#pragma unroll
+            for (int i = 0; i < 8; i++) o8[i] += __shfl_down_sync(0xffffffffu, o8[i], off);
+        if (vr_row == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) sm_o[warp][vr_col * 8 + i] = o8[i];
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL; i++) sm_o[warp][lane * DPL + i] = o[i];
+    }
     __syncthreads();
     if (warp == 0) {
         float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
@@ -278,7 +321,7 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
 #pragma unroll
             for (int i = 0; i < DPL; i++) acc[i] += sm_o[w][lane * DPL + i] * f;
         }
-        if (nsplit == 1) {
+        if (nsplit == 1 || (counters && live == 1)) {
             const float inv = Lt > 0.f ? 1.0f / Lt : 0.f;
 #pragma unroll
             for (int i = 0; i < DPL; i++) O[qbase + lane * DPL + i] = (TO)(acc[i] * inv);
@@ -291,12 +334,12 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
     }
     // With a ticket counter per (batch, head) the CTA that finishes last merges the partials itself (same order and
     // arithmetic as decode_attn_combine_kernel) and puts the counter back to zero: no second launch.
-    if (nsplit > 1 && counters) {
+    if (nsplit > 1 && counters && live > 1) {
         __shared__ uint32_t s_last;
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();
-            s_last = atomicAdd(&counters[batch * heads + head], 1u) == nsplit - 1;
+            s_last = atomicAdd(&counters[batch * heads + head], 1u) == live - 1;
         }
         __syncthreads();
         if (s_last) {
@@ -304,14 +347,33 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const TQ* __restrict__
             const uint32_t d = threadIdx.x;
             if (d < HD) {
                 const float* pp = part + ((size_t)batch * heads + head) * nsplit * (HD + 2);
-                float Mx = -INFINITY;
-                for (uint32_t sp = 0; sp < nsplit; sp++) Mx = fmaxf(Mx, pp[sp * (HD + 2)]);
-                float L = 0.f, a = 0.f;
-                for (uint32_t sp = 0; sp < nsplit; sp++) {
-                    const float ms = pp[sp * (HD + 2)];
-                    const float f = (ms == -INFINITY) ? 0.f : expf(ms - Mx);
-                    L += pp[sp * (HD + 2) + 1] * f;
-                    a += pp[sp * (HD + 2) + 2 + d] * f;
+                float Mx = -INFINITY, L = 0.f, a = 0.f;
+                if (live <= 8) {
+                    // all partials requested together
+                    float ms[8], ls[8], as[8];
+#pragma unroll
+                    for (uint32_t sp = 0; sp < 8; sp++) {
+                        const bool on = sp < live;
+                        ms[sp] = on ? __ldcg(pp + sp * (HD + 2)) : -INFINITY;
+                        ls[sp] = on ? __ldcg(pp + sp * (HD + 2) + 1) : 0.f;
+                        as[sp] = on ? __ldcg(pp + sp * (HD + 2) + 2 + d) : 0.f;
+                    }
+#pragma unroll
+                    for (uint32_t sp = 0; sp < 8; sp++) Mx = fmaxf(Mx, ms[sp]);
+#pragma unroll
+                    for (uint32_t sp = 0; sp < 8; sp++) {
+                        const float f = (ms[sp] == -INFINITY) ? 0.f : expf(ms[sp] - Mx);
+                        L += ls[sp] * f;
+                        a += as[sp] * f;
+                    }
+                } else {
+                    for (uint32_t sp = 0; sp < live; sp++) Mx = fmaxf(Mx, pp[sp * (HD + 2)]);
+                    for (uint32_t sp = 0; sp < live; sp++) {
+                        const float ms = pp[sp * (HD + 2)];
+                        const float f = (ms == -INFINITY) ? 0.f : expf(ms - Mx);
+                        L += pp[sp * (HD + 2) + 1] * f;
+                        a += pp[sp * (HD + 2) + 2 + d] * f;
+                    }
                 }
                 O[qbase + d] = (TO)(L > 0.f ? a / L : 0.f);
             }

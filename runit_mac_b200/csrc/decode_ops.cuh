@@ -28,15 +28,19 @@ int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* resu
 
 // gemv.cu: one fused-dequant GEMV with up to three row segments sharing the input (Q|K|V) — any format.
 int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const void* const* w, void* const* y,
-                      const uint32_t* rows, const void* x, uint32_t k);
+                      const uint32_t* rows, const void* x, uint32_t k,
+                      // norm_gamma != nullptr: x is the un-normalised vector; RMSNorm(x) * gamma is what the matrices multiply
+                      const float* norm_gamma = nullptr, float norm_eps = 0.f);
 int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
-                   uint32_t m, uint32_t k);
+                   uint32_t m, uint32_t k, const float* norm_gamma = nullptr, float norm_eps = 0.f);
 // moe.cu
 int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,
                            size_t scratch_bytes, uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
                            const float* next_gamma, float* next_xn, float next_eps,    // next_*: also RMSNorm the result
-                           uint32_t* route_counter,    // zeroed word: router and routing in one launch (T == 1)
+                           // 1024 zeroed words (zero again after every launch): with T == 1, router and routing run in one
+                           // launch and the weighted sum of the experts runs inside the down-projection launch
+                           uint32_t* route_counter,
                            // pre_gamma != nullptr: the block first writes RMSNorm(pre_x) into x (inside the routing launch when T == 1)
                            const float* pre_x, const float* pre_gamma, float pre_eps);
 size_t moe_scratch_bytes_impl(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k);

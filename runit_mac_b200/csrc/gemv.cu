@@ -30,6 +30,15 @@ struct GemvCall {
     // fused all-gather: the same output slice in the memory of the other GPUs
     float* peer_y[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint32_t n_peer = 0;
+    // grouped, one token: weighted sum of the slots (+ residual) by the last tile of every row tile
+    const float* cmb_w = nullptr;
+    const float* cmb_res = nullptr;
+    float* cmb_out = nullptr;
+    uint32_t* cmb_cnt = nullptr;
+    bool late_trigger = false, grp_early = false;   // see GemvArgs
+    // RMSNorm prologue: x is the un-normalised vector, gamma f32 [k]
+    const float* norm_gamma = nullptr;
+    float norm_eps = 0.f;
 };
 
 static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
@@ -89,6 +98,17 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
         a.grp_lo = c.grp_lo;
         a.grp_cnt = c.grp_experts;
         RUNIT_REQUIRE(ctx, (uint64_t)tiles * c.grp_slots < (1ull << 31), "%s: too many grouped tiles", nm);
+        if (c.cmb_out) {
+            RUNIT_REQUIRE(ctx, c.cmb_w && c.cmb_cnt && !c.dual && !c.out_f16 && !c.x_f16 && c.grp_slots <= 32,
+                          "%s: the fused weighted sum takes f32 slots of one token", nm);
+            a.cmb_w = c.cmb_w;
+            a.cmb_res = c.cmb_res;
+            a.cmb_out = c.cmb_out;
+            a.cmb_cnt = c.cmb_cnt;
+            a.cmb_slots = c.grp_slots;
+        }
+        a.late_trigger = c.late_trigger ? 1 : 0;
+        a.grp_early = c.grp_early ? 1 : 0;
         tiles *= c.grp_slots;
         total_rows *= c.grp_slots;
     }
@@ -108,6 +128,12 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
             a.peer_y[p] = c.peer_y[p];
         }
         a.n_peer = c.n_peer;
+    }
+    if (c.norm_gamma) {
+        RUNIT_REQUIRE(ctx, c.batch == 1 && !c.x_f16 && !c.grp_expert && runit_aligned(c.norm_gamma, 4),
+                      "%s: the RMSNorm prologue takes one f32 input vector", nm);
+        a.norm_gamma = c.norm_gamma;
+        a.norm_eps = c.norm_eps;
     }
     a.status = ctx->d_status;
     a.n_tiles = tiles;
@@ -139,8 +165,11 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
 
 // Plain single-matrix call shared by the twins below.
 static int32_t gemv1(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res,
-                     uint32_t m, uint32_t k, bool x_f16, bool out_f16, int res_kind) {
+                     uint32_t m, uint32_t k, bool x_f16, bool out_f16, int res_kind, const float* norm_gamma = nullptr,
+                     float norm_eps = 0.f) {
     GemvCall c;
+    c.norm_gamma = norm_gamma;
+    c.norm_eps = norm_eps;
     c.name = name;
     c.fmt = fmt;
     c.w[0] = w;
@@ -194,8 +223,15 @@ static int32_t fused_ffn(runit_ctx* ctx, const char* name, int fmt, const void* 
 // With w2 != nullptr the launch computes silu(w.x) * (w2.x) (gate/up fusion).
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
-                     uint32_t n_slots, int32_t expert_lo) {
+                     uint32_t n_slots, int32_t expert_lo, const float* cmb_w, const float* cmb_res, float* cmb_out,
+                     uint32_t* cmb_cnt, int order) {
     GemvCall c;
+    c.late_trigger = order == 1;
+    c.grp_early = order == 2;
+    c.cmb_w = cmb_w;
+    c.cmb_res = cmb_res;
+    c.cmb_out = cmb_out;
+    c.cmb_cnt = cmb_cnt;
     c.name = name;
     c.fmt = fmt;
     c.w[0] = w;
@@ -214,8 +250,10 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
 }
 
 int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const void* const* w, void* const* y,
-                      const uint32_t* rows, const void* x, uint32_t k) {
+                      const uint32_t* rows, const void* x, uint32_t k, const float* norm_gamma, float norm_eps) {
     GemvCall c;
+    c.norm_gamma = norm_gamma;
+    c.norm_eps = norm_eps;
     c.name = name;
     c.fmt = fmt;
     c.nseg = nseg;
@@ -230,8 +268,8 @@ int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const
 }
 
 int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
-                   uint32_t m, uint32_t k) {
-    return gemv1(ctx, name, fmt, w, x, y, res_f32, m, k, false, false, res_f32 ? RES_F32 : RES_NONE);
+                   uint32_t m, uint32_t k, const float* norm_gamma, float norm_eps) {
+    return gemv1(ctx, name, fmt, w, x, y, res_f32, m, k, false, false, res_f32 ? RES_F32 : RES_NONE, norm_gamma, norm_eps);
 }
 
 }  // namespace runit
@@ -321,6 +359,23 @@ int32_t runit_fused_qkv_q4k_f32(runit_ctx_t* ctx, const void* w_q, const void* w
 int32_t runit_fused_ffn_q4k_f32(runit_ctx_t* ctx, const void* w_gate, const void* w_up, const void* x, void* act_out,
                                 uint32_t ff_dim, uint32_t k) {
     return fused_ffn(ctx, "fused_ffn_q4k_f32", RUNIT_FMT_Q4K, w_gate, w_up, x, act_out, ff_dim, k);
+}
+
+int32_t runit_rms_norm_gemv_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* x, const void* gamma, float eps,
+                                void* output, const void* residual, uint32_t m, uint32_t k) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, gamma && m > 0, "rms_norm_gemv_f32: null gamma or m == 0");
+    return gemv_plain(ctx, "rms_norm_gemv_f32", fmt, weight, x, output, residual, m, k, (const float*)gamma, eps);
+}
+int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_q, const void* w_k, const void* w_v, const void* x,
+                                     const void* gamma, float eps, void* out_q, void* out_k, void* out_v, uint32_t q_dim,
+                                     uint32_t kv_dim, uint32_t k) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, gamma, "rms_norm_fused_qkv_f32: null gamma");
+    const void* ws[3] = {w_q, w_k, w_v};
+    void* ys[3] = {out_q, out_k, out_v};
+    const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
+    return gemv_segments(ctx, "rms_norm_fused_qkv_f32", fmt, 3, ws, ys, rows, x, k, (const float*)gamma, eps);
 }
 
 int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* input, void* output,

@@ -84,6 +84,26 @@ struct GemvArgs {
     // stored at the same index of these vectors, which live in the memory of the other GPUs (plain peer stores).
     float* peer_y[7];
     uint32_t n_peer;
+    // RMSNorm prologue (batch 1, f32 input), active when norm_gamma != nullptr: x is the un-normalised hidden state and the
+    // kernel multiplies with x * rsqrt(mean(x^2) + eps) * gamma (crates/kernels/shaders/norm.metal:95-154 feeding the
+    // GEMV, crates/engine/src/forward.rs:1528-1569).  Every CTA computes the scale itself from the k inputs.
+    const float* norm_gamma;
+    float norm_eps;
+    // Grouped mode with the weighted sum of the slots fused in (one token), active when cmb_out != nullptr: after storing
+    // its rows of y[slot], every tile takes a ticket on cmb_cnt[row tile]; the tile that takes the last of the cmb_slots
+    // tickets writes cmb_out[r] = cmb_res[r] + sum_i cmb_w[i] * y[i][r] (i ascending, as moe_combine_kernel does) for the
+    // rows of the tile and puts the counter back to zero.
+    // Dependent-launch ordering for two grouped launches in a row (gate/up, then down) whose expert ids were written by the
+    // kernel BEFORE the first one.  late_trigger: this kernel lets its successor start only after its own dependency wait
+    // returned, i.e. once everything older than itself has completed.  grp_early: the predecessor was launched with
+    // late_trigger, so the expert ids are final when this kernel starts: it requests its first weight stages before
+    // its own wait (the activations come from the predecessor and follow the wait).
+    int32_t late_trigger, grp_early;
+    const float* cmb_w;
+    const float* cmb_res;
+    float* cmb_out;
+    uint32_t* cmb_cnt;
+    uint32_t cmb_slots;
 };
 
 // Tensor maps of the weight matrices (bulk-load path): one per segment, plus the second matrix of
@@ -306,6 +326,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float red[kKS][kRT][B];
     __shared__ __align__(8) uint64_t mbar[kKS][4];
+    __shared__ float s_norm[kKS + 1];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
@@ -313,8 +334,12 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     const uint32_t ring_u32 = smem_u32(ring);
     const uint32_t bar0 = smem_u32(&mbar[warp][0]);
 
-    grid_launch_dependents();                   // let the next kernel of the stream begin its own prologue
-    if (LD != 1 || a.grp_expert != nullptr) grid_dependency_wait();
+    if (!a.late_trigger) grid_launch_dependents();   // let the next kernel of the stream begin its own prologue
+    const bool early_weights = LD == 1 && (a.grp_expert == nullptr || a.grp_early);
+    if (!early_weights) {
+        grid_dependency_wait();
+        if (a.late_trigger) grid_launch_dependents();
+    }
     constexpr int TPC = kKS / KSL;              // tiles per CTA
     // With csplit > 1 (host guarantees KSL == 4) a cluster of csplit CTAs shares one tile: CTA c of the
     // cluster and warp w take K-slice w*csplit + c of 4*csplit slices; partial sums meet in CTA 0 through
@@ -437,6 +462,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
 
     // Wait until stage `it` has landed for this lane (`pending` = cp.async groups that may stay open).
     bool timed_out = false;
+    float norm_r = 1.f;      // RMSNorm prologue: scale of the input vector (set after the dependency wait)
     auto wait_stage = [&](int it, auto pending) {
         if (LD == 1) {
             // after one failed wait the warp stops waiting (its results are reported as invalid)
@@ -469,6 +495,14 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
             }
         }
         __syncwarp();   // in-place: every lane has read its inputs before anyone overwrites them
+        if constexpr (B == 1 && !XF16) {
+            if (a.norm_gamma != nullptr) {
+                const uint32_t e0 = (slice + n_slices * it) * T::UE + lane * EPL;
+#pragma unroll
+                for (int i = 0; i < EPL; i++)
+                    if (e0 + i < a.k) v[0][i] = v[0][i] * norm_r * a.norm_gamma[e0 + i];
+            }
+        }
         if (MATH == 1) {
             prep_int_block<EPL, T::UE / 32, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(slot + L::XP_OFF, v[0], lane);
             return;
@@ -522,15 +556,36 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
     // draining.  Weights do not depend on the predecessor, so (outside grouped mode, where the expert id does)
     // their first stages are requested before the dependency wait; activations, residual and every store
     // come after it.
-    if (LD == 1 && a.grp_expert == nullptr) {
+    if (early_weights) {
 #pragma unroll
         for (int s = 0; s < S; s++) issue(s, 1);
         grid_dependency_wait();
+        if (a.late_trigger) grid_launch_dependents();
 #pragma unroll
         for (int s = 0; s < S; s++) issue(s, 2);
     } else {
 #pragma unroll
         for (int s = 0; s < S; s++) issue(s);
+    }
+    // RMSNorm prologue: the scale of the whole input vector, computed by this CTA while its first stages are in flight
+    // (summation order of the stand-alone kernel's warps differs: the scale agrees to rounding)
+    if constexpr (B == 1 && !XF16) {
+        if (a.norm_gamma != nullptr) {
+            const float* xg = reinterpret_cast<const float*>(xbase);
+            float sq = 0.f;
+            for (uint32_t i = threadIdx.x; i < a.k; i += kNT) {
+                const float t = xg[i];
+                sq = fmaf(t, t, sq);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) s_norm[warp] = sq;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int i = 0; i < kKS; i++) tot += s_norm[i];
+            norm_r = rsqrtf(tot / (float)a.k + a.norm_eps);
+        }
     }
 
     for (int it = 0; it < n_it; it++) {
@@ -639,6 +694,31 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                 for (uint32_t p = 0; p < a.n_peer; p++) a.peer_y[p][o] = v;
             }
         }
+        if constexpr (B == 1 && !DUAL && !XF16) {
+            if (a.cmb_out != nullptr && tile_ok) {
+                const uint32_t t = tile % a.grp_tiles;   // row tile, shared by the slots
+                __threadfence();                         // this lane's row of y[slot] is visible before the ticket is
+                __syncwarp();
+                uint32_t ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&a.cmb_cnt[t], 1u);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == a.cmb_slots - 1) {
+                    __threadfence();                     // the other slots' rows, published before their tickets
+                    if (lane == 0) a.cmb_cnt[t] = 0;     // at rest again for the next launch
+                    const uint32_t r = t * RPT + lane;
+                    if (r < sg.rows) {
+                        const float* y0 = reinterpret_cast<const float*>(a.seg[0].y);
+                        float acc = 0.f;
+                        for (uint32_t i = 0; i < a.cmb_slots; i++) {
+                            const int32_t eid = a.grp_expert[i] - a.grp_lo;
+                            if (eid >= 0 && (uint32_t)eid < a.grp_cnt)
+                                acc = fmaf(a.cmb_w[i], __ldcg(y0 + (size_t)i * a.ldy + r), acc);
+                        }
+                        a.cmb_out[r] = (a.cmb_res ? a.cmb_res[r] : 0.f) + acc;
+                    }
+                }
+            }
+        }
     }
 }
 
@@ -664,6 +744,17 @@ __global__ void __launch_bounds__(128) gemv_simple_kernel(const GemvArgs a, int 
     const GemvSeg sg = a.seg[si];
     const uint32_t row = grow - base;
     const int nmat = a.dual ? 2 : 1;
+    float norm_r = 1.f;
+    if (!XF16 && a.norm_gamma != nullptr) {   // RMSNorm prologue (batch 1): every warp computes the scale itself
+        float sq = 0.f;
+        for (uint32_t i = lane; i < a.k; i += 32) {
+            const float t = reinterpret_cast<const float*>(a.x)[i];
+            sq = fmaf(t, t, sq);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        norm_r = rsqrtf(sq / (float)a.k + a.norm_eps);
+    }
     for (int b = 0; b < batch; b++) {
         float res2[2] = {0.f, 0.f};
         for (int mi = 0; mi < nmat; mi++) {
@@ -672,8 +763,9 @@ __global__ void __launch_bounds__(128) gemv_simple_kernel(const GemvArgs a, int 
             for (uint32_t blk = lane; blk < a.nb; blk += 32) {
                 auto X = [&](uint32_t i) -> float {
                     const size_t o = (size_t)b * a.k + i;
-                    return XF16 ? __half2float(reinterpret_cast<const __half*>(a.x)[o])
-                                : reinterpret_cast<const float*>(a.x)[o];
+                    if (XF16) return __half2float(reinterpret_cast<const __half*>(a.x)[o]);
+                    const float xv = reinterpret_cast<const float*>(a.x)[o];
+                    return a.norm_gamma != nullptr ? xv * norm_r * a.norm_gamma[i] : xv;
                 };
                 if (FMT == RUNIT_FMT_Q8_0) {
                     const uint8_t* p = rp + (size_t)blk * 34;

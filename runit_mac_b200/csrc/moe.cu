@@ -157,18 +157,32 @@ __global__ void __launch_bounds__(256) route_fused_kernel(const float* __restric
                                                            float* logits, uint32_t E, uint32_t K, uint32_t k, int renorm,
                                                            int32_t* __restrict__ out_idx, float* __restrict__ out_w, uint32_t* counter,
                                                            const float* __restrict__ gamma, float eps, float* __restrict__ xn_out) {
-    grid_dependency_wait();
-    grid_launch_dependents();
     __shared__ uint32_t s_last;
     __shared__ __align__(16) float xs[KPL * 32];
     __shared__ float part[8];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t e = blockIdx.x * 8 + warp;
+    // the router row and gamma do not depend on the previous kernel of the chain: they are requested before the wait
+    float4 wv[KPL / 4];
+    float gv[KPL / 8];
+    if (e < E) {
+        const float4* wrow = reinterpret_cast<const float4*>(w + (size_t)e * K);
+#pragma unroll
+        for (int i = 0; i < KPL / 4; i++) wv[i] = wrow[lane + 32 * i];
+    }
     if (gamma) {
+#pragma unroll
+        for (int j = 0; j < KPL / 8; j++) gv[j] = gamma[threadIdx.x + 256 * j];
+    }
+    grid_dependency_wait();
+    grid_launch_dependents();
+    if (gamma) {
+        float xv[KPL / 8];
+#pragma unroll
+        for (int j = 0; j < KPL / 8; j++) xv[j] = x[threadIdx.x + 256 * j];
         float sq = 0.f;
-        for (uint32_t i = threadIdx.x; i < K; i += 256) {
-            const float v = x[i];
-            sq = fmaf(v, v, sq);
-        }
+#pragma unroll
+        for (int j = 0; j < KPL / 8; j++) sq = fmaf(xv[j], xv[j], sq);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         if (lane == 0) part[warp] = sq;
@@ -177,23 +191,22 @@ __global__ void __launch_bounds__(256) route_fused_kernel(const float* __restric
 #pragma unroll
         for (int i = 0; i < 8; i++) tot += part[i];
         const float r = rsqrtf(tot / (float)K + eps);
-        for (uint32_t i = threadIdx.x; i < K; i += 256) {
-            const float v = x[i] * r * gamma[i];
-            xs[i] = v;
-            if (blockIdx.x == 0) xn_out[i] = v;
+#pragma unroll
+        for (int j = 0; j < KPL / 8; j++) {
+            const float v = xv[j] * r * gv[j];
+            xs[threadIdx.x + 256 * j] = v;
+            if (blockIdx.x == 0) xn_out[threadIdx.x + 256 * j] = v;
         }
         __syncthreads();
     }
-    const uint32_t e = blockIdx.x * 8 + warp;
     if (e < E) {
         const float4* xr = gamma ? reinterpret_cast<const float4*>(xs) : reinterpret_cast<const float4*>(x);
-        const float4* wrow = reinterpret_cast<const float4*>(w + (size_t)e * K);
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
         for (int i = 0; i < KPL / 4; i++) {
-            const float4 wv = wrow[lane + 32 * i], v = xr[lane + 32 * i];
-            a0 = fmaf(wv.x, v.x, a0); a1 = fmaf(wv.y, v.y, a1);
-            a2 = fmaf(wv.z, v.z, a2); a3 = fmaf(wv.w, v.w, a3);
+            const float4 v = xr[lane + 32 * i];
+            a0 = fmaf(wv[i].x, v.x, a0); a1 = fmaf(wv[i].y, v.y, a1);
+            a2 = fmaf(wv[i].z, v.z, a2); a3 = fmaf(wv[i].w, v.w, a3);
         }
         float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
@@ -353,9 +366,18 @@ int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gat
     }
     const uint32_t slots = T * k;
     // gate+up+SiLU for every (token, expert) slot: act[s][ff]
-    st = gemv_grouped(ctx, "moe_gate_up", RUNIT_FMT_Q4K, gate, up, E, ff, h, x, k, s.act, idx, slots);
+    const bool fused_sum = fused_route && h <= 32 * 960;
+    st = gemv_grouped(ctx, "moe_gate_up", RUNIT_FMT_Q4K, gate, up, E, ff, h, x, k, s.act, idx, slots, 0, nullptr, nullptr, nullptr,
+                      nullptr, fused_sum ? 1 : 0);
     if (st != RUNIT_OK) return st;
     // down: y[s][h] = Wd[e_s] . act[s]
+    if (fused_sum) {
+        // one token: the last down-projection tile of every 32 rows adds the experts' rows (same order as moe_combine_kernel)
+        st = gemv_grouped(ctx, "moe_down", RUNIT_FMT_Q4K, down, nullptr, E, h, ff, s.act, 1, s.y, idx, slots, 0, wts,
+                          (const float*)residual, (float*)out, route_counter + 32, 2);
+        if (st != RUNIT_OK || !next_gamma) return st;
+        return launch_rms_norm(ctx, (const float*)out, next_xn, next_gamma, false, next_eps, h, T);
+    }
     st = gemv_grouped(ctx, "moe_down", RUNIT_FMT_Q4K, down, nullptr, E, h, ff, s.act, 1, s.y, idx, slots);
     if (st != RUNIT_OK) return st;
     runit_launch_chain(ctx, moe_combine_kernel, dim3((h + 255) / 256, T), dim3(256), (const float*)s.y, (const float*)wts, (const float*)residual, (float*)out, T, h, k);

@@ -131,7 +131,15 @@ int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float*
 // n_experts stacked ones; an id outside that range marks an unused slot.
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
-                     uint32_t n_slots, int32_t expert_lo = 0);
+                     uint32_t n_slots, int32_t expert_lo = 0,
+                     // cmb_out != nullptr (one token): out = res + sum_i cmb_w[i] * y[i], written by the last tile of every
+                     // 32-row tile; cmb_cnt = rows / 32 (rounded up) zeroed words, zero again when the launch ends
+                     const float* cmb_w = nullptr, const float* cmb_res = nullptr, float* cmb_out = nullptr,
+                     uint32_t* cmb_cnt = nullptr,
+                     // dependent-launch ordering of a gate/up + down pair whose expert ids come from the kernel before the
+                     // pair: 1 = first of the pair (releases its successor only after its own wait), 2 = second of the pair
+                     // (reads the ids and requests weights before its wait); 0 = neither
+                     int order = 0);
 // gemv.cu: the one-kernel barrier over peer memory behind runit_peer_barrier.
 int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch,
                             uint32_t* epoch_ptr);

@@ -238,6 +238,9 @@ _TWINS = [
     ("scale_accumulate_f16", "dispatch.rs:1639 (src, acc, weight, n)"),
     ("add_f16_into_f32", "dispatch.rs:316 (src, acc, n)"),
     ("gemv_batched_f32", "no twin: (fmt, weight, input, output, residual, m, k, batch)"),
+    ("rms_norm_gemv_f32", "no twin: RMSNorm inside the GEMV (fmt, weight, x, gamma_f32, eps, output, residual, m, k)"),
+    ("rms_norm_fused_qkv_f32", "no twin: RMSNorm inside Q|K|V (fmt, w_q, w_k, w_v, x, gamma_f32, eps, out_q, out_k, out_v, "
+                               "q_dim, kv_dim, k)"),
     ("rms_norm_f32_f32", "dispatch.rs:152 (x, y, gamma_f16, eps, hidden, num_rows)"),
     ("rms_norm_f32_f32_f32g", "dispatch.rs:177 (x, y, gamma_f32, eps, hidden, num_rows)"),
     ("fused_rope_qk_f32", "dispatch.rs:945 (q, k, head_dim, q_heads, kv_heads, pos, theta)"),

@@ -487,3 +487,46 @@ def test_non_finite_activations_are_not_masked(ctx, oracle, fmt):
     # a finite input still gives a finite, correct result afterwards
     x = rng.normal(0, 1, k).astype(np.float32)
     assert_close(O, O.gemv(fmt, w, x, m, k, O.TIER_F64), run_gemv(ctx, R, name, w, x, m, k), what="after non-finite")
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 2])
+def test_rms_norm_inside_the_gemv(ctx, oracle, fmt):
+    """RMSNorm (norm.metal:95-154, f32 gamma) fused into the GEMV and into Q|K|V: compared with the oracle's norm followed by
+    its GEMV; staged kernel with and without dependent launch, the other arithmetic paths, and the simple kernel."""
+    import runit_mac_b200 as R
+    O = oracle
+    eps = 1e-5
+    for m, k in ((512, 2048), (37, 1024), (70, 2080 if fmt != 2 else 2304)):
+        rng = np.random.default_rng(7000 + fmt * 10 + m)
+        w = O.rand_weights(fmt, rng, m, k)
+        x = rng.normal(0, 3.0, k).astype(np.float32)
+        gamma = rng.normal(1, 0.2, k).astype(np.float32)
+        res = rng.normal(0, 1, m).astype(np.float32)
+        xn = O.rms_norm_f32(x, gamma, eps)
+        ref = O.gemv(fmt, w, xn, m, k)
+        wb, xb, gb, rb = ctx.buffer_from(w), ctx.buffer_from(x), ctx.buffer_from(gamma), ctx.buffer_from(res)
+        yb = ctx.new_buffer(m * 4)
+        for knob, val in (("pdl", 0), ("pdl", 1), ("gemv_math", 1), ("gemv_math", 2), ("gemv_variant", 1)):
+            ctx.set_tuning(knob, val)
+            try:
+                R.rms_norm_gemv_f32(ctx, fmt, wb, xb, gb, eps, yb, None, m, k)
+                ctx.flush()
+                assert_close(O, ref, yb.download(np.float32, m), what="norm+gemv fmt=%d %dx%d %s=%d" % (fmt, m, k, knob, val))
+                R.rms_norm_gemv_f32(ctx, fmt, wb, xb, gb, eps, yb, rb, m, k)
+                ctx.flush()
+                assert_close(O, ref + res, yb.download(np.float32, m), what="norm+gemv+res fmt=%d %dx%d" % (fmt, m, k))
+            finally:
+                ctx.set_tuning(knob, 0)
+    # Q|K|V with the norm inside
+    q_dim, kv_dim, k = 1024, 256, 2048
+    rng = np.random.default_rng(7100 + fmt)
+    ws = [O.rand_weights(fmt, rng, n, k) for n in (q_dim, kv_dim, kv_dim)]
+    x = rng.normal(0, 0.5, k).astype(np.float32)
+    gamma = rng.normal(1, 0.2, k).astype(np.float32)
+    xn = O.rms_norm_f32(x, gamma, eps)
+    outs = [ctx.new_buffer(n * 4) for n in (q_dim, kv_dim, kv_dim)]
+    R.rms_norm_fused_qkv_f32(ctx, fmt, *[ctx.buffer_from(w) for w in ws], ctx.buffer_from(x), ctx.buffer_from(gamma), eps, *outs,
+                             q_dim, kv_dim, k)
+    ctx.flush()
+    for o, w, n in zip(outs, ws, (q_dim, kv_dim, kv_dim)):
+        assert_close(O, O.gemv(fmt, w, xn, n, k), o.download(np.float32, n), what="norm+qkv fmt=%d" % fmt)
