@@ -204,6 +204,18 @@ int32_t runit_rms_norm_gemv_f32(runit_ctx_t*, int32_t fmt, const void* weight, c
 int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t*, int32_t fmt, const void* w_q, const void* w_k, const void* w_v, const void* x,
                                      const void* gamma, float eps, void* out_q, void* out_k, void* out_v, uint32_t q_dim,
                                      uint32_t kv_dim, uint32_t k);
+/* Greedy lm_head: the GEMV of runit_rms_norm_gemv_f32 (gamma may be NULL: then x is used as it is) whose epilogue also
+ * finds the index of the largest logit, lowest index among equal values (argmax after lm_head, forward.rs:1967-1973):
+ * logits f32 [m] and result int32 [1] come out of one launch.  Needs 16-byte aligned weight rows and m <= 2,097,152. */
+int32_t runit_gemv_argmax_f32(runit_ctx_t*, int32_t fmt, const void* weight, const void* x, const void* gamma, float eps,
+                              void* logits, void* result, uint32_t m, uint32_t k);
+/* Row-sharded greedy lm_head: rank `rank` multiplies its rows_total / world rows (logits_local f32, this rank's slice) and
+ * stores its (largest logit, global row index) pair, 8 bytes, into slot `rank` of every rank's pair table pairs_all[p]
+ * (uint2 [world], peer-mapped memory, plain stores).  After runit_peer_barrier, runit_argmax_pairs over the own table gives
+ * the same token on every rank: an 8-byte all-gather instead of the logits. */
+int32_t runit_gemv_argmax_allgather(runit_ctx_t*, int32_t fmt, const void* w_local, const void* x, void* logits_local,
+                                    void* const* pairs_all, uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k);
+int32_t runit_argmax_pairs(runit_ctx_t*, const void* pairs, uint32_t n, void* result);
 /* Fused Q|K|V with an f32 bias (the benchmark configuration states an f32 bias); bias may be NULL. */
 int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
                                          void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,

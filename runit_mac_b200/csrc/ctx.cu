@@ -91,6 +91,9 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
         return RUNIT_ERR_ALLOC;
     }
     // Staging area of the batched GEMV (its activations, quantised once per call): 4 MiB = K up to 232,960.
+    // Greedy epilogue of the GEMV: 65536 tile pairs (2,097,152 rows) behind a zeroed ticket word.
+    if (cudaMalloc(&c->d_am, 256 + 65536 * 8) == cudaSuccess) cudaMemset(c->d_am, 0, 256);
+    else { c->d_am = nullptr; cudaGetLastError(); }
     if (cudaMalloc(&c->d_xq, 4u << 20) == cudaSuccess) c->xq_bytes = 4u << 20;
     else { c->d_xq = nullptr; cudaGetLastError(); }
     {
@@ -152,6 +155,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     cudaStreamSynchronize(ctx->stream);   // Drop flushes, context.rs:299-304
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->d_xq) cudaFree(ctx->d_xq);
+    if (ctx->d_am) cudaFree(ctx->d_am);
     if (ctx->d_abort) cudaFree(ctx->d_abort);
     if (ctx->stream_rec) delete static_cast<std::vector<runit::StreamRec>*>(ctx->stream_rec);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);

@@ -154,8 +154,7 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
     int32_t* argmax_out = m->state + 3;
     if (with_logits) {
         if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h,
-                             (const float*)m->w.out_norm, c.eps))) return st;
-        if ((st = launch_argmax(ctx, m->logits, false, argmax_out, c.vocab))) return st;
+                             (const float*)m->w.out_norm, c.eps, argmax_out))) return st;   // argmax inside the launch
     }
     runit_launch_chain(ctx, advance_kernel, dim3(1), dim3(32), m->state, argmax_out, m->out_tokens, m->out_cap, with_logits ? 1 : 0);
     return runit_after_launch(ctx, "advance");
@@ -354,15 +353,15 @@ int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uin
 void* runit_model_logits(runit_model_t* m) { return m ? (void*)m->logits : nullptr; }
 uint64_t runit_model_launches_per_token(runit_model_t* m) {
     if (!m) return 0;
-    // embed + per layer (q|k|v with its RMSNorm, [rope +] attention, o-proj, [norm,] MoE block) + lm_head with its RMSNorm, argmax,
+    // embed + per layer (q|k|v with its RMSNorm, [rope +] attention, o-proj, [norm,] MoE block) + lm_head with its RMSNorm and the argmax,
     // advance.  MoE block at hidden 1024 / 2048 / 4096: norm + router + routing, gate/up, down + weighted sum (3); else
     // norm, router, routing, gate/up, down, weighted sum.  Expert-parallel: router + routing, gate/up, down, partial sums,
-    // barrier, sum (6).
+    // barrier, sum (6; 7 with router and routing apart).
     const bool fused = m->cfg.hidden == 1024 || m->cfg.hidden == 2048 || m->cfg.hidden == 4096;
-    const uint64_t moe = m->ep_world > 1 ? 6 : (fused ? 3 : 5);
+    const uint64_t moe = m->ep_world > 1 ? (fused ? 6 : 7) : (fused ? 3 : 5);
     const uint64_t attn = (m->cfg.head_dim == 128 || m->cfg.head_dim == 64) ? 1 : 2;   // rope + cache update fused into the attention launch
     const uint64_t norm2 = fused ? 0 : 1;
-    return 1 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + norm2 + moe) + 3;
+    return 1 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + norm2 + moe) + 2;
 }
 
 }  // extern "C"

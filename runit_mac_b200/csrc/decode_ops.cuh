@@ -32,7 +32,9 @@ int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const
                       // norm_gamma != nullptr: x is the un-normalised vector; RMSNorm(x) * gamma is what the matrices multiply
                       const float* norm_gamma = nullptr, float norm_eps = 0.f);
 int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
-                   uint32_t m, uint32_t k, const float* norm_gamma = nullptr, float norm_eps = 0.f);
+                   uint32_t m, uint32_t k, const float* norm_gamma = nullptr, float norm_eps = 0.f,
+                   // argmax_token != nullptr: the index of the largest result is written there by the launch itself
+                   int32_t* argmax_token = nullptr);
 // moe.cu
 int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,

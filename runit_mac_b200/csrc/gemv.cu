@@ -36,6 +36,11 @@ struct GemvCall {
     float* cmb_out = nullptr;
     uint32_t* cmb_cnt = nullptr;
     bool late_trigger = false, grp_early = false;   // see GemvArgs
+    // greedy epilogue: (largest result, row index + am_base) into am_dst[0..am_ndst) and the index into am_token
+    bool am = false;
+    uint32_t am_base = 0, am_ndst = 0;
+    uint2* am_dst[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int32_t* am_token = nullptr;
     // RMSNorm prologue: x is the un-normalised vector, gamma f32 [k]
     const float* norm_gamma = nullptr;
     float norm_eps = 0.f;
@@ -129,6 +134,20 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
         }
         a.n_peer = c.n_peer;
     }
+    if (c.am) {
+        RUNIT_REQUIRE(ctx, c.batch == 1 && c.nseg == 1 && !c.dual && !c.out_f16 && !c.x_f16 && !c.grp_expert && !simple && ctx->d_am &&
+                      tiles <= 65536 && c.am_ndst <= 8,
+                      "%s: the greedy epilogue takes one f32 segment of at most 2,097,152 rows with 16-byte aligned weight rows", nm);
+        a.am_part = reinterpret_cast<uint2*>((uint8_t*)ctx->d_am + 256);
+        a.am_cnt = reinterpret_cast<uint32_t*>(ctx->d_am);
+        a.am_base = c.am_base;
+        a.am_ndst = c.am_ndst;
+        for (uint32_t d = 0; d < c.am_ndst; d++) {
+            RUNIT_REQUIRE(ctx, c.am_dst[d] && runit_aligned(c.am_dst[d], 8), "%s: null or misaligned pair destination", nm);
+            a.am_dst[d] = c.am_dst[d];
+        }
+        a.am_token = c.am_token;
+    }
     if (c.norm_gamma) {
         RUNIT_REQUIRE(ctx, c.batch == 1 && !c.x_f16 && !c.grp_expert && runit_aligned(c.norm_gamma, 4),
                       "%s: the RMSNorm prologue takes one f32 input vector", nm);
@@ -166,8 +185,12 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
 // Plain single-matrix call shared by the twins below.
 static int32_t gemv1(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res,
                      uint32_t m, uint32_t k, bool x_f16, bool out_f16, int res_kind, const float* norm_gamma = nullptr,
-                     float norm_eps = 0.f) {
+                     float norm_eps = 0.f, int32_t* argmax_token = nullptr) {
     GemvCall c;
+    if (argmax_token) {
+        c.am = true;
+        c.am_token = argmax_token;
+    }
     c.norm_gamma = norm_gamma;
     c.norm_eps = norm_eps;
     c.name = name;
@@ -268,8 +291,9 @@ int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const
 }
 
 int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
-                   uint32_t m, uint32_t k, const float* norm_gamma, float norm_eps) {
-    return gemv1(ctx, name, fmt, w, x, y, res_f32, m, k, false, false, res_f32 ? RES_F32 : RES_NONE, norm_gamma, norm_eps);
+                   uint32_t m, uint32_t k, const float* norm_gamma, float norm_eps, int32_t* argmax_token) {
+    return gemv1(ctx, name, fmt, w, x, y, res_f32, m, k, false, false, res_f32 ? RES_F32 : RES_NONE, norm_gamma, norm_eps,
+                 argmax_token);
 }
 
 }  // namespace runit
@@ -365,7 +389,7 @@ int32_t runit_rms_norm_gemv_f32(runit_ctx_t* ctx, int32_t fmt, const void* weigh
                                 void* output, const void* residual, uint32_t m, uint32_t k) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, gamma && m > 0, "rms_norm_gemv_f32: null gamma or m == 0");
-    return gemv_plain(ctx, "rms_norm_gemv_f32", fmt, weight, x, output, residual, m, k, (const float*)gamma, eps);
+    return gemv_plain(ctx, "rms_norm_gemv_f32", fmt, weight, x, output, residual, m, k, (const float*)gamma, eps, nullptr);
 }
 int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_q, const void* w_k, const void* w_v, const void* x,
                                      const void* gamma, float eps, void* out_q, void* out_k, void* out_v, uint32_t q_dim,
@@ -376,6 +400,57 @@ int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t* ctx, int32_t fmt, const void* 
     void* ys[3] = {out_q, out_k, out_v};
     const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
     return gemv_segments(ctx, "rms_norm_fused_qkv_f32", fmt, 3, ws, ys, rows, x, k, (const float*)gamma, eps);
+}
+
+// (largest value, index) pairs pushed by the ranks -> index of the overall maximum (lowest index among equal values).
+__global__ void argmax_pairs_kernel(const uint2* __restrict__ pairs, uint32_t n, int32_t* __restrict__ result) {
+    grid_dependency_wait();
+    grid_launch_dependents();
+    float bv = -INFINITY;
+    uint32_t bi = 0xFFFFFFFFu;
+    for (uint32_t i = threadIdx.x; i < n; i += 32) {
+        const uint2 pr = __ldcg(&pairs[i]);
+        am_better(bv, bi, __uint_as_float(pr.x), pr.y);
+    }
+    am_warp_reduce(bv, bi);
+    if (threadIdx.x == 0) result[0] = (int32_t)bi;
+}
+
+int32_t runit_gemv_argmax_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* x, const void* gamma, float eps,
+                              void* logits, void* result, uint32_t m, uint32_t k) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, result && runit_aligned(result, 4) && m > 0, "gemv_argmax_f32: null or misaligned result, or m == 0");
+    return gemv_plain(ctx, "gemv_argmax_f32", fmt, weight, x, logits, nullptr, m, k, (const float*)gamma, eps, (int32_t*)result);
+}
+
+int32_t runit_gemv_argmax_allgather(runit_ctx_t* ctx, int32_t fmt, const void* w_local, const void* x, void* logits_local,
+                                    void* const* pairs_all, uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, pairs_all && world >= 1 && world <= 8 && rank < world && rows_total > 0 && rows_total % world == 0,
+                  "gemv_argmax_allgather: world=%u rank=%u rows=%u unsupported (1..8 ranks, rows divisible)", world, rank, rows_total);
+    const uint32_t n = rows_total / world;
+    GemvCall c;
+    c.name = "gemv_argmax_allgather";
+    c.fmt = fmt;
+    c.w[0] = w_local;
+    c.x = x;
+    c.y[0] = logits_local;
+    c.rows[0] = n;
+    c.k = k;
+    c.am = true;
+    c.am_base = rank * n;
+    for (uint32_t p = 0; p < world; p++) {
+        RUNIT_REQUIRE(ctx, pairs_all[p], "gemv_argmax_allgather: null pair table for rank %u", p);
+        c.am_dst[c.am_ndst++] = reinterpret_cast<uint2*>(pairs_all[p]) + rank;
+    }
+    return gemv_dispatch(ctx, c);
+}
+
+int32_t runit_argmax_pairs(runit_ctx_t* ctx, const void* pairs, uint32_t n, void* result) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, pairs && result && n > 0 && runit_aligned(pairs, 8) && runit_aligned(result, 4), "argmax_pairs: bad argument");
+    runit_launch_chain(ctx, argmax_pairs_kernel, dim3(1), dim3(32), (const uint2*)pairs, n, (int32_t*)result);
+    return runit_after_launch(ctx, "argmax_pairs");
 }
 
 int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* input, void* output,

@@ -104,7 +104,32 @@ struct GemvArgs {
     float* cmb_out;
     uint32_t* cmb_cnt;
     uint32_t cmb_slots;
+    // Greedy epilogue (batch 1, f32 results of one segment; argmax_f16 after lm_head, crates/engine/src/forward.rs:1967-1973),
+    // active when am_part != nullptr: every 32-row tile files (largest result, its row index + am_base) in am_part[tile]
+    // and takes a ticket on *am_cnt; the tile with the last ticket reduces the n_tiles pairs (the lowest index wins among
+    // equal values), stores the pair into every am_dst[i] (own memory or a peer's: plain stores), the index into *am_token
+    // when that is not null, and puts the counter back to zero.
+    uint2* am_part;
+    uint32_t* am_cnt;
+    uint32_t am_base;
+    uint2* am_dst[8];
+    uint32_t am_ndst;
+    int32_t* am_token;
 };
+
+// (value, index) pairs of the greedy epilogue: the larger value wins, the lower index among equal values; a NaN never
+// replaces a number.
+__device__ __forceinline__ void am_better(float& bv, uint32_t& bi, float ov, uint32_t oi) {
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
+__device__ __forceinline__ void am_warp_reduce(float& bv, uint32_t& bi) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        am_better(bv, bi, ov, oi);
+    }
+}
 
 // Tensor maps of the weight matrices (bulk-load path): one per segment, plus the second matrix of
 // a fused gate/up launch in slot 3.
@@ -680,6 +705,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
         }
         const uint32_t row = row0 + (DUAL ? (lane & 15) : lane);
         const bool writer = DUAL ? (lane < 16 && row_ok) : row_ok;
+        float v_first = -INFINITY;   // this lane's final result of batch row 0 (greedy epilogue)
         if (writer) {
 #pragma unroll
             for (int b = 0; b < B; b++) {
@@ -692,9 +718,38 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                 if (a.out_f16) reinterpret_cast<__half*>(sg.y)[o] = __float2half_rn(v);
                 else reinterpret_cast<float*>(sg.y)[o] = v;
                 for (uint32_t p = 0; p < a.n_peer; p++) a.peer_y[p][o] = v;
+                if (b == 0) v_first = v;
             }
         }
         if constexpr (B == 1 && !DUAL && !XF16) {
+            if (a.am_part != nullptr && tile_ok) {
+                float bv = writer ? v_first : -INFINITY;
+                uint32_t bi = writer ? a.am_base + row : 0xFFFFFFFFu;
+                am_warp_reduce(bv, bi);
+                uint32_t ticket = 0;
+                if (lane == 0) {
+                    __stcg(&a.am_part[tile], make_uint2(__float_as_uint(bv), bi));
+                    __threadfence();                     // the pair is visible before the ticket is
+                    ticket = atomicAdd(a.am_cnt, 1u);
+                }
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == a.n_tiles - 1) {
+                    __threadfence();
+                    bv = -INFINITY;
+                    bi = 0xFFFFFFFFu;
+                    for (uint32_t i = lane; i < a.n_tiles; i += 32) {
+                        const uint2 pr = __ldcg(&a.am_part[i]);
+                        am_better(bv, bi, __uint_as_float(pr.x), pr.y);
+                    }
+                    am_warp_reduce(bv, bi);
+                    if (lane == 0) {
+                        const uint2 pr = make_uint2(__float_as_uint(bv), bi);
+                        for (uint32_t d = 0; d < a.am_ndst; d++) *a.am_dst[d] = pr;
+                        if (a.am_token) *a.am_token = (int32_t)bi;
+                        *a.am_cnt = 0;                   // at rest again for the next launch
+                    }
+                }
+            }
             if (a.cmb_out != nullptr && tile_ok) {
                 const uint32_t t = tile % a.grp_tiles;   // row tile, shared by the slots
                 __threadfence();                         // this lane's row of y[slot] is visible before the ticket is

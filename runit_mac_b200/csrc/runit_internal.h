@@ -50,6 +50,7 @@ struct runit_ctx {
     int32_t* d_status = nullptr;        // device address of the status word written by kernels with bounded waits
     int32_t* h_status = nullptr;        // the same word, host side (pinned, mapped)
     uint32_t* d_abort = nullptr;        // device word: set by the first peer barrier that gave up; later barriers skip their wait
+    void* d_am = nullptr;               // greedy epilogue of the GEMV: ticket word at 0, result pair at 16, per-tile pairs from 256
     void* d_xq = nullptr;               // staging area of the batched GEMV's quantised activations
     size_t xq_bytes = 0;
     void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation

@@ -241,6 +241,11 @@ _TWINS = [
     ("rms_norm_gemv_f32", "no twin: RMSNorm inside the GEMV (fmt, weight, x, gamma_f32, eps, output, residual, m, k)"),
     ("rms_norm_fused_qkv_f32", "no twin: RMSNorm inside Q|K|V (fmt, w_q, w_k, w_v, x, gamma_f32, eps, out_q, out_k, out_v, "
                                "q_dim, kv_dim, k)"),
+    ("gemv_argmax_f32", "no twin: lm_head GEMV with the argmax in its epilogue (fmt, weight, x, gamma_f32 or None, eps, logits, "
+                        "result_i32, m, k)"),
+    ("gemv_argmax_allgather", "no twin: row-sharded greedy lm_head (fmt, w_local, x, logits_local, pairs_all[world] pointer "
+                              "table, world, rank, rows_total, k)"),
+    ("argmax_pairs", "no twin: (pairs, n, result_i32)"),
     ("rms_norm_f32_f32", "dispatch.rs:152 (x, y, gamma_f16, eps, hidden, num_rows)"),
     ("rms_norm_f32_f32_f32g", "dispatch.rs:177 (x, y, gamma_f32, eps, hidden, num_rows)"),
     ("fused_rope_qk_f32", "dispatch.rs:945 (q, k, head_dim, q_heads, kv_heads, pos, theta)"),

@@ -245,6 +245,45 @@ class FusedAllGatherGemv:
         return self.y[half * self.rows_total:(half + 1) * self.rows_total]
 
 
+class FusedGreedyLmHead:
+    """Row-sharded greedy lm_head: every rank multiplies its rows, finds its own (largest logit, global row) pair in the
+    GEMV's epilogue and stores the 8 bytes into every rank's pair table (peer stores into symmetric memory); one barrier
+    kernel, then each rank reduces the `world` pairs to the token.  8 bytes per rank cross NVLink instead of the logits.
+    Two pair tables alternate from call to call, for the reason given in FusedAllGatherGemv."""
+
+    def __init__(self, R, ctx, torch, dist, fmt, w_local, rows_total, k, world, rank):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        self.R, self.ctx, self.torch = R, ctx, torch
+        self.fmt, self.w, self.rows_total, self.k, self.world, self.rank = fmt, w_local, rows_total, k, world, rank
+        self.pairs = symm.empty(2 * 2 * 8, dtype=torch.int32, device="cuda")     # two tables of 8 (value bits, index) pairs
+        self.pad = symm.empty(64, dtype=torch.int32, device="cuda")
+        self.pairs.zero_()
+        self.pad.zero_()
+        torch.cuda.synchronize()
+        group = dist.group.WORLD
+        self._hq = symm.rendezvous(self.pairs, group)
+        self._hp = symm.rendezvous(self.pad, group)
+        base = [int(p) for p in self._hq.buffer_ptrs]
+        self.pair_ptrs = [(C.c_void_p * world)(*[b + half * 64 for b in base]) for half in (0, 1)]
+        self.pad_ptrs = (C.c_void_p * world)(*[int(p) for p in self._hp.buffer_ptrs])
+        self.logits_local = torch.empty(rows_total // world, dtype=torch.float32, device="cuda")
+        self.token = torch.empty(1, dtype=torch.int32, device="cuda")
+        self.epoch = 0
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def __call__(self, x):
+        """Returns the device word holding the token of this call (the same on every rank)."""
+        self.epoch += 1
+        half = self.epoch & 1
+        self.R.gemv_argmax_allgather(self.ctx, self.fmt, self.w, x, self.logits_local, self.pair_ptrs[half], self.world, self.rank,
+                                     self.rows_total, self.k)
+        self.R.peer_barrier(self.ctx, self.pad_ptrs, self.world, self.rank, self.epoch)
+        self.R.argmax_pairs(self.ctx, self.pairs.data_ptr() + half * 64, self.world, self.token)
+        return self.token
+
+
 class FusedEpDecodeMoe:
     """Expert-parallel MoE block for decode sizes with replicated tokens: every rank routes the tokens itself, runs the
     experts it owns and stores its weighted partial sums into every rank's buffer (peer stores into symmetric memory);

@@ -530,3 +530,39 @@ def test_rms_norm_inside_the_gemv(ctx, oracle, fmt):
     ctx.flush()
     for o, w, n in zip(outs, ws, (q_dim, kv_dim, kv_dim)):
         assert_close(O, O.gemv(fmt, w, xn, n, k), o.download(np.float32, n), what="norm+qkv fmt=%d" % fmt)
+
+
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_greedy_epilogue_of_the_gemv(ctx, oracle, fmt):
+    """lm_head with the argmax inside the launch (argmax after lm_head, forward.rs:1967-1973): the token equals the argmax of
+    the logits the same launch wrote (lowest index among equal values), with and without the RMSNorm prologue, on ragged
+    row counts, repeatedly (the ticket counter returns to zero), and with duplicated rows (a tie)."""
+    import runit_mac_b200 as R
+    O = oracle
+    for m, k in ((50304 // 8, 2048), (1000, 512), (31, 256)):
+        rng = np.random.default_rng(8800 + fmt + m)
+        w = O.rand_weights(fmt, rng, m, k)
+        rb = w.size // m
+        w = w.reshape(m, rb)
+        w[m // 2] = w[3]                       # rows 3 and m/2 give the same logit: a tie if it is the maximum
+        x = rng.normal(0, 1, k).astype(np.float32)
+        gamma = rng.normal(1, 0.1, k).astype(np.float32)
+        wb, xb, gb = ctx.buffer_from(w.reshape(-1)), ctx.buffer_from(x), ctx.buffer_from(gamma)
+        lb, tb = ctx.new_buffer(m * 4), ctx.new_buffer(16)
+        for g in (None, gb):
+            for rep in range(3):
+                R.gemv_argmax_f32(ctx, fmt, wb, xb, g, 1e-5, lb, tb, m, k)
+                ctx.flush()
+                logits = lb.download(np.float32, m)
+                assert int(tb.download(np.int32, 1)[0]) == int(np.argmax(logits)), (fmt, m, k, g is not None, rep)
+            xin = x if g is None else O.rms_norm_f32(x, gamma, 1e-5)
+            assert_close(O, O.gemv(fmt, w.reshape(-1), xin, m, k), logits, what="gemv_argmax logits")
+        # force the tie to be the maximum: one input that aligns with row 3
+        xt = np.zeros(k, np.float32)
+        xt[:] = O.dequant_rows(fmt, w[3].copy(), 1, k).reshape(-1)
+        ctx.call("memcpy_h2d", xb, xt.ctypes.data, xt.nbytes)
+        R.gemv_argmax_f32(ctx, fmt, wb, xb, None, 0.0, lb, tb, m, k)
+        ctx.flush()
+        logits = lb.download(np.float32, m)
+        assert int(tb.download(np.int32, 1)[0]) == int(np.argmax(logits))
+        assert logits[3] == logits[m // 2]

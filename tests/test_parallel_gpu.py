@@ -67,6 +67,14 @@ def run_rank(rank, world, port, q):
             assert torch.equal(yf, yw), "fused all-gather differs from the NCCL all-gather"
         assert torch.equal(want[0], y)
         y_fused = got[0].cpu().numpy()
+    if world > 1:
+        # greedy variant: every rank finds the (largest logit, row) pair of its slice in the GEMV's epilogue, 8 bytes per rank
+        # are exchanged; four calls in a row with different inputs, each must give the argmax of the gathered logits
+        greedy = P.FusedGreedyLmHead(R, ctx, torch, dist, 2, be.w_local, M_ROWS, K_IN, world, rank)
+        toks = [greedy(xi).clone() for xi in xs_lm]
+        ctx.flush()
+        for tk, yw in zip(toks, want):
+            assert int(tk.item()) == int(torch.argmax(yw).item()), "sharded greedy lm_head differs from argmax of the gathered logits"
     out_ep = None
     if world > 1:
         # decode-size block with replicated tokens and the combine fused over peer memory: three calls in a row give the
@@ -184,7 +192,7 @@ def test_sharded_paths_match_oracle(oracle):
             assert np.array_equal(r[4][0], res[0][4][0]), "ranks disagree on the bits of the fused expert-parallel block"
             tok_full, tok_ep, lpt = r[4][2]
             assert (tok_ep == tok_full).all(), ("expert-parallel decode differs from the single-GPU decode", tok_full, tok_ep)
-            assert (tok_ep == res[0][4][2][1]).all() and len(set(tok_ep[7:].tolist())) > 3 and lpt >= 2 + 2 * 11 + 3
+            assert (tok_ep == res[0][4][2][1]).all() and len(set(tok_ep[7:].tolist())) > 3 and lpt >= 1 + 2 * 10 + 2
 
 
 def test_peer_barrier_times_out_without_a_peer(ctx):
