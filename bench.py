@@ -543,14 +543,23 @@ def run_sharded_lm_head(R, ctx, torch, dist, stream, rank, world, steps=20):
         be.set_lm_head(fmt, w, n, K)
         ms = _time_steps(torch, dist, stream, ctx, lambda: P.sharded_gemv(be, dist, torch, x, M, world, rank), steps, world)
         ms_local = _time_steps(torch, dist, stream, ctx, lambda: be.local_gemv(x), steps, world)
+        if world == 1:
+            logits, tok = torch.empty(M, dtype=torch.float32, device="cuda"), torch.empty(4, dtype=torch.int32, device="cuda")
+            ms_g1 = _time_steps(torch, dist, stream, ctx, lambda: R.gemv_argmax_f32(ctx, fmt, w, x, None, 0.0, logits, tok, M, K), steps, world)
         alg = M * rb + 4 * (K + M)
         out[name] = {"us_per_call": ms * 1e3, "us_local_gemv": ms_local * 1e3, "aggregate_gbs": alg / (ms * 1e-3) / 1e9,
                      "rows_per_rank": n}
+        if world == 1:
+            out[name]["us_per_call_greedy_epilogue"] = ms_g1 * 1e3
         if world > 1:
             try:
                 fused = P.FusedAllGatherGemv(R, ctx, torch, dist, fmt, w, M, K, world, rank)
                 ms_f = _time_steps(torch, dist, stream, ctx, lambda: fused(x), steps, world)
                 out[name].update({"us_per_call_fused_peer_stores": ms_f * 1e3, "aggregate_gbs_fused": alg / (ms_f * 1e-3) / 1e9})
+                # greedy: the argmax runs in the GEMV's epilogue and 8 bytes per rank are exchanged instead of the logits
+                greedy = P.FusedGreedyLmHead(R, ctx, torch, dist, fmt, w, M, K, world, rank)
+                ms_g = _time_steps(torch, dist, stream, ctx, lambda: greedy(x), steps, world)
+                out[name].update({"us_per_call_greedy_pairs": ms_g * 1e3, "aggregate_gbs_greedy": alg / (ms_g * 1e-3) / 1e9})
             except Exception as exc:   # symmetric memory unavailable on this host: keep the NCCL figures
                 out[name]["fused_unavailable"] = repr(exc)[:200]
         w.free()

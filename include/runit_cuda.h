@@ -350,6 +350,30 @@ int32_t runit_argmax_f16(runit_ctx_t*, const void* input, void* result, uint32_t
 /* no twin: f32 input (sampler.rs:111-116 on the device) */
 int32_t runit_argmax_f32(runit_ctx_t*, const void* input, void* result, uint32_t n);
 
+/* ── token sampling on the device: the reference's host sampler (crates/engine/src/sampler.rs:61-111) as one launch ──
+ * Steps, in the reference's order: end-of-sequence ids suppressed while the context is shorter than min_tokens;
+ * repetition penalty once per occurrence of a token in the context; temperature 0 -> argmax (last index among equal
+ * maxima, as Iterator::max_by); else scores / temperature, softmax, top-k (the first k entries in index order with
+ * p >= the k-th largest), top-p (descending order until the running sum has reached p), and the draw r = rng * total over
+ * the survivors in index order.  The generator is the reference's xorshift64 (sampler.rs:12-27); its state lives in
+ * device memory and advances by one draw.  top_k in 0..1024 (0 = off); with top-k off and top_p < 1 the nucleus must lie
+ * within the 1024 most probable tokens (else status: RUNIT_ERR_UNSUPPORTED at the next flush, most probable token returned). */
+typedef struct {
+    float   temperature;          /* 0 = greedy */
+    int32_t top_k;                /* 0 = off */
+    float   top_p;                /* >= 1 = off */
+    float   repetition_penalty;   /* 1 = off */
+    int32_t min_tokens;
+} runit_sampler_cfg;
+/* logits f32 [n]; scores_scratch f32 [n] (holds the final distribution afterwards, unless greedy); context int32 tokens,
+ * the range [ctx_begin, ctx_end) of it is the context, or, when ctx_range is not NULL, the two device words it points to
+ * give that range; eos_ids int32 [n_eos]; rng_state uint64 [1]; result int32 [1].  All pointers are device pointers. */
+int32_t runit_sample_f32(runit_ctx_t*, const void* logits, void* scores_scratch, uint32_t n, const runit_sampler_cfg* cfg,
+                         const void* context, const void* ctx_range, uint32_t ctx_begin, uint32_t ctx_end, const void* eos_ids,
+                         uint32_t n_eos, void* rng_state, void* result);
+/* SimpleRng::new (sampler.rs:15-17): the state to store in rng_state for a seed */
+uint64_t runit_sampler_seed_state(uint64_t seed);
+
 /* ── greedy decoder for an OLMoE-shaped model with Q4_K matrices: the role of Executor::forward_greedy,
  *    crates/engine/src/forward.rs:1795-1975, with token id, position and arg-max kept on the device ── */
 typedef struct {
@@ -389,6 +413,12 @@ int32_t runit_model_forward_greedy(runit_model_t* model, int32_t token_id, int32
 /* prompt (forced tokens) + n_gen greedy steps without host round trips; out_tokens: n_prompt+n_gen int32 on the host */
 int32_t runit_model_generate_greedy(runit_model_t* model, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen,
                                     int32_t start_pos, int32_t skip_prompt_logits, int32_t* out_tokens);
+/* The same loop with the sampler in place of the argmax (generate.rs:299, 346: the context of a draw is what has been
+ * generated so far, empty for the first one).  eos_ids: host array, at most 16.  The command list of the sampled step is
+ * recorded on first use and again whenever cfg changes. */
+int32_t runit_model_generate_sampled(runit_model_t* model, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen,
+                                     int32_t start_pos, const runit_sampler_cfg* cfg, uint64_t seed, const int32_t* eos_ids,
+                                     uint32_t n_eos, int32_t* out_tokens);
 void*   runit_model_logits(runit_model_t* model);           /* device pointer, f32 [vocab], of the last step */
 uint64_t runit_model_launches_per_token(runit_model_t* model);
 

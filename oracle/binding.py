@@ -18,7 +18,7 @@ __all__ = [
     "gemv_f32w", "silu_mul_f32", "silu_mul_f16", "scale_accumulate_f16", "add_f16_into_f32",
     "topk_softmax", "moe_layer_q4k", "moe_grouped_q4k_bf16", "bf16_round", "rms_norm_f32", "rope_qk_f32", "kv_copy_to_cache_f16",
     "decode_attention_f32q_f16kv", "argmax_f32", "ModelCfg", "ModelWeights", "decode_step",
-    "compare", "DiffStats", "f32_to_f16_bits", "f16_bits_to_f32",
+    "compare", "DiffStats", "f32_to_f16_bits", "f16_bits_to_f32", "SamplerCfg", "SamplerRng", "sample", "sampler_argmax_last",
 ]
 
 Q8_0, Q4_0, Q4K, Q5_0, Q5K, Q6K = 0, 1, 2, 3, 4, 5
@@ -60,6 +60,12 @@ class ModelCfg(C.Structure):
 class ModelWeights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("tok_emb", "attn_norm", "ffn_norm", "out_norm", "wq", "wk",
                                           "wv", "wo", "router", "gate", "up", "down", "lm_head")]
+
+
+class SamplerCfg(C.Structure):
+    """SamplerConfig without the seed (crates/engine/src/sampler.rs:31-45)."""
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repetition_penalty", C.c_float),
+                ("min_tokens", C.c_int32)]
 
 
 def lib():
@@ -106,6 +112,15 @@ def lib():
         L.ro_decode_attention_f32q_f16kv.argtypes = [C.c_void_p] * 4 + [C.c_int] * 5
         L.ro_argmax_f32.restype = C.c_int32
         L.ro_argmax_f32.argtypes = [C.c_void_p, C.c_size_t]
+        L.ro_sampler_seed_state.restype = C.c_uint64
+        L.ro_sampler_seed_state.argtypes = [C.c_uint64]
+        L.ro_sampler_next_f32.restype = C.c_float
+        L.ro_sampler_next_f32.argtypes = [C.POINTER(C.c_uint64)]
+        L.ro_sampler_argmax_last.restype = C.c_int32
+        L.ro_sampler_argmax_last.argtypes = [C.c_void_p, C.c_size_t]
+        L.ro_sample.restype = C.c_int32
+        L.ro_sample.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(SamplerCfg), C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t,
+                                C.POINTER(C.c_uint64), C.c_void_p]
         L.ro_decode_step.restype = C.c_int32
         L.ro_decode_step.argtypes = [C.POINTER(ModelCfg), C.POINTER(ModelWeights), C.c_void_p,
                                      C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
@@ -339,6 +354,32 @@ def decode_attention_f32q_f16kv(q, kc, vc, kv_len, heads, kv_heads, head_dim, kv
 def argmax_f32(v) -> int:
     v = _c(v, np.float32)
     return int(lib().ro_argmax_f32(_p(v), C.c_size_t(v.size)))
+
+
+class SamplerRng:
+    """SimpleRng (sampler.rs:12-27)."""
+
+    def __init__(self, seed: int):
+        self.state = C.c_uint64(lib().ro_sampler_seed_state(C.c_uint64(seed)))
+
+    def next_f32(self) -> float:
+        return float(lib().ro_sampler_next_f32(C.byref(self.state)))
+
+
+def sampler_argmax_last(v) -> int:
+    v = _c(v, np.float32)
+    return int(lib().ro_sampler_argmax_last(_p(v), C.c_size_t(v.size)))
+
+
+def sample(logits, cfg: SamplerCfg, context, eos_ids, rng: SamplerRng, want_probs: bool = False):
+    """sample() of sampler.rs:61-111.  Returns the token, or (token, vector the draw was made from)."""
+    logits = _c(logits, np.float32)
+    context = _c(np.asarray(context, np.int32), np.int32)
+    eos_ids = _c(np.asarray(eos_ids, np.int32), np.int32)
+    probs = np.empty(logits.size, np.float32) if want_probs else None
+    tok = int(lib().ro_sample(_p(logits), C.c_size_t(logits.size), C.byref(cfg), _p(context), C.c_size_t(context.size),
+                              _p(eos_ids), C.c_size_t(eos_ids.size), C.byref(rng.state), _p(probs) if want_probs else None))
+    return (tok, probs) if want_probs else tok
 
 
 def decode_step(cfg: ModelCfg, weights: ModelWeights, kc: np.ndarray, vc: np.ndarray, token: int,

@@ -779,6 +779,104 @@ int32_t ro_argmax_f32(const float* v, size_t n) {
 
 /* crates/engine/src/forward.rs:1795-1975 with every matrix Q4_K, an f32 router and the
  * F32 MoE mode; K/V rounded to f16 on the way into the cache. */
+/* ───────────── host sampler (crates/engine/src/sampler.rs) ───────────── */
+uint64_t ro_sampler_seed_state(uint64_t seed) {                     /* SimpleRng::new, sampler.rs:15-17 */
+    return seed == 0 ? 0x9e3779b97f4a7c15ull : (seed ^ 0x9e3779b97f4a7c15ull);
+}
+float ro_sampler_next_f32(uint64_t* state) {                         /* next_u64 + next_f32, sampler.rs:18-27 */
+    uint64_t x = *state;
+    x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+    *state = x;
+    return (float)(x >> 11) / (float)(1ull << 53);
+}
+/* max_by with partial_cmp(..).unwrap_or(Equal): a later element replaces the running maximum unless it compares Less
+ * (sampler.rs:114-119); NaN compares as Equal, so it replaces too. */
+int32_t ro_sampler_argmax_last(const float* v, size_t n) {
+    if (n == 0) return 0;
+    size_t best = 0;
+    for (size_t i = 1; i < n; i++)
+        if (!(v[i] < v[best])) best = i;
+    return (int32_t)best;
+}
+static int cmp_desc_f32(const void* a, const void* b) {
+    const float x = *(const float*)a, y = *(const float*)b;
+    return x > y ? -1 : (x < y ? 1 : 0);
+}
+typedef struct { float p; uint32_t i; } ro_pi;
+static int cmp_desc_pi(const void* a, const void* b) {
+    const ro_pi* x = (const ro_pi*)a; const ro_pi* y = (const ro_pi*)b;
+    if (x->p > y->p) return -1;
+    if (x->p < y->p) return 1;
+    return x->i < y->i ? -1 : (x->i > y->i ? 1 : 0);   /* the reference's unstable sort leaves equal entries open: by index here */
+}
+int32_t ro_sample(const float* logits, size_t n, const ro_sampler_cfg* cfg, const int32_t* context, size_t n_context,
+                  const int32_t* eos_ids, size_t n_eos, uint64_t* rng_state, float* probs_out) {
+    float* s = (float*)malloc(n * sizeof(float));
+    int32_t result;
+    memcpy(s, logits, n * sizeof(float));
+    if (n_context < (size_t)cfg->min_tokens)                         /* sampler.rs:64-71 */
+        for (size_t e = 0; e < n_eos; e++)
+            if (eos_ids[e] >= 0 && (size_t)eos_ids[e] < n) s[eos_ids[e]] = -INFINITY;
+    if (cfg->repetition_penalty != 1.0f)                             /* sampler.rs:74-76, 124-135: once per occurrence */
+        for (size_t c = 0; c < n_context; c++) {
+            const int32_t t = context[c];
+            if (t >= 0 && (size_t)t < n) {
+                if (s[t] > 0.0f) s[t] /= cfg->repetition_penalty;
+                else s[t] *= cfg->repetition_penalty;
+            }
+        }
+    if (cfg->temperature == 0.0f) {                                  /* sampler.rs:79 */
+        result = ro_sampler_argmax_last(s, n);
+        goto done;
+    }
+    for (size_t i = 0; i < n; i++) s[i] /= cfg->temperature;         /* sampler.rs:82 */
+    {                                                                /* softmax_inplace, sampler.rs:137-142 */
+        float mx = -INFINITY, sum = 0.0f;
+        for (size_t i = 0; i < n; i++) mx = fmaxf(mx, s[i]);
+        for (size_t i = 0; i < n; i++) { s[i] = expf(s[i] - mx); sum += s[i]; }
+        for (size_t i = 0; i < n; i++) s[i] /= sum;
+    }
+    if (cfg->top_k > 0 && (size_t)cfg->top_k < n) {                  /* topk_filter, sampler.rs:144-152 */
+        float* sorted = (float*)malloc(n * sizeof(float));
+        memcpy(sorted, s, n * sizeof(float));
+        qsort(sorted, n, sizeof(float), cmp_desc_f32);
+        const float thr = sorted[cfg->top_k - 1];
+        free(sorted);
+        size_t kept = 0;
+        for (size_t i = 0; i < n; i++) {
+            if (s[i] >= thr && kept < (size_t)cfg->top_k) kept++;
+            else s[i] = 0.0f;
+        }
+    }
+    if (cfg->top_p < 1.0f) {                                         /* topp_filter, sampler.rs:154-162 */
+        ro_pi* order = (ro_pi*)malloc(n * sizeof(ro_pi));
+        for (size_t i = 0; i < n; i++) { order[i].p = s[i]; order[i].i = (uint32_t)i; }
+        qsort(order, n, sizeof(ro_pi), cmp_desc_pi);
+        float cum = 0.0f;
+        for (size_t r = 0; r < n; r++) {
+            if (cum >= cfg->top_p) s[order[r].i] = 0.0f;
+            else cum += s[order[r].i];
+        }
+        free(order);
+    }
+    {                                                                /* sampler.rs:98-110 */
+        float total = 0.0f;
+        for (size_t i = 0; i < n; i++) total += s[i];
+        if (total <= 0.0f) { result = ro_sampler_argmax_last(s, n); goto done; }
+        const float r = ro_sampler_next_f32(rng_state) * total;
+        float cum = 0.0f;
+        for (size_t i = 0; i < n; i++) {
+            cum += s[i];
+            if (r <= cum) { result = (int32_t)i; goto done; }
+        }
+        result = ro_sampler_argmax_last(s, n);
+    }
+done:
+    if (probs_out) memcpy(probs_out, s, n * sizeof(float));
+    free(s);
+    return result;
+}
+
 int32_t ro_decode_step(const ro_model_cfg* c, const ro_model_weights* w, uint16_t* kc, uint16_t* vc,
                        int32_t token, int32_t pos, float* logits_out) {
     int h = c->hidden, hd = c->head_dim;

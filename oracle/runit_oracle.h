@@ -106,6 +106,22 @@ void     ro_decode_attention_f32q_f16kv(const float* q, const uint16_t* kc, cons
                                         int head_dim, int kv_head_stride);
 int32_t  ro_argmax_f32(const float* v, size_t n);
 
+/* Host sampler of the reference, crates/engine/src/sampler.rs:12-168, restated line for line (sequential sums, the
+ * reference's order of operations).  probs_out (may be NULL): the vector the draw was made from (n floats; for the
+ * greedy path the penalised scores).  rng_state: xorshift64 state, advanced by one draw when a draw is made. */
+typedef struct {
+    float   temperature;
+    int32_t top_k;
+    float   top_p;
+    float   repetition_penalty;
+    int32_t min_tokens;
+} ro_sampler_cfg;
+uint64_t ro_sampler_seed_state(uint64_t seed);                      /* sampler.rs:15-17 */
+float    ro_sampler_next_f32(uint64_t* state);                      /* sampler.rs:18-27 */
+int32_t  ro_sampler_argmax_last(const float* v, size_t n);          /* sampler.rs:114-119: Iterator::max_by keeps the LAST maximum */
+int32_t  ro_sample(const float* logits, size_t n, const ro_sampler_cfg* cfg, const int32_t* context, size_t n_context,
+                   const int32_t* eos_ids, size_t n_eos, uint64_t* rng_state, float* probs_out);
+
 /* Full OLMoE-shaped decoder with Q4_K matrices (op order of Executor::forward_greedy,
  * crates/engine/src/forward.rs:1795-1975). */
 typedef struct {

@@ -173,6 +173,10 @@ int32_t runit_flush(runit_ctx_t* ctx) {
         const int32_t why = ctx->h_status[0];
         ctx->h_status[0] = 0;
         if (ctx->d_abort) cudaMemset(ctx->d_abort, 0, 4);   // the stream is idle: barriers wait again after this report
+        if (why == 4) {
+            runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "sampler: top-k is off and the nucleus is wider than the 1024 most probable tokens (code %d)", why);
+            if (ctx->sticky_status == RUNIT_OK) ctx->sticky_status = RUNIT_ERR_UNSUPPORTED;   // reported by this flush
+        } else
         runit_fail(ctx, RUNIT_ERR_TIMEOUT, why == 3 ? "a peer barrier gave up: a rank never announced its epoch (code %d)"
                                                     : "a kernel gave up a bounded wait (a copy or a dependency never completed; code %d)", why);
     }

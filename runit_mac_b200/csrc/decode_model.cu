@@ -11,6 +11,7 @@
 #include "runit_internal.h"
 #include "tma.cuh"
 
+#include <cstring>
 #include <new>
 #include <vector>
 
@@ -39,6 +40,13 @@ struct runit_model {
     uint32_t* ep_epoch = nullptr;       // device word: barrier epoch, advanced by the barrier kernel, never reset
     cudaGraphExec_t graph_full = nullptr;    // step with lm_head + argmax
     cudaGraphExec_t graph_prompt = nullptr;  // step without them (prompt positions whose logits nobody reads)
+    // sampled decoding: the step with lm_head + sampler, recorded on first use and when the configuration changes
+    cudaGraphExec_t graph_sampled = nullptr;
+    runit_sampler_cfg sampler_cfg{};
+    uint32_t sampler_n_eos = 0;
+    float* scores = nullptr;                 // [vocab]
+    int32_t* eos = nullptr;                  // [16]
+    unsigned long long* rng = nullptr;
     std::vector<void*> owned;
 };
 
@@ -75,6 +83,7 @@ __global__ void advance_kernel(int32_t* state, const int32_t* argmax_result, int
         }
         state[1] += 1;
         state[2] += 1;
+        state[5] = state[2];   // end of the sampler's context range {state[4], state[5]} inside out_tokens
     }
 }
 
@@ -89,7 +98,7 @@ static int32_t dev_alloc(runit_model* m, void** p, size_t bytes) {
 }
 
 // Issue the launches of one decode step on the context's stream.
-static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
+static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced, bool sampled = false) {
     runit_ctx* ctx = m->ctx;
     const runit_model_cfg& c = m->cfg;
     const uint32_t h = c.hidden, hd = c.head_dim, q_dim = c.n_heads * hd, kv_dim = c.n_kv_heads * hd;
@@ -152,7 +161,13 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
             return st;
     }
     int32_t* argmax_out = m->state + 3;
-    if (with_logits) {
+    if (with_logits && sampled) {
+        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h,
+                             (const float*)m->w.out_norm, c.eps))) return st;
+        // the context of the draw: what has been generated so far, out_tokens[state[4] .. state[5])
+        if ((st = runit_sample_f32(ctx, m->logits, m->scores, (uint32_t)c.vocab, &m->sampler_cfg, m->out_tokens, m->state + 4, 0, 0,
+                                   m->eos, m->sampler_n_eos, m->rng, argmax_out))) return st;
+    } else if (with_logits) {
         if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h,
                              (const float*)m->w.out_norm, c.eps, argmax_out))) return st;   // argmax inside the launch
     }
@@ -160,12 +175,12 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced) {
     return runit_after_launch(ctx, "advance");
 }
 
-static int32_t record_graph(runit_model* m, bool with_logits, cudaGraphExec_t* out) {
+static int32_t record_graph(runit_model* m, bool with_logits, cudaGraphExec_t* out, bool sampled = false) {
     runit_ctx* ctx = m->ctx;
     RUNIT_CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
     stream_rec_begin(ctx);
-    int32_t st = issue_step(m, with_logits, m->forced_cap);
+    int32_t st = issue_step(m, with_logits, m->forced_cap, sampled);
     ctx->capturing = false;
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
@@ -244,6 +259,7 @@ static int32_t model_create_impl(runit_ctx_t* ctx, const runit_model_cfg* cfg, c
     A((void**)&m->attn_counters, (size_t)c.n_heads * 4);
     A((void**)&m->ep_epoch, 64);
     A((void**)&m->moe_counters, 4096);
+    A((void**)&m->scores, (size_t)c.vocab * 4); A((void**)&m->eos, 64); A((void**)&m->rng, 8);
     A((void**)&m->state, 64); A((void**)&m->forced, (size_t)m->forced_cap * 4); A((void**)&m->out_tokens, (size_t)m->out_cap * 4);
     if (st == RUNIT_OK) {
         cudaMemsetAsync(m->kc, 0, kv_elems * 2, ctx->stream);
@@ -284,6 +300,7 @@ int32_t runit_model_destroy(runit_model_t* m) {
     cudaStreamSynchronize(m->ctx->stream);
     if (m->graph_full) cudaGraphExecDestroy(m->graph_full);
     if (m->graph_prompt) cudaGraphExecDestroy(m->graph_prompt);
+    if (m->graph_sampled) cudaGraphExecDestroy(m->graph_sampled);
     for (void* p : m->owned) cudaFree(p);
     delete m;
     return RUNIT_OK;
@@ -322,9 +339,47 @@ int32_t runit_model_forward_greedy(runit_model_t* m, int32_t token_id, int32_t p
 // entirely on the device.  out_tokens (host, n_prompt + n_gen entries): out_tokens[i] is the arg-max token
 // after step i; prompt steps before the last give -1 when skip_prompt_logits is set (their logits are not
 // computed).  The generated continuation is out_tokens[n_prompt-1 ...].  One synchronisation at the end.
+static int32_t generate_impl(runit_model_t* m, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen, int32_t start_pos,
+                             int32_t skip_prompt_logits, int32_t* out_tokens, cudaGraphExec_t graph_step);
+
 int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen,
                                     int32_t start_pos, int32_t skip_prompt_logits, int32_t* out_tokens) {
     if (!m) return RUNIT_ERR_BAD_ARG;
+    return generate_impl(m, prompt, n_prompt, n_gen, start_pos, skip_prompt_logits, out_tokens, m->graph_full);
+}
+
+int32_t runit_model_generate_sampled(runit_model_t* m, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen, int32_t start_pos,
+                                     const runit_sampler_cfg* cfg, uint64_t seed, const int32_t* eos_ids, uint32_t n_eos,
+                                     int32_t* out_tokens) {
+    if (!m) return RUNIT_ERR_BAD_ARG;
+    runit_ctx* ctx = m->ctx;
+    RUNIT_REQUIRE(ctx, cfg && n_eos <= 16 && (eos_ids || n_eos == 0) && n_prompt > 0, "model_generate_sampled: null configuration or more than 16 eos ids");
+    RUNIT_REQUIRE(ctx, m->ep_world == 1, "model_generate_sampled: the expert-parallel decoder is greedy only");
+    const bool same = m->graph_sampled && memcmp(&m->sampler_cfg, cfg, sizeof(*cfg)) == 0 && m->sampler_n_eos == n_eos;
+    if (!same) {
+        RUNIT_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        if (m->graph_sampled) cudaGraphExecDestroy(m->graph_sampled);
+        m->graph_sampled = nullptr;
+        m->sampler_cfg = *cfg;
+        m->sampler_n_eos = n_eos;
+        // an eager launch of the sampler checks the configuration before it is recorded (its result is discarded)
+        int32_t st = runit_sample_f32(ctx, m->logits, m->scores, (uint32_t)m->cfg.vocab, &m->sampler_cfg, m->out_tokens, nullptr, 0, 0,
+                                      m->eos, 0, m->rng, m->state + 3);
+        if (st == RUNIT_OK) st = runit_flush(ctx);
+        if (st == RUNIT_OK) st = record_graph(m, true, &m->graph_sampled, true);
+        if (st != RUNIT_OK) return st;
+    }
+    const unsigned long long state0 = runit_sampler_seed_state(seed);
+    int32_t eos_host[16] = {0};
+    for (uint32_t i = 0; i < n_eos; i++) eos_host[i] = eos_ids[i];
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->rng, &state0, 8, cudaMemcpyHostToDevice, ctx->stream));
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->eos, eos_host, 64, cudaMemcpyHostToDevice, ctx->stream));
+    RUNIT_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));   // the sources live on this stack frame
+    return generate_impl(m, prompt, n_prompt, n_gen, start_pos, 1, out_tokens, m->graph_sampled);
+}
+
+static int32_t generate_impl(runit_model_t* m, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen, int32_t start_pos,
+                             int32_t skip_prompt_logits, int32_t* out_tokens, cudaGraphExec_t graph_step) {
     runit_ctx* ctx = m->ctx;
     RUNIT_REQUIRE(ctx, prompt && n_prompt > 0 && out_tokens, "model_generate_greedy: null or empty prompt");
     const uint32_t n_steps = n_prompt + n_gen;
@@ -334,13 +389,16 @@ int32_t runit_model_generate_greedy(runit_model_t* m, const int32_t* prompt, uin
     for (uint32_t i = 0; i < n_prompt; i++)
         RUNIT_REQUIRE(ctx, prompt[i] >= 0 && prompt[i] < m->cfg.vocab, "model_generate_greedy: token id %d out of range", prompt[i]);
     RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->forced, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, ctx->stream));
-    int32_t st = runit_model_reset(m, prompt[0], start_pos);
+    // the sampler's context range inside out_tokens: from the step that produces the first generated token to the current step
+    const int32_t range[2] = {(int32_t)n_prompt - 1, 0};
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->state + 4, range, sizeof(range), cudaMemcpyHostToDevice, ctx->stream));
+    int32_t st = runit_model_reset(m, prompt[0], start_pos);   // synchronises: `range` lives on this stack frame
     if (st != RUNIT_OK) return st;
     // Steps past the prompt are not forced: their entries are negative and the step takes the previous argmax.
     RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(m->forced + n_prompt, 0xFF, (size_t)(m->forced_cap - n_prompt) * 4, ctx->stream));
     for (uint32_t i = 0; i < n_steps; i++) {
         const bool prompt_step = i + 1 < n_prompt;
-        cudaGraphExec_t g = (prompt_step && skip_prompt_logits) ? m->graph_prompt : m->graph_full;
+        cudaGraphExec_t g = (prompt_step && skip_prompt_logits) ? m->graph_prompt : graph_step;
         RUNIT_CUDA_TRY(ctx, cudaGraphLaunch(g, ctx->stream));
         // a bounded wait already gave up (e.g. a rank of the expert-parallel group is missing): stop feeding the stream,
         // the flush below reports it

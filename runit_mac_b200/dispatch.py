@@ -283,6 +283,24 @@ class ModelCfg(C.Structure):
                                          "top_k", "ff", "max_seq", "renorm")] + [("eps", C.c_float), ("theta", C.c_float)]
 
 
+class SamplerCfg(C.Structure):
+    """runit_sampler_cfg; SamplerConfig without the seed (crates/engine/src/sampler.rs:31-45)."""
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repetition_penalty", C.c_float),
+                ("min_tokens", C.c_int32)]
+
+
+def sampler_seed_state(ctx: Context, seed: int) -> int:
+    """State of a SimpleRng::new(seed) generator (sampler.rs:15-17), to be stored in the sampler's rng_state word."""
+    return int(ctx.lib.runit_sampler_seed_state(seed))
+
+
+def sample_f32(ctx: Context, logits, scores_scratch, n: int, cfg: SamplerCfg, context, ctx_begin: int, ctx_end: int, eos_ids,
+               n_eos: int, rng_state, result, ctx_range=None):
+    """sample() of sampler.rs:61-111 as one launch; all buffers on the device."""
+    ctx._check(ctx.lib.runit_sample_f32(ctx.handle, _ptr(logits), _ptr(scores_scratch), n, C.byref(cfg), _ptr(context), _ptr(ctx_range),
+                                        ctx_begin, ctx_end, _ptr(eos_ids), n_eos, _ptr(rng_state), _ptr(result)))
+
+
 class ModelWeights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("tok_emb", "attn_norm", "ffn_norm", "out_norm", "wq", "wk", "wv", "wo", "router",
                                           "gate", "up", "down", "lm_head")]
@@ -315,6 +333,16 @@ class Model:
         self.ctx._check(self.ctx.lib.runit_model_generate_greedy(
             self.handle, prompt.ctypes.data_as(C.POINTER(C.c_int32)), len(prompt), n_gen, start_pos,
             int(skip_prompt_logits), out.ctypes.data_as(C.POINTER(C.c_int32))))
+        return out
+
+    def generate_sampled(self, prompt, n_gen: int, cfg: SamplerCfg, seed: int, eos_ids=(), start_pos: int = 0) -> np.ndarray:
+        """The generate loop of generate.rs:299-350 with the sampler on the device."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        eos = np.ascontiguousarray(np.asarray(eos_ids, np.int32))
+        out = np.empty(len(prompt) + n_gen, np.int32)
+        self.ctx._check(self.ctx.lib.runit_model_generate_sampled(
+            self.handle, prompt.ctypes.data_as(C.POINTER(C.c_int32)), len(prompt), n_gen, start_pos, C.byref(cfg), seed,
+            eos.ctypes.data_as(C.POINTER(C.c_int32)), len(eos), out.ctypes.data_as(C.POINTER(C.c_int32))))
         return out
 
     def logits(self) -> np.ndarray:
@@ -382,5 +410,5 @@ def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top
             w.download(np.float32, T * top_k).reshape(T, top_k))
 
 
-__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "moe_scratch_bytes", "moe_layer_q4k_host", "moe_grouped_scratch_bytes", "moe_layer_q4k_bf16_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "SamplerCfg", "sample_f32", "sampler_seed_state", "moe_scratch_bytes", "moe_layer_q4k_host", "moe_grouped_scratch_bytes", "moe_layer_q4k_bf16_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
            "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K", "FMT_Q5_0", "FMT_Q5K", "FMT_Q6K"] + [n for n, _ in _TWINS]

@@ -376,3 +376,45 @@ def test_q5_0_q5k_q6k_decoders_follow_the_reference_formulas(oracle):
         a, b = O.gemv(fmt, w, x, 5, 512, O.TIER_DEQUANT), O.gemv(fmt, w, x, 5, 512, O.TIER_F64)
         assert np.allclose(a, b, rtol=2e-5, atol=1e-6 * np.abs(b).max())
         assert np.allclose(b, O.dequant_rows(fmt, w, 5, 512).astype(np.float64) @ x.astype(np.float64), rtol=1e-6)
+
+
+def test_sampler_restatement_against_the_reference_tests():
+    """The three tests the reference holds for its sampler (crates/engine/src/sampler.rs:163-190) and an independent
+    restatement of its generator (sampler.rs:12-27) in Python integers."""
+    import oracle as O
+    # greedy_picks_max
+    assert O.sampler_argmax_last(np.array([0.1, 5.0, 2.0], np.float32)) == 1
+    # temperature_zero_is_greedy: SamplerConfig::greedy() = temperature 0, top_k 40, top_p 0.95, penalty 1.1, min_tokens 1
+    greedy = O.SamplerCfg(0.0, 40, 0.95, 1.1, 1)
+    assert O.sample(np.arange(10, dtype=np.float32), greedy, [], [], O.SamplerRng(42)) == 9
+    # repetition_penalty_reduces_repeated: [1, 5, 3] with context [1] and penalty 2 -> 5 / 2 at index 1, the rest unchanged
+    cfg = O.SamplerCfg(0.0, 0, 1.0, 2.0, 0)
+    tok, scores = O.sample(np.array([1.0, 5.0, 3.0], np.float32), cfg, [1], [], O.SamplerRng(1), want_probs=True)
+    assert abs(scores[1] - 2.5) < 1e-6 and abs(scores[0] - 1.0) < 1e-6 and tok == 2
+    # the penalty applies once per occurrence, negative scores are multiplied
+    _, scores = O.sample(np.array([-1.0, 8.0, 3.0], np.float32), cfg, [1, 0, 1], [], O.SamplerRng(1), want_probs=True)
+    assert scores.tolist() == [-2.0, 2.0, 3.0]
+    # Iterator::max_by keeps the last of equal maxima
+    assert O.sampler_argmax_last(np.array([7.0, 1.0, 7.0, 0.0], np.float32)) == 2
+    # generator: xorshift64 (13, 7, 17), seed ^ 0x9e3779b97f4a7c15, (x >> 11) as f32 / 2^53 as f32
+    M = (1 << 64) - 1
+    for seed in (0, 1, 42, 0xDEADBEEF):
+        x = 0x9e3779b97f4a7c15 if seed == 0 else seed ^ 0x9e3779b97f4a7c15
+        rng = O.SamplerRng(seed)
+        for _ in range(50):
+            x ^= (x << 13) & M
+            x ^= x >> 7
+            x ^= (x << 17) & M
+            want = np.float32(np.float32(x >> 11) / np.float32(2.0 ** 53))
+            assert np.float32(rng.next_f32()) == want
+    # min_tokens suppresses the end-of-sequence ids; top-k keeps the first k entries in index order that reach the threshold
+    cfg = O.SamplerCfg(0.0, 0, 1.0, 1.0, 3)
+    assert O.sample(np.array([1.0, 9.0, 3.0], np.float32), cfg, [0, 0], [1], O.SamplerRng(1)) == 2
+    assert O.sample(np.array([1.0, 9.0, 3.0], np.float32), cfg, [0, 0, 0], [1], O.SamplerRng(1)) == 1
+    cfg = O.SamplerCfg(1.0, 2, 1.0, 1.0, 0)
+    _, p = O.sample(np.array([2.0, 2.0, 2.0, 5.0, 1.0], np.float32), cfg, [], [], O.SamplerRng(3), want_probs=True)
+    assert (p > 0).tolist() == [True, True, False, False, False]   # the threshold is p(2.0); the later, larger entry finds k taken
+    # top-p: descending order until the running sum has reached p
+    cfg = O.SamplerCfg(1.0, 0, 0.6, 1.0, 0)
+    _, p = O.sample(np.log(np.array([0.5, 0.3, 0.15, 0.05], np.float32)), cfg, [], [], O.SamplerRng(3), want_probs=True)
+    assert (p > 0).tolist() == [True, True, False, False]
