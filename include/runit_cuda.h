@@ -419,6 +419,16 @@ int32_t runit_model_generate_greedy(runit_model_t* model, const int32_t* prompt,
 int32_t runit_model_generate_sampled(runit_model_t* model, const int32_t* prompt, uint32_t n_prompt, uint32_t n_gen,
                                      int32_t start_pos, const runit_sampler_cfg* cfg, uint64_t seed, const int32_t* eos_ids,
                                      uint32_t n_eos, int32_t* out_tokens);
+/* Executor::prefill (crates/engine/src/prefill.rs:29-255): the whole prompt in one batched pass from an empty cache
+ * (tensor-core GEMMs with bf16 operands over the Q4_K matrices, causal attention over the f16 cache, the batched MoE
+ * block).  Afterwards the cache holds positions 0 .. n-1, *next_token is the argmax of the last position's logits, and
+ * runit_model_generate_greedy(&next, 1, n_gen, n, ...) continues.  head_dim 64 or 128; tokens: host array. */
+int32_t runit_model_prefill(runit_model_t* model, const int32_t* tokens, uint32_t n, int32_t* next_token);
+/* The causal attention kernel of the prefill by itself: q f32 [T][heads*head_dim] (already rotated), caches f16
+ * [kv_heads][max_seq][head_dim] holding positions 0 .. start_pos+T-1, out bf16 [T][heads*head_dim]; query t sees keys
+ * 0 .. start_pos+t (attention.metal:36-158). */
+int32_t runit_prefill_attention_f16kv(runit_ctx_t*, const void* q, const void* kcache, const void* vcache, void* out_bf16, uint32_t T,
+                                      uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t max_seq, uint32_t start_pos);
 void*   runit_model_logits(runit_model_t* model);           /* device pointer, f32 [vocab], of the last step */
 uint64_t runit_model_launches_per_token(runit_model_t* model);
 

@@ -47,6 +47,14 @@ struct runit_model {
     float* scores = nullptr;                 // [vocab]
     int32_t* eos = nullptr;                  // [16]
     unsigned long long* rng = nullptr;
+    // batched prefill (allocated on first use, for prompts up to max_seq)
+    struct {
+        float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *proj = nullptr, *xn2 = nullptr;
+        void *xn_bf16 = nullptr, *ao_bf16 = nullptr, *moe_scratch = nullptr;
+        int32_t *tokens = nullptr, *tables = nullptr;
+        size_t moe_bytes = 0;
+        uint32_t rows_alloc = 0;
+    } pf;
     std::vector<void*> owned;
 };
 
@@ -304,6 +312,88 @@ int32_t runit_model_destroy(runit_model_t* m) {
     for (void* p : m->owned) cudaFree(p);
     delete m;
     return RUNIT_OK;
+}
+
+// After a batched prefill: the decoder stands at position n with the token the last position produced.
+__global__ void prefill_finish_kernel(int32_t* state, int32_t n) {
+    if (threadIdx.x == 0) {
+        state[0] = state[3];
+        state[1] = n;
+        state[2] = 0;
+        state[5] = 0;
+    }
+}
+
+// Executor::prefill (crates/engine/src/prefill.rs:29-255): the whole prompt in one batched pass from an empty cache; the
+// cache then holds positions 0 .. n-1 and *next_token is the argmax of the last position's logits (they stay readable
+// through runit_model_logits).  Decoding continues with runit_model_generate_greedy(&next, 1, n_gen, n, ...).
+int32_t runit_model_prefill(runit_model_t* m, const int32_t* tokens, uint32_t n, int32_t* next_token) {
+    if (!m) return RUNIT_ERR_BAD_ARG;
+    runit_ctx* ctx = m->ctx;
+    const runit_model_cfg& c = m->cfg;
+    RUNIT_REQUIRE(ctx, tokens && n > 0 && next_token, "model_prefill: null or empty prompt");     // prefill.rs:35-37
+    RUNIT_REQUIRE(ctx, n <= (uint32_t)c.max_seq, "model_prefill: %u tokens exceed max_seq %d", n, c.max_seq);
+    RUNIT_REQUIRE(ctx, m->ep_world == 1, "model_prefill: not available on the expert-parallel decoder");
+    const uint32_t h = c.hidden, hd = c.head_dim, q_dim = c.n_heads * hd, kv_dim = c.n_kv_heads * hd;
+    RUNIT_REQUIRE(ctx, (hd == 64 || hd == 128) && q_dim % 256 == 0 && kv_dim % 256 == 0 && c.ff % 256 == 0,
+                  "model_prefill: head_dim 64/128 and projection widths that are multiples of 256 only");
+    for (uint32_t i = 0; i < n; i++)
+        RUNIT_REQUIRE(ctx, tokens[i] >= 0 && tokens[i] < c.vocab, "model_prefill: token id %d out of range", tokens[i]);   // prefill.rs:55-57
+    int32_t st = RUNIT_OK;
+    if (!m->pf.x) {
+        const uint32_t cap = (uint32_t)c.max_seq;
+        m->pf.rows_alloc = (cap + 255) / 256 * 256 + 256;
+        m->pf.moe_bytes = runit_moe_grouped_scratch_bytes(cap, h, c.ff, c.n_experts, c.top_k);
+        auto A = [&](void** p, size_t b) { if (st == RUNIT_OK) st = dev_alloc(m, p, b); };
+        A((void**)&m->pf.x, (size_t)cap * h * 4); A((void**)&m->pf.q, (size_t)cap * q_dim * 4);
+        A((void**)&m->pf.k, (size_t)cap * kv_dim * 4); A((void**)&m->pf.v, (size_t)cap * kv_dim * 4);
+        A((void**)&m->pf.proj, (size_t)cap * h * 4); A((void**)&m->pf.xn2, (size_t)cap * h * 4);
+        A(&m->pf.xn_bf16, (size_t)m->pf.rows_alloc * h * 2); A(&m->pf.ao_bf16, (size_t)m->pf.rows_alloc * q_dim * 2);
+        A(&m->pf.moe_scratch, m->pf.moe_bytes);
+        A((void**)&m->pf.tokens, (size_t)cap * 4); A((void**)&m->pf.tables, (size_t)(3 * ((cap + 255) / 256) + 4) * 4);
+        if (st != RUNIT_OK) return st;
+        // rows past the prompt are read by the GEMMs' tile loads (never stored): keep them finite
+        cudaMemsetAsync(m->pf.xn_bf16, 0, (size_t)m->pf.rows_alloc * h * 2, ctx->stream);
+        cudaMemsetAsync(m->pf.ao_bf16, 0, (size_t)m->pf.rows_alloc * q_dim * 2, ctx->stream);
+    }
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->pf.tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if ((st = dense_tiles_prepare(ctx, m->pf.tables, n))) return st;
+    if ((st = prefill_embed(ctx, (const float*)m->w.tok_emb, m->pf.tokens, m->pf.x, n, h))) return st;
+    const size_t rb_h = runit_row_bytes(RUNIT_FMT_Q4K, h), rb_q = runit_row_bytes(RUNIT_FMT_Q4K, q_dim), rb_ff = runit_row_bytes(RUNIT_FMT_Q4K, c.ff);
+    const size_t kv_layer = (size_t)c.n_kv_heads * c.max_seq * hd;
+    for (int l = 0; l < c.n_layers; l++) {
+        const uint8_t* wq = (const uint8_t*)m->w.wq + (size_t)l * q_dim * rb_h;
+        const uint8_t* wk = (const uint8_t*)m->w.wk + (size_t)l * kv_dim * rb_h;
+        const uint8_t* wv = (const uint8_t*)m->w.wv + (size_t)l * kv_dim * rb_h;
+        const uint8_t* wo = (const uint8_t*)m->w.wo + (size_t)l * h * rb_q;
+        // attention block (prefill.rs:84-150)
+        if ((st = prefill_norm_bf16(ctx, m->pf.x, (const float*)m->w.attn_norm + (size_t)l * h, m->pf.xn_bf16, c.eps, n, h))) return st;
+        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_q", wq, nullptr, q_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.q, q_dim, n, m->pf.tables))) return st;
+        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_k", wk, nullptr, kv_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.k, kv_dim, n, m->pf.tables))) return st;
+        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_v", wv, nullptr, kv_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.v, kv_dim, n, m->pf.tables))) return st;
+        __half* kcl = m->kc + (size_t)l * kv_layer;
+        __half* vcl = m->vc + (size_t)l * kv_layer;
+        if ((st = prefill_rope_cache(ctx, m->pf.q, m->pf.k, m->pf.v, kcl, vcl, hd, c.n_heads, c.n_kv_heads, 0, c.theta, c.max_seq, n))) return st;
+        if ((st = prefill_attention(ctx, m->pf.q, kcl, vcl, m->pf.ao_bf16, n, c.n_heads, c.n_kv_heads, hd, c.max_seq, 0))) return st;
+        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_o", wo, nullptr, h, q_dim, m->pf.ao_bf16, m->pf.rows_alloc, m->pf.proj, h, n, m->pf.tables))) return st;
+        if ((st = prefill_add_rows(ctx, m->pf.x, m->pf.proj, (size_t)n * h))) return st;
+        // mixture-of-experts block on all tokens at once (prefill.rs:153-215 runs it token by token)
+        if ((st = launch_rms_norm(ctx, m->pf.x, m->pf.xn2, (const float*)m->w.ffn_norm + (size_t)l * h, false, c.eps, h, n))) return st;
+        const size_t eg = (size_t)c.n_experts * c.ff * rb_h, ed = (size_t)c.n_experts * h * rb_ff;
+        if ((st = runit_moe_layer_q4k_bf16(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h, (const uint8_t*)m->w.gate + (size_t)l * eg,
+                                           (const uint8_t*)m->w.up + (size_t)l * eg, (const uint8_t*)m->w.down + (size_t)l * ed, m->pf.xn2, m->pf.x,
+                                           m->pf.x, nullptr, nullptr, m->pf.moe_scratch, m->pf.moe_bytes, n, h, c.ff, c.n_experts, c.top_k, c.renorm)))
+            return st;
+    }
+    // final norm + lm_head on the last position only (prefill.rs:229-250), through the decode path's launch
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->x, m->pf.x + (size_t)(n - 1) * h, (size_t)h * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h, (const float*)m->w.out_norm, c.eps,
+                         m->state + 3)))
+        return st;
+    prefill_finish_kernel<<<1, 32, 0, ctx->stream>>>(m->state, (int32_t)n);
+    if ((st = runit_after_launch(ctx, "prefill_finish"))) return st;
+    RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(next_token, m->state, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return runit_flush(ctx);
 }
 
 // Clear the KV position: the next step runs at `pos` with input token `token`.

@@ -35,6 +35,18 @@ int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, con
                    uint32_t m, uint32_t k, const float* norm_gamma = nullptr, float norm_eps = 0.f,
                    // argmax_token != nullptr: the index of the largest result is written there by the launch itself
                    int32_t* argmax_token = nullptr);
+// prefill.cu: launchers of the batched prefill's own kernels
+int32_t prefill_embed(runit_ctx* ctx, const float* emb, const int32_t* tokens, float* x, uint32_t T, uint32_t h);
+int32_t prefill_norm_bf16(runit_ctx* ctx, const float* x, const float* gamma, void* y_bf16, float eps, uint32_t T, uint32_t h);
+int32_t prefill_rope_cache(runit_ctx* ctx, float* q, const float* k, const float* v, void* kcache, void* vcache, uint32_t hd, uint32_t heads,
+                           uint32_t kv_heads, uint32_t start_pos, float theta, uint32_t max_seq, uint32_t T);
+int32_t prefill_attention(runit_ctx* ctx, const float* q, const void* kcache, const void* vcache, void* out_bf16, uint32_t T, uint32_t heads,
+                          uint32_t kv_heads, uint32_t hd, uint32_t max_seq, uint32_t start_pos);
+int32_t prefill_add_rows(runit_ctx* ctx, float* x, const float* y, size_t n);
+// moe_grouped.cu: the tensor-core GEMM of the batched MoE block used on a dense matrix (see there)
+int32_t dense_tiles_prepare(runit_ctx* ctx, int32_t* tables, uint32_t T);
+int32_t dense_gemm_q4k_bf16(runit_ctx* ctx, const char* name, const void* w, const void* w_up, uint32_t rows, uint32_t K,
+                            const void* x_bf16, uint32_t x_rows, void* out, uint32_t ld, uint32_t T, const int32_t* tables);
 // moe.cu
 int32_t moe_layer_q4k_impl(runit_ctx* ctx, const void* router_w, const void* gate, const void* up, const void* down,
                            const void* x, const void* residual, void* out, int32_t* idx_out, float* w_out, void* scratch,

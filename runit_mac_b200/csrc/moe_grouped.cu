@@ -619,7 +619,51 @@ static int32_t check_shapes(runit_ctx* ctx, const char* who, uint32_t T, uint32_
     return RUNIT_OK;
 }
 
+// ── dense use of the same kernels: one "expert" that owns the whole matrix, tokens in their own order ──
+__global__ void dense_tiles_kernel(uint32_t T, int32_t* tile_expert, int32_t* tile_nvalid, int32_t* tile_row0, int32_t* n_tok_tiles) {
+    const uint32_t n = (T + pair::kTokPair - 1) / pair::kTokPair;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        tile_expert[i] = 0;
+        tile_nvalid[i] = (int32_t)min((uint32_t)pair::kTokPair, T - i * pair::kTokPair);
+        tile_row0[i] = (int32_t)(i * pair::kTokPair);
+    }
+    if (threadIdx.x == 0) n_tok_tiles[0] = (int32_t)n;
+}
+
 }  // namespace gg
+
+// Tile tables for dense_gemm_q4k_bf16 over T tokens: `tables` holds 3 * ceil(T / 256) + 4 int32.
+int32_t dense_tiles_prepare(runit_ctx* ctx, int32_t* tables, uint32_t T) {
+    const uint32_t n = (T + gg::pair::kTokPair - 1) / gg::pair::kTokPair;
+    gg::dense_tiles_kernel<<<1, 256, 0, ctx->stream>>>(T, tables + 4, tables + 4 + n, tables + 4 + 2 * n, tables);
+    return runit_after_launch(ctx, "dense_tiles");
+}
+
+// out[t][r] = sum_k bf16(W[r][k]) * x[t][k] (f32 out, w_up == nullptr), or out[t][r] = bf16(silu(W.x) * (W_up.x)) (bf16 out):
+// the grouped tensor-core GEMM with every token tile on expert 0.  x_bf16 has x_rows rows allocated, at least
+// ceil(T / 256) * 256 + 256 (a tile's load may reach past its last valid row; what it reads there is never stored).
+int32_t dense_gemm_q4k_bf16(runit_ctx* ctx, const char* name, const void* w, const void* w_up, uint32_t rows, uint32_t K,
+                            const void* x_bf16, uint32_t x_rows, void* out, uint32_t ld, uint32_t T, const int32_t* tables) {
+    RUNIT_REQUIRE(ctx, w && x_bf16 && out && tables && T > 0, "%s: null pointer", name);
+    RUNIT_REQUIRE(ctx, K % 256 == 0 && rows % 256 == 0, "%s: rows %u and K %u must be multiples of 256", name, rows, K);
+    const uint32_t n = (T + gg::pair::kTokPair - 1) / gg::pair::kTokPair;
+    RUNIT_REQUIRE(ctx, x_rows >= n * gg::pair::kTokPair + 256, "%s: activation buffer too short", name);
+    gg::Args a{};
+    a.w0 = (const uint8_t*)w;
+    a.w1 = (const uint8_t*)w_up;
+    a.rows = rows;
+    a.K = K;
+    a.nb = rows / gg::kRows;
+    a.tile_expert = tables + 4;
+    a.tile_nvalid = tables + 4 + n;
+    a.tile_row0 = tables + 4 + 2 * n;
+    a.n_tok_tiles = tables;
+    a.out = out;
+    a.ld = ld;
+    a.status = ctx->d_status;
+    if (w_up) return gg::launch_pair<true>(ctx, name, a, x_bf16, x_rows, 1, n * (rows / 128));
+    return gg::launch_pair<false>(ctx, name, a, x_bf16, x_rows, 1, n * (rows / 256));
+}
 
 // moe.cu
 int32_t moe_router(runit_ctx* ctx, const float* router_w, const float* x, float* logits, uint32_t E, uint32_t h, uint32_t T);

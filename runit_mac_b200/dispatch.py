@@ -246,6 +246,8 @@ _TWINS = [
     ("gemv_argmax_allgather", "no twin: row-sharded greedy lm_head (fmt, w_local, x, logits_local, pairs_all[world] pointer "
                               "table, world, rank, rows_total, k)"),
     ("argmax_pairs", "no twin: (pairs, n, result_i32)"),
+    ("prefill_attention_f16kv", "dispatch.rs flash_attention_f16 with q_len = seq (prefill.rs:134-145): (q_f32, kcache, vcache, out_bf16, T, "
+                                "heads, kv_heads, head_dim, max_seq, start_pos)"),
     ("rms_norm_f32_f32", "dispatch.rs:152 (x, y, gamma_f16, eps, hidden, num_rows)"),
     ("rms_norm_f32_f32_f32g", "dispatch.rs:177 (x, y, gamma_f32, eps, hidden, num_rows)"),
     ("fused_rope_qk_f32", "dispatch.rs:945 (q, k, head_dim, q_heads, kv_heads, pos, theta)"),
@@ -344,6 +346,13 @@ class Model:
             self.handle, prompt.ctypes.data_as(C.POINTER(C.c_int32)), len(prompt), n_gen, start_pos, C.byref(cfg), seed,
             eos.ctypes.data_as(C.POINTER(C.c_int32)), len(eos), out.ctypes.data_as(C.POINTER(C.c_int32))))
         return out
+
+    def prefill(self, tokens) -> int:
+        """Executor::prefill (prefill.rs:29-255): batched pass over the prompt from an empty cache; returns the next token."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        nxt = C.c_int32(-1)
+        self.ctx._check(self.ctx.lib.runit_model_prefill(self.handle, tokens.ctypes.data_as(C.POINTER(C.c_int32)), len(tokens), C.byref(nxt)))
+        return nxt.value
 
     def logits(self) -> np.ndarray:
         out = np.empty(self.cfg.vocab, np.float32)

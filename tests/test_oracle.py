@@ -418,3 +418,59 @@ def test_sampler_restatement_against_the_reference_tests():
     cfg = O.SamplerCfg(1.0, 0, 0.6, 1.0, 0)
     _, p = O.sample(np.log(np.array([0.5, 0.3, 0.15, 0.05], np.float32)), cfg, [], [], O.SamplerRng(3), want_probs=True)
     assert (p > 0).tolist() == [True, True, False, False]
+
+
+def _small_host_model(O, seed=11):
+    """A 2-layer decoder on the host (zero-mean Q4_K weights, the shapes of the GPU tests' small model)."""
+    from test_decode_gpu import SMALL, rand_q4k_zero_mean
+    c = dict(SMALL)
+    L, h, E, ff, V = c["n_layers"], c["hidden"], c["n_experts"], c["ff"], c["vocab"]
+    q_dim, kv_dim = c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"]
+    shapes = {"wq": (L * q_dim, h), "wk": (L * kv_dim, h), "wv": (L * kv_dim, h), "wo": (L * h, q_dim),
+              "gate": (L * E * ff, h), "up": (L * E * ff, h), "down": (L * E * h, ff), "lm_head": (V, h)}
+    rng = np.random.default_rng(seed)
+    host = {n: rand_q4k_zero_mean(O, rng, r, k).reshape(-1) for n, (r, k) in shapes.items()}
+    host.update({"tok_emb": rng.normal(0, 0.02, (V, h)).astype(np.float32), "attn_norm": np.ones((L, h), np.float32),
+                 "ffn_norm": np.ones((L, h), np.float32), "out_norm": np.ones(h, np.float32),
+                 "router": rng.normal(0, 0.02, (L, E, h)).astype(np.float32)})
+    return c, host
+
+
+def test_prefill_restatement_agrees_with_the_decode_oracle():
+    """The batched prefill's restatement (bf16 GEMM operands, f16 attention operands) against the decode oracle run token by
+    token in f32 over the same prompt: the same cache and logits to bf16 operand rounding (1e-2 of their spread rms, 8e-2 at
+    worst), the same next token.  Ties the prefill restatement to the arithmetic that is pinned on the reference's formulas."""
+    import oracle as O
+    from oracle import prefill as OP
+    c, host = _small_host_model(O)
+    prompt = np.random.default_rng(5).integers(0, c["vocab"], 24).astype(np.int32)
+    tok, logits, kc, vc = OP.prefill(c, host, prompt)
+    ocfg = O.ModelCfg(**c)
+    ow = O.ModelWeights(**{k: v.ctypes.data for k, v in host.items()})
+    kc2 = np.zeros_like(kc)
+    vc2 = np.zeros_like(vc)
+    for pos, t in enumerate(prompt):
+        ref_tok, ref_logits = O.decode_step(ocfg, ow, kc2, vc2, int(t), pos, want_logits=True)
+    T = len(prompt)
+    spread = float(np.std(ref_logits))
+    # a bf16 operand carries a relative rounding of up to 2^-9: about 0.4 % rms per GEMM output, a few times that at worst
+    d = np.abs(logits - ref_logits)
+    assert d.max() <= 8e-2 * spread and np.sqrt((d ** 2).mean()) <= 1e-2 * spread, (d.max(), spread)
+    assert tok == ref_tok or abs(ref_logits[tok] - ref_logits[ref_tok]) <= 8e-2 * spread
+    for a, b in ((kc, kc2), (vc, vc2)):
+        a, b = a[:, :, :T].astype(np.float32), b[:, :, :T].astype(np.float32)
+        assert np.abs(a - b).max() <= 8e-2 * float(np.std(b)) and np.sqrt(((a - b) ** 2).mean()) <= 1e-2 * float(np.std(b))
+    # the attention restatement alone against a plain f64 softmax
+    rng = np.random.default_rng(2)
+    heads, kvh, hd, T = 4, 2, 64, 70
+    q = rng.normal(0, 1, (T, heads * hd)).astype(np.float32)
+    kcs = rng.normal(0, 1, (kvh, 128, hd)).astype(np.float16)
+    vcs = rng.normal(0, 1, (kvh, 128, hd)).astype(np.float16)
+    got = OP.causal_attention_f16(q, kcs, vcs, heads, kvh, hd)
+    for h in range(heads):
+        K, V = kcs[h // 2, :T].astype(np.float64), vcs[h // 2, :T].astype(np.float64)
+        s = q[:, h * hd:(h + 1) * hd].astype(np.float64) @ K.T / np.sqrt(hd)
+        s = np.where(np.arange(T)[None, :] <= np.arange(T)[:, None], s, -np.inf)
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        ref = (p / p.sum(axis=1, keepdims=True)) @ V
+        assert np.abs(got[:, h * hd:(h + 1) * hd] - ref).max() < 5e-3
