@@ -488,6 +488,17 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
     out["olmoe_decode_q4k"] = {"decode_tok_s": 64 / max(dt_all - dt_prompt, 1e-9), "prompt_tok_s": 128 / dt_prompt,
                                "tokens_total_s": 192 / dt_all, "launches_per_token": int(model.launches_per_token),
                                "note": "wall clock around one call that runs 192 recorded steps and synchronises once"}
+    # the same prompts through the batched prefill (tensor-core GEMMs, causal attention over the cache)
+    pf = {}
+    for n_tok in (128, 1024, 2048):
+        pr = np.random.default_rng(n_tok).integers(0, 50304, n_tok).astype(np.int32)
+        model.prefill(pr)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            model.prefill(pr)
+        dt = (time.perf_counter() - t0) / 3
+        pf["T%d" % n_tok] = {"ms": dt * 1e3, "tokens_per_s": n_tok / dt}
+    out["olmoe_decode_q4k"]["batched_prefill"] = pf
     model.close()
     if rank == 0:
         out["gguf_load"] = run_gguf_load(ctx)
