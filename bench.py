@@ -707,7 +707,33 @@ def run_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=
     recv = torch.bincount((idx // n_local).flatten().long(), minlength=world).to(torch.float64)
     if world > 1:
         dist.all_reduce(recv)
-    return {"ms_per_layer": ms, "tokens_per_s_all_ranks": T_total / (ms * 1e-3), "tokens_per_rank": T,
+    native = {}
+    if world > 1:
+        # the same block with the library's own exchange (peer stores, two barrier kernels, no host read), for both
+        # expert placements; the routing is the given Zipf routing, so the router weights only have to reproduce it:
+        # a one-hot router would need E = h columns; instead the block routes with its own router on x and the given
+        # routing is left to the NCCL variant above.  The load figures below are the native block's own.
+        try:
+            router = torch.randn(E, h, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)) * 0.02
+            # a popularity that falls with the expert index, as in the Zipf routing above: a bias direction in x
+            bias = torch.randn(h, device="cuda", generator=torch.Generator(device="cuda").manual_seed(6))
+            router = router + (2.5 / torch.arange(1, E + 1, device="cuda", dtype=torch.float32) ** 0.5)[:, None] * bias[None, :] / h
+            xb = x + bias[None, :]
+            for placement in (0, 1):
+                epp = P.FusedEpPrefillMoe(R, ctx, torch, dist, router, gate, up, down, E, h, ff, k, False, world, rank, T, placement=placement)
+                ms_n = _time_steps(torch, dist, stream, ctx, lambda: epp(xb), steps, world)
+                _o, i_n, _w = epp(xb)
+                ctx.flush()
+                owner = (i_n % world) if placement else (i_n // n_local)
+                rc = torch.bincount(owner.flatten().long(), minlength=world).to(torch.float64)
+                dist.all_reduce(rc)
+                native["placement_%s" % ("mod" if placement else "block")] = {
+                    "ms_per_layer": ms_n, "tokens_per_s_all_ranks": T_total / (ms_n * 1e-3),
+                    "slots_per_rank_max": float(rc.max().item()), "slots_per_rank_mean": float(rc.mean().item())}
+                del epp
+        except Exception as exc:
+            native["unavailable"] = repr(exc)[:200]
+    return {"native_peer_stores": native, "ms_per_layer": ms, "tokens_per_s_all_ranks": T_total / (ms * 1e-3), "tokens_per_rank": T,
             "slots_per_rank_max": float(recv.max().item()), "slots_per_rank_mean": float(recv.mean().item())}
 
 

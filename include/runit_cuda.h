@@ -232,6 +232,23 @@ int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const vo
  *    announces in stream order after its own reads of result n), or put a second barrier after the consumer. ── */
 int32_t runit_gemv_allgather_f32(runit_ctx_t*, int32_t fmt, const void* w_local, const void* x, void* const* y_all,
                                  uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k);
+/* ── expert-parallel MoE block for prefill-sized batches (no twin: the reference is single-device) ──
+ * Tokens are data-parallel (the same T on every rank), experts are split over the ranks (E / world each; placement 0:
+ * expert e on rank e / (E/world), 1: on rank e % world); token rows are stored into the owners' receive buffers and the
+ * expert outputs back into the senders' return buffers with plain peer stores, two bounded barriers per call, no host
+ * read and no collective library on the data path.  The result equals runit_moe_layer_q4k_bf16 on one GPU bit for bit.
+ * Peer-mapped buffers, one per rank, given as pointer tables of `world` entries (this rank's own included):
+ *   recv_rows   bf16  [world * T * k][h]     recv_meta  int32 [world * T * k][2]     recv_counts  int32 [world]
+ *   return_rows f32   [T * k][h]             signal_pads uint32 [>= world], zeroed before the first call
+ * epoch counts the calls on these buffers from 1 (it uses barrier epochs 2*epoch-1 and 2*epoch).  scratch: local memory,
+ * runit_moe_ep_prefill_scratch_bytes, 1024-byte aligned.  x / residual / out: f32 [T][h]; idx_out / w_out may be NULL. */
+size_t  runit_moe_ep_prefill_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, uint32_t world);
+int32_t runit_moe_layer_q4k_bf16_ep(runit_ctx_t*, const void* router_w, const void* gate_local, const void* up_local,
+                                    const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,
+                                    void* scratch, size_t scratch_bytes, void* const* recv_rows_all, void* const* recv_meta_all,
+                                    void* const* recv_counts_all, void* const* return_rows_all, void* const* signal_pads, uint32_t T,
+                                    uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm, uint32_t world, uint32_t rank,
+                                    uint32_t epoch, int32_t placement);
 /* One-kernel barrier over peer memory.  signal_pads: HOST array of `world` DEVICE pointers, entry p = rank p's pad of at
  * least `world` uint32 words (zero before the first use), as mapped into this process.  Announces `epoch` (> 0,
  * strictly increasing from call to call) to every rank and waits until every rank has announced it; a rank that does

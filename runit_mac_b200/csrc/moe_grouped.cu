@@ -500,6 +500,18 @@ __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ x
     }
 }
 
+// The same permutation for rows that are bf16 already (slots received from other ranks): xperm[pos(s)][:] = x[s][:].
+__global__ void __launch_bounds__(256) gather_bf16_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ pos_of_slot,
+                                                           __nv_bfloat16* __restrict__ xperm, uint32_t S, uint32_t h) {
+    const uint32_t s = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (s >= S) return;
+    const int32_t pos = pos_of_slot[s];
+    if (pos < 0) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)s * h);
+    uint4* dst = reinterpret_cast<uint4*>(xperm + (size_t)pos * h);
+    for (uint32_t c = lane; c < h / 8; c += 32) dst[c] = src[c];
+}
+
 // out[t] = (residual ? residual[t] : 0) + sum_i w[t][i] * y[pos(t, i)]   (routing order; product and sum rounded
 // separately, like the reference's scale-accumulate followed by the residual add).
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ pos_of_slot,
@@ -582,9 +594,11 @@ static int32_t launch_pair(runit_ctx* ctx, const char* name, const Args& a, cons
 }
 
 // The expert part of the block for given routing (idx int32 [T][k], w f32 [T][k]).
+// x_bf16 != nullptr: the rows are bf16 already, one per slot (k == 1); out == nullptr: the weighted sum is left to the
+// caller, who finds the expert outputs in s.y at row s.pos_of_slot[slot].
 static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, const void* up, const void* down,
                             const float* x, const int32_t* idx, const float* w, const float* residual, float* out,
-                            uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k) {
+                            uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, const void* x_bf16 = nullptr) {
     const uint32_t S = T * k;
     RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(s.counts, 0, 4 * 256, ctx->stream));
     count_kernel<<<(S + 4095) / 4096, 256, 0, ctx->stream>>>(idx, S, E, s.counts, s.pos_of_slot);
@@ -593,7 +607,8 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
     place_kernel<<<E, 1024, 0, ctx->stream>>>(idx, S, E, s.counts, pair::kTokPair, s.pos_of_slot, s.tile_expert,
                                               s.tile_nvalid, s.tile_row0, s.n_tok_tiles);
     if ((st = runit_after_launch(ctx, "moe_grouped_place")) != RUNIT_OK) return st;
-    gather_kernel<<<(S + 7) / 8, 256, 0, ctx->stream>>>(x, s.pos_of_slot, s.xperm, S, h, k);
+    if (x_bf16) gather_bf16_kernel<<<(S + 7) / 8, 256, 0, ctx->stream>>>((const __nv_bfloat16*)x_bf16, s.pos_of_slot, s.xperm, S, h);
+    else gather_kernel<<<(S + 7) / 8, 256, 0, ctx->stream>>>(x, s.pos_of_slot, s.xperm, S, h, k);
     if ((st = runit_after_launch(ctx, "moe_grouped_gather")) != RUNIT_OK) return st;
 
     const uint32_t rows = s.max_tiles * kTok + 256;
@@ -607,6 +622,7 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
     a2.out = s.y; a2.ld = h; a2.status = ctx->d_status;
     if ((st = launch_pair<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, E, s.max_tiles * (ff / 128))) != RUNIT_OK) return st;
     if ((st = launch_pair<false>(ctx, "moe_grouped_down", a2, s.act, rows, E, s.max_tiles * (h / 256))) != RUNIT_OK) return st;
+    if (!out) return RUNIT_OK;
     combine_kernel<<<dim3((h / 4 + 255) / 256, T), 256, 0, ctx->stream>>>(s.y, s.pos_of_slot, w, residual, out, h, k);
     return runit_after_launch(ctx, "moe_grouped_combine");
 }
@@ -631,6 +647,30 @@ __global__ void dense_tiles_kernel(uint32_t T, int32_t* tile_expert, int32_t* ti
 }
 
 }  // namespace gg
+
+// Expert outputs of S slots whose rows are bf16 already (slot s: expert idx[s] of the E local ones, or an id outside
+// [0, E) for an unused slot): the two grouped GEMMs without the weighted sum.  *y_out is the f32 output [rows][h] in the
+// permuted order, *pos_out the row of every slot (-1 for unused slots); both live inside `scratch`
+// (runit_moe_grouped_scratch_bytes(S, h, ff, E, 1) bytes, 1024-byte aligned).
+int32_t moe_grouped_slots_bf16(runit_ctx* ctx, const void* gate, const void* up, const void* down, const void* x_bf16,
+                               const int32_t* idx, void* scratch, size_t scratch_bytes, uint32_t S, uint32_t h, uint32_t ff, uint32_t E,
+                               const float** y_out, const int32_t** pos_out) {
+    int32_t st = gg::check_shapes(ctx, "moe_grouped_slots_bf16", S, h, ff, E, 1);
+    if (st != RUNIT_OK) return st;
+    const gg::Scratch s = gg::carve(scratch, S, h, ff, E, 1);
+    if (s.bytes > scratch_bytes)
+        return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "moe_grouped_slots_bf16: scratch has %zu bytes, needs %zu", scratch_bytes, s.bytes);
+    *y_out = s.y;
+    *pos_out = s.pos_of_slot;
+    return gg::experts_impl(ctx, s, gate, up, down, nullptr, idx, nullptr, nullptr, nullptr, S, h, ff, E, 1, x_bf16);
+}
+
+// The weighted sum of the batched block by itself: out[t] = residual[t] + sum_i w[t][i] * y[pos_of_slot[t*k+i]].
+int32_t moe_grouped_combine(runit_ctx* ctx, const float* y, const int32_t* pos_of_slot, const float* w, const float* residual, float* out,
+                            uint32_t T, uint32_t h, uint32_t k) {
+    gg::combine_kernel<<<dim3((h / 4 + 255) / 256, T), 256, 0, ctx->stream>>>(y, pos_of_slot, w, residual, out, h, k);
+    return runit_after_launch(ctx, "moe_grouped_combine");
+}
 
 // Tile tables for dense_gemm_q4k_bf16 over T tokens: `tables` holds 3 * ceil(T / 256) + 4 int32.
 int32_t dense_tiles_prepare(runit_ctx* ctx, int32_t* tables, uint32_t T) {

@@ -271,6 +271,7 @@ _TWINS = [
     ("gemv_allgather_f32", "no twin: (fmt, w_local, x, y_all[world] pointer table, world, rank, rows_total, k)"),
     ("peer_barrier", "no twin: (signal_pads[world] pointer table, world, rank, epoch)"),
     ("moe_layer_q4k_ep", "no twin: expert-parallel decode block with replicated tokens, combine fused over peer memory"),
+    ("moe_layer_q4k_bf16_ep", "no twin: expert-parallel batched block, token rows exchanged by peer stores"),
     ("fill_weights", "no twin: (fmt, dst, n_blocks, seed, sigma)"),
     ("fill_weights_q4k_zero_mean", "no twin: (dst, n_blocks, seed, sigma), Q4_K blocks with zero-mean weights"),
     ("fill_normal_f32", "no twin: (dst, n, seed, sigma)"),

@@ -284,6 +284,54 @@ class FusedGreedyLmHead:
         return self.token
 
 
+class FusedEpPrefillMoe:
+    """Expert-parallel MoE block for prefill-sized batches with the exchange done by the library's own kernels: every
+    rank routes its T tokens, stores each (token, expert) row into the receive buffer of the expert's owner (peer stores
+    into symmetric memory), the owners run the grouped tensor-core GEMMs over what they received and store the outputs
+    back into the senders' slots; two barrier kernels, no host read, no collective library call.  The NCCL variant with
+    torch indexing is `ep_moe_forward_counted`.  placement 1 puts expert e on rank e % world (spreads a popularity that
+    falls with the expert index), 0 on rank e // (E / world)."""
+
+    def __init__(self, R, ctx, torch, dist, router, gate_local, up_local, down_local, E, h, ff, k, renorm, world, rank, T, placement=0):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        self.R, self.ctx, self.torch = R, ctx, torch
+        self.w = (router, gate_local, up_local, down_local)
+        self.E, self.h, self.ff, self.k, self.renorm, self.world, self.rank, self.T = E, h, ff, k, renorm, world, rank, T
+        self.placement = placement
+        S = T * k
+        self.recv_rows = symm.empty(world * S * h, dtype=torch.bfloat16, device="cuda")
+        self.recv_meta = symm.empty(world * S * 2, dtype=torch.int32, device="cuda")
+        self.recv_counts = symm.empty(64, dtype=torch.int32, device="cuda")
+        self.return_rows = symm.empty(S * h, dtype=torch.float32, device="cuda")
+        self.pad = symm.empty(64, dtype=torch.int32, device="cuda")
+        self.pad.zero_()
+        self.recv_counts.zero_()
+        torch.cuda.synchronize()
+        group = dist.group.WORLD
+        self._handles = [symm.rendezvous(t, group) for t in (self.recv_rows, self.recv_meta, self.recv_counts, self.return_rows, self.pad)]
+        self.tables = [(C.c_void_p * world)(*[int(p) for p in hnd.buffer_ptrs]) for hnd in self._handles]
+        self.scratch_bytes = ctx.lib.runit_moe_ep_prefill_scratch_bytes(T, h, ff, E, k, world)
+        self.scratch = ctx.new_buffer(self.scratch_bytes)
+        self.out = torch.empty(T, h, dtype=torch.float32, device="cuda")
+        self.idx = torch.empty(T, k, dtype=torch.int32, device="cuda")
+        self.wts = torch.empty(T, k, dtype=torch.float32, device="cuda")
+        self.epoch = 0
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def __call__(self, x, residual=None):
+        """x: f32 [T][h], this rank's tokens.  Returns (out [T][h], idx [T][k], weights [T][k])."""
+        assert x.shape[0] == self.T
+        self.epoch += 1
+        router, gate, up, down = self.w
+        rows, meta, counts, ret, pads = self.tables
+        self.R.moe_layer_q4k_bf16_ep(self.ctx, router, gate, up, down, x, residual, self.out, self.idx, self.wts, self.scratch,
+                                     self.scratch_bytes, rows, meta, counts, ret, pads, self.T, self.h, self.ff, self.E, self.k,
+                                     int(self.renorm), self.world, self.rank, self.epoch, self.placement)
+        return self.out, self.idx, self.wts
+
+
 class FusedEpDecodeMoe:
     """Expert-parallel MoE block for decode sizes with replicated tokens: every rank routes the tokens itself, runs the
     experts it owns and stores its weighted partial sums into every rank's buffer (peer stores into symmetric memory);

@@ -75,6 +75,33 @@ def run_rank(rank, world, port, q):
         ctx.flush()
         for tk, yw in zip(toks, want):
             assert int(tk.item()) == int(torch.argmax(yw).item()), "sharded greedy lm_head differs from argmax of the gathered logits"
+    if world > 1:
+        # prefill-size block with the library's own dispatch (peer stores, two barrier kernels): this rank's tokens through
+        # the expert-parallel block, twice per placement, against the single-GPU batched block over all experts: same bits
+        T2, rb2 = 96, O.row_bytes(O.Q4K, H)
+        rngp = np.random.default_rng(77 + rank)
+        xp = torch.from_numpy(rngp.normal(0, 1, (T2, H)).astype(np.float32)).cuda()
+        resp = torch.from_numpy(rngp.normal(0, 1, (T2, H)).astype(np.float32)).cuda()
+        full = {n: torch.from_numpy(d[n]).cuda() for n in ("gate", "up", "down")}
+        router_t = torch.from_numpy(d["router"]).cuda()
+        nbg = R.moe_grouped_scratch_bytes(ctx, T2, H, FF, E, K_TOP)
+        sg = ctx.new_buffer(nbg)
+        ref_out = torch.empty(T2, H, device="cuda")
+        ref_idx = torch.empty(T2, K_TOP, dtype=torch.int32, device="cuda")
+        R.moe_layer_q4k_bf16(ctx, router_t, full["gate"], full["up"], full["down"], xp, resp, ref_out, ref_idx, None, sg, nbg, T2, H, FF, E,
+                             K_TOP, 0)
+        ctx.flush()
+        for placement in (0, 1):
+            own = [e for e in range(E) if (e % world if placement else e // nl) == rank]
+            pick = lambda a, per: torch.from_numpy(np.concatenate([a.reshape(E, per)[e] for e in own])).cuda()
+            epp = P.FusedEpPrefillMoe(R, ctx, torch, dist, router_t, pick(d["gate"], FF * rb_h), pick(d["up"], FF * rb_h),
+                                      pick(d["down"], H * rb_ff), E, H, FF, K_TOP, False, world, rank, T2, placement=placement)
+            for _ in range(2):
+                o, i_p, _w = epp(xp, resp)
+                ctx.flush()
+                assert torch.equal(i_p, ref_idx), "expert-parallel prefill block routes differently"
+                assert torch.equal(o, ref_out), "expert-parallel prefill block differs from the single-GPU batched block"
+            dist.barrier()
     out_ep = None
     if world > 1:
         # decode-size block with replicated tokens and the combine fused over peer memory: three calls in a row give the
