@@ -719,6 +719,20 @@ def run_expert_parallel_prefill(R, ctx, torch, dist, stream, rank, world, steps=
             bias = torch.randn(h, device="cuda", generator=torch.Generator(device="cuda").manual_seed(6))
             router = router + (2.5 / torch.arange(1, E + 1, device="cuda", dtype=torch.float32) ** 0.5)[:, None] * bias[None, :] / h
             xb = x + bias[None, :]
+            # one GPU, all experts, all T_total tokens with the same router and token distribution: what the split has to beat
+            gate1, up1 = ctx.new_buffer(E * ff * rb(h)), ctx.new_buffer(E * ff * rb(h))
+            down1 = ctx.new_buffer(E * h * rb(ff))
+            for i, (b, rows, kk) in enumerate(((gate1, E * ff, h), (up1, E * ff, h), (down1, E * h, ff))):
+                R.fill_weights(ctx, 2, b, rows * (kk // 256), 377 + i, 0.01)
+            x1 = torch.randn(T_total, h, device="cuda", generator=g) + bias[None, :]
+            o1 = torch.empty(T_total, h, device="cuda")
+            nb1 = R.moe_grouped_scratch_bytes(ctx, T_total, h, ff, E, k)
+            s1 = ctx.new_buffer(nb1)
+            ms_1 = _time_steps(torch, dist, stream, ctx, lambda: R.moe_layer_q4k_bf16(ctx, router, gate1, up1, down1, x1, None, o1, None, None,
+                                                                                      s1, nb1, T_total, h, ff, E, k, 0), steps, world)
+            native["one_gpu_all_tokens_same_router_ms"] = ms_1
+            for b in (gate1, up1, down1, s1):
+                b.free()
             for placement in (0, 1):
                 epp = P.FusedEpPrefillMoe(R, ctx, torch, dist, router, gate, up, down, E, h, ff, k, False, world, rank, T, placement=placement)
                 ms_n = _time_steps(torch, dist, stream, ctx, lambda: epp(xb), steps, world)

@@ -12,8 +12,9 @@
 //   4 barrier      peer_barrier_kernel (bounded wait, sticky give-up)
 //   5 fix up       the owner turns the count tables into one expert id per receive row (-1 past a region's count)
 //   6 experts      the two grouped tcgen05 GEMMs of the batched block over the receive rows
-//   7 return       one warp per used receive row: the f32 expert output goes back into the slot it came from, in the
-//                  memory of the rank that sent it
+//   7 return       fused into the second GEMM: its epilogue stores every f32 expert output straight into the slot it came
+//                  from, in the memory of the rank that sent it (a table of row destinations, built from 5), so the
+//                  transfer runs under the GEMM
 //   8 barrier
 //   9 weighted sum out[t] = residual[t] + sum_i w[t][i] * y[t*k+i] in routing order (the batched block's kernel)
 // A receive buffer is only written between a rank's barrier 8 of one call and barrier 4 of the next, and only read
@@ -34,7 +35,8 @@ int32_t moe_router(runit_ctx* ctx, const float* router_w, const float* x, float*
 int32_t moe_topk(runit_ctx* ctx, const float* logits, uint32_t E, uint32_t k, int32_t renorm, uint32_t T, int32_t* idx, float* w);
 int32_t moe_grouped_slots_bf16(runit_ctx* ctx, const void* gate, const void* up, const void* down, const void* x_bf16,
                                const int32_t* idx, void* scratch, size_t scratch_bytes, uint32_t S, uint32_t h, uint32_t ff, uint32_t E,
-                               const float** y_out, const int32_t** pos_out);
+                               const float** y_out, const int32_t** pos_out, const void* ret_meta, const int32_t* ret_cnt,
+                               void* const* ret_rows_all, uint32_t world, uint32_t cap_src);
 int32_t moe_grouped_combine(runit_ctx* ctx, const float* y, const int32_t* pos_of_slot, const float* w, const float* residual, float* out,
                             uint32_t T, uint32_t h, uint32_t k);
 
@@ -90,21 +92,6 @@ __global__ void __launch_bounds__(256) fixup_kernel(const int2* __restrict__ met
     if (i >= total) return;
     const uint32_t r = i / cap_src, j = i - r * cap_src;
     idx_local[i] = j < (uint32_t)cnt[r] ? meta[i].x : -1;
-}
-
-// Expert output of every used receive row back into the slot of the rank it came from.
-__global__ void __launch_bounds__(256) return_kernel(const float* __restrict__ y, const int32_t* __restrict__ pos_of_slot,
-                                                      const int2* __restrict__ meta, const int32_t* __restrict__ cnt, const Peers ry,
-                                                      uint32_t cap_src, uint32_t total, uint32_t h) {
-    const uint32_t i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (i >= total) return;
-    const uint32_t r = i / cap_src, j = i - r * cap_src;
-    if (j >= (uint32_t)cnt[r]) return;
-    const int32_t pos = pos_of_slot[i];
-    if (pos < 0) return;
-    const float4* src = reinterpret_cast<const float4*>(y + (size_t)pos * h);
-    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(ry.p[r]) + (size_t)meta[i].y * h);
-    for (uint32_t c = lane; c < h / 4; c += 32) dst[c] = __ldg(src + c);
 }
 
 __global__ void __launch_bounds__(256) iota_kernel(int32_t* p, uint32_t n) {
@@ -205,11 +192,10 @@ int32_t runit_moe_layer_q4k_bf16_ep(runit_ctx_t* ctx, const void* router_w, cons
     if ((st = runit_after_launch(ctx, "moe_ep_prefill_fixup"))) return st;
     const float* y = nullptr;
     const int32_t* pos = nullptr;
+    // the down GEMM's epilogue stores every expert output straight into the slot of the rank it came from
     if ((st = moe_grouped_slots_bf16(ctx, gate_local, up_local, down_local, rx.p[rank], l.idx_local, l.grouped, l.grouped_bytes, total, h, ff,
-                                     n_local, &y, &pos)))
+                                     n_local, &y, &pos, meta, cnt, return_rows_all, world, cap_src)))
         return st;
-    epp::return_kernel<<<(total + 7) / 8, 256, 0, ctx->stream>>>(y, pos, meta, cnt, ry, cap_src, total, h);
-    if ((st = runit_after_launch(ctx, "moe_ep_prefill_return"))) return st;
     if ((st = peer_barrier_launch(ctx, signal_pads, world, rank, 2 * epoch, nullptr))) return st;
     return moe_grouped_combine(ctx, (const float*)ry.p[rank], l.iota, w, (const float*)residual, (float*)out, T, h, k);
 }

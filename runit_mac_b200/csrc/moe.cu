@@ -45,6 +45,69 @@ __global__ void __launch_bounds__(256) router_f32_kernel(const float* __restrict
     }
 }
 
+// The same product for many tokens: a tiled f32 GEMM (CTA: TM tokens x 64 experts, thread: TM/16 x 4, K in chunks of 32
+// through shared memory; TM = 32 when 64-token tiles would leave SMs idle).  Every logit is one fused multiply-add chain
+// over k in ascending order, whatever the tile.
+template <int TM>
+__global__ void __launch_bounds__(256) router_f32_tiled_kernel(const float* __restrict__ w, const float* __restrict__ x,
+                                                                float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
+    constexpr int RT = TM / 16;                  // token rows per thread
+    __shared__ __align__(16) float xs[32][TM + 4];   // [k][token]
+    __shared__ __align__(16) float ws[32][68];       // [k][expert]
+    const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const uint32_t e0 = blockIdx.x * 64, t0 = blockIdx.y * TM;
+    float acc[RT][4];
+#pragma unroll
+    for (int i = 0; i < RT; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (uint32_t kc = 0; kc < K; kc += 32) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const uint32_t i = tid + 256 * j, row = i >> 3, kq = i & 7;
+            float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (e0 + row < E) wv = *reinterpret_cast<const float4*>(w + (size_t)(e0 + row) * K + kc + kq * 4);
+            ws[kq * 4][row] = wv.x; ws[kq * 4 + 1][row] = wv.y; ws[kq * 4 + 2][row] = wv.z; ws[kq * 4 + 3][row] = wv.w;
+            if (row < TM) {
+                float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t0 + row < T) xv = *reinterpret_cast<const float4*>(x + (size_t)(t0 + row) * K + kc + kq * 4);
+                xs[kq * 4][row] = xv.x; xs[kq * 4 + 1][row] = xv.y; xs[kq * 4 + 2][row] = xv.z; xs[kq * 4 + 3][row] = xv.w;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 32; kk++) {
+            float av[RT];
+            if constexpr (RT == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(&xs[kk][ty * 4]);
+                av[0] = a.x; av[1] = a.y; av[2] = a.z; av[3] = a.w;
+            } else {
+                const float2 a = *reinterpret_cast<const float2*>(&xs[kk][ty * 2]);
+                av[0] = a.x; av[1] = a.y;
+            }
+            const float4 b = *reinterpret_cast<const float4*>(&ws[kk][tx * 4]);
+            const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < RT; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(bv[j], av[i], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RT; i++) {
+        const uint32_t t = t0 + ty * RT + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t e = e0 + tx * 4 + j;
+            if (e < E) logits[(size_t)t * E + e] = acc[i][j];
+        }
+    }
+}
+
 // Generic fallback for any K (multiple of 4).
 __global__ void __launch_bounds__(256) router_f32_generic_kernel(const float* __restrict__ w, const float* __restrict__ x,
                                                                   float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
@@ -303,6 +366,14 @@ static MoeScratch moe_carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uin
 
 // Shared with the batched block (moe_grouped.cu).
 int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
+    if (T >= 32 && K % 32 == 0 && runit_aligned(w, 16) && runit_aligned(x, 16)) {
+        const uint32_t ge = (E + 63) / 64;
+        if (ge * ((T + 63) / 64) >= (uint32_t)ctx->sm_count)
+            runit_launch_chain(ctx, router_f32_tiled_kernel<64>, dim3(ge, (T + 63) / 64), dim3(256), w, x, logits, E, K, T);
+        else
+            runit_launch_chain(ctx, router_f32_tiled_kernel<32>, dim3(ge, (T + 31) / 32), dim3(256), w, x, logits, E, K, T);
+        return runit_after_launch(ctx, "moe_router_f32_tiled");
+    }
     dim3 grid((E + 7) / 8, T < 64 ? T : 64);
     if (K == 2048) runit_launch_chain(ctx, router_f32_kernel<64>, dim3(grid), dim3(256), w, x, logits, E, K, T);
     else if (K == 1024) runit_launch_chain(ctx, router_f32_kernel<32>, dim3(grid), dim3(256), w, x, logits, E, K, T);

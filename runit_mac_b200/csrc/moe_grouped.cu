@@ -50,6 +50,10 @@ struct Args {
     const int32_t* n_tok_tiles;   // device-resident count
     void* out;                    // bf16 [rows_padded][ld] (fused gate/up) or f32 [rows_padded][ld]
     uint32_t ld;
+    // f32 output only: when not null, row r of the permuted order is stored at row_ptr[r] instead of out + r * ld.  The
+    // pointers may lie in another GPU's memory (plain stores): the expert outputs of an expert-parallel block go straight
+    // back to the ranks that sent the tokens while the GEMM is still running.
+    float* const* row_ptr;
     int32_t* status;
 };
 
@@ -322,9 +326,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_b, const __grid
                 } else {
                     float* out = reinterpret_cast<float*>(a.out);
                     const uint32_t col = rb * 256 + rank * 128 + quarter * 32 + lane;
+                    if (a.row_ptr != nullptr) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (cg * 32 + i < nvalid) out[(row0 + cg * 32 + i) * a.ld + col] = __uint_as_float(v[i]);
+                        for (int i = 0; i < 32; i++)
+                            if (cg * 32 + i < nvalid) a.row_ptr[row0 + cg * 32 + i][col] = __uint_as_float(v[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (cg * 32 + i < nvalid) out[(row0 + cg * 32 + i) * a.ld + col] = __uint_as_float(v[i]);
+                    }
                 }
             }
             tc_fence_before_sync();
@@ -512,6 +522,22 @@ __global__ void __launch_bounds__(256) gather_bf16_kernel(const __nv_bfloat16* _
     for (uint32_t c = lane; c < h / 8; c += 32) dst[c] = src[c];
 }
 
+// Destination of every permuted row of an expert-parallel block: receive row i (region r = i / cap_src of rank r, used
+// while i % cap_src < cnt[r]) came from slot meta[i].y of rank r and goes back to row meta[i].y of that rank's return buffer.
+struct ReturnPeers {
+    float* p[8];
+};
+__global__ void __launch_bounds__(256) row_ptr_kernel(const int32_t* __restrict__ pos_of_slot, const int2* __restrict__ meta,
+                                                       const int32_t* __restrict__ cnt, const ReturnPeers ry, float** __restrict__ table,
+                                                       uint32_t cap_src, uint32_t total, uint32_t h) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const uint32_t r = i / cap_src, j = i - r * cap_src;
+    if (j >= (uint32_t)cnt[r]) return;
+    const int32_t pos = pos_of_slot[i];
+    if (pos >= 0) table[pos] = ry.p[r] + (size_t)meta[i].y * h;
+}
+
 // out[t] = (residual ? residual[t] : 0) + sum_i w[t][i] * y[pos(t, i)]   (routing order; product and sum rounded
 // separately, like the reference's scale-accumulate followed by the residual add).
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ pos_of_slot,
@@ -598,7 +624,10 @@ static int32_t launch_pair(runit_ctx* ctx, const char* name, const Args& a, cons
 // caller, who finds the expert outputs in s.y at row s.pos_of_slot[slot].
 static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, const void* up, const void* down,
                             const float* x, const int32_t* idx, const float* w, const float* residual, float* out,
-                            uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, const void* x_bf16 = nullptr) {
+                            uint32_t T, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, const void* x_bf16 = nullptr,
+                            // expert-parallel return fused into the down GEMM: see row_ptr_kernel (cap_src > 0 turns it on)
+                            const int2* ret_meta = nullptr, const int32_t* ret_cnt = nullptr, const ReturnPeers* ret_peers = nullptr,
+                            uint32_t cap_src = 0) {
     const uint32_t S = T * k;
     RUNIT_CUDA_TRY(ctx, cudaMemsetAsync(s.counts, 0, 4 * 256, ctx->stream));
     count_kernel<<<(S + 4095) / 4096, 256, 0, ctx->stream>>>(idx, S, E, s.counts, s.pos_of_slot);
@@ -620,6 +649,13 @@ static int32_t experts_impl(runit_ctx* ctx, const Scratch& s, const void* gate, 
     a2.w0 = (const uint8_t*)down; a2.w1 = nullptr; a2.rows = h; a2.K = ff; a2.nb = h / kRows;
     a2.tile_expert = s.tile_expert; a2.tile_nvalid = s.tile_nvalid; a2.tile_row0 = s.tile_row0; a2.n_tok_tiles = s.n_tok_tiles;
     a2.out = s.y; a2.ld = h; a2.status = ctx->d_status;
+    if (cap_src > 0) {
+        // the table of row destinations lives in the output area the GEMM no longer writes (8 bytes per row of 4*h)
+        float** table = reinterpret_cast<float**>(s.y);
+        row_ptr_kernel<<<(S + 255) / 256, 256, 0, ctx->stream>>>(s.pos_of_slot, ret_meta, ret_cnt, *ret_peers, table, cap_src, S, h);
+        if ((st = runit_after_launch(ctx, "moe_grouped_row_ptr")) != RUNIT_OK) return st;
+        a2.row_ptr = table;
+    }
     if ((st = launch_pair<true>(ctx, "moe_grouped_gate_up", a1, s.xperm, rows, E, s.max_tiles * (ff / 128))) != RUNIT_OK) return st;
     if ((st = launch_pair<false>(ctx, "moe_grouped_down", a2, s.act, rows, E, s.max_tiles * (h / 256))) != RUNIT_OK) return st;
     if (!out) return RUNIT_OK;
@@ -652,9 +688,12 @@ __global__ void dense_tiles_kernel(uint32_t T, int32_t* tile_expert, int32_t* ti
 // [0, E) for an unused slot): the two grouped GEMMs without the weighted sum.  *y_out is the f32 output [rows][h] in the
 // permuted order, *pos_out the row of every slot (-1 for unused slots); both live inside `scratch`
 // (runit_moe_grouped_scratch_bytes(S, h, ff, E, 1) bytes, 1024-byte aligned).
+// ret_*: the outputs go straight into the return buffers of the ranks the rows came from (row_ptr_kernel), *y_out is
+// then unused.
 int32_t moe_grouped_slots_bf16(runit_ctx* ctx, const void* gate, const void* up, const void* down, const void* x_bf16,
                                const int32_t* idx, void* scratch, size_t scratch_bytes, uint32_t S, uint32_t h, uint32_t ff, uint32_t E,
-                               const float** y_out, const int32_t** pos_out) {
+                               const float** y_out, const int32_t** pos_out, const void* ret_meta, const int32_t* ret_cnt,
+                               void* const* ret_rows_all, uint32_t world, uint32_t cap_src) {
     int32_t st = gg::check_shapes(ctx, "moe_grouped_slots_bf16", S, h, ff, E, 1);
     if (st != RUNIT_OK) return st;
     const gg::Scratch s = gg::carve(scratch, S, h, ff, E, 1);
@@ -662,6 +701,12 @@ int32_t moe_grouped_slots_bf16(runit_ctx* ctx, const void* gate, const void* up,
         return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "moe_grouped_slots_bf16: scratch has %zu bytes, needs %zu", scratch_bytes, s.bytes);
     *y_out = s.y;
     *pos_out = s.pos_of_slot;
+    if (ret_rows_all) {
+        gg::ReturnPeers rp{};
+        for (uint32_t p = 0; p < world && p < 8; p++) rp.p[p] = (float*)ret_rows_all[p];
+        return gg::experts_impl(ctx, s, gate, up, down, nullptr, idx, nullptr, nullptr, nullptr, S, h, ff, E, 1, x_bf16, (const int2*)ret_meta,
+                                ret_cnt, &rp, cap_src);
+    }
     return gg::experts_impl(ctx, s, gate, up, down, nullptr, idx, nullptr, nullptr, nullptr, S, h, ff, E, 1, x_bf16);
 }
 
