@@ -170,7 +170,8 @@ class GemvSet:
 
 def measure_batch8(R, ctx, torch, stream, gset, reps=5):
     """The same GEMV set at batch 8 (the second batch size of the configuration): every matrix is streamed once for 8
-    activation rows (integer tensor-core path of gemv_imma.cu); q, k, v and gate, up are separate launches here.
+    activation rows (integer tensor-core path of gemv_imma.cu); q | k | v and gate | up are one launch each, their
+    activations are prepared once.
     Returns (GB/s on the algorithmic bytes, launches per token)."""
     B = 8
     fmt = gset.fmt
@@ -184,12 +185,9 @@ def measure_batch8(R, ctx, torch, stream, gset, reps=5):
 
     def run():
         for w in gset.w:
-            R.gemv_batched_f32(ctx, fmt, w["q"], xn, q, None, Q_DIM, HIDDEN, B)
-            R.gemv_batched_f32(ctx, fmt, w["k"], xn, kk, None, KV_DIM, HIDDEN, B)
-            R.gemv_batched_f32(ctx, fmt, w["v"], xn, v, None, KV_DIM, HIDDEN, B)
+            R.gemv_batched_multi_f32(ctx, fmt, (w["q"], w["k"], w["v"]), xn, (q, kk, v), (Q_DIM, KV_DIM, KV_DIM), HIDDEN, B)
             R.gemv_batched_f32(ctx, fmt, w["o"], q, x, x, HIDDEN, Q_DIM, B)
-            R.gemv_batched_f32(ctx, fmt, w["gate"], xn, gate, None, INTER, HIDDEN, B)
-            R.gemv_batched_f32(ctx, fmt, w["up"], xn, up, None, INTER, HIDDEN, B)
+            R.gemv_batched_multi_f32(ctx, fmt, (w["gate"], w["up"]), xn, (gate, up), (INTER, INTER), HIDDEN, B)
             R.gemv_batched_f32(ctx, fmt, w["down"], act, x, x, HIDDEN, INTER, B)
         R.gemv_batched_f32(ctx, fmt, gset.lm_head, xn, logits, None, VOCAB, HIDDEN, B)
     run()
@@ -1062,7 +1060,14 @@ def main():
                     line["partitioned"] = {"lm_head_q4k_row_sharded_us": lh.get("us_per_call_fused_peer_stores", lh.get("us_per_call")),
                                            "lm_head_q4k_row_sharded_gbs": lh.get("aggregate_gbs_fused", lh.get("aggregate_gbs")),
                                            "olmoe_decode_expert_parallel_tok_s": ep.get("decode_tok_s"),
-                                           "qwen3_prefill_block_expert_parallel_ms": pf.get("ms_per_layer"),
+                                           "lm_head_q4k_greedy_pairs_us": lh.get("us_per_call_greedy_pairs"),
+                                           # the library's own exchange (peer stores), the better of the two expert placements,
+                                           # beside one GPU running all tokens and all experts with the same router
+                                           "qwen3_prefill_block_expert_parallel_ms": min(
+                                               [v["ms_per_layer"] for v in (pf.get("native_peer_stores") or {}).values()
+                                                if isinstance(v, dict) and "ms_per_layer" in v] or [pf.get("ms_per_layer")]),
+                                           "qwen3_prefill_block_one_gpu_ms": (pf.get("native_peer_stores") or {}).get("one_gpu_all_tokens_same_router_ms"),
+                                           "qwen3_prefill_block_nccl_torch_ms": pf.get("ms_per_layer"),
                                            "scaling": "strong (one workload split over the ranks)"}
                 print(json.dumps(line), flush=True)
             state["printed"] = True

@@ -195,6 +195,10 @@ int32_t runit_fused_ffn_q4k_f32(runit_ctx_t*, const void* w_gate, const void* w_
  * NULL); weights streamed once for the whole batch; batch in 1..8. */
 int32_t runit_gemv_batched_f32(runit_ctx_t*, int32_t fmt, const void* weight, const void* input, void* output,
                                const void* residual, uint32_t m, uint32_t k, uint32_t batch);
+/* The same for up to three matrices that share the input (q | k | v, gate | up): one launch, the activations are
+ * prepared once; outputs[i] f32 [batch][rows[i]].  (Host pointer tables of n_mats device pointers.) */
+int32_t runit_gemv_batched_multi_f32(runit_ctx_t*, int32_t fmt, uint32_t n_mats, const void* const* weights, const void* input,
+                                     void* const* outputs, const uint32_t* rows, uint32_t k, uint32_t batch);
 /* RMSNorm fused into the GEMV that consumes it: x is the un-normalised f32 vector [k], gamma f32 [k]; the matrices multiply
  * x * rsqrt(mean(x^2) + eps) * gamma (the reference runs rms_norm_f32_f32_f32g, forward.rs:1528-1569 / dispatch.rs:177, then the
  * GEMV, as two encoders).  Every CTA computes the scale itself, so the scale agrees with the stand-alone operator to
@@ -216,6 +220,9 @@ int32_t runit_gemv_argmax_f32(runit_ctx_t*, int32_t fmt, const void* weight, con
 int32_t runit_gemv_argmax_allgather(runit_ctx_t*, int32_t fmt, const void* w_local, const void* x, void* logits_local,
                                     void* const* pairs_all, uint32_t world, uint32_t rank, uint32_t rows_total, uint32_t k);
 int32_t runit_argmax_pairs(runit_ctx_t*, const void* pairs, uint32_t n, void* result);
+/* runit_peer_barrier followed by runit_argmax_pairs over this rank's own table (uint2 [world]) in one launch */
+int32_t runit_peer_barrier_argmax(runit_ctx_t*, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch,
+                                  const void* pairs, void* result);
 /* Fused Q|K|V with an f32 bias (the benchmark configuration states an f32 bias); bias may be NULL. */
 int32_t runit_fused_qkv_f32bias_q8_0_f32(runit_ctx_t*, const void* w_q, const void* w_k, const void* w_v, const void* x_vec,
                                          void* out_q, void* out_k, void* out_v, const void* bias_q, const void* bias_k,

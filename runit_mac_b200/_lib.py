@@ -19,7 +19,7 @@ _CTYPES = {
     "size_t": C.c_size_t, "float": C.c_float, "void*": C.c_void_p, "const void*": C.c_void_p,
     "const char*": C.c_char_p, "runit_ctx_t*": C.c_void_p, "runit_ctx_t**": C.POINTER(C.c_void_p),
     "void**": C.POINTER(C.c_void_p), "int32_t*": C.POINTER(C.c_int32), "uint32_t*": C.POINTER(C.c_uint32),
-    "const int32_t*": C.POINTER(C.c_int32), "const uint64_t*": C.POINTER(C.c_uint64),
+    "const int32_t*": C.POINTER(C.c_int32), "const uint64_t*": C.POINTER(C.c_uint64), "const uint32_t*": C.POINTER(C.c_uint32),
     "const runit_model_cfg*": C.c_void_p, "const runit_sampler_cfg*": C.c_void_p, "const runit_model_weights*": C.c_void_p, "runit_model_t*": C.c_void_p,
     "int32_t*": C.POINTER(C.c_int32),
     "runit_model_t**": C.POINTER(C.c_void_p), "const void* const*": C.POINTER(C.c_void_p),

@@ -453,6 +453,24 @@ int32_t runit_argmax_pairs(runit_ctx_t* ctx, const void* pairs, uint32_t n, void
     return runit_after_launch(ctx, "argmax_pairs");
 }
 
+int32_t runit_gemv_batched_multi_f32(runit_ctx_t* ctx, int32_t fmt, uint32_t n_mats, const void* const* weights, const void* input,
+                                     void* const* outputs, const uint32_t* rows, uint32_t k, uint32_t batch) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, n_mats >= 1 && n_mats <= 3 && weights && outputs && rows && input, "gemv_batched_multi_f32: 1..3 matrices, no null table");
+    RUNIT_REQUIRE(ctx, batch >= 1 && batch <= 8, "gemv_batched_multi_f32: batch=%u not in 1..8", batch);
+    bool ok = gemv_imma_applies(ctx, fmt, k, batch) && runit_aligned(input, 16) && (k / 256 * 144) % 16 == 0 && ctx->tune.gemv_variant != 1;
+    for (uint32_t i = 0; i < n_mats; i++) {
+        RUNIT_REQUIRE(ctx, weights[i] && outputs[i] && rows[i] > 0, "gemv_batched_multi_f32: null matrix or output %u", i);
+        ok = ok && runit_aligned(weights[i], 16) && runit_aligned(outputs[i], 4);
+    }
+    if (ok) return gemv_imma_multi(ctx, fmt, n_mats, weights, (const float*)input, (float* const*)outputs, nullptr, rows, k, batch);
+    for (uint32_t i = 0; i < n_mats; i++) {      // other formats and batch 1: one launch per matrix
+        const int32_t st = runit_gemv_batched_f32(ctx, fmt, weights[i], input, outputs[i], nullptr, rows[i], k, batch);
+        if (st != RUNIT_OK) return st;
+    }
+    return RUNIT_OK;
+}
+
 int32_t runit_gemv_batched_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight, const void* input, void* output,
                                const void* residual, uint32_t m, uint32_t k, uint32_t batch) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
@@ -496,32 +514,47 @@ struct PeerPads {
 // abort: device word of the context.  The first barrier that gives up sets it; while it is set every later barrier still
 // announces its epoch and advances the epoch word but does not wait, so a queue of recorded barriers behind a missing
 // rank costs one time limit in total instead of one each.  runit_flush clears it when it reports the time-out.
+// pairs != nullptr: after the barrier, lane p reads the (value, index) pair that rank p pushed into slot p of this rank's
+// table (runit_gemv_argmax_allgather) and the warp reduces them to the greedy token in *pair_result.
 __global__ void peer_barrier_kernel(const PeerPads pp, uint32_t world, uint32_t rank, uint32_t epoch, int32_t* status,
-                                    uint32_t* epoch_ptr, uint32_t* abort) {
+                                    uint32_t* epoch_ptr, uint32_t* abort, const uint2* pairs, int32_t* pair_result) {
     uint32_t* const* pads = pp.p;
     const uint32_t p = threadIdx.x;
     if (epoch_ptr) epoch = *epoch_ptr + 1u;
     const bool aborted = abort && *reinterpret_cast<volatile uint32_t*>(abort) != 0u;
     __syncwarp();
     if (p == 0 && epoch_ptr) *epoch_ptr = epoch;   // read by every lane above; the following kernels see the new value
-    if (p >= world) return;
-    // The stores of the preceding kernels (results pushed into the peers' memory) are ordered before the flag.
-    __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pads[p] + rank), "r"(epoch) : "memory");
-    if (aborted) return;
-    const uint32_t* mine = pads[rank] + p;
-    const long long t0 = clock64();
-    while (true) {
-        uint32_t v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-        if ((int32_t)(v - epoch) >= 0) break;
-        if (clock64() - t0 > (1ll << 30)) {   // about half a second: the peer never signalled
-            if (status) atomicExch(status, 3);
-            if (abort) atomicExch(abort, 1u);
-            break;
+    if (p < world) {
+        // The stores of the preceding kernels (results pushed into the peers' memory) are ordered before the flag.
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pads[p] + rank), "r"(epoch) : "memory");
+        if (!aborted) {
+            const uint32_t* mine = pads[rank] + p;
+            const long long t0 = clock64();
+            while (true) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                if ((int32_t)(v - epoch) >= 0) break;
+                if (clock64() - t0 > (1ll << 30)) {   // about half a second: the peer never signalled
+                    if (status) atomicExch(status, 3);
+                    if (abort) atomicExch(abort, 1u);
+                    break;
+                }
+                __nanosleep(200);
+            }
         }
-        __nanosleep(200);
     }
+    if (pairs == nullptr) return;
+    __syncwarp();
+    float bv = -INFINITY;
+    uint32_t bi = 0xFFFFFFFFu;
+    if (p < world) {
+        const uint2 pr = __ldcg(&pairs[p]);    // written by rank p before the flag this lane has just acquired
+        bv = __uint_as_float(pr.x);
+        bi = pr.y;
+    }
+    am_warp_reduce(bv, bi);
+    if (p == 0) pair_result[0] = (int32_t)bi;
 }
 
 int32_t runit_gemv_allgather_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_local, const void* x, void* const* y_all,
@@ -546,6 +579,13 @@ int32_t runit_gemv_allgather_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_lo
     return gemv_dispatch(ctx, c);
 }
 
+int32_t runit_peer_barrier_argmax(runit_ctx_t* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch,
+                                  const void* pairs, void* result) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, epoch > 0 && pairs && result && runit_aligned(pairs, 8) && runit_aligned(result, 4), "peer_barrier_argmax: bad argument");
+    return runit::peer_barrier_launch(ctx, signal_pads, world, rank, epoch, nullptr, pairs, (int32_t*)result);
+}
+
 int32_t runit_peer_barrier(runit_ctx_t* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, epoch > 0, "peer_barrier: epoch must be positive");
@@ -555,14 +595,16 @@ int32_t runit_peer_barrier(runit_ctx_t* ctx, void* const* signal_pads, uint32_t 
 }  // extern "C"
 
 namespace runit {
-int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr) {
+int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch, uint32_t* epoch_ptr,
+                            const void* pairs, int32_t* pair_result) {
     RUNIT_REQUIRE(ctx, signal_pads && world >= 1 && world <= 8 && rank < world && (epoch > 0 || epoch_ptr), "peer_barrier: bad argument");
     PeerPads h{};
     for (uint32_t p = 0; p < world; p++) {
         RUNIT_REQUIRE(ctx, signal_pads[p] && runit_aligned(signal_pads[p], 4), "peer_barrier: null or misaligned pad %u", p);
         h.p[p] = (uint32_t*)signal_pads[p];
     }
-    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status, epoch_ptr, ctx->d_abort);
+    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(h, world, rank, epoch, ctx->d_status, epoch_ptr, ctx->d_abort, (const uint2*)pairs,
+                                                   pair_result);
     return runit_after_launch(ctx, "peer_barrier");
 }
 }  // namespace runit

@@ -67,12 +67,18 @@ __global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict
 }
 
 // ───────────────────────── main kernel ─────────────────────────
+// Up to three matrices that share the activations (q | k | v, gate | up) ride one launch: segment i owns the row tiles
+// [tile0[i], tile0[i+1]) and has its own tensor map, row count, output and residual.
 struct Args {
     const uint8_t* xq;
-    float* y;
-    const float* res;
-    uint32_t m, units, batch, csplit;
+    float* y[3];
+    const float* res[3];
+    uint32_t m[3], tile0[3];
+    uint32_t nseg, units, batch, csplit;
     int32_t* status;
+};
+struct Maps {
+    CUtensorMap m[3];
 };
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -111,7 +117,7 @@ __device__ __forceinline__ void tile_mma(float (&acc)[4], const uint32_t (&a)[4]
 }
 
 template <int FMT, int RW>
-__global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ CUtensorMap wmap, const Args a) {
+__global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ Maps wmaps, const Args a) {
     constexpr int WBYTES = RW * 144;                       // one warp's weight box
     constexpr int STAGE = kUnitBytes + 4 * WBYTES;
     constexpr int MT = RW / 16;                            // m16 tiles per warp
@@ -123,7 +129,15 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const uint32_t crank = a.csplit > 1 ? cluster_ctarank() : 0;
     const uint32_t tile = blockIdx.x / a.csplit;
-    const uint32_t row_tile0 = tile * (4 * RW);
+    int si = 0;
+#pragma unroll
+    for (int i = 1; i < 3; i++)
+        if (i < (int)a.nseg && tile >= a.tile0[i]) si = i;
+    const CUtensorMap* wmap = &wmaps.m[si];
+    const uint32_t row_tile0 = (tile - a.tile0[si]) * (4 * RW);
+    const uint32_t seg_m = a.m[si];
+    float* const seg_y = a.y[si];
+    const float* const seg_res = a.res[si];
     const uint32_t u_begin = (uint32_t)(((uint64_t)a.units * crank) / a.csplit), u_end = (uint32_t)(((uint64_t)a.units * (crank + 1)) / a.csplit);
     const uint32_t nu = u_end - u_begin;
     const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[kStages]);
@@ -142,7 +156,7 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
         mbar_expect_tx(bar_full + 8 * s, STAGE);
 #pragma unroll
         for (int w = 0; w < 4; w++)
-            tma_load_2d(sb + kUnitBytes + w * WBYTES, &wmap, (int32_t)(u * 144), (int32_t)(row_tile0 + w * RW), bar_full + 8 * s);
+            tma_load_2d(sb + kUnitBytes + w * WBYTES, wmap, (int32_t)(u * 144), (int32_t)(row_tile0 + w * RW), bar_full + 8 * s);
     };
     auto issue_x = [&](uint32_t i) {   // its quantised activations
         const uint32_t s = i % kStages, u = u_begin + i;
@@ -243,10 +257,10 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
             float v = red[r][c];
             for (uint32_t p = 1; p < a.csplit; p++) v += ld_cluster_f32(&red[r][c], p);
             const uint32_t row = row_tile0 + r;
-            if (row < a.m && c < a.batch) {
-                const size_t o = (size_t)c * a.m + row;
-                if (a.res) v += a.res[o];
-                a.y[o] = v;
+            if (row < seg_m && c < a.batch) {
+                const size_t o = (size_t)c * seg_m + row;
+                if (seg_res) v += seg_res[o];
+                seg_y[o] = v;
             }
         }
     }
@@ -255,7 +269,7 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
 }
 
 template <int FMT, int RW>
-static int32_t launch(runit_ctx* ctx, const CUtensorMap& map, const Args& a, uint32_t tiles) {
+static int32_t launch(runit_ctx* ctx, const Maps& map, const Args& a, uint32_t tiles) {
     constexpr int smem = kStages * (kUnitBytes + 4 * RW * 144) + 128;
     auto kern = gemv_imma_kernel<FMT, RW>;
     static bool configured[16] = {false};
@@ -297,8 +311,9 @@ bool gemv_imma_applies(const runit_ctx* ctx, int fmt, uint32_t k, uint32_t batch
     return (size_t)(k / 256) * imma::kUnitBytes <= ctx->xq_bytes;
 }
 
-int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
-                  uint32_t batch) {
+// n_mats (1..3) matrices over the same activations in one launch; the activations are quantised once.
+int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* const* w, const float* x, float* const* y,
+                        const float* const* res, const uint32_t* m, uint32_t k, uint32_t batch) {
     using namespace imma;
     const uint32_t units = k / 256;
     if (fmt == RUNIT_FMT_Q4K) xq_prepare_kernel<RUNIT_FMT_Q4K><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
@@ -307,25 +322,48 @@ int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float*
     if (st != RUNIT_OK) return st;
     // rows per warp: 32 when that still gives every SM two CTAs, else 16
     const uint32_t sms = (uint32_t)ctx->sm_count;
-    const uint32_t tiles32 = (m + 127) / 128, tiles16 = (m + 63) / 64;
+    uint32_t tiles32 = 0, tiles16 = 0;
+    for (uint32_t i = 0; i < n_mats; i++) {
+        tiles32 += (m[i] + 127) / 128;
+        tiles16 += (m[i] + 63) / 64;
+    }
     const bool rw32 = tiles32 >= 2 * sms;
     const uint32_t tiles = rw32 ? tiles32 : tiles16;
     uint32_t csplit = 1;
     while (csplit < 8 && tiles * csplit < 4 * sms && units / (csplit * 2) >= 3) csplit *= 2;
     Args a{};
+    Maps maps{};
     a.xq = (const uint8_t*)ctx->d_xq;
-    a.y = y;
-    a.res = res;
-    a.m = m;
+    a.nseg = n_mats;
+    uint32_t t0 = 0;
+    for (uint32_t i = 0; i < 3; i++) {
+        const uint32_t s = i < n_mats ? i : 0;      // unused entries repeat segment 0 (never selected)
+        a.y[i] = y[s];
+        a.res[i] = res ? res[s] : nullptr;
+        a.m[i] = m[s];
+        a.tile0[i] = i < n_mats ? t0 : 0xFFFFFFFFu;
+        if (i < n_mats) {
+            st = runit_get_tmap(ctx, w[i], m[i], (uint64_t)units * 144, rw32 ? 32 : 16, 144, &maps.m[i]);
+            if (st != RUNIT_OK) return st;
+            t0 += rw32 ? (m[i] + 127) / 128 : (m[i] + 63) / 64;
+        } else {
+            maps.m[i] = maps.m[0];
+        }
+    }
     a.units = units;
     a.batch = batch;
     a.csplit = csplit;
     a.status = ctx->d_status;
-    CUtensorMap map;
-    st = runit_get_tmap(ctx, w, m, (uint64_t)units * 144, rw32 ? 32 : 16, 144, &map);
-    if (st != RUNIT_OK) return st;
-    if (fmt == RUNIT_FMT_Q4K) return rw32 ? launch<RUNIT_FMT_Q4K, 32>(ctx, map, a, tiles) : launch<RUNIT_FMT_Q4K, 16>(ctx, map, a, tiles);
-    return rw32 ? launch<RUNIT_FMT_Q4_0, 32>(ctx, map, a, tiles) : launch<RUNIT_FMT_Q4_0, 16>(ctx, map, a, tiles);
+    if (fmt == RUNIT_FMT_Q4K) return rw32 ? launch<RUNIT_FMT_Q4K, 32>(ctx, maps, a, tiles) : launch<RUNIT_FMT_Q4K, 16>(ctx, maps, a, tiles);
+    return rw32 ? launch<RUNIT_FMT_Q4_0, 32>(ctx, maps, a, tiles) : launch<RUNIT_FMT_Q4_0, 16>(ctx, maps, a, tiles);
+}
+
+int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
+                  uint32_t batch) {
+    const void* ws[1] = {w};
+    float* ys[1] = {y};
+    const float* rs[1] = {res};
+    return gemv_imma_multi(ctx, fmt, 1, ws, x, ys, rs, &m, k, batch);
 }
 
 }  // namespace runit

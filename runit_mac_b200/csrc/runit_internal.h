@@ -128,6 +128,8 @@ namespace runit {
 bool gemv_imma_applies(const runit_ctx* ctx, int fmt, uint32_t k, uint32_t batch);
 int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
                   uint32_t batch);
+int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* const* w, const float* x, float* const* y,
+                        const float* const* res, const uint32_t* m, uint32_t k, uint32_t batch);
 // gemv.cu: grouped GEMVs over stacked expert matrices (MoE block).  Slot s uses expert slot_expert[s] - expert_lo of the
 // n_experts stacked ones; an id outside that range marks an unused slot.
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
@@ -143,7 +145,7 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
                      int order = 0);
 // gemv.cu: the one-kernel barrier over peer memory behind runit_peer_barrier.
 int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch,
-                            uint32_t* epoch_ptr);
+                            uint32_t* epoch_ptr, const void* pairs = nullptr, int32_t* pair_result = nullptr);
 // moe.cu: expert-parallel decode block (runit_moe_layer_q4k_ep); epoch_ptr != nullptr keeps the epoch in a device word.
 int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* gate_local, const void* up_local,
                               const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,

@@ -246,6 +246,7 @@ _TWINS = [
     ("gemv_argmax_allgather", "no twin: row-sharded greedy lm_head (fmt, w_local, x, logits_local, pairs_all[world] pointer "
                               "table, world, rank, rows_total, k)"),
     ("argmax_pairs", "no twin: (pairs, n, result_i32)"),
+    ("peer_barrier_argmax", "no twin: (signal_pads[world], world, rank, epoch, pairs, result_i32)"),
     ("prefill_attention_f16kv", "dispatch.rs flash_attention_f16 with q_len = seq (prefill.rs:134-145): (q_f32, kcache, vcache, out_bf16, T, "
                                 "heads, kv_heads, head_dim, max_seq, start_pos)"),
     ("rms_norm_f32_f32", "dispatch.rs:152 (x, y, gamma_f16, eps, hidden, num_rows)"),
@@ -279,6 +280,15 @@ _TWINS = [
 for _n, _d in _TWINS:
     globals()[_n] = _twin(_n, _d)
 del _n, _d
+
+def gemv_batched_multi_f32(ctx: Context, fmt: int, weights, x, outputs, rows, k: int, batch: int):
+    """Up to three matrices over the same activations in one launch (q | k | v, gate | up); no twin in the reference."""
+    n = len(weights)
+    wt = (C.c_void_p * n)(*[_ptr(w) for w in weights])
+    ot = (C.c_void_p * n)(*[_ptr(o) for o in outputs])
+    rt = (C.c_uint32 * n)(*[int(r) for r in rows])
+    ctx._check(ctx.lib.runit_gemv_batched_multi_f32(ctx.handle, fmt, n, wt, _ptr(x), ot, rt, k, batch))
+
 
 class ModelCfg(C.Structure):
     """runit_model_cfg; field names follow ModelConfig (crates/engine/src/config.rs:42-89)."""
@@ -420,5 +430,5 @@ def moe_layer_q4k_host(ctx: Context, router, gate, up, down, x, *, h, ff, E, top
             w.download(np.float32, T * top_k).reshape(T, top_k))
 
 
-__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "SamplerCfg", "sample_f32", "sampler_seed_state", "moe_scratch_bytes", "moe_layer_q4k_host", "moe_grouped_scratch_bytes", "moe_layer_q4k_bf16_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
+__all__ = ["Context", "DeviceBuffer", "Graph", "KernelError", "Model", "ModelCfg", "ModelWeights", "SamplerCfg", "sample_f32", "sampler_seed_state", "gemv_batched_multi_f32", "moe_scratch_bytes", "moe_layer_q4k_host", "moe_grouped_scratch_bytes", "moe_layer_q4k_bf16_host", "row_bytes", "BLOCK_ELEMS", "BLOCK_BYTES",
            "FMT_Q8_0", "FMT_Q4_0", "FMT_Q4K", "FMT_Q5_0", "FMT_Q5K", "FMT_Q6K"] + [n for n, _ in _TWINS]

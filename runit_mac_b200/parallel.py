@@ -248,7 +248,7 @@ class FusedAllGatherGemv:
 class FusedGreedyLmHead:
     """Row-sharded greedy lm_head: every rank multiplies its rows, finds its own (largest logit, global row) pair in the
     GEMV's epilogue and stores the 8 bytes into every rank's pair table (peer stores into symmetric memory); one barrier
-    kernel, then each rank reduces the `world` pairs to the token.  8 bytes per rank cross NVLink instead of the logits.
+    kernel, whose warp then reduces the `world` pairs to the token.  8 bytes per rank cross NVLink instead of the logits.
     Two pair tables alternate from call to call, for the reason given in FusedAllGatherGemv."""
 
     def __init__(self, R, ctx, torch, dist, fmt, w_local, rows_total, k, world, rank):
@@ -279,8 +279,7 @@ class FusedGreedyLmHead:
         half = self.epoch & 1
         self.R.gemv_argmax_allgather(self.ctx, self.fmt, self.w, x, self.logits_local, self.pair_ptrs[half], self.world, self.rank,
                                      self.rows_total, self.k)
-        self.R.peer_barrier(self.ctx, self.pad_ptrs, self.world, self.rank, self.epoch)
-        self.R.argmax_pairs(self.ctx, self.pairs.data_ptr() + half * 64, self.world, self.token)
+        self.R.peer_barrier_argmax(self.ctx, self.pad_ptrs, self.world, self.rank, self.epoch, self.pairs.data_ptr() + half * 64, self.token)
         return self.token
 
 

@@ -566,3 +566,27 @@ def test_greedy_epilogue_of_the_gemv(ctx, oracle, fmt):
         logits = lb.download(np.float32, m)
         assert int(tb.download(np.int32, 1)[0]) == int(np.argmax(logits))
         assert logits[3] == logits[m // 2]
+
+
+@pytest.mark.parametrize("batch", [8, 3])
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_batched_gemv_of_several_matrices_in_one_launch(ctx, oracle, fmt, batch):
+    """q | k | v and gate | up at batch 2..8: one launch over up to three matrices that share the activations (prepared once)
+    gives what the single-matrix launches give, and the oracle's values."""
+    import runit_mac_b200 as R
+    O = oracle
+    for rows, k in (((3584, 512, 512), 3584), ((1000, 37), 2048), ((96,), 512)):
+        rng = np.random.default_rng(9000 + fmt + batch + len(rows))
+        ws = [O.rand_weights(fmt, rng, m, k) for m in rows]
+        x = rng.normal(0, 1, (batch, k)).astype(np.float32)
+        wb, xb = [ctx.buffer_from(w) for w in ws], ctx.buffer_from(x)
+        outs = [ctx.new_buffer(batch * m * 4) for m in rows]
+        R.gemv_batched_multi_f32(ctx, fmt, wb, xb, outs, rows, k, batch)
+        ctx.flush()
+        for w, m, o, b1 in zip(ws, rows, outs, wb):
+            got = o.download(np.float32, batch * m)
+            assert_close(O, O.gemv(fmt, w, x, m, k), got, what="multi batched fmt=%d %dx%d batch=%d" % (fmt, m, k, batch))
+            single = ctx.new_buffer(batch * m * 4)
+            R.gemv_batched_f32(ctx, fmt, b1, xb, single, None, m, k, batch)
+            ctx.flush()
+            assert np.array_equal(single.download(np.float32, batch * m), got)
