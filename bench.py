@@ -841,6 +841,8 @@ def main():
     ap.add_argument("--one", default="", help="fmt,m,k[,batch]: launch this one GEMV shape three times and exit (for ncu captures)")
     ap.add_argument("--block", default="", help="T: run the Qwen3-MoE-shaped batched MoE block on T tokens, print its figures and exit")
     ap.add_argument("--decode", action="store_true", help="only the OLMoE-shaped greedy decode figure (tok/s), then exit")
+    ap.add_argument("--prefill", default="", help="T: batched prefill of T tokens on a 2-layer OLMoE-shaped decoder, three times, then exit "
+                                                  "(the small case for ncu captures of the prefill kernels)")
     ap.add_argument("--shapes", action="store_true", help="per-shape GEMV table (one JSON line per shape) instead of the headline run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -881,6 +883,29 @@ def main():
             R.gemv_batched_f32(ctx, fmt, w, x, y, None, m, k, batch)
         ctx.flush()
         print(json.dumps({"one": args.one, "launches": ctx.launches}))
+        return
+    if args.prefill:
+        T = int(args.prefill)
+        L, h, E, ff = 2, 2048, 64, 1024
+        rbq = lambda kk: kk // 256 * 144
+        shapes = {"wq": (L * h, h), "wk": (L * h, h), "wv": (L * h, h), "wo": (L * h, h), "gate": (L * E * ff, h),
+                  "up": (L * E * ff, h), "down": (L * E * h, ff), "lm_head": (50304, h)}
+        dev = {}
+        for i, (name, (rows, kk)) in enumerate(shapes.items()):
+            dev[name] = ctx.new_buffer(rows * rbq(kk))
+            R.fill_weights_q4k_zero_mean(ctx, dev[name], rows * (kk // 256), 31 + i, 6e-5)
+        for name, n, sig in (("tok_emb", 50304 * h, 1.0), ("router", L * E * h, 0.02)):
+            dev[name] = ctx.new_buffer(4 * n)
+            R.fill_normal_f32(ctx, dev[name], n, 77 + len(name), sig)
+        ones = np.ones(L * h, np.float32)
+        dev["attn_norm"], dev["ffn_norm"], dev["out_norm"] = ctx.buffer_from(ones), ctx.buffer_from(ones), ctx.buffer_from(ones[:h])
+        cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=50304, n_experts=E, top_k=8, ff=ff,
+                         max_seq=max(2048, T), renorm=0, eps=1e-5, theta=10000.0)
+        model = R.Model(ctx, cfg, dev)
+        pr = np.random.default_rng(T).integers(0, 50304, T).astype(np.int32)
+        toks = [model.prefill(pr) for _ in range(3)]
+        print(json.dumps({"prefill_tokens": T, "layers": L, "next_token": toks, "launches": ctx.launches}))
+        model.close()
         return
     if args.shapes:
         return run_shapes(R, ctx, torch, stream)

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) router_f32_kernel(const float* __restrict
 }
 
 // The same product for many tokens: a tiled f32 GEMM (CTA: TM tokens x 64 experts, thread: TM/16 x 4, K in chunks of 32
-// through shared memory; TM = 32 when 64-token tiles would leave SMs idle).  Every logit is one fused multiply-add chain
+// through shared memory; TM = 32 or 16 when larger token tiles would leave SMs idle).  Every logit is one fused multiply-add chain
 // over k in ascending order, whatever the tile.
 template <int TM>
 __global__ void __launch_bounds__(256) router_f32_tiled_kernel(const float* __restrict__ w, const float* __restrict__ x,
@@ -83,9 +83,11 @@ __global__ void __launch_bounds__(256) router_f32_tiled_kernel(const float* __re
             if constexpr (RT == 4) {
                 const float4 a = *reinterpret_cast<const float4*>(&xs[kk][ty * 4]);
                 av[0] = a.x; av[1] = a.y; av[2] = a.z; av[3] = a.w;
-            } else {
+            } else if constexpr (RT == 2) {
                 const float2 a = *reinterpret_cast<const float2*>(&xs[kk][ty * 2]);
                 av[0] = a.x; av[1] = a.y;
+            } else {
+                av[0] = xs[kk][ty];
             }
             const float4 b = *reinterpret_cast<const float4*>(&ws[kk][tx * 4]);
             const float bv[4] = {b.x, b.y, b.z, b.w};
@@ -366,12 +368,17 @@ static MoeScratch moe_carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uin
 
 // Shared with the batched block (moe_grouped.cu).
 int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
-    if (T >= 32 && K % 32 == 0 && runit_aligned(w, 16) && runit_aligned(x, 16)) {
+    // measured (h = 2048, warm): the tiled kernel has a floor of about 85 us (one CTA walks all of K) and wins from about
+    // 4096 tokens x 128 experts (134 against 226 us); below that one warp per expert is faster (2048 x 64: 60 against 88 us)
+    const bool big = (uint64_t)T * E >= 400000ull;
+    if (ctx->tune.router_variant != 1 && (big || ctx->tune.router_variant == 2) && K % 32 == 0 && runit_aligned(w, 16) && runit_aligned(x, 16)) {
         const uint32_t ge = (E + 63) / 64;
         if (ge * ((T + 63) / 64) >= (uint32_t)ctx->sm_count)
             runit_launch_chain(ctx, router_f32_tiled_kernel<64>, dim3(ge, (T + 63) / 64), dim3(256), w, x, logits, E, K, T);
-        else
+        else if (ge * ((T + 31) / 32) >= (uint32_t)ctx->sm_count)
             runit_launch_chain(ctx, router_f32_tiled_kernel<32>, dim3(ge, (T + 31) / 32), dim3(256), w, x, logits, E, K, T);
+        else
+            runit_launch_chain(ctx, router_f32_tiled_kernel<16>, dim3(ge, (T + 15) / 16), dim3(256), w, x, logits, E, K, T);
         return runit_after_launch(ctx, "moe_router_f32_tiled");
     }
     dim3 grid((E + 7) / 8, T < 64 ? T : 64);

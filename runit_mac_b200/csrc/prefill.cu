@@ -119,7 +119,7 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(128) prefill_attn_kernel(const float* __restrict__ q, const __half* __restrict__ kc,
+__global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __restrict__ q, const __half* __restrict__ kc,
                                                             const __half* __restrict__ vc, __nv_bfloat16* __restrict__ out, uint32_t T,
                                                             uint32_t heads, uint32_t kv_heads, uint32_t max_seq, uint32_t start_pos,
                                                             float scale) {

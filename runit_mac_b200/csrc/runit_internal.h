@@ -23,7 +23,8 @@ struct runit_tuning {
     int32_t stream_fuse = 0;    // recorded command lists: 1 = runs of consecutive GEMVs become one persistent launch
     int32_t stream_cfg = 0;     // warps per SM x ring stages of that launch: 0 = default, 1..3 = alternatives
     int32_t stream_ksl = 0;     // 0 = warps per tile chosen per GEMV, else forced (experiments)
-    int32_t stream_dynamic = 0; // 1 = CTAs take items from a shared counter instead of the fixed split (experiments)
+    int32_t stream_dynamic = 0;
+    int32_t router_variant = 0;   // batched f32 router: 0 = by size, 1 = one warp per expert, 2 = tiled GEMM (experiments) // 1 = CTAs take items from a shared counter instead of the fixed split (experiments)
 };
 
 // Cached tensor map of one weight matrix view (encoding costs ~1 us on the host).
