@@ -96,8 +96,8 @@ __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ x, co
 // ───────────────────────── causal attention over the f16 cache, tensor cores ─────────────────────────
 // softmax(q.K^T / sqrt(hd)) . V with the causal mask key <= start_pos + query (attention.metal:36-158), online softmax.
 //   grid (ceil(T / 64), heads), 4 warps; a warp owns 16 queries, the CTA walks the keys in blocks of 64.
-//   q (f32) is rounded to f16 and kept as MMA A fragments; K and V blocks are staged in shared memory (rows padded to
-//   HD + 8 halves: ldmatrix reads without bank conflicts); S = q.K^T and O += P.V are mma.sync m16n8k16 (f16 operands,
+//   q (f32) is rounded to f16 and kept as MMA A fragments; K and V blocks are staged in shared memory by cp.async, two
+//   stages deep (rows padded to HD + 8 halves: ldmatrix reads without bank conflicts); S = q.K^T and O += P.V are mma.sync m16n8k16 (f16 operands,
 //   f32 accumulators); P is rounded to f16 for the second product, the usual flash-attention arrangement.
 //   Output bf16 [T][heads * HD]: the B operand of the output projection GEMM.
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
@@ -126,8 +126,10 @@ __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __res
     constexpr int LDS = HD + 8;                  // row pitch in halves
     constexpr int KS = HD / 16;                  // k16 steps of q.K^T
     constexpr int ND = HD / 8;                   // n8 tiles of the output
-    __shared__ __align__(16) __half Ks[64 * LDS];
-    __shared__ __align__(16) __half Vs[64 * LDS];
+    // two stages of (K block, V block): the next block is copied (cp.async) while the current one is multiplied
+    extern __shared__ __align__(16) uint8_t attn_smem[];
+    __half* const Ks = reinterpret_cast<__half*>(attn_smem);                    // [2][64 * LDS]
+    __half* const Vs = Ks + 2 * 64 * LDS;                                      // [2][64 * LDS]
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const uint32_t head = blockIdx.y, kvh = head / (heads / kv_heads);
     const uint32_t q0 = blockIdx.x * 64, ld = heads * HD;
@@ -157,22 +159,33 @@ __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __res
     const uint32_t kv_total = start_pos + T;                                   // cache rows that hold data
     const uint32_t last_q = min(T, q0 + 64) - 1;
     const uint32_t n_blocks = (start_pos + last_q) / 64 + 1;                   // key blocks any query of this CTA may see
-    const uint32_t ks_u32 = smem_u32(Ks), vs_u32 = smem_u32(Vs);
-    for (uint32_t kb = 0; kb < n_blocks; kb++) {
-        __syncthreads();                                                       // the previous block has been consumed
-        // stage K and V rows kb*64 .. +63 (rows past the data are zeros)
+    // stage K and V rows kb*64 .. +63 into buffer `buf` (rows past the data are zeros)
+    auto stage = [&](uint32_t kb, uint32_t buf) {
         constexpr int CPR = HD / 8;                                            // 16-byte chunks per row
+        __half* kd = Ks + buf * 64 * LDS;
+        __half* vd = Vs + buf * 64 * LDS;
         for (uint32_t c = tid; c < 64 * CPR; c += 128) {
             const uint32_t r = c / CPR, cc = c % CPR, key = kb * 64 + r;
-            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
             if (key < kv_total && key < max_seq) {
-                kv4 = *reinterpret_cast<const uint4*>(kbase + (size_t)key * HD + cc * 8);
-                vv4 = *reinterpret_cast<const uint4*>(vbase + (size_t)key * HD + cc * 8);
+                cp_async16(smem_u32(kd + r * LDS + cc * 8), kbase + (size_t)key * HD + cc * 8);
+                cp_async16(smem_u32(vd + r * LDS + cc * 8), vbase + (size_t)key * HD + cc * 8);
+            } else {
+                *reinterpret_cast<uint4*>(kd + r * LDS + cc * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + r * LDS + cc * 8) = make_uint4(0, 0, 0, 0);
             }
-            *reinterpret_cast<uint4*>(Ks + r * LDS + cc * 8) = kv4;
-            *reinterpret_cast<uint4*>(Vs + r * LDS + cc * 8) = vv4;
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    stage(0, 0);
+    for (uint32_t kb = 0; kb < n_blocks; kb++) {
+        if (kb + 1 < n_blocks) {
+            stage(kb + 1, (kb + 1) & 1);       // its buffer was released by the barrier that ended block kb - 1
+            cp_async_wait<1>();                // block kb has landed (for this thread's copies)
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();                       // ... and for everyone's
+        const uint32_t ks_u32 = smem_u32(Ks + (kb & 1) * 64 * LDS), vs_u32 = smem_u32(Vs + (kb & 1) * 64 * LDS);
         // S = q.K^T for 64 keys: 8 n-tiles of 8 keys
         float s[8][4];
 #pragma unroll
@@ -234,6 +247,7 @@ __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __res
                 mma_f16(o[nd + 1], pa[kt], b[2], b[3]);
             }
         }
+        __syncthreads();                       // every warp is done with buffer kb & 1: block kb + 2 may overwrite it
     }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
@@ -278,11 +292,18 @@ int32_t prefill_attention(runit_ctx* ctx, const float* q, const void* kcache, co
     RUNIT_REQUIRE(ctx, T > 0 && heads % kv_heads == 0 && (uint64_t)start_pos + T <= max_seq, "prefill_attention: bad shape");
     const float scale = 1.0f / sqrtf((float)hd);
     const dim3 grid((T + 63) / 64, heads);
+    const size_t smem = (size_t)4 * 64 * (hd + 8) * 2;      // two stages of a K and a V block
+    static bool configured[64] = {false};
+    if (ctx->device >= 0 && ctx->device < 64 && !configured[ctx->device]) {
+        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(pf::prefill_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 64 * 136 * 2));
+        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(pf::prefill_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 64 * 72 * 2));
+        configured[ctx->device] = true;
+    }
     if (hd == 128)
-        pf::prefill_attn_kernel<128><<<grid, 128, 0, ctx->stream>>>(q, (const __half*)kcache, (const __half*)vcache, (__nv_bfloat16*)out_bf16, T,
+        pf::prefill_attn_kernel<128><<<grid, 128, smem, ctx->stream>>>(q, (const __half*)kcache, (const __half*)vcache, (__nv_bfloat16*)out_bf16, T,
                                                                     heads, kv_heads, max_seq, start_pos, scale);
     else
-        pf::prefill_attn_kernel<64><<<grid, 128, 0, ctx->stream>>>(q, (const __half*)kcache, (const __half*)vcache, (__nv_bfloat16*)out_bf16, T,
+        pf::prefill_attn_kernel<64><<<grid, 128, smem, ctx->stream>>>(q, (const __half*)kcache, (const __half*)vcache, (__nv_bfloat16*)out_bf16, T,
                                                                    heads, kv_heads, max_seq, start_pos, scale);
     return runit_after_launch(ctx, "prefill_attention");
 }
