@@ -63,7 +63,7 @@ static inline int32_t launch_staged(runit_ctx* ctx, const GemvArgs& a, const Gem
     // ones are folded into one persistent launch (gemv_stream.cu).
     if constexpr (FMT != RUNIT_FMT_Q8_0 && B == 1 && !XF16 && LD == 1 && MATH == 2) {
         if (ctx->capturing && ctx->tune.stream_fuse && a.grp_expert == nullptr && a.n_peer == 0 && a.res_kind != RES_F16 &&
-            a.norm_gamma == nullptr) {
+            a.norm_gamma == nullptr && a.am_part == nullptr) {
             StreamRec r;
             memset(&r, 0, sizeof(r));
             r.func = reinterpret_cast<const void*>(kern);

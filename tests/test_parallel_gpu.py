@@ -222,6 +222,61 @@ def test_sharded_paths_match_oracle(oracle):
             assert (tok_ep == res[0][4][2][1]).all() and len(set(tok_ep[7:].tolist())) > 3 and lpt >= 1 + 2 * 10 + 2
 
 
+def test_partitioned_kernels_with_one_rank(ctx, oracle):
+    """The kernels of the partitioned paths with a group of one (every "peer" table points at this GPU's own buffers), so
+    that a single-GPU run still executes them: the greedy lm_head (pair pushed into the own table, barrier kernel that
+    reduces it) and the expert-parallel prefill block (dispatch, counts, barrier, grouped GEMMs with the return fused into
+    the epilogue, barrier, weighted sum), each against its single-GPU counterpart."""
+    import ctypes as C
+    import torch
+    import runit_mac_b200 as R
+    O = oracle
+    d = make_data(O)
+    tab = lambda t: (C.c_void_p * 1)(t.data_ptr())
+    # greedy lm_head
+    w = torch.from_numpy(d["lm"]).cuda()
+    x = torch.from_numpy(d["x_lm"]).cuda()
+    logits = torch.empty(M_ROWS, device="cuda")
+    pairs = torch.zeros(16, dtype=torch.int32, device="cuda")
+    pad = torch.zeros(64, dtype=torch.int32, device="cuda")
+    tok = torch.full((4,), -1, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2, 3):
+        R.gemv_argmax_allgather(ctx, 2, w, x, logits, tab(pairs), 1, 0, M_ROWS, K_IN)
+        R.peer_barrier_argmax(ctx, tab(pad), 1, 0, epoch, pairs, tok)
+        ctx.flush()
+        assert int(tok[0].item()) == int(torch.argmax(logits).item())
+    st = O.compare(O.gemv(O.Q4K, d["lm"], d["x_lm"], M_ROWS, K_IN), logits.cpu().numpy(), rel_tol=1e-3)
+    assert st.n_mismatch_rel == 0, st
+    # expert-parallel prefill block, world = 1, against the plain batched block: same bits
+    T = 80
+    rng = np.random.default_rng(9)
+    xp = torch.from_numpy(rng.normal(0, 1, (T, H)).astype(np.float32)).cuda()
+    res = torch.from_numpy(rng.normal(0, 1, (T, H)).astype(np.float32)).cuda()
+    router = torch.from_numpy(d["router"]).cuda()
+    gate, up, down = (torch.from_numpy(d[n]).cuda() for n in ("gate", "up", "down"))
+    nbg = R.moe_grouped_scratch_bytes(ctx, T, H, FF, E, K_TOP)
+    sg = ctx.new_buffer(nbg)
+    ref_out = torch.empty(T, H, device="cuda")
+    ref_idx = torch.empty(T, K_TOP, dtype=torch.int32, device="cuda")
+    R.moe_layer_q4k_bf16(ctx, router, gate, up, down, xp, res, ref_out, ref_idx, None, sg, nbg, T, H, FF, E, K_TOP, 0)
+    S = T * K_TOP
+    rows = torch.empty(S * H, dtype=torch.bfloat16, device="cuda")
+    meta = torch.empty(S * 2, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(64, dtype=torch.int32, device="cuda")
+    ret = torch.empty(S * H, dtype=torch.float32, device="cuda")
+    pad2 = torch.zeros(64, dtype=torch.int32, device="cuda")
+    nb = ctx.lib.runit_moe_ep_prefill_scratch_bytes(T, H, FF, E, K_TOP, 1)
+    scratch = ctx.new_buffer(nb)
+    out = torch.empty(T, H, device="cuda")
+    idx = torch.empty(T, K_TOP, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2):
+        for placement in (0, 1):
+            R.moe_layer_q4k_bf16_ep(ctx, router, gate, up, down, xp, res, out, idx, None, scratch, nb, tab(rows), tab(meta), tab(cnt),
+                                    tab(ret), tab(pad2), T, H, FF, E, K_TOP, 0, 1, 0, 2 * epoch - 1 + placement, placement)
+            ctx.flush()
+            assert torch.equal(idx, ref_idx) and torch.equal(out, ref_out)
+
+
 def test_peer_barrier_times_out_without_a_peer(ctx):
     """Failure detection without a fault: a two-rank barrier whose second rank never signals (its flag word is a
     local buffer nothing writes) gives up after its time limit; the next flush reports the time-out and the
