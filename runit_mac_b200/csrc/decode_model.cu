@@ -22,6 +22,10 @@ struct runit_model {
     // device state
     __half* kc = nullptr;       // [L][kv_heads][max_seq][head_dim]
     __half* vc = nullptr;
+    bool ep_fused = false;      // exchange inside the GEMVs (tuning key ep_fused_exchange at creation)
+    float* ep_copies = nullptr; // per-CTA copies of the summed hidden state (expert parallelism), ep_copies_rows rows
+    uint32_t ep_copies_rows = 0;
+    float* x2 = nullptr;        // second hidden-state buffer (expert parallelism: the summed state is formed next to the old one)
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *logits = nullptr;
     float* attn_part = nullptr;
     uint32_t* attn_counters = nullptr;   // one ticket counter per head, zero at rest
@@ -117,6 +121,30 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced, b
     int32_t st;
     runit_launch_chain(ctx, embed_kernel, dim3(8), dim3(256), (const float*)m->w.tok_emb, m->x, m->state, m->forced, n_forced, h, c.vocab);
     if ((st = runit_after_launch(ctx, "embed")) != RUNIT_OK) return st;
+    // Expert parallelism with the exchange inside the GEMVs (hidden 1024 / 2048 / 4096): a block leaves its result as
+    // partial sums in every rank's buffer; the next reader of the hidden state forms residual + sum in its prologue, into
+    // the other of two buffers.
+    // Opt-in (tuning key ep_fused_exchange, read when the model is created): it brings the launch count down to the single
+    // GPU's, but measured 1077 tok/s against 1380 with the exchange as three small launches (OLMoE shape, 2 GPUs): the flag
+    // round trip and the sum then sit in the prologue of every CTA of the consuming GEMV.
+    const bool ep_fused = m->ep_fused && m->ep_world > 1 && (h == 1024 || h == 2048 || h == 4096);
+    float* xc = m->x;            // the hidden state
+    float* xo = m->x2;
+    bool pending = false;
+    EpWait wait{};
+    wait.partial = (const float*)m->ep_partial[m->ep_rank];
+    wait.pad = (const uint32_t*)m->ep_pads[m->ep_rank];
+    wait.world = m->ep_world;
+    wait.epoch = m->ep_epoch;
+    wait.copies = m->ep_copies;
+    wait.copies_rows = m->ep_copies_rows;
+    EpPush push{};
+    push.partial_all = m->ep_partial;
+    push.pads = m->ep_pads;
+    push.world = m->ep_world;
+    push.rank = m->ep_rank;
+    push.epoch = m->ep_epoch;
+    push.done = m->moe_counters + 1;
     for (int l = 0; l < c.n_layers; l++) {
         const uint8_t* wq = (const uint8_t*)m->w.wq + (size_t)l * q_dim * rb_h;
         const uint8_t* wk = (const uint8_t*)m->w.wk + (size_t)l * kv_dim * rb_h;
@@ -127,7 +155,14 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced, b
         const void* ws[3] = {wq, wk, wv};
         void* ys[3] = {m->q, m->k, m->v};
         const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
-        if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, m->x, h, (const float*)m->w.attn_norm + (size_t)l * h, c.eps)))
+        const EpWait* w_now = nullptr;
+        if (pending) {
+            wait.residual = xc;
+            w_now = &wait;
+            float* t = xc; xc = xo; xo = t;
+            pending = false;
+        }
+        if ((st = gemv_segments(ctx, "qkv_q4k", RUNIT_FMT_Q4K, 3, ws, ys, rows, xc, h, (const float*)m->w.attn_norm + (size_t)l * h, c.eps, w_now)))
             return st;
         __half* kcl = m->kc + (size_t)l * kv_layer;
         __half* vcl = m->vc + (size_t)l * kv_layer;
@@ -142,42 +177,57 @@ static int32_t issue_step(runit_model* m, bool with_logits, uint32_t n_forced, b
                                               c.n_kv_heads, hd, c.max_seq, m->attn_counters)))
                 return st;
         }
-        if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, m->x, m->x, h, q_dim))) return st;
+        if ((st = gemv_plain(ctx, "attn_out_q4k", RUNIT_FMT_Q4K, wo, m->ao, xc, xc, h, q_dim))) return st;
         // MoE block (forward.rs:1898-1931)
         // (the block's RMSNorm runs inside its routing launch)
         const float* ffn_gamma = (const float*)m->w.ffn_norm + (size_t)l * h;
         const uint32_t e_local = c.n_experts / m->ep_world;
         const size_t eg = (size_t)e_local * c.ff * rb_h, ed = (size_t)e_local * h * rb_ff;
+        if (ep_fused) {
+            if ((st = moe_layer_q4k_ep_push_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
+                                                 (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
+                                                 (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, xc, ffn_gamma, c.eps, m->moe_scratch,
+                                                 m->moe_scratch_bytes, h, c.ff, c.n_experts, c.top_k, c.renorm, m->moe_counters, &push)))
+                return st;
+            pending = true;
+            continue;
+        }
         if (m->ep_world > 1) {
-            // experts split over the ranks, combine fused over peer memory; then the next operator's RMSNorm
+            // experts split over the ranks, combine over peer memory as launches of its own (other hidden sizes)
             if ((st = moe_layer_q4k_ep_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
                                             (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
-                                            (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr, m->moe_scratch,
+                                            (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, xc, xc, nullptr, nullptr, m->moe_scratch,
                                             m->moe_scratch_bytes, m->ep_partial, m->ep_pads, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
-                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, m->moe_counters, m->x, ffn_gamma,
+                                            m->ep_world, m->ep_rank, 0, m->ep_epoch, m->moe_counters, xc, ffn_gamma,
                                             c.eps)))
                 return st;
             continue;
         }
         if ((st = moe_layer_q4k_impl(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h,
                                      (const uint8_t*)m->w.gate + (size_t)l * eg, (const uint8_t*)m->w.up + (size_t)l * eg,
-                                     (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, m->x, m->x, nullptr, nullptr,
+                                     (const uint8_t*)m->w.down + (size_t)l * ed, m->xn, xc, xc, nullptr, nullptr,
                                      m->moe_scratch, m->moe_scratch_bytes, 1, h, c.ff, c.n_experts, c.top_k, c.renorm,
                                      // (the next operator's RMSNorm runs inside that operator's own launch)
                                      nullptr, nullptr, c.eps, m->moe_counters,
-                                     m->x, ffn_gamma, c.eps)))
+                                     xc, ffn_gamma, c.eps)))
             return st;
+    }
+    const EpWait* w_last = nullptr;
+    if (pending && with_logits) {
+        wait.residual = xc;
+        w_last = &wait;
+        float* t = xc; xc = xo; xo = t;
     }
     int32_t* argmax_out = m->state + 3;
     if (with_logits && sampled) {
-        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h,
-                             (const float*)m->w.out_norm, c.eps))) return st;
+        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, xc, m->logits, nullptr, c.vocab, h,
+                             (const float*)m->w.out_norm, c.eps, nullptr, w_last))) return st;
         // the context of the draw: what has been generated so far, out_tokens[state[4] .. state[5])
         if ((st = runit_sample_f32(ctx, m->logits, m->scores, (uint32_t)c.vocab, &m->sampler_cfg, m->out_tokens, m->state + 4, 0, 0,
                                    m->eos, m->sampler_n_eos, m->rng, argmax_out))) return st;
     } else if (with_logits) {
-        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, m->x, m->logits, nullptr, c.vocab, h,
-                             (const float*)m->w.out_norm, c.eps, argmax_out))) return st;   // argmax inside the launch
+        if ((st = gemv_plain(ctx, "lm_head_q4k", RUNIT_FMT_Q4K, m->w.lm_head, xc, m->logits, nullptr, c.vocab, h,
+                             (const float*)m->w.out_norm, c.eps, argmax_out, w_last))) return st;   // argmax inside the launch
     }
     runit_launch_chain(ctx, advance_kernel, dim3(1), dim3(32), m->state, argmax_out, m->out_tokens, m->out_cap, with_logits ? 1 : 0);
     return runit_after_launch(ctx, "advance");
@@ -248,6 +298,7 @@ static int32_t model_create_impl(runit_ctx_t* ctx, const runit_model_cfg* cfg, c
     m->w = *weights;
     m->ep_world = world;
     m->ep_rank = rank;
+    m->ep_fused = ctx->tune.ep_fused_exchange != 0;
     for (uint32_t p = 0; world > 1 && p < world; p++) {
         m->ep_partial[p] = partial_all[p];
         m->ep_pads[p] = signal_pads[p];
@@ -260,13 +311,19 @@ static int32_t model_create_impl(runit_ctx_t* ctx, const runit_model_cfg* cfg, c
     int32_t st = RUNIT_OK;
     auto A = [&](void** p, size_t b) { if (st == RUNIT_OK) st = dev_alloc(m, p, b); };
     A((void**)&m->kc, kv_elems * 2); A((void**)&m->vc, kv_elems * 2);
-    A((void**)&m->x, h * 4); A((void**)&m->xn, h * 4); A((void**)&m->q, q_dim * 4); A((void**)&m->k, kv_dim * 4);
+    A((void**)&m->x, h * 4); A((void**)&m->x2, h * 4); A((void**)&m->xn, h * 4); A((void**)&m->q, q_dim * 4); A((void**)&m->k, kv_dim * 4);
     A((void**)&m->v, kv_dim * 4); A((void**)&m->ao, q_dim * 4); A((void**)&m->logits, (size_t)c.vocab * 4);
     A((void**)&m->attn_part, (size_t)c.n_heads * m->nsplit * (c.head_dim + 2) * 4);
     A(&m->moe_scratch, m->moe_scratch_bytes);
     A((void**)&m->attn_counters, (size_t)c.n_heads * 4);
     A((void**)&m->ep_epoch, 64);
     A((void**)&m->moe_counters, 4096);
+    if (world > 1) {
+        // one row per 32-row tile of the widest launch that may consume an exchange (q|k|v or lm_head)
+        const uint32_t widest = (uint32_t)c.vocab > q_dim + 2 * kv_dim ? (uint32_t)c.vocab : q_dim + 2 * kv_dim;
+        m->ep_copies_rows = 4 * ((widest + 31) / 32 + 3);      // a cluster split along K has up to 4 CTAs per tile
+        A((void**)&m->ep_copies, (size_t)m->ep_copies_rows * h * 4);
+    }
     A((void**)&m->scores, (size_t)c.vocab * 4); A((void**)&m->eos, 64); A((void**)&m->rng, 8);
     A((void**)&m->state, 64); A((void**)&m->forced, (size_t)m->forced_cap * 4); A((void**)&m->out_tokens, (size_t)m->out_cap * 4);
     if (st == RUNIT_OK) {
@@ -504,9 +561,9 @@ uint64_t runit_model_launches_per_token(runit_model_t* m) {
     // embed + per layer (q|k|v with its RMSNorm, [rope +] attention, o-proj, [norm,] MoE block) + lm_head with its RMSNorm and the argmax,
     // advance.  MoE block at hidden 1024 / 2048 / 4096: norm + router + routing, gate/up, down + weighted sum (3); else
     // norm, router, routing, gate/up, down, weighted sum.  Expert-parallel: router + routing, gate/up, down, partial sums,
-    // barrier, sum (6; 7 with router and routing apart).
+    // barrier, sum (6; 7 with router and routing apart; 3 with the opt-in exchange inside the GEMVs).
     const bool fused = m->cfg.hidden == 1024 || m->cfg.hidden == 2048 || m->cfg.hidden == 4096;
-    const uint64_t moe = m->ep_world > 1 ? (fused ? 6 : 7) : (fused ? 3 : 5);
+    const uint64_t moe = m->ep_world > 1 ? (fused ? (m->ep_fused ? 3 : 6) : 7) : (fused ? 3 : 5);
     const uint64_t attn = (m->cfg.head_dim == 128 || m->cfg.head_dim == 64) ? 1 : 2;   // rope + cache update fused into the attention launch
     const uint64_t norm2 = fused ? 0 : 1;
     return 1 + (uint64_t)m->cfg.n_layers * (1 + attn + 1 + norm2 + moe) + 2;

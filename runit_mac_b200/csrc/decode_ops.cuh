@@ -30,11 +30,13 @@ int32_t launch_argmax(runit_ctx* ctx, const void* in, bool in_f16, int32_t* resu
 int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const void* const* w, void* const* y,
                       const uint32_t* rows, const void* x, uint32_t k,
                       // norm_gamma != nullptr: x is the un-normalised vector; RMSNorm(x) * gamma is what the matrices multiply
-                      const float* norm_gamma = nullptr, float norm_eps = 0.f);
+                      const float* norm_gamma = nullptr, float norm_eps = 0.f,
+                      // expert parallelism: x is first formed as residual + the ranks' partial sums (see EpWait)
+                      const EpWait* ep_wait = nullptr);
 int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
                    uint32_t m, uint32_t k, const float* norm_gamma = nullptr, float norm_eps = 0.f,
                    // argmax_token != nullptr: the index of the largest result is written there by the launch itself
-                   int32_t* argmax_token = nullptr);
+                   int32_t* argmax_token = nullptr, const EpWait* ep_wait = nullptr);
 // prefill.cu: launchers of the batched prefill's own kernels
 int32_t prefill_embed(runit_ctx* ctx, const float* emb, const int32_t* tokens, float* x, uint32_t T, uint32_t h);
 int32_t prefill_norm_bf16(runit_ctx* ctx, const float* x, const float* gamma, void* y_bf16, float eps, uint32_t T, uint32_t h);

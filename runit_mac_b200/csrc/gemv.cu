@@ -36,6 +36,8 @@ struct GemvCall {
     float* cmb_out = nullptr;
     uint32_t* cmb_cnt = nullptr;
     bool late_trigger = false, grp_early = false;   // see GemvArgs
+    const EpPush* ep_push = nullptr;
+    const EpWait* ep_wait = nullptr;
     // greedy epilogue: (largest result, row index + am_base) into am_dst[0..am_ndst) and the index into am_token
     bool am = false;
     uint32_t am_base = 0, am_ndst = 0;
@@ -103,7 +105,21 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
         a.grp_lo = c.grp_lo;
         a.grp_cnt = c.grp_experts;
         RUNIT_REQUIRE(ctx, (uint64_t)tiles * c.grp_slots < (1ull << 31), "%s: too many grouped tiles", nm);
-        if (c.cmb_out) {
+        if (c.ep_push) {
+            const EpPush& e = *c.ep_push;
+            RUNIT_REQUIRE(ctx, c.cmb_w && c.cmb_cnt && e.partial_all && e.pads && e.epoch && e.done && e.world >= 1 && e.world <= 8 && e.rank < e.world,
+                          "%s: bad expert-parallel push", nm);
+            for (uint32_t p = 0; p < e.world; p++) {
+                RUNIT_REQUIRE(ctx, e.partial_all[p] && e.pads[p], "%s: null peer buffer %u", nm, p);
+                a.ep_peer[p] = (float*)e.partial_all[p];
+                a.ep_pad[p] = (uint32_t*)e.pads[p];
+            }
+            a.ep_npeer = e.world;
+            a.ep_rank = e.rank;
+            a.ep_epoch = e.epoch;
+            a.ep_done = e.done;
+        }
+        if (c.cmb_out || c.ep_push) {
             RUNIT_REQUIRE(ctx, c.cmb_w && c.cmb_cnt && !c.dual && !c.out_f16 && !c.x_f16 && c.grp_slots <= 32,
                           "%s: the fused weighted sum takes f32 slots of one token", nm);
             a.cmb_w = c.cmb_w;
@@ -148,6 +164,21 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
         }
         a.am_token = c.am_token;
     }
+    if (c.ep_wait) {
+        const EpWait& e = *c.ep_wait;
+        RUNIT_REQUIRE(ctx, c.batch == 1 && !c.x_f16 && !c.dual && !c.grp_expert && !simple && e.partial && e.pad && e.residual && e.epoch &&
+                          e.world >= 1 && e.world <= 8 && e.residual != c.x,
+                      "%s: bad expert-parallel wait (the summed hidden state needs a buffer of its own)", nm);
+        a.epw_partial = e.partial;
+        a.epw_pad = e.pad;
+        a.epw_res = e.residual;
+        a.epw_out = (float*)const_cast<void*>(c.x);
+        a.epw_copies = e.copies;
+        a.epw_epoch = e.epoch;
+        // (the grid is at most one CTA per 32-row tile; checked against the scratch below, once the tiles are known)
+        a.epw_abort = ctx->d_abort;
+        a.epw_world = e.world;
+    }
     if (c.norm_gamma) {
         RUNIT_REQUIRE(ctx, c.batch == 1 && !c.x_f16 && !c.grp_expert && runit_aligned(c.norm_gamma, 4),
                       "%s: the RMSNorm prologue takes one f32 input vector", nm);
@@ -172,6 +203,11 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
             if (st != RUNIT_OK) return st;
         }
     }
+    if (c.ep_wait && (!c.ep_wait->copies || 4 * tiles > c.ep_wait->copies_rows))    // a cluster split along K has up to 4 CTAs per tile
+        return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "%s: the expert-parallel prologue needs %u copies of the hidden state, has %u", nm, 4 * tiles,
+                          c.ep_wait->copies ? c.ep_wait->copies_rows : 0u);
+    if (c.ep_wait && !tma)
+        return runit_fail(ctx, RUNIT_ERR_UNSUPPORTED, "%s: the expert-parallel prologue needs the tiled bulk-load path (4-bit formats)", nm);
     switch (c.fmt) {
         case RUNIT_FMT_Q8_0:
             return gemv_launch_q8_0(ctx, a, maps, tiles, total_rows, cpb, tma, c.batch, c.x_f16, simple, nm);
@@ -185,8 +221,9 @@ static int32_t gemv_dispatch(runit_ctx* ctx, const GemvCall& c) {
 // Plain single-matrix call shared by the twins below.
 static int32_t gemv1(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res,
                      uint32_t m, uint32_t k, bool x_f16, bool out_f16, int res_kind, const float* norm_gamma = nullptr,
-                     float norm_eps = 0.f, int32_t* argmax_token = nullptr) {
+                     float norm_eps = 0.f, int32_t* argmax_token = nullptr, const EpWait* ep_wait = nullptr) {
     GemvCall c;
+    c.ep_wait = ep_wait;
     if (argmax_token) {
         c.am = true;
         c.am_token = argmax_token;
@@ -247,8 +284,9 @@ static int32_t fused_ffn(runit_ctx* ctx, const char* name, int fmt, const void* 
 int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* w2, uint32_t n_experts,
                      uint32_t rows, uint32_t k, const void* x, uint32_t xdiv, void* y, const int32_t* slot_expert,
                      uint32_t n_slots, int32_t expert_lo, const float* cmb_w, const float* cmb_res, float* cmb_out,
-                     uint32_t* cmb_cnt, int order) {
+                     uint32_t* cmb_cnt, int order, const EpPush* ep) {
     GemvCall c;
+    c.ep_push = ep;
     c.late_trigger = order == 1;
     c.grp_early = order == 2;
     c.cmb_w = cmb_w;
@@ -273,8 +311,9 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
 }
 
 int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const void* const* w, void* const* y,
-                      const uint32_t* rows, const void* x, uint32_t k, const float* norm_gamma, float norm_eps) {
+                      const uint32_t* rows, const void* x, uint32_t k, const float* norm_gamma, float norm_eps, const EpWait* ep_wait) {
     GemvCall c;
+    c.ep_wait = ep_wait;
     c.norm_gamma = norm_gamma;
     c.norm_eps = norm_eps;
     c.name = name;
@@ -291,9 +330,9 @@ int32_t gemv_segments(runit_ctx* ctx, const char* name, int fmt, int nseg, const
 }
 
 int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, const void* x, void* y, const void* res_f32,
-                   uint32_t m, uint32_t k, const float* norm_gamma, float norm_eps, int32_t* argmax_token) {
+                   uint32_t m, uint32_t k, const float* norm_gamma, float norm_eps, int32_t* argmax_token, const EpWait* ep_wait) {
     return gemv1(ctx, name, fmt, w, x, y, res_f32, m, k, false, false, res_f32 ? RES_F32 : RES_NONE, norm_gamma, norm_eps,
-                 argmax_token);
+                 argmax_token, ep_wait);
 }
 
 }  // namespace runit
@@ -389,7 +428,7 @@ int32_t runit_rms_norm_gemv_f32(runit_ctx_t* ctx, int32_t fmt, const void* weigh
                                 void* output, const void* residual, uint32_t m, uint32_t k) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, gamma && m > 0, "rms_norm_gemv_f32: null gamma or m == 0");
-    return gemv_plain(ctx, "rms_norm_gemv_f32", fmt, weight, x, output, residual, m, k, (const float*)gamma, eps, nullptr);
+    return gemv_plain(ctx, "rms_norm_gemv_f32", fmt, weight, x, output, residual, m, k, (const float*)gamma, eps, nullptr, nullptr);
 }
 int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t* ctx, int32_t fmt, const void* w_q, const void* w_k, const void* w_v, const void* x,
                                      const void* gamma, float eps, void* out_q, void* out_k, void* out_v, uint32_t q_dim,
@@ -399,7 +438,7 @@ int32_t runit_rms_norm_fused_qkv_f32(runit_ctx_t* ctx, int32_t fmt, const void* 
     const void* ws[3] = {w_q, w_k, w_v};
     void* ys[3] = {out_q, out_k, out_v};
     const uint32_t rows[3] = {q_dim, kv_dim, kv_dim};
-    return gemv_segments(ctx, "rms_norm_fused_qkv_f32", fmt, 3, ws, ys, rows, x, k, (const float*)gamma, eps);
+    return gemv_segments(ctx, "rms_norm_fused_qkv_f32", fmt, 3, ws, ys, rows, x, k, (const float*)gamma, eps, nullptr);
 }
 
 // (largest value, index) pairs pushed by the ranks -> index of the overall maximum (lowest index among equal values).
@@ -420,7 +459,7 @@ int32_t runit_gemv_argmax_f32(runit_ctx_t* ctx, int32_t fmt, const void* weight,
                               void* logits, void* result, uint32_t m, uint32_t k) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
     RUNIT_REQUIRE(ctx, result && runit_aligned(result, 4) && m > 0, "gemv_argmax_f32: null or misaligned result, or m == 0");
-    return gemv_plain(ctx, "gemv_argmax_f32", fmt, weight, x, logits, nullptr, m, k, (const float*)gamma, eps, (int32_t*)result);
+    return gemv_plain(ctx, "gemv_argmax_f32", fmt, weight, x, logits, nullptr, m, k, (const float*)gamma, eps, (int32_t*)result, nullptr);
 }
 
 int32_t runit_gemv_argmax_allgather(runit_ctx_t* ctx, int32_t fmt, const void* w_local, const void* x, void* logits_local,

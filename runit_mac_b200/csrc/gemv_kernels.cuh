@@ -109,6 +109,28 @@ struct GemvArgs {
     // and takes a ticket on *am_cnt; the tile with the last ticket reduces the n_tiles pairs (the lowest index wins among
     // equal values), stores the pair into every am_dst[i] (own memory or a peer's: plain stores), the index into *am_token
     // when that is not null, and puts the counter back to zero.
+    // Expert-parallel decode without launches of its own.
+    // Producer (grouped down projection with cmb_*, ep_npeer > 0): the weighted sum over THIS rank's slots goes, instead of
+    // cmb_out, into slot ep_rank of every rank's partial buffer ep_peer[p] (f32 [2][world][rows], the half chosen by the
+    // parity of the epoch = *ep_epoch + 1; plain peer stores); the warp that completes the last row tile (ticket on
+    // *ep_done) makes everything visible system-wide, stores the epoch into word ep_rank of every rank's flag pad and
+    // advances *ep_epoch.
+    // Consumer (batch-1 GEMV with epw_partial != nullptr): after its dependency wait every CTA waits (bounded) until all
+    // ranks' flags have reached *epw_epoch, adds residual + the world partials in rank order for all k inputs, stores
+    // them to epw_out (= this launch's x: every CTA writes the same bits) and goes on from there.
+    float* ep_peer[8];
+    uint32_t* ep_pad[8];
+    uint32_t ep_npeer, ep_rank;
+    uint32_t* ep_epoch;
+    uint32_t* ep_done;
+    const float* epw_partial;
+    const uint32_t* epw_pad;
+    const float* epw_res;
+    float* epw_out;
+    float* epw_copies;           // [grid][k]: one copy of the summed state per CTA
+    const uint32_t* epw_epoch;
+    uint32_t* epw_abort;
+    uint32_t epw_world;
     uint2* am_part;
     uint32_t* am_cnt;
     uint32_t am_base;
@@ -586,6 +608,40 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
         for (int s = 0; s < S; s++) issue(s, 1);
         grid_dependency_wait();
         if (a.late_trigger) grid_launch_dependents();
+        if constexpr (B == 1 && !XF16 && !DUAL) {
+            if (a.epw_partial != nullptr) {
+                const uint32_t epoch = *a.epw_epoch;     // advanced by the launch that pushed this rank's partial sums
+                if (warp == 0 && (uint32_t)lane < a.epw_world) {
+                    const bool aborted = a.epw_abort && *reinterpret_cast<volatile uint32_t*>(a.epw_abort) != 0u;
+                    const long long t0 = clock64();
+                    while (!aborted) {
+                        uint32_t v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.epw_pad + lane) : "memory");
+                        if ((int32_t)(v - epoch) >= 0) break;
+                        if (clock64() - t0 > (1ll << 30)) {   // about half a second: a rank never raised its flag
+                            if (a.status) atomicExch(a.status, 3);
+                            if (a.epw_abort) atomicExch(a.epw_abort, 1u);
+                            break;
+                        }
+                        __nanosleep(100);
+                    }
+                }
+                __syncthreads();
+                // every CTA forms the summed hidden state in a copy of its own (192 CTAs storing the same 8 KB would queue up on
+                // the same lines); CTA 0 also stores the copy that later launches read
+                const float* part = a.epw_partial + (size_t)(epoch & 1u) * a.epw_world * a.k;
+                float* mine = a.epw_copies + (size_t)blockIdx.x * a.k;
+                for (uint32_t i = threadIdx.x; i < a.k; i += kNT) {
+                    float v = a.epw_res[i];
+                    for (uint32_t r = 0; r < a.epw_world; r++) v += __ldcg(part + (size_t)r * a.k + i);   // rank order, as ep_reduce_kernel
+                    mine[i] = v;
+                    if (blockIdx.x == 0) a.epw_out[i] = v;
+                }
+                xbase = reinterpret_cast<const uint8_t*>(mine);
+                fence_proxy_async();     // the bulk loads of x below read what this CTA has just stored
+                __syncthreads();
+            }
+        }
 #pragma unroll
         for (int s = 0; s < S; s++) issue(s, 2);
     } else {
@@ -750,7 +806,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                     }
                 }
             }
-            if (a.cmb_out != nullptr && tile_ok) {
+            if ((a.cmb_out != nullptr || a.ep_npeer != 0) && tile_ok) {
                 const uint32_t t = tile % a.grp_tiles;   // row tile, shared by the slots
                 __threadfence();                         // this lane's row of y[slot] is visible before the ticket is
                 __syncwarp();
@@ -769,7 +825,35 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
                             if (eid >= 0 && (uint32_t)eid < a.grp_cnt)
                                 acc = fmaf(a.cmb_w[i], __ldcg(y0 + (size_t)i * a.ldy + r), acc);
                         }
-                        a.cmb_out[r] = (a.cmb_res ? a.cmb_res[r] : 0.f) + acc;
+                        if (a.ep_npeer == 0) {
+                            a.cmb_out[r] = (a.cmb_res ? a.cmb_res[r] : 0.f) + acc;
+                        } else {
+                            const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.ep_epoch) + 1u;
+                            const size_t o = ((size_t)(epoch & 1u) * a.ep_npeer + a.ep_rank) * sg.rows + r;
+                            for (uint32_t p = 0; p < a.ep_npeer; p++) a.ep_peer[p][o] = acc;
+                        }
+                    }
+                    if (a.ep_npeer != 0) {
+                        // the partial sums of this row tile are out: the warp that files the last row tile raises the flags
+                        const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.ep_epoch) + 1u;
+                        __syncwarp();                    // the lanes' peer stores are ordered before lane 0's fence
+                        uint32_t done = 0;
+                        if (lane == 0) {
+                            __threadfence_system();
+                            done = atomicAdd(a.ep_done, 1u);
+                        }
+                        done = __shfl_sync(0xffffffffu, done, 0);
+                        if (done == a.grp_tiles - 1) {
+                            if (lane == 0) __threadfence_system();
+                            __syncwarp();
+                            if ((uint32_t)lane < a.ep_npeer)
+                                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.ep_pad[lane] + a.ep_rank), "r"(epoch) : "memory");
+                            __syncwarp();
+                            if (lane == 0) {
+                                *a.ep_done = 0;
+                                *a.ep_epoch = epoch;     // read by the kernels that follow in the stream
+                            }
+                        }
                     }
                 }
             }

@@ -559,6 +559,36 @@ int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* 
     return runit_after_launch(ctx, "moe_ep_reduce");
 }
 
+// Expert-parallel decode block of one token without launches of its own for the exchange: routing, grouped gate/up, and a
+// grouped down projection whose epilogue pushes this rank's weighted partial sum to every rank and raises the flags
+// (EpPush); the residual add and the sum over the ranks happen in the prologue of the next GEMV that reads the hidden
+// state (EpWait).  Three launches, as on one GPU.
+int32_t moe_layer_q4k_ep_push_impl(runit_ctx* ctx, const void* router_w, const void* gate_local, const void* up_local,
+                                   const void* down_local, float* xn, const float* pre_x, const float* pre_gamma, float pre_eps,
+                                   void* scratch, size_t scratch_bytes, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
+                                   uint32_t* counters, const EpPush* push) {
+    RUNIT_REQUIRE(ctx, router_w && gate_local && up_local && down_local && xn && pre_x && pre_gamma && scratch && counters && push,
+                  "moe_layer_q4k_ep_push: null pointer");
+    RUNIT_REQUIRE(ctx, (h == 1024 || h == 2048 || h == 4096) && ff % 256 == 0 && E % push->world == 0 && k <= 32 && k <= E,
+                  "moe_layer_q4k_ep_push: hidden 1024 / 2048 / 4096, experts divisible by the ranks");
+    const MoeScratch s = moe_carve(scratch, 1, h, ff, E, k);
+    if (s.bytes > scratch_bytes)
+        return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "moe_layer_q4k_ep_push: scratch has %zu bytes, needs %zu", scratch_bytes, s.bytes);
+    int32_t st;
+    const dim3 grid((E + 7) / 8);
+    if (h == 2048) runit_launch_chain(ctx, route_fused_kernel<64>, grid, dim3(256), (const float*)router_w, pre_x, s.logits, E, h, k, (int)renorm, s.idx, s.w, counters, pre_gamma, pre_eps, xn);
+    else if (h == 1024) runit_launch_chain(ctx, route_fused_kernel<32>, grid, dim3(256), (const float*)router_w, pre_x, s.logits, E, h, k, (int)renorm, s.idx, s.w, counters, pre_gamma, pre_eps, xn);
+    else runit_launch_chain(ctx, route_fused_kernel<128>, grid, dim3(256), (const float*)router_w, pre_x, s.logits, E, h, k, (int)renorm, s.idx, s.w, counters, pre_gamma, pre_eps, xn);
+    if ((st = runit_after_launch(ctx, "moe_route_fused")) != RUNIT_OK) return st;
+    const uint32_t n_local = E / push->world;
+    const int32_t lo = (int32_t)(push->rank * n_local);
+    st = gemv_grouped(ctx, "moe_gate_up_ep", RUNIT_FMT_Q4K, gate_local, up_local, n_local, ff, h, xn, k, s.act, s.idx, k, lo, nullptr, nullptr,
+                      nullptr, nullptr, 1);
+    if (st != RUNIT_OK) return st;
+    return gemv_grouped(ctx, "moe_down_ep_push", RUNIT_FMT_Q4K, down_local, nullptr, n_local, h, ff, s.act, 1, s.y, s.idx, k, lo, s.w, nullptr,
+                        nullptr, counters + 32, 2, push);
+}
+
 }  // namespace runit
 
 using namespace runit;

@@ -24,6 +24,7 @@ struct runit_tuning {
     int32_t stream_cfg = 0;     // warps per SM x ring stages of that launch: 0 = default, 1..3 = alternatives
     int32_t stream_ksl = 0;     // 0 = warps per tile chosen per GEMV, else forced (experiments)
     int32_t stream_dynamic = 0;
+    int32_t ep_fused_exchange = 0;   // expert-parallel decoder: 1 = exchange inside the GEMVs (no launches of its own; measured slower)
     int32_t router_variant = 0;   // batched f32 router: 0 = by size, 1 = one warp per expert, 2 = tiled GEMM (experiments) // 1 = CTAs take items from a shared counter instead of the fixed split (experiments)
 };
 
@@ -125,6 +126,23 @@ static inline size_t runit_row_bytes(int fmt, uint32_t k) {
 }
 
 namespace runit {
+// Expert-parallel decode without launches of its own (GemvArgs::ep_* / epw_* in gemv_kernels.cuh).
+struct EpPush {          // producer: the grouped down projection of a rank
+    void* const* partial_all;    // every rank's partial buffer f32 [2][world][rows]
+    void* const* pads;           // every rank's flag pad
+    uint32_t world, rank;
+    uint32_t* epoch;             // device word, advanced by the launch
+    uint32_t* done;              // zeroed device word (ticket over the row tiles)
+};
+struct EpWait {          // consumer: the next GEMV that reads the hidden state
+    const float* partial;        // this rank's partial buffer
+    const uint32_t* pad;         // this rank's flag pad
+    const float* residual;       // hidden state before the block
+    float* copies;               // scratch f32 [copies_rows][k]: one copy of the summed state per CTA of the consuming launch
+    uint32_t copies_rows;
+    uint32_t world;
+    const uint32_t* epoch;
+};
 // gemv_imma.cu: batched GEMV of the 4-bit formats on the integer tensor-core path.
 bool gemv_imma_applies(const runit_ctx* ctx, int fmt, uint32_t k, uint32_t batch);
 int32_t gemv_imma(runit_ctx* ctx, int fmt, const void* w, const float* x, float* y, const float* res, uint32_t m, uint32_t k,
@@ -143,10 +161,17 @@ int32_t gemv_grouped(runit_ctx* ctx, const char* name, int fmt, const void* w, c
                      // dependent-launch ordering of a gate/up + down pair whose expert ids come from the kernel before the
                      // pair: 1 = first of the pair (releases its successor only after its own wait), 2 = second of the pair
                      // (reads the ids and requests weights before its wait); 0 = neither
-                     int order = 0);
+                     int order = 0,
+                     // expert parallelism: the weighted sum of this rank's slots goes to every rank's partial buffer (cmb_out unused)
+                     const EpPush* ep = nullptr);
 // gemv.cu: the one-kernel barrier over peer memory behind runit_peer_barrier.
 int32_t peer_barrier_launch(runit_ctx* ctx, void* const* signal_pads, uint32_t world, uint32_t rank, uint32_t epoch,
                             uint32_t* epoch_ptr, const void* pairs = nullptr, int32_t* pair_result = nullptr);
+// moe.cu: the same block for one token with the exchange inside the down projection's epilogue (see there)
+int32_t moe_layer_q4k_ep_push_impl(runit_ctx* ctx, const void* router_w, const void* gate_local, const void* up_local,
+                                   const void* down_local, float* xn, const float* pre_x, const float* pre_gamma, float pre_eps,
+                                   void* scratch, size_t scratch_bytes, uint32_t h, uint32_t ff, uint32_t E, uint32_t k, int32_t renorm,
+                                   uint32_t* counters, const EpPush* push);
 // moe.cu: expert-parallel decode block (runit_moe_layer_q4k_ep); epoch_ptr != nullptr keeps the epoch in a device word.
 int32_t moe_layer_q4k_ep_impl(runit_ctx* ctx, const void* router_w, const void* gate_local, const void* up_local,
                               const void* down_local, const void* x, const void* residual, void* out, void* idx_out, void* w_out,

@@ -119,7 +119,9 @@ def run_rank(rank, world, port, q):
             prev = o
         out_ep = (o.cpu().numpy(), i_ep.cpu().numpy())
         dist.barrier()
-        out_ep = out_ep + (ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank),)
+        # hidden 512: the exchange as launches of its own; hidden 1024 with the opt-in exchange inside the GEMVs (partial sums
+        # pushed by the down projection's epilogue, summed in the prologue of the next GEMV): the same launch count as one GPU
+        out_ep = out_ep + ([ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank, hidden) for hidden in (512, 1024)],)
     res = (rank, y.cpu().numpy(), out.cpu().numpy(), idx.cpu().numpy(), out_ep)
     if world > 1:
         dist.destroy_process_group()
@@ -128,13 +130,15 @@ def run_rank(rank, world, port, q):
     return res
 
 
-def ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank):
+def ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank, hidden=512):
     """Small OLMoE-shaped decoder twice on this rank: all experts local, and experts split over the ranks with the
     fused peer-memory combine.  Returns both greedy token sequences."""
     import ctypes as C
     import torch.distributed._symmetric_memory as symm
     from test_decode_gpu import SMALL, rand_q4k_zero_mean
     c = dict(SMALL)
+    c["hidden"] = hidden
+    c["n_heads"] = hidden // c["head_dim"]
     L, h, E, ff, V = c["n_layers"], c["hidden"], c["n_experts"], c["ff"], c["vocab"]
     q_dim, kv_dim = c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"]
     rb = lambda k: k // 256 * 144
@@ -162,15 +166,19 @@ def ep_decode_tokens(R, P, O, ctx, torch, dist, world, rank):
     pp = (C.c_void_p * world)(*[int(p) for p in hp.buffer_ptrs])
     dist.barrier()
     torch.cuda.synchronize()
+    ctx.set_tuning("ep_fused_exchange", 1 if hidden == 1024 else 0)     # read when the model is created
     model = R.Model(ctx, R.ModelCfg(**c), {n: ctx.buffer_from(a) for n, a in local.items()}, ep=(world, rank, pq, pp))
+    ctx.set_tuning("ep_fused_exchange", 0)
     dist.barrier()
     tok_ep = model.generate_greedy(prompt, 24)
     tok_ep2 = model.generate_greedy(prompt, 24)       # a second run on the same model: epochs keep growing
     assert (tok_ep == tok_ep2).all()
     lpt = int(model.launches_per_token)
+    # the single-GPU decoder's count for the same shape: 1 + L * (q|k|v, attention, o-proj, [norm,] MoE block) + 2
+    lpt_one = 1 + L * (3 + (3 if hidden in (1024, 2048, 4096) else 6)) + 2
     dist.barrier()
     model.close()
-    return tok_full, tok_ep, lpt
+    return tok_full, tok_ep, lpt, lpt_one
 
 
 def test_sharded_paths_match_oracle(oracle):
@@ -217,9 +225,11 @@ def test_sharded_paths_match_oracle(oracle):
             st = O.compare(ref_res, r[4][0], rel_tol=1e-3)
             assert st.n_mismatch_rel == 0, st
             assert np.array_equal(r[4][0], res[0][4][0]), "ranks disagree on the bits of the fused expert-parallel block"
-            tok_full, tok_ep, lpt = r[4][2]
-            assert (tok_ep == tok_full).all(), ("expert-parallel decode differs from the single-GPU decode", tok_full, tok_ep)
-            assert (tok_ep == res[0][4][2][1]).all() and len(set(tok_ep[7:].tolist())) > 3 and lpt >= 1 + 2 * 10 + 2
+            for case, (tok_full, tok_ep, lpt, lpt_one) in enumerate(r[4][2]):
+                assert (tok_ep == tok_full).all(), ("expert-parallel decode differs from the single-GPU decode", case, tok_full, tok_ep)
+                assert (tok_ep == res[0][4][2][case][1]).all() and len(set(tok_ep[7:].tolist())) > 3
+                # hidden 512: the exchange costs launches; hidden 1024: none
+                assert (lpt > lpt_one) if case == 0 else (lpt == lpt_one), (case, lpt, lpt_one)
 
 
 def test_partitioned_kernels_with_one_rank(ctx, oracle):
