@@ -471,6 +471,21 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
         scratch.free()
         # Qwen3-MoE-shaped batched block (4096 tokens, 128 experts, Zipf routing) on the tensor cores
         out["moe_block_qwen3_shape_bf16"] = run_block(R, ctx, torch, stream, T=4096, reps=10)
+        # dense feed-forward block of a prefill pass at the Qwen2.5-7B shape (hidden 3584, intermediate 18944), 2048 tokens
+        Td, hd_, ffd = 2048, HIDDEN, INTER
+        wts = [ctx.new_buffer(r * rb(kk)) for r, kk in ((ffd, hd_), (ffd, hd_), (hd_, ffd))]
+        for i, (b, (r, kk)) in enumerate(zip(wts, ((ffd, hd_), (ffd, hd_), (hd_, ffd)))):
+            R.fill_weights(ctx, R.FMT_Q4K, b, r * (kk // 256), 611 + i, 0.01)
+        xd, od = torch.randn(Td, hd_, device="cuda"), torch.empty(Td, hd_, device="cuda")
+        nbd = ctx.lib.runit_ffn_q4k_bf16_scratch_bytes(Td, hd_, ffd)
+        sd = ctx.new_buffer(nbd)
+        msd = timed(lambda: R.ffn_q4k_bf16(ctx, wts[0], wts[1], wts[2], xd, None, 0.0, xd, od, sd, nbd, Td, hd_, ffd), 5)
+        fl = 2.0 * 3 * Td * hd_ * ffd
+        peak, kind = measured_tensor_peak()
+        out["dense_ffn_qwen7b_prefill_bf16"] = {"tokens": Td, "ms": msd, "tflops": fl / (msd * 1e-3) / 1e12,
+                                               "frac_of_tensor_peak": fl / (msd * 1e-3) / 1e12 / peak, "peak_tflops": peak, "peak_kind": kind}
+        for b in wts + [sd]:
+            b.free()
     # full OLMoE-shaped greedy decode: 128-token prompt, 64 greedy steps, f16 KV, no host round trips
     cfg = R.ModelCfg(n_layers=L, hidden=h, n_heads=16, n_kv_heads=16, head_dim=128, vocab=50304, n_experts=E, top_k=k, ff=ff,
                      max_seq=2048, renorm=0, eps=1e-5, theta=10000.0)
@@ -843,6 +858,8 @@ def main():
     ap.add_argument("--decode", action="store_true", help="only the OLMoE-shaped greedy decode figure (tok/s), then exit")
     ap.add_argument("--prefill", default="", help="T: batched prefill of T tokens on a 2-layer OLMoE-shaped decoder, three times, then exit "
                                                   "(the small case for ncu captures of the prefill kernels)")
+    ap.add_argument("--ffn", default="", help="T: the dense feed-forward block (Qwen2.5-7B shape) on T tokens, three times, then exit "
+                                              "(the small case for ncu captures of the dense tcgen05 GEMM)")
     ap.add_argument("--shapes", action="store_true", help="per-shape GEMV table (one JSON line per shape) instead of the headline run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -883,6 +900,21 @@ def main():
             R.gemv_batched_f32(ctx, fmt, w, x, y, None, m, k, batch)
         ctx.flush()
         print(json.dumps({"one": args.one, "launches": ctx.launches}))
+        return
+    if args.ffn:
+        T = int(args.ffn)
+        rbq = lambda kk: kk // 256 * 144
+        dims = ((INTER, HIDDEN), (INTER, HIDDEN), (HIDDEN, INTER))
+        wts = [ctx.new_buffer(r * rbq(kk)) for r, kk in dims]
+        for i, (b, (r, kk)) in enumerate(zip(wts, dims)):
+            R.fill_weights(ctx, R.FMT_Q4K, b, r * (kk // 256), 611 + i, 0.01)
+        xd, od = torch.randn(T, HIDDEN, device="cuda"), torch.empty(T, HIDDEN, device="cuda")
+        nbd = ctx.lib.runit_ffn_q4k_bf16_scratch_bytes(T, HIDDEN, INTER)
+        sd = ctx.new_buffer(nbd)
+        for _ in range(3):
+            R.ffn_q4k_bf16(ctx, wts[0], wts[1], wts[2], xd, None, 0.0, xd, od, sd, nbd, T, HIDDEN, INTER)
+        ctx.flush()
+        print(json.dumps({"ffn_tokens": T, "finite": bool(torch.isfinite(od).all().item()), "launches": ctx.launches}))
         return
     if args.prefill:
         T = int(args.prefill)

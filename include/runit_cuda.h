@@ -453,6 +453,14 @@ int32_t runit_model_prefill(runit_model_t* model, const int32_t* tokens, uint32_
  * 0 .. start_pos+t (attention.metal:36-158). */
 int32_t runit_prefill_attention_f16kv(runit_ctx_t*, const void* q, const void* kcache, const void* vcache, void* out_bf16, uint32_t T,
                                       uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t max_seq, uint32_t start_pos);
+/* Dense feed-forward block of a prefill pass (prefill.rs:217-227: gemm_f16 gate, gemm_f16 up, silu_mul_f16, gemm_f16 down,
+ * add_f16) on the tensor cores with bf16 operands: out[t] = residual[t] + Wd . bf16(silu(Wg . xb[t]) * (Wu . xb[t])), where
+ * xb = bf16(x) or, when gamma is not NULL, bf16(RMSNorm(x) * gamma) (the rms_norm_f16 of prefill.rs:150-151).  x / residual /
+ * out f32 [T][h] (residual may be NULL or equal to out); Q4_K matrices; scratch 1024-byte aligned. */
+size_t  runit_ffn_q4k_bf16_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff);
+int32_t runit_ffn_q4k_bf16(runit_ctx_t*, const void* w_gate, const void* w_up, const void* w_down, const void* x, const void* gamma,
+                           float eps, const void* residual, void* out, void* scratch, size_t scratch_bytes, uint32_t T, uint32_t h,
+                           uint32_t ff);
 void*   runit_model_logits(runit_model_t* model);           /* device pointer, f32 [vocab], of the last step */
 uint64_t runit_model_launches_per_token(runit_model_t* model);
 

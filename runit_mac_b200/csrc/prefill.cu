@@ -83,6 +83,16 @@ __global__ void rope_cache_rows_kernel(float* __restrict__ q, const float* __res
     }
 }
 
+// y[t][:] = bf16(x[t][:])
+__global__ void __launch_bounds__(256) to_bf16_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, size_t n4) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n4) return;
+    const float4 a = reinterpret_cast<const float4*>(x)[i];
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(y) + 2 * i;
+    o[0] = __floats2bfloat162_rn(a.x, a.y);
+    o[1] = __floats2bfloat162_rn(a.z, a.w);
+}
+
 // x[t][:] += y[t][:]
 __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n4) {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
@@ -319,6 +329,51 @@ int32_t prefill_add_rows(runit_ctx* ctx, float* x, const float* y, size_t n) {
 using namespace runit;
 
 extern "C" {
+
+// Dense feed-forward block of a prefill pass (prefill.rs:217-227: gate GEMM, up GEMM, silu_mul, down GEMM, residual add) on
+// the tensor cores: out[t] = residual[t] + Wd . bf16(silu(Wg . xb[t]) * (Wu . xb[t])), xb = bf16(x) or, with gamma,
+// bf16(RMSNorm(x) * gamma).  The two GEMM launches of moe_grouped.cu with one "expert" that owns the whole matrices.
+size_t runit_ffn_q4k_bf16_scratch_bytes(uint32_t T, uint32_t h, uint32_t ff) {
+    const size_t rows = ((size_t)T + 255) / 256 * 256 + 256, tiles = ((size_t)T + 255) / 256;
+    auto up = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+    return up(4 * (3 * tiles + 4)) + up(rows * h * 2) + up(rows * ff * 2) + up((size_t)T * h * 4);
+}
+
+int32_t runit_ffn_q4k_bf16(runit_ctx_t* ctx, const void* w_gate, const void* w_up, const void* w_down, const void* x, const void* gamma,
+                           float eps, const void* residual, void* out, void* scratch, size_t scratch_bytes, uint32_t T, uint32_t h,
+                           uint32_t ff) {
+    if (!ctx) return RUNIT_ERR_BAD_ARG;
+    RUNIT_REQUIRE(ctx, w_gate && w_up && w_down && x && out && scratch && T > 0, "ffn_q4k_bf16: null pointer or no tokens");
+    RUNIT_REQUIRE(ctx, h % 256 == 0 && ff % 256 == 0 && h > 0 && ff > 0, "ffn_q4k_bf16: hidden %u and intermediate %u must be multiples of 256", h, ff);
+    RUNIT_REQUIRE(ctx, runit_aligned(scratch, 1024) && runit_aligned(x, 16) && runit_aligned(out, 16) && (!residual || runit_aligned(residual, 16)) &&
+                           runit_aligned(w_gate, 16) && runit_aligned(w_up, 16) && runit_aligned(w_down, 16),
+                  "ffn_q4k_bf16: scratch must be 1024-byte aligned, tensors 16-byte aligned");
+    if (runit_ffn_q4k_bf16_scratch_bytes(T, h, ff) > scratch_bytes)
+        return runit_fail(ctx, RUNIT_ERR_BUFFER_SIZE, "ffn_q4k_bf16: scratch has %zu bytes, needs %zu", scratch_bytes,
+                          runit_ffn_q4k_bf16_scratch_bytes(T, h, ff));
+    const size_t rows = ((size_t)T + 255) / 256 * 256 + 256, tiles = ((size_t)T + 255) / 256;
+    auto up = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+    uint8_t* p = (uint8_t*)scratch;
+    int32_t* tables = (int32_t*)p;              p += up(4 * (3 * tiles + 4));
+    void* xb = p;                               p += up(rows * h * 2);
+    void* act = p;                              p += up(rows * ff * 2);
+    float* y = (float*)p;
+    int32_t st;
+    if ((st = dense_tiles_prepare(ctx, tables, T))) return st;
+    if (gamma) {
+        if ((st = prefill_norm_bf16(ctx, (const float*)x, (const float*)gamma, xb, eps, T, h))) return st;
+    } else {
+        const size_t n4 = (size_t)T * h / 4;
+        pf::to_bf16_rows_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((const float*)x, (__nv_bfloat16*)xb, n4);
+        if ((st = runit_after_launch(ctx, "ffn_to_bf16"))) return st;
+    }
+    if ((st = dense_gemm_q4k_bf16(ctx, "ffn_gate_up", w_gate, w_up, ff, h, xb, (uint32_t)rows, act, ff, T, tables))) return st;
+    float* dst = residual ? y : (float*)out;
+    if ((st = dense_gemm_q4k_bf16(ctx, "ffn_down", w_down, nullptr, h, ff, act, (uint32_t)rows, dst, h, T, tables))) return st;
+    if (!residual) return RUNIT_OK;
+    if (residual != out) RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(out, residual, (size_t)T * h * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return prefill_add_rows(ctx, (float*)out, y, (size_t)T * h);
+}
 
 // Stand-alone entry of the attention kernel (tests, other callers): q f32 [T][heads*hd] already rotated, caches f16
 // [kv_heads][max_seq][hd] holding positions 0 .. start_pos + T - 1, out bf16 [T][heads*hd].

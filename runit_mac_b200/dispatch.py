@@ -249,6 +249,8 @@ _TWINS = [
     ("peer_barrier_argmax", "no twin: (signal_pads[world], world, rank, epoch, pairs, result_i32)"),
     ("prefill_attention_f16kv", "dispatch.rs flash_attention_f16 with q_len = seq (prefill.rs:134-145): (q_f32, kcache, vcache, out_bf16, T, "
                                 "heads, kv_heads, head_dim, max_seq, start_pos)"),
+    ("ffn_q4k_bf16", "prefill.rs:217-227 as one call: (w_gate, w_up, w_down, x, gamma_or_None, eps, residual_or_None, out, scratch, "
+                     "scratch_bytes, T, h, ff)"),
     ("rms_norm_f32_f32", "dispatch.rs:152 (x, y, gamma_f16, eps, hidden, num_rows)"),
     ("rms_norm_f32_f32_f32g", "dispatch.rs:177 (x, y, gamma_f32, eps, hidden, num_rows)"),
     ("fused_rope_qk_f32", "dispatch.rs:945 (q, k, head_dim, q_heads, kv_heads, pos, theta)"),

@@ -114,3 +114,32 @@ def test_olmoe_shaped_prefill_128_tokens(ctx, oracle):
     out = model.generate_greedy(np.array([tok], np.int32), 8, start_pos=128)
     assert (out >= 0).all()
     model.close()
+
+
+@pytest.mark.parametrize("T", [1, 100, 300])
+def test_dense_ffn_block(ctx, oracle, T):
+    """The dense feed-forward block of a prefill pass (prefill.rs:217-227) on the tensor cores, with and without the RMSNorm in
+    front and the residual, against the bf16-operand restatement (the batched block's oracle with one expert, weight 1)."""
+    import runit_mac_b200 as R
+    O = oracle
+    h, ff = 512, 768
+    rng = np.random.default_rng(40 + T)
+    wg, wu, wd = O.rand_q4k(rng, ff, h), O.rand_q4k(rng, ff, h), O.rand_q4k(rng, h, ff)
+    x = rng.normal(0, 1, (T, h)).astype(np.float32)
+    res = rng.normal(0, 1, (T, h)).astype(np.float32)
+    gamma = rng.normal(1, 0.1, h).astype(np.float32)
+    nb = ctx.lib.runit_ffn_q4k_bf16_scratch_bytes(T, h, ff)
+    scratch = ctx.new_buffer(nb)
+    wb = [ctx.buffer_from(w) for w in (wg, wu, wd)]
+    ob = ctx.new_buffer(T * h * 4)
+    routing = (np.zeros((T, 1), np.int32), np.ones((T, 1), np.float32))
+    for use_gamma, use_res in ((False, False), (True, True), (False, True)):
+        xin = O.rms_norm_f32(x, gamma, 1e-5) if use_gamma else x
+        ref, _, _ = O.moe_grouped_q4k_bf16(None, wg, wu, wd, xin, h=h, ff=ff, E=1, top_k=1, residual=res if use_res else None, routing=routing)
+        R.ffn_q4k_bf16(ctx, *wb, ctx.buffer_from(x), ctx.buffer_from(gamma) if use_gamma else None, 1e-5,
+                       ctx.buffer_from(res) if use_res else None, ob, scratch, nb, T, h, ff)
+        ctx.flush()
+        got = ob.download(np.float32, T * h).reshape(T, h)
+        scale = np.maximum(np.abs(ref), np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+        rel = float((np.abs(got - ref) / scale).max())
+        assert rel <= 4e-3, (T, use_gamma, use_res, rel)
