@@ -94,6 +94,8 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
     // Greedy epilogue of the GEMV: 65536 tile pairs (2,097,152 rows) behind a zeroed ticket word.
     if (cudaMalloc(&c->d_am, 256 + 65536 * 8) == cudaSuccess) cudaMemset(c->d_am, 0, 256);
     else { c->d_am = nullptr; cudaGetLastError(); }
+    if (cudaMalloc((void**)&c->d_xq_ctl, 4096) == cudaSuccess) cudaMemset(c->d_xq_ctl, 0, 4096);
+    else { c->d_xq_ctl = nullptr; cudaGetLastError(); }
     if (cudaMalloc(&c->d_xq, 4u << 20) == cudaSuccess) c->xq_bytes = 4u << 20;
     else { c->d_xq = nullptr; cudaGetLastError(); }
     {
@@ -156,6 +158,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->d_xq) cudaFree(ctx->d_xq);
     if (ctx->d_am) cudaFree(ctx->d_am);
+    if (ctx->d_xq_ctl) cudaFree(ctx->d_xq_ctl);
     if (ctx->d_abort) cudaFree(ctx->d_abort);
     if (ctx->stream_rec) delete static_cast<std::vector<runit::StreamRec>*>(ctx->stream_rec);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -207,6 +210,7 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "stream_dynamic")) ctx->tune.stream_dynamic = value;
     else if (!strcmp(key, "router_variant")) ctx->tune.router_variant = value;
     else if (!strcmp(key, "ep_fused_exchange")) ctx->tune.ep_fused_exchange = value;
+    else if (!strcmp(key, "imma_fold")) ctx->tune.imma_fold = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);
     return RUNIT_OK;
 }

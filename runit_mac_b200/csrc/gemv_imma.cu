@@ -35,13 +35,10 @@ __device__ __forceinline__ int k_slot(int e) {
     return 16 * (e & 1) + 4 * (e >> 3) + ((e & 7) >> 1);
 }
 
-// One CTA per unit, one warp per activation row (rows >= batch are written as zeros).
+// Activation row n of unit u by one warp (rows >= batch are written as zeros).
 template <int FMT>
-__global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict__ x, uint8_t* __restrict__ xq, uint32_t k,
-                                                          uint32_t batch) {
-    const uint32_t u = blockIdx.x, n = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t* dst = xq + (size_t)u * kUnitBytes;
-    grid_launch_dependents();   // the consumer may start fetching its weights; it waits for this grid before reading xq
+__device__ __forceinline__ void prepare_row(const float* __restrict__ x, uint8_t* __restrict__ dst, uint32_t k, uint32_t batch, uint32_t u,
+                                            uint32_t n, uint32_t lane) {
     for (int bt = 0; bt < 8; bt++) {
         const float v = n < batch ? x[(size_t)n * k + (size_t)u * 256 + bt * 32 + lane] : 0.f;
         float amax = fabsf(v);
@@ -66,6 +63,14 @@ __global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict
     }
 }
 
+// One CTA per unit, one warp per activation row: the pre-pass as a launch of its own (launches too small to carry it).
+template <int FMT>
+__global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict__ x, uint8_t* __restrict__ xq, uint32_t k,
+                                                          uint32_t batch) {
+    grid_launch_dependents();   // the consumer may start fetching its weights; it waits for this grid before reading xq
+    prepare_row<FMT>(x, xq + (size_t)blockIdx.x * kUnitBytes, k, batch, blockIdx.x, threadIdx.x >> 5, threadIdx.x & 31);
+}
+
 // ───────────────────────── main kernel ─────────────────────────
 // Up to three matrices that share the activations (q | k | v, gate | up) ride one launch: segment i owns the row tiles
 // [tile0[i], tile0[i+1]) and has its own tensor map, row count, output and residual.
@@ -76,6 +81,12 @@ struct Args {
     uint32_t m[3], tile0[3];
     uint32_t nseg, units, batch, csplit;
     int32_t* status;
+    // The pre-pass inside this launch (ctl != nullptr): CTA u < units quantises unit u of x first and publishes the number
+    // of this launch in ctl[64 + u]; a CTA asks for a unit's quantised activations only once its word shows that number.
+    // ctl[0] = number of the last finished launch (advanced by the CTA that leaves last), ctl[1] = exit tickets.
+    const float* x;
+    uint32_t k;
+    uint32_t* ctl;
 };
 struct Maps {
     CUtensorMap m[3];
@@ -158,8 +169,21 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
         for (int w = 0; w < 4; w++)
             tma_load_2d(sb + kUnitBytes + w * WBYTES, wmap, (int32_t)(u * 144), (int32_t)(row_tile0 + w * RW), bar_full + 8 * s);
     };
+    uint32_t launch_no = 0;
     auto issue_x = [&](uint32_t i) {   // its quantised activations
         const uint32_t s = i % kStages, u = u_begin + i;
+        if (a.ctl != nullptr) {
+            // wait (bounded) until the CTA that quantises unit u has published this launch's number
+            const long long t0 = clock64();
+            while (true) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.ctl + 64 + u) : "memory");
+                if (v == launch_no) break;
+                if (clock64() - t0 > (1ll << 28)) { timed_out = true; break; }
+                __nanosleep(40);
+            }
+            fence_proxy_async();       // the bulk load below reads what another CTA stored with ordinary stores
+        }
         bulk_load_1d(base + s * STAGE, a.xq + (size_t)u * kUnitBytes, kUnitBytes, bar_full + 8 * s);
     };
     auto issue = [&](uint32_t i) { issue_w(i); issue_x(i); };
@@ -168,6 +192,18 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     if (tid == 0)
         for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue_w(i);
     grid_dependency_wait();
+    if (a.ctl != nullptr) {
+        // the launch number is read after the wait: the launch before this one has advanced it by then
+        launch_no = *reinterpret_cast<volatile uint32_t*>(a.ctl) + 1u;
+        if (blockIdx.x < a.units) {
+            uint8_t* dst = const_cast<uint8_t*>(a.xq) + (size_t)blockIdx.x * kUnitBytes;
+            prepare_row<FMT>(a.x, dst, a.k, a.batch, blockIdx.x, warp, lane);
+            prepare_row<FMT>(a.x, dst, a.k, a.batch, blockIdx.x, warp + 4, lane);
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) atomicExch(&a.ctl[64 + blockIdx.x], launch_no);
+        }
+    }
     if (tid == 0)
         for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue_x(i);
 
@@ -265,6 +301,14 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
         }
     }
     if (a.csplit > 1) cluster_sync();   // keep every CTA's partial sums alive until rank 0 has read them
+    if (a.ctl != nullptr && tid == 0) {
+        __threadfence();
+        if (atomicAdd(&a.ctl[1], 1u) == gridDim.x - 1) {   // every CTA has consumed its units: the next launch may number itself
+            a.ctl[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t*>(a.ctl) = launch_no;
+        }
+    }
     if (timed_out && a.status) atomicExch(a.status, 1);
 }
 
@@ -316,10 +360,7 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
                         const float* const* res, const uint32_t* m, uint32_t k, uint32_t batch) {
     using namespace imma;
     const uint32_t units = k / 256;
-    if (fmt == RUNIT_FMT_Q4K) xq_prepare_kernel<RUNIT_FMT_Q4K><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
-    else xq_prepare_kernel<RUNIT_FMT_Q4_0><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
-    int32_t st = runit_after_launch(ctx, "gemv_batched_quantise_x");
-    if (st != RUNIT_OK) return st;
+    int32_t st = RUNIT_OK;
     // rows per warp: 32 when that still gives every SM two CTAs, else 16
     const uint32_t sms = (uint32_t)ctx->sm_count;
     uint32_t tiles32 = 0, tiles16 = 0;
@@ -354,6 +395,20 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
     a.batch = batch;
     a.csplit = csplit;
     a.status = ctx->d_status;
+    // Opt-in (tuning key imma_fold): the activation pre-pass rides inside the launch when the grid has a CTA per unit (all
+    // of them resident in the first wave, so a CTA that waits for a unit never keeps its producer off the machine) and the
+    // flag table covers the units.  Measured slower than the pre-pass as a small launch of its own (the quantisation and
+    // the flag round trip then sit at the head of every CTA), so the default is the separate launch.
+    const bool fold = ctx->d_xq_ctl && tiles * csplit >= units && units <= 960 && tiles * csplit >= 2 * units && ctx->tune.imma_fold != 0;
+    if (fold) {
+        a.x = x;
+        a.k = k;
+        a.ctl = ctx->d_xq_ctl;
+    } else {
+        if (fmt == RUNIT_FMT_Q4K) xq_prepare_kernel<RUNIT_FMT_Q4K><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
+        else xq_prepare_kernel<RUNIT_FMT_Q4_0><<<units, 256, 0, ctx->stream>>>(x, (uint8_t*)ctx->d_xq, k, batch);
+        if ((st = runit_after_launch(ctx, "gemv_batched_quantise_x")) != RUNIT_OK) return st;
+    }
     if (fmt == RUNIT_FMT_Q4K) return rw32 ? launch<RUNIT_FMT_Q4K, 32>(ctx, maps, a, tiles) : launch<RUNIT_FMT_Q4K, 16>(ctx, maps, a, tiles);
     return rw32 ? launch<RUNIT_FMT_Q4_0, 32>(ctx, maps, a, tiles) : launch<RUNIT_FMT_Q4_0, 16>(ctx, maps, a, tiles);
 }

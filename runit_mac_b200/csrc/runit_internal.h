@@ -24,6 +24,8 @@ struct runit_tuning {
     int32_t stream_cfg = 0;     // warps per SM x ring stages of that launch: 0 = default, 1..3 = alternatives
     int32_t stream_ksl = 0;     // 0 = warps per tile chosen per GEMV, else forced (experiments)
     int32_t stream_dynamic = 0;
+    int32_t imma_fold = 0;           // batched 4-bit GEMV: 1 = activation pre-pass inside the GEMV launch where the grid allows (measured slower:
+                                     // 950 against 1331 GB/s over the 7B set at batch 8), 0 = a launch of its own
     int32_t ep_fused_exchange = 0;   // expert-parallel decoder: 1 = exchange inside the GEMVs (no launches of its own; measured slower)
     int32_t router_variant = 0;   // batched f32 router: 0 = by size, 1 = one warp per expert, 2 = tiled GEMM (experiments) // 1 = CTAs take items from a shared counter instead of the fixed split (experiments)
 };
@@ -53,6 +55,7 @@ struct runit_ctx {
     int32_t* h_status = nullptr;        // the same word, host side (pinned, mapped)
     uint32_t* d_abort = nullptr;        // device word: set by the first peer barrier that gave up; later barriers skip their wait
     void* d_am = nullptr;               // greedy epilogue of the GEMV: ticket word at 0, result pair at 16, per-tile pairs from 256
+    uint32_t* d_xq_ctl = nullptr;       // batched GEMV with the pre-pass inside: launch number, exit tickets, one flag per unit (from word 64)
     void* d_xq = nullptr;               // staging area of the batched GEMV's quantised activations
     size_t xq_bytes = 0;
     void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation

@@ -568,13 +568,22 @@ def test_greedy_epilogue_of_the_gemv(ctx, oracle, fmt):
         assert logits[3] == logits[m // 2]
 
 
+@pytest.mark.parametrize("fold", [0, 1])
 @pytest.mark.parametrize("batch", [8, 3])
 @pytest.mark.parametrize("fmt", [1, 2])
-def test_batched_gemv_of_several_matrices_in_one_launch(ctx, oracle, fmt, batch):
+def test_batched_gemv_of_several_matrices_in_one_launch(ctx, oracle, fmt, batch, fold):
     """q | k | v and gate | up at batch 2..8: one launch over up to three matrices that share the activations (prepared once)
     gives what the single-matrix launches give, and the oracle's values."""
     import runit_mac_b200 as R
     O = oracle
+    ctx.set_tuning("imma_fold", fold)      # 1: the activation pre-pass inside the GEMV launch (opt-in variant)
+    try:
+        _multi_cases(ctx, R, O, fmt, batch)
+    finally:
+        ctx.set_tuning("imma_fold", 0)
+
+
+def _multi_cases(ctx, R, O, fmt, batch):
     for rows, k in (((3584, 512, 512), 3584), ((1000, 37), 2048), ((96,), 512)):
         rng = np.random.default_rng(9000 + fmt + batch + len(rows))
         ws = [O.rand_weights(fmt, rng, m, k) for m in rows]
