@@ -23,7 +23,7 @@ _KINDS = {
 }
 
 # ggml type id -> kernel format id of include/runit_cuda.h (RUNIT_FMT_*)
-KERNEL_FORMATS = {8: 0, 2: 1, 12: 2}
+KERNEL_FORMATS = {8: 0, 2: 1, 12: 2, 6: 3, 13: 4, 14: 5}     # Q8_0, Q4_0, Q4_K, Q5_0, Q5_K, Q6_K
 
 
 class GgufError(RuntimeError):
@@ -205,8 +205,8 @@ class GgufFile:
         return bytes(buf[: t.data_size()])
 
     def upload_weight(self, ctx, name: str) -> WeightBuf:
-        """Packed bytes of ``name`` in a new device buffer.  ``fmt`` is the kernel format id for Q8_0 / Q4_0 / Q4_K
-        tensors and None for the others (F32 / F16 norms, router, embeddings are uploaded as they are)."""
+        """Packed bytes of ``name`` in a new device buffer.  ``fmt`` is the kernel format id for Q8_0 / Q4_0 / Q4_K / Q5_0 /
+        Q5_K / Q6_K tensors and None for the others (F32 / F16 norms, router, embeddings are uploaded as they are)."""
         t = self.tensor(name)
         buf = ctx.new_buffer(max(16, t.data_size()))
         _check(_api().runit_gguf_upload_tensor(ctx.handle, self._h, name.encode(), C.c_void_p(buf.ptr), buf.nbytes))

@@ -39,6 +39,30 @@ def test_upload_and_gemv_from_a_gguf_file(ctx, oracle, tmp_path):
     assert np.array_equal(nb.buffer.download(np.float32, 2048), norm)
 
 
+def test_kquant_tensors_of_a_mixed_file_stay_packed(ctx, oracle, tmp_path):
+    """A Q4_K_M file mixes Q6_K / Q5_K (and older files Q5_0) tensors among the Q4_K ones; the reference expands them to
+    f16 at load (crates/engine/src/forward.rs:900-949, 979-1012).  Here they are uploaded as stored and multiplied packed."""
+    import runit_mac_b200 as R
+    from runit_mac_b200.gguf import GgufDtype as D, parse_gguf_file
+    O = oracle
+    rng = np.random.default_rng(13)
+    shapes = {"blk.0.ffn_down.weight": (O.Q6K, D.Q6K, 130, 1024, "q6k"), "blk.0.attn_v.weight": (O.Q5K, D.Q5K, 64, 512, "q5k"),
+              "token_embd.weight": (O.Q5_0, D.Q5_0, 100, 256, "q5_0")}
+    ws = {n: O.rand_weights(f, rng, m, k) for n, (f, _, m, k, _) in shapes.items()}
+    path = tmp_path / "mixed.gguf"
+    path.write_bytes(build_gguf([("general.architecture", T_STR, "qwen2")], [(n, [k, m], dt, ws[n]) for n, (_, dt, m, k, _) in shapes.items()]))
+    g = parse_gguf_file(path)
+    for n, (fmt, dt, m, k, kname) in shapes.items():
+        wb = g.upload_weight(ctx, n)
+        assert (wb.fmt, wb.rows, wb.k, wb.dtype) == (fmt, m, k, dt)
+        assert wb.buffer.download(np.uint8, ws[n].nbytes).tobytes() == ws[n].tobytes()
+        x = rng.normal(0, 1, k).astype(np.float32)
+        yb = ctx.new_buffer(m * 4)
+        getattr(R, "gemv_%s_f32in_f32out" % kname)(ctx, wb.buffer, ctx.buffer_from(x), yb, m, k)
+        ctx.flush()
+        assert_close(O, O.gemv(fmt, ws[n], x, m, k, O.TIER_F64), yb.download(np.float32, m), what=n)
+
+
 def test_merged_expert_tensors_feed_the_moe_layer(ctx, oracle, tmp_path):
     """`ffn_*_exps` tensors ([K, rows, E] in file order) stay one packed buffer each (crates/engine/src/forward.rs:1321-1418
     slices them per expert instead)."""
