@@ -290,7 +290,7 @@ def run_shapes(R, ctx, torch, stream, reps=20, min_bytes=600e6):
     names = {FMT_Q8_0: "q8_0", FMT_Q4_0: "q4_0", FMT_Q4K: "q4k", FMT_Q5_0: "q5_0", FMT_Q5K: "q5k", FMT_Q6K: "q6k"}
     for fmt in (FMT_Q4K, FMT_Q4_0, FMT_Q8_0, FMT_Q6K, FMT_Q5K, FMT_Q5_0):
         for m, k in SHAPES[fmt]:
-            for batch in ((1, 8) if (m, k) in ((18944, 3584), (4864, 896)) else (1,)):
+            for batch in ((1, 8) if fmt <= FMT_Q4K and (m, k) in ((18944, 3584), (4864, 896)) else (1,)):
                 wbytes = m * row_bytes(fmt, k)
                 n_inst = int(min(64, max(2, np.ceil(min_bytes / wbytes))))
                 ws = []
