@@ -10,6 +10,7 @@
 // copies are 4-byte ones from the aligned word below); f32 accumulation, shuffle reduction, optional f32 residual.
 // HBM-bound in principle; at ~7 instructions per weight it is issue-bound at roughly half the HBM rate on B200.
 #include "gemv_common.cuh"
+#include "gemv_int8.cuh"
 #include "runit_internal.h"
 #include "tma.cuh"
 
@@ -151,6 +152,144 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_kquant_kernel(const Args a) 
     cp_async_wait<0>();
 }
 
+// ───────────────────────── Q6_K, tile kernel ─────────────────────────
+// Lane = row.  Every warp owns a tile of 32 rows and walks all superblocks of K (4 tiles per CTA, no reduction across
+// warps).  Per superblock the warp copies the 32 rows' 210 bytes into its own two-stage ring (4-byte cp.async from the aligned word
+// below each row's start: a row's superblock starts on a 2-byte boundary only) together with the 256 activations, which
+// it then turns into three signed 8-bit limbs per element with one power-of-two scale per 32 (prep_int_block: 23 bits,
+// exact to f32 rounding).  Every lane decodes its own row: a word of ql low nibbles, a word of ql high nibbles and a word
+// of qh give four weights each of the reference's four groups q1..q4 (forward.rs:920-949) as 6-bit fields in bytes,
+// which meet the limbs in dp4a; the "- 32" is taken through the blocks' sums.  About 1.7 instructions per weight instead
+// of 7, and scales, d and the activations are read once per row-lane instead of once per weight.
+namespace q6t {
+
+constexpr int kPitch = 220;                       // bytes per row in a stage: 53 words + 2 (an odd number of words)
+constexpr int kXOff = 32 * kPitch;                // activations of the unit: 1024 bytes raw, prepared in place
+constexpr int kStage = kXOff + 1024;
+constexpr int kS = 2;
+
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+struct Args {
+    const uint8_t* w;
+    const float* x;
+    float* y;
+    const float* res;
+    uint32_t m, nb, row_bytes;
+};
+
+__global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
+    extern __shared__ __align__(16) uint8_t q6_smem[];
+    grid_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* ring = q6_smem + warp * (kS * kStage);
+    const uint32_t row0 = (blockIdx.x * 4 + warp) * 32;       // every warp owns a tile of 32 rows and walks all of K
+    if (row0 >= a.m) return;
+    const uint32_t rows_here = min(32u, a.m - row0);
+    const int n_it = (int)a.nb;
+
+    auto issue = [&](int it) {
+        if (it < n_it) {
+            const uint32_t u = (uint32_t)it;
+            const uint32_t st = smem_u32(ring + (it % kS) * kStage);
+            for (uint32_t r = 0; r < rows_here; r++) {
+                const size_t start = (size_t)(row0 + r) * a.row_bytes + (size_t)u * 210;
+                const uint32_t shift = (uint32_t)(start & 3u);           // 0 or 2 (the matrix itself is 16-byte aligned)
+                const uint8_t* src = a.w + start - shift;
+                cp_async4(st + r * kPitch + 4 * lane, src + 4 * lane);
+                // words 32 .. 52; with shift 0 the last word holds only two bytes of the row (its f16 d): the copy takes two
+                // bytes from memory, nothing is read past the row
+                if (lane < 20 || (lane == 20 && shift != 0))
+                    cp_async4(st + r * kPitch + 4 * (32 + lane), src + 4 * (32 + lane));
+                else if (lane == 20)     // two bytes from memory, the other two filled with zeros
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, 2;\n" ::"r"(st + r * kPitch + 208), "l"(src + 208) : "memory");
+            }
+            const float* xu = a.x + (size_t)u * 256;
+            cp_async16(st + kXOff + 16 * lane, xu + 4 * lane);
+            cp_async16(st + kXOff + 16 * (32 + lane), xu + 4 * (32 + lane));
+        }
+        cp_async_commit();
+    };
+    grid_dependency_wait();      // x (and the residual) may come from the previous kernel of the chain
+#pragma unroll
+    for (int s = 0; s < kS; s++) issue(s);
+    float acc = 0.f;
+    for (int it = 0; it < n_it; it++) {
+        cp_async_wait<kS - 1>();
+        __syncwarp();
+        uint8_t* stg = ring + (it % kS) * kStage;
+        {   // activations of the unit -> limbs, scales, block sums (in place)
+            float v[8];
+            const float4* xr = reinterpret_cast<const float4*>(stg + kXOff) + 2 * lane;
+            const float4 t0 = xr[0], t1 = xr[1];
+            v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
+            __syncwarp();
+            prep_int_block<8, 8, 0>(stg + kXOff, v, lane);
+            __syncwarp();
+        }
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t u = (uint32_t)it;
+            const uint32_t sh8 = (uint32_t)((((size_t)(row0 + lane) * a.row_bytes + (size_t)u * 210) & 3u) * 8u);   // 0 or 16
+            const uint32_t* rw = reinterpret_cast<const uint32_t*>(stg + lane * kPitch);
+            auto W = [&](int j) -> uint32_t { return __funnelshift_r(rw[j], rw[j + 1], sh8); };
+            const uint8_t* xq = stg + kXOff;
+            const float* sx = reinterpret_cast<const float*>(xq + IntX<8>::SCALE);
+            const int* sv = reinterpret_cast<const int*>(xq + IntX<8>::VSUM);
+            const uint32_t sc_w[4] = {W(48), W(49), W(50), W(51)};           // 16 signed scales
+            const float d = half_bits_to_float(W(52) & 0xFFFFu);
+            float unit_acc = 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                // the 128 weights of this half as 6-bit fields in bytes: q[j][g] = elements 32 j + 4 g .. + 3 of the half
+                uint32_t q[4][8];
+#pragma unroll
+                for (int g = 0; g < 8; g++) {
+                    const uint32_t wa = W(16 * h + g), wc = W(16 * h + 8 + g), wh = W(32 + 8 * h + g);
+                    q[0][g] = (wa & 0x0F0F0F0Fu) | ((wh & 0x03030303u) << 4);
+                    q[1][g] = (wc & 0x0F0F0F0Fu) | ((wh & 0x0C0C0C0Cu) << 2);
+                    q[2][g] = ((wa >> 4) & 0x0F0F0F0Fu) | (wh & 0x30303030u);
+                    q[3][g] = ((wc >> 4) & 0x0F0F0F0Fu) | ((wh >> 2) & 0x30303030u);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int b = 4 * h + j;
+                    const uint4* xl = reinterpret_cast<const uint4*>(xq + b * 96);     // limb l of the block: xl[2 l], xl[2 l + 1]
+                    int s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        const uint4 l0 = xl[hf], l1 = xl[2 + hf], l2 = xl[4 + hf];
+                        const uint32_t x0[4] = {l0.x, l0.y, l0.z, l0.w}, x1[4] = {l1.x, l1.y, l1.z, l1.w}, x2[4] = {l2.x, l2.y, l2.z, l2.w};
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            s0 = dp4a_u8s8(q[j][4 * hf + c], x0[c], s0);
+                            s1 = dp4a_u8s8(q[j][4 * hf + c], x1[c], s1);
+                            s2 = dp4a_u8s8(q[j][4 * hf + c], x2[c], s2);
+                        }
+                    }
+                    // sum q * v over the block, exact in every limb; the reference's q - 32 through the block's sum of v
+                    const float dot = fmaf((float)s2, 65536.f, fmaf((float)s1, 256.f, (float)s0)) - 32.f * (float)sv[b];
+                    const int scb = (int)(int8_t)((sc_w[(2 * b) >> 2] >> (8 * ((2 * b) & 3))) & 0xFFu);   // scales[8 half + 2 group]
+                    unit_acc = fmaf((float)scb * sx[b], dot, unit_acc);
+                }
+            }
+            acc = fmaf(d, unit_acc, acc);
+        }
+        __syncwarp();
+        issue(it + kS);
+    }
+    cp_async_wait<0>();
+    if ((uint32_t)lane < rows_here) {
+        const uint32_t row = row0 + lane;
+        a.y[row] = a.res ? a.res[row] + acc : acc;
+    }
+}
+
+}  // namespace q6t
+
 template <int FMT>
 static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const void* x, void* y, const void* res, uint32_t m, uint32_t k) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
@@ -160,6 +299,37 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
     RUNIT_REQUIRE(ctx, k > 0 && k % be == 0 && k <= (1u << 24), "%s: k=%u is not a positive multiple of %u", name, k, be);
     RUNIT_REQUIRE(ctx, runit_aligned(w, 16) && runit_aligned(x, 16) && runit_aligned(y, 4) && (!res || runit_aligned(res, 4)),
                   "%s: weights and input 16-byte aligned, output 4-byte aligned", name);
+    // the tile kernel needs a tile of 32 rows per warp: with fewer than two warps' worth of tiles per scheduler the first
+    // kernel (one warp per row) keeps more of the machine busy
+    if (FMT == RUNIT_FMT_Q6K && ctx->tune.kquant_variant != 1 && ((m + 31) / 32 >= 8u * (uint32_t)ctx->sm_count || ctx->tune.kquant_variant == 2)) {
+        q6t::Args t;
+        t.w = (const uint8_t*)w;
+        t.x = (const float*)x;
+        t.y = (float*)y;
+        t.res = (const float*)res;
+        t.m = m;
+        t.nb = k / 256;
+        t.row_bytes = (k / 256) * 210u;
+        constexpr int smem = 4 * q6t::kS * q6t::kStage;
+        static bool configured[64] = {false};
+        if (ctx->device >= 0 && ctx->device < 64 && !configured[ctx->device]) {
+            RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(q6t::gemv_q6k_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            configured[ctx->device] = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((m + 127) / 128);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = ctx->tune.pdl ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, q6t::gemv_q6k_tile_kernel, t);
+        if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "launch of %s failed: %s", name, cudaGetErrorString(e));
+        return runit_after_launch(ctx, name);
+    }
     Args a;
     a.w = (const uint8_t*)w;
     a.x = (const float*)x;
