@@ -890,14 +890,20 @@ def main():
 
     if args.one:
         f, m, k, *rest = args.one.split(",")
-        fmt = {"q8_0": FMT_Q8_0, "q4_0": FMT_Q4_0, "q4k": FMT_Q4K}[f]
+        fmt = {"q8_0": FMT_Q8_0, "q4_0": FMT_Q4_0, "q4k": FMT_Q4K, "q5_0": FMT_Q5_0, "q5k": FMT_Q5K, "q6k": FMT_Q6K}[f]
         m, k, batch = int(m), int(k), int(rest[0]) if rest else 1
         w = ctx.new_buffer(m * row_bytes(fmt, k))
-        R.fill_weights(ctx, fmt, w, m * (k // BLOCK[fmt][0]), 5, 0.01)
+        if fmt <= FMT_Q4K:
+            R.fill_weights(ctx, fmt, w, m * (k // BLOCK[fmt][0]), 5, 0.01)
+        else:       # no generator for these formats: any bytes stream at the same speed
+            ctx.call("memset", w, 0x11, m * row_bytes(fmt, k))
         x, y = ctx.new_buffer(4 * k * batch), ctx.new_buffer(4 * m * batch)
         R.fill_normal_f32(ctx, x, k * batch, 3, 1.0)
         for _ in range(3):
-            R.gemv_batched_f32(ctx, fmt, w, x, y, None, m, k, batch)
+            if fmt <= FMT_Q4K:
+                R.gemv_batched_f32(ctx, fmt, w, x, y, None, m, k, batch)
+            else:
+                getattr(R, "gemv_%s_f32in_f32out" % f)(ctx, w, x, y, m, k)
         ctx.flush()
         print(json.dumps({"one": args.one, "launches": ctx.launches}))
         return

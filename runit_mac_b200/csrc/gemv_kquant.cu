@@ -196,17 +196,22 @@ __global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
         if (it < n_it) {
             const uint32_t u = (uint32_t)it;
             const uint32_t st = smem_u32(ring + (it % kS) * kStage);
+            // row r: 53 words from the aligned word below its superblock; lane l copies words l and l + 32 (l < 21).  With
+            // shift 0 the last word holds only two bytes of the row (its f16 d): that copy takes two bytes from memory
+            // (the rest is filled with zeros), so nothing is read past the row.  Branch-free: the size is an operand.
+            const uint8_t* p = a.w + (size_t)row0 * a.row_bytes + (size_t)u * 210;
+            uint32_t dst = st + 4 * lane;
+#pragma unroll 4
             for (uint32_t r = 0; r < rows_here; r++) {
-                const size_t start = (size_t)(row0 + r) * a.row_bytes + (size_t)u * 210;
-                const uint32_t shift = (uint32_t)(start & 3u);           // 0 or 2 (the matrix itself is 16-byte aligned)
-                const uint8_t* src = a.w + start - shift;
-                cp_async4(st + r * kPitch + 4 * lane, src + 4 * lane);
-                // words 32 .. 52; with shift 0 the last word holds only two bytes of the row (its f16 d): the copy takes two
-                // bytes from memory, nothing is read past the row
-                if (lane < 20 || (lane == 20 && shift != 0))
-                    cp_async4(st + r * kPitch + 4 * (32 + lane), src + 4 * (32 + lane));
-                else if (lane == 20)     // two bytes from memory, the other two filled with zeros
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, 2;\n" ::"r"(st + r * kPitch + 208), "l"(src + 208) : "memory");
+                const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 3u);      // 0 or 2
+                const uint8_t* src = p - shift + 4 * lane;
+                cp_async4(dst, src);
+                if (lane < 21) {
+                    const uint32_t nbytes = (lane == 20 && shift == 0) ? 2u : 4u;
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst + 128), "l"(src + 128), "r"(nbytes) : "memory");
+                }
+                p += a.row_bytes;
+                dst += kPitch;
             }
             const float* xu = a.x + (size_t)u * 256;
             cp_async16(st + kXOff + 16 * lane, xu + 4 * lane);
@@ -235,7 +240,11 @@ __global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
             const uint32_t u = (uint32_t)it;
             const uint32_t sh8 = (uint32_t)((((size_t)(row0 + lane) * a.row_bytes + (size_t)u * 210) & 3u) * 8u);   // 0 or 16
             const uint32_t* rw = reinterpret_cast<const uint32_t*>(stg + lane * kPitch);
-            auto W = [&](int j) -> uint32_t { return __funnelshift_r(rw[j], rw[j + 1], sh8); };
+            uint32_t rv[54];                     // the row's words, once; word 53 is never part of a result
+#pragma unroll
+            for (int j = 0; j < 53; j++) rv[j] = rw[j];
+            rv[53] = 0;
+            auto W = [&](int j) -> uint32_t { return __funnelshift_r(rv[j], rv[j + 1], sh8); };
             const uint8_t* xq = stg + kXOff;
             const float* sx = reinterpret_cast<const float*>(xq + IntX<8>::SCALE);
             const int* sv = reinterpret_cast<const int*>(xq + IntX<8>::VSUM);
