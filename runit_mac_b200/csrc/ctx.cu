@@ -96,6 +96,8 @@ static int32_t ctx_init(int32_t device, cudaStream_t adopt, bool adopt_stream, r
     else { c->d_am = nullptr; cudaGetLastError(); }
     if (cudaMalloc((void**)&c->d_xq_ctl, 4096) == cudaSuccess) cudaMemset(c->d_xq_ctl, 0, 4096);
     else { c->d_xq_ctl = nullptr; cudaGetLastError(); }
+    if (cudaMalloc(&c->d_kq, 8192 + (1u << 20)) == cudaSuccess) cudaMemset(c->d_kq, 0, 8192);
+    else { c->d_kq = nullptr; cudaGetLastError(); }
     if (cudaMalloc(&c->d_xq, 4u << 20) == cudaSuccess) c->xq_bytes = 4u << 20;
     else { c->d_xq = nullptr; cudaGetLastError(); }
     {
@@ -159,6 +161,7 @@ int32_t runit_ctx_destroy(runit_ctx_t* ctx) {
     if (ctx->d_xq) cudaFree(ctx->d_xq);
     if (ctx->d_am) cudaFree(ctx->d_am);
     if (ctx->d_xq_ctl) cudaFree(ctx->d_xq_ctl);
+    if (ctx->d_kq) cudaFree(ctx->d_kq);
     if (ctx->d_abort) cudaFree(ctx->d_abort);
     if (ctx->stream_rec) delete static_cast<std::vector<runit::StreamRec>*>(ctx->stream_rec);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);

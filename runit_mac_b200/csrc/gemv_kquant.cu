@@ -180,21 +180,31 @@ struct Args {
     float* y;
     const float* res;
     uint32_t m, nb, row_bytes;
+    // split > 0 (matrices with few rows): a CTA owns ONE tile and one of `split` shares of K; its 4 warps take every
+    // 4 * split-th superblock each, the CTA files one partial sum per row in part[share][row], and the CTA that takes the
+    // last of the tile's tickets adds the shares in order (deterministic) and stores the rows.
+    uint32_t split;
+    float* part;
+    uint32_t* tickets;       // one word per tile, zero at rest
 };
 
 __global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
     extern __shared__ __align__(16) uint8_t q6_smem[];
+    __shared__ float red[4][32];
+    __shared__ uint32_t s_last;
     grid_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint8_t* ring = q6_smem + warp * (kS * kStage);
-    const uint32_t row0 = (blockIdx.x * 4 + warp) * 32;       // every warp owns a tile of 32 rows and walks all of K
+    // split == 0: every warp owns a tile of 32 rows and walks all of K; else the CTA owns tile blockIdx.x
+    const uint32_t row0 = a.split ? blockIdx.x * 32 : (blockIdx.x * 4 + warp) * 32;
     if (row0 >= a.m) return;
     const uint32_t rows_here = min(32u, a.m - row0);
-    const int n_it = (int)a.nb;
+    const uint32_t u0 = a.split ? blockIdx.y * 4 + warp : 0u, ustep = a.split ? 4u * a.split : 1u;
+    const int n_it = u0 < a.nb ? (int)((a.nb - u0 + ustep - 1) / ustep) : 0;
 
     auto issue = [&](int it) {
         if (it < n_it) {
-            const uint32_t u = (uint32_t)it;
+            const uint32_t u = u0 + ustep * (uint32_t)it;
             const uint32_t st = smem_u32(ring + (it % kS) * kStage);
             // row r: 53 words from the aligned word below its superblock; lane l copies words l and l + 32 (l < 21).  With
             // shift 0 the last word holds only two bytes of the row (its f16 d): that copy takes two bytes from memory
@@ -237,7 +247,7 @@ __global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
             __syncwarp();
         }
         if ((uint32_t)lane < rows_here) {
-            const uint32_t u = (uint32_t)it;
+            const uint32_t u = u0 + ustep * (uint32_t)it;
             const uint32_t sh8 = (uint32_t)((((size_t)(row0 + lane) * a.row_bytes + (size_t)u * 210) & 3u) * 8u);   // 0 or 16
             const uint32_t* rw = reinterpret_cast<const uint32_t*>(stg + lane * kPitch);
             uint32_t rv[54];                     // the row's words, once; word 53 is never part of a result
@@ -291,9 +301,32 @@ __global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
         issue(it + kS);
     }
     cp_async_wait<0>();
-    if ((uint32_t)lane < rows_here) {
-        const uint32_t row = row0 + lane;
-        a.y[row] = a.res ? a.res[row] + acc : acc;
+    if (a.split == 0) {
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t row = row0 + lane;
+            a.y[row] = a.res ? a.res[row] + acc : acc;
+        }
+        return;
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        const float v = ((red[0][lane] + red[1][lane]) + red[2][lane]) + red[3][lane];
+        if ((uint32_t)lane < rows_here) __stcg(&a.part[(size_t)blockIdx.y * a.m + row0 + lane], v);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) s_last = atomicAdd(&a.tickets[blockIdx.x], 1u) == a.split - 1;
+    }
+    __syncthreads();
+    if (s_last && warp == 0) {
+        __threadfence();
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t row = row0 + lane;
+            float v = a.res ? a.res[row] : 0.f;
+            for (uint32_t sp = 0; sp < a.split; sp++) v += __ldcg(&a.part[(size_t)sp * a.m + row]);
+            a.y[row] = v;
+        }
+        if (lane == 0) a.tickets[blockIdx.x] = 0;
     }
 }
 
@@ -310,8 +343,20 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
                   "%s: weights and input 16-byte aligned, output 4-byte aligned", name);
     // the tile kernel needs a tile of 32 rows per warp: with fewer than two warps' worth of tiles per scheduler the first
     // kernel (one warp per row) keeps more of the machine busy
-    if (FMT == RUNIT_FMT_Q6K && ctx->tune.kquant_variant != 1 && ((m + 31) / 32 >= 8u * (uint32_t)ctx->sm_count || ctx->tune.kquant_variant == 2)) {
+    if (FMT == RUNIT_FMT_Q6K && ctx->tune.kquant_variant != 1) {
         q6t::Args t;
+        const uint32_t tiles = (m + 31) / 32, sms = (uint32_t)ctx->sm_count, nbk = k / 256;
+        // few tiles: shares of K go to different CTAs (2..16 shares, at least two superblocks per warp, up to 4 CTAs per SM)
+        uint32_t split = 0;
+        if (tiles < 8 * sms && ctx->d_kq && tiles <= 2048 && nbk >= 8) {
+            split = 1;
+            while (split < 16 && tiles * split * 2 <= 8 * sms && nbk / (4 * split * 2) >= 2) split *= 2;
+            if ((size_t)split * m * 4 > (1u << 20)) split = 0;
+        }
+        if (tiles < 8 * sms && split == 0 && ctx->tune.kquant_variant != 2) goto first_kernel;
+        t.split = split;
+        t.part = reinterpret_cast<float*>((uint8_t*)ctx->d_kq + 8192);
+        t.tickets = reinterpret_cast<uint32_t*>(ctx->d_kq);
         t.w = (const uint8_t*)w;
         t.x = (const float*)x;
         t.y = (float*)y;
@@ -326,7 +371,7 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
             configured[ctx->device] = true;
         }
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((m + 127) / 128);
+        cfg.gridDim = split ? dim3(tiles, split) : dim3((m + 127) / 128);
         cfg.blockDim = dim3(128);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = ctx->stream;
@@ -339,6 +384,7 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
         if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "launch of %s failed: %s", name, cudaGetErrorString(e));
         return runit_after_launch(ctx, name);
     }
+first_kernel:
     Args a;
     a.w = (const uint8_t*)w;
     a.x = (const float*)x;

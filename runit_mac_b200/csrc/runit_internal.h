@@ -57,6 +57,7 @@ struct runit_ctx {
     uint32_t* d_abort = nullptr;        // device word: set by the first peer barrier that gave up; later barriers skip their wait
     void* d_am = nullptr;               // greedy epilogue of the GEMV: ticket word at 0, result pair at 16, per-tile pairs from 256
     uint32_t* d_xq_ctl = nullptr;       // batched GEMV with the pre-pass inside: launch number, exit tickets, one flag per unit (from word 64)
+    void* d_kq = nullptr;               // Q6_K GEMV with K split over CTAs: 2048 tile tickets (zero at rest), then 1 MiB of partial sums
     void* d_xq = nullptr;               // staging area of the batched GEMV's quantised activations
     size_t xq_bytes = 0;
     void* encode_tiled = nullptr;       // cuTensorMapEncodeTiled, resolved at context creation

@@ -78,9 +78,9 @@ def test_known_answer_blocks_and_argument_checks(ctx, oracle):
 
 
 def test_q6k_tile_kernel(ctx, oracle):
-    """The Q6_K kernel for large matrices (lane = row, 32-row tiles per warp, dp4a against three 8-bit limbs of the
-    activations; chosen by size, forced here on small and ragged shapes): the oracle's values at the bar of the other
-    kernel, rows that start two bytes off a word boundary, the in-place residual, a non-finite activation, and agreement
+    """The Q6_K tile kernel (lane = row, 32-row tiles, dp4a against three 8-bit limbs of the activations; forced here also on
+    shapes it would leave to the first kernel; (130, 18944) and (301, 2048) split K over several CTAs per tile, the others
+    over the four warps of one): the oracle's values at the bar of the other kernel, rows that start two bytes off a word boundary, the in-place residual, a non-finite activation, and agreement
     with the first kernel."""
     import runit_mac_b200 as R
     O = oracle
