@@ -332,6 +332,280 @@ __global__ void __launch_bounds__(128) gemv_q6k_tile_kernel(const Args a) {
 
 }  // namespace q6t
 
+// ───────────────────────── Q5_K, tile kernel ─────────────────────────
+// The same arrangement for Q5_K: superblocks are 176 bytes and rows 16-byte aligned, so a tile's unit arrives by 16-byte
+// cp.async (11 per row) at a pitch of 176 bytes (an odd multiple of 16: lane = row reads 128 bits without bank conflicts).
+// A word of qs gives four low-nibble weights of block 2j and four high-nibble weights of block 2j + 1; their fifth bits
+// are a nibble of qh (bit e % 8 of qh[e / 8], forward.rs:979-1012), spread into bit 4 of four bytes by one multiply.
+namespace q5t {
+
+constexpr int kPitch = 176;
+constexpr int kXOff = 32 * kPitch;
+constexpr int kStage = kXOff + 1024;
+constexpr int kS = 2;
+
+__global__ void __launch_bounds__(128) gemv_q5k_tile_kernel(const q6t::Args a) {
+    extern __shared__ __align__(16) uint8_t q5_smem[];
+    __shared__ float red[4][32];
+    __shared__ uint32_t s_last;
+    grid_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* ring = q5_smem + warp * (kS * kStage);
+    const uint32_t row0 = a.split ? blockIdx.x * 32 : (blockIdx.x * 4 + warp) * 32;
+    if (row0 >= a.m) return;
+    const uint32_t rows_here = min(32u, a.m - row0);
+    const uint32_t u0 = a.split ? blockIdx.y * 4 + warp : 0u, ustep = a.split ? 4u * a.split : 1u;
+    const int n_it = u0 < a.nb ? (int)((a.nb - u0 + ustep - 1) / ustep) : 0;
+
+    auto issue = [&](int it) {
+        if (it < n_it) {
+            const uint32_t u = u0 + ustep * (uint32_t)it;
+            const uint32_t st = smem_u32(ring + (it % kS) * kStage);
+            const uint8_t* base = a.w + (size_t)row0 * a.row_bytes + (size_t)u * 176;
+#pragma unroll
+            for (int i = 0; i < 11; i++) {
+                const uint32_t c = (uint32_t)lane + 32u * i, r = c / 11u, col = c - 11u * r;      // 352 chunks of 16 bytes
+                if (r < rows_here) cp_async16(st + r * kPitch + 16 * col, base + (size_t)r * a.row_bytes + 16 * col);
+            }
+            const float* xu = a.x + (size_t)u * 256;
+            cp_async16(st + kXOff + 16 * lane, xu + 4 * lane);
+            cp_async16(st + kXOff + 16 * (32 + lane), xu + 4 * (32 + lane));
+        }
+        cp_async_commit();
+    };
+    grid_dependency_wait();
+#pragma unroll
+    for (int s = 0; s < kS; s++) issue(s);
+    float acc = 0.f;
+    for (int it = 0; it < n_it; it++) {
+        cp_async_wait<kS - 1>();
+        __syncwarp();
+        uint8_t* stg = ring + (it % kS) * kStage;
+        {
+            float v[8];
+            const float4* xr = reinterpret_cast<const float4*>(stg + kXOff) + 2 * lane;
+            const float4 t0 = xr[0], t1 = xr[1];
+            v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
+            __syncwarp();
+            prep_int_block<8, 8, 0>(stg + kXOff, v, lane);
+            __syncwarp();
+        }
+        if ((uint32_t)lane < rows_here) {
+            const uint4* ru = reinterpret_cast<const uint4*>(stg + lane * kPitch);
+            const uint8_t* xq = stg + kXOff;
+            const float* sx = reinterpret_cast<const float*>(xq + IntX<8>::SCALE);
+            const int* sv = reinterpret_cast<const int*>(xq + IntX<8>::VSUM);
+            const uint4 hd = ru[0];                                   // d, dmin, 12 bytes of packed 6-bit scales and mins
+            const float d = half_bits_to_float(hd.x), dmin = half_bits_to_float(hd.x >> 16);
+            const Q4KScales sc = q4k_unpack_scales(hd.y, hd.z, hd.w);   // get_scale_min_k4 for j (sl, ml) and j + 4 (sh, mh)
+            const uint4 h0 = ru[1], h1 = ru[2];
+            const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            float unit_acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint4 qa = ru[3 + 2 * j], qb = ru[4 + 2 * j];
+                const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                uint32_t lo[8], hi[8];
+#pragma unroll
+                for (int g = 0; g < 8; g++) {
+                    const int sh = 8 * (g >> 1) + 4 * (g & 1);
+                    const uint32_t nl = (qh[2 * j] >> sh) & 15u, nh = (qh[2 * j + 1] >> sh) & 15u;
+                    lo[g] = (w[g] & 0x0F0F0F0Fu) | (((nl * 0x00204081u) & 0x01010101u) << 4);
+                    hi[g] = ((w[g] >> 4) & 0x0F0F0F0Fu) | (((nh * 0x00204081u) & 0x01010101u) << 4);
+                }
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const int b = 2 * j + half;
+                    const uint32_t* q = half ? hi : lo;
+                    const uint4* xl = reinterpret_cast<const uint4*>(xq + b * 96);
+                    int s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        const uint4 l0 = xl[hf], l1 = xl[2 + hf], l2 = xl[4 + hf];
+                        const uint32_t x0[4] = {l0.x, l0.y, l0.z, l0.w}, x1[4] = {l1.x, l1.y, l1.z, l1.w}, x2[4] = {l2.x, l2.y, l2.z, l2.w};
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            s0 = q6t::dp4a_u8s8(q[4 * hf + c], x0[c], s0);
+                            s1 = q6t::dp4a_u8s8(q[4 * hf + c], x1[c], s1);
+                            s2 = q6t::dp4a_u8s8(q[4 * hf + c], x2[c], s2);
+                        }
+                    }
+                    const float dot = fmaf((float)s2, 65536.f, fmaf((float)s1, 256.f, (float)s0));
+                    const float scw = (float)(((half ? sc.sh : sc.sl) >> (8 * j)) & 0xFFu), mnw = (float)(((half ? sc.mh : sc.ml) >> (8 * j)) & 0xFFu);
+                    unit_acc = fmaf(sx[b], d * scw * dot - dmin * mnw * (float)sv[b], unit_acc);
+                }
+            }
+            acc += unit_acc;
+        }
+        __syncwarp();
+        issue(it + kS);
+    }
+    cp_async_wait<0>();
+    if (a.split == 0) {
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t row = row0 + lane;
+            a.y[row] = a.res ? a.res[row] + acc : acc;
+        }
+        return;
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        const float v = ((red[0][lane] + red[1][lane]) + red[2][lane]) + red[3][lane];
+        if ((uint32_t)lane < rows_here) __stcg(&a.part[(size_t)blockIdx.y * a.m + row0 + lane], v);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) s_last = atomicAdd(&a.tickets[blockIdx.x], 1u) == a.split - 1;
+    }
+    __syncthreads();
+    if (s_last && warp == 0) {
+        __threadfence();
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t row = row0 + lane;
+            float v = a.res ? a.res[row] : 0.f;
+            for (uint32_t sp = 0; sp < a.split; sp++) v += __ldcg(&a.part[(size_t)sp * a.m + row]);
+            a.y[row] = v;
+        }
+        if (lane == 0) a.tickets[blockIdx.x] = 0;
+    }
+}
+
+}  // namespace q5t
+
+// ───────────────────────── Q5_0, tile kernel ─────────────────────────
+// Q5_0 with K a multiple of 256: a unit is eight 22-byte blocks (176 bytes, 256 weights), rows are then multiples of
+// 176 bytes and the copy is the Q5_K one (16-byte cp.async, pitch 176).  Inside the unit the blocks alternate between
+// word-aligned and two bytes off, which a compile-time funnel shift takes care of.  A word of qs gives four low-nibble weights (elements 4 g ..) and four
+// high-nibble weights (elements 16 + 4 g ..); their fifth bits are nibbles g and 4 + g of qh (forward.rs:900-918); the
+// "- 16" is taken through the block's sum of activations.
+namespace q50t {
+
+constexpr int kPitch = 176;
+constexpr int kXOff = 32 * kPitch;
+constexpr int kStage = kXOff + 1024;
+constexpr int kS = 2;
+
+__global__ void __launch_bounds__(128) gemv_q5_0_tile_kernel(const q6t::Args a) {
+    extern __shared__ __align__(16) uint8_t q50_smem[];
+    __shared__ float red[4][32];
+    __shared__ uint32_t s_last;
+    grid_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* ring = q50_smem + warp * (kS * kStage);
+    const uint32_t row0 = a.split ? blockIdx.x * 32 : (blockIdx.x * 4 + warp) * 32;
+    if (row0 >= a.m) return;
+    const uint32_t rows_here = min(32u, a.m - row0);
+    const uint32_t u0 = a.split ? blockIdx.y * 4 + warp : 0u, ustep = a.split ? 4u * a.split : 1u;
+    const int n_it = u0 < a.nb ? (int)((a.nb - u0 + ustep - 1) / ustep) : 0;
+
+    auto issue = [&](int it) {
+        if (it < n_it) {
+            const uint32_t u = u0 + ustep * (uint32_t)it;
+            const uint32_t st = smem_u32(ring + (it % kS) * kStage);
+            const uint8_t* base = a.w + (size_t)row0 * a.row_bytes + (size_t)u * 176;
+#pragma unroll
+            for (int i = 0; i < 11; i++) {
+                const uint32_t c = (uint32_t)lane + 32u * i, r = c / 11u, col = c - 11u * r;
+                if (r < rows_here) cp_async16(st + r * kPitch + 16 * col, base + (size_t)r * a.row_bytes + 16 * col);
+            }
+            const float* xu = a.x + (size_t)u * 256;
+            cp_async16(st + kXOff + 16 * lane, xu + 4 * lane);
+            cp_async16(st + kXOff + 16 * (32 + lane), xu + 4 * (32 + lane));
+        }
+        cp_async_commit();
+    };
+    grid_dependency_wait();
+#pragma unroll
+    for (int s = 0; s < kS; s++) issue(s);
+    float acc = 0.f;
+    for (int it = 0; it < n_it; it++) {
+        cp_async_wait<kS - 1>();
+        __syncwarp();
+        uint8_t* stg = ring + (it % kS) * kStage;
+        {
+            float v[8];
+            const float4* xr = reinterpret_cast<const float4*>(stg + kXOff) + 2 * lane;
+            const float4 t0 = xr[0], t1 = xr[1];
+            v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
+            __syncwarp();
+            prep_int_block<8, 8, 0>(stg + kXOff, v, lane);
+            __syncwarp();
+        }
+        if ((uint32_t)lane < rows_here) {
+            const uint4* ru = reinterpret_cast<const uint4*>(stg + lane * kPitch);
+            uint32_t al[45];                         // the unit's 44 words (al[44] only feeds discarded bytes)
+#pragma unroll
+            for (int j = 0; j < 11; j++) {
+                const uint4 t = ru[j];
+                al[4 * j] = t.x; al[4 * j + 1] = t.y; al[4 * j + 2] = t.z; al[4 * j + 3] = t.w;
+            }
+            al[44] = 0;
+            // 32 bits at the (even, compile-time) byte offset e of the unit
+            auto F = [&](int e) -> uint32_t { return (e & 3) ? __funnelshift_r(al[e >> 2], al[(e >> 2) + 1], 16) : al[e >> 2]; };
+            const uint8_t* xq = stg + kXOff;
+            const float* sx = reinterpret_cast<const float*>(xq + IntX<8>::SCALE);
+            const int* sv = reinterpret_cast<const int*>(xq + IntX<8>::VSUM);
+#pragma unroll
+            for (int b = 0; b < 8; b++) {
+                const float d = half_bits_to_float(F(22 * b) & 0xFFFFu);
+                const uint32_t qh = F(22 * b + 2);
+                const uint4* xl = reinterpret_cast<const uint4*>(xq + b * 96);
+                int s0 = 0, s1 = 0, s2 = 0;
+                uint32_t w[4];
+#pragma unroll
+                for (int g = 0; g < 4; g++) w[g] = F(22 * b + 6 + 4 * g);
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++) {
+                    const uint4 l0 = xl[hf], l1 = xl[2 + hf], l2 = xl[4 + hf];
+                    const uint32_t x0[4] = {l0.x, l0.y, l0.z, l0.w}, x1[4] = {l1.x, l1.y, l1.z, l1.w}, x2[4] = {l2.x, l2.y, l2.z, l2.w};
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        const uint32_t nib = (qh >> (16 * hf + 4 * g)) & 15u;
+                        const uint32_t q = ((hf ? (w[g] >> 4) : w[g]) & 0x0F0F0F0Fu) | (((nib * 0x00204081u) & 0x01010101u) << 4);
+                        s0 = q6t::dp4a_u8s8(q, x0[g], s0);
+                        s1 = q6t::dp4a_u8s8(q, x1[g], s1);
+                        s2 = q6t::dp4a_u8s8(q, x2[g], s2);
+                    }
+                }
+                const float dot = fmaf((float)s2, 65536.f, fmaf((float)s1, 256.f, (float)s0)) - 16.f * (float)sv[b];
+                acc = fmaf(d * sx[b], dot, acc);
+            }
+        }
+        __syncwarp();
+        issue(it + kS);
+    }
+    cp_async_wait<0>();
+    if (a.split == 0) {
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t row = row0 + lane;
+            a.y[row] = a.res ? a.res[row] + acc : acc;
+        }
+        return;
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        const float v = ((red[0][lane] + red[1][lane]) + red[2][lane]) + red[3][lane];
+        if ((uint32_t)lane < rows_here) __stcg(&a.part[(size_t)blockIdx.y * a.m + row0 + lane], v);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) s_last = atomicAdd(&a.tickets[blockIdx.x], 1u) == a.split - 1;
+    }
+    __syncthreads();
+    if (s_last && warp == 0) {
+        __threadfence();
+        if ((uint32_t)lane < rows_here) {
+            const uint32_t row = row0 + lane;
+            float v = a.res ? a.res[row] : 0.f;
+            for (uint32_t sp = 0; sp < a.split; sp++) v += __ldcg(&a.part[(size_t)sp * a.m + row]);
+            a.y[row] = v;
+        }
+        if (lane == 0) a.tickets[blockIdx.x] = 0;
+    }
+}
+
+}  // namespace q50t
+
 template <int FMT>
 static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const void* x, void* y, const void* res, uint32_t m, uint32_t k) {
     if (!ctx) return RUNIT_ERR_BAD_ARG;
@@ -343,14 +617,16 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
                   "%s: weights and input 16-byte aligned, output 4-byte aligned", name);
     // the tile kernel needs a tile of 32 rows per warp: with fewer than two warps' worth of tiles per scheduler the first
     // kernel (one warp per row) keeps more of the machine busy
-    if (FMT == RUNIT_FMT_Q6K && ctx->tune.kquant_variant != 1) {
+    if ((FMT != RUNIT_FMT_Q5_0 || k % 256 == 0) && ctx->tune.kquant_variant != 1) {
         q6t::Args t;
         const uint32_t tiles = (m + 31) / 32, sms = (uint32_t)ctx->sm_count, nbk = k / 256;
-        // few tiles: shares of K go to different CTAs (2..16 shares, at least two superblocks per warp, up to 4 CTAs per SM)
+        // few tiles: shares of K go to different CTAs (2..16 shares, about one superblock per warp at least, fewer than 8 CTAs
+        // per SM; measured on 3584 x 3584: 4 shares 15 -> 9 us, and on 18944 x 3584 two shares gain nothing)
         uint32_t split = 0;
         if (tiles < 8 * sms && ctx->d_kq && tiles <= 2048 && nbk >= 8) {
             split = 1;
-            while (split < 16 && tiles * split * 2 <= 8 * sms && nbk / (4 * split * 2) >= 2) split *= 2;
+            while (split < 16 && tiles * split * 2 < 8 * sms && 4 * split * 2 <= nbk + 2) split *= 2;
+            if (ctx->tune.kquant_split > 0) split = (uint32_t)min(16, ctx->tune.kquant_split);
             if ((size_t)split * m * 4 > (1u << 20)) split = 0;
         }
         if (tiles < 8 * sms && split == 0 && ctx->tune.kquant_variant != 2) goto first_kernel;
@@ -363,11 +639,12 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
         t.res = (const float*)res;
         t.m = m;
         t.nb = k / 256;
-        t.row_bytes = (k / 256) * 210u;
-        constexpr int smem = 4 * q6t::kS * q6t::kStage;
+        t.row_bytes = (k / 256) * (FMT == RUNIT_FMT_Q6K ? 210u : 176u);
+        constexpr int smem = FMT == RUNIT_FMT_Q6K ? 4 * q6t::kS * q6t::kStage : FMT == RUNIT_FMT_Q5K ? 4 * q5t::kS * q5t::kStage : 4 * q50t::kS * q50t::kStage;
+        auto kern = FMT == RUNIT_FMT_Q6K ? q6t::gemv_q6k_tile_kernel : FMT == RUNIT_FMT_Q5K ? q5t::gemv_q5k_tile_kernel : q50t::gemv_q5_0_tile_kernel;
         static bool configured[64] = {false};
         if (ctx->device >= 0 && ctx->device < 64 && !configured[ctx->device]) {
-            RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(q6t::gemv_q6k_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             configured[ctx->device] = true;
         }
         cudaLaunchConfig_t cfg = {};
@@ -380,7 +657,7 @@ static int32_t launch(runit_ctx* ctx, const char* name, const void* w, const voi
         attr[0].val.programmaticStreamSerializationAllowed = ctx->tune.pdl ? 1 : 0;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, q6t::gemv_q6k_tile_kernel, t);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kern, t);
         if (e != cudaSuccess) return runit_fail(ctx, RUNIT_ERR_LAUNCH, "launch of %s failed: %s", name, cudaGetErrorString(e));
         return runit_after_launch(ctx, name);
     }

@@ -77,45 +77,47 @@ def test_known_answer_blocks_and_argument_checks(ctx, oracle):
             bad()
 
 
-def test_q6k_tile_kernel(ctx, oracle):
-    """The Q6_K tile kernel (lane = row, 32-row tiles, dp4a against three 8-bit limbs of the activations; forced here also on
+@pytest.mark.parametrize("fmt,tag", [(5, "q6k"), (4, "q5k"), (3, "q5_0")])
+def test_kquant_tile_kernel(ctx, oracle, fmt, tag):
+    """The Q6_K, Q5_K and Q5_0 tile kernels (lane = row, 32-row tiles, dp4a against three 8-bit limbs of the activations; forced here also on
     shapes it would leave to the first kernel; (130, 18944) and (301, 2048) split K over several CTAs per tile, the others
-    over the four warps of one): the oracle's values at the bar of the other kernel, rows that start two bytes off a word boundary, the in-place residual, a non-finite activation, and agreement
+    over the four warps of one): the oracle's values at the bar of the other kernel, rows that start two bytes off a word boundary (Q6_K), the in-place residual, a non-finite activation, and agreement
     with the first kernel."""
     import runit_mac_b200 as R
     O = oracle
+    gemv, gemv_add = getattr(R, "gemv_%s_f32in_f32out" % tag), getattr(R, "gemv_%s_add_f32_f32in" % tag)
     ctx.set_tuning("kquant_variant", 2)
     try:
         for m, k in ((3, 256), (65, 1024), (37, 3584), (301, 2048), (130, 18944), (41, 768), (129, 1280)):
             rng = np.random.default_rng(6000 + m + k)
-            w = O.rand_weights(5, rng, m, k)
+            w = O.rand_weights(fmt, rng, m, k)
             x = rng.normal(0, 1, k).astype(np.float32)
             x[rng.integers(0, k, 3)] *= 300.0              # outliers: the limbs keep 23 bits per 32-block
             res = rng.normal(0, 1, m).astype(np.float32)
-            ref = O.gemv(5, w, x, m, k, O.TIER_F64)
+            ref = O.gemv(fmt, w, x, m, k, O.TIER_F64)
             wb, xb, yb = ctx.buffer_from(w), ctx.buffer_from(x), ctx.new_buffer(max(16, 4 * m))
-            R.gemv_q6k_f32in_f32out(ctx, wb, xb, yb, m, k)
+            gemv(ctx, wb, xb, yb, m, k)
             ctx.flush()
             got = yb.download(np.float32, m)
-            st = assert_close(O, ref, got, what="q6k tile kernel %dx%d" % (m, k))
+            st = assert_close(O, ref, got, what=tag + " tile kernel %dx%d" % (m, k))
             assert st.max_rel < 2e-5, st
             rb = ctx.buffer_from(res)
-            R.gemv_q6k_add_f32_f32in(ctx, wb, xb, rb, rb, m, k)
+            gemv_add(ctx, wb, xb, rb, rb, m, k)
             ctx.flush()
-            assert_close(O, ref + res, rb.download(np.float32, m), what="q6k tile kernel + residual")
+            assert_close(O, ref + res, rb.download(np.float32, m), what=tag + " tile kernel + residual")
             ctx.set_tuning("kquant_variant", 1)
-            R.gemv_q6k_f32in_f32out(ctx, wb, xb, yb, m, k)
+            gemv(ctx, wb, xb, yb, m, k)
             ctx.flush()
             ctx.set_tuning("kquant_variant", 2)
-            assert_close(O, yb.download(np.float32, m), got, rel_tol=1e-5, what="q6k tile kernel against the first kernel")
+            assert_close(O, yb.download(np.float32, m), got, rel_tol=1e-5, what=tag + " tile kernel against the first kernel")
         # a NaN and an Inf among the activations reach every output as non-finite values
         m, k = 40, 1024
-        w = O.rand_weights(5, np.random.default_rng(1), m, k)
+        w = O.rand_weights(fmt, np.random.default_rng(1), m, k)
         for bad in (np.nan, np.inf):
             x = np.ones(k, np.float32)
             x[517] = bad
             yb = ctx.new_buffer(4 * m)
-            R.gemv_q6k_f32in_f32out(ctx, ctx.buffer_from(w), ctx.buffer_from(x), yb, m, k)
+            gemv(ctx, ctx.buffer_from(w), ctx.buffer_from(x), yb, m, k)
             ctx.flush()
             assert not np.isfinite(yb.download(np.float32, m)).any()
     finally:
