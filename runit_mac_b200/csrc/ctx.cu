@@ -214,6 +214,9 @@ int32_t runit_set_tuning(runit_ctx_t* ctx, const char* key, int32_t value) {
     else if (!strcmp(key, "router_variant")) ctx->tune.router_variant = value;
     else if (!strcmp(key, "ep_fused_exchange")) ctx->tune.ep_fused_exchange = value;
     else if (!strcmp(key, "imma_fold")) ctx->tune.imma_fold = value;
+    else if (!strcmp(key, "imma_rw")) ctx->tune.imma_rw = value;
+    else if (!strcmp(key, "imma_csplit")) ctx->tune.imma_csplit = value;
+    else if (!strcmp(key, "imma_stages")) ctx->tune.imma_stages = value;
     else if (!strcmp(key, "kquant_variant")) ctx->tune.kquant_variant = value;
     else if (!strcmp(key, "kquant_split")) ctx->tune.kquant_split = value;
     else return runit_fail(ctx, RUNIT_ERR_BAD_ARG, "unknown tuning key '%s'", key);

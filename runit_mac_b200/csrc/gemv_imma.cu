@@ -9,10 +9,16 @@
 //     and 15-bit integers q = rint(x / s), stored as a signed high byte and an unsigned low byte in the order the
 //     MMA's B fragments want them, plus s and s * sum(q) per block (for the "- min" / "- 8" terms).  Relative error of
 //     an activation <= 2^-15 of its block maximum, far inside the 1e-3 bar; products and block sums are exact integers.
-//   * the weight nibbles are the MMA's A operand after one mask (low nibbles) or shift+mask (high nibbles).
-//   * per k32 tile: 2 MMAs (high and low activation byte), v = 256 * hi + lo, acc += (scale_w * s) * v - (min_w * s*sum q).
+//     (Q4_0.  Q4_K: one scale per 256-unit and activation row, s = max|x| / 32767, so that the 6-bit block scales stay
+//     integer factors: see prepare_row<Q4_K>.)
+//   * the weight nibbles are the MMA's A operand after one mask (low nibbles) or shift+mask (high nibbles; Q4_K feeds
+//     the high nibbles unshifted, as 16 * nibble, and gives the low-nibble tiles 16 * scale instead).
+//   * Q4_0, per k32 tile: 2 MMAs (high and low activation byte), v = 256 * hi + lo, acc += (scale_w * s) * v - (min_w * s*sum q).
+//   * Q4_K, per k32 tile: 2 MMAs and 8 integer multiply-adds (sc_j times the two limbs' tiles, summed over the unit's eight
+//     blocks in int32); per unit: three more MMAs give sum_j m_j * (block sum of the activation integers) exactly, then one
+//     conversion and acc += s * (d * V - dmin * M).  4.2 -> 2.8 thread instructions per weight.
 //   * CTA = 4 warps on the same K range, each with its own rows (RW = 16 or 32 per warp); the activation unit of a stage
-//     is shared by the 4 warps, the weight boxes arrive by TMA (box RW rows x 144 bytes), 3 stages, mbarrier pipeline.
+//     is shared by the 4 warps, the CTA's weight box arrives by TMA (4 RW rows x 144 bytes), 3 stages (2..8 by a knob), mbarrier pipeline.
 //     Few-tile shapes split K over a thread-block cluster and reduce through distributed shared memory.
 // Reference formulas: Q4_0 value d * (nibble - 8), low nibble = element 2i, high = 2i + 1
 // (crates/kernels/shaders/gemv_q4_0.metal:26-49); Q4_K value d*sc*q - dmin*m (crates/engine/src/forward.rs:1026-1057).
@@ -24,7 +30,7 @@ namespace runit {
 namespace imma {
 
 constexpr int kUnitBytes = 4608;   // activations of one 256-K unit: 4096 bytes of limbs + 256 scales + 256 block sums
-constexpr int kStages = 3;
+constexpr int kMaxStages = 8;       // ring depth is a launch argument (Args::stages, 2..8)
 
 // ───────────────────────── activation pre-pass ─────────────────────────
 // Slot of element e (0..31) of a block in the MMA's K order.  Q4_K: natural.  Q4_0: word t of the block holds
@@ -63,6 +69,52 @@ __device__ __forceinline__ void prepare_row(const float* __restrict__ x, uint8_t
     }
 }
 
+// Q4_K: ONE scale per unit and activation row (s = max|x| over the 256 elements / 32767, q = rint(x / s) as a signed high
+// byte and an unsigned low byte, in the same fragment order).  With a common scale the weights' 6-bit block scales stay
+// integers: the kernel adds sc_j * (q . xq) over the unit's eight blocks in int32 and converts once per unit.  The block
+// sums of xq (for the "- dmin * m_j" term) are kept exactly as three bytes each (signed high, two unsigned), laid out as
+// the B fragments of one more MMA per limb whose A operand is the row's eight 6-bit minimums:
+//   [4096, 4128)        s of the 8 activation rows (f32)
+//   [4128 + 64 l, ...)  limb l (0 = bits 16.., 1 = bits 8..15, 2 = bits 0..7) of the block sums: [activation row][8 bytes in
+//                       the order blocks 0, 2, 4, 6, 1, 3, 5, 7] (the order of the unpacked minimums ml | mh)
+template <>
+__device__ __forceinline__ void prepare_row<RUNIT_FMT_Q4K>(const float* __restrict__ x, uint8_t* __restrict__ dst, uint32_t k, uint32_t batch,
+                                                           uint32_t u, uint32_t n, uint32_t lane) {
+    float v[8];
+    float amax = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int bt = 0; bt < 8; bt++) {
+        v[bt] = n < batch ? x[(size_t)n * k + (size_t)u * 256 + bt * 32 + lane] : 0.f;
+        amax = fmaxf(amax, fabsf(v[bt]));
+        bad |= !(fabsf(v[bt]) <= 3.0e38f);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // an Inf or a NaN in the unit gives a NaN scale: every row's result of that activation row becomes NaN, as a
+    // non-finite activation does (to +-Inf or NaN) in the reference's f32 multiply-add chain
+    bad = __any_sync(0xffffffffu, bad);
+    const float s = bad ? __uint_as_float(0x7FC00000u) : amax * (1.0f / 32767.0f);
+    const float inv = (amax > 0.f && !bad) ? 32767.0f / amax : 0.f;
+#pragma unroll
+    for (int bt = 0; bt < 8; bt++) {
+        const int q = __float2int_rn(v[bt] * inv);
+        int qs = q;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);
+        uint8_t* p = dst + ((bt * 8 + n) * 4 + ((lane & 15) >> 2)) * 16 + (lane >> 4) * 4 + (lane & 3);
+        p[0] = (uint8_t)(q >> 8);      // signed high byte
+        p[8] = (uint8_t)(q & 255);     // unsigned low byte
+        if (lane == 0) {
+            uint8_t* sp = dst + 4128 + n * 8 + (bt >> 1) + 4 * (bt & 1);
+            sp[0] = (uint8_t)(qs >> 16);
+            sp[64] = (uint8_t)((qs >> 8) & 255);
+            sp[128] = (uint8_t)(qs & 255);
+        }
+    }
+    if (lane == 0) reinterpret_cast<float*>(dst + 4096)[n] = s;
+}
+
 // One CTA per unit, one warp per activation row: the pre-pass as a launch of its own (launches too small to carry it).
 template <int FMT>
 __global__ void __launch_bounds__(256) xq_prepare_kernel(const float* __restrict__ x, uint8_t* __restrict__ xq, uint32_t k,
@@ -79,7 +131,7 @@ struct Args {
     float* y[3];
     const float* res[3];
     uint32_t m[3], tile0[3];
-    uint32_t nseg, units, batch, csplit;
+    uint32_t nseg, units, batch, csplit, stages;
     int32_t* status;
     // The pre-pass inside this launch (ctl != nullptr): CTA u < units quantises unit u of x first and publishes the number
     // of this launch in ctl[64 + u]; a CTA asks for a unit's quantised activations only once its word shows that number.
@@ -127,13 +179,23 @@ __device__ __forceinline__ void tile_mma(float (&acc)[4], const uint32_t (&a)[4]
     acc[3] = fmaf(v3, sw1 * xs1, fmaf(-mw1, xm1, acc[3]));
 }
 
+// One k32 tile of the Q4_K path: the two limbs' int32 tiles times the rows' integer block scales, into the unit's sums.
+__device__ __forceinline__ void tile_mma_int(int (&ih)[4], int (&il)[4], const uint32_t (&a)[4], const uint8_t* xaddr, int sc0, int sc1) {
+    const uint4 bf = *reinterpret_cast<const uint4*>(xaddr);
+    int ch[4], cl[4];
+    mma_u8s8(ch, a, bf.x, bf.y);
+    mma_u8u8(cl, a, bf.z, bf.w);
+    ih[0] += sc0 * ch[0]; ih[1] += sc0 * ch[1]; ih[2] += sc1 * ch[2]; ih[3] += sc1 * ch[3];
+    il[0] += sc0 * cl[0]; il[1] += sc0 * cl[1]; il[2] += sc1 * cl[2]; il[3] += sc1 * cl[3];
+}
+
 template <int FMT, int RW>
 __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ Maps wmaps, const Args a) {
     constexpr int WBYTES = RW * 144;                       // one warp's weight box
     constexpr int STAGE = kUnitBytes + 4 * WBYTES;
     constexpr int MT = RW / 16;                            // m16 tiles per warp
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * kStages];
+    __shared__ __align__(8) uint64_t bars[2 * kMaxStages];
     __shared__ float red[4 * RW][8];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     const uint8_t* base_p = smem_raw + (base - smem_u32(smem_raw));
@@ -151,9 +213,10 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     const float* const seg_res = a.res[si];
     const uint32_t u_begin = (uint32_t)(((uint64_t)a.units * crank) / a.csplit), u_end = (uint32_t)(((uint64_t)a.units * (crank + 1)) / a.csplit);
     const uint32_t nu = u_end - u_begin;
-    const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[kStages]);
+    const uint32_t kStages = a.stages;
+    const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[kMaxStages]);
     if (tid == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (uint32_t s = 0; s < kStages; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 4);
         }
@@ -165,9 +228,7 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
         const uint32_t s = i % kStages, u = u_begin + i;
         const uint32_t sb = base + s * STAGE;
         mbar_expect_tx(bar_full + 8 * s, STAGE);
-#pragma unroll
-        for (int w = 0; w < 4; w++)
-            tma_load_2d(sb + kUnitBytes + w * WBYTES, wmap, (int32_t)(u * 144), (int32_t)(row_tile0 + w * RW), bar_full + 8 * s);
+        tma_load_2d(sb + kUnitBytes, wmap, (int32_t)(u * 144), (int32_t)row_tile0, bar_full + 8 * s);   // one box: the four warps' rows
     };
     uint32_t launch_no = 0;
     auto issue_x = [&](uint32_t i) {   // its quantised activations
@@ -232,21 +293,39 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
             const uint8_t* r1 = r0 + 8 * 144;
             if (FMT == RUNIT_FMT_Q4K) {
                 const uint4 h0 = *reinterpret_cast<const uint4*>(r0), h1 = *reinterpret_cast<const uint4*>(r1);
-                const float d0 = half_bits_to_float(h0.x), n0 = half_bits_to_float(h0.x >> 16);
-                const float d1 = half_bits_to_float(h1.x), n1 = half_bits_to_float(h1.x >> 16);
                 const Q4KScales s0 = q4k_unpack_scales(h0.y, h0.z, h0.w), s1 = q4k_unpack_scales(h1.y, h1.z, h1.w);
+                // sum over the unit's blocks of sc_j * (nibbles . activation limb), 16-fold: low-nibble tiles take 16 * sc_j,
+                // high-nibble tiles are fed as (w & 0xF0F0F0F0) = 16 * nibble.  |ih| <= 16 * 8 * 63 * 32 * 15 * 128 < 2^29,
+                // |il| <= 16 * 8 * 63 * 32 * 15 * 255 < 2^30
+                int ih[4] = {0, 0, 0, 0}, il[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const uint32_t w00 = lds32(r0 + 16 + 32 * j + 4 * t), w01 = lds32(r0 + 32 + 32 * j + 4 * t);
                     const uint32_t w10 = lds32(r1 + 16 + 32 * j + 4 * t), w11 = lds32(r1 + 32 + 32 * j + 4 * t);
                     const uint32_t alo[4] = {w00 & 0x0F0F0F0Fu, w10 & 0x0F0F0F0Fu, w01 & 0x0F0F0F0Fu, w11 & 0x0F0F0F0Fu};
-                    const uint32_t ahi[4] = {(w00 >> 4) & 0x0F0F0F0Fu, (w10 >> 4) & 0x0F0F0F0Fu, (w01 >> 4) & 0x0F0F0F0Fu,
-                                             (w11 >> 4) & 0x0F0F0F0Fu};
+                    const uint32_t ahi[4] = {w00 & 0xF0F0F0F0u, w10 & 0xF0F0F0F0u, w01 & 0xF0F0F0F0u, w11 & 0xF0F0F0F0u};
                     // low nibbles: sub-block j (elements 64j..64j+31); high nibbles: sub-block j+4 (64j+32..64j+63)
-                    tile_mma(acc[mt], alo, xb + (2 * j) * 512, scb + (2 * j) * 32, d0 * byte_to_float(s0.sl, j), n0 * byte_to_float(s0.ml, j),
-                             d1 * byte_to_float(s1.sl, j), n1 * byte_to_float(s1.ml, j));
-                    tile_mma(acc[mt], ahi, xb + (2 * j + 1) * 512, scb + (2 * j + 1) * 32, d0 * byte_to_float(s0.sh, j),
-                             n0 * byte_to_float(s0.mh, j), d1 * byte_to_float(s1.sh, j), n1 * byte_to_float(s1.mh, j));
+                    tile_mma_int(ih, il, alo, xb + (2 * j) * 512, (int)(__byte_perm(s0.sl, 0u, 0x4440u + j) << 4), (int)(__byte_perm(s1.sl, 0u, 0x4440u + j) << 4));
+                    tile_mma_int(ih, il, ahi, xb + (2 * j + 1) * 512, (int)__byte_perm(s0.sh, 0u, 0x4440u + j), (int)__byte_perm(s1.sh, 0u, 0x4440u + j));
+                }
+                // sum over the blocks of m_j * (block sum of the activation integers): one MMA per limb of the sums, A = the
+                // rows' minimums in K slots 0..7 (lanes t = 0, 1), zeros elsewhere
+                const uint32_t am[4] = {t == 0 ? s0.ml : t == 1 ? s0.mh : 0u, t == 0 ? s1.ml : t == 1 ? s1.mh : 0u, 0u, 0u};
+                const uint8_t* sl = sb + 4128 + g * 8 + (t & 1) * 4;
+                const uint32_t b_h = t < 2 ? lds32(sl) : 0u, b_m = t < 2 ? lds32(sl + 64) : 0u, b_l = t < 2 ? lds32(sl + 128) : 0u;
+                int mh[4], mm[4], ml[4];
+                mma_u8s8(mh, am, b_h, 0u);
+                mma_u8u8(mm, am, b_m, 0u);
+                mma_u8u8(ml, am, b_l, 0u);
+                const float2 xs = *reinterpret_cast<const float2*>(sb + 4096 + 8 * t);
+                const float d0 = half_bits_to_float(h0.x) * 0.0625f, n0 = half_bits_to_float(h0.x >> 16);
+                const float d1 = half_bits_to_float(h1.x) * 0.0625f, n1 = half_bits_to_float(h1.x >> 16);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float vq = fmaf((float)ih[e], 256.f, (float)il[e]);
+                    const float vm = (float)(mh[e] * 65536 + mm[e] * 256 + ml[e]);      // |.| <= 8 * 63 * 32 * 32767 < 2^29
+                    const float dd = e < 2 ? d0 : d1, nn = e < 2 ? n0 : n1;
+                    acc[mt][e] = fmaf((e & 1) ? xs.y : xs.x, fmaf(dd, vq, -nn * vm), acc[mt][e]);
                 }
             } else {
 #pragma unroll
@@ -314,11 +393,11 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
 
 template <int FMT, int RW>
 static int32_t launch(runit_ctx* ctx, const Maps& map, const Args& a, uint32_t tiles) {
-    constexpr int smem = kStages * (kUnitBytes + 4 * RW * 144) + 128;
+    const int smem = (int)a.stages * (kUnitBytes + 4 * RW * 144) + 128;
     auto kern = gemv_imma_kernel<FMT, RW>;
     static bool configured[16] = {false};
     if (ctx->device < 16 && !configured[ctx->device]) {
-        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxStages * (kUnitBytes + 4 * RW * 144) + 128 > 227 * 1024 ? 227 * 1024 : kMaxStages * (kUnitBytes + 4 * RW * 144) + 128));
         configured[ctx->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -368,10 +447,11 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
         tiles32 += (m[i] + 127) / 128;
         tiles16 += (m[i] + 63) / 64;
     }
-    const bool rw32 = tiles32 >= 2 * sms;
+    const bool rw32 = ctx->tune.imma_rw ? ctx->tune.imma_rw == 32 : tiles32 >= 2 * sms;
     const uint32_t tiles = rw32 ? tiles32 : tiles16;
     uint32_t csplit = 1;
     while (csplit < 8 && tiles * csplit < 4 * sms && units / (csplit * 2) >= 3) csplit *= 2;
+    if (ctx->tune.imma_csplit > 0 && ctx->tune.imma_csplit <= 8 && units >= (uint32_t)ctx->tune.imma_csplit) csplit = (uint32_t)ctx->tune.imma_csplit;
     Args a{};
     Maps maps{};
     a.xq = (const uint8_t*)ctx->d_xq;
@@ -384,7 +464,7 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
         a.m[i] = m[s];
         a.tile0[i] = i < n_mats ? t0 : 0xFFFFFFFFu;
         if (i < n_mats) {
-            st = runit_get_tmap(ctx, w[i], m[i], (uint64_t)units * 144, rw32 ? 32 : 16, 144, &maps.m[i]);
+            st = runit_get_tmap(ctx, w[i], m[i], (uint64_t)units * 144, rw32 ? 128 : 64, 144, &maps.m[i]);
             if (st != RUNIT_OK) return st;
             t0 += rw32 ? (m[i] + 127) / 128 : (m[i] + 63) / 64;
         } else {
@@ -394,6 +474,7 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
     a.units = units;
     a.batch = batch;
     a.csplit = csplit;
+    a.stages = ctx->tune.imma_stages >= 2 && ctx->tune.imma_stages <= (rw32 ? 6 : 8) ? (uint32_t)ctx->tune.imma_stages : 3u;
     a.status = ctx->d_status;
     // Opt-in (tuning key imma_fold): the activation pre-pass rides inside the launch when the grid has a CTA per unit (all
     // of them resident in the first wave, so a CTA that waits for a unit never keeps its producer off the machine) and the

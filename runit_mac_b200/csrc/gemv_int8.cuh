@@ -53,7 +53,10 @@ struct IntX {
 
 // Quantise this lane's EPL consecutive elements v[] (block of 32 = 32/EPL lanes) and store limbs, scale, sum.
 //   ORDER 0: natural element order inside the block; ORDER 1 (Q4_0): even elements first, then odd ones.
-template <int EPL, int NB, int ORDER>
+//   LIMBS 3: 23-bit integers (the text above).  LIMBS 2: 16-bit integers in two signed bytes, |q| <= 127 * 256 + 127 (the
+//   top sliver of a binade takes half the scale): activations rounded to 2^-16 .. 2^-15 of their block maximum, a third
+//   fewer dp4a and shared-memory reads; the third limb's 32 bytes stay unused.
+template <int EPL, int NB, int ORDER, int LIMBS = 3>
 __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL], int lane) {
     constexpr int LPB = 32 / EPL;                 // lanes per block
     const uint32_t mb = block_max_bits<EPL, LPB>(v);
@@ -61,14 +64,16 @@ __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL
     (void)m;
     const uint32_t e = mb >> 23;                  // biased exponent of the block maximum (255: a non-finite activation)
     const bool live = e >= 22u && e < 255u;       // zero / denormal-tiny blocks contribute nothing
-    const float inv = live ? __uint_as_float((275u - e) << 23) : 0.f;     // 2^22 / 2^(e-126)
+    const uint32_t sh = (LIMBS == 2 && live && m * __uint_as_float((268u - e) << 23) > 32639.0f) ? 1u : 0u;
+    const float inv = live ? __uint_as_float(((LIMBS == 2 ? 268u - sh : 275u) - e) << 23) : 0.f;     // 2^22 (2^14) / 2^(e-126)
     // a block that holds an Inf or a NaN gets a NaN scale: every row's sum becomes NaN, as a non-finite activation
     // does (to +-Inf or NaN) in the reference's f32 multiply-add chain
-    const float scale = live ? __uint_as_float((e - 21u) << 23) : (e == 255u ? __uint_as_float(0x7FC00000u) : 0.f);    // 2^(e-126) / 2^22
+    const float scale = live ? __uint_as_float((e - (LIMBS == 2 ? 14u - sh : 21u)) << 23)
+                             : (e == 255u ? __uint_as_float(0x7FC00000u) : 0.f);    // 1 / inv
     int a0[EPL], a1[EPL], a2[EPL], vs = 0;
 #pragma unroll
     for (int i = 0; i < EPL; i++) {
-        const int q = live ? __float2int_rn(v[i] * inv) : 0;   // exact product, one rounding; |q| < 2^22
+        const int q = live ? __float2int_rn(v[i] * inv) : 0;   // exact product, one rounding; |q| < 2^22 (2^15)
         vs += q;
         a0[i] = (int)(int8_t)q;
         const int q1 = (q - a0[i]) >> 8;
@@ -85,7 +90,7 @@ __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL
     if (EPL == 8) {
         if (ORDER == 0) {
 #pragma unroll
-            for (int l = 0; l < 3; l++) {
+            for (int l = 0; l < LIMBS; l++) {
                 const int* a = l == 0 ? a0 : (l == 1 ? a1 : a2);
                 uint2 w;
                 w.x = pack4(a[0], a[1], a[2], a[3]);
@@ -94,7 +99,7 @@ __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL
             }
         } else {
 #pragma unroll
-            for (int l = 0; l < 3; l++) {
+            for (int l = 0; l < LIMBS; l++) {
                 const int* a = l == 0 ? a0 : (l == 1 ? a1 : a2);
                 *reinterpret_cast<uint32_t*>(base + l * 32 + t * 4) = pack4(a[0], a[2], a[4], a[6]);        // even elements
                 *reinterpret_cast<uint32_t*>(base + l * 32 + 16 + t * 4) = pack4(a[1], a[3], a[5], a[7]);   // odd elements
@@ -102,7 +107,7 @@ __device__ __forceinline__ void prep_int_block(uint8_t* xq, const float (&v)[EPL
         }
     } else {   // EPL == 4 (Q8_0)
 #pragma unroll
-        for (int l = 0; l < 3; l++) {
+        for (int l = 0; l < LIMBS; l++) {
             const int* a = l == 0 ? a0 : (l == 1 ? a1 : a2);
             *reinterpret_cast<uint32_t*>(base + l * 32 + t * 4) = pack4(a[0], a[1], a[2], a[3]);
         }
@@ -209,22 +214,21 @@ __device__ __forceinline__ float unit_q8_0_i8(const uint8_t* up, const uint8_t* 
             const uint32_t dw = w[o0 >> 2];
             const float d = half_bits_to_float((o0 & 2) ? (dw >> 16) : dw);
             const uint4* xl = reinterpret_cast<const uint4*>(xq + blk * 96);
-            int s0 = 0, s1 = 0, s2 = 0;
+            int s0 = 0, s1 = 0;
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const uint4 l0 = xl[h], l1 = xl[2 + h], l2 = xl[4 + h];
-                const uint32_t x0[4] = {l0.x, l0.y, l0.z, l0.w}, x1[4] = {l1.x, l1.y, l1.z, l1.w}, x2[4] = {l2.x, l2.y, l2.z, l2.w};
+                const uint4 l0 = xl[h], l1 = xl[2 + h];
+                const uint32_t x0[4] = {l0.x, l0.y, l0.z, l0.w}, x1[4] = {l1.x, l1.y, l1.z, l1.w};
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     const int wi = s + 4 * h + c;
                     const uint32_t Q = ((o0 + 2) & 2) ? __funnelshift_r(w[wi], w[wi + 1], 16) : w[wi];
                     s0 = dp4a_ss(Q, x0[c], s0);
                     s1 = dp4a_ss(Q, x1[c], s1);
-                    s2 = dp4a_ss(Q, x2[c], s2);
                 }
             }
-            // |q| up to 127: the limb sums are combined in f32 (each is exact, < 2^20)
-            acc += (d * sx[blk]) * fmaf(65536.f, (float)s2, fmaf(256.f, (float)s1, (float)s0));
+            // two limbs (16-bit activations): |s1 * 256 + s0| <= 32 * 127 * 32639 < 2^28, exact in int32
+            acc += (d * sx[blk]) * (float)(s1 * 256 + s0);
         }
     }
     return acc;

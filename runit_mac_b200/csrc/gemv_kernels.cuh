@@ -551,7 +551,7 @@ __global__ void __launch_bounds__(kNT, S <= 2 ? 4 : 3) gemv_staged_kernel(const 
             }
         }
         if (MATH == 1) {
-            prep_int_block<EPL, T::UE / 32, FMT == RUNIT_FMT_Q4_0 ? 1 : 0>(slot + L::XP_OFF, v[0], lane);
+            prep_int_block<EPL, T::UE / 32, FMT == RUNIT_FMT_Q4_0 ? 1 : 0, FMT == RUNIT_FMT_Q8_0 ? 2 : 3>(slot + L::XP_OFF, v[0], lane);
             return;
         }
         if constexpr (MATH == 2) {

@@ -26,6 +26,7 @@ struct runit_tuning {
     int32_t stream_dynamic = 0;
     int32_t kquant_split = 0;        // K-quant tile kernels: 0 = shares of K chosen from the shape, 1..16 = this many (power of two)
     int32_t kquant_variant = 0;      // Q6_K / Q5_K / Q5_0 GEMV: 0 = tile kernel (lane = row, dp4a), 1 = one warp per row (the first kernel; cross-check)
+    int32_t imma_rw = 0, imma_csplit = 0, imma_stages = 0;   // batched 4-bit GEMV: rows per warp (16 / 32), cluster size over K, ring depth; 0 = chosen from the shape
     int32_t imma_fold = 0;           // batched 4-bit GEMV: 1 = activation pre-pass inside the GEMV launch where the grid allows (measured slower:
                                      // 950 against 1331 GB/s over the 7B set at batch 8), 0 = a launch of its own
     int32_t ep_fused_exchange = 0;   // expert-parallel decoder: 1 = exchange inside the GEMVs (no launches of its own; measured slower)
