@@ -17,7 +17,7 @@
 //   * Q4_K, per k32 tile: 2 MMAs and 8 integer multiply-adds (sc_j times the two limbs' tiles, summed over the unit's eight
 //     blocks in int32); per unit: three more MMAs give sum_j m_j * (block sum of the activation integers) exactly, then one
 //     conversion and acc += s * (d * V - dmin * M).  4.2 -> 2.8 thread instructions per weight.
-//   * CTA = 4 warps on the same K range, each with its own rows (RW = 16 or 32 per warp); the activation unit of a stage
+//   * CTA = 4 consumer warps on the same K range (a fifth warp issues the copies), each with its own rows (RW = 16 or 32 per warp); the activation unit of a stage
 //     is shared by the 4 warps, the CTA's weight box arrives by TMA (4 RW rows x 144 bytes), 3 stages (2..8 by a knob), mbarrier pipeline.
 //     Few-tile shapes split K over a thread-block cluster and reduce through distributed shared memory.
 // Reference formulas: Q4_0 value d * (nibble - 8), low nibble = element 2i, high = 2i + 1
@@ -190,7 +190,7 @@ __device__ __forceinline__ void tile_mma_int(int (&ih)[4], int (&il)[4], const u
 }
 
 template <int FMT, int RW>
-__global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ Maps wmaps, const Args a) {
+__global__ void __launch_bounds__(160) gemv_imma_kernel(const __grid_constant__ Maps wmaps, const Args a) {
     constexpr int WBYTES = RW * 144;                       // one warp's weight box
     constexpr int STAGE = kUnitBytes + 4 * WBYTES;
     constexpr int MT = RW / 16;                            // m16 tiles per warp
@@ -250,23 +250,32 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     auto issue = [&](uint32_t i) { issue_w(i); issue_x(i); };
     // The weights do not depend on the activation pre-pass: their first loads go out before the dependency wait
     // (programmatic dependent launch), the activations after it.
-    if (tid == 0)
-        for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue_w(i);
+    const bool producer = tid == 128;      // lane 0 of warp 4 issues every copy; warps 0..3 consume
+    if (producer)
+        for (uint32_t i = 0; i < kStages && i < nu; i++) issue_w(i);
     grid_dependency_wait();
     if (a.ctl != nullptr) {
         // the launch number is read after the wait: the launch before this one has advanced it by then
         launch_no = *reinterpret_cast<volatile uint32_t*>(a.ctl) + 1u;
         if (blockIdx.x < a.units) {
             uint8_t* dst = const_cast<uint8_t*>(a.xq) + (size_t)blockIdx.x * kUnitBytes;
-            prepare_row<FMT>(a.x, dst, a.k, a.batch, blockIdx.x, warp, lane);
-            prepare_row<FMT>(a.x, dst, a.k, a.batch, blockIdx.x, warp + 4, lane);
+            if (warp < 4) {
+                prepare_row<FMT>(a.x, dst, a.k, a.batch, blockIdx.x, warp, lane);
+                prepare_row<FMT>(a.x, dst, a.k, a.batch, blockIdx.x, warp + 4, lane);
+            }
             __threadfence();
             __syncthreads();
             if (tid == 0) atomicExch(&a.ctl[64 + blockIdx.x], launch_no);
         }
     }
-    if (tid == 0)
-        for (uint32_t i = 0; i < kStages - 1 && i < nu; i++) issue_x(i);
+    if (producer) {
+        for (uint32_t i = 0; i < kStages && i < nu; i++) issue_x(i);
+        // the ring's later rounds: stage j % kStages is free once all four warps have released unit j - kStages
+        for (uint32_t j = kStages; j < nu; j++) {
+            if (!mbar_wait(bar_empty + 8 * (j % kStages), ((j / kStages) - 1) & 1)) { timed_out = true; break; }
+            issue(j);
+        }
+    }
 
     float acc[MT][4];
 #pragma unroll
@@ -274,14 +283,8 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
 
-    for (uint32_t i = 0; i < nu; i++) {
+    for (uint32_t i = 0; i < (warp < 4 ? nu : 0u); i++) {
         const uint32_t s = i % kStages;
-        if (tid == 0 && i + kStages - 1 < nu) {
-            const uint32_t j = i + kStages - 1, sj = j % kStages;
-            // the stage being refilled was used by unit j - kStages: wait until all four warps have released it
-            if (j >= kStages && !mbar_wait(bar_empty + 8 * sj, ((j / kStages) - 1) & 1)) timed_out = true;
-            issue(j);
-        }
         if (!mbar_wait(bar_full + 8 * s, (i / kStages) & 1)) { timed_out = true; break; }
         const uint8_t* sb = base_p + s * STAGE;
         const uint8_t* wb = sb + kUnitBytes + warp * WBYTES;
@@ -358,7 +361,7 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
 
     // partial sums of this CTA: rows (warp * RW + mt * 16 + g, + 8), columns 2t, 2t+1
 #pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
+    for (int mt = 0; mt < (warp < 4 ? MT : 0); mt++) {
         red[warp * RW + mt * 16 + g][2 * t] = acc[mt][0];
         red[warp * RW + mt * 16 + g][2 * t + 1] = acc[mt][1];
         red[warp * RW + mt * 16 + g + 8][2 * t] = acc[mt][2];
@@ -366,7 +369,7 @@ __global__ void __launch_bounds__(128) gemv_imma_kernel(const __grid_constant__ 
     }
     if (a.csplit > 1) cluster_sync();
     else __syncthreads();
-    if (crank == 0) {
+    if (crank == 0 && tid < 128) {
         for (uint32_t e = tid; e < 4 * RW * 8; e += 128) {
             const uint32_t r = e % (4 * RW), c = e / (4 * RW);      // consecutive threads -> consecutive rows of one column
             float v = red[r][c];
@@ -402,7 +405,7 @@ static int32_t launch(runit_ctx* ctx, const Maps& map, const Args& a, uint32_t t
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * a.csplit);
-    cfg.blockDim = dim3(128);
+    cfg.blockDim = dim3(160);      // four consumer warps + the producer warp
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
@@ -450,7 +453,8 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
     const bool rw32 = ctx->tune.imma_rw ? ctx->tune.imma_rw == 32 : tiles32 >= 2 * sms;
     const uint32_t tiles = rw32 ? tiles32 : tiles16;
     uint32_t csplit = 1;
-    while (csplit < 8 && tiles * csplit < 4 * sms && units / (csplit * 2) >= 3) csplit *= 2;
+    // measured (rows per warp x cluster size x ring depth on six shapes): split K while the grid stays within two CTAs per SM
+    while (csplit < 8 && tiles * csplit * 2 <= 2 * sms && units / (csplit * 2) >= 3) csplit *= 2;
     if (ctx->tune.imma_csplit > 0 && ctx->tune.imma_csplit <= 8 && units >= (uint32_t)ctx->tune.imma_csplit) csplit = (uint32_t)ctx->tune.imma_csplit;
     Args a{};
     Maps maps{};
@@ -474,7 +478,17 @@ int32_t gemv_imma_multi(runit_ctx* ctx, int fmt, uint32_t n_mats, const void* co
     a.units = units;
     a.batch = batch;
     a.csplit = csplit;
-    a.stages = ctx->tune.imma_stages >= 2 && ctx->tune.imma_stages <= (rw32 ? 6 : 8) ? (uint32_t)ctx->tune.imma_stages : 3u;
+    {   // ring depth: as deep as shared memory allows with every CTA of the grid resident (one wave), at most half the
+        // CTA's units and 6, at least 3; a grid of several waves keeps 3 (more CTAs per SM pay more than a deeper ring)
+        const uint32_t stage_bytes = imma::kUnitBytes + 4 * (rw32 ? 32 : 16) * 144, grid = tiles * csplit;
+        const uint32_t want_per_sm = (grid + sms - 1) / sms, fit3 = (220u * 1024) / (3 * stage_bytes);
+        uint32_t st3 = 3;
+        if (want_per_sm <= fit3) st3 = (220u * 1024) / (want_per_sm * stage_bytes);
+        const uint32_t nu = units / csplit;
+        st3 = st3 < nu / 2 ? st3 : nu / 2;
+        a.stages = st3 < 3 ? 3u : (st3 > 6 ? 6u : st3);
+        if (ctx->tune.imma_stages >= 2 && ctx->tune.imma_stages <= (rw32 ? 6 : 8)) a.stages = (uint32_t)ctx->tune.imma_stages;
+    }
     a.status = ctx->d_status;
     // Opt-in (tuning key imma_fold): the activation pre-pass rides inside the launch when the grid has a CTA per unit (all
     // of them resident in the first wave, so a CTA that waits for a unit never keeps its producer off the machine) and the
