@@ -351,7 +351,7 @@ def zipf_routing(torch, T, E, k, seed, s=1.1):
     return idx, w
 
 
-def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8):
+def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8, zipf_s=1.1, name="qwen3-moe"):
     """Qwen3-MoE-shaped batched MoE block (hidden 2048, 128 experts, top-8, expert intermediate 768, Q4_K experts
     dequantised to bf16 tiles feeding the tcgen05 grouped GEMM), T tokens ~ N(0,1), Zipf(1.1) expert popularity.
     Timed per layer over the expert part (permutation, both grouped GEMMs, combine) with the routing given."""
@@ -360,7 +360,7 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
     for i, (b, rows, kk) in enumerate(((gate, E * ff, h), (up, E * ff, h), (down, E * h, ff))):
         R.fill_weights(ctx, FMT_Q4K, b, rows * (kk // 256), 5 + i, 0.01)
     x = torch.randn(T, h, device="cuda")
-    idx, w = zipf_routing(torch, T, E, k, 1)
+    idx, w = zipf_routing(torch, T, E, k, 1, s=zipf_s)
     out = torch.empty(T, h, device="cuda")
     nbytes = R.moe_grouped_scratch_bytes(ctx, T, h, ff, E, k)
     scratch = ctx.new_buffer(nbytes)
@@ -386,8 +386,10 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
     flops = 2.0 * T * k * 3 * h * ff                  # useful multiply-adds of the three expert products
     padded = 2.0 * issued_cols * 3 * h * ff            # what the MMAs issue
     peak, kind = measured_tensor_peak()
-    return {"workload": "qwen3-moe-shaped MoE block, %d tokens, %d experts top-%d, hidden %d, intermediate %d, Q4_K -> bf16 tiles, "
-                        "Zipf(1.1) routing" % (T, E, k, h, ff),
+    wbytes = int((cnt > 0).sum().item()) * 3 * h * ff * 144 // 256       # every expert that has a slot is streamed once
+    return {"workload": "%s-shaped MoE block, %d tokens, %d experts top-%d, hidden %d, intermediate %d, Q4_K -> bf16 tiles, "
+                        "Zipf(%.1f) routing" % (name, T, E, k, h, ff, zipf_s),
+            "weight_gbs": wbytes / (ms * 1e-3) / 1e9,
             "ms_per_layer": ms, "tokens_per_s": T / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
             "frac_of_tensor_peak": flops / (ms * 1e-3) / 1e12 / peak, "peak_tflops": peak, "peak_kind": kind,
             "issued_over_useful_flops": padded / flops, "token_tiles": tiles, "slots_per_expert_max": int(cnt.max().item()),
@@ -855,6 +857,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE-layer / OLMoE-decode / sharded lm_head figures")
     ap.add_argument("--one", default="", help="fmt,m,k[,batch]: launch this one GEMV shape three times and exit (for ncu captures)")
     ap.add_argument("--block", default="", help="T: run the Qwen3-MoE-shaped batched MoE block on T tokens, print its figures and exit")
+    ap.add_argument("--block-shape", default="qwen3", choices=("qwen3", "olmoe"), help="shape of the --block run")
     ap.add_argument("--decode", action="store_true", help="only the OLMoE-shaped greedy decode figure (tok/s), then exit")
     ap.add_argument("--prefill", default="", help="T: batched prefill of T tokens on a 2-layer OLMoE-shaped decoder, three times, then exit "
                                                   "(the small case for ncu captures of the prefill kernels)")
@@ -952,7 +955,11 @@ def main():
         print(json.dumps(ex["olmoe_decode_q4k"]), flush=True)
         return
     if args.block:
-        print(json.dumps(run_block(R, ctx, torch, stream, T=int(args.block), reps=max(args.steps // 2, 3))), flush=True)
+        if args.block_shape == "olmoe":     # BASELINE configs[2]: 64 experts, intermediate 1024, routing without skew
+            print(json.dumps(run_block(R, ctx, torch, stream, T=int(args.block), reps=max(args.steps // 2, 3), E=64, ff=1024, zipf_s=0.0,
+                                       name="olmoe")), flush=True)
+        else:
+            print(json.dumps(run_block(R, ctx, torch, stream, T=int(args.block), reps=max(args.steps // 2, 3))), flush=True)
         return
     sets = [GemvSet(R, ctx, FMT_Q4K, 1002 + rank, args.layers), GemvSet(R, ctx, FMT_Q4_0, 2002 + rank, args.layers)]
     bytes_fmt = [pass_bytes(s.fmt, args.layers) for s in sets]
