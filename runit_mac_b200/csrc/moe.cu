@@ -110,6 +110,94 @@ __global__ void __launch_bounds__(256) router_f32_tiled_kernel(const float* __re
     }
 }
 
+// Many tokens, few experts: the same product with K split over the eight warps of a CTA.  CTA = 16 tokens x 64 experts;
+// warp w multiplies the whole tile over its eighth of K (chunks of 32 staged by cp.async in its own two shared-memory
+// buffers, rows as in memory), a lane keeps 4 tokens x 8 experts (tokens ty + 4 i, experts tx + 8 j: consecutive rows per load, no bank
+// conflicts) and reads 12 x 128 bits per 128 multiply-adds; the eight partial tiles are added in warp order.  Every logit is
+// eight fused multiply-add chains over ascending k, added in order: the same bits whatever T is.  K must be a multiple of 256.
+constexpr int kRsPitch = 36;                                    // floats per staged row (32 + 4)
+constexpr int kRsWarpFloats = (16 + 64) * kRsPitch;             // one warp's slice
+__global__ void __launch_bounds__(256) router_f32_splitk_kernel(const float* __restrict__ w, const float* __restrict__ x,
+                                                                 float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
+    grid_dependency_wait();      // inputs come from the previous kernel of the chain
+    grid_launch_dependents();
+    extern __shared__ __align__(16) float rs_smem[];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, ty = lane >> 3, tx = lane & 7;
+    const uint32_t e0 = blockIdx.x * 64, t0 = blockIdx.y * 16;
+    float* xs = rs_smem + warp * (2 * kRsWarpFloats);            // two buffers of [16][36] + [64][36]
+    float* ws = xs + 16 * kRsPitch;
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+    const uint32_t kw = K / 8, k_begin = warp * kw, n_chunks = kw / 32;
+    const uint32_t lrow = lane >> 3, lkq = lane & 7;             // a copy instruction covers 4 rows x 32 k
+    // two buffers per warp: chunk c + 1 is copied (cp.async, 16 bytes per lane and row group) while chunk c is multiplied;
+    // rows past T or E are copied from row 0 of the same matrix (never stored)
+    auto stage = [&](uint32_t c) {
+        if (c < n_chunks) {
+            const uint32_t kc = k_begin + 32 * c;
+            const uint32_t xb = smem_u32(xs + (c & 1) * kRsWarpFloats), wb = smem_u32(ws + (c & 1) * kRsWarpFloats);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t row = lrow + 4 * j, tr = t0 + row < T ? t0 + row : 0u;
+                cp_async16(xb + (row * kRsPitch + 4 * lkq) * 4, x + (size_t)tr * K + kc + 4 * lkq);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const uint32_t row = lrow + 4 * j, er = e0 + row < E ? e0 + row : 0u;
+                cp_async16(wb + (row * kRsPitch + 4 * lkq) * 4, w + (size_t)er * K + kc + 4 * lkq);
+            }
+        }
+        cp_async_commit();
+    };
+    stage(0);
+    for (uint32_t c = 0; c < n_chunks; c++) {
+        stage(c + 1);
+        cp_async_wait<1>();
+        __syncwarp();
+        const float* xs_c = xs + (c & 1) * kRsWarpFloats;
+        const float* ws_c = ws + (c & 1) * kRsWarpFloats;
+#pragma unroll
+        for (int k4 = 0; k4 < 8; k4++) {
+            float4 xa[4], wb[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) xa[i] = *reinterpret_cast<const float4*>(xs_c + (ty + 4 * i) * kRsPitch + 4 * k4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) wb[j] = *reinterpret_cast<const float4*>(ws_c + (tx + 8 * j) * kRsPitch + 4 * k4);
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float a = acc[i][j];
+                    a = fmaf(wb[j].x, xa[i].x, a);
+                    a = fmaf(wb[j].y, xa[i].y, a);
+                    a = fmaf(wb[j].z, xa[i].z, a);
+                    a = fmaf(wb[j].w, xa[i].w, a);
+                    acc[i][j] = a;
+                }
+        }
+        __syncwarp();
+    }
+    // the eight partial tiles meet in shared memory ([warp][token][expert]) and are added in warp order
+    __syncthreads();
+    float* red = rs_smem;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) red[(warp * 16 + ty + 4 * i) * 64 + tx + 8 * j] = acc[i][j];
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const uint32_t o = tid + 256 * q, tok = o >> 6, e = o & 63;
+        float v = red[tok * 64 + e];
+#pragma unroll
+        for (int p = 1; p < 8; p++) v += red[(p * 16 + tok) * 64 + e];
+        if (t0 + tok < T && e0 + e < E) logits[(size_t)(t0 + tok) * E + e0 + e] = v;
+    }
+}
+
 // Generic fallback for any K (multiple of 4).
 __global__ void __launch_bounds__(256) router_f32_generic_kernel(const float* __restrict__ w, const float* __restrict__ x,
                                                                   float* __restrict__ logits, uint32_t E, uint32_t K, uint32_t T) {
@@ -368,8 +456,22 @@ static MoeScratch moe_carve(void* base, uint32_t T, uint32_t h, uint32_t ff, uin
 
 // Shared with the batched block (moe_grouped.cu).
 int32_t moe_router(runit_ctx* ctx, const float* w, const float* x, float* logits, uint32_t E, uint32_t K, uint32_t T) {
-    // measured (h = 2048, warm): the tiled kernel has a floor of about 85 us (one CTA walks all of K) and wins from about
-    // 4096 tokens x 128 experts (134 against 226 us); below that one warp per expert is faster (2048 x 64: 60 against 88 us)
+    // (the tiled kernel, one CTA per 64 tokens walking all of K, has a floor of about 85 us: it serves K that is not a
+    // multiple of 256 at large sizes and stays selectable, router_variant = 2)
+    // measured (h = 2048, warm, us): one warp per expert / tiled / split over the warps of a CTA: 64 experts x 256 tokens
+    // 10 / 87 / 22, x 1024: 32 / 87 / 22, x 2048: 60 / 87 / 22, x 4096: 117 / 122 / 42; 128 experts x 256: 19 / 86 / 22,
+    // x 1024: 62 / 87 / 23, x 4096: 230 / 134 / 82 (the split kernel re-reads the router for every 16 tokens: about 4 TB/s from L2)
+    if ((((uint64_t)T * E >= 49152ull && ctx->tune.router_variant == 0) || ctx->tune.router_variant == 3) && K % 256 == 0 && runit_aligned(w, 16) &&
+        runit_aligned(x, 16)) {
+        constexpr int smem = 8 * 2 * kRsWarpFloats * 4;
+        static bool configured[64] = {false};
+        if (ctx->device >= 0 && ctx->device < 64 && !configured[ctx->device]) {
+            RUNIT_CUDA_TRY(ctx, cudaFuncSetAttribute(router_f32_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            configured[ctx->device] = true;
+        }
+        runit_launch_chain_smem(ctx, router_f32_splitk_kernel, dim3((E + 63) / 64, (T + 15) / 16), dim3(256), smem, w, x, logits, E, K, T);
+        return runit_after_launch(ctx, "moe_router_f32_splitk");
+    }
     const bool big = (uint64_t)T * E >= 400000ull;
     if (ctx->tune.router_variant != 1 && (big || ctx->tune.router_variant == 2) && K % 32 == 0 && runit_aligned(w, 16) && runit_aligned(x, 16)) {
         const uint32_t ge = (E + 63) / 64;

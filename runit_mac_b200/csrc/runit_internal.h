@@ -30,7 +30,7 @@ struct runit_tuning {
     int32_t imma_fold = 0;           // batched 4-bit GEMV: 1 = activation pre-pass inside the GEMV launch where the grid allows (measured slower:
                                      // 950 against 1331 GB/s over the 7B set at batch 8), 0 = a launch of its own
     int32_t ep_fused_exchange = 0;   // expert-parallel decoder: 1 = exchange inside the GEMVs (no launches of its own; measured slower)
-    int32_t router_variant = 0;   // batched f32 router: 0 = by size, 1 = one warp per expert, 2 = tiled GEMM (experiments) // 1 = CTAs take items from a shared counter instead of the fixed split (experiments)
+    int32_t router_variant = 0;   // batched f32 router: 0 = by size, 1 = one warp per expert, 2 = tiled GEMM, 3 = GEMM with K split over the warps of a CTA (tests force each)
 };
 
 // Cached tensor map of one weight matrix view (encoding costs ~1 us on the host).
@@ -111,6 +111,22 @@ static inline void runit_launch_chain(runit_ctx* ctx, void (*kern)(KArgs...), di
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl != 0 ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // errors surface in runit_after_launch
+}
+
+// The same with dynamic shared memory.
+template <typename... KArgs, typename... Args>
+static inline void runit_launch_chain_smem(runit_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem_bytes, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

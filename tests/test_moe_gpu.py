@@ -80,6 +80,34 @@ def test_router_gemv_f32(ctx, oracle):
         assert_close(O, ref, got, rel_tol=1e-5, what="router")
 
 
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+def test_router_gemm_many_tokens(ctx, oracle, variant):
+    """The f32 router for prefill sizes: the kernel chosen by size (0), one warp per expert (1), the tiled GEMM (2) and the
+    GEMM with K split over the warps of a CTA (3), ragged token and expert counts included, against the same f64-exact
+    product; logits of one token do not depend on how many tokens ride along."""
+    import runit_mac_b200 as R
+    O = oracle
+    rng = np.random.default_rng(30 + variant)
+    ctx.set_tuning("router_variant", variant)
+    try:
+        for E, h, T in ((64, 2048, 300), (128, 2048, 131), (60, 1024, 129), (64, 512, 16)):
+            w = rng.normal(0, 0.02, (E, h)).astype(np.float32)
+            x = rng.normal(0, 1, (T, h)).astype(np.float32)
+            wb, lg = ctx.buffer_from(w), ctx.new_buffer(T * E * 4)
+            R.moe_router_f32(ctx, wb, ctx.buffer_from(x), lg, E, h, T)
+            ctx.flush()
+            got = lg.download(np.float32, T * E).reshape(T, E)
+            ref = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32)
+            assert_close(O, ref, got, rel_tol=1e-5, what="router, variant %d" % variant)
+            if variant == 3 and T >= 117:
+                lg2 = ctx.new_buffer(17 * E * 4)
+                R.moe_router_f32(ctx, wb, ctx.buffer_from(x[100:117]), lg2, E, h, 17)
+                ctx.flush()
+                assert np.array_equal(lg2.download(np.float32, 17 * E).reshape(17, E), got[100:117])
+    finally:
+        ctx.set_tuning("router_variant", 0)
+
+
 def test_moe_golden_fixture(ctx, oracle):
     import runit_mac_b200 as R
     G = np.load(GOLD)
