@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ x, co
 
 // ───────────────────────── causal attention over the f16 cache, tensor cores ─────────────────────────
 // softmax(q.K^T / sqrt(hd)) . V with the causal mask key <= start_pos + query (attention.metal:36-158), online softmax.
-//   grid (ceil(T / 64), heads), 4 warps; a warp owns 16 queries, the CTA walks the keys in blocks of 64.
+//   grid (heads, ceil(T / 64)), 4 warps; a warp owns 16 queries, the CTA walks the keys in blocks of 64.
 //   q (f32) is rounded to f16 and kept as MMA A fragments; K and V blocks are staged in shared memory by cp.async, two
 //   stages deep (rows padded to HD + 8 halves: ldmatrix reads without bank conflicts); S = q.K^T and O += P.V are mma.sync m16n8k16 (f16 operands,
 //   f32 accumulators); P is rounded to f16 for the second product, the usual flash-attention arrangement.
@@ -141,8 +141,9 @@ __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __res
     __half* const Ks = reinterpret_cast<__half*>(attn_smem);                    // [2][64 * LDS]
     __half* const Vs = Ks + 2 * 64 * LDS;                                      // [2][64 * LDS]
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t head = blockIdx.y, kvh = head / (heads / kv_heads);
-    const uint32_t q0 = blockIdx.x * 64, ld = heads * HD;
+    const uint32_t head = blockIdx.x, kvh = head / (heads / kv_heads);
+    // the last query blocks see the most keys: they are scheduled first (longest first), so that the short ones fill the tail
+    const uint32_t q0 = (gridDim.y - 1 - blockIdx.y) * 64, ld = heads * HD;
     const uint32_t row_a = q0 + warp * 16 + g, row_b = row_a + 8;     // this thread's two query rows
     const __half* kbase = kc + (size_t)kvh * max_seq * HD;
     const __half* vbase = vc + (size_t)kvh * max_seq * HD;
@@ -301,7 +302,7 @@ int32_t prefill_attention(runit_ctx* ctx, const float* q, const void* kcache, co
     RUNIT_REQUIRE(ctx, hd == 128 || hd == 64, "prefill_attention: head_dim %u unsupported (64 or 128)", hd);
     RUNIT_REQUIRE(ctx, T > 0 && heads % kv_heads == 0 && (uint64_t)start_pos + T <= max_seq, "prefill_attention: bad shape");
     const float scale = 1.0f / sqrtf((float)hd);
-    const dim3 grid((T + 63) / 64, heads);
+    const dim3 grid(heads, (T + 63) / 64);      // heads fastest: the launch order walks the query blocks from the last (most keys) to the first
     const size_t smem = (size_t)4 * 64 * (hd + 8) * 2;      // two stages of a K and a V block
     static bool configured[64] = {false};
     if (ctx->device >= 0 && ctx->device < 64 && !configured[ctx->device]) {
