@@ -1089,7 +1089,10 @@ def main():
                          "traffic": NCU_TRAFFIC_RATIO * bytes_fmt[0] / q4k_launches,
                          "traffic_note": "ncu capture of the 152064x3584 Q4_K launch (profiles/gemv_q4k_lm_head_152064x3584_ncu.md): dram read "
                                          "306.80 MB + write 4.71 MB for 307.18 MB algorithmic = x1.0141; scaled to the average launch of "
-                                         "the pass (weights are streamed once by every launch, so traffic grows with the bytes)",
+                                         "the pass (weights are streamed once by every launch, so traffic grows with the bytes); the "
+                                         "launches that dominate the pass were captured as well "
+                                         "(profiles/gemv_q4k_ffn_shapes_traffic_b200.md): 18944x3584 38.24 MB and 3584x18944 38.30 MB of "
+                                         "DRAM traffic for 38.28 MB algorithmic = x1.00",
                          "bytes_per_launch": bytes_fmt[0] / q4k_launches, "launches_per_token": q4k_launches,
                          "avg_launch_us": q4k_ms * 1e3 / q4k_launches},
             "per_format": {"q4k_gbs": achieved, "q4_0_gbs": bytes_fmt[1] / (fmt_ms[1] / (args.steps * TPS) * 1e-3) / 1e9},
