@@ -474,3 +474,34 @@ def test_prefill_restatement_agrees_with_the_decode_oracle():
         p = np.exp(s - s.max(axis=1, keepdims=True))
         ref = (p / p.sum(axis=1, keepdims=True)) @ V
         assert np.abs(got[:, h * hd:(h + 1) * hd] - ref).max() < 5e-3
+
+
+def test_decoders_against_the_upstream_definition_of_the_block_formats(oracle):
+    """tests/golden/ggml_dequant.npz holds seeded blocks and what the `gguf` Python package (upstream's own numpy
+    dequantisation) makes of them.  Q8_0 and Q5_0: the reference decodes like upstream, so the oracle must give the same bits.
+    Q4_0 and Q4_K: the reference orders things differently (element 2i / 2i+1 from the two nibbles of byte i; scale slots j
+    and j + 4 for the two nibble halves of chunk j, where upstream uses 2j and 2j + 1) - after exactly that re-ordering the
+    bits agree as well, which pins the f16 fields, the 6-bit unpacking, the nibble extraction and the arithmetic order of
+    the oracle to an implementation written by someone else."""
+    O = oracle
+    G = np.load(Path(__file__).parent / "golden" / "ggml_dequant.npz")
+    for name, fmt in (("q8_0", 0), ("q5_0", 3)):
+        raw, ref = G[name + "_raw"], G[name + "_ggml"]
+        assert np.array_equal(O.dequant_rows(fmt, raw, raw.shape[0], ref.shape[1]), ref), name
+    raw, ref = G["q4_0_raw"], G["q4_0_ggml"]
+    m = raw.shape[0]
+    mine = O.dequant_rows(1, raw, m, ref.shape[1]).reshape(m, -1, 32)
+    up = ref.reshape(m, -1, 32)
+    assert np.array_equal(mine[..., 0::2], up[..., :16]) and np.array_equal(mine[..., 1::2], up[..., 16:])
+    # Q4_K: move upstream's slots (2j, 2j+1) into the reference's (j, j+4), decode with the oracle, compare with upstream
+    raw, ref = G["q4k_raw"].copy(), G["q4k_ggml"]
+    blk = raw.reshape(m, -1, 144)
+    s = blk[..., 4:16].astype(np.uint8)
+    sc = np.empty(s.shape[:-1] + (8,), np.uint8)
+    mn = np.empty_like(sc)
+    sc[..., :4], mn[..., :4] = s[..., 0:4] & 63, s[..., 4:8] & 63                                  # get_scale_min_k4, j < 4
+    sc[..., 4:] = (s[..., 8:12] & 15) | ((s[..., 0:4] >> 6) << 4)
+    mn[..., 4:] = (s[..., 8:12] >> 4) | ((s[..., 4:8] >> 6) << 4)
+    perm = [0, 2, 4, 6, 1, 3, 5, 7]                  # reference slot j <- upstream slot 2j, slot j + 4 <- 2j + 1
+    blk[..., 4:16] = O.pack_q4k_scales(sc[..., perm], mn[..., perm])
+    assert np.array_equal(O.dequant_rows(2, blk.reshape(m, -1), m, ref.shape[1]), ref)
