@@ -5,15 +5,16 @@
 // mma.sync.m16n8k32 (8-bit integer operands, one MMA = 16 rows x 8 activation rows x 32 K = exactly one Q4_0 block or
 // one Q4_K sub-block), so the per-block scale is applied to an int32 tile in registers and nothing else has to be
 // dequantised:
-//   * a pre-pass quantises the activations once per call: per 32-block and activation row a scale s = max|x| / 16383
-//     and 15-bit integers q = rint(x / s), stored as a signed high byte and an unsigned low byte in the order the
-//     MMA's B fragments want them, plus s and s * sum(q) per block (for the "- min" / "- 8" terms).  Relative error of
-//     an activation <= 2^-15 of its block maximum, far inside the 1e-3 bar; products and block sums are exact integers.
-//     (Q4_0.  Q4_K: one scale per 256-unit and activation row, s = max|x| / 32767, so that the 6-bit block scales stay
-//     integer factors: see prepare_row<Q4_K>.)
+//   * a pre-pass quantises the activations once per call: per 256-element unit and activation row a scale
+//     s = max|x| / 32767 and 16-bit integers q = rint(x / s), stored as a signed high byte and an unsigned low byte in the
+//     order the MMA's B fragments want them, plus the integer block sums of q (for the "- min" / "- 8" terms).  Error of an
+//     activation <= 2^-16 of its unit's maximum, far inside the 1e-3 bar; products and block sums are exact integers.
+//     With one scale per unit Q4_K's 6-bit block scales stay integer factors (prepare_row<Q4_K>), and Q4_0's "- 8" is an
+//     integer multiply-add.
 //   * the weight nibbles are the MMA's A operand after one mask (low nibbles) or shift+mask (high nibbles; Q4_K feeds
 //     the high nibbles unshifted, as 16 * nibble, and gives the low-nibble tiles 16 * scale instead).
-//   * Q4_0, per k32 tile: 2 MMAs (high and low activation byte), v = 256 * hi + lo, acc += (scale_w * s) * v - (min_w * s*sum q).
+//   * Q4_0, per k32 tile: 2 MMAs (high and low activation byte), v = 256 * hi + lo - 8 * sum(q), unit sum += d_w * v; per
+//     unit acc += s * unit sum.
 //   * Q4_K, per k32 tile: 2 MMAs and 8 integer multiply-adds (sc_j times the two limbs' tiles, summed over the unit's eight
 //     blocks in int32); per unit: three more MMAs give sum_j m_j * (block sum of the activation integers) exactly, then one
 //     conversion and acc += s * (d * V - dmin * M).  4.2 -> 2.8 thread instructions per weight.
@@ -41,32 +42,43 @@ __device__ __forceinline__ int k_slot(int e) {
     return 16 * (e & 1) + 4 * (e >> 3) + ((e & 7) >> 1);
 }
 
-// Activation row n of unit u by one warp (rows >= batch are written as zeros).
+// Activation row n of unit u by one warp (rows >= batch are written as zeros).  ONE scale per unit and activation row:
+// s = max|x| over the 256 elements / 32767, q = rint(x / s) as a signed high byte and an unsigned low byte in the order
+// the MMA's B fragments want them.  Q4_0 (this template): behind the limbs
+//   [4096, 4128)   s of the 8 activation rows (f32)
+//   [4128, 4384)   block sums of q as int32, [block][activation row] (for the "- 8" of the weights: exact integers)
 template <int FMT>
 __device__ __forceinline__ void prepare_row(const float* __restrict__ x, uint8_t* __restrict__ dst, uint32_t k, uint32_t batch, uint32_t u,
                                             uint32_t n, uint32_t lane) {
-    for (int bt = 0; bt < 8; bt++) {
-        const float v = n < batch ? x[(size_t)n * k + (size_t)u * 256 + bt * 32 + lane] : 0.f;
-        float amax = fabsf(v);
+    float v[8];
+    float amax = 0.f;
+    bool bad = false;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        // an Inf or a NaN in the block (fmaxf would drop the NaN) gives a NaN scale: every row's result of that activation
-        // row becomes NaN, as a non-finite activation does (to +-Inf or NaN) in the reference's f32 multiply-add chain
-        const bool bad = __any_sync(0xffffffffu, !(fabsf(v) <= 3.0e38f));
-        const float s = bad ? __uint_as_float(0x7FC00000u) : amax * (1.0f / 16383.0f);
-        const int q = (amax > 0.f && !bad) ? __float2int_rn(v * (16383.0f / amax)) : 0;
+    for (int bt = 0; bt < 8; bt++) {
+        v[bt] = n < batch ? x[(size_t)n * k + (size_t)u * 256 + bt * 32 + lane] : 0.f;
+        amax = fmaxf(amax, fabsf(v[bt]));
+        bad |= !(fabsf(v[bt]) <= 3.0e38f);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // an Inf or a NaN in the unit gives a NaN scale: every row's result of that activation row becomes NaN, as a
+    // non-finite activation does (to +-Inf or NaN) in the reference's f32 multiply-add chain
+    bad = __any_sync(0xffffffffu, bad);
+    const float s = bad ? __uint_as_float(0x7FC00000u) : amax * (1.0f / 32767.0f);
+    const float inv = (amax > 0.f && !bad) ? 32767.0f / amax : 0.f;
+    const int slot = k_slot<FMT>((int)lane);
+#pragma unroll
+    for (int bt = 0; bt < 8; bt++) {
+        const int q = __float2int_rn(v[bt] * inv);
         int qs = q;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);
-        const int slot = k_slot<FMT>((int)lane);
         uint8_t* p = dst + ((bt * 8 + n) * 4 + ((slot & 15) >> 2)) * 16 + (slot >> 4) * 4 + (slot & 3);
         p[0] = (uint8_t)(q >> 8);      // signed high byte
         p[8] = (uint8_t)(q & 255);     // unsigned low byte
-        if (lane == 0) {
-            reinterpret_cast<float*>(dst + 4096)[bt * 8 + n] = s;
-            reinterpret_cast<float*>(dst + 4096 + 256)[bt * 8 + n] = s * (float)qs;
-        }
+        if (lane == 0) reinterpret_cast<int*>(dst + 4128)[bt * 8 + n] = qs;
     }
+    if (lane == 0) reinterpret_cast<float*>(dst + 4096)[n] = s;
 }
 
 // Q4_K: ONE scale per unit and activation row (s = max|x| over the 256 elements / 32767, q = rint(x / s) as a signed high
@@ -158,26 +170,6 @@ __device__ __forceinline__ void mma_u8u8(int (&c)[4], const uint32_t (&a)[4], ui
 // around the MMAs (instruction-level parallelism inside a warp), while the "memory" clobber of the barrier wait keeps
 // them behind the wait.
 __device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
-
-// One k32 tile: A = nibbles of rows (g, g+8), B = the activation block; adds the scaled tile into acc.
-// sw0/sw1, mw0/mw1: weight scale and min of rows g / g+8 for this block; xs/xm: activation scale and block sum of
-// columns 2t, 2t+1 (packed float2 loads).
-__device__ __forceinline__ void tile_mma(float (&acc)[4], const uint32_t (&a)[4], const uint8_t* xaddr, const uint8_t* saddr, float sw0,
-                                         float mw0, float sw1, float mw1) {
-    const uint4 bf = *reinterpret_cast<const uint4*>(xaddr);
-    const uint32_t bh0 = bf.x, bh1 = bf.y, bl0 = bf.z, bl1 = bf.w;
-    const float2 xs = *reinterpret_cast<const float2*>(saddr), xm = *reinterpret_cast<const float2*>(saddr + 256);
-    const float xs0 = xs.x, xs1 = xs.y, xm0 = xm.x, xm1 = xm.y;
-    int ch[4], cl[4];
-    mma_u8s8(ch, a, bh0, bh1);
-    mma_u8u8(cl, a, bl0, bl1);
-    const float v0 = (float)(ch[0] * 256 + cl[0]), v1 = (float)(ch[1] * 256 + cl[1]);
-    const float v2 = (float)(ch[2] * 256 + cl[2]), v3 = (float)(ch[3] * 256 + cl[3]);
-    acc[0] = fmaf(v0, sw0 * xs0, fmaf(-mw0, xm0, acc[0]));
-    acc[1] = fmaf(v1, sw0 * xs1, fmaf(-mw0, xm1, acc[1]));
-    acc[2] = fmaf(v2, sw1 * xs0, fmaf(-mw1, xm0, acc[2]));
-    acc[3] = fmaf(v3, sw1 * xs1, fmaf(-mw1, xm1, acc[3]));
-}
 
 // One k32 tile of the Q4_K path: the two limbs' int32 tiles times the rows' integer block scales, into the unit's sums.
 __device__ __forceinline__ void tile_mma_int(int (&ih)[4], int (&il)[4], const uint32_t (&a)[4], const uint8_t* xaddr, int sc0, int sc1) {
@@ -289,7 +281,6 @@ __global__ void __launch_bounds__(160) gemv_imma_kernel(const __grid_constant__ 
         const uint8_t* sb = base_p + s * STAGE;
         const uint8_t* wb = sb + kUnitBytes + warp * WBYTES;
         const uint8_t* xb = sb + (g * 4 + t) * 16;       // + bt * 512: limbs of block bt for column g, K quarter t
-        const uint8_t* scb = sb + 4096 + (2 * t) * 4;    // + bt * 32: scales of columns 2t, 2t+1
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
             const uint8_t* r0 = wb + (mt * 16 + g) * 144;
@@ -331,6 +322,7 @@ __global__ void __launch_bounds__(160) gemv_imma_kernel(const __grid_constant__ 
                     acc[mt][e] = fmaf((e & 1) ? xs.y : xs.x, fmaf(dd, vq, -nn * vm), acc[mt][e]);
                 }
             } else {
+                float au[4] = {0.f, 0.f, 0.f, 0.f};      // the unit's sums, before the activation scale
 #pragma unroll
                 for (int b = 0; b < 8; b++) {
                     // block b of the unit sits at byte 18b of the row: f16 scale, then 16 bytes of nibbles; for even b the
@@ -351,8 +343,24 @@ __global__ void __launch_bounds__(160) gemv_imma_kernel(const __grid_constant__ 
                     }
                     const uint32_t aa[4] = {w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
                     const float d0 = half_bits_to_float(sc0), d1 = half_bits_to_float(sc1);
-                    tile_mma(acc[mt], aa, xb + b * 512, scb + b * 32, d0, 8.0f * d0, d1, 8.0f * d1);
+                    const uint4 bf = *reinterpret_cast<const uint4*>(xb + b * 512);
+                    const int2 sq = *reinterpret_cast<const int2*>(sb + 4128 + b * 32 + 8 * t);   // block sums of columns 2t, 2t+1
+                    int ch[4], cl[4];
+                    mma_u8s8(ch, aa, bf.x, bf.y);
+                    mma_u8u8(cl, aa, bf.z, bf.w);
+                    // sum (nibble - 8) * q over the block, exact: |.| <= 32 * 15 * 32767 + 8 * 32 * 32767 < 2^25
+                    const int v0 = ch[0] * 256 + cl[0] - 8 * sq.x, v1 = ch[1] * 256 + cl[1] - 8 * sq.y;
+                    const int v2 = ch[2] * 256 + cl[2] - 8 * sq.x, v3 = ch[3] * 256 + cl[3] - 8 * sq.y;
+                    au[0] = fmaf((float)v0, d0, au[0]);
+                    au[1] = fmaf((float)v1, d0, au[1]);
+                    au[2] = fmaf((float)v2, d1, au[2]);
+                    au[3] = fmaf((float)v3, d1, au[3]);
                 }
+                const float2 xs = *reinterpret_cast<const float2*>(sb + 4096 + 8 * t);
+                acc[mt][0] = fmaf(xs.x, au[0], acc[mt][0]);
+                acc[mt][1] = fmaf(xs.y, au[1], acc[mt][1]);
+                acc[mt][2] = fmaf(xs.x, au[2], acc[mt][2]);
+                acc[mt][3] = fmaf(xs.y, au[3], acc[mt][3]);
             }
         }
         __syncwarp();
