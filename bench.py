@@ -397,6 +397,66 @@ def run_block(R, ctx, torch, stream, T=4096, reps=20, E=128, h=2048, ff=768, k=8
             "finite": bool(torch.isfinite(out).all().item())}
 
 
+def run_q8_0_pass(R, ctx, torch, stream, layers=24, reps=20):
+    """BASELINE configs[0] as a throughput figure: all GEMVs of one Qwen2.5-0.5B-shaped decode token in Q8_0 (hidden 896;
+    fused q | k | v 896 -> 1152 with f32 bias; o 896 -> 896 + residual; fused gate / up 896 -> 4864 + SiLU; down 4864 -> 896 +
+    residual; 24 layers; lm_head 896 -> 151936), batch 1, f32 activations, every layer a distinct weight instance (0.53 GB per
+    token), recorded once and replayed between CUDA events."""
+    H, QD, KV, FF, V = 896, 896, 128, 4864, 151936
+    rb = lambda k: k // 32 * 34
+    f4 = lambda n: ctx.new_buffer(4 * n)
+    ws = []
+    for l in range(layers):
+        d = {}
+        for i, (name, m, k) in enumerate((("q", QD, H), ("k", KV, H), ("v", KV, H), ("o", H, QD), ("gate", FF, H), ("up", FF, H), ("down", H, FF))):
+            d[name] = ctx.new_buffer(m * rb(k))
+            R.fill_weights(ctx, FMT_Q8_0, d[name], m * (k // 32), 9000 + l * 16 + i, 0.02)
+        ws.append(d)
+    lm = ctx.new_buffer(V * rb(H))
+    R.fill_weights(ctx, FMT_Q8_0, lm, V * (H // 32), 9999, 0.02)
+    x, xn, q, kk, v, act, logits = f4(H), f4(H), f4(QD), f4(KV), f4(KV), f4(FF), f4(V)
+    bq, bk, bv = f4(QD), f4(KV), f4(KV)
+    for b_, n, sd in ((xn, H, 1), (q, QD, 2), (act, FF, 3), (bq, QD, 4), (bk, KV, 5), (bv, KV, 6)):
+        R.fill_normal_f32(ctx, b_, n, 70 + sd, 1.0)
+    ctx.call("memset", x, 0, 4 * H)
+
+    def run():
+        for w in ws:
+            R.fused_qkv_f32bias_q8_0_f32(ctx, w["q"], w["k"], w["v"], xn, q, kk, v, bq, bk, bv, QD, KV, H)
+            R.gemv_q8_0_add_f32_f32in(ctx, w["o"], q, x, x, H, QD)
+            R.fused_ffn_q8_0_f32(ctx, w["gate"], w["up"], xn, act, FF, H)
+            R.gemv_q8_0_add_f32_f32in(ctx, w["down"], act, x, x, H, FF)
+        R.gemv_q8_0_f32in_f32out(ctx, lm, xn, logits, V, H)
+    l0 = ctx.launches
+    run()
+    ctx.flush()
+    launches = ctx.launches - l0
+    ctx.graph_begin(); run(); g = ctx.graph_end()
+    for _ in range(3):
+        g.launch()
+    ctx.flush()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        g.launch()
+    e1.record(stream)
+    ctx.flush()
+    us = e0.elapsed_time(e1) / reps * 1e3
+    g.destroy()
+    wbytes = layers * ((QD + 2 * KV) * rb(H) + H * rb(QD) + 2 * FF * rb(H) + H * rb(FF)) + V * rb(H)
+    act_bytes = layers * (4 * H + 8 * (QD + 2 * KV) + 4 * QD + 8 * H + 4 * H + 4 * FF + 4 * FF + 8 * H) + 4 * H + 4 * V
+    peak, kind = measured_peak()
+    gbs = (wbytes + act_bytes) / us / 1e3
+    for w in ws:
+        for b_ in w.values():
+            b_.free()
+    lm.free()
+    return {"workload": "qwen2.5-0.5b decode GEMV set (24 layers + lm_head), Q8_0, batch 1, f32 activations, f32 q|k|v bias",
+            "us_per_token": us, "gbs": gbs, "frac_of_peak": gbs / peak, "peak_kind": kind, "launches_per_token": int(launches),
+            "algorithmic_bytes_per_token": int(wbytes + act_bytes),
+            "note": "97 launches of 1-10 MB each are bound by launch and pipeline-fill latency; the 145 MB lm_head alone runs at 0.63"}
+
+
 def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False, stop=lambda: False):
     """Figures for the other rows of the path: one OLMoE-shaped MoE layer (1/16/256 tokens), the full
     OLMoE-shaped greedy decode (tok/s) and, at N>1, the row-sharded lm_head with its all-gather."""
@@ -517,6 +577,8 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
     model.close()
     if rank == 0:
         out["gguf_load"] = run_gguf_load(ctx)
+        if not decode_only:
+            out["q8_0_qwen0_5b_gemv_pass"] = run_q8_0_pass(R, ctx, torch, stream)
     def go_on():
         # the ranks decide together whether the next sharded measurement starts (it holds collectives)
         t = torch.tensor([1 if stop() else 0], device="cuda")
