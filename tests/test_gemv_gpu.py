@@ -252,7 +252,7 @@ def test_fused_ffn(ctx, oracle, fmt, ff, k):
 
 
 @pytest.mark.parametrize("fmt,m,k,batch", [(1, 37900, 512, 8), (2, 37900, 512, 7), (1, 200, 18944, 5), (2, 200, 18944, 8),
-                                           (2, 18944, 3584, 8)])
+                                           (2, 18944, 3584, 8), (1, 18944, 3584, 8), (2, 37900, 3584, 8)])
 def test_batched_gemv_tensor_core_path_shapes(ctx, oracle, fmt, m, k, batch):
     """The integer tensor-core path of the 4-bit formats: 32 rows per warp (many tiles), K split over clusters of 8
     (few tiles, long K), ragged last tile, and the FFN shape of the benchmark configuration."""
@@ -274,6 +274,36 @@ def test_batched_gemv_tensor_core_path_shapes(ctx, oracle, fmt, m, k, batch):
     R.gemv_batched_f32(ctx, fmt, ctx.buffer_from(w), ctx.buffer_from(x), yb, ctx.buffer_from(res), m, k, batch)
     ctx.flush()
     assert np.array_equal(got, yb.download(np.float32, batch * m).reshape(batch, m))
+
+
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_batched_gemv_launch_shapes(ctx, oracle, fmt):
+    """Every launch shape of the integer tensor-core path that the size rules can pick (rows per warp 16 / 32, cluster size
+    1 / 2 / 4 / 8 over K, ring depth 2 / 3 / 6), forced on one ragged matrix: the same results to the bar, and the same bits
+    whenever the reduction order is the same (same cluster size)."""
+    import runit_mac_b200 as R
+    O = oracle
+    m, k, batch = 1000, 3584, 8
+    rng = np.random.default_rng(77 + fmt)
+    w = O.rand_weights(fmt, rng, m, k)
+    x = rng.normal(0, 1, (batch, k)).astype(np.float32)
+    ref = O.gemv(fmt, w, x, m, k, O.TIER_F64)
+    wb, xb, yb = ctx.buffer_from(w), ctx.buffer_from(x), ctx.new_buffer(batch * m * 4)
+    first = {}
+    try:
+        for rw in (16, 32):
+            for cs in (1, 2, 4, 8):
+                for stages in (2, 3, 6):
+                    for key, val in (("imma_rw", rw), ("imma_csplit", cs), ("imma_stages", stages)):
+                        ctx.set_tuning(key, val)
+                    R.gemv_batched_f32(ctx, fmt, wb, xb, yb, None, m, k, batch)
+                    ctx.flush()
+                    got = yb.download(np.float32, batch * m)
+                    assert_close(O, ref, got, what="batched, %d rows per warp, cluster of %d, %d stages" % (rw, cs, stages))
+                    assert np.array_equal(first.setdefault(cs, got), got), (rw, cs, stages)
+    finally:
+        for key in ("imma_rw", "imma_csplit", "imma_stages"):
+            ctx.set_tuning(key, 0)
 
 
 @pytest.mark.parametrize("fmt", [0, 1, 2])
