@@ -53,7 +53,8 @@ struct runit_model {
     unsigned long long* rng = nullptr;
     // batched prefill (allocated on first use, for prompts up to max_seq)
     struct {
-        float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *proj = nullptr, *xn2 = nullptr;
+        float *x = nullptr, *q = nullptr, *qkv = nullptr, *proj = nullptr, *xn2 = nullptr;
+        uint8_t* wqkv = nullptr;            // per layer the rows of wq, wk, wv in one matrix: the three projections are one GEMM
         void *xn_bf16 = nullptr, *ao_bf16 = nullptr, *moe_scratch = nullptr;
         int32_t *tokens = nullptr, *tables = nullptr;
         size_t moe_bytes = 0;
@@ -403,7 +404,8 @@ int32_t runit_model_prefill(runit_model_t* m, const int32_t* tokens, uint32_t n,
         m->pf.moe_bytes = runit_moe_grouped_scratch_bytes(cap, h, c.ff, c.n_experts, c.top_k);
         auto A = [&](void** p, size_t b) { if (st == RUNIT_OK) st = dev_alloc(m, p, b); };
         A((void**)&m->pf.x, (size_t)cap * h * 4); A((void**)&m->pf.q, (size_t)cap * q_dim * 4);
-        A((void**)&m->pf.k, (size_t)cap * kv_dim * 4); A((void**)&m->pf.v, (size_t)cap * kv_dim * 4);
+        A((void**)&m->pf.qkv, (size_t)cap * (q_dim + 2 * kv_dim) * 4);
+        A((void**)&m->pf.wqkv, (size_t)c.n_layers * (q_dim + 2 * kv_dim) * runit_row_bytes(RUNIT_FMT_Q4K, h));
         A((void**)&m->pf.proj, (size_t)cap * h * 4); A((void**)&m->pf.xn2, (size_t)cap * h * 4);
         A(&m->pf.xn_bf16, (size_t)m->pf.rows_alloc * h * 2); A(&m->pf.ao_bf16, (size_t)m->pf.rows_alloc * q_dim * 2);
         A(&m->pf.moe_scratch, m->pf.moe_bytes);
@@ -412,6 +414,15 @@ int32_t runit_model_prefill(runit_model_t* m, const int32_t* tokens, uint32_t n,
         // rows past the prompt are read by the GEMMs' tile loads (never stored): keep them finite
         cudaMemsetAsync(m->pf.xn_bf16, 0, (size_t)m->pf.rows_alloc * h * 2, ctx->stream);
         cudaMemsetAsync(m->pf.ao_bf16, 0, (size_t)m->pf.rows_alloc * q_dim * 2, ctx->stream);
+        // q | k | v of a layer as one matrix (a copy of 0.56 bytes per weight of the three projections): 192 tiles of one
+        // GEMM launch keep the CTA pairs busy where three launches of 64 tiles each ran one tile per pair
+        const size_t rbh = runit_row_bytes(RUNIT_FMT_Q4K, h), qb = (size_t)q_dim * rbh, kb = (size_t)kv_dim * rbh;
+        for (int l = 0; l < c.n_layers; l++) {
+            uint8_t* dst = m->pf.wqkv + (size_t)l * (qb + 2 * kb);
+            cudaMemcpyAsync(dst, (const uint8_t*)m->w.wq + (size_t)l * qb, qb, cudaMemcpyDeviceToDevice, ctx->stream);
+            cudaMemcpyAsync(dst + qb, (const uint8_t*)m->w.wk + (size_t)l * kb, kb, cudaMemcpyDeviceToDevice, ctx->stream);
+            cudaMemcpyAsync(dst + qb + kb, (const uint8_t*)m->w.wv + (size_t)l * kb, kb, cudaMemcpyDeviceToDevice, ctx->stream);
+        }
     }
     RUNIT_CUDA_TRY(ctx, cudaMemcpyAsync(m->pf.tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
     if ((st = dense_tiles_prepare(ctx, m->pf.tables, n))) return st;
@@ -419,18 +430,17 @@ int32_t runit_model_prefill(runit_model_t* m, const int32_t* tokens, uint32_t n,
     const size_t rb_h = runit_row_bytes(RUNIT_FMT_Q4K, h), rb_q = runit_row_bytes(RUNIT_FMT_Q4K, q_dim), rb_ff = runit_row_bytes(RUNIT_FMT_Q4K, c.ff);
     const size_t kv_layer = (size_t)c.n_kv_heads * c.max_seq * hd;
     for (int l = 0; l < c.n_layers; l++) {
-        const uint8_t* wq = (const uint8_t*)m->w.wq + (size_t)l * q_dim * rb_h;
-        const uint8_t* wk = (const uint8_t*)m->w.wk + (size_t)l * kv_dim * rb_h;
-        const uint8_t* wv = (const uint8_t*)m->w.wv + (size_t)l * kv_dim * rb_h;
+        const uint32_t qkv_dim = q_dim + 2 * kv_dim;
+        const uint8_t* wqkv = m->pf.wqkv + (size_t)l * qkv_dim * rb_h;
         const uint8_t* wo = (const uint8_t*)m->w.wo + (size_t)l * h * rb_q;
         // attention block (prefill.rs:84-150)
         if ((st = prefill_norm_bf16(ctx, m->pf.x, (const float*)m->w.attn_norm + (size_t)l * h, m->pf.xn_bf16, c.eps, n, h))) return st;
-        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_q", wq, nullptr, q_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.q, q_dim, n, m->pf.tables))) return st;
-        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_k", wk, nullptr, kv_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.k, kv_dim, n, m->pf.tables))) return st;
-        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_v", wv, nullptr, kv_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.v, kv_dim, n, m->pf.tables))) return st;
+        if ((st = dense_gemm_q4k_bf16(ctx, "prefill_qkv", wqkv, nullptr, qkv_dim, h, m->pf.xn_bf16, m->pf.rows_alloc, m->pf.qkv, qkv_dim, n, m->pf.tables))) return st;
         __half* kcl = m->kc + (size_t)l * kv_layer;
         __half* vcl = m->vc + (size_t)l * kv_layer;
-        if ((st = prefill_rope_cache(ctx, m->pf.q, m->pf.k, m->pf.v, kcl, vcl, hd, c.n_heads, c.n_kv_heads, 0, c.theta, c.max_seq, n))) return st;
+        if ((st = prefill_rope_cache(ctx, m->pf.qkv, m->pf.q, m->pf.qkv + q_dim, m->pf.qkv + q_dim + kv_dim, kcl, vcl, hd, c.n_heads, c.n_kv_heads, 0,
+                                     c.theta, c.max_seq, n, qkv_dim)))
+            return st;
         if ((st = prefill_attention(ctx, m->pf.q, kcl, vcl, m->pf.ao_bf16, n, c.n_heads, c.n_kv_heads, hd, c.max_seq, 0))) return st;
         if ((st = dense_gemm_q4k_bf16(ctx, "prefill_o", wo, nullptr, h, q_dim, m->pf.ao_bf16, m->pf.rows_alloc, m->pf.proj, h, n, m->pf.tables))) return st;
         if ((st = prefill_add_rows(ctx, m->pf.x, m->pf.proj, (size_t)n * h))) return st;

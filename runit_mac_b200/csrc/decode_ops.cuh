@@ -40,8 +40,10 @@ int32_t gemv_plain(runit_ctx* ctx, const char* name, int fmt, const void* w, con
 // prefill.cu: launchers of the batched prefill's own kernels
 int32_t prefill_embed(runit_ctx* ctx, const float* emb, const int32_t* tokens, float* x, uint32_t T, uint32_t h);
 int32_t prefill_norm_bf16(runit_ctx* ctx, const float* x, const float* gamma, void* y_bf16, float eps, uint32_t T, uint32_t h);
-int32_t prefill_rope_cache(runit_ctx* ctx, float* q, const float* k, const float* v, void* kcache, void* vcache, uint32_t hd, uint32_t heads,
-                           uint32_t kv_heads, uint32_t start_pos, float theta, uint32_t max_seq, uint32_t T);
+// q_in / k / v have rows of `ld` floats (0: as wide as their own heads); q_out [T][heads * hd] receives the rotated queries
+int32_t prefill_rope_cache(runit_ctx* ctx, const float* q_in, float* q_out, const float* k, const float* v, void* kcache, void* vcache,
+                           uint32_t hd, uint32_t heads, uint32_t kv_heads, uint32_t start_pos, float theta, uint32_t max_seq, uint32_t T,
+                           uint32_t ld);
 int32_t prefill_attention(runit_ctx* ctx, const float* q, const void* kcache, const void* vcache, void* out_bf16, uint32_t T, uint32_t heads,
                           uint32_t kv_heads, uint32_t hd, uint32_t max_seq, uint32_t start_pos);
 int32_t prefill_add_rows(runit_ctx* ctx, float* x, const float* y, size_t n);

@@ -56,9 +56,11 @@ __global__ void __launch_bounds__(256) rms_norm_bf16_kernel(const float* __restr
 
 // Rotary embedding of q (in place) and k for every position, then k (rotated) and v into the f16 caches: the arithmetic
 // per element of rope_kv_kernel (fused_rope.metal:17-56, activation.metal:13-44).  grid (T, max(heads, kv_heads)).
-__global__ void rope_cache_rows_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+// q_in / k / v: rows of `ld` floats (one matrix [T][q | k | v] when the three projections were one GEMM, ld = its width;
+// or three matrices with ld = 0: rows as wide as their own heads); q_out: [T][heads * hd], may be q_in when ld = 0.
+__global__ void rope_cache_rows_kernel(const float* q_in, float* q_out, const float* __restrict__ k, const float* __restrict__ v,
                                        __half* __restrict__ kc, __half* __restrict__ vc, uint32_t hd, uint32_t heads, uint32_t kv_heads,
-                                       uint32_t start_pos, float theta, uint32_t max_seq) {
+                                       uint32_t start_pos, float theta, uint32_t max_seq, uint32_t ld) {
     const uint32_t t = blockIdx.x, hid = blockIdx.y, d = threadIdx.x, half = hd / 2;
     if (d >= half) return;
     const uint32_t pos = start_pos + t;
@@ -66,18 +68,19 @@ __global__ void rope_cache_rows_kernel(float* __restrict__ q, const float* __res
     const float angle = (float)pos * freq;
     const float c = cosf(angle), s = sinf(angle);
     if (hid < heads) {
-        float* p = q + ((size_t)t * heads + hid) * hd;
-        const float a = p[d], b = p[d + half];
+        const float* pi = q_in + (size_t)t * (ld ? ld : heads * hd) + (size_t)hid * hd;
+        float* p = q_out + ((size_t)t * heads + hid) * hd;
+        const float a = pi[d], b = pi[d + half];
         p[d] = a * c - b * s;
         p[d + half] = a * s + b * c;
     }
     if (hid < kv_heads && pos < max_seq) {
-        const float* p = k + ((size_t)t * kv_heads + hid) * hd;
+        const float* p = k + (size_t)t * (ld ? ld : kv_heads * hd) + (size_t)hid * hd;
         const float a = p[d], b = p[d + half];
         const size_t o = ((size_t)hid * max_seq + pos) * hd;
         kc[o + d] = __float2half_rn(a * c - b * s);
         kc[o + d + half] = __float2half_rn(a * s + b * c);
-        const float* vp = v + ((size_t)t * kv_heads + hid) * hd;
+        const float* vp = v + (size_t)t * (ld ? ld : kv_heads * hd) + (size_t)hid * hd;
         vc[o + d] = __float2half_rn(vp[d]);
         vc[o + d + half] = __float2half_rn(vp[d + half]);
     }
@@ -289,11 +292,12 @@ int32_t prefill_norm_bf16(runit_ctx* ctx, const float* x, const float* gamma, vo
     return runit_after_launch(ctx, "prefill_rms_norm_bf16");
 }
 
-int32_t prefill_rope_cache(runit_ctx* ctx, float* q, const float* k, const float* v, void* kcache, void* vcache, uint32_t hd, uint32_t heads,
-                           uint32_t kv_heads, uint32_t start_pos, float theta, uint32_t max_seq, uint32_t T) {
+int32_t prefill_rope_cache(runit_ctx* ctx, const float* q_in, float* q_out, const float* k, const float* v, void* kcache, void* vcache,
+                           uint32_t hd, uint32_t heads, uint32_t kv_heads, uint32_t start_pos, float theta, uint32_t max_seq, uint32_t T,
+                           uint32_t ld) {
     const uint32_t hmax = heads > kv_heads ? heads : kv_heads;
-    pf::rope_cache_rows_kernel<<<dim3(T, hmax), hd / 2, 0, ctx->stream>>>(q, k, v, (__half*)kcache, (__half*)vcache, hd, heads, kv_heads,
-                                                                           start_pos, theta, max_seq);
+    pf::rope_cache_rows_kernel<<<dim3(T, hmax), hd / 2, 0, ctx->stream>>>(q_in, q_out, k, v, (__half*)kcache, (__half*)vcache, hd, heads,
+                                                                           kv_heads, start_pos, theta, max_seq, ld);
     return runit_after_launch(ctx, "prefill_rope_cache");
 }
 
