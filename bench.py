@@ -574,6 +574,16 @@ def run_extras(R, ctx, torch, dist, stream, rank, world, args, decode_only=False
         dt = (time.perf_counter() - t0) / 3
         pf["T%d" % n_tok] = {"ms": dt * 1e3, "tokens_per_s": n_tok / dt}
     out["olmoe_decode_q4k"]["batched_prefill"] = pf
+    # the same request served the way an engine would: the prompt through the batched prefill, then 63 recorded decode steps
+    # from the cache it filled (bf16 GEMM operands in the prompt pass: the tokens are compared with the token-by-token run)
+    model.prefill(prompt)
+    t0 = time.perf_counter()
+    nxt = model.prefill(prompt)
+    cont = model.generate_greedy(np.array([nxt], np.int32), 63, start_pos=128)
+    dt_srv = time.perf_counter() - t0
+    out["olmoe_decode_q4k"]["prompt_by_batched_prefill"] = {
+        "ms_total": dt_srv * 1e3, "tokens_total_s": 192 / dt_srv,
+        "same_tokens_as_token_by_token": bool(np.array_equal(np.asarray(cont, np.int32), np.asarray(toks[128:192], np.int32)))}
     model.close()
     if rank == 0:
         out["gguf_load"] = run_gguf_load(ctx)
