@@ -443,9 +443,9 @@ int32_t runit_model_prefill(runit_model_t* m, const int32_t* tokens, uint32_t n,
             return st;
         if ((st = prefill_attention(ctx, m->pf.q, kcl, vcl, m->pf.ao_bf16, n, c.n_heads, c.n_kv_heads, hd, c.max_seq, 0))) return st;
         if ((st = dense_gemm_q4k_bf16(ctx, "prefill_o", wo, nullptr, h, q_dim, m->pf.ao_bf16, m->pf.rows_alloc, m->pf.proj, h, n, m->pf.tables))) return st;
-        if ((st = prefill_add_rows(ctx, m->pf.x, m->pf.proj, (size_t)n * h))) return st;
-        // mixture-of-experts block on all tokens at once (prefill.rs:153-215 runs it token by token)
-        if ((st = launch_rms_norm(ctx, m->pf.x, m->pf.xn2, (const float*)m->w.ffn_norm + (size_t)l * h, false, c.eps, h, n))) return st;
+        // residual add and the block's RMSNorm in one launch; then the mixture-of-experts block on all tokens at once
+        // (prefill.rs:153-215 runs it token by token)
+        if ((st = prefill_add_rms_norm(ctx, m->pf.x, m->pf.proj, (const float*)m->w.ffn_norm + (size_t)l * h, m->pf.xn2, c.eps, n, h))) return st;
         const size_t eg = (size_t)c.n_experts * c.ff * rb_h, ed = (size_t)c.n_experts * h * rb_ff;
         if ((st = runit_moe_layer_q4k_bf16(ctx, (const float*)m->w.router + (size_t)l * c.n_experts * h, (const uint8_t*)m->w.gate + (size_t)l * eg,
                                            (const uint8_t*)m->w.up + (size_t)l * eg, (const uint8_t*)m->w.down + (size_t)l * ed, m->pf.xn2, m->pf.x,

@@ -47,6 +47,8 @@ int32_t prefill_rope_cache(runit_ctx* ctx, const float* q_in, float* q_out, cons
 int32_t prefill_attention(runit_ctx* ctx, const float* q, const void* kcache, const void* vcache, void* out_bf16, uint32_t T, uint32_t heads,
                           uint32_t kv_heads, uint32_t hd, uint32_t max_seq, uint32_t start_pos);
 int32_t prefill_add_rows(runit_ctx* ctx, float* x, const float* y, size_t n);
+// x += y, then out = RMSNorm(x) * gamma, T rows of h (one launch; the bits of prefill_add_rows + launch_rms_norm)
+int32_t prefill_add_rms_norm(runit_ctx* ctx, float* x, const float* y, const float* gamma, float* out, float eps, uint32_t T, uint32_t h);
 // moe_grouped.cu: the tensor-core GEMM of the batched MoE block used on a dense matrix (see there)
 int32_t dense_tiles_prepare(runit_ctx* ctx, int32_t* tables, uint32_t T);
 int32_t dense_gemm_q4k_bf16(runit_ctx* ctx, const char* name, const void* w, const void* w_up, uint32_t rows, uint32_t K,

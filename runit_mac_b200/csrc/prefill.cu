@@ -106,6 +106,32 @@ __global__ void __launch_bounds__(256) add_rows_kernel(float* __restrict__ x, co
     reinterpret_cast<float4*>(x)[i] = a;
 }
 
+// x[t][:] += y[t][:], then out[t][:] = x[t][:] * rsqrt(mean(x[t]^2) + eps) * gamma: the residual add after the o-projection
+// and the RMSNorm in front of the feed-forward block as one launch, one CTA per token; the norm's arithmetic is
+// rms_norm_kernel's (thread order, shuffle tree, part[0..7] in order), so the bits are those of the two launches.
+__global__ void __launch_bounds__(256) add_rms_norm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
+                                                                 float* __restrict__ out, float eps, uint32_t hidden) {
+    __shared__ float part[8];
+    float* row = x + (size_t)blockIdx.x * hidden;
+    const float* add = y + (size_t)blockIdx.x * hidden;
+    float* o = out + (size_t)blockIdx.x * hidden;
+    float s = 0.f;
+    for (uint32_t i = threadIdx.x; i < hidden; i += 256) {
+        const float v = row[i] + add[i];
+        row[i] = v;
+        s = fmaf(v, v, s);
+    }
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += part[i];
+    const float r = rsqrtf(tot / (float)hidden + eps);
+    for (uint32_t i = threadIdx.x; i < hidden; i += 256) o[i] = row[i] * r * gamma[i];     // each thread re-reads what it stored
+}
+
 // ───────────────────────── causal attention over the f16 cache, tensor cores ─────────────────────────
 // softmax(q.K^T / sqrt(hd)) . V with the causal mask key <= start_pos + query (attention.metal:36-158), online softmax.
 //   grid (heads, ceil(T / 64)), 4 warps; a warp owns 16 queries, the CTA walks the keys in blocks of 64.
@@ -321,6 +347,11 @@ int32_t prefill_attention(runit_ctx* ctx, const float* q, const void* kcache, co
         pf::prefill_attn_kernel<64><<<grid, 128, smem, ctx->stream>>>(q, (const __half*)kcache, (const __half*)vcache, (__nv_bfloat16*)out_bf16, T,
                                                                    heads, kv_heads, max_seq, start_pos, scale);
     return runit_after_launch(ctx, "prefill_attention");
+}
+
+int32_t prefill_add_rms_norm(runit_ctx* ctx, float* x, const float* y, const float* gamma, float* out, float eps, uint32_t T, uint32_t h) {
+    pf::add_rms_norm_rows_kernel<<<T, 256, 0, ctx->stream>>>(x, y, gamma, out, eps, h);
+    return runit_after_launch(ctx, "prefill_add_rms_norm");
 }
 
 int32_t prefill_add_rows(runit_ctx* ctx, float* x, const float* y, size_t n) {
